@@ -1,0 +1,252 @@
+"""ctypes front end of the CPU oracle (``lapid_oracle.c``). TEST INFRASTRUCTURE ONLY.
+
+Only the tests, the smoke check and the benchmark's CPU-baseline legs import this module; the
+shipped package never does. Two builds of the same C source exist:
+
+* the parity copy (``-O2 -ffp-contract=off``, portable ISA), built by ``make -C oracle`` /
+  ``build()`` and shipped next to the source;
+* the timed copy (``-O3 -march=native``), compiled on first use on the machine that runs it
+  (``load(fast=True)``), because ``-march=native`` code must not travel between hosts.
+
+Function names follow the reference's: ``layout``, ``quantize``, ``dequantize``,
+``from_ggml_blocks`` (crates/lapid-quant/src/lib.rs:97-160), ``quantize_row_sums``
+(crates/lapid-cpu/src/matmul/quant.rs:30) and ``matmul`` (crates/lapid-cpu/src/matmul/mod.rs:165).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import hashlib
+import os
+import subprocess
+import tempfile
+from dataclasses import dataclass
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SRC = os.path.join(HERE, "lapid_oracle.c")
+
+# dtype codes shared with crates/lapid-c/src/lib.rs:37-60
+INT8, Q4_K, Q6_K = 4, 6, 8
+FORMATS = {"int8": INT8, "q4_k": Q4_K, "q6_k": Q6_K}
+
+ERRORS = {1: "invalid_launch", 2: "shape_mismatch", 3: "out_of_bounds", 4: "unsupported_dtype"}
+
+
+class OracleError(RuntimeError):
+    def __init__(self, code: str, message: str):
+        super().__init__(f"{code}: {message}")
+        self.code = code
+
+
+class _View(C.Structure):
+    _fields_ = [("offset", C.c_size_t), ("batch_stride", C.c_size_t), ("row_stride", C.c_size_t)]
+
+
+@dataclass(frozen=True)
+class Layout:
+    rows: int
+    cols: int
+    qs_offset: int
+    qs_bytes: int
+    scales_offset: int
+    scales_bytes: int
+    total: int
+
+
+def _compile(out: str, flags: list[str]) -> None:
+    cmd = ["gcc", "-std=c11", *flags, "-ffp-contract=off", "-fno-fast-math", "-fopenmp", "-fPIC", "-shared",
+           "-o", out, SRC, "-lm"]
+    subprocess.run(cmd, check=True, capture_output=True)
+
+
+def build() -> str:
+    """Build the portable parity copy beside the source and return its path."""
+    out = os.path.join(HERE, "liblapid_oracle.so")
+    if not os.path.exists(out) or os.path.getmtime(out) < os.path.getmtime(SRC):
+        _compile(out, ["-O2"])
+    return out
+
+
+def _build_native() -> str:
+    with open(SRC, "rb") as f:
+        tag = hashlib.sha1(f.read()).hexdigest()[:12]
+    try:
+        with open("/proc/cpuinfo") as f:
+            flags = next((l for l in f if l.startswith("flags")), "")
+        tag += hashlib.sha1(flags.encode()).hexdigest()[:8]
+    except OSError:
+        pass
+    out = os.path.join(tempfile.gettempdir(), f"liblapid_oracle_native_{tag}.so")
+    if not os.path.exists(out):
+        tmp = out + f".{os.getpid()}"
+        _compile(tmp, ["-O3", "-march=native"])
+        os.replace(tmp, out)
+    return out
+
+
+class Oracle:
+    def __init__(self, path: str):
+        lib = C.CDLL(path)
+        self.lib = lib
+        self.path = path
+        sz = C.c_size_t
+        lib.lo_f32_to_f16.restype = C.c_uint16
+        lib.lo_f32_to_f16.argtypes = [C.c_float]
+        lib.lo_f16_to_f32.restype = C.c_float
+        lib.lo_f16_to_f32.argtypes = [C.c_uint16]
+        lib.lo_nearest_int.restype = C.c_int
+        lib.lo_nearest_int.argtypes = [C.c_float]
+        lib.lo_layout.argtypes = [C.c_int, sz, sz, C.POINTER(sz)]
+        lib.lo_quantize.argtypes = [C.c_int, C.c_void_p, sz, sz, C.c_void_p]
+        lib.lo_dequantize.argtypes = [C.c_int, C.c_void_p, sz, sz, C.c_void_p]
+        lib.lo_dequantize_row.argtypes = [C.c_int, C.c_void_p, sz, sz, sz, C.c_void_p]
+        lib.lo_from_ggml_blocks.argtypes = [C.c_int, C.c_void_p, sz, sz, sz, C.c_void_p]
+        lib.lo_quantize_row_sums.argtypes = [C.c_void_p, sz, C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.lo_quantize_row_sums.restype = None
+        lib.lo_quantize_q4k_block.argtypes = [C.c_void_p, C.c_void_p]
+        lib.lo_quantize_q6k_block.argtypes = [C.c_void_p, C.c_void_p]
+        lib.lo_dequantize_q4k_block.argtypes = [C.c_void_p, C.c_void_p]
+        lib.lo_dequantize_q6k_block.argtypes = [C.c_void_p, C.c_void_p]
+        lib.lo_matmul.argtypes = [C.c_int, C.c_void_p, sz, _View, C.c_void_p, sz, sz, sz, C.c_void_p, C.c_void_p, sz,
+                                  _View, sz, sz, sz, sz, C.c_int, C.c_int, C.POINTER(C.c_int)]
+        lib.lo_num_threads.restype = C.c_int
+        lib.lo_set_num_threads.argtypes = [C.c_int]
+
+    # ---- scalar helpers
+    def f32_to_f16_bits(self, v: float) -> int:
+        return int(self.lib.lo_f32_to_f16(C.c_float(v)))
+
+    def f16_bits_to_f32(self, h: int) -> float:
+        return float(self.lib.lo_f16_to_f32(C.c_uint16(h)))
+
+    def nearest_int(self, v: float) -> int:
+        return int(self.lib.lo_nearest_int(C.c_float(v)))
+
+    def num_threads(self) -> int:
+        return int(self.lib.lo_num_threads())
+
+    def set_num_threads(self, n: int) -> None:
+        self.lib.lo_set_num_threads(int(n))
+
+    # ---- lapid-quant surface
+    def layout(self, fmt: int, rows: int, cols: int) -> Layout:
+        out = (C.c_size_t * 5)()
+        if self.lib.lo_layout(fmt, rows, cols, out) != 0:
+            raise OracleError("invalid_launch", f"format {fmt}: cols {cols} is not a multiple of the block length")
+        return Layout(rows, cols, *[int(x) for x in out])
+
+    def quantize(self, fmt: int, data: np.ndarray, rows: int, cols: int) -> np.ndarray:
+        data = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
+        if data.size != rows * cols:
+            raise OracleError("shape_mismatch", f"quantize: data has {data.size} elements, expected {rows}x{cols}")
+        l = self.layout(fmt, rows, cols)
+        out = np.empty(l.total, dtype=np.uint8)
+        if self.lib.lo_quantize(fmt, data.ctypes.data, rows, cols, out.ctypes.data) != 0:
+            raise OracleError("invalid_launch", "quantize: bad format or shape")
+        return out
+
+    def dequantize(self, fmt: int, qbytes: np.ndarray, rows: int, cols: int) -> np.ndarray:
+        qbytes = np.ascontiguousarray(qbytes, dtype=np.uint8)
+        l = self.layout(fmt, rows, cols)
+        if qbytes.size < l.scales_offset + l.scales_bytes:
+            raise OracleError("out_of_bounds", f"dequantize: buffer too small ({qbytes.size} < {l.total})")
+        out = np.empty((rows, cols), dtype=np.float32)
+        if self.lib.lo_dequantize(fmt, qbytes.ctypes.data, rows, cols, out.ctypes.data) != 0:
+            raise OracleError("invalid_launch", "dequantize: bad format or shape")
+        return out
+
+    def from_ggml_blocks(self, fmt: int, blocks: np.ndarray, rows: int, cols: int) -> np.ndarray:
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        l = self.layout(fmt, rows, cols)
+        out = np.empty(l.total, dtype=np.uint8)
+        rc = self.lib.lo_from_ggml_blocks(fmt, blocks.ctypes.data, blocks.size, rows, cols, out.ctypes.data)
+        if rc == -2:
+            raise OracleError("shape_mismatch", f"from_ggml_blocks: got {blocks.size} bytes for [{rows}, {cols}]")
+        if rc != 0:
+            raise OracleError("invalid_launch", "from_ggml_blocks: bad format or shape")
+        return out
+
+    def quantize_block(self, fmt: int, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        assert x.size == 256
+        out = np.empty(144 if fmt == Q4_K else 210, dtype=np.uint8)
+        (self.lib.lo_quantize_q4k_block if fmt == Q4_K else self.lib.lo_quantize_q6k_block)(x.ctypes.data, out.ctypes.data)
+        return out
+
+    def dequantize_block(self, fmt: int, b: np.ndarray) -> np.ndarray:
+        b = np.ascontiguousarray(b, dtype=np.uint8)
+        out = np.empty(256, dtype=np.float32)
+        (self.lib.lo_dequantize_q4k_block if fmt == Q4_K else self.lib.lo_dequantize_q6k_block)(b.ctypes.data, out.ctypes.data)
+        return out
+
+    # ---- lapid-cpu surface
+    def quantize_row_sums(self, x: np.ndarray, want_bs: bool = True):
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+        k = x.size
+        assert k % 32 == 0
+        q = np.empty(k, dtype=np.int8)
+        s = np.empty(k // 32, dtype=np.float32)
+        bs = np.empty(k // 32, dtype=np.float32) if want_bs else None
+        self.lib.lo_quantize_row_sums(x.ctypes.data, k, q.ctypes.data, s.ctypes.data, bs.ctypes.data if want_bs else None)
+        return q, s, bs
+
+    def matmul(self, fmt: int, a: np.ndarray, w: np.ndarray, n: int, k: int, *, batch: int = 1, m: int | None = None,
+               a_view: tuple[int, int, int] | None = None, out: np.ndarray | None = None,
+               out_view: tuple[int, int, int] | None = None, bias: np.ndarray | None = None,
+               w_shape: tuple[int, int] | None = None, force_f32_act: bool = False, fma: bool = True):
+        """Run one MatMul launch with a quantized, transposed B. Returns ``(out, path)``; ``path`` is
+        "int8_act" or "f32_act". Views are ``(offset, batch_stride, row_stride)`` in elements."""
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.uint8)
+        flat = a.reshape(-1)
+        if m is None:
+            m = flat.size // (batch * k) if k else 0
+        av = a_view or (0, m * k, k)
+        ov = out_view or (0, m * n, n)
+        if out is None:
+            out = np.zeros(batch * m * n, dtype=np.float32)
+        oflat = out.reshape(-1)
+        assert oflat.flags.c_contiguous and oflat.dtype == np.float32
+        if bias is not None:
+            bias = np.ascontiguousarray(bias, dtype=np.float32)
+        wr, wc = w_shape or (n, k)
+        path = C.c_int(-1)
+        rc = self.lib.lo_matmul(fmt, flat.ctypes.data, flat.size, _View(*av), w.ctypes.data, w.size, wr, wc,
+                                bias.ctypes.data if bias is not None else None, oflat.ctypes.data, oflat.size,
+                                _View(*ov), batch, m, n, k, int(force_f32_act), int(fma), C.byref(path))
+        if rc != 0:
+            raise OracleError(ERRORS.get(rc, "backend"), f"matmul [{batch},{m},{n},{k}] format {fmt}")
+        return out, {0: "int8_act", 1: "f32_act"}.get(path.value, "none")
+
+
+_cache: dict[bool, Oracle] = {}
+
+
+def load(fast: bool = False) -> Oracle:
+    """The parity copy by default; ``fast=True`` compiles and loads the timed ``-march=native`` copy."""
+    if fast not in _cache:
+        _cache[fast] = Oracle(_build_native() if fast else build())
+    return _cache[fast]
+
+
+# ---------------------------------------------------------------------------------------------
+# Seeded synthetic inputs shared by the oracle side and the GPU side of every parity test: a
+# counter-based generator, so any slice can be produced independently and identically anywhere.
+# value(seed, i) = std * sqrt(-2 ln u1) * cos(2 pi u2), with (u1, u2) from splitmix64(seed * 2^40 + i).
+def _splitmix64(x: np.ndarray) -> np.ndarray:
+    x = (x + np.uint64(0x9E3779B97F4A7C15)).astype(np.uint64)
+    x = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    x = (x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    return x ^ (x >> np.uint64(31))
+
+
+def normal(seed: int, n: int, std: float = 1.0, start: int = 0) -> np.ndarray:
+    """``n`` float32 draws of N(0, std) for counters ``start .. start + n``."""
+    with np.errstate(over="ignore"):
+        idx = np.arange(start, start + n, dtype=np.uint64) + (np.uint64(seed) << np.uint64(40))
+        h = _splitmix64(idx)
+    u1 = ((h >> np.uint64(40)).astype(np.float64) + 1.0) / 16777217.0   # (0, 1)
+    u2 = ((h >> np.uint64(16)) & np.uint64(0xFFFFFF)).astype(np.float64) / 16777216.0
+    z = np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)
+    return (z * std).astype(np.float32)

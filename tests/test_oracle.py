@@ -1,0 +1,351 @@
+"""Pins the CPU oracle: every known-answer / property test the reference holds for the
+quantized-matmul path, restated against ``oracle/lapid_oracle.c``, plus independent cross-checks
+(numpy float16 conversion, the third-party ``gguf`` package's dequantizers and Q8_0 quantizer).
+
+Reference tests ported here (file:line within the reference tree):
+  crates/lapid-quant/src/imp.rs:275-389   layout_sizes, i8_test_vector, zero_groups,
+                                          round_trip_error_bounds, k_formats, ggml_blocks_round_trip
+  crates/lapid-quant/src/kquant.rs:419-452 nearest_int_rounds_half_even, round_trip_relative_error,
+                                          zeros_and_constants
+  crates/lapid-cpu/src/kquant.rs:360-386   dequant_matches_ggml, tiles_match_dequant_reference
+  crates/lapid-cpu/src/matmul/qkernels.rs:217-255 simd_tiles_match_scalar (scalar tile vs dequant)
+  crates/lapid-cpu/src/matmul/quant.rs:191-215    quantize_row_roundtrip
+  crates/lapid-cpu/src/matmul/matmul_tests.rs:30-139 quantized_large_m_matches_dequantized_f32,
+                                          kquant_matmul_matches_dequantized_f32
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.refgen import make_blocks, noise, rnd
+
+INT8, Q4_K, Q6_K = O.INT8, O.Q4_K, O.Q6_K
+
+
+def rel_err(got, want):
+    got = np.asarray(got, dtype=np.float64).reshape(-1)
+    want = np.asarray(want, dtype=np.float64).reshape(-1)
+    return float(np.sqrt(((got - want) ** 2).sum() / max((want ** 2).sum(), 1e-30)))
+
+
+# ------------------------------------------------------------------ half conversions
+def test_f16_to_f32_matches_numpy_for_every_half(oracle):
+    allh = np.arange(1 << 16, dtype=np.uint16)
+    want = allh.view(np.float16).astype(np.float32).view(np.uint32)
+    got = np.array([np.float32(oracle.f16_bits_to_f32(int(h))) for h in allh], dtype=np.float32).view(np.uint32)
+    finite = (allh & 0x7C00) != 0x7C00
+    assert np.array_equal(got[finite], want[finite])
+    inf = (allh & 0x7FFF) == 0x7C00
+    assert np.array_equal(got[inf], want[inf])
+
+
+def test_f32_to_f16_round_to_nearest_even(oracle):
+    rng = np.random.default_rng(5)
+    # exact halves, their midpoints and neighbours, subnormals, overflow edge, random values
+    halves = np.arange(1 << 16, dtype=np.uint16).view(np.float16).astype(np.float32)
+    halves = halves[np.isfinite(halves)]
+    mids = (halves[:-1].astype(np.float64) + halves[1:].astype(np.float64)) / 2
+    mids = mids[np.isfinite(mids)].astype(np.float32)
+    cand = np.concatenate([
+        halves[::17], mids[::13], np.nextafter(mids[::29], np.float32(np.inf)), np.nextafter(mids[::31], np.float32(-np.inf)),
+        rng.standard_normal(20000).astype(np.float32) * np.float32(0.02),
+        rng.standard_normal(5000).astype(np.float32) * np.float32(1e-6),
+        np.array([0.0, -0.0, 65504.0, 65519.9, 65520.0, 1e9, -1e9, 2.0 ** -24, 2.0 ** -25, 2.0 ** -25 * 1.0001, 5.96e-8,
+                  16.0 / 127.0, np.inf, -np.inf], dtype=np.float32),
+    ])
+    with np.errstate(over="ignore"):
+        want = cand.astype(np.float16).view(np.uint16)
+    got = np.array([oracle.f32_to_f16_bits(float(v)) for v in cand], dtype=np.uint16)
+    assert np.array_equal(got, want)
+    assert oracle.f32_to_f16_bits(float("nan")) & 0x7C00 == 0x7C00 and oracle.f32_to_f16_bits(float("nan")) & 0x3FF
+
+
+def test_nearest_int_rounds_half_even(oracle):
+    assert [oracle.nearest_int(v) for v in (0.5, 1.5, -0.5, -1.5, 2.4)] == [0, 2, 0, -2, 2]
+
+
+# ------------------------------------------------------------------ lapid-quant: layout and Int8
+def test_layout_sizes(oracle):
+    l = oracle.layout(INT8, 1, 32)
+    assert (l.qs_bytes, l.scales_offset, l.scales_bytes, l.total) == (32, 256, 2, 512)
+    l = oracle.layout(INT8, 768, 768)
+    assert l.scales_offset == 768 * 768 and l.total % 256 == 0
+    for fmt, bb in ((Q4_K, 144), (Q6_K, 210)):
+        l = oracle.layout(fmt, 3, 512)
+        assert (l.qs_offset, l.qs_bytes, l.scales_offset, l.scales_bytes) == (0, 3 * 2 * bb, 3 * 2 * bb, 0)
+        assert l.total == (3 * 2 * bb + 255) // 256 * 256
+    # sizes quoted for the benchmark shapes
+    assert oracle.layout(Q4_K, 4096, 4096).total == 9_437_184
+    assert oracle.layout(Q6_K, 4096, 4096).total == 13_762_560
+    assert oracle.layout(INT8, 4096, 4096).total == 17_825_792
+    assert oracle.layout(Q4_K, 14336, 4096).total == 33_030_144
+    with pytest.raises(O.OracleError):
+        oracle.layout(Q4_K, 2, 128)
+    with pytest.raises(O.OracleError):
+        oracle.layout(INT8, 2, 48)
+
+
+def test_i8_test_vector(oracle):
+    ramp = np.arange(32, dtype=np.float32) - 16.0
+    q = oracle.quantize(INT8, ramp, 1, 32)
+    expect = [-127, -119, -111, -103, -95, -87, -79, -71, -64, -56, -48, -40, -32, -24, -16, -8, 0, 8, 16, 24, 32, 40,
+              48, 56, 64, 71, 79, 87, 95, 103, 111, 119]
+    assert q[:32].view(np.int8).tolist() == expect
+    assert q[256:258].tolist() == [0x08, 0x30]  # f16 bits 0x3008, little endian
+    assert not q[32:256].any() and not q[258:].any()
+    assert q.size == 512
+
+
+def test_zero_groups(oracle):
+    q = oracle.quantize(INT8, np.zeros(64, dtype=np.float32), 2, 32)
+    l = oracle.layout(INT8, 2, 32)
+    assert not q[l.scales_offset:l.scales_offset + l.scales_bytes].any()
+    assert not oracle.dequantize(INT8, q, 2, 32).any()
+
+
+def test_round_trip_error_bounds_int8(oracle):
+    rows, cols = 7, 96
+    x = noise(rows * cols, 42, 3.0)
+    q = oracle.quantize(INT8, x, rows, cols)
+    assert q.size == oracle.layout(INT8, rows, cols).total
+    y = oracle.dequantize(INT8, q, rows, cols).reshape(-1)
+    g = x.reshape(rows, cols // 32, 32)
+    amax = np.abs(g).max(axis=2, keepdims=True)
+    tol = amax / 127.0 * 0.5 + amax * 1e-3 + 1e-6
+    assert (np.abs(g - y.reshape(g.shape)) <= tol).all()
+
+
+def test_k_formats(oracle):
+    rows, cols = 3, 512
+    x = noise(rows * cols, 11, 2.0)
+    for fmt, tol, bb in ((Q4_K, 0.25, 144), (Q6_K, 0.06, 210)):
+        q = oracle.quantize(fmt, x, rows, cols)
+        l = oracle.layout(fmt, rows, cols)
+        assert q.size == l.total and l.qs_bytes == rows * 2 * bb
+        y = oracle.dequantize(fmt, q, rows, cols)
+        assert (np.abs(x - y.reshape(-1)) < tol).all()
+        assert np.array_equal(oracle.from_ggml_blocks(fmt, q[:l.qs_bytes], rows, cols), q)
+        with pytest.raises(O.OracleError):
+            oracle.from_ggml_blocks(fmt, q[:l.qs_bytes - 1], rows, cols)
+
+
+def test_ggml_blocks_round_trip_int8(oracle):
+    rows, cols = 3, 64
+    x = noise(rows * cols, 7, 1.0)
+    ours = oracle.quantize(INT8, x, rows, cols)
+    l = oracle.layout(INT8, rows, cols)
+    ng = rows * cols // 32
+    blocks = np.empty((ng, 34), dtype=np.uint8)
+    blocks[:, :2] = ours[l.scales_offset:l.scales_offset + 2 * ng].reshape(ng, 2)
+    blocks[:, 2:] = ours[:ng * 32].reshape(ng, 32)
+    assert np.array_equal(oracle.from_ggml_blocks(INT8, blocks.reshape(-1), rows, cols), ours)
+
+
+# ------------------------------------------------------------------ lapid-quant: K formats
+def test_round_trip_relative_error(oracle):
+    x = noise(256, 3)
+    x[17] = 4.0
+    rms = np.sqrt((x.astype(np.float64) ** 2).mean())
+    for fmt, tol in ((Q4_K, 0.08), (Q6_K, 0.02)):
+        y = oracle.dequantize_block(fmt, oracle.quantize_block(fmt, x))
+        err = np.sqrt(((x - y).astype(np.float64) ** 2).mean())
+        assert err / rms < tol
+
+
+def test_zeros_and_constants(oracle):
+    for fmt in (Q4_K, Q6_K):
+        for c in (0.0, 1.0, -2.5):
+            b = oracle.quantize_block(fmt, np.full(256, c, dtype=np.float32))
+            y = oracle.dequantize_block(fmt, b)
+            assert (np.abs(y - c) <= abs(c) * 0.01 + 1e-6).all(), (fmt, c)
+            if c == 0.0:
+                assert not b.any()  # kquant.rs:304-307 for Q6_K; scale 0 everywhere for Q4_K
+
+
+gguf = pytest.importorskip("gguf")
+
+
+def _gguf_deq(fmt, blocks):
+    from gguf import quants
+    t = {Q4_K: gguf.GGMLQuantizationType.Q4_K, Q6_K: gguf.GGMLQuantizationType.Q6_K,
+         INT8: gguf.GGMLQuantizationType.Q8_0}[fmt]
+    return quants.dequantize(blocks, t)
+
+
+@pytest.mark.parametrize("fmt,bb,d_off,dm_off", [(Q4_K, 144, 0, 2), (Q6_K, 210, 208, None)])
+def test_dequant_bit_exact_vs_independent_dequantizer(oracle, fmt, bb, d_off, dm_off):
+    """`dequant_matches_ggml`: random valid blocks decode to the same f32 bits as an independent
+    implementation of GGUF's K-quant dequantizers."""
+    blocks = make_blocks(bb, 64, 7, d_off, dm_off)
+    # vary d / dmin across blocks (finite halves of several magnitudes, a negative one, a subnormal)
+    b2 = blocks.reshape(64, bb)
+    ds = np.array([0.01, 0.25, 3e-5, -0.02, 6e-8, 1.5, 0.003, 7.0], dtype=np.float16).view(np.uint8).reshape(8, 2)
+    for i in range(64):
+        b2[i, d_off:d_off + 2] = ds[i % 8]
+        if dm_off is not None:
+            b2[i, dm_off:dm_off + 2] = ds[(i * 3 + 1) % 8]
+    want = _gguf_deq(fmt, b2.copy()).reshape(64, 256).astype(np.float32)
+    got = np.stack([oracle.dequantize_block(fmt, b2[i]) for i in range(64)])
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # and whole-matrix dequantize == per-block
+    full = oracle.dequantize(fmt, np.concatenate([blocks, np.zeros((-blocks.size) % 256, np.uint8)]), 8, 2048)
+    assert np.array_equal(full.reshape(64, 256).view(np.uint32), want.view(np.uint32))
+
+
+def test_quantized_bytes_decode_identically_elsewhere(oracle):
+    """Bytes produced by the oracle's quantizers are valid GGUF blocks: the independent dequantizer
+    reads them to the same values the oracle does (cross-checks packing order and scale packing)."""
+    x = O.normal(3, 16 * 1024, 0.02)
+    for fmt, bb in ((Q4_K, 144), (Q6_K, 210)):
+        q = oracle.quantize(fmt, x, 16, 1024)
+        mine = oracle.dequantize(fmt, q, 16, 1024)
+        other = _gguf_deq(fmt, q[:16 * 4 * bb].reshape(64, bb)).reshape(16, 1024).astype(np.float32)
+        assert np.array_equal(mine.view(np.uint32), other.view(np.uint32))
+        assert rel_err(mine, x) < (0.08 if fmt == Q4_K else 0.02)
+
+
+def test_int8_bytes_match_independent_q8_0_quantizer(oracle):
+    from gguf import quants
+    rows, cols = 5, 256
+    x = O.normal(9, rows * cols, 0.7).reshape(rows, cols)
+    x[2, 40:72] = 0.0
+    want = quants.quantize(x, gguf.GGMLQuantizationType.Q8_0).reshape(-1)  # AoS 34-byte blocks
+    ours = oracle.quantize(INT8, x, rows, cols)
+    assert np.array_equal(oracle.from_ggml_blocks(INT8, want, rows, cols), ours)
+    deq = quants.dequantize(want.reshape(rows, -1), gguf.GGMLQuantizationType.Q8_0).astype(np.float32)
+    assert np.array_equal(oracle.dequantize(INT8, ours, rows, cols).view(np.uint32), deq.reshape(rows, cols).view(np.uint32))
+
+
+# ------------------------------------------------------------------ lapid-cpu: activations, tiles
+def test_quantize_row_roundtrip(oracle):
+    x = np.array([((i * 37) % 29) * 0.37 - 5.0 for i in range(64)], dtype=np.float32)
+    q, s, _ = oracle.quantize_row_sums(x)
+    v = q.astype(np.float32).reshape(2, 32) * s[:, None]
+    assert (np.abs(v - x.reshape(2, 32)) <= s[:, None] * 0.5 + 1e-6).all()
+    x = np.array([((i * 53) % 61) * 0.21 - 6.0 + (0.5 if i % 32 == 5 else 0.0) for i in range(96)], dtype=np.float32)
+    q, s, bs = oracle.quantize_row_sums(x)
+    # numpy restatement: d = amax/127, id = 1/d, round half even, bs = d * sum(q)
+    g = x.reshape(3, 32)
+    d = (np.abs(g).max(axis=1) / np.float32(127.0)).astype(np.float32)
+    idv = (np.float32(1.0) / d).astype(np.float32)
+    qq = np.clip(np.rint((g * idv[:, None]).astype(np.float32)), -127, 127).astype(np.int8)
+    assert np.array_equal(q.reshape(3, 32), qq) and np.array_equal(s, d)
+    assert np.array_equal(bs, d * qq.astype(np.int32).sum(axis=1).astype(np.float32))
+    q, s, bs = oracle.quantize_row_sums(np.zeros(32, dtype=np.float32))
+    assert not q.any() and s[0] == 0.0 and bs[0] == 0.0
+
+
+def test_tiles_match_dequant_reference(oracle):
+    rows, n, k = 5, 6, 512
+    x = np.array([((i * 37 % 101) - 50.0) * 0.013 for i in range(rows * k)], dtype=np.float32).reshape(rows, k)
+    for fmt, bb, d_off, dm_off in ((Q4_K, 144, 0, 2), (Q6_K, 210, 208, None)):
+        raw = make_blocks(bb, n * k // 256, 11, d_off, dm_off)
+        w = np.concatenate([raw, np.zeros((-raw.size) % 256, np.uint8)])
+        deq = oracle.dequantize(fmt, w, n, k)
+        got, path = oracle.matmul(fmt, x, w, n, k, m=rows)
+        assert path == "int8_act"
+        got = got.reshape(rows, n)
+        for r in range(rows):
+            q, s, _ = oracle.quantize_row_sums(x[r])
+            xa = q.astype(np.float32) * np.repeat(s, 32)
+            want = (xa.astype(np.float64)[None, :] * deq.astype(np.float64)).sum(axis=1)
+            assert (np.abs(want - got[r]) <= 1e-3 * np.maximum(np.abs(want), 1.0)).all(), fmt
+
+
+def test_int8_tile_matches_dequant_reference(oracle):
+    rows, n, k = 5, 7, 96
+    l = oracle.layout(INT8, n, k)
+    w = np.zeros(l.total, dtype=np.uint8)
+    for i in range(l.qs_bytes):
+        b = (i * 73 + 11) % 251
+        w[i] = 0x81 if b == 0x80 else b
+    sc = np.array([0.01 + (g % 7) * 0.003 for g in range(n * k // 32)], dtype=np.float32).astype(np.float16)
+    w[l.scales_offset:l.scales_offset + l.scales_bytes] = sc.view(np.uint8)
+    x = O.normal(4, rows * k, 1.0).reshape(rows, k)
+    got, path = oracle.matmul(INT8, x, w, n, k, m=rows)
+    assert path == "int8_act"
+    deq = oracle.dequantize(INT8, w, n, k)
+    for r in range(rows):
+        q, s, _ = oracle.quantize_row_sums(x[r], want_bs=False)
+        xa = q.astype(np.float64) * np.repeat(s, 32)
+        want = (xa[None, :] * deq.astype(np.float64)).sum(axis=1)
+        assert (np.abs(want - got.reshape(rows, n)[r]) <= 1e-3 * np.maximum(np.abs(want), 1.0)).all()
+
+
+# ------------------------------------------------------------------ lapid-cpu: whole launches
+def test_kquant_matmul_matches_dequantized_f32(oracle):
+    seed = 50
+    for fmt in (Q4_K, Q6_K):
+        for (m, n, k, pad) in [(1, 37, 512, 0), (3, 20, 256, 4), (6, 9, 256, 0), (20, 45, 256, 3), (130, 70, 512, 0),
+                               (33, 300, 1024, 0)]:
+            seed += 1
+            w = rnd(n * k, seed)
+            qb = oracle.quantize(fmt, w, n, k)
+            deq = oracle.dequantize(fmt, qb, n, k).astype(np.float64)
+            rs = k + pad
+            a = rnd(m * rs, seed + 7)
+            want = a.reshape(m, rs)[:, :k].astype(np.float64) @ deq.T
+            for fma in (True, False):
+                got, path = oracle.matmul(fmt, a, qb, n, k, m=m, a_view=(0, 0, rs), fma=fma)
+                assert path == ("int8_act" if m <= 8 else "f32_act")
+                tol = 2e-2 if m <= 8 else 2e-5
+                assert rel_err(got, want) <= tol, (fmt, m, n, k)
+
+
+def test_quantized_large_m_matches_dequantized_f32_int8(oracle):
+    seed = 1
+    for (batch, m, n, k, pad, epi) in [(1, 9, 45, 96, 0, False), (2, 35, 70, 128, 5, True), (1, 130, 200, 256, 3, True)]:
+        seed += 1
+        w = rnd(n * k, seed)
+        qb = oracle.quantize(INT8, w, n, k)
+        deq = oracle.dequantize(INT8, qb, n, k).astype(np.float64)
+        rs = k + pad
+        a = rnd(batch * m * rs, seed + 7)
+        bias = rnd(n, seed + 9)
+        want = a.reshape(batch * m, rs)[:, :k].astype(np.float64) @ deq.T + (bias.astype(np.float64) if epi else 0.0)
+        got, path = oracle.matmul(INT8, a, qb, n, k, batch=batch, m=m, a_view=(0, m * rs, rs), bias=bias if epi else None)
+        assert path == "f32_act"
+        assert rel_err(got, want) <= 2e-5
+
+
+def test_strided_output_view_and_validation(oracle):
+    """matmul_strided_output_view (matmul_tests.rs:141-218) for the quantized rows, plus the
+    launch checks of matmul::run (mod.rs:186-247)."""
+    k, n, off, batch = 64, 40, 7, 3
+    for m in (2, 30):
+        a = rnd(batch * m * k, 100 + m)
+        w = rnd(n * k, 101 + m)
+        qb = oracle.quantize(INT8, w, n, k)
+        deq = oracle.dequantize(INT8, qb, n, k).astype(np.float64)
+        total = off + m * batch * n + 5
+        out = np.full(total, -1.0, dtype=np.float32)
+        oracle.matmul(INT8, a, qb, n, k, batch=batch, m=m, out=out, out_view=(off, n, batch * n))
+        want = np.full(total, -1.0)
+        prod = a.reshape(batch, m, k).astype(np.float64) @ deq.T
+        for bt in range(batch):
+            for i in range(m):
+                o = off + bt * n + i * batch * n
+                want[o:o + n] = prod[bt, i]
+        assert rel_err(out[want != -1.0], want[want != -1.0]) <= (2e-2 if batch * m <= 8 else 5e-3)
+        assert (out[want == -1.0] == -1.0).all()
+    qb = oracle.quantize(Q4_K, rnd(4 * 256, 1), 4, 256)
+    a = rnd(2 * 256, 2)
+    with pytest.raises(O.OracleError) as e:
+        oracle.matmul(Q4_K, a, qb, 5, 256, m=2, w_shape=(4, 256))
+    assert e.value.code == "shape_mismatch"
+    with pytest.raises(O.OracleError) as e:
+        oracle.matmul(Q4_K, a, qb, 4, 256, m=2, out=np.zeros(7, np.float32))
+    assert e.value.code == "out_of_bounds"
+    with pytest.raises(O.OracleError) as e:
+        oracle.matmul(Q4_K, a, qb[:500], 4, 256, m=2)
+    assert e.value.code == "out_of_bounds"
+    out, _ = oracle.matmul(Q4_K, np.zeros(0, np.float32), qb, 4, 0, m=2, w_shape=(4, 0))
+    assert out.size == 8 and not out.any()
+
+
+def test_seeded_generator_is_counter_based():
+    a = O.normal(3, 1000, 0.02)
+    b = O.normal(3, 400, 0.02, start=600)
+    assert np.array_equal(a[600:], b)
+    assert abs(float(a.std()) - 0.02) < 0.002 and abs(float(a.mean())) < 0.003
+    assert not np.array_equal(O.normal(4, 1000, 0.02), a)
