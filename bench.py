@@ -1,0 +1,442 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path on B200, one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (``config.workload = "decode_gemv_sweep"``): the decode GEMV sweep over
+Llama-3-8B-shaped projections -- (N x K) in {4096x4096, 1024x4096, 14336x4096, 4096x14336},
+batch M in {1, 2, 4, 8}, Q4_K weights -- 16 launches per step, each over its own weight copy
+(311 MB of weights per step, 2.5x the L2, so every launch streams from HBM). Inputs are synthetic:
+weights N(0, 0.02) quantized on the device by the library's own quantizer, activations N(0, 1).
+
+  value        GB/s of algorithmic bytes (weights + 4MK + 4MN per GEMV) with everything resident
+               in HBM; the step is one CUDA-graph replay of the 16 launches
+  e2e          the same bytes through the C-ABI `execute` call with host buffers: one `write` of
+               the activations from pinned memory, one `execute` (16 launches, waits), one
+               `download` of the outputs -- per step, inside the timed region
+  roofline     for the GEMV kernel: algorithmic bytes per launch / mean launch time, against the
+               measured HBM copy bandwidth
+  cpu_baseline the oracle's restatement of lapid-cpu's path, timed on this host's cores
+  cases        per (format, shape, M) GB/s, each timed alone over cold weight copies
+
+``--impl reference`` times the CPU restatement of lapid-cpu's path (the reference itself is Rust
+and cannot be built where no Rust toolchain exists) on the same workload.
+With --gpus N (torchrun, one rank per GPU) every rank streams its own copy of the sweep (the
+column-parallel case: independent weight shards, no collective) -> weak scaling.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [(4096, 4096, "q/o"), (1024, 4096, "k/v"), (14336, 4096, "gate/up"), (4096, 14336, "down")]
+MS = [1, 2, 4, 8]
+FMT_NAMES = {4: "int8", 6: "q4_k", 8: "q6_k"}
+
+
+def weight_bytes(fmt: int, n: int, k: int) -> int:
+    if fmt == 6:
+        b = n * k // 256 * 144
+    elif fmt == 8:
+        b = n * k // 256 * 210
+    else:
+        b = (n * k + 255) // 256 * 256 + n * k // 32 * 2
+    return (b + 255) // 256 * 256
+
+
+def algo_bytes(fmt: int, m: int, n: int, k: int) -> int:
+    return weight_bytes(fmt, n, k) + 4 * m * k + 4 * m * n
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples = []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                self.samples.append((mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def start(self):
+        if self.nv:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._t:
+            self._t.join()
+
+    def summary(self):
+        if not self.nv or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        seen = set()
+        for _, r in self.samples:
+            for n, bit in names.items():
+                if r & bit:
+                    seen.add(n)
+        mhz = sorted(s[0] for s in self.samples)
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(seen), "samples": len(mhz)}
+
+
+# ---------------------------------------------------------------------------------------------
+def run_reference(args, rank: int, world: int):
+    """CPU arm: the oracle's restatement of lapid-cpu's decode path on the same 16 GEMVs."""
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    o = O.load(fast=True)
+    cores = o.num_threads()
+    fmt = 6
+    rng = np.random.default_rng(0)
+    ws, xs = {}, {}
+    for (n, k, _) in SHAPES:
+        w = (rng.standard_normal(n * k, dtype=np.float32) * np.float32(0.02))
+        ws[(n, k)] = o.quantize(fmt, w, n, k)
+    for m in MS:
+        for kk in (4096, 14336):
+            xs[(m, kk)] = rng.standard_normal(m * kk, dtype=np.float32)
+    cases = [(m, n, k) for (n, k, _) in SHAPES for m in MS]
+    step_bytes = sum(algo_bytes(fmt, m, n, k) for (m, n, k) in cases)
+
+    def step():
+        for (m, n, k) in cases:
+            o.matmul(fmt, xs[(m, k)], ws[(n, k)], n, k, m=m)
+
+    for _ in range(max(1, min(args.warmup, 3))):
+        step()
+    steps = max(1, args.steps)
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        step()
+        done += 1
+        if time.perf_counter() - t0 > 120.0:  # keep the arm within minutes on slow hosts
+            break
+    dt = (time.perf_counter() - t0) / done
+    val = step_bytes / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "q4k_decode_gemv_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": done, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 x q4_k -> f32", "data": "synthetic",
+        "config": {"workload": "decode_gemv_sweep", "format": "q4_k", "shapes": [[n, k] for (n, k, _) in SHAPES],
+                   "batch_m": MS, "launches_per_step": len(cases)},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{done} full steps of the 16-GEMV sweep (weights stay in host memory/LLC)"},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "C restatement of lapid-cpu's int8-activation decode path (the Rust reference cannot be built here); "
+                "gcc -O3 -march=native, OpenMP over output columns",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+    import lapid_b200 as lp
+    from lapid_b200.backend import MatView, matmul_launch
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    be = lp.Backend(local_rank)
+    if os.environ.get("LAPID_B200_PDL") is not None:
+        be.set_option("pdl", os.environ["LAPID_B200_PDL"])
+    stream = torch.cuda.Stream(device=dev)
+    be.set_stream(stream.cuda_stream)
+    peak, peak_kind = measured_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def quantized(fmt, n, k, seed):
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed)
+        w = torch.randn(n * k, device=dev, generator=g) * 0.02
+        out = torch.empty(weight_bytes(fmt, n, k), dtype=torch.uint8, device=dev)
+        torch.cuda.synchronize()
+        be.quantize_into(fmt, be.wrap_tensor(w), n, k, be.wrap_tensor(out))
+        return out
+
+    fmt = 6
+    cases = [(m, n, k) for (n, k, _) in SHAPES for m in MS]
+    base = {(n, k): quantized(fmt, n, k, 100 + i) for i, (n, k, _) in enumerate(SHAPES)}
+    # one distinct weight copy per launch; packed activations and outputs
+    a_off, o_off, ao, oo = [], [], 0, 0
+    for (m, n, k) in cases:
+        a_off.append(ao)
+        o_off.append(oo)
+        ao += m * k
+        oo += m * n
+    g = torch.Generator(device=dev)
+    g.manual_seed(200)
+    acts = torch.randn(ao, device=dev, generator=g)
+    outs = torch.zeros(oo, device=dev)
+    wcopies = [base[(n, k)].clone() for (m, n, k) in cases]
+    torch.cuda.synchronize()
+    bufs = [be.wrap_tensor(acts), be.wrap_tensor(outs)] + [be.wrap_tensor(w) for w in wcopies]
+    launches = []
+    for i, (m, n, k) in enumerate(cases):
+        l = matmul_launch(fmt, m, n, k, inputs=(0, 2 + i), output=1, out=MatView(o_off[i], m * n, n))
+        import dataclasses as dc
+        l = dc.replace(l, dims=dc.replace(l.dims, a=MatView(a_off[i], m * k, k)))
+        launches.append(l)
+    be.prepare(launches)
+    step_bytes = sum(algo_bytes(fmt, m, n, k) for (m, n, k) in cases)
+    run = be.packed(launches, bufs)
+
+    # ---- device-resident timing: one CUDA graph replay per step
+    be.take_launch_count()
+    with torch.cuda.stream(stream):
+        run()
+    stream.synchronize()
+    launches_per_step = be.take_launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        be.set_stream(torch.cuda.current_stream().cuda_stream)
+        run()
+    be.set_stream(stream.cuda_stream)
+    be.take_launch_count()
+
+    sampler = ClockSampler(local_rank)
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        stream.synchronize()
+        barrier()
+        sampler.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        ev1.record(stream)
+        stream.synchronize()
+        ms_total = ev0.elapsed_time(ev1)
+        # keep the same load running briefly so the clock sampler sees the GPU under this load
+        t_end = time.perf_counter() + 0.4
+        while time.perf_counter() < t_end:
+            for _ in range(50):
+                graph.replay()
+            stream.synchronize()
+        sampler.stop()
+    barrier()
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = world * step_bytes / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end through the C ABI with host buffers
+    be.set_stream(0)  # the device's own stream: execute() waits on it
+    h_acts = torch.randn(ao).pin_memory()
+    h_out = torch.empty(oo).pin_memory()
+    e2e_bufs = [be.alloc(ao * 4), be.alloc(oo * 4)] + bufs[2:]
+    arr, cb = be._pack(launches, e2e_bufs)
+    from lapid_b200 import _lib
+    lib = _lib.lib()
+
+    def e2e_step():
+        be.write_ptr(e2e_bufs[0], 0, h_acts.data_ptr(), ao * 4)
+        _lib.check(lib.lapid_b200_execute(be._h, arr, len(launches), cb, len(e2e_bufs)))
+        be.download_ptr(e2e_bufs[1], h_out.data_ptr(), oo * 4)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e_steps = max(args.steps, 1)
+    t0 = time.perf_counter()
+    for _ in range(e_steps):
+        e2e_step()
+    e2e_s = (time.perf_counter() - t0) / e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_val = world * step_bytes / e2e_s / 1e9
+    # the e2e outputs must be the resident path's outputs for the same activations
+    be.set_stream(stream.cuda_stream)
+
+    if rank != 0:
+        return
+
+    # ---- per-case timing over cold copies (rank 0, N = 1 only): the kbench method scaled to B200's L2
+    case_rows = []
+    roof = None
+    if world == 1 and not args.no_cases:
+        POOL = 512 << 20
+        for f in (6, 8, 4):
+            for si, (n, k, tag) in enumerate(SHAPES):
+                wq = base[(n, k)] if f == 6 else quantized(f, n, k, 300 + si)
+                wb = wq.numel()
+                copies = max(2, min(256, -(-POOL // wb)))
+                pool = wq.repeat(copies).view(copies, wb)
+                for m in MS:
+                    a = torch.randn(m * k, device=dev)
+                    o = torch.zeros(m * n, device=dev)
+                    torch.cuda.synchronize()
+                    cb_ = [be.wrap_tensor(a), be.wrap_tensor(o)] + [be.wrap_tensor(pool[c]) for c in range(copies)]
+                    ls = [matmul_launch(f, m, n, k, inputs=(0, 2 + c), output=1) for c in range(copies)]
+                    be.prepare(ls)
+                    rn = be.packed(ls[:1], cb_)
+                    with torch.cuda.stream(stream):
+                        rn()  # first use of a kernel variant sets its attributes: keep that out of the capture
+                    stream.synchronize()
+                    rn = be.packed(ls, cb_)
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr, stream=stream):
+                        be.set_stream(torch.cuda.current_stream().cuda_stream)
+                        rn()
+                    be.set_stream(stream.cuda_stream)
+                    with torch.cuda.stream(stream):
+                        for _ in range(3):
+                            gr.replay()
+                        times = []
+                        for _ in range(7):
+                            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                            e0.record(stream)
+                            gr.replay()
+                            e1.record(stream)
+                            stream.synchronize()
+                            times.append(e0.elapsed_time(e1) / copies)
+                    times.sort()
+                    us = times[len(times) // 2] * 1e3
+                    gbs = algo_bytes(f, m, n, k) / (us * 1e-6) / 1e9
+                    case_rows.append({"fmt": FMT_NAMES[f], "n": n, "k": k, "m": m, "us": round(us, 3),
+                                      "gbs": round(gbs, 1), "frac": round(gbs / peak, 4)})
+                    del gr, rn, cb_, ls
+                del pool
+                torch.cuda.empty_cache()
+        q4 = [r for r in case_rows if r["fmt"] == "q4_k"]
+        tot_b = sum(algo_bytes(6, r["m"], r["n"], r["k"]) for r in q4)
+        tot_t = sum(r["us"] for r in q4) * 1e-6
+        roof = tot_b / tot_t / 1e9
+
+    achieved = roof if roof is not None else value / world
+    line = {
+        "metric": "q4k_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 x q4_k -> f32", "data": "synthetic",
+        "config": {"workload": "decode_gemv_sweep", "format": "q4_k", "shapes": [[n, k] for (n, k, _) in SHAPES],
+                   "batch_m": MS, "launches_per_step": len(cases), "weight_bytes_per_step": sum(w.numel() for w in wcopies),
+                   "l2": "every launch has its own weight copy; 311 MB per step > 126 MB L2", "cuda_graph": True,
+                   "parallelism": f"replicas x{world} (column-parallel shards, no collective)" if world > 1 else "single"},
+        "clocks": sampler.summary(),
+        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": ao * 4, "d2h_bytes_per_step": oo * 4,
+                "ms_per_step": e2e_s * 1e3, "calls_per_step": "write + execute(16 launches, waits) + download"},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind,
+                     "what": "Q4_K GEMV launches (act-quant pre-pass + GEMV), algorithmic bytes / mean launch time"},
+    }
+    if case_rows:
+        line["cases"] = case_rows
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(cases, fmt)
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline(cases, fmt):
+    """The oracle's timed copy on this host's cores over one full step of the same sweep."""
+    from oracle import oracle as O
+    o = O.load(fast=True)
+    rng = np.random.default_rng(0)
+    ws = {}
+    for (n, k, _) in SHAPES:
+        ws[(n, k)] = o.quantize(fmt, rng.standard_normal(n * k, dtype=np.float32) * np.float32(0.02), n, k)
+    xs = {(m, kk): rng.standard_normal(m * kk, dtype=np.float32) for m in MS for kk in (4096, 14336)}
+    step_bytes = sum(algo_bytes(fmt, m, n, k) for (m, n, k) in cases)
+
+    def step():
+        for (m, n, k) in cases:
+            o.matmul(fmt, xs[(m, k)], ws[(n, k)], n, k, m=m)
+
+    step()
+    t0 = time.perf_counter()
+    done = 0
+    while done < 3 or (time.perf_counter() - t0 < 10.0 and done < 50):
+        step()
+        done += 1
+        if time.perf_counter() - t0 > 30.0:
+            break
+    dt = (time.perf_counter() - t0) / done
+    return {"value": step_bytes / dt / 1e9, "unit": "GB/s", "cores": o.num_threads(), "kind": "port",
+            "sample": f"{done} full steps of the 16-GEMV Q4_K sweep, {dt * 1e3:.1f} ms per step"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cases", action="store_true", help="skip the per-case breakdown")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

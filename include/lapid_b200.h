@@ -1,0 +1,191 @@
+/*
+ * lapid_b200.h -- C ABI of the B200 (sm_100a) backend for lapid's quantized matmul path.
+ *
+ * The library is a sibling of lapid-cuda: it implements the part of lapid's backend operator
+ * surface that a `Kernel::MatMul` launch with a quantized, transposed B needs
+ * (`lapid_compiler::Backend`, crates/lapid-compiler/src/backend.rs:8-63, and the MatMul launch
+ * types of crates/lapid-compiler/src/ir.rs:226-282, :483-488), plus the lapid-quant byte-format
+ * functions (crates/lapid-quant/src/lib.rs:97-160), behind plain C types so that a Rust
+ * `impl Backend` can bind it with `extern "C"`.
+ *
+ * Conventions follow lapid-c (crates/lapid-c/src/error.rs:16-97, src/handle.rs:28-50):
+ *  - every fallible function returns an int32 status, 0 = LAPID_B200_OK;
+ *  - details of the last failure on the calling thread are a JSON object
+ *    {"status": n, "error": "<lapid error code>", "message": "..."} from lapid_b200_last_error();
+ *  - out-parameters come last and are untouched on failure;
+ *  - handles are opaque and reference counted; *_retain / *_free accept NULL;
+ *  - no exception or abort crosses the boundary; all functions are thread-safe. Launches on one
+ *    device are serialised on that device's stream, as lapid-cuda does
+ *    (crates/lapid-cuda/src/lib.rs:155-159).
+ *
+ * There is no CPU fallback: without a CUDA device every device function fails with
+ * LAPID_B200_ERR_DEVICE_UNAVAILABLE.
+ */
+#ifndef LAPID_B200_H
+#define LAPID_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define LAPID_B200_API __attribute__((visibility("default")))
+#else
+#define LAPID_B200_API
+#endif
+
+#define LAPID_B200_ABI_VERSION 1u
+
+/* Status codes: the values of lapid-c's LAPID_ERR_* (crates/lapid-c/src/error.rs:16-36). */
+typedef int32_t lapid_b200_status;
+#define LAPID_B200_OK 0
+#define LAPID_B200_ERR_INVALID_ARGUMENT 1
+#define LAPID_B200_ERR_SHAPE_MISMATCH 2
+#define LAPID_B200_ERR_UNSUPPORTED_DTYPE 3
+#define LAPID_B200_ERR_NOT_FOUND 4
+#define LAPID_B200_ERR_DEVICE_UNAVAILABLE 7
+#define LAPID_B200_ERR_BACKEND 8          /* "cuda", "invalid_launch", "bad_launch" */
+#define LAPID_B200_ERR_OUT_OF_MEMORY 9    /* "out_of_memory", "too_large" */
+#define LAPID_B200_ERR_INDEX_OUT_OF_RANGE 10 /* "out_of_bounds", "index_out_of_range" */
+#define LAPID_B200_ERR_ABI_MISMATCH 11
+#define LAPID_B200_ERR_INTERNAL 13
+
+/* Element type codes: lapid-c's LAPID_DTYPE_* (crates/lapid-c/src/lib.rs:37-60). INT8 is
+ * lapid's plane layout of GGUF Q8_0 (crates/lapid-quant/src/lib.rs:5-17). */
+#define LAPID_B200_DTYPE_F32 0
+#define LAPID_B200_DTYPE_F16 1
+#define LAPID_B200_DTYPE_BF16 2
+#define LAPID_B200_DTYPE_I32 3
+#define LAPID_B200_DTYPE_INT8 4
+#define LAPID_B200_DTYPE_Q4_K 6
+#define LAPID_B200_DTYPE_Q6_K 8
+
+typedef struct lapid_b200_device lapid_b200_device;
+typedef struct lapid_b200_buffer lapid_b200_buffer;
+
+/* ---- library ------------------------------------------------------------------------- */
+/* lapid_abi_version / lapid_check_abi (crates/lapid-c/src/lib.rs:110-125). */
+LAPID_B200_API uint32_t lapid_b200_abi_version(void);
+LAPID_B200_API lapid_b200_status lapid_b200_check_abi(uint32_t expected);
+/* lapid_last_error (crates/lapid-c/src/error.rs:104-118): JSON of the calling thread's last
+ * failure, valid until the next failing call on this thread; NULL when there was none. */
+LAPID_B200_API const char *lapid_b200_last_error(void);
+
+/* ---- device (Backend::name / device_name; `Device::cuda`, crates/lapid/src/device.rs) ---- */
+/* Opens CUDA device `ordinal` (it must be compute capability 10.x) with its own stream. */
+LAPID_B200_API lapid_b200_status lapid_b200_device_open(int32_t ordinal, lapid_b200_device **out);
+LAPID_B200_API void lapid_b200_device_retain(lapid_b200_device *dev);
+LAPID_B200_API void lapid_b200_device_free(lapid_b200_device *dev);
+/* Backend::device_name: writes a NUL-terminated name, truncated to `cap` bytes. */
+LAPID_B200_API lapid_b200_status lapid_b200_device_name(const lapid_b200_device *dev, char *out, size_t cap);
+/* Makes later launches and copies of this device use `cuda_stream` (a cudaStream_t, e.g. the
+ * stream of a framework that owns the surrounding work); NULL restores the device's own stream.
+ * No counterpart in the reference, whose CUDA backend owns its single stream
+ * (crates/lapid-cuda/src/execute.rs:1-3). */
+LAPID_B200_API lapid_b200_status lapid_b200_device_set_stream(lapid_b200_device *dev, void *cuda_stream);
+/* Waits for everything queued on the device's stream. */
+LAPID_B200_API lapid_b200_status lapid_b200_device_synchronize(lapid_b200_device *dev);
+/* Options, the counterpart of the reference's environment switches
+ * (crates/lapid-cpu/src/matmul/mod.rs:52-57, crates/lapid-cuda/src/lib.rs:13-23):
+ *   "gemv_max_rows" = "0".."8" (default 8, the reference's SMALL_M, crates/lapid-cpu/src/matmul/mod.rs:45):
+ *                     launches with batch*m above it take the GEMM path;
+ *   "gemm"          = "f32": GEMM rows use the exact-f32 kernel (lapid-cpu's qdeq numerics);
+ *   "pdl"           = "1" (default) | "0": programmatic dependent launch between the kernels of
+ *                     a launch sequence (weights are staged while the producer still runs). */
+LAPID_B200_API lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const char *key, const char *value);
+
+/* ---- buffers (Backend::alloc / upload / write / download, backend.rs:17-50) ------------- */
+LAPID_B200_API lapid_b200_status lapid_b200_alloc(lapid_b200_device *dev, size_t bytes, lapid_b200_buffer **out);
+LAPID_B200_API lapid_b200_status lapid_b200_upload(lapid_b200_device *dev, const void *host, size_t bytes, lapid_b200_buffer **out);
+/* A buffer over device memory the caller owns (16-byte aligned, alive until the handle is
+ * freed); the library never frees it. Counterpart of `map_host`'s "view without copying"
+ * (backend.rs:21-26) for memory that is already on the device. */
+LAPID_B200_API lapid_b200_status lapid_b200_wrap(lapid_b200_device *dev, void *device_ptr, size_t bytes, lapid_b200_buffer **out);
+/* Overwrites bytes [offset, offset + bytes) from host memory; ordered before later launches. */
+LAPID_B200_API lapid_b200_status lapid_b200_write(lapid_b200_buffer *buf, size_t offset, const void *host, size_t bytes);
+/* Copies the first `bytes` bytes back to host memory after waiting for pending work. */
+LAPID_B200_API lapid_b200_status lapid_b200_download(lapid_b200_buffer *buf, void *host, size_t bytes);
+LAPID_B200_API void lapid_b200_buffer_retain(lapid_b200_buffer *buf);
+LAPID_B200_API void lapid_b200_buffer_free(lapid_b200_buffer *buf);
+LAPID_B200_API size_t lapid_b200_buffer_size(const lapid_b200_buffer *buf);
+LAPID_B200_API void *lapid_b200_buffer_device_ptr(const lapid_b200_buffer *buf);
+
+/* ---- launches (Kernel::MatMul, ir.rs:226-282; Launch, ir.rs:483-488) ---------------------- */
+/* MatView (ir.rs:249-254): offsets and strides in ELEMENTS. */
+typedef struct lapid_b200_matview {
+    uint64_t offset, batch_stride, row_stride;
+} lapid_b200_matview;
+
+/* View of an epilogue extra over the rank-3 space [batch, m, n] (ir.rs `View`): element
+ * (bt, i, j) at offset + bt*strides[0] + i*strides[1] + j*strides[2]; a bias over n is {0,0,1}. */
+typedef struct lapid_b200_view3 {
+    uint64_t offset;
+    int64_t strides[3];
+} lapid_b200_view3;
+
+#define LAPID_B200_KERNEL_MATMUL 2 /* position of MatMul in `enum Kernel`, ir.rs:395-414 */
+
+/* Fused epilogues (MatMulSpec.epilogue, ir.rs:234-247). The reference accepts any expression;
+ * this backend accepts the two shapes lapid's lowering emits for projections
+ * (crates/lapid-compiler/src/lower/emit.rs:199-262): none, and `Load(0) + Load(1)`. */
+#define LAPID_B200_EPILOGUE_NONE 0
+#define LAPID_B200_EPILOGUE_ADD 1
+
+typedef struct lapid_b200_launch {
+    int32_t kind;         /* LAPID_B200_KERNEL_MATMUL */
+    int32_t a_dtype;      /* MatMulSpec.a_dtype: F32 */
+    int32_t b_dtype;      /* MatMulSpec.b_dtype: INT8 | Q4_K | Q6_K */
+    int32_t out_dtype;    /* MatMulSpec.out_dtype: F32 */
+    int32_t b_transposed; /* must be 1 for a quantized B */
+    int32_t epilogue;     /* LAPID_B200_EPILOGUE_* */
+    int32_t extra_dtype;  /* dtype of extras[0] when epilogue == ADD: F32 */
+    int32_t n_inputs;     /* 2, or 3 with an extra */
+    uint64_t batch, m, n, k;         /* MatMulDims */
+    lapid_b200_matview a, b, out;    /* b: offset 0, batch_stride 0 (quantized B, ir.rs:232-233) */
+    lapid_b200_view3 extra;          /* MatMulDims.extra_views[0] */
+    uint32_t inputs[3];   /* BufIds: a, b, extras[0] -- indices into `buffers` of execute */
+    uint32_t output;      /* BufId of the output */
+} lapid_b200_launch;
+
+/* Backend::prepare (backend.rs:51-54): validates the launches and sizes the device's scratch so
+ * that `execute` allocates nothing afterwards. Optional; execute also works cold. */
+LAPID_B200_API lapid_b200_status lapid_b200_prepare(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n_launches);
+/* Backend::execute (backend.rs:55-58): runs the launches in order and waits; launch k+1 sees
+ * all writes of launch k; `buffers[id]` is the buffer of BufId `id` (ids may alias). */
+LAPID_B200_API lapid_b200_status lapid_b200_execute(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n_launches,
+                                     lapid_b200_buffer *const *buffers, size_t n_buffers);
+/* Same, but returns once the work is queued on the device's stream (for callers that run a whole
+ * token in one stream or capture it in a CUDA graph). Call prepare first when capturing. No
+ * counterpart in the reference, whose execute always waits. */
+LAPID_B200_API lapid_b200_status lapid_b200_execute_async(lapid_b200_device *dev, const lapid_b200_launch *launches,
+                                           size_t n_launches, lapid_b200_buffer *const *buffers, size_t n_buffers);
+/* Backend::take_profile (backend.rs:59-62) restricted to this path: number of kernels this
+ * library launched on `dev` since the last call. */
+LAPID_B200_API uint64_t lapid_b200_take_launch_count(lapid_b200_device *dev);
+
+/* ---- lapid-quant surface (crates/lapid-quant/src/lib.rs:84-160) ---------------------------- */
+typedef struct lapid_b200_layout {
+    uint64_t rows, cols, qs_offset, qs_bytes, scales_offset, scales_bytes, total;
+} lapid_b200_layout;
+/* `layout(format, rows, cols)` (lib.rs:97-125). Host only; needs no device. */
+LAPID_B200_API lapid_b200_status lapid_b200_quant_layout(int32_t format, uint64_t rows, uint64_t cols, lapid_b200_layout *out);
+/* `dequantize` (lib.rs:136-139) on the device: src holds a quantized [rows, cols] matrix, dst
+ * receives rows*cols f32, bit-identical to lapid-quant's values. */
+LAPID_B200_API lapid_b200_status lapid_b200_dequantize(lapid_b200_device *dev, int32_t format, const lapid_b200_buffer *src,
+                                        uint64_t rows, uint64_t cols, lapid_b200_buffer *dst);
+/* `quantize` (lib.rs:131-133) on the device: src holds rows*cols f32, dst receives layout.total
+ * bytes, byte-identical to lapid-quant's output (padding zeroed). */
+LAPID_B200_API lapid_b200_status lapid_b200_quantize(lapid_b200_device *dev, int32_t format, const lapid_b200_buffer *src,
+                                      uint64_t rows, uint64_t cols, lapid_b200_buffer *dst);
+/* `from_ggml_blocks` (lib.rs:147-149): GGUF blocks (`src_bytes` of them in src) -> lapid layout. */
+LAPID_B200_API lapid_b200_status lapid_b200_from_ggml_blocks(lapid_b200_device *dev, int32_t format, const lapid_b200_buffer *src,
+                                              uint64_t src_bytes, uint64_t rows, uint64_t cols,
+                                              lapid_b200_buffer *dst);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LAPID_B200_H */

@@ -1,0 +1,282 @@
+"""Python mirror of the reference's backend interface for the quantized-matmul path.
+
+Names and argument meanings follow ``lapid_compiler`` (crates/lapid-compiler/src/backend.rs:8-63,
+crates/lapid-compiler/src/ir.rs:226-282, :483-488); every method is a thin call into the C ABI.
+Errors are :class:`lapid_b200.LapidError` carrying the reference's error codes ("invalid_launch",
+"shape_mismatch", "out_of_bounds", "buffer_aliasing", "unsupported_dtype", ...).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import check
+
+
+class DType(enum.IntEnum):
+    """crates/lapid-tensor/src/dtype.rs:15-55, numbered as lapid-c does (crates/lapid-c/src/lib.rs:37-60)."""
+    F32 = 0
+    F16 = 1
+    BF16 = 2
+    I32 = 3
+    Int8 = 4
+    Q4K = 6
+    Q6K = 8
+
+
+class Epilogue(enum.IntEnum):
+    """The two epilogue shapes this backend accepts: none, and ``Load(0) + Load(1)``."""
+    NONE = 0
+    ADD = 1
+
+
+@dataclass(frozen=True)
+class MatView:
+    """ir.rs:249-261 -- element offsets and strides."""
+    offset: int = 0
+    batch_stride: int = 0
+    row_stride: int = 0
+
+    @staticmethod
+    def contiguous(rows: int, cols: int) -> "MatView":
+        return MatView(0, rows * cols, cols)
+
+
+@dataclass(frozen=True)
+class View:
+    """View of an epilogue extra over [batch, m, n]."""
+    offset: int = 0
+    strides: tuple = (0, 0, 1)
+
+
+@dataclass(frozen=True)
+class MatMulSpec:
+    """ir.rs:239-247. ``epilogue`` is an :class:`Epilogue` instead of an expression tree."""
+    a_dtype: DType = DType.F32
+    b_dtype: DType = DType.Q4K
+    b_transposed: bool = True
+    extra_dtypes: tuple = ()
+    out_dtype: DType = DType.F32
+    epilogue: Epilogue = Epilogue.NONE
+
+
+@dataclass(frozen=True)
+class MatMulDims:
+    """ir.rs:263-274."""
+    batch: int
+    m: int
+    n: int
+    k: int
+    a: MatView
+    b: MatView
+    out: MatView
+    extra_views: tuple = ()
+
+
+@dataclass(frozen=True)
+class Launch:
+    """ir.rs:483-488 with ``kernel = Kernel::MatMul(spec, dims)``; inputs/output are BufIds."""
+    spec: MatMulSpec
+    dims: MatMulDims
+    inputs: tuple
+    output: int
+    kind: int = 2  # LAPID_B200_KERNEL_MATMUL
+
+    def to_c(self) -> _lib.LaunchC:
+        s, d = self.spec, self.dims
+        c = _lib.LaunchC()
+        c.kind = self.kind
+        c.a_dtype, c.b_dtype, c.out_dtype = int(s.a_dtype), int(s.b_dtype), int(s.out_dtype)
+        c.b_transposed = int(bool(s.b_transposed))
+        c.epilogue = int(s.epilogue)
+        c.extra_dtype = int(s.extra_dtypes[0]) if s.extra_dtypes else 0
+        c.n_inputs = len(self.inputs)
+        c.batch, c.m, c.n, c.k = d.batch, d.m, d.n, d.k
+        for name, v in (("a", d.a), ("b", d.b), ("out", d.out)):
+            mv = getattr(c, name)
+            mv.offset, mv.batch_stride, mv.row_stride = v.offset, v.batch_stride, v.row_stride
+        if d.extra_views:
+            ev = d.extra_views[0]
+            c.extra.offset = ev.offset
+            for i in range(3):
+                c.extra.strides[i] = ev.strides[i]
+        if len(self.inputs) > 3:
+            raise _lib.LapidError(8, "invalid_launch", f"expected at most 3 inputs, got {len(self.inputs)}")
+        for i, b in enumerate(self.inputs):
+            c.inputs[i] = b
+        c.output = self.output
+        return c
+
+
+def matmul_launch(b_dtype: DType, m: int, n: int, k: int, *, batch: int = 1, a_row_stride: Optional[int] = None,
+                  inputs=(0, 1), output=2, bias_input: Optional[int] = None, out: Optional[MatView] = None) -> Launch:
+    """The launch lapid lowers ``x.matmul_t(w)`` to: contiguous A (or padded rows), quantized
+    transposed B, contiguous f32 output (the `mm` helper of kbench_tests.rs:86-107)."""
+    rs = a_row_stride if a_row_stride is not None else k
+    spec = MatMulSpec(b_dtype=DType(b_dtype), extra_dtypes=(DType.F32,) if bias_input is not None else (),
+                      epilogue=Epilogue.ADD if bias_input is not None else Epilogue.NONE)
+    dims = MatMulDims(batch, m, n, k, a=MatView(0, m * rs, rs), b=MatView(0, 0, k), out=out or MatView.contiguous(m, n),
+                      extra_views=(View(0, (0, 0, 1)),) if bias_input is not None else ())
+    ins = tuple(inputs) + ((bias_input,) if bias_input is not None else ())
+    return Launch(spec, dims, ins, output)
+
+
+class Buffer:
+    """``DeviceData``: a reference-counted device buffer handle."""
+
+    def __init__(self, backend: "Backend", handle: int, keep=None):
+        self.backend = backend
+        self._h = C.c_void_p(handle)
+        self._keep = keep  # whatever owns wrapped memory (e.g. a torch tensor)
+
+    @property
+    def nbytes(self) -> int:
+        return int(_lib.lib().lapid_b200_buffer_size(self._h))
+
+    @property
+    def device_ptr(self) -> int:
+        return int(_lib.lib().lapid_b200_buffer_device_ptr(self._h) or 0)
+
+    def write(self, offset: int, data) -> None:
+        self.backend.write(self, offset, data)
+
+    def download(self, nbytes: Optional[int] = None) -> np.ndarray:
+        return self.backend.download(self, nbytes)
+
+    def free(self) -> None:
+        if self._h:
+            _lib.lib().lapid_b200_buffer_free(self._h)
+            self._h = C.c_void_p(None)
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _host_bytes(data) -> np.ndarray:
+    arr = np.ascontiguousarray(data)
+    return arr.reshape(-1).view(np.uint8)
+
+
+class Backend:
+    """``impl Backend`` for one B200. ``Backend(0)`` opens CUDA device 0."""
+
+    def __init__(self, ordinal: int = 0):
+        h = C.c_void_p()
+        check(_lib.lib().lapid_b200_check_abi(1))
+        check(_lib.lib().lapid_b200_device_open(ordinal, C.byref(h)))
+        self._h = h
+        self.ordinal = ordinal
+
+    def name(self) -> str:
+        return "b200"
+
+    def device_name(self) -> str:
+        buf = C.create_string_buffer(256)
+        check(_lib.lib().lapid_b200_device_name(self._h, buf, 256))
+        return buf.value.decode()
+
+    def set_option(self, key: str, value: str) -> None:
+        check(_lib.lib().lapid_b200_device_set_option(self._h, key.encode(), str(value).encode()))
+
+    def set_stream(self, cuda_stream: int) -> None:
+        check(_lib.lib().lapid_b200_device_set_stream(self._h, C.c_void_p(cuda_stream or None)))
+
+    def synchronize(self) -> None:
+        check(_lib.lib().lapid_b200_device_synchronize(self._h))
+
+    # ---- buffers
+    def alloc(self, nbytes: int) -> Buffer:
+        h = C.c_void_p()
+        check(_lib.lib().lapid_b200_alloc(self._h, nbytes, C.byref(h)))
+        return Buffer(self, h.value)
+
+    def upload(self, data) -> Buffer:
+        b = _host_bytes(data)
+        h = C.c_void_p()
+        check(_lib.lib().lapid_b200_upload(self._h, b.ctypes.data, b.size, C.byref(h)))
+        return Buffer(self, h.value)
+
+    def wrap(self, device_ptr: int, nbytes: int, keep=None) -> Buffer:
+        h = C.c_void_p()
+        check(_lib.lib().lapid_b200_wrap(self._h, C.c_void_p(device_ptr), nbytes, C.byref(h)))
+        return Buffer(self, h.value, keep)
+
+    def wrap_tensor(self, t) -> Buffer:
+        """A buffer over a contiguous CUDA torch tensor's memory (kept alive by the buffer)."""
+        assert t.is_cuda and t.is_contiguous()
+        return self.wrap(t.data_ptr(), t.numel() * t.element_size(), keep=t)
+
+    def write(self, buf: Buffer, offset: int, data) -> None:
+        b = _host_bytes(data)
+        check(_lib.lib().lapid_b200_write(buf._h, offset, b.ctypes.data, b.size))
+
+    def write_ptr(self, buf: Buffer, offset: int, host_ptr: int, nbytes: int) -> None:
+        check(_lib.lib().lapid_b200_write(buf._h, offset, C.c_void_p(host_ptr), nbytes))
+
+    def download(self, buf: Buffer, nbytes: Optional[int] = None) -> np.ndarray:
+        n = buf.nbytes if nbytes is None else nbytes
+        out = np.empty(n, dtype=np.uint8)
+        check(_lib.lib().lapid_b200_download(buf._h, out.ctypes.data, n))
+        return out
+
+    def download_ptr(self, buf: Buffer, host_ptr: int, nbytes: int) -> None:
+        check(_lib.lib().lapid_b200_download(buf._h, C.c_void_p(host_ptr), nbytes))
+
+    # ---- launches
+    @staticmethod
+    def _pack(launches: Sequence[Launch], buffers: Sequence[Buffer]):
+        arr = (_lib.LaunchC * len(launches))(*[l.to_c() for l in launches])
+        bufs = (C.c_void_p * len(buffers))(*[b._h for b in buffers])
+        return arr, bufs
+
+    def prepare(self, launches: Sequence[Launch]) -> None:
+        arr = (_lib.LaunchC * len(launches))(*[l.to_c() for l in launches])
+        check(_lib.lib().lapid_b200_prepare(self._h, arr, len(launches)))
+
+    def execute(self, launches: Sequence[Launch], buffers: Sequence[Buffer]) -> None:
+        arr, bufs = self._pack(launches, buffers)
+        check(_lib.lib().lapid_b200_execute(self._h, arr, len(launches), bufs, len(buffers)))
+
+    def execute_async(self, launches: Sequence[Launch], buffers: Sequence[Buffer]) -> None:
+        arr, bufs = self._pack(launches, buffers)
+        check(_lib.lib().lapid_b200_execute_async(self._h, arr, len(launches), bufs, len(buffers)))
+
+    def packed(self, launches: Sequence[Launch], buffers: Sequence[Buffer]):
+        """Pre-marshalled launch arrays for hot loops: returns a zero-argument callable that
+        queues the launches asynchronously (no Python-side conversion per call)."""
+        arr, bufs = self._pack(launches, buffers)
+        fn, h, n, nb = _lib.lib().lapid_b200_execute_async, self._h, len(launches), len(buffers)
+
+        def run():
+            check(fn(h, arr, n, bufs, nb))
+        run.keep = (arr, bufs, list(buffers))
+        return run
+
+    def take_launch_count(self) -> int:
+        return int(_lib.lib().lapid_b200_take_launch_count(self._h))
+
+    # ---- lapid-quant on the device
+    def quantize_into(self, fmt: int, src: Buffer, rows: int, cols: int, dst: Buffer) -> None:
+        check(_lib.lib().lapid_b200_quantize(self._h, int(fmt), src._h, rows, cols, dst._h))
+
+    def dequantize_into(self, fmt: int, src: Buffer, rows: int, cols: int, dst: Buffer) -> None:
+        check(_lib.lib().lapid_b200_dequantize(self._h, int(fmt), src._h, rows, cols, dst._h))
+
+    def close(self) -> None:
+        if self._h:
+            _lib.lib().lapid_b200_device_free(self._h)
+            self._h = C.c_void_p(None)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,67 @@
+// Activation rows -> int8 per 32-element group, the pre-pass of the decode path.
+//
+// Arithmetic of lapid-cpu's `quantize_row_scalar` (crates/lapid-cpu/src/matmul/quant.rs:68-89):
+//   amax = max |x| over the group (NaN ignored), d = amax / 127, id = d > 0 ? 1/d : 0,
+//   q = clamp(i32((x*id + 12582912.0) - 12582912.0), -127, 127)   (round half to even),
+//   s[g] = d (f32), bs[g] = d * f32(sum q)   (bs only for weight formats with a min term).
+// Note x * (1/(amax/127)), not x * (127/amax): the two differ in the last bit.
+//
+// One warp per group: lane t owns element t; max and sum are warp reductions (both are
+// order-independent: max of floats, sum of small integers). The kernel moves 5.25 bytes per
+// element and is latency-bound at decode sizes; what matters is that it is a single short wave.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lb {
+
+__global__ void __launch_bounds__(256) act_quant_kernel(ActQuantArgs p) {
+    // Under programmatic dependent launch: let the consumer's CTAs start staging weights now,
+    // and do not read the activations before the producer grid has completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int lane = threadIdx.x & 31;
+    const uint32_t kg = p.k / GROUP;
+    const uint64_t n_groups = (uint64_t)p.rows * kg;
+    const uint64_t warps = (uint64_t)gridDim.x * (blockDim.x >> 5);
+    for (uint64_t gi = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); gi < n_groups; gi += warps) {
+        uint32_t r = (uint32_t)(gi / kg), g = (uint32_t)(gi % kg);
+        const float *row = p.a + p.a_off + (uint64_t)(r / p.m) * p.a_bs + (uint64_t)(r % p.m) * p.a_rs;
+        float x = row[g * GROUP + lane];
+        float amax = fabsf(x);
+        if (!(amax == amax)) amax = 0.0f;  // f32::max ignores a NaN operand
+#pragma unroll
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        float d = xdiv(amax, 127.0f);
+        float id = d > 0.0f ? xdiv(1.0f, d) : 0.0f;
+        float rr = xsub(xadd(xmul(x, id), 12582912.0f), 12582912.0f);
+        int q = (rr != rr) ? 0 : (int)rr;  // `as i32`: NaN -> 0, saturating
+        q = q < -127 ? -127 : (q > 127 ? 127 : q);
+        int sum = q;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        p.qa[(uint64_t)r * p.k + g * GROUP + lane] = (int8_t)q;
+        if (lane == 0) {
+            p.da[(uint64_t)r * kg + g] = d;
+            if (p.bs) p.bs[(uint64_t)r * kg + g] = xmul(d, (float)sum);
+        }
+    }
+}
+
+cudaError_t launch_act_quant(const ActQuantArgs &args, int sm_count, bool pdl, cudaStream_t stream) {
+    uint64_t n_groups = (uint64_t)args.rows * (args.k / GROUP);
+    if (n_groups == 0) return cudaSuccess;
+    uint64_t ctas = (n_groups + 7) / 8;
+    uint64_t cap = (uint64_t)sm_count * 8;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(ctas < cap ? ctas : cap));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, act_quant_kernel, args);
+}
+
+}  // namespace lb

@@ -1,0 +1,678 @@
+// Host side of the library: the device / buffer objects behind the C handles, launch
+// validation and dispatch, and the extern "C" entry points declared in lapid_b200.h.
+//
+// It mirrors, for the quantized-matmul path only:
+//   Backend::{alloc, upload, write, download, prepare, execute}  crates/lapid-compiler/src/backend.rs:8-63
+//   launch validation of matmul::run                             crates/lapid-cpu/src/matmul/mod.rs:165-262
+//   buffer-id and aliasing checks of run_launch                  crates/lapid-cpu/src/lib.rs:380-397
+//   QMat::new (shape and size checks of the quantized operand)   crates/lapid-cpu/src/qmat.rs:38-60
+//   status codes, last-error JSON, panic guard                   crates/lapid-c/src/error.rs:16-97
+#include "../../include/lapid_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+
+#include "kernels.h"
+
+namespace {
+
+// ------------------------------------------------------------------ errors
+struct Error {
+    const char *code;  // lapid's `Error::code` strings
+    std::string message;
+};
+
+[[noreturn]] void fail(const char *code, std::string msg) { throw Error{code, std::move(msg)}; }
+
+// crates/lapid-c/src/error.rs:49-66
+int32_t status_of(const char *code) {
+    auto is = [&](const char *s) { return std::strcmp(code, s) == 0; };
+    if (is("invalid_argument")) return LAPID_B200_ERR_INVALID_ARGUMENT;
+    if (is("shape_mismatch")) return LAPID_B200_ERR_SHAPE_MISMATCH;
+    if (is("unsupported_dtype") || is("unsupported")) return LAPID_B200_ERR_UNSUPPORTED_DTYPE;
+    if (is("not_found")) return LAPID_B200_ERR_NOT_FOUND;
+    if (is("device_unavailable") || is("cuda_unavailable")) return LAPID_B200_ERR_DEVICE_UNAVAILABLE;
+    if (is("backend") || is("cuda") || is("invalid_launch") || is("bad_launch") || is("wrong_backend") ||
+        is("buffer_aliasing") || is("read_only_buffer"))
+        return LAPID_B200_ERR_BACKEND;
+    if (is("out_of_memory") || is("too_large")) return LAPID_B200_ERR_OUT_OF_MEMORY;
+    if (is("index_out_of_range") || is("out_of_bounds")) return LAPID_B200_ERR_INDEX_OUT_OF_RANGE;
+    if (is("abi_mismatch")) return LAPID_B200_ERR_ABI_MISMATCH;
+    return LAPID_B200_ERR_INTERNAL;
+}
+
+thread_local std::string g_last_error;
+thread_local bool g_has_error = false;
+
+std::string json_escape(const std::string &s) {
+    std::string o;
+    for (unsigned char c : s) {
+        if (c == '"' || c == '\\') {
+            o += '\\';
+            o += (char)c;
+        } else if (c < 0x20) {
+            char buf[8];
+            std::snprintf(buf, sizeof buf, "\\u%04x", c);
+            o += buf;
+        } else {
+            o += (char)c;
+        }
+    }
+    return o;
+}
+
+int32_t record(const Error &e) {
+    int32_t st = status_of(e.code);
+    g_last_error = "{\"status\": " + std::to_string(st) + ", \"error\": \"" + json_escape(e.code) + "\", \"message\": \"" +
+                   json_escape(e.message) + "\"}";
+    g_has_error = true;
+    return st;
+}
+
+template <class F> int32_t guard(F &&f) {
+    try {
+        f();
+        return LAPID_B200_OK;
+    } catch (const Error &e) {
+        return record(e);
+    } catch (const std::bad_alloc &) {
+        return record(Error{"out_of_memory", "host allocation failed"});
+    } catch (const std::exception &e) {
+        return record(Error{"panic", e.what()});
+    } catch (...) {
+        return record(Error{"panic", "unknown exception"});
+    }
+}
+
+void cuda_check(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return;
+    const char *code = (e == cudaErrorMemoryAllocation) ? "out_of_memory" : "cuda";
+    fail(code, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
+}
+
+// ------------------------------------------------------------------ layout (lapid-quant lib.rs:84-125)
+bool is_quant(int32_t dt) { return dt == LAPID_B200_DTYPE_INT8 || dt == LAPID_B200_DTYPE_Q4_K || dt == LAPID_B200_DTYPE_Q6_K; }
+uint64_t block_elems(int32_t dt) { return dt == LAPID_B200_DTYPE_INT8 ? 32 : 256; }
+uint64_t block_bytes(int32_t dt) { return dt == LAPID_B200_DTYPE_Q4_K ? 144 : (dt == LAPID_B200_DTYPE_Q6_K ? 210 : 0); }
+uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+
+lapid_b200_layout layout_of(int32_t fmt, uint64_t rows, uint64_t cols) {
+    if (!is_quant(fmt)) fail("unsupported_dtype", "dtype " + std::to_string(fmt) + " is not a supported quantized format");
+    uint64_t be = block_elems(fmt);
+    if (cols % be != 0)
+        fail("invalid_launch", "quantized matrix cols " + std::to_string(cols) + " not a multiple of " + std::to_string(be));
+    if (cols != 0 && rows > UINT64_MAX / 2 / cols) fail("too_large", "quantized matrix size overflows");
+    lapid_b200_layout l{};
+    l.rows = rows;
+    l.cols = cols;
+    if (block_bytes(fmt)) {
+        uint64_t n = rows * (cols / be) * block_bytes(fmt);
+        l.qs_offset = 0;
+        l.qs_bytes = n;
+        l.scales_offset = n;
+        l.scales_bytes = 0;
+        l.total = align_up(n, 256);
+        return l;
+    }
+    l.qs_offset = 0;
+    l.qs_bytes = rows * cols;
+    l.scales_offset = align_up(l.qs_bytes, 256);
+    l.scales_bytes = rows * (cols / 32) * 2;
+    l.total = align_up(l.scales_offset + l.scales_bytes, 256);
+    return l;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ handles
+struct lapid_b200_device {
+    std::atomic<int> refs{1};
+    int ordinal = 0;
+    int sm_count = 0;
+    std::string name;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    std::mutex mu;  // serialises launches, like lapid-cuda's mutex-guarded Exec
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    std::atomic<uint64_t> launches{0};
+    bool pdl = true;
+    uint32_t gemv_max_rows = 8;
+    bool gemm_f32 = true;  // exact-f32 GEMM for rows > gemv_max_rows (the tensor-core path is opt-in until built)
+
+    void make_current() const { cuda_check(cudaSetDevice(ordinal), "cudaSetDevice"); }
+    ~lapid_b200_device() {
+        if (cudaSetDevice(ordinal) == cudaSuccess) {
+            if (scratch) cudaFree(scratch);
+            if (own_stream) cudaStreamDestroy(own_stream);
+        }
+    }
+    // Grow-only scratch; growing waits for the stream first (nothing may still use the old block).
+    void ensure_scratch(size_t bytes) {
+        if (bytes <= scratch_bytes) return;
+        cuda_check(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+        if (scratch) cuda_check(cudaFree(scratch), "cudaFree");
+        scratch = nullptr;
+        scratch_bytes = 0;
+        size_t want = (bytes + (1u << 20) - 1) & ~(size_t)((1u << 20) - 1);
+        cuda_check(cudaMalloc(&scratch, want), "cudaMalloc(scratch)");
+        scratch_bytes = want;
+    }
+};
+
+struct lapid_b200_buffer {
+    std::atomic<int> refs{1};
+    lapid_b200_device *dev = nullptr;  // retained
+    void *ptr = nullptr;
+    size_t bytes = 0;
+    bool owned = true;
+};
+
+namespace {
+
+void device_release(lapid_b200_device *d) {
+    if (d && d->refs.fetch_sub(1) == 1) delete d;
+}
+
+void buffer_release(lapid_b200_buffer *b) {
+    if (!b || b->refs.fetch_sub(1) != 1) return;
+    if (b->owned && b->ptr && cudaSetDevice(b->dev->ordinal) == cudaSuccess) {
+        // frees are ordered after the work queued on the device's stream
+        cudaStreamSynchronize(b->dev->stream);
+        cudaFree(b->ptr);
+    }
+    device_release(b->dev);
+    delete b;
+}
+
+lapid_b200_device *need(lapid_b200_device *d) {
+    if (!d) fail("invalid_argument", "device is NULL");
+    return d;
+}
+lapid_b200_buffer *need(lapid_b200_buffer *b, const char *what) {
+    if (!b) fail("invalid_argument", std::string(what) + " is NULL");
+    return b;
+}
+
+lapid_b200_buffer *new_buffer(lapid_b200_device *dev, void *ptr, size_t bytes, bool owned) {
+    auto *b = new lapid_b200_buffer();
+    dev->refs.fetch_add(1);
+    b->dev = dev;
+    b->ptr = ptr;
+    b->bytes = bytes;
+    b->owned = owned;
+    return b;
+}
+
+// ------------------------------------------------------------------ launch validation + dispatch
+struct Plan {
+    bool noop = false;
+    bool zero_k = false;
+    bool gemv = false;
+    uint32_t rows = 0;
+    lapid_b200_layout wl{};
+    size_t scratch = 0;  // bytes of activation scratch the launch needs
+};
+
+std::string dims_str(const lapid_b200_launch &l) {
+    return "[" + std::to_string(l.batch) + ", " + std::to_string(l.m) + ", " + std::to_string(l.n) + ", " +
+           std::to_string(l.k) + "]";
+}
+
+// Checks that need no buffers (prepare runs these alone).
+Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
+    Plan p;
+    if (l.kind != LAPID_B200_KERNEL_MATMUL) fail("unsupported", "kernel kind " + std::to_string(l.kind) + " is not MatMul");
+    if (!is_quant(l.b_dtype))
+        fail("unsupported_dtype", "b200 matmul: b dtype " + std::to_string(l.b_dtype) + " (want int8, q4_k or q6_k)");
+    if (l.a_dtype != LAPID_B200_DTYPE_F32 || l.out_dtype != LAPID_B200_DTYPE_F32)
+        fail("unsupported_dtype", "b200 matmul: a and out must be f32");
+    if (l.epilogue != LAPID_B200_EPILOGUE_NONE && l.epilogue != LAPID_B200_EPILOGUE_ADD)
+        fail("unsupported", "b200 matmul: epilogue " + std::to_string(l.epilogue));
+    int want_inputs = l.epilogue == LAPID_B200_EPILOGUE_ADD ? 3 : 2;
+    if (l.n_inputs != want_inputs)
+        fail("invalid_launch", "expected " + std::to_string(want_inputs) + " inputs, got " + std::to_string(l.n_inputs));
+    if (l.epilogue == LAPID_B200_EPILOGUE_ADD && l.extra_dtype != LAPID_B200_DTYPE_F32)
+        fail("unsupported_dtype", "b200 matmul: extra must be f32");
+    const uint64_t lim = 1ull << 31;  // 32-bit indexing inside the kernels
+    if (l.batch >= lim || l.m >= lim || l.n >= lim || l.k >= lim || l.batch * l.m >= lim)
+        fail("too_large", "b200 matmul: dimensions " + dims_str(l) + " exceed 32-bit indexing");
+    if (l.batch * l.m * l.n == 0) {
+        p.noop = true;
+        return p;
+    }
+    p.rows = (uint32_t)(l.batch * l.m);
+    if (l.k == 0) {
+        p.zero_k = true;
+        return p;
+    }
+    if (!l.b_transposed || l.b.offset != 0 || l.b.batch_stride != 0)
+        fail("invalid_launch", "b200 matmul: quantized B must be transposed with zero offset and batch stride");
+    p.wl = layout_of(l.b_dtype, l.n, l.k);
+    if (l.b.row_stride != l.k)
+        fail("shape_mismatch", "b200 matmul: quantized B row stride " + std::to_string(l.b.row_stride) + ", expected k = " +
+                                   std::to_string(l.k));
+    p.gemv = p.rows <= dev.gemv_max_rows;
+    if (p.gemv) {
+        size_t qa = align_up((uint64_t)p.rows * l.k, 256);
+        size_t sc = align_up((uint64_t)p.rows * (l.k / 32) * 4, 256);
+        p.scratch = qa + 2 * sc;
+    }
+    return p;
+}
+
+void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_buffer *const *buffers, size_t n_buffers) {
+    Plan p = plan_launch(dev, l);
+    auto get = [&](uint32_t id) -> lapid_b200_buffer * {
+        if (id >= n_buffers || !buffers[id])
+            fail("invalid_launch", "buffer id " + std::to_string(id) + " out of range (" + std::to_string(n_buffers) + " buffers)");
+        if (buffers[id]->dev != &dev) fail("wrong_backend", "buffer " + std::to_string(id) + " belongs to another device");
+        return buffers[id];
+    };
+    lapid_b200_buffer *out = get(l.output);
+    lapid_b200_buffer *ins[3] = {nullptr, nullptr, nullptr};
+    for (int i = 0; i < l.n_inputs; i++) {
+        ins[i] = get(l.inputs[i]);
+        if (ins[i]->ptr == out->ptr)
+            fail("buffer_aliasing", "input buffer " + std::to_string(l.inputs[i]) + " is the output buffer " + std::to_string(l.output));
+    }
+    if (p.noop) return;
+    uint64_t out_elems = out->bytes / 4;
+    uint64_t last = l.out.offset + (l.batch - 1) * l.out.batch_stride + (l.m - 1) * l.out.row_stride + l.n;
+    if (out_elems < last)
+        fail("out_of_bounds", "b200 matmul: output holds " + std::to_string(out_elems) + " < " + std::to_string(last) + " elements");
+    if (l.k > 0) {
+        uint64_t alast = l.a.offset + (l.batch - 1) * l.a.batch_stride + (l.m - 1) * l.a.row_stride + l.k;
+        if (ins[0]->bytes / 4 < alast)
+            fail("out_of_bounds", "b200 matmul a: view reaches element " + std::to_string(alast) + ", buffer holds " +
+                                      std::to_string(ins[0]->bytes / 4));
+    }
+    const float *extra = nullptr;
+    if (l.epilogue == LAPID_B200_EPILOGUE_ADD) {
+        // lowest and highest element the view touches over [batch, m, n]
+        int64_t lo = (int64_t)l.extra.offset, hi = (int64_t)l.extra.offset;
+        const uint64_t ext[3] = {l.batch, l.m, l.n};
+        for (int d = 0; d < 3; d++) {
+            int64_t span = l.extra.strides[d] * (int64_t)(ext[d] - 1);
+            (span < 0 ? lo : hi) += span;
+        }
+        if (lo < 0 || (uint64_t)hi >= ins[2]->bytes / 4)
+            fail("out_of_bounds", "b200 matmul extra 0: view spans [" + std::to_string(lo) + ", " + std::to_string(hi) +
+                                      "], buffer holds " + std::to_string(ins[2]->bytes / 4));
+        extra = (const float *)ins[2]->ptr;
+    }
+
+    lb::GemvArgs g{};
+    g.out = (float *)out->ptr;
+    g.out_off = l.out.offset;
+    g.out_bs = l.out.batch_stride;
+    g.out_rs = l.out.row_stride;
+    g.extra = extra;
+    g.ex_off = l.extra.offset;
+    g.ex_s0 = l.extra.strides[0];
+    g.ex_s1 = l.extra.strides[1];
+    g.ex_s2 = l.extra.strides[2];
+    g.rows = p.rows;
+    g.m = (uint32_t)l.m;
+    g.n = (uint32_t)l.n;
+    g.k = (uint32_t)l.k;
+    if (p.zero_k) {
+        cuda_check(lb::launch_fill_zero_k(g, dev.stream), "fill launch");
+        dev.launches++;
+        return;
+    }
+    if (ins[1]->bytes < p.wl.scales_offset + p.wl.scales_bytes)
+        fail("out_of_bounds", "b200: quantized [" + std::to_string(l.n) + ", " + std::to_string(l.k) + "] needs " +
+                                  std::to_string(p.wl.total) + " bytes, buffer has " + std::to_string(ins[1]->bytes));
+    if (((uintptr_t)ins[1]->ptr & 15) != 0) fail("invalid_launch", "b200: quantized B must be 16-byte aligned");
+
+    if (p.gemv) {
+        dev.ensure_scratch(p.scratch);
+        size_t qa_b = align_up((uint64_t)p.rows * l.k, 256), sc_b = align_up((uint64_t)p.rows * (l.k / 32) * 4, 256);
+        lb::ActQuantArgs q{};
+        q.a = (const float *)ins[0]->ptr;
+        q.a_off = l.a.offset;
+        q.a_bs = l.a.batch_stride;
+        q.a_rs = l.a.row_stride;
+        q.rows = p.rows;
+        q.m = (uint32_t)l.m;
+        q.k = (uint32_t)l.k;
+        q.qa = (int8_t *)dev.scratch;
+        q.da = (float *)((char *)dev.scratch + qa_b);
+        q.bs = l.b_dtype == LAPID_B200_DTYPE_Q4_K ? (float *)((char *)dev.scratch + qa_b + sc_b) : nullptr;
+        cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl, dev.stream), "act_quant launch");
+        g.w = (const uint8_t *)ins[1]->ptr;
+        g.w_bytes = ins[1]->bytes;
+        g.scales_offset = p.wl.scales_offset;
+        g.qa = q.qa;
+        g.da = q.da;
+        g.bs = q.bs;
+        cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        dev.launches += 2;
+        return;
+    }
+    lb::GemmF32Args f{};
+    f.w = (const uint8_t *)ins[1]->ptr;
+    f.scales_offset = p.wl.scales_offset;
+    f.a = (const float *)ins[0]->ptr;
+    f.a_off = l.a.offset;
+    f.a_bs = l.a.batch_stride;
+    f.a_rs = l.a.row_stride;
+    f.out = g.out;
+    f.out_off = g.out_off;
+    f.out_bs = g.out_bs;
+    f.out_rs = g.out_rs;
+    f.extra = extra;
+    f.ex_off = g.ex_off;
+    f.ex_s0 = g.ex_s0;
+    f.ex_s1 = g.ex_s1;
+    f.ex_s2 = g.ex_s2;
+    f.rows = p.rows;
+    f.m = g.m;
+    f.n = g.n;
+    f.k = g.k;
+    cuda_check(lb::launch_qgemm_f32(l.b_dtype, f, dev.stream), "qgemm_f32 launch");
+    dev.launches++;
+}
+
+void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n, lapid_b200_buffer *const *buffers,
+                  size_t nbuf, bool wait) {
+    need(dev);
+    if (n && !launches) fail("invalid_argument", "launches is NULL");
+    if (nbuf && !buffers) fail("invalid_argument", "buffers is NULL");
+    std::lock_guard<std::mutex> lock(dev->mu);
+    dev->make_current();
+    for (size_t i = 0; i < n; i++) run_launch(*dev, launches[i], buffers, nbuf);
+    if (wait) cuda_check(cudaStreamSynchronize(dev->stream), "cudaStreamSynchronize");
+}
+
+}  // namespace
+
+// ================================================================== extern "C"
+extern "C" {
+
+uint32_t lapid_b200_abi_version(void) { return LAPID_B200_ABI_VERSION; }
+
+lapid_b200_status lapid_b200_check_abi(uint32_t expected) {
+    return guard([&] {
+        if (expected != LAPID_B200_ABI_VERSION)
+            fail("abi_mismatch", "header ABI " + std::to_string(expected) + ", library ABI " + std::to_string(LAPID_B200_ABI_VERSION));
+    });
+}
+
+const char *lapid_b200_last_error(void) { return g_has_error ? g_last_error.c_str() : nullptr; }
+
+lapid_b200_status lapid_b200_device_open(int32_t ordinal, lapid_b200_device **out) {
+    return guard([&] {
+        if (!out) fail("invalid_argument", "out is NULL");
+        int count = 0;
+        cudaError_t e = cudaGetDeviceCount(&count);
+        if (e != cudaSuccess || count == 0)
+            fail("cuda_unavailable", std::string("no CUDA device: ") + (e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e)));
+        if (ordinal < 0 || ordinal >= count)
+            fail("device_unavailable", "CUDA device " + std::to_string(ordinal) + " does not exist (" + std::to_string(count) + " devices)");
+        cudaDeviceProp prop{};
+        cuda_check(cudaGetDeviceProperties(&prop, ordinal), "cudaGetDeviceProperties");
+        if (prop.major != 10)
+            fail("device_unavailable", std::string(prop.name) + " is compute capability " + std::to_string(prop.major) + "." +
+                                           std::to_string(prop.minor) + "; this library carries sm_100a code only");
+        auto *d = new lapid_b200_device();
+        d->ordinal = ordinal;
+        d->sm_count = prop.multiProcessorCount;
+        d->name = prop.name;
+        try {
+            d->make_current();
+            cuda_check(cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+            d->stream = d->own_stream;
+        } catch (...) {
+            delete d;
+            throw;
+        }
+        *out = d;
+    });
+}
+
+void lapid_b200_device_retain(lapid_b200_device *dev) {
+    if (dev) dev->refs.fetch_add(1);
+}
+void lapid_b200_device_free(lapid_b200_device *dev) { device_release(dev); }
+
+lapid_b200_status lapid_b200_device_name(const lapid_b200_device *dev, char *out, size_t cap) {
+    return guard([&] {
+        if (!dev || !out || cap == 0) fail("invalid_argument", "device, out or cap is NULL/0");
+        std::string s = dev->name + " (sm_100a, " + std::to_string(dev->sm_count) + " SMs)";
+        size_t n = s.size() < cap - 1 ? s.size() : cap - 1;
+        std::memcpy(out, s.data(), n);
+        out[n] = 0;
+    });
+}
+
+lapid_b200_status lapid_b200_device_set_stream(lapid_b200_device *dev, void *cuda_stream) {
+    return guard([&] {
+        need(dev);
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->stream = cuda_stream ? (cudaStream_t)cuda_stream : dev->own_stream;
+    });
+}
+
+lapid_b200_status lapid_b200_device_synchronize(lapid_b200_device *dev) {
+    return guard([&] {
+        need(dev);
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        cuda_check(cudaStreamSynchronize(dev->stream), "cudaStreamSynchronize");
+    });
+}
+
+lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const char *key, const char *value) {
+    return guard([&] {
+        need(dev);
+        if (!key || !value) fail("invalid_argument", "key or value is NULL");
+        std::lock_guard<std::mutex> lock(dev->mu);
+        std::string k = key, v = value;
+        if (k == "pdl") {
+            dev->pdl = v != "0";
+        } else if (k == "gemv_max_rows") {
+            int r = std::atoi(value);
+            if (r < 0 || r > 8) fail("invalid_argument", "gemv_max_rows must be in 0..8");
+            dev->gemv_max_rows = (uint32_t)r;
+        } else if (k == "gemm") {
+            if (v == "f32") dev->gemm_f32 = true;
+            else fail("invalid_argument", "gemm must be \"f32\"");
+        } else {
+            fail("invalid_argument", "unknown option \"" + k + "\"");
+        }
+    });
+}
+
+lapid_b200_status lapid_b200_alloc(lapid_b200_device *dev, size_t bytes, lapid_b200_buffer **out) {
+    return guard([&] {
+        need(dev);
+        if (!out) fail("invalid_argument", "out is NULL");
+        dev->make_current();
+        void *p = nullptr;
+        cuda_check(cudaMalloc(&p, bytes ? bytes : 1), "cudaMalloc");
+        *out = new_buffer(dev, p, bytes, true);
+    });
+}
+
+lapid_b200_status lapid_b200_upload(lapid_b200_device *dev, const void *host, size_t bytes, lapid_b200_buffer **out) {
+    return guard([&] {
+        need(dev);
+        if (!out || (bytes && !host)) fail("invalid_argument", "out or host is NULL");
+        dev->make_current();
+        void *p = nullptr;
+        cuda_check(cudaMalloc(&p, bytes ? bytes : 1), "cudaMalloc");
+        cudaError_t e = cudaSuccess;
+        {
+            std::lock_guard<std::mutex> lock(dev->mu);
+            if (bytes) e = cudaMemcpyAsync(p, host, bytes, cudaMemcpyHostToDevice, dev->stream);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);  // `host` may be reused on return
+        }
+        if (e != cudaSuccess) {
+            cudaFree(p);
+            cuda_check(e, "upload");
+        }
+        *out = new_buffer(dev, p, bytes, true);
+    });
+}
+
+lapid_b200_status lapid_b200_wrap(lapid_b200_device *dev, void *device_ptr, size_t bytes, lapid_b200_buffer **out) {
+    return guard([&] {
+        need(dev);
+        if (!out || !device_ptr) fail("invalid_argument", "out or device_ptr is NULL");
+        if ((uintptr_t)device_ptr & 15) fail("invalid_argument", "wrapped device memory must be 16-byte aligned");
+        *out = new_buffer(dev, device_ptr, bytes, false);
+    });
+}
+
+lapid_b200_status lapid_b200_write(lapid_b200_buffer *buf, size_t offset, const void *host, size_t bytes) {
+    return guard([&] {
+        need(buf, "buffer");
+        if (bytes && !host) fail("invalid_argument", "host is NULL");
+        if (offset > buf->bytes || bytes > buf->bytes - offset)
+            fail("out_of_bounds", "write of " + std::to_string(bytes) + " bytes at " + std::to_string(offset) + " into a buffer of " +
+                                      std::to_string(buf->bytes));
+        if (!bytes) return;
+        lapid_b200_device *dev = buf->dev;
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        cuda_check(cudaMemcpyAsync((char *)buf->ptr + offset, host, bytes, cudaMemcpyHostToDevice, dev->stream), "write");
+        // pageable memory is staged before the call returns; pinned memory must stay valid until
+        // the copy ran, so wait: `host` may be reused when this returns (Backend::write contract)
+        cuda_check(cudaStreamSynchronize(dev->stream), "write");
+    });
+}
+
+lapid_b200_status lapid_b200_download(lapid_b200_buffer *buf, void *host, size_t bytes) {
+    return guard([&] {
+        need(buf, "buffer");
+        if (bytes && !host) fail("invalid_argument", "host is NULL");
+        if (bytes > buf->bytes)
+            fail("out_of_bounds", "download of " + std::to_string(bytes) + " bytes from a buffer of " + std::to_string(buf->bytes));
+        lapid_b200_device *dev = buf->dev;
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        if (bytes) cuda_check(cudaMemcpyAsync(host, buf->ptr, bytes, cudaMemcpyDeviceToHost, dev->stream), "download");
+        cuda_check(cudaStreamSynchronize(dev->stream), "download");
+    });
+}
+
+void lapid_b200_buffer_retain(lapid_b200_buffer *buf) {
+    if (buf) buf->refs.fetch_add(1);
+}
+void lapid_b200_buffer_free(lapid_b200_buffer *buf) { buffer_release(buf); }
+size_t lapid_b200_buffer_size(const lapid_b200_buffer *buf) { return buf ? buf->bytes : 0; }
+void *lapid_b200_buffer_device_ptr(const lapid_b200_buffer *buf) { return buf ? buf->ptr : nullptr; }
+
+lapid_b200_status lapid_b200_prepare(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n) {
+    return guard([&] {
+        need(dev);
+        if (n && !launches) fail("invalid_argument", "launches is NULL");
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        size_t scratch = 0;
+        for (size_t i = 0; i < n; i++) {
+            Plan p = plan_launch(*dev, launches[i]);
+            if (p.scratch > scratch) scratch = p.scratch;
+        }
+        dev->ensure_scratch(scratch);
+    });
+}
+
+lapid_b200_status lapid_b200_execute(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n,
+                                     lapid_b200_buffer *const *buffers, size_t nbuf) {
+    return guard([&] { execute_impl(dev, launches, n, buffers, nbuf, true); });
+}
+
+lapid_b200_status lapid_b200_execute_async(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n,
+                                           lapid_b200_buffer *const *buffers, size_t nbuf) {
+    return guard([&] { execute_impl(dev, launches, n, buffers, nbuf, false); });
+}
+
+uint64_t lapid_b200_take_launch_count(lapid_b200_device *dev) { return dev ? dev->launches.exchange(0) : 0; }
+
+lapid_b200_status lapid_b200_quant_layout(int32_t format, uint64_t rows, uint64_t cols, lapid_b200_layout *out) {
+    return guard([&] {
+        if (!out) fail("invalid_argument", "out is NULL");
+        *out = layout_of(format, rows, cols);
+    });
+}
+
+lapid_b200_status lapid_b200_dequantize(lapid_b200_device *dev, int32_t format, const lapid_b200_buffer *src, uint64_t rows,
+                                        uint64_t cols, lapid_b200_buffer *dst) {
+    return guard([&] {
+        need(dev);
+        if (!src || !dst) fail("invalid_argument", "src or dst is NULL");
+        if (cols == 0) fail("invalid_launch", "quantized cols must be positive");
+        lapid_b200_layout l = layout_of(format, rows, cols);
+        if (src->bytes < l.scales_offset + l.scales_bytes)
+            fail("out_of_bounds", "dequantize: buffer too small (" + std::to_string(src->bytes) + " < " + std::to_string(l.total) + ")");
+        if (dst->bytes / 4 < rows * cols)
+            fail("out_of_bounds", "dequantize: out has " + std::to_string(dst->bytes / 4) + " elements, expected " + std::to_string(rows * cols));
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        cuda_check(lb::launch_dequantize(format, src->ptr, rows, cols, l.scales_offset, (float *)dst->ptr, dev->sm_count, dev->stream),
+                   "dequantize launch");
+        dev->launches++;
+        cuda_check(cudaStreamSynchronize(dev->stream), "dequantize");
+    });
+}
+
+lapid_b200_status lapid_b200_quantize(lapid_b200_device *dev, int32_t format, const lapid_b200_buffer *src, uint64_t rows,
+                                      uint64_t cols, lapid_b200_buffer *dst) {
+    return guard([&] {
+        need(dev);
+        if (!src || !dst) fail("invalid_argument", "src or dst is NULL");
+        if (cols == 0) fail("invalid_launch", "quantized cols must be positive");
+        lapid_b200_layout l = layout_of(format, rows, cols);
+        if (src->bytes / 4 < rows * cols)
+            fail("shape_mismatch", "quantize: data has " + std::to_string(src->bytes / 4) + " elements, expected " +
+                                       std::to_string(rows) + "x" + std::to_string(cols));
+        if (dst->bytes < l.total)
+            fail("out_of_bounds", "quantize: output holds " + std::to_string(dst->bytes) + " < " + std::to_string(l.total) + " bytes");
+        if (((uintptr_t)src->ptr & 15) != 0) fail("invalid_launch", "quantize: source must be 16-byte aligned");
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        cuda_check(lb::launch_quantize(format, (const float *)src->ptr, rows, cols, l.scales_offset, l.total, dst->ptr, dev->sm_count,
+                                       dev->stream),
+                   "quantize launch");
+        dev->launches++;
+        cuda_check(cudaStreamSynchronize(dev->stream), "quantize");
+    });
+}
+
+lapid_b200_status lapid_b200_from_ggml_blocks(lapid_b200_device *dev, int32_t format, const lapid_b200_buffer *src,
+                                              uint64_t src_bytes, uint64_t rows, uint64_t cols, lapid_b200_buffer *dst) {
+    return guard([&] {
+        need(dev);
+        if (!src || !dst) fail("invalid_argument", "src or dst is NULL");
+        if (cols == 0) fail("invalid_launch", "quantized cols must be positive");
+        lapid_b200_layout l = layout_of(format, rows, cols);
+        uint64_t want = block_bytes(format) ? l.qs_bytes : rows * (cols / 32) * 34;
+        if (src_bytes != want || src->bytes < src_bytes)
+            fail("shape_mismatch", "from_ggml_blocks: got " + std::to_string(src_bytes) + " bytes, expected " + std::to_string(want));
+        if (dst->bytes < l.total)
+            fail("out_of_bounds", "from_ggml_blocks: output holds " + std::to_string(dst->bytes) + " < " + std::to_string(l.total));
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        cuda_check(cudaMemsetAsync(dst->ptr, 0, l.total, dev->stream), "memset");
+        if (block_bytes(format)) {
+            if (want) cuda_check(cudaMemcpyAsync(dst->ptr, src->ptr, want, cudaMemcpyDeviceToDevice, dev->stream), "copy");
+        } else {
+            cuda_check(lb::launch_q8_0_to_planes(src->ptr, dst->ptr, l.scales_offset, rows * (cols / 32), dev->sm_count, dev->stream),
+                       "q8_0 repack launch");
+            dev->launches++;
+        }
+        cuda_check(cudaStreamSynchronize(dev->stream), "from_ggml_blocks");
+    });
+}
+
+}  // extern "C"

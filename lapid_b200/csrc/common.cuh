@@ -1,0 +1,73 @@
+// Shared device helpers: block geometry of the GGUF formats lapid keeps (Q4_K, Q6_K) and of its
+// Int8 plane layout, exact (never contracted) f32 arithmetic for the bit-exact paths, and the
+// 6-bit scale/min unpacking of Q4_K headers.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lb {
+
+constexpr int FMT_INT8 = 4;  // lapid dtype codes (crates/lapid-c/src/lib.rs:37-60)
+constexpr int FMT_Q4K = 6;
+constexpr int FMT_Q6K = 8;
+
+constexpr int GROUP = 32;
+constexpr int QK = 256;
+constexpr int Q4K_BYTES = 144;
+constexpr int Q6K_BYTES = 210;
+
+// Separately rounded IEEE operations. nvcc fuses a*b+c into an FMA unless told otherwise; the
+// reference never does ("do not simplify the arithmetic", crates/lapid-quant/src/kquant.rs:3-4),
+// so every operation that must reproduce its bits goes through these.
+__device__ __forceinline__ float xmul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float xadd(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float xsub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float xdiv(float a, float b) { return __fdiv_rn(a, b); }
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t h) {
+    return __half2float(__ushort_as_half((unsigned short)h));
+}
+
+// ggml's nearest_int (crates/lapid-quant/src/kquant.rs:25-28): round half to even through the
+// 1.5 * 2^23 offset, valid for |x| <= 4194303.
+__device__ __forceinline__ int nearest_int(float f) {
+    float v = xadd(f, 12582912.0f);
+    return (int)(__float_as_uint(v) & 0x007fffffu) - 0x00400000;
+}
+
+// 6-bit scale and min of sub-block j (0..8) from the 12 packed bytes of a Q4_K header
+// (crates/lapid-quant/src/kquant.rs:178-184). `s` points at the 12 bytes.
+__device__ __forceinline__ void scale_min_k4(int j, const uint8_t *s, int &sc, int &mn) {
+    if (j < 4) {
+        sc = s[j] & 63;
+        mn = s[j + 4] & 63;
+    } else {
+        sc = (s[j + 4] & 0xF) | ((s[j - 4] >> 6) << 4);
+        mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
+    }
+}
+
+// The same unpacking from the three 32-bit words that hold the 12 bytes (w0 = bytes 0..3,
+// w1 = 4..7, w2 = 8..11): scales and mins of sub-blocks 2p and 2p+1 for pair p.
+__device__ __forceinline__ void scale_min_pair(int p, uint32_t w0, uint32_t w1, uint32_t w2, int &sc0, int &mn0,
+                                               int &sc1, int &mn1) {
+    if (p < 2) {
+        int sh = 16 * p;  // bytes 2p, 2p+1 of w0 (scales) and w1 (mins)
+        sc0 = (w0 >> sh) & 63;
+        sc1 = (w0 >> (sh + 8)) & 63;
+        mn0 = (w1 >> sh) & 63;
+        mn1 = (w1 >> (sh + 8)) & 63;
+    } else {
+        int sh = 16 * (p - 2);  // j = 2p, 2p+1 -> bytes j+4 = 8+2(p-2).. of the 12, i.e. w2
+        uint32_t b0 = (w2 >> sh) & 0xff, b1 = (w2 >> (sh + 8)) & 0xff;
+        uint32_t lo0 = (w0 >> sh) & 0xff, lo1 = (w0 >> (sh + 8)) & 0xff;  // s[j-4]
+        uint32_t hi0 = (w1 >> sh) & 0xff, hi1 = (w1 >> (sh + 8)) & 0xff;  // s[j]
+        sc0 = (b0 & 0xF) | ((lo0 >> 6) << 4);
+        mn0 = (b0 >> 4) | ((hi0 >> 6) << 4);
+        sc1 = (b1 & 0xF) | ((lo1 >> 6) << 4);
+        mn1 = (b1 >> 4) | ((hi1 >> 6) << 4);
+    }
+}
+
+}  // namespace lb

@@ -1,0 +1,104 @@
+// Dequantization to f32, bit-identical to lapid-quant, and the GGUF -> lapid layout conversion.
+//
+//   dequantize_q4k   crates/lapid-quant/src/kquant.rs:337-352   y = (d*sc)*q - (dmin*m)
+//   dequantize_q6k   crates/lapid-quant/src/kquant.rs:376-396   y = (d*sc)*(q-32)
+//   Int8 rows        crates/lapid-quant/src/imp.rs:143-148      y = f32(q) * f32(d)
+//   from_ggml_blocks crates/lapid-quant/src/imp.rs:171-200
+//
+// One CTA of 256 threads expands one 256-element super-block (or eight Int8 groups); thread t
+// owns element t, so stores are fully coalesced and the block's bytes are read through L1.
+// The kernels are bound by the 4 bytes written per element (HBM store bandwidth).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lb {
+
+__global__ void __launch_bounds__(256) dequant_q4k_kernel(const uint8_t *__restrict__ src, float *__restrict__ dst,
+                                                          uint64_t n_blocks) {
+    for (uint64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x) {
+        const uint8_t *b = src + blk * Q4K_BYTES;
+        int e = threadIdx.x;
+        int j = e >> 6, h = (e >> 5) & 1, l = e & 31;
+        float d = half_bits_to_float(b[0] | (b[1] << 8));
+        float dmin = half_bits_to_float(b[2] | (b[3] << 8));
+        int sc, mn;
+        scale_min_k4(2 * j + h, b + 4, sc, mn);
+        float d1 = xmul(d, (float)sc);
+        float m1 = xmul(dmin, (float)mn);
+        int q = (b[16 + 32 * j + l] >> (4 * h)) & 15;
+        dst[blk * QK + e] = xsub(xmul(d1, (float)q), m1);
+    }
+}
+
+__global__ void __launch_bounds__(256) dequant_q6k_kernel(const uint8_t *__restrict__ src, float *__restrict__ dst,
+                                                          uint64_t n_blocks) {
+    for (uint64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x) {
+        const uint8_t *b = src + blk * Q6K_BYTES;
+        int e = threadIdx.x;
+        int n = e >> 7, w = (e >> 5) & 3, l = e & 31;
+        float d = half_bits_to_float(b[208] | (b[209] << 8));
+        int lo = (b[64 * n + 32 * (w & 1) + l] >> (4 * (w >> 1))) & 15;
+        int hi = (b[128 + 32 * n + l] >> (2 * w)) & 3;
+        int q = (lo | (hi << 4)) - 32;
+        int sc = (int8_t)b[192 + 8 * n + 2 * w + (l >> 4)];
+        dst[blk * QK + e] = xmul(xmul(d, (float)sc), (float)q);
+    }
+}
+
+__global__ void __launch_bounds__(256) dequant_int8_kernel(const int8_t *__restrict__ qs,
+                                                           const uint16_t *__restrict__ scales,
+                                                           float *__restrict__ dst, uint64_t n_elems) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_elems; i += stride) {
+        float d = half_bits_to_float(scales[i >> 5]);
+        dst[i] = xmul((float)qs[i], d);
+    }
+}
+
+// GGUF block_q8_0 (f16 d + 32 x i8, 34 bytes) -> quants plane + scales plane. One thread per byte
+// of payload; thread 0 of each group also moves the scale.
+__global__ void __launch_bounds__(256) q8_0_to_planes_kernel(const uint8_t *__restrict__ blocks,
+                                                             uint8_t *__restrict__ qs, uint8_t *__restrict__ scales,
+                                                             uint64_t n_groups) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_groups * 32; i += stride) {
+        uint64_t g = i >> 5;
+        int t = (int)(i & 31);
+        const uint8_t *b = blocks + g * 34;
+        qs[i] = b[2 + t];
+        if (t < 2) scales[g * 2 + t] = b[t];
+    }
+}
+
+static int grid_for(uint64_t work_items, int sm_count) {
+    uint64_t want = work_items;
+    uint64_t cap = (uint64_t)sm_count * 8;  // 8 resident CTAs of 256 threads per SM
+    return (int)(want < cap ? (want ? want : 1) : cap);
+}
+
+cudaError_t launch_dequantize(int fmt, const void *src, uint64_t rows, uint64_t cols, uint64_t scales_offset,
+                              float *dst, int sm_count, cudaStream_t stream) {
+    uint64_t n = rows * cols;
+    if (n == 0) return cudaSuccess;
+    if (fmt == FMT_Q4K) {
+        dequant_q4k_kernel<<<grid_for(n / QK, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n / QK);
+    } else if (fmt == FMT_Q6K) {
+        dequant_q6k_kernel<<<grid_for(n / QK, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n / QK);
+    } else {
+        const uint8_t *p = (const uint8_t *)src;
+        dequant_int8_kernel<<<grid_for((n + 255) / 256, sm_count), 256, 0, stream>>>(
+            (const int8_t *)p, (const uint16_t *)(p + scales_offset), dst, n);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_q8_0_to_planes(const void *blocks, void *dst, uint64_t scales_offset, uint64_t n_groups,
+                                  int sm_count, cudaStream_t stream) {
+    if (n_groups == 0) return cudaSuccess;
+    uint8_t *d = (uint8_t *)dst;
+    q8_0_to_planes_kernel<<<grid_for((n_groups * 32 + 255) / 256, sm_count), 256, 0, stream>>>(
+        (const uint8_t *)blocks, d, d + scales_offset, n_groups);
+    return cudaGetLastError();
+}
+
+}  // namespace lb

@@ -1,0 +1,71 @@
+// Host-callable launchers of the CUDA kernels. Everything here is asynchronous on `stream`.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lb {
+
+// ---- dequant.cu
+cudaError_t launch_dequantize(int fmt, const void *src, uint64_t rows, uint64_t cols, uint64_t scales_offset,
+                              float *dst, int sm_count, cudaStream_t stream);
+cudaError_t launch_q8_0_to_planes(const void *blocks, void *dst, uint64_t scales_offset, uint64_t n_groups,
+                                  int sm_count, cudaStream_t stream);
+
+// ---- quantize.cu
+cudaError_t launch_quantize(int fmt, const float *src, uint64_t rows, uint64_t cols, uint64_t scales_offset,
+                            uint64_t total_bytes, void *dst, int sm_count, cudaStream_t stream);
+
+// ---- actquant.cu
+// Activation rows -> int8 per 32-group. Row r = bt*m + i starts at a + a_off + bt*a_bs + i*a_rs.
+// qa: [rows][k] int8; da: [rows][k/32] f32 group scales; bs: [rows][k/32] f32 = da * sum(q)
+// (written only when bs != nullptr, i.e. for Q4_K weights).
+struct ActQuantArgs {
+    const float *a;
+    uint64_t a_off, a_bs, a_rs;
+    uint32_t rows, m, k;
+    int8_t *qa;
+    float *da;
+    float *bs;
+};
+cudaError_t launch_act_quant(const ActQuantArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+
+// ---- qgemv.cu
+struct GemvArgs {
+    const uint8_t *w;       // quantized [n, k] matrix in lapid-quant layout
+    uint64_t w_bytes;       // bytes readable behind `w`
+    uint64_t scales_offset; // Int8 only
+    const int8_t *qa;       // quantized activations, see ActQuantArgs
+    const float *da;
+    const float *bs;
+    float *out;             // row r = bt*m + i at out + out_off + bt*out_bs + i*out_rs
+    uint64_t out_off, out_bs, out_rs;
+    const float *extra;     // epilogue `acc + extra[bt, i, j]`, nullptr for none
+    uint64_t ex_off;
+    int64_t ex_s0, ex_s1, ex_s2;
+    uint32_t rows, m, n, k;
+};
+// rows in 1..8. Returns cudaErrorInvalidValue for an unsupported combination.
+cudaError_t launch_qgemv(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+// Opt in to the dynamic shared memory the GEMV variants need; once per device.
+cudaError_t qgemv_init();
+
+// out[bt, i, j] = 0 (+ extra) for the k == 0 case (crates/lapid-cpu/src/matmul/mod.rs:237-247).
+cudaError_t launch_fill_zero_k(const GemvArgs &args, cudaStream_t stream);
+
+// ---- qgemm_f32.cu
+// Exact-f32 GEMM for more than 8 activation rows (rows = batch*m, flattened like GemvArgs).
+struct GemmF32Args {
+    const uint8_t *w;
+    uint64_t scales_offset;
+    const float *a;
+    uint64_t a_off, a_bs, a_rs;
+    float *out;
+    uint64_t out_off, out_bs, out_rs;
+    const float *extra;
+    uint64_t ex_off;
+    int64_t ex_s0, ex_s1, ex_s2;
+    uint32_t rows, m, n, k;
+};
+cudaError_t launch_qgemm_f32(int fmt, const GemmF32Args &args, cudaStream_t stream);
+
+}  // namespace lb

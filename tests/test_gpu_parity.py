@@ -1,0 +1,337 @@
+"""Parity of the CUDA path against the CPU oracle, through the C ABI, on a B200.
+
+Bars (stated here, checked below):
+  * dequantized weights, quantized bytes, layout conversion ........ bit / byte exact
+  * decode (batch*m <= 8, int8 activations) vs the oracle's restatement of lapid-cpu:
+        max_rel <= 1e-3  where max_rel = max|got-ref| / max(|ref|, rms(ref))   (expected ~1e-6:
+        the integer dot products are exact, only the order of the f32 group sums differs)
+  * exact-f32 GEMM (batch*m > 8) vs the oracle's qdeq with FMA accumulation ... bit exact
+Shapes are the reference's own test shapes (crates/lapid-cpu/src/matmul/matmul_tests.rs:30-139,
+crates/lapid/tests/round3_ops.rs:121-151) plus the benchmark's.
+"""
+import numpy as np
+import pytest
+
+import lapid_b200 as lp
+from lapid_b200 import quant
+from lapid_b200.backend import MatView, matmul_launch
+from oracle import oracle as O
+from tests.refgen import make_blocks, rnd
+
+pytestmark = pytest.mark.gpu
+
+FMTS = [(lp.DType.Int8, "int8"), (lp.DType.Q4K, "q4_k"), (lp.DType.Q6K, "q6_k")]
+
+
+@pytest.fixture(scope="module")
+def be():
+    return lp.Backend(0)
+
+
+def max_rel(got, ref):
+    got = np.asarray(got, np.float64).reshape(-1)
+    ref = np.asarray(ref, np.float64).reshape(-1)
+    rms = np.sqrt((ref ** 2).mean())
+    return float((np.abs(got - ref) / np.maximum(np.abs(ref), max(rms, 1e-30))).max())
+
+
+def rel_l2(got, ref):
+    got = np.asarray(got, np.float64).reshape(-1)
+    ref = np.asarray(ref, np.float64).reshape(-1)
+    return float(np.sqrt(((got - ref) ** 2).sum() / max((ref ** 2).sum(), 1e-30)))
+
+
+def run_matmul(be, fmt, a, qb, m, n, k, *, batch=1, a_row_stride=None, bias=None, out=None, out_view=None):
+    bufs = [be.upload(a), be.upload(qb)]
+    out_host = np.zeros(batch * m * n, np.float32) if out is None else out
+    bufs.append(be.upload(out_host))
+    bias_id = None
+    if bias is not None:
+        bufs.append(be.upload(bias))
+        bias_id = 3
+    l = matmul_launch(fmt, m, n, k, batch=batch, a_row_stride=a_row_stride, bias_input=bias_id, out=out_view)
+    be.prepare([l])
+    be.execute([l], bufs)
+    return bufs[2].download().view(np.float32)
+
+
+# ------------------------------------------------------------------ lapid-quant surface
+def test_device_name_and_launch_counter(be):
+    assert "B200" in be.device_name() or "sm_100a" in be.device_name()
+    be.take_launch_count()
+    x = O.normal(1, 256)
+    qb = quant.quantize(be, quant.Format.Q4K, x, 1, 256)
+    assert qb.size == 256 and be.take_launch_count() == 1
+
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_golden_vectors(be, oracle, fmt, name):
+    g = np.load(__file__.replace("test_gpu_parity.py", "golden/golden.npz"))
+    n, k = 24, 512
+    w = O.normal(10 + int(fmt), n * k, 0.02)
+    assert np.array_equal(quant.quantize(be, fmt, w, n, k), g[f"w_{name}"])          # quantizer bytes
+    deq = quant.dequantize(be, fmt, g[f"w_{name}"], n, k)
+    assert np.array_equal(deq.view(np.uint32), g[f"deq_{name}"])                      # dequant bits
+    x3 = O.normal(20, 3 * k)
+    y3 = run_matmul(be, fmt, x3, g[f"w_{name}"], 3, n, k)
+    assert max_rel(y3, g[f"y3_{name}"]) <= 1e-3
+    assert max_rel(y3, g[f"y3_{name}"]) <= 2e-5  # what the arithmetic should actually achieve
+    x12 = O.normal(21, 12 * k)
+    y12 = run_matmul(be, fmt, x12, g[f"w_{name}"], 12, n, k)
+    assert np.array_equal(y12.view(np.uint32), g[f"y12_{name}"].reshape(-1).view(np.uint32))
+
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_dequantize_bit_exact_random_blocks(be, oracle, fmt, name):
+    rows, cols = 16, 2048
+    if fmt == lp.DType.Int8:
+        l = oracle.layout(int(fmt), rows, cols)
+        rng = np.random.default_rng(3)
+        qb = np.zeros(l.total, np.uint8)
+        qb[:l.qs_bytes] = rng.integers(0, 256, l.qs_bytes, dtype=np.uint8)
+        sc = (rng.standard_normal(rows * cols // 32) * 0.01).astype(np.float16)
+        qb[l.scales_offset:l.scales_offset + l.scales_bytes] = sc.view(np.uint8)
+    else:
+        bb, d_off, dm_off = (144, 0, 2) if fmt == lp.DType.Q4K else (210, 208, None)
+        raw = make_blocks(bb, rows * cols // 256, 7, d_off, dm_off)
+        b2 = raw.reshape(-1, bb)
+        ds = np.array([0.01, 0.25, 3e-5, -0.02, 6e-8, 1.5, 0.003, 7.0], np.float16).view(np.uint8).reshape(8, 2)
+        for i in range(b2.shape[0]):
+            b2[i, d_off:d_off + 2] = ds[i % 8]
+            if dm_off is not None:
+                b2[i, dm_off:dm_off + 2] = ds[(i * 3 + 1) % 8]
+        qb = np.concatenate([raw, np.zeros((-raw.size) % 256, np.uint8)])
+    want = oracle.dequantize(int(fmt), qb, rows, cols)
+    got = quant.dequantize(be, fmt, qb, rows, cols)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_quantize_byte_exact(be, oracle, fmt, name):
+    rows, cols = 37, 1024
+    x = O.normal(40 + int(fmt), rows * cols, 0.02).reshape(rows, cols)
+    x[3, 256:512] = 0.0            # an all-zero super-block
+    x[4, :256] = 1.0               # constants
+    x[5, 0:32] = -2.5
+    x[6, 17] = 4.0                 # an outlier
+    x[7, 300:330] = np.abs(x[7, 300:330])  # a sub-block with min > 0
+    x[8, :] *= 1e-20               # values below the quantizers' epsilon
+    x[9, :64] = np.linspace(-1, 1, 64, dtype=np.float32)
+    want = oracle.quantize(int(fmt), x, rows, cols)
+    got = quant.quantize(be, fmt, x, rows, cols)
+    diff = np.flatnonzero(got != want)
+    assert diff.size == 0, (name, diff[:10], got[diff[:10]], want[diff[:10]])
+
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_quantize_reference_noise_inputs(be, oracle, fmt, name):
+    # the value distribution of the reference's own round-trip tests (uniform in [-2, 2))
+    from tests.refgen import noise
+    rows, cols = 3, 512
+    x = noise(rows * cols, 11, 2.0)
+    assert np.array_equal(quant.quantize(be, fmt, x, rows, cols), oracle.quantize(int(fmt), x, rows, cols))
+
+
+def test_from_ggml_blocks(be, oracle):
+    rows, cols = 3, 64
+    x = O.normal(7, rows * cols)
+    ours = oracle.quantize(O.INT8, x, rows, cols)
+    l = oracle.layout(O.INT8, rows, cols)
+    ng = rows * cols // 32
+    blocks = np.empty((ng, 34), np.uint8)
+    blocks[:, :2] = ours[l.scales_offset:l.scales_offset + 2 * ng].reshape(ng, 2)
+    blocks[:, 2:] = ours[:ng * 32].reshape(ng, 32)
+    assert np.array_equal(quant.from_ggml_blocks(be, quant.Format.Int8, blocks, rows, cols), ours)
+    for fmt in (quant.Format.Q4K, quant.Format.Q6K):
+        q = oracle.quantize(int(fmt), O.normal(8, 3 * 512, 0.02), 3, 512)
+        lq = oracle.layout(int(fmt), 3, 512)
+        assert np.array_equal(quant.from_ggml_blocks(be, fmt, q[:lq.qs_bytes], 3, 512), q)
+        with pytest.raises(lp.LapidError) as e:
+            quant.from_ggml_blocks(be, fmt, q[:lq.qs_bytes - 1], 3, 512)
+        assert e.value.code == "shape_mismatch"
+
+
+# ------------------------------------------------------------------ decode path
+@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_gemv_matches_oracle_all_row_counts(be, oracle, fmt, name, m):
+    n, k = 301, 1024  # n not a multiple of any columns-per-task; k = half a stage
+    w = O.normal(100 + int(fmt), n * k, 0.02)
+    qb = oracle.quantize(int(fmt), w, n, k)
+    a = O.normal(200 + m, m * k)
+    want, path = oracle.matmul(int(fmt), a, qb, n, k, m=m)
+    assert path == "int8_act"
+    got = run_matmul(be, fmt, a, qb, m, n, k)
+    assert max_rel(got, want) <= 1e-3
+    assert max_rel(got, want) <= 2e-5
+
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_gemv_reference_test_shapes(be, oracle, fmt, name):
+    # kquant_matmul_matches_dequantized_f32 (m <= 8 rows), with row padding, vs oracle and vs f64
+    seed = 50
+    for (m, n, k, pad) in [(1, 37, 512, 0), (3, 20, 256, 4), (6, 9, 256, 0), (1, 36, 768, 0), (3, 36, 768, 1),
+                           (2, 1030, 4096, 0), (8, 77, 14336, 0), (1, 5, 2304, 0)]:
+        if fmt != lp.DType.Int8 and k % 256:
+            continue
+        seed += 1
+        w = rnd(n * k, seed) if n * k < 100000 else O.normal(seed, n * k, 0.5)
+        qb = oracle.quantize(int(fmt), w, n, k)
+        rs = k + pad
+        a = rnd(m * rs, seed + 7) if m * rs < 100000 else O.normal(seed + 7, m * rs)
+        want, _ = oracle.matmul(int(fmt), a, qb, n, k, m=m, a_view=(0, 0, rs))
+        got = run_matmul(be, fmt, a, qb, m, n, k, a_row_stride=rs)
+        assert max_rel(got, want) <= 1e-3, (name, m, n, k)
+        deq = oracle.dequantize(int(fmt), qb, n, k).astype(np.float64)
+        f64 = a.reshape(m, rs)[:, :k].astype(np.float64) @ deq.T
+        assert rel_l2(got, f64) <= 2e-2  # the reference's own bound for its int8-activation path
+
+
+def test_gemv_int8_k_not_multiple_of_256(be, oracle):
+    for (m, n, k) in [(2, 40, 96), (1, 7, 32), (4, 33, 2080)]:
+        w = O.normal(3, n * k, 0.1)
+        qb = oracle.quantize(O.INT8, w, n, k)
+        a = O.normal(4, m * k)
+        want, _ = oracle.matmul(O.INT8, a, qb, n, k, m=m)
+        got = run_matmul(be, lp.DType.Int8, a, qb, m, n, k)
+        assert max_rel(got, want) <= 2e-5, (m, n, k)
+
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_config1_full_size_matvec(be, oracle, fmt, name):
+    # weight [4096, 4096] N(0, 0.02) seed 0, activation [1, 4096] N(0, 1) seed 1
+    n = k = 4096
+    w = O.normal(0, n * k, 0.02)
+    qb = quant.quantize(be, fmt, w, n, k)          # device quantizer ...
+    assert np.array_equal(qb, oracle.quantize(int(fmt), w, n, k))  # ... byte-identical to the oracle
+    x = O.normal(1, k)
+    want, _ = oracle.matmul(int(fmt), x, qb, n, k, m=1)
+    got = run_matmul(be, fmt, x, qb, 1, n, k)
+    assert max_rel(got, want) <= 1e-3
+    assert max_rel(got, want) <= 2e-5
+
+
+def test_gemv_special_activations(be, oracle):
+    n, k = 64, 512
+    qb = oracle.quantize(O.Q4_K, O.normal(5, n * k, 0.02), n, k)
+    a = O.normal(6, 2 * k).reshape(2, k)
+    a[0, 32:64] = 0.0          # an all-zero group: d = 0, id = 0
+    a[1, 100] = 1e6            # one huge value flattens its group
+    a[1, 256:288] = 0.5        # ties: x*id lands on .5 boundaries
+    want, _ = oracle.matmul(O.Q4_K, a, qb, n, k, m=2)
+    got = run_matmul(be, lp.DType.Q4K, a, qb, 2, n, k)
+    assert max_rel(got, want) <= 2e-5
+
+
+# ------------------------------------------------------------------ exact-f32 GEMM path
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_gemm_f32_bit_exact_vs_oracle(be, oracle, fmt, name):
+    seed = 70
+    for (batch, m, n, k, pad, epi) in [(1, 9, 45, 256, 0, False), (2, 35, 70, 512, 5, True), (1, 130, 200, 256, 3, True),
+                                       (1, 20, 45, 256, 3, False), (1, 33, 300, 1024, 0, False)]:
+        seed += 1
+        w = rnd(n * k, seed)
+        qb = oracle.quantize(int(fmt), w, n, k)
+        rs = k + pad
+        a = rnd(batch * m * rs, seed + 7)
+        bias = rnd(n, seed + 9) if epi else None
+        want, path = oracle.matmul(int(fmt), a, qb, n, k, batch=batch, m=m, a_view=(0, m * rs, rs), bias=bias, fma=True)
+        assert path == "f32_act"
+        got = run_matmul(be, fmt, a, qb, m, n, k, batch=batch, a_row_stride=rs, bias=bias)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (name, batch, m, n, k)
+
+
+# ------------------------------------------------------------------ views, epilogue, validation
+def test_strided_output_view_and_bias(be, oracle):
+    k, n, off, batch = 64, 40, 7, 3
+    for m in (2, 30):
+        a = rnd(batch * m * k, 100 + m)
+        qb = oracle.quantize(O.INT8, rnd(n * k, 101 + m), n, k)
+        total = off + m * batch * n + 5
+        want = np.full(total, -1.0, np.float32)
+        oracle.matmul(O.INT8, a, qb, n, k, batch=batch, m=m, out=want, out_view=(off, n, batch * n))
+        got = run_matmul(be, lp.DType.Int8, a, qb, m, n, k, batch=batch, out=np.full(total, -1.0, np.float32),
+                         out_view=MatView(off, n, batch * n))
+        touched = want != -1.0
+        assert (got[~touched] == -1.0).all()  # nothing outside the view is written
+        assert max_rel(got[touched], want[touched]) <= (2e-5 if batch * m <= 8 else 0.0)
+    # bias epilogue on the decode path
+    m, n, k = 4, 50, 512
+    qb = oracle.quantize(O.Q6_K, O.normal(9, n * k, 0.02), n, k)
+    a, bias = O.normal(10, m * k), O.normal(11, n)
+    want, _ = oracle.matmul(O.Q6_K, a, qb, n, k, m=m, bias=bias)
+    assert max_rel(run_matmul(be, lp.DType.Q6K, a, qb, m, n, k, bias=bias), want) <= 2e-5
+
+
+def test_zero_sized_launches(be, oracle):
+    qb = oracle.quantize(O.Q4_K, O.normal(1, 4 * 256, 0.02), 4, 256)
+    out = run_matmul(be, lp.DType.Q4K, np.zeros(1, np.float32), qb[:256], 2, 4, 0, out=np.full(8, 9.0, np.float32))
+    assert not out.any()  # k == 0 writes zeros
+    out = run_matmul(be, lp.DType.Q4K, np.zeros(1, np.float32), qb, 0, 4, 256, out=np.full(8, 9.0, np.float32))
+    assert (out == 9.0).all()  # m == 0 is a no-op
+
+
+def test_launch_validation_codes(be, oracle):
+    n, k, m = 4, 256, 2
+    qb = oracle.quantize(O.Q4_K, rnd(n * k, 1), n, k)
+    a = rnd(m * k, 2)
+    bufs = [be.upload(a), be.upload(qb), be.alloc(m * n * 4)]
+
+    def code(l, bs=bufs):
+        with pytest.raises(lp.LapidError) as e:
+            be.execute([l], bs)
+        return e.value.code
+
+    ok = matmul_launch(lp.DType.Q4K, m, n, k)
+    be.execute([ok], bufs)
+    import dataclasses as dc
+    assert code(dc.replace(ok, dims=dc.replace(ok.dims, n=5))) == "out_of_bounds"       # weights too small for [5, k]
+    assert code(dc.replace(ok, dims=dc.replace(ok.dims, b=MatView(0, 0, 512)))) == "shape_mismatch"
+    assert code(dc.replace(ok, dims=dc.replace(ok.dims, b=MatView(1, 0, k)))) == "invalid_launch"
+    assert code(dc.replace(ok, spec=dc.replace(ok.spec, b_transposed=False))) == "invalid_launch"
+    assert code(dc.replace(ok, dims=dc.replace(ok.dims, k=128, b=MatView(0, 0, 128)))) == "invalid_launch"  # k % 256
+    assert code(dc.replace(ok, dims=dc.replace(ok.dims, m=3, out=MatView.contiguous(3, n)))) == "out_of_bounds"
+    assert code(dc.replace(ok, dims=dc.replace(ok.dims, a=MatView(1, m * k, k)))) == "out_of_bounds"
+    assert code(dc.replace(ok, spec=dc.replace(ok.spec, b_dtype=lp.DType.F16))) == "unsupported_dtype"
+    assert code(dc.replace(ok, inputs=(0, 1, 1))) == "invalid_launch"       # 3 inputs without an epilogue
+    assert code(dc.replace(ok, inputs=(0, 7))) == "invalid_launch"          # BufId out of range
+    assert code(dc.replace(ok, inputs=(2, 1))) == "buffer_aliasing"         # input is the output
+    assert code(dc.replace(ok, kind=3)) == "unsupported"
+    # the device stays usable after every rejected launch
+    be.execute([ok], bufs)
+    want, _ = oracle.matmul(O.Q4_K, a, qb, n, k, m=m)
+    assert max_rel(bufs[2].download().view(np.float32), want) <= 2e-5
+
+
+def test_launch_sequences_see_earlier_writes(be, oracle):
+    # launch 2 consumes launch 1's output (o_proj after q_proj in a layer): [1,512] -> [1,256] -> [1,64]
+    w1 = oracle.quantize(O.Q4_K, O.normal(1, 256 * 512, 0.05), 256, 512)
+    w2 = oracle.quantize(O.Q6_K, O.normal(2, 64 * 256, 0.05), 64, 256)
+    x = O.normal(3, 512)
+    bufs = [be.upload(x), be.upload(w1), be.alloc(256 * 4), be.upload(w2), be.alloc(64 * 4)]
+    l1 = matmul_launch(lp.DType.Q4K, 1, 256, 512, inputs=(0, 1), output=2)
+    l2 = matmul_launch(lp.DType.Q6K, 1, 64, 256, inputs=(2, 3), output=4)
+    for _ in range(3):
+        be.execute([l1, l2], bufs)
+    h, _ = oracle.matmul(O.Q4_K, x, w1, 256, 512, m=1)
+    want, _ = oracle.matmul(O.Q6_K, bufs[2].download().view(np.float32), w2, 64, 256, m=1)
+    assert max_rel(bufs[2].download().view(np.float32), h) <= 2e-5
+    assert max_rel(bufs[4].download().view(np.float32), want) <= 2e-5
+
+
+def test_write_then_execute_ordering_and_wrap(be, oracle):
+    import torch
+    n, k = 128, 512
+    qb = oracle.quantize(O.Q4_K, O.normal(1, n * k, 0.02), n, k)
+    wt = torch.from_numpy(qb).cuda()
+    at = torch.zeros(k, device="cuda")
+    ot = torch.zeros(n, device="cuda")
+    torch.cuda.synchronize()
+    bufs = [be.wrap_tensor(at), be.wrap_tensor(wt), be.wrap_tensor(ot)]
+    l = matmul_launch(lp.DType.Q4K, 1, n, k)
+    for seed in (5, 6):
+        x = O.normal(seed, k)
+        bufs[0].write(0, x)
+        be.execute([l], bufs)
+        want, _ = oracle.matmul(O.Q4_K, x, qb, n, k, m=1)
+        assert max_rel(ot.cpu().numpy(), want) <= 2e-5
