@@ -184,8 +184,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     be = lp.Backend(local_rank)
-    if os.environ.get("LAPID_B200_PDL") is not None:
-        be.set_option("pdl", os.environ["LAPID_B200_PDL"])
+    for kv in filter(None, os.environ.get("LAPID_B200_OPTS", "").split(",")):  # e.g. "pdl=0,gemv=generic"
+        key, _, val = kv.partition("=")
+        be.set_option(key, val)
     stream = torch.cuda.Stream(device=dev)
     be.set_stream(stream.cuda_stream)
     peak, peak_kind = measured_peaks()

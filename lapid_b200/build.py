@@ -22,6 +22,7 @@ SOURCES = {
     "quantize.cu": ["-fmad=false"],
     "actquant.cu": ["-fmad=false"],
     "qgemv.cu": [],
+    "qgemv_q4k.cu": [],
     "qgemm_f32.cu": [],
     "backend.cc": ["-x", "cu"],
 }

@@ -18,6 +18,7 @@
 #include <mutex>
 #include <new>
 #include <string>
+#include <vector>
 
 #include "kernels.h"
 
@@ -143,14 +144,19 @@ struct lapid_b200_device {
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
     std::atomic<uint64_t> launches{0};
+    int *status_host = nullptr;  // pinned, mapped: kernels report a bounded wait that gave up here
+    int *status_dev = nullptr;
     bool pdl = true;
     uint32_t gemv_max_rows = 8;
+    bool act_reuse = true;  // share / hoist activation pre-passes inside one launch list
+    bool gemv_fast = true;   // specialised GEMV kernels where the shape allows; off = generic kernel only
     bool gemm_f32 = true;  // exact-f32 GEMM for rows > gemv_max_rows (the tensor-core path is opt-in until built)
 
     void make_current() const { cuda_check(cudaSetDevice(ordinal), "cudaSetDevice"); }
     ~lapid_b200_device() {
         if (cudaSetDevice(ordinal) == cudaSuccess) {
             if (scratch) cudaFree(scratch);
+            if (status_host) cudaFreeHost(status_host);
             if (own_stream) cudaStreamDestroy(own_stream);
         }
     }
@@ -219,6 +225,22 @@ struct Plan {
     uint32_t rows = 0;
     lapid_b200_layout wl{};
     size_t scratch = 0;  // bytes of activation scratch the launch needs
+    bool fast = false;   // specialised Q4_K GEMV (activations as 336-byte records)
+};
+
+// Where the quantized activations of a decode launch live in the scratch, and who makes them.
+struct ActSlot {
+    const void *ptr = nullptr;  // key: the A operand
+    uint64_t off = 0, bs = 0, rs = 0;
+    uint32_t rows = 0, m = 0, k = 0;
+    int records = 0;
+    size_t offset = 0;     // into the device scratch
+    bool hoisted = false;  // quantized by the batched pre-pass at the head of the call
+    bool done = false;
+    bool same(const ActSlot &o) const {
+        return ptr == o.ptr && off == o.off && bs == o.bs && rs == o.rs && rows == o.rows && m == o.m && k == o.k &&
+               records == o.records;
+    }
 };
 
 std::string dims_str(const lapid_b200_launch &l) {
@@ -263,12 +285,16 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
     if (p.gemv) {
         size_t qa = align_up((uint64_t)p.rows * l.k, 256);
         size_t sc = align_up((uint64_t)p.rows * (l.k / 32) * 4, 256);
-        p.scratch = qa + 2 * sc;
+        size_t rec = align_up((uint64_t)p.rows * ((l.k + 255) / 256) * lb::REC, 256);  // record layout of the fast path
+        p.scratch = qa + 2 * sc > rec ? qa + 2 * sc : rec;
+        p.fast = dev.gemv_fast && l.b_dtype == LAPID_B200_DTYPE_Q4_K && l.k % 256 == 0 && l.k >= 256 &&
+                 (size_t)p.rows * (l.k / 256) * lb::REC <= 150 * 1024;
     }
     return p;
 }
 
-void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_buffer *const *buffers, size_t n_buffers) {
+void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_buffer *const *buffers, size_t n_buffers,
+                ActSlot *slot) {
     Plan p = plan_launch(dev, l);
     auto get = [&](uint32_t id) -> lapid_b200_buffer * {
         if (id >= n_buffers || !buffers[id])
@@ -334,7 +360,13 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
     if (((uintptr_t)ins[1]->ptr & 15) != 0) fail("invalid_launch", "b200: quantized B must be 16-byte aligned");
 
     if (p.gemv) {
-        dev.ensure_scratch(p.scratch);
+        ActSlot local;
+        if (!slot) {  // not planned by the caller: a private slot at the start of the scratch
+            dev.ensure_scratch(p.scratch);
+            local.records = p.fast ? 1 : 0;
+            slot = &local;
+        }
+        char *base = (char *)dev.scratch + slot->offset;
         size_t qa_b = align_up((uint64_t)p.rows * l.k, 256), sc_b = align_up((uint64_t)p.rows * (l.k / 32) * 4, 256);
         lb::ActQuantArgs q{};
         q.a = (const float *)ins[0]->ptr;
@@ -344,18 +376,29 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         q.rows = p.rows;
         q.m = (uint32_t)l.m;
         q.k = (uint32_t)l.k;
-        q.qa = (int8_t *)dev.scratch;
-        q.da = (float *)((char *)dev.scratch + qa_b);
-        q.bs = l.b_dtype == LAPID_B200_DTYPE_Q4_K ? (float *)((char *)dev.scratch + qa_b + sc_b) : nullptr;
-        cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl, dev.stream), "act_quant launch");
+        q.qa = (int8_t *)base;
+        q.da = (float *)(base + qa_b);
+        q.bs = l.b_dtype == LAPID_B200_DTYPE_Q4_K ? (float *)(base + qa_b + sc_b) : nullptr;
+        q.records = slot->records;
         g.w = (const uint8_t *)ins[1]->ptr;
         g.w_bytes = ins[1]->bytes;
         g.scales_offset = p.wl.scales_offset;
         g.qa = q.qa;
         g.da = q.da;
         g.bs = q.bs;
-        cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
-        dev.launches += 2;
+        g.a = q.a;
+        g.a_off = q.a_off;
+        g.a_bs = q.a_bs;
+        g.a_rs = q.a_rs;
+        g.status = dev.status_dev;
+        if (!slot->done) {
+            cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl, dev.stream), "act_quant launch");
+            dev.launches++;
+            slot->done = true;
+        }
+        if (slot->records) cuda_check(lb::launch_qgemv_q4k_fast(g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        else cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        dev.launches++;
         return;
     }
     lb::GemmF32Args f{};
@@ -389,8 +432,112 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
     if (nbuf && !buffers) fail("invalid_argument", "buffers is NULL");
     std::lock_guard<std::mutex> lock(dev->mu);
     dev->make_current();
-    for (size_t i = 0; i < n; i++) run_launch(*dev, launches[i], buffers, nbuf);
-    if (wait) cuda_check(cudaStreamSynchronize(dev->stream), "cudaStreamSynchronize");
+    // Plan the activation pre-passes of the decode launches of this list:
+    //  * launches that read the same A operand (q/k/v, gate/up) share one quantized copy, as long
+    //    as no launch in between writes the buffer it comes from;
+    //  * operands that no earlier launch of the list writes do not depend on anything in the
+    //    list, so their pre-passes are hoisted into one batched launch at the head of the call
+    //    and the GEMVs then follow each other directly.
+    std::vector<ActSlot> slots;
+    std::vector<int> slot_of(n, -1);
+    size_t scratch_total = 0;
+    {
+        struct Range { const char *lo, *hi; };
+        std::vector<Range> written;
+        int last = -1;  // most recent slot, reusable by a non-hoisted launch
+        for (size_t i = 0; i < n; i++) {
+            const lapid_b200_launch &l = launches[i];
+            if (l.kind != LAPID_B200_KERNEL_MATMUL || !is_quant(l.b_dtype)) break;  // run_launch reports it
+            Plan p = plan_launch(*dev, l);
+            lapid_b200_buffer *ab = l.n_inputs > 0 && l.inputs[0] < nbuf ? buffers[l.inputs[0]] : nullptr;
+            lapid_b200_buffer *ob = l.output < nbuf ? buffers[l.output] : nullptr;
+            if (p.gemv && ab) {
+                ActSlot key;
+                key.ptr = ab->ptr;
+                key.off = l.a.offset;
+                key.bs = l.a.batch_stride;
+                key.rs = l.a.row_stride;
+                key.rows = p.rows;
+                key.m = (uint32_t)l.m;
+                key.k = (uint32_t)l.k;
+                key.records = p.fast ? 1 : 0;
+                bool clean = true;  // nothing in the list so far wrote the buffer A lives in
+                for (const Range &w : written)
+                    if ((const char *)ab->ptr < w.hi && w.lo < (const char *)ab->ptr + ab->bytes) clean = false;
+                int found = -1;
+                if (dev->act_reuse) {
+                    if (clean) {
+                        for (size_t s2 = 0; s2 < slots.size(); s2++)
+                            if (slots[s2].hoisted && slots[s2].same(key)) found = (int)s2;
+                    } else if (last >= 0 && slots[last].same(key) && !slots[last].hoisted) {
+                        found = last;  // same operand as the launch right before, not rewritten since (checked below)
+                    }
+                }
+                if (found < 0) {
+                    key.hoisted = clean && dev->act_reuse;
+                    key.offset = scratch_total;
+                    scratch_total += p.scratch;
+                    slots.push_back(key);
+                    found = (int)slots.size() - 1;
+                }
+                slot_of[i] = found;
+                last = found;
+            }
+            if (ob && !p.noop) {
+                written.push_back({(const char *)ob->ptr, (const char *)ob->ptr + ob->bytes});
+                // a write into the buffer the latest non-hoisted slot was read from invalidates it
+                if (last >= 0 && !slots[last].hoisted && (const char *)slots[last].ptr >= (const char *)ob->ptr &&
+                    (const char *)slots[last].ptr < (const char *)ob->ptr + ob->bytes)
+                    last = -1;
+            }
+        }
+    }
+    dev->ensure_scratch(scratch_total);
+    {
+        lb::ActQuantBatch batch;
+        batch.count = 0;
+        uint64_t groups = 0;
+        auto flush = [&]() {
+            if (batch.count == 0) return;
+            cuda_check(lb::launch_act_quant_batch(batch, dev->sm_count, dev->pdl, dev->stream), "act_quant launch");
+            dev->launches++;
+            batch.count = 0;
+            groups = 0;
+        };
+        for (ActSlot &sl : slots) {
+            if (!sl.hoisted) continue;
+            char *base = (char *)dev->scratch + sl.offset;
+            size_t qa_b = align_up((uint64_t)sl.rows * sl.k, 256), sc_b = align_up((uint64_t)sl.rows * (sl.k / 32) * 4, 256);
+            lb::ActQuantArgs &q = batch.item[batch.count];
+            q = lb::ActQuantArgs{};
+            q.a = (const float *)sl.ptr;
+            q.a_off = sl.off;
+            q.a_bs = sl.bs;
+            q.a_rs = sl.rs;
+            q.rows = sl.rows;
+            q.m = sl.m;
+            q.k = sl.k;
+            q.qa = (int8_t *)base;
+            q.da = (float *)(base + qa_b);
+            q.bs = (float *)(base + qa_b + sc_b);  // written for every format; only Q4_K reads it
+            q.records = sl.records;
+            groups += (uint64_t)sl.rows * (sl.k / 32);
+            batch.group_end[batch.count] = groups;
+            batch.count++;
+            sl.done = true;
+            if (batch.count == lb::ACT_BATCH_MAX) flush();
+        }
+        flush();
+    }
+    for (size_t i = 0; i < n; i++) run_launch(*dev, launches[i], buffers, nbuf, slot_of[i] >= 0 ? &slots[slot_of[i]] : nullptr);
+    if (wait) {
+        cuda_check(cudaStreamSynchronize(dev->stream), "cudaStreamSynchronize");
+        if (*dev->status_host != 0) {
+            int st = *dev->status_host;
+            *dev->status_host = 0;
+            fail("backend", "a device-side wait gave up (status " + std::to_string(st) + "); the results of this call are invalid");
+        }
+    }
 }
 
 }  // namespace
@@ -431,6 +578,9 @@ lapid_b200_status lapid_b200_device_open(int32_t ordinal, lapid_b200_device **ou
             d->make_current();
             cuda_check(cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking), "cudaStreamCreate");
             d->stream = d->own_stream;
+            cuda_check(cudaHostAlloc((void **)&d->status_host, sizeof(int), cudaHostAllocMapped), "cudaHostAlloc");
+            *d->status_host = 0;
+            cuda_check(cudaHostGetDevicePointer((void **)&d->status_dev, d->status_host, 0), "cudaHostGetDevicePointer");
         } catch (...) {
             delete d;
             throw;
@@ -483,6 +633,14 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             int r = std::atoi(value);
             if (r < 0 || r > 8) fail("invalid_argument", "gemv_max_rows must be in 0..8");
             dev->gemv_max_rows = (uint32_t)r;
+        } else if (k == "gemv") {
+            if (v == "fast") dev->gemv_fast = true;
+            else if (v == "generic") dev->gemv_fast = false;
+            else fail("invalid_argument", "gemv must be \"fast\" or \"generic\"");
+        } else if (k == "act_reuse") {
+            dev->act_reuse = v != "0";
+        } else if (k == "gemv_ctas_per_sm") {
+            lb::qgemv_q4k_fast_set_cta_cap(std::atoi(value));
         } else if (k == "gemm") {
             if (v == "f32") dev->gemm_f32 = true;
             else fail("invalid_argument", "gemm must be \"f32\"");
@@ -578,11 +736,8 @@ lapid_b200_status lapid_b200_prepare(lapid_b200_device *dev, const lapid_b200_la
         if (n && !launches) fail("invalid_argument", "launches is NULL");
         std::lock_guard<std::mutex> lock(dev->mu);
         dev->make_current();
-        size_t scratch = 0;
-        for (size_t i = 0; i < n; i++) {
-            Plan p = plan_launch(*dev, launches[i]);
-            if (p.scratch > scratch) scratch = p.scratch;
-        }
+        size_t scratch = 0;  // every decode launch may get its own slot (see execute)
+        for (size_t i = 0; i < n; i++) scratch += plan_launch(*dev, launches[i]).scratch;
         dev->ensure_scratch(scratch);
     });
 }

@@ -26,8 +26,20 @@ struct ActQuantArgs {
     int8_t *qa;
     float *da;
     float *bs;
+    // records != 0: instead of the three planes, write one ACT_RECORD-byte record per
+    // (row, 256-element block) at qa: four times [64 quants | da_2p da_2p+1 bs_2p bs_2p+1], 16 pad.
+    int records;
 };
+constexpr int REC = 336;
 cudaError_t launch_act_quant(const ActQuantArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+// Up to ACT_BATCH_MAX operands in one launch; group_end[i] = running total of 32-groups.
+constexpr int ACT_BATCH_MAX = 24;
+struct ActQuantBatch {
+    ActQuantArgs item[ACT_BATCH_MAX];
+    uint64_t group_end[ACT_BATCH_MAX];
+    int count;
+};
+cudaError_t launch_act_quant_batch(const ActQuantBatch &batch, int sm_count, bool pdl, cudaStream_t stream);
 
 // ---- qgemv.cu
 struct GemvArgs {
@@ -37,6 +49,9 @@ struct GemvArgs {
     const int8_t *qa;       // quantized activations, see ActQuantArgs
     const float *da;
     const float *bs;
+    const float *a;         // f32 activations (kernels that quantize them in their prologue)
+    uint64_t a_off, a_bs, a_rs;
+    int *status;            // host-visible word; a kernel ORs a bit in when one of its bounded waits gave up
     float *out;             // row r = bt*m + i at out + out_off + bt*out_bs + i*out_rs
     uint64_t out_off, out_bs, out_rs;
     const float *extra;     // epilogue `acc + extra[bt, i, j]`, nullptr for none
@@ -48,6 +63,12 @@ struct GemvArgs {
 cudaError_t launch_qgemv(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // Opt in to the dynamic shared memory the GEMV variants need; once per device.
 cudaError_t qgemv_init();
+
+// ---- qgemv_q4k.cu: fast path for Q4_K with 1..4 rows
+// Reads the activations as 336-byte records (ActQuantArgs::records) from args.qa.
+bool qgemv_q4k_fast_supported(const GemvArgs &args);
+cudaError_t launch_qgemv_q4k_fast(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+void qgemv_q4k_fast_set_cta_cap(int cap);  // tuning: at most this many CTAs per SM (0 = as many as fit)
 
 // out[bt, i, j] = 0 (+ extra) for the k == 0 case (crates/lapid-cpu/src/matmul/mod.rs:237-247).
 cudaError_t launch_fill_zero_k(const GemvArgs &args, cudaStream_t stream);

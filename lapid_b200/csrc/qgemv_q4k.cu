@@ -1,0 +1,321 @@
+// Q4_K decode GEMV, fast path for 1..8 activation rows (arithmetic: see qgemv.cu; this file only
+// changes how the work is laid out on the machine).
+//
+//  * Weights reach the SM through per-warp rings of shared-memory stages filled by the bulk-copy
+//    engine (`cp.async.bulk` global -> shared, completion on an mbarrier): one instruction, issued
+//    by one lane, moves the 4.6 KB of contiguous weight bytes a warp consumes per step (32
+//    super-blocks). No registers or load/store-unit slots are spent on the stream, requests are
+//    whole 128-byte lines, and a warp never waits for another warp.
+//  * One lane owns one 144-byte super-block of the stage (nine conflict-free 128-bit shared
+//    loads: the lane stride of 144 = 9*16 bytes walks all bank groups). G lanes (8, 16 or 32,
+//    the power of two covering K/256) share one weight row; a warp works on 32/G rows at once
+//    and finishes a row with log2(G) shuffles.
+//  * The 12 packed scale/min bytes of a block are decoded for all eight sub-blocks with eight
+//    logic operations on three words; high nibbles are used in place (16*q, an exact power of
+//    two folded into the scale), so unpacking costs two logic operations per word.
+//  * The int8 activations live in shared memory as one 336-byte record per (row, super-block):
+//    four times [64 quants | da_2p da_2p+1 bs_2p bs_2p+1], padded so that the lanes' 128-bit
+//    reads (stride 336 = 21*16 bytes) are bank-conflict free. The pre-pass kernel writes the
+//    records in this layout; the prologue copies them with `cp.async`, all copies in flight at
+//    once (one L2 round trip, hidden behind the weight requests).
+//  * The rings are filled before the programmatic-dependent-launch wait: weights never depend on
+//    the kernel that produces the activations, so they stream while that kernel still runs.
+//  * Every mbarrier wait is bounded; a wait that gives up records it in a host-visible status
+//    word and the kernel runs to its end (with a wrong result that the host then rejects).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lb {
+
+constexpr int STAGE_BYTES = 32 * Q4K_BYTES;  // 4608
+constexpr int BAR_BYTES = 256;               // warps * STAGES * 8 <= 256
+
+__device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(s32(dst)),
+                 "l"(src), "r"(bytes), "r"(s32(bar))
+                 : "memory");
+}
+// Bounded wait for the phase with the given parity. Returns false when it gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < (1u << 22); spin++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(s32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// unsigned bytes of a (0..240) times signed bytes of b
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ float u8f(uint32_t w, int byte) { return (float)((w >> (8 * byte)) & 0xffu); }
+
+// float(byte `sel` of w) * d, exactly: the byte is planted in the mantissa of 2^23 with one PRMT and
+// the bias is removed inside one fused multiply-add (d * (2^23 + b) - d * 2^23 = d * b needs 17
+// bits, so the result is exact and equals the reference's separately rounded d * f32(b)).
+__device__ __forceinline__ float scale_byte(uint32_t w, uint32_t sel, float d, float neg_d23) {
+    return fmaf(d, __uint_as_float(__byte_perm(w, 0x4B000000u, sel)), neg_d23);
+}
+
+// One 64-weight pair of a super-block against one activation row: two groups of 32.
+__device__ __forceinline__ float pair_dot(const uint32_t (&v)[8], const uint32_t (&al)[8], const uint32_t (&ah)[8], float s0,
+                                          float m0, float s1, float m1, float da0, float da1, float bs0, float bs1,
+                                          float acc) {
+    int l0 = 0, l1 = 0, h0 = 0, h1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        l0 = dp4a_us(v[i] & 0x0F0F0F0Fu, al[i], l0);
+        l1 = dp4a_us(v[i + 4] & 0x0F0F0F0Fu, al[i + 4], l1);
+        h0 = dp4a_us(v[i] & 0xF0F0F0F0u, ah[i], h0);
+        h1 = dp4a_us(v[i + 4] & 0xF0F0F0F0u, ah[i + 4], h1);
+    }
+    acc = fmaf(s0 * da0, (float)(l0 + l1), acc);
+    acc = fmaf(-m0, bs0, acc);
+    acc = fmaf(s1 * da1, (float)(h0 + h1), acc);
+    acc = fmaf(-m1, bs1, acc);
+    return acc;
+}
+
+// REGACT: one activation row whose super-block index per lane never changes (K/256 <= G): the
+// lane keeps its 336-byte activation record in registers for the whole kernel.
+// Warps per CTA: small CTAs for one or two rows (many CTAs per SM, so that one slot can be left to
+// the next kernel), larger ones beyond, where the activation records are the bigger share of the
+// shared memory and are better amortised over more warps.
+template <int M> struct Shape { static constexpr int WARPS = M <= 2 ? 4 : 8, MIN_CTAS = M <= 2 ? 5 : 2; };
+
+template <int M, int G, bool REGACT>
+__global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_q4k_fast_kernel(GemvArgs p) {
+    constexpr int STAGES = 2;
+    constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int RPW = 32 / G;
+    const int sub = lane / G, gl = lane % G;
+    const uint32_t n = p.n, nblk = p.k / QK;
+    const uint32_t iters = (nblk + G - 1) / G;
+    const uint32_t tasks = (n + RPW - 1) / RPW;
+    // CTA c owns tasks [t_lo, t_hi); its warps take them round-robin
+    const uint32_t t_lo = (uint32_t)(((uint64_t)tasks * blockIdx.x) / gridDim.x);
+    const uint32_t t_hi = (uint32_t)(((uint64_t)tasks * (blockIdx.x + 1)) / gridDim.x);
+
+    uint64_t *bars = (uint64_t *)smem + warp * STAGES;
+    uint8_t *ring = smem + BAR_BYTES + (size_t)warp * (STAGES * STAGE_BYTES);
+    uint8_t *acts = smem + BAR_BYTES + (size_t)FAST_WARPS * STAGES * STAGE_BYTES;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; s++) mbar_init(bars + s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    // producer cursor (task, step within the task, ring slot)
+    uint32_t pt = t_lo + warp, pit = 0, pslot = 0;
+    // One stage = the contiguous run of super-blocks the warp consumes in one step: all blocks of
+    // its 32/G rows when a row fits in G lanes, else 32 blocks of its single row.
+    auto issue = [&]() {
+        if (pt >= t_hi) return;
+        if (lane == 0) {
+            const uint32_t row0 = pt * RPW;
+            uint32_t first, count;
+            if (iters == 1) {
+                first = row0 * nblk;
+                count = min((uint32_t)RPW, n - row0) * nblk;
+            } else {
+                first = row0 * nblk + pit * 32;
+                count = min(32u, nblk - pit * 32);
+            }
+            mbar_expect_tx(bars + pslot, count * Q4K_BYTES);
+            bulk_g2s(ring + (size_t)pslot * STAGE_BYTES, p.w + (uint64_t)first * Q4K_BYTES, count * Q4K_BYTES, bars + pslot);
+        }
+        pslot ^= 1;
+        if (++pit == iters) {
+            pit = 0;
+            pt += FAST_WARPS;
+        }
+    };
+    issue();
+    issue();
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    uint32_t ra[REGACT ? 80 : 1];
+    if constexpr (REGACT) {
+        const uint4 *src = (const uint4 *)((const uint8_t *)p.qa + (size_t)min((uint32_t)gl, nblk - 1) * REC);
+#pragma unroll
+        for (int i = 0; i < 20; i++) {
+            const uint4 t = __ldg(src + i);
+            ra[4 * i] = t.x; ra[4 * i + 1] = t.y; ra[4 * i + 2] = t.z; ra[4 * i + 3] = t.w;
+        }
+    } else {
+        const uint32_t chunks = p.rows * nblk * (REC / 16);
+        const uint8_t *src = (const uint8_t *)p.qa;
+        for (uint32_t c = threadIdx.x; c < chunks; c += FAST_THREADS)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(acts + 16 * c)), "l"(src + 16 * (size_t)c) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+    }
+
+    float acc[M];
+    bool healthy = true;
+    uint32_t cslot = 0, cpar = 0;
+    for (uint32_t t = t_lo + warp; t < t_hi; t += FAST_WARPS) {
+        const uint32_t row = t * RPW + sub;
+#pragma unroll
+        for (int r = 0; r < M; r++) acc[r] = 0.0f;
+        for (uint32_t it = 0; it < iters; it++) {
+            if (healthy && !mbar_wait(bars + cslot, cpar)) {
+                healthy = false;
+                if (lane == 0 && p.status) atomicOr(p.status, 1);
+            }
+            const uint32_t b = it * G + gl;
+            if (healthy && row < n && b < nblk && gl < nblk) {
+                const uint8_t *blk = ring + (size_t)cslot * STAGE_BYTES + (size_t)(iters == 1 ? sub * nblk + gl : gl) * Q4K_BYTES;
+                const uint4 h = *(const uint4 *)blk;
+                const float d = half_bits_to_float(h.x & 0xffff), dmin = half_bits_to_float(h.x >> 16);
+                const float nd = d * -8388608.0f, ndmin = dmin * -8388608.0f;
+                const uint32_t w0 = h.y, w1 = h.z, w2 = h.w;
+                // bytes: sc_lo = scales 0..3, sc_hi = scales 4..7, likewise the mins
+                const uint32_t sc_lo = w0 & 0x3F3F3F3Fu, mn_lo = w1 & 0x3F3F3F3Fu;
+                const uint32_t sc_hi = (w2 & 0x0F0F0F0Fu) | (((w0 >> 6) & 0x03030303u) << 4);
+                const uint32_t mn_hi = ((w2 >> 4) & 0x0F0F0F0Fu) | (((w1 >> 6) & 0x03030303u) << 4);
+#pragma unroll
+                for (int pp = 0; pp < 4; pp++) {
+                    const uint32_t scw = pp < 2 ? sc_lo : sc_hi, mnw = pp < 2 ? mn_lo : mn_hi;
+                    const uint32_t sel0 = 0x7440u + 2 * (pp & 1), sel1 = sel0 + 1;  // {byte, 0, 0, 0x4B}
+                    const float s0 = scale_byte(scw, sel0, d, nd), m0 = scale_byte(mnw, sel0, dmin, ndmin);
+                    // the high nibbles are used as 16*q: fold the exact factor 1/16 into their scale
+                    const float s1 = scale_byte(scw, sel1, d, nd) * 0.0625f, m1 = scale_byte(mnw, sel1, dmin, ndmin);
+                    const uint4 qa_ = *(const uint4 *)(blk + 16 + 32 * pp), qb_ = *(const uint4 *)(blk + 32 + 32 * pp);
+                    const uint32_t v[8] = {qa_.x, qa_.y, qa_.z, qa_.w, qb_.x, qb_.y, qb_.z, qb_.w};
+                    if constexpr (REGACT) {
+                        const uint32_t al[8] = {ra[20 * pp], ra[20 * pp + 1], ra[20 * pp + 2], ra[20 * pp + 3],
+                                                ra[20 * pp + 4], ra[20 * pp + 5], ra[20 * pp + 6], ra[20 * pp + 7]};
+                        const uint32_t ah[8] = {ra[20 * pp + 8], ra[20 * pp + 9], ra[20 * pp + 10], ra[20 * pp + 11],
+                                                ra[20 * pp + 12], ra[20 * pp + 13], ra[20 * pp + 14], ra[20 * pp + 15]};
+                        acc[0] = pair_dot(v, al, ah, s0, m0, s1, m1, __uint_as_float(ra[20 * pp + 16]), __uint_as_float(ra[20 * pp + 17]),
+                                          __uint_as_float(ra[20 * pp + 18]), __uint_as_float(ra[20 * pp + 19]), acc[0]);
+                    } else {
+#pragma unroll
+                        for (int r = 0; r < M; r++) {
+                            const uint4 *rec = (const uint4 *)(acts + ((size_t)r * nblk + b) * REC + 80 * pp);
+                            const uint4 a0 = rec[0], a1 = rec[1], a2 = rec[2], a3 = rec[3], sc = rec[4];
+                            const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                            const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+                            acc[r] = pair_dot(v, al, ah, s0, m0, s1, m1, __uint_as_float(sc.x), __uint_as_float(sc.y),
+                                              __uint_as_float(sc.z), __uint_as_float(sc.w), acc[r]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();  // every lane is done reading the slot before it is refilled
+            issue();
+            cslot ^= 1;
+            if (cslot == 0) cpar ^= 1;
+        }
+#pragma unroll
+        for (int r = 0; r < M; r++) {
+            float v = acc[r];
+#pragma unroll
+            for (int o = G / 2; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (gl == 0 && row < n) {
+                const uint32_t bt = r / p.m, i = r % p.m;
+                if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
+                p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
+            }
+        }
+    }
+}
+
+static int g_cta_cap = 0;  // 0 = as many CTAs per SM as fit; set through qgemv_q4k_fast_set_cta_cap
+
+void qgemv_q4k_fast_set_cta_cap(int cap) { g_cta_cap = cap; }
+
+template <int M, int G, bool REGACT>
+static cudaError_t launch_fast(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t stream) {
+    auto kern = qgemv_q4k_fast_kernel<M, G, REGACT>;
+    constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
+    const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * STAGE_BYTES + (REGACT ? 0 : (size_t)a.rows * (a.k / QK) * REC);
+    static size_t configured = 0, occ_smem = 0;
+    static int ctas_per_sm = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
+    if (ctas_per_sm == 0 || occ_smem != smem) {
+        int occ = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, FAST_THREADS, smem);
+        if (e != cudaSuccess) return e;
+        ctas_per_sm = occ > 0 ? occ : 1;
+        occ_smem = smem;
+    }
+    // Leave one CTA slot per SM to the next kernel of the stream: under programmatic dependent
+    // launch its CTAs move in while this kernel still runs and fill their rings, so the weight
+    // stream does not stop at the kernel boundary.
+    int per_sm = ctas_per_sm >= 4 ? ctas_per_sm - 1 : ctas_per_sm;
+    if (g_cta_cap > 0) per_sm = g_cta_cap < ctas_per_sm ? g_cta_cap : ctas_per_sm;
+    constexpr int RPW = 32 / G;
+    const uint32_t tasks = (a.n + RPW - 1) / RPW;
+    // every SM gets the same number of CTAs and every CTA the same share of the tasks
+    uint32_t grid = (uint32_t)sm_count * (uint32_t)per_sm;
+    const uint32_t useful = (tasks + FAST_WARPS - 1) / FAST_WARPS;
+    if (grid > useful) grid = useful;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(FAST_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, a);
+}
+
+template <int M> static cudaError_t launch_fast_g(const GemvArgs &a, int sm, bool pdl, cudaStream_t s) {
+    const uint32_t nblk = a.k / QK;
+    if (nblk <= 8) return launch_fast<M, 8, false>(a, sm, pdl, s);
+    if (nblk <= 16) return launch_fast<M, 16, false>(a, sm, pdl, s);
+    return launch_fast<M, 32, false>(a, sm, pdl, s);
+}
+
+bool qgemv_q4k_fast_supported(const GemvArgs &a) {
+    return a.rows >= 1 && a.rows <= 8 && a.k % QK == 0 && a.k >= QK &&
+           (size_t)a.rows * (a.k / QK) * REC <= 150 * 1024 && ((uintptr_t)a.w & 15) == 0;
+}
+
+cudaError_t launch_qgemv_q4k_fast(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
+    switch (a.rows) {
+        case 1: return launch_fast_g<1>(a, sm_count, pdl, s);
+        case 2: return launch_fast_g<2>(a, sm_count, pdl, s);
+        case 3: return launch_fast_g<3>(a, sm_count, pdl, s);
+        case 4: return launch_fast_g<4>(a, sm_count, pdl, s);
+        case 5: return launch_fast_g<5>(a, sm_count, pdl, s);
+        case 6: return launch_fast_g<6>(a, sm_count, pdl, s);
+        case 7: return launch_fast_g<7>(a, sm_count, pdl, s);
+        case 8: return launch_fast_g<8>(a, sm_count, pdl, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace lb

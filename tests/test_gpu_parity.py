@@ -171,7 +171,8 @@ def test_gemv_reference_test_shapes(be, oracle, fmt, name):
     # kquant_matmul_matches_dequantized_f32 (m <= 8 rows), with row padding, vs oracle and vs f64
     seed = 50
     for (m, n, k, pad) in [(1, 37, 512, 0), (3, 20, 256, 4), (6, 9, 256, 0), (1, 36, 768, 0), (3, 36, 768, 1),
-                           (2, 1030, 4096, 0), (8, 77, 14336, 0), (1, 5, 2304, 0)]:
+                           (2, 1030, 4096, 0), (8, 77, 14336, 0), (1, 5, 2304, 0), (4, 50, 14336, 0), (3, 40, 8192, 8),
+                           (2, 3, 16384, 0), (1, 300, 28672, 0)]:
         if fmt != lp.DType.Int8 and k % 256:
             continue
         seed += 1
@@ -335,3 +336,38 @@ def test_write_then_execute_ordering_and_wrap(be, oracle):
         be.execute([l], bufs)
         want, _ = oracle.matmul(O.Q4_K, x, qb, n, k, m=1)
         assert max_rel(ot.cpu().numpy(), want) <= 2e-5
+
+
+def test_activation_sharing_and_hoisting(be, oracle):
+    """Launches that read the same input share one activation pre-pass, pre-passes of inputs that
+    the list does not write are hoisted to its head, and a write to the input in between is seen."""
+    k = 256
+    ws = [oracle.quantize(O.Q4_K, O.normal(30 + i, k * k, 0.08), k, k) for i in range(4)]
+    x = O.normal(40, k)
+    # buffers: 0 x, 1..4 weights, 5..7 outputs of q/k/v, 8 out of launch 5
+    bufs = [be.upload(x)] + [be.upload(w) for w in ws] + [be.alloc(k * 4) for _ in range(4)]
+    ls = [matmul_launch(lp.DType.Q4K, 1, k, k, inputs=(0, 1), output=5),
+          matmul_launch(lp.DType.Q4K, 1, k, k, inputs=(0, 2), output=6),
+          matmul_launch(lp.DType.Q4K, 1, k, k, inputs=(0, 3), output=7),
+          matmul_launch(lp.DType.Q4K, 1, k, k, inputs=(5, 4), output=0),   # overwrites x with W4 . out_q
+          matmul_launch(lp.DType.Q4K, 1, k, k, inputs=(0, 1), output=8)]   # must see the new x
+    be.prepare(ls)
+    for opt in ("1", "0"):
+        be.set_option("act_reuse", opt)
+        bufs[0].write(0, x)
+        be.take_launch_count()
+        be.execute(ls, bufs)
+        launched = be.take_launch_count()
+        q1, _ = oracle.matmul(O.Q4_K, x, ws[0], k, k, m=1)
+        q2, _ = oracle.matmul(O.Q4_K, x, ws[1], k, k, m=1)
+        q3, _ = oracle.matmul(O.Q4_K, x, ws[2], k, k, m=1)
+        got1 = bufs[5].download().view(np.float32)
+        x2, _ = oracle.matmul(O.Q4_K, got1, ws[3], k, k, m=1)
+        got_x2 = bufs[0].download().view(np.float32)
+        q5, _ = oracle.matmul(O.Q4_K, got_x2, ws[0], k, k, m=1)
+        for got, want in ((got1, q1), (bufs[6].download().view(np.float32), q2), (bufs[7].download().view(np.float32), q3),
+                          (got_x2, x2), (bufs[8].download().view(np.float32), q5)):
+            assert max_rel(got, want) <= 2e-5
+        # 5 GEMVs; pre-passes: one shared by q/k/v (hoisted), one for out_q, one for the rewritten x
+        assert launched == (8 if opt == "1" else 10)
+    be.set_option("act_reuse", "1")
