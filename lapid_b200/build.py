@@ -24,6 +24,7 @@ SOURCES = {
     "qgemv.cu": [],
     "qgemv_q4k.cu": [],
     "qgemm_f32.cu": [],
+    "qgemm_tc.cu": [],
     "backend.cc": ["-x", "cu"],
 }
 

@@ -150,7 +150,7 @@ struct lapid_b200_device {
     uint32_t gemv_max_rows = 8;
     bool act_reuse = true;  // share / hoist activation pre-passes inside one launch list
     bool gemv_fast = true;   // specialised GEMV kernels where the shape allows; off = generic kernel only
-    bool gemm_f32 = true;  // exact-f32 GEMM for rows > gemv_max_rows (the tensor-core path is opt-in until built)
+    bool gemm_f32 = false;  // true: rows > gemv_max_rows always take the exact-f32 GEMM instead of the tensor cores
 
     void make_current() const { cuda_check(cudaSetDevice(ordinal), "cudaSetDevice"); }
     ~lapid_b200_device() {
@@ -226,6 +226,7 @@ struct Plan {
     lapid_b200_layout wl{};
     size_t scratch = 0;  // bytes of activation scratch the launch needs
     bool fast = false;   // specialised Q4_K GEMV (activations as 336-byte records)
+    bool tc = false;     // tensor-core GEMM (needs a bf16 copy of the activations in the scratch)
 };
 
 // Where the quantized activations of a decode launch live in the scratch, and who makes them.
@@ -289,6 +290,9 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
         p.scratch = qa + 2 * sc > rec ? qa + 2 * sc : rec;
         p.fast = dev.gemv_fast && l.b_dtype == LAPID_B200_DTYPE_Q4_K && l.k % 256 == 0 && l.k >= 256 &&
                  (size_t)p.rows * (l.k / 256) * lb::REC <= 150 * 1024;
+    } else {
+        p.tc = !dev.gemm_f32 && l.b_dtype == LAPID_B200_DTYPE_Q4_K && l.k % 256 == 0 && l.k >= 256;
+        if (p.tc) p.scratch = align_up(lb::qgemm_tc_scratch_bytes(p.rows, (uint32_t)l.k), 256);
     }
     return p;
 }
@@ -401,6 +405,36 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         dev.launches++;
         return;
     }
+    if (p.tc) {
+        lb::GemmTcArgs t{};
+        t.w = (const uint8_t *)ins[1]->ptr;
+        t.a = (const float *)ins[0]->ptr;
+        t.a_off = l.a.offset;
+        t.a_bs = l.a.batch_stride;
+        t.a_rs = l.a.row_stride;
+        t.out = g.out;
+        t.out_off = g.out_off;
+        t.out_bs = g.out_bs;
+        t.out_rs = g.out_rs;
+        t.extra = extra;
+        t.ex_off = g.ex_off;
+        t.ex_s0 = g.ex_s0;
+        t.ex_s1 = g.ex_s1;
+        t.ex_s2 = g.ex_s2;
+        t.rows = p.rows;
+        t.m = g.m;
+        t.n = g.n;
+        t.k = g.k;
+        t.status = dev.status_dev;
+        if (lb::qgemm_tc_supported(l.b_dtype, t)) {
+            size_t off = 0;
+            if (slot) off = slot->offset;
+            else dev.ensure_scratch(p.scratch);
+            cuda_check(lb::launch_qgemm_tc(t, (char *)dev.scratch + off, dev.sm_count, dev.stream), "qgemm_tc launch");
+            dev.launches += 2;
+            return;
+        }
+    }
     lb::GemmF32Args f{};
     f.w = (const uint8_t *)ins[1]->ptr;
     f.scales_offset = p.wl.scales_offset;
@@ -482,6 +516,13 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
                 }
                 slot_of[i] = found;
                 last = found;
+            }
+            if (p.tc) {
+                ActSlot sl;
+                sl.offset = scratch_total;
+                scratch_total += p.scratch;
+                slots.push_back(sl);
+                slot_of[i] = (int)slots.size() - 1;
             }
             if (ob && !p.noop) {
                 written.push_back({(const char *)ob->ptr, (const char *)ob->ptr + ob->bytes});
@@ -643,7 +684,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             lb::qgemv_q4k_fast_set_cta_cap(std::atoi(value));
         } else if (k == "gemm") {
             if (v == "f32") dev->gemm_f32 = true;
-            else fail("invalid_argument", "gemm must be \"f32\"");
+            else if (v == "tc") dev->gemm_f32 = false;
+            else fail("invalid_argument", "gemm must be \"tc\" or \"f32\"");
         } else {
             fail("invalid_argument", "unknown option \"" + k + "\"");
         }

@@ -89,4 +89,21 @@ struct GemmF32Args {
 };
 cudaError_t launch_qgemm_f32(int fmt, const GemmF32Args &args, cudaStream_t stream);
 
+// ---- qgemm_tc.cu: tcgen05 tensor-core GEMM (Q4_K weights, bf16 operands, f32 accumulation)
+struct GemmTcArgs {
+    const uint8_t *w;
+    const float *a;
+    uint64_t a_off, a_bs, a_rs;
+    float *out;
+    uint64_t out_off, out_bs, out_rs;
+    const float *extra;
+    uint64_t ex_off;
+    int64_t ex_s0, ex_s1, ex_s2;
+    uint32_t rows, m, n, k;
+    int *status;
+};
+bool qgemm_tc_supported(int fmt, const GemmTcArgs &args);
+size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t k);  // bf16 copy of the activations
+cudaError_t launch_qgemm_tc(const GemmTcArgs &args, void *a_bf16_scratch, int sm_count, cudaStream_t stream);
+
 }  // namespace lb

@@ -1,0 +1,366 @@
+// Prefill GEMM on the 5th-generation tensor cores: out[m, n] = sum_k A[m, k] * dequant(W)[n, k] for
+// Q4_K weights, bf16 operands, f32 accumulation in tensor memory.
+//
+// Reference semantics: lapid-cpu's path for more than 8 rows multiplies f32 activations by the
+// dequantized f32 weights (crates/lapid-cpu/src/matmul/qdeq.rs:57-123); lapid-cuda's tensor-core
+// kernel rounds both operands to f16 (crates/lapid-cuda/src/codegen/kquant.rs:335-519). Here both
+// operands are rounded to bf16 (weights: bf16 of lapid-quant's f32 value d1*q - m1, computed with
+// one fused multiply-add), products are exact and sums are f32, so the result differs from the
+// f32 reference by the operand rounding only (2^-9 relative per operand).
+//
+// One CTA computes a 128 (weight rows) x MT (activation rows, 64/128/256) output tile, K in steps
+// of 64 (one Q4_K "pair": 32 bytes of quants = two 32-element sub-blocks):
+//   warp 0     one lane drives TMA: per super-block a 2-D tensor-map copy of the 128 rows' packed
+//              144-byte blocks (`cp.async.bulk.tensor.2d`, no multicast), per k-step a 128-byte
+//              swizzled copy of the bf16 activation tile
+//   warp 1     allocates tensor memory; one lane issues `tcgen05.mma` (M=128, N=MT, K=16, four
+//              per k-step) on shared-memory descriptors and commits to mbarriers
+//   warps 2-9  dequantize: thread (row, half) expands one 32-element sub-block per k-step from
+//              the staged packed bytes to bf16 and stores it in the 128-byte-swizzled K-major
+//              layout the tensor core reads; afterwards they are the epilogue: `tcgen05.ld`
+//              32 lanes x 32 columns at a time, optional `+ extra`, coalesced f32 stores
+// The weight tile is the M side of the MMA and the activations the N side, so 64 prefill rows
+// use a 128x64 instruction at full rate instead of padding to 128 rows.
+// Every mbarrier wait is bounded: a wait that gives up sets a bit in the host-visible status
+// word, the roles fall through to the end, tensor memory is released and the kernel returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lb {
+
+namespace tc {
+
+constexpr int TN = 128;            // weight rows per tile
+constexpr int KS = 64;             // k per stage
+constexpr int RAW_BYTES = TN * Q4K_BYTES;  // 18432
+constexpr int B_BYTES = TN * 128;  // bf16 weight tile of one stage
+constexpr int THREADS = 320;       // 10 warps
+constexpr int DEQ_WARPS = 8;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+template <int MT> struct Cfg {
+    static constexpr int STAGES = MT == 256 ? 3 : 4;
+    static constexpr int A_BYTES = MT * 128;
+    static constexpr int STAGE_BYTES = B_BYTES + A_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * RAW_BYTES + 256 /*barriers*/ + 1024 /*alignment slack*/;
+};
+
+__device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < SPIN_LIMIT; spin++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(s32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     s32(dst)),
+                 "l"((uint64_t)map), "r"(x), "r"(y), "r"(s32(bar))
+                 : "memory");
+}
+
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
+}
+
+// f32 bits of (2^23 + byte `sel` of w): the byte planted in the mantissa by one PRMT
+__device__ __forceinline__ float biased(uint32_t w, uint32_t sel) { return __uint_as_float(__byte_perm(w, 0x4B000000u, sel)); }
+
+template <int MT>
+__global__ void __launch_bounds__(THREADS, 1)
+qgemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, GemmTcArgs p) {
+    using C = Cfg<MT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *stage0 = smem;
+    uint8_t *raw0 = smem + C::STAGES * C::STAGE_BYTES;
+    uint64_t *bars = (uint64_t *)(raw0 + 2 * RAW_BYTES);
+    uint64_t *full_a = bars, *full_b = bars + C::STAGES, *empty = bars + 2 * C::STAGES;
+    uint64_t *raw_full = bars + 3 * C::STAGES, *raw_empty = raw_full + 2, *acc_full = raw_full + 4;
+    uint32_t *tmem_slot = (uint32_t *)(acc_full + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t n0 = blockIdx.x * TN, m0 = blockIdx.y * MT;
+    const uint32_t nblk = p.k / QK, ksteps = p.k / KS;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(full_a + s, 1);
+            mbar_init(full_b + s, DEQ_WARPS);
+            mbar_init(empty + s, 1);
+        }
+        for (int r = 0; r < 2; r++) {
+            mbar_init(raw_full + r, 1);
+            mbar_init(raw_empty + r, DEQ_WARPS);
+        }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"((uint32_t)MT) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    bool healthy = true;
+
+    if (warp == 0) {
+        // ---------------- TMA producer
+        if (lane == 0) {
+            for (uint32_t ks = 0; ks < ksteps && healthy; ks++) {
+                const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
+                if ((ks & 3) == 0) {  // a new super-block of packed weights for the 128 rows
+                    const uint32_t b = ks >> 2, r = b & 1, ur = b >> 1;
+                    if (!mbar_wait(raw_empty + r, (ur & 1) ^ 1)) { healthy = false; break; }
+                    mbar_expect_tx(raw_full + r, RAW_BYTES);
+                    tma_load_2d(raw0 + r * RAW_BYTES, &map_w, (int)(b * Q4K_BYTES), (int)n0, raw_full + r);
+                }
+                if (!mbar_wait(empty + s, (u & 1) ^ 1)) { healthy = false; break; }
+                mbar_expect_tx(full_a + s, C::A_BYTES);
+                tma_load_2d(stage0 + s * C::STAGE_BYTES + B_BYTES, &map_a, (int)(ks * KS), (int)m0, full_a + s);
+            }
+            if (!healthy && p.status) atomicOr(p.status, 2);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            // D f32, A and B bf16, both K-major, M = 128, N = MT
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
+            for (uint32_t ks = 0; ks < ksteps && healthy; ks++) {
+                const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
+                if (!mbar_wait(full_a + s, u & 1) || !mbar_wait(full_b + s, u & 1)) { healthy = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t wt = s32(stage0 + s * C::STAGE_BYTES), at = wt + B_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < KS / 16; kk++)
+                    mma_bf16(tmem_base, smem_desc(wt + kk * 32), smem_desc(at + kk * 32), idesc, (ks | kk) ? 1u : 0u);
+                mma_commit(empty + s);  // the stage may be refilled once these MMAs have read it
+            }
+            mma_commit(acc_full);
+            if (!healthy && p.status) atomicOr(p.status, 4);
+        }
+    } else {
+        // ---------------- dequantize: thread = (weight row of the tile, which 32 of the 64 k)
+        const int dw = warp - 2;
+        const int row = 32 * (dw & 3) + lane, half = dw >> 2;
+        float d1[4], m1[4];
+        for (uint32_t ks = 0; ks < ksteps && healthy; ks++) {
+            const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
+            const uint32_t b = ks >> 2, pp = ks & 3, r = b & 1, ur = b >> 1;
+            const uint8_t *blk = raw0 + r * RAW_BYTES + row * Q4K_BYTES;
+            if (pp == 0) {
+                if (!mbar_wait(raw_full + r, ur & 1)) { healthy = false; break; }
+                const uint4 h = *(const uint4 *)blk;
+                const float d = half_bits_to_float(h.x & 0xffff), dmin = half_bits_to_float(h.x >> 16);
+                const float nd = d * -8388608.0f, ndmin = dmin * -8388608.0f;
+                const uint32_t w0 = h.y, w1 = h.z, w2 = h.w;
+                const uint32_t sc_lo = w0 & 0x3F3F3F3Fu, mn_lo = w1 & 0x3F3F3F3Fu;
+                const uint32_t sc_hi = (w2 & 0x0F0F0F0Fu) | (((w0 >> 6) & 0x03030303u) << 4);
+                const uint32_t mn_hi = ((w2 >> 4) & 0x0F0F0F0Fu) | (((w1 >> 6) & 0x03030303u) << 4);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {  // sub-block 2q + half
+                    const uint32_t scw = q < 2 ? sc_lo : sc_hi, mnw = q < 2 ? mn_lo : mn_hi;
+                    const uint32_t sel = 0x7440u + 2 * (q & 1) + half;
+                    d1[q] = fmaf(d, biased(scw, sel), nd);        // d * sc, exact (see qgemv_q4k.cu)
+                    m1[q] = fmaf(dmin, biased(mnw, sel), ndmin);  // dmin * m, exact
+                }
+            }
+            const uint4 qa = *(const uint4 *)(blk + 16 + 32 * pp), qb = *(const uint4 *)(blk + 32 + 32 * pp);
+            if (pp == 3) {  // last read of this block's packed bytes
+                __syncwarp();
+                if (lane == 0) mbar_arrive(raw_empty + r);
+            }
+            const float sd = pp == 0 ? d1[0] : pp == 1 ? d1[1] : pp == 2 ? d1[2] : d1[3];
+            const float nm = -(pp == 0 ? m1[0] : pp == 1 ? m1[1] : pp == 2 ? m1[2] : m1[3]);
+            uint32_t v[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+            if (!mbar_wait(empty + s, (u & 1) ^ 1)) { healthy = false; break; }
+            uint8_t *dst = stage0 + s * C::STAGE_BYTES + row * 128;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {  // 16-byte chunk = 8 consecutive k = two packed words
+                uint32_t o[4];
+#pragma unroll
+                for (int w = 0; w < 2; w++) {
+                    const uint32_t t = (half ? (v[2 * c + w] >> 4) : v[2 * c + w]) & 0x0F0F0F0Fu;
+                    const float e0 = fmaf(sd, biased(t, 0x7440u) - 8388608.0f, nm);
+                    const float e1 = fmaf(sd, biased(t, 0x7441u) - 8388608.0f, nm);
+                    const float e2 = fmaf(sd, biased(t, 0x7442u) - 8388608.0f, nm);
+                    const float e3 = fmaf(sd, biased(t, 0x7443u) - 8388608.0f, nm);
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(e0, e1), hi = __floats2bfloat162_rn(e2, e3);
+                    o[2 * w] = *(uint32_t *)&lo;
+                    o[2 * w + 1] = *(uint32_t *)&hi;
+                }
+                const int chunk = (4 * half + c) ^ (row & 7);
+                *(uint4 *)(dst + 16 * chunk) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_b + s);
+        }
+        if (!healthy && lane == 0 && p.status) atomicOr(p.status, 8);
+
+        // ---------------- epilogue: TMEM lane = weight row, column = activation row
+        if (healthy && mbar_wait(acc_full, 0)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int quarter = warp & 3;  // the TMEM lanes this warp may read
+            const uint32_t n = n0 + 32 * quarter + lane;
+            constexpr int COLS = MT / 2;   // each half of the epilogue warps takes half of the columns
+            const int cbase = half * COLS;
+#pragma unroll 1
+            for (int c0 = 0; c0 < COLS; c0 += 32) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(cbase + c0);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                      "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                      "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (n < p.n) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const uint32_t m = m0 + cbase + c0 + j;
+                        if (m < p.rows) {
+                            const uint32_t bt = m / p.m, i = m % p.m;
+                            float v = __uint_as_float(r[j]);
+                            if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)n * p.ex_s2];
+                            p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + n] = v;
+                        }
+                    }
+                }
+            }
+        } else if (lane == 0 && p.status) {
+            atomicOr(p.status, 16);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)MT) : "memory");
+    }
+}
+
+// f32 activation rows (any row stride) -> contiguous bf16 [rows, k]
+__global__ void __launch_bounds__(256) a_to_bf16_kernel(GemmTcArgs p, __nv_bfloat16 *dst) {
+    const uint64_t total = (uint64_t)p.rows * p.k / 2;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t e = 2 * i;
+        const uint32_t r = (uint32_t)(e / p.k), c = (uint32_t)(e % p.k);
+        const float *src = p.a + p.a_off + (uint64_t)(r / p.m) * p.a_bs + (uint64_t)(r % p.m) * p.a_rs + c;
+        ((__nv_bfloat162 *)dst)[i] = __floats2bfloat162_rn(src[0], src[1]);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+template <int MT>
+static cudaError_t launch_mt(const GemmTcArgs &a, const CUtensorMap &mw, const CUtensorMap &ma, cudaStream_t stream) {
+    auto kern = qgemm_q4k_tc_kernel<MT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT>::SMEM);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    dim3 grid((a.n + TN - 1) / TN, (a.rows + MT - 1) / MT);
+    kern<<<grid, THREADS, Cfg<MT>::SMEM, stream>>>(mw, ma, a);
+    return cudaGetLastError();
+}
+
+}  // namespace tc
+
+bool qgemm_tc_supported(int fmt, const GemmTcArgs &a) {
+    return fmt == FMT_Q4K && a.k % QK == 0 && a.k >= QK && a.rows >= 1 && ((uintptr_t)a.w & 15) == 0 && tc::encode_fn() != nullptr;
+}
+
+size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t k) { return (size_t)rows * k * 2; }
+
+cudaError_t launch_qgemm_tc(const GemmTcArgs &a, void *a_bf16_scratch, int sm_count, cudaStream_t stream) {
+    using namespace tc;
+    if (a.rows == 0 || a.n == 0) return cudaSuccess;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    const uint32_t mt = a.rows <= 64 ? 64 : (a.rows <= 128 ? 128 : 256);
+
+    uint64_t half_elems = (uint64_t)a.rows * a.k / 2;
+    unsigned cgrid = (unsigned)((half_elems + 255) / 256 > (uint64_t)sm_count * 8 ? (uint64_t)sm_count * 8 : (half_elems + 255) / 256);
+    a_to_bf16_kernel<<<cgrid, 256, 0, stream>>>(a, (__nv_bfloat16 *)a_bf16_scratch);
+    cudaError_t ce = cudaGetLastError();
+    if (ce != cudaSuccess) return ce;
+
+    CUtensorMap mw, ma;
+    {   // packed weights as bytes: [n rows][row_bytes], box = one 144-byte block of 128 rows
+        cuuint64_t dims[2] = {(cuuint64_t)(a.k / QK) * Q4K_BYTES, a.n};
+        cuuint64_t strides[1] = {(cuuint64_t)(a.k / QK) * Q4K_BYTES};
+        cuuint32_t box[2] = {Q4K_BYTES, TN};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)a.w, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    {   // bf16 activations [rows][k], box = 64 k (128 bytes, swizzled) x MT rows
+        cuuint64_t dims[2] = {a.k, a.rows};
+        cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};
+        cuuint32_t box[2] = {KS, mt};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_bf16_scratch, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    switch (mt) {
+        case 64: return launch_mt<64>(a, mw, ma, stream);
+        case 128: return launch_mt<128>(a, mw, ma, stream);
+        default: return launch_mt<256>(a, mw, ma, stream);
+    }
+}
+
+}  // namespace lb

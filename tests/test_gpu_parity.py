@@ -77,8 +77,12 @@ def test_golden_vectors(be, oracle, fmt, name):
     assert max_rel(y3, g[f"y3_{name}"]) <= 1e-3
     assert max_rel(y3, g[f"y3_{name}"]) <= 2e-5  # what the arithmetic should actually achieve
     x12 = O.normal(21, 12 * k)
+    be.set_option("gemm", "f32")
     y12 = run_matmul(be, fmt, x12, g[f"w_{name}"], 12, n, k)
+    be.set_option("gemm", "tc")
     assert np.array_equal(y12.view(np.uint32), g[f"y12_{name}"].reshape(-1).view(np.uint32))
+    y12t = run_matmul(be, fmt, x12, g[f"w_{name}"], 12, n, k)  # tensor cores for Q4_K, exact kernel otherwise
+    assert rel_l2(y12t, g[f"y12_{name}"]) <= 4e-3 and max_rel(y12t, g[f"y12_{name}"]) <= 2e-2
 
 
 @pytest.mark.parametrize("fmt,name", FMTS)
@@ -227,6 +231,14 @@ def test_gemv_special_activations(be, oracle):
 # ------------------------------------------------------------------ exact-f32 GEMM path
 @pytest.mark.parametrize("fmt,name", FMTS)
 def test_gemm_f32_bit_exact_vs_oracle(be, oracle, fmt, name):
+    be.set_option("gemm", "f32")
+    try:
+        _gemm_f32_cases(be, oracle, fmt, name)
+    finally:
+        be.set_option("gemm", "tc")
+
+
+def _gemm_f32_cases(be, oracle, fmt, name):
     seed = 70
     for (batch, m, n, k, pad, epi) in [(1, 9, 45, 256, 0, False), (2, 35, 70, 512, 5, True), (1, 130, 200, 256, 3, True),
                                        (1, 20, 45, 256, 3, False), (1, 33, 300, 1024, 0, False)]:
@@ -240,6 +252,60 @@ def test_gemm_f32_bit_exact_vs_oracle(be, oracle, fmt, name):
         assert path == "f32_act"
         got = run_matmul(be, fmt, a, qb, m, n, k, batch=batch, a_row_stride=rs, bias=bias)
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (name, batch, m, n, k)
+
+
+# ------------------------------------------------------------------ tensor-core GEMM path (Q4_K)
+def bf16_round(x):
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32)
+
+
+def test_gemm_tensor_core_q4k(be, oracle):
+    """bf16 tensor-core prefill: stated bounds vs lapid-cpu's f32 path are rel_l2 <= 4e-3 and
+    max_rel <= 2e-2 (both operands rounded to bf16, 2^-9 each; the reference allows 2e-3 for its
+    f16 tensor-core kernel, crates/lapid-cuda/src/kquant_tests.rs:191-192). Against the same
+    product computed from bf16-rounded operands the result must agree to summation-order noise."""
+    seed = 90
+    for (batch, m, n, k, pad, epi) in [(1, 64, 256, 512, 0, False), (1, 20, 45, 256, 3, False), (1, 130, 70, 512, 0, True),
+                                       (1, 33, 300, 1024, 0, False), (2, 137, 300, 2048, 8, True), (1, 9, 128, 256, 0, False),
+                                       (1, 512, 1024, 4096, 0, False), (1, 300, 130, 14336, 0, False)]:
+        seed += 1
+        big = n * k > 200000
+        w = O.normal(seed, n * k, 0.02) if big else rnd(n * k, seed)
+        qb = oracle.quantize(O.Q4_K, w, n, k)
+        rs = k + pad
+        a = O.normal(seed + 7, batch * m * rs) if big else rnd(batch * m * rs, seed + 7)
+        bias = rnd(n, seed + 9) if epi else None
+        got = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, batch=batch, a_row_stride=rs, bias=bias).reshape(batch * m, n)
+        deq = oracle.dequantize(O.Q4_K, qb, n, k)
+        av = a.reshape(batch * m, rs)[:, :k]
+        b64 = bias.astype(np.float64) if epi else 0.0
+        exact = av.astype(np.float64) @ deq.astype(np.float64).T + b64
+        assert rel_l2(got, exact) <= 4e-3, (m, n, k, rel_l2(got, exact))
+        assert max_rel(got, exact) <= 2e-2, (m, n, k, max_rel(got, exact))
+        rounded = bf16_round(av).astype(np.float64) @ bf16_round(deq).astype(np.float64).T + b64
+        assert rel_l2(got, rounded) <= 2e-5, (m, n, k, rel_l2(got, rounded))
+    if True:  # the exact path still answers for the same launch when asked
+        be.set_option("gemm", "f32")
+        got = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, batch=batch, a_row_stride=rs)
+        be.set_option("gemm", "tc")
+        want, _ = oracle.matmul(O.Q4_K, a, qb, n, k, batch=batch, m=m, a_view=(0, m * rs, rs))
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_gemm_tensor_core_strided_output(be, oracle):
+    k, n, off, batch, m = 256, 40, 7, 3, 30
+    a = rnd(batch * m * k, 100)
+    qb = oracle.quantize(O.Q4_K, rnd(n * k, 101), n, k)
+    total = off + m * batch * n + 5
+    got = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, batch=batch, out=np.full(total, -1.0, np.float32),
+                     out_view=MatView(off, n, batch * n))
+    want = np.full(total, -1.0, np.float32)
+    oracle.matmul(O.Q4_K, a, qb, n, k, batch=batch, m=m, out=want, out_view=(off, n, batch * n))
+    touched = want != -1.0
+    assert (got[~touched] == -1.0).all()
+    assert rel_l2(got[touched], want[touched]) <= 4e-3
 
 
 # ------------------------------------------------------------------ views, epilogue, validation
