@@ -10,15 +10,17 @@
 //
 // One CTA computes a 128 (weight rows) x MT (activation rows, 64/128/256) output tile, K in steps
 // of 64 (one Q4_K "pair": 32 bytes of quants = two 32-element sub-blocks):
-//   warp 0     one lane drives TMA: per super-block a 2-D tensor-map copy of the 128 rows' packed
-//              144-byte blocks (`cp.async.bulk.tensor.2d`, no multicast), per k-step a 128-byte
-//              swizzled copy of the bf16 activation tile
+//   warp 0     one lane drives TMA for the activations: per k-step a 128-byte swizzled 2-D copy
+//              of the bf16 activation tile (`cp.async.bulk.tensor.2d`, no multicast)
+//   warp 18    one lane drives TMA for the weights: per super-block a 2-D tensor-map copy of the
+//              tile rows' packed 144-byte blocks, one super-block ahead of its consumers
 //   warp 1     allocates tensor memory; one lane issues `tcgen05.mma` (M=128, N=MT, K=16, four
 //              per k-step) on shared-memory descriptors and commits to mbarriers
-//   warps 2-9  dequantize: thread (row, half) expands one 32-element sub-block per k-step from
+//   warps 2-17 dequantize: thread (row, half) expands one 32-element sub-block per k-step from
 //              the staged packed bytes to bf16 and stores it in the 128-byte-swizzled K-major
-//              layout the tensor core reads; afterwards they are the epilogue: `tcgen05.ld`
-//              32 lanes x 32 columns at a time, optional `+ extra`, coalesced f32 stores
+//              layout the tensor core reads (warps 2-9 the even k-steps, 10-17 the odd ones);
+//              afterwards warps 2-9 are the epilogue: `tcgen05.ld` 32 lanes x 32 columns at a
+//              time, optional `+ extra`, coalesced f32 stores
 // The weight tile is the M side of the MMA and the activations the N side, so 64 prefill rows
 // use a 128x64 instruction at full rate instead of padding to 128 rows.
 // Every mbarrier wait is bounded: a wait that gives up sets a bit in the host-visible status
@@ -37,15 +39,21 @@ constexpr int TN = 128;            // weight rows per tile
 constexpr int KS = 64;             // k per stage
 constexpr int RAW_BYTES = TN * Q4K_BYTES;  // 18432
 constexpr int B_BYTES = TN * 128;  // bf16 weight tile of one stage
-constexpr int THREADS = 320;       // 10 warps
-constexpr int DEQ_WARPS = 8;
+constexpr int THREADS = 608;       // 19 warps
+constexpr int DEQ_WARPS = 16;      // two groups of eight: even and odd k-steps
+constexpr int GROUP_WARPS = 8;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
-template <int MT> struct Cfg {
-    static constexpr int STAGES = MT == 256 ? 3 : 4;
+// MT activation rows x (NT * 128) weight rows per CTA. NT = 2 keeps two accumulators (all 512
+// columns of tensor memory at MT = 256) so that one activation tile feeds twice the weights: the
+// bf16 activation tile is the larger part of what an SM pulls from L2 per k-step.
+template <int MT, int NT> struct Cfg {
+    static constexpr int STAGES = NT == 2 ? 2 : (MT == 256 ? 3 : 4);
     static constexpr int A_BYTES = MT * 128;
-    static constexpr int STAGE_BYTES = B_BYTES + A_BYTES;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * RAW_BYTES + 256 /*barriers*/ + 1024 /*alignment slack*/;
+    static constexpr int W_BYTES = NT * B_BYTES;
+    static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
+    static constexpr int RAW = NT * RAW_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * RAW + 256 /*barriers*/ + 1024 /*alignment slack*/;
 };
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -58,7 +66,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+// Bounded wait. A waiter that is not on the critical path sleeps between polls so that it does not
+// take issue slots from the dequantizing warps.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t sleep_ns = 0) {
     for (uint32_t spin = 0; spin < SPIN_LIMIT; spin++) {
         uint32_t ok;
         asm volatile(
@@ -67,8 +77,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
             : "r"(s32(bar)), "r"(parity)
             : "memory");
         if (ok) return true;
+        if (sleep_ns) __nanosleep(sleep_ns);
     }
     return false;
+}
+
+// Two f32 lanes in one 64-bit register pair: Blackwell's packed f32 pipe halves the instruction
+// count of the dequantization.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+// {lo, hi} f32 -> packed bf16x2 with lo in the low half
+__device__ __forceinline__ uint32_t to_bf16x2(uint64_t v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
 }
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
@@ -95,27 +132,27 @@ __device__ __forceinline__ void mma_commit(uint64_t *bar) {
 // f32 bits of (2^23 + byte `sel` of w): the byte planted in the mantissa by one PRMT
 __device__ __forceinline__ float biased(uint32_t w, uint32_t sel) { return __uint_as_float(__byte_perm(w, 0x4B000000u, sel)); }
 
-template <int MT>
+template <int MT, int NT>
 __global__ void __launch_bounds__(THREADS, 1)
 qgemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, GemmTcArgs p) {
-    using C = Cfg<MT>;
+    using C = Cfg<MT, NT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *stage0 = smem;
     uint8_t *raw0 = smem + C::STAGES * C::STAGE_BYTES;
-    uint64_t *bars = (uint64_t *)(raw0 + 2 * RAW_BYTES);
+    uint64_t *bars = (uint64_t *)(raw0 + 2 * C::RAW);
     uint64_t *full_a = bars, *full_b = bars + C::STAGES, *empty = bars + 2 * C::STAGES;
     uint64_t *raw_full = bars + 3 * C::STAGES, *raw_empty = raw_full + 2, *acc_full = raw_full + 4;
     uint32_t *tmem_slot = (uint32_t *)(acc_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t n0 = blockIdx.x * TN, m0 = blockIdx.y * MT;
+    const uint32_t n0 = blockIdx.x * (TN * NT), m0 = blockIdx.y * MT;
     const uint32_t nblk = p.k / QK, ksteps = p.k / KS;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) {
             mbar_init(full_a + s, 1);
-            mbar_init(full_b + s, DEQ_WARPS);
+            mbar_init(full_b + s, NT == 2 ? DEQ_WARPS : GROUP_WARPS);
             mbar_init(empty + s, 1);
         }
         for (int r = 0; r < 2; r++) {
@@ -126,7 +163,7 @@ qgemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"((uint32_t)MT) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"((uint32_t)(MT * NT)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -136,21 +173,29 @@ qgemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     bool healthy = true;
 
     if (warp == 0) {
-        // ---------------- TMA producer
+        // ---------------- TMA producer, activation tiles: one 128-byte-swizzled box per k-step
         if (lane == 0) {
             for (uint32_t ks = 0; ks < ksteps && healthy; ks++) {
                 const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
-                if ((ks & 3) == 0) {  // a new super-block of packed weights for the 128 rows
-                    const uint32_t b = ks >> 2, r = b & 1, ur = b >> 1;
-                    if (!mbar_wait(raw_empty + r, (ur & 1) ^ 1)) { healthy = false; break; }
-                    mbar_expect_tx(raw_full + r, RAW_BYTES);
-                    tma_load_2d(raw0 + r * RAW_BYTES, &map_w, (int)(b * Q4K_BYTES), (int)n0, raw_full + r);
-                }
-                if (!mbar_wait(empty + s, (u & 1) ^ 1)) { healthy = false; break; }
+                if (!mbar_wait(empty + s, (u & 1) ^ 1, 64)) { healthy = false; break; }
                 mbar_expect_tx(full_a + s, C::A_BYTES);
-                tma_load_2d(stage0 + s * C::STAGE_BYTES + B_BYTES, &map_a, (int)(ks * KS), (int)m0, full_a + s);
+                tma_load_2d(stage0 + s * C::STAGE_BYTES + C::W_BYTES, &map_a, (int)(ks * KS), (int)m0, full_a + s);
             }
             if (!healthy && p.status) atomicOr(p.status, 2);
+        }
+    } else if (warp == 18) {
+        // ---------------- TMA producer, packed weights: one super-block of every row of the tile
+        // per copy, a whole super-block (four k-steps) ahead of the dequantizing warps
+        if (lane == 0) {
+            for (uint32_t b = 0; b < nblk && healthy; b++) {
+                const uint32_t r = b & 1, ur = b >> 1;
+                if (!mbar_wait(raw_empty + r, (ur & 1) ^ 1, 64)) { healthy = false; break; }
+                mbar_expect_tx(raw_full + r, C::RAW);
+#pragma unroll
+                for (int t = 0; t < NT; t++)
+                    tma_load_2d(raw0 + r * C::RAW + t * RAW_BYTES, &map_w, (int)(b * Q4K_BYTES), (int)(n0 + t * TN), raw_full + r);
+            }
+            if (!healthy && p.status) atomicOr(p.status, 32);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer
@@ -159,27 +204,34 @@ qgemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
             for (uint32_t ks = 0; ks < ksteps && healthy; ks++) {
                 const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
-                if (!mbar_wait(full_a + s, u & 1) || !mbar_wait(full_b + s, u & 1)) { healthy = false; break; }
+                if (!mbar_wait(full_a + s, u & 1, 32) || !mbar_wait(full_b + s, u & 1, 32)) { healthy = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t wt = s32(stage0 + s * C::STAGE_BYTES), at = wt + B_BYTES;
+                const uint32_t wt = s32(stage0 + s * C::STAGE_BYTES), at = wt + C::W_BYTES;
 #pragma unroll
-                for (int kk = 0; kk < KS / 16; kk++)
-                    mma_bf16(tmem_base, smem_desc(wt + kk * 32), smem_desc(at + kk * 32), idesc, (ks | kk) ? 1u : 0u);
+                for (int t = 0; t < NT; t++)
+#pragma unroll
+                    for (int kk = 0; kk < KS / 16; kk++)
+                        mma_bf16(tmem_base + t * MT, smem_desc(wt + t * B_BYTES + kk * 32), smem_desc(at + kk * 32), idesc,
+                                 (ks | kk) ? 1u : 0u);
                 mma_commit(empty + s);  // the stage may be refilled once these MMAs have read it
             }
             mma_commit(acc_full);
             if (!healthy && p.status) atomicOr(p.status, 4);
         }
     } else {
-        // ---------------- dequantize: thread = (weight row of the tile, which 32 of the 64 k)
-        const int dw = warp - 2;
+        // ---------------- dequantize: thread = (weight row of the tile, which 32 of the 64 k); the
+        // first eight warps take the even k-steps, the other eight the odd ones, so that a warp
+        // has two MMA periods for one k-step and the groups' waits overlap
+        // (NT = 2: the two groups own the two 128-row sub-tiles instead and every warp does every k-step)
+        const int dw = (warp - 2) & 7, grp = (warp - 2) >> 3;
         const int row = 32 * (dw & 3) + lane, half = dw >> 2;
-        float d1[4], m1[4];
-        for (uint32_t ks = 0; ks < ksteps && healthy; ks++) {
+        const int sub = NT == 2 ? grp : 0;        // weight sub-tile of this thread
+        float d1[4], m1[4];                       // sub-block scales of this thread's pairs of the current super-block
+        for (uint32_t ks = (NT == 2 ? 0 : grp); ks < ksteps && healthy; ks += (NT == 2 ? 1 : 2)) {
             const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
             const uint32_t b = ks >> 2, pp = ks & 3, r = b & 1, ur = b >> 1;
-            const uint8_t *blk = raw0 + r * RAW_BYTES + row * Q4K_BYTES;
-            if (pp == 0) {
+            const uint8_t *blk = raw0 + r * C::RAW + sub * RAW_BYTES + row * Q4K_BYTES;
+            if (NT == 2 ? pp == 0 : pp < 2) {  // first k-step of this thread in the block
                 if (!mbar_wait(raw_full + r, ur & 1)) { healthy = false; break; }
                 const uint4 h = *(const uint4 *)blk;
                 const float d = half_bits_to_float(h.x & 0xffff), dmin = half_bits_to_float(h.x >> 16);
@@ -188,37 +240,40 @@ qgemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const uint32_t sc_lo = w0 & 0x3F3F3F3Fu, mn_lo = w1 & 0x3F3F3F3Fu;
                 const uint32_t sc_hi = (w2 & 0x0F0F0F0Fu) | (((w0 >> 6) & 0x03030303u) << 4);
                 const uint32_t mn_hi = ((w2 >> 4) & 0x0F0F0F0Fu) | (((w1 >> 6) & 0x03030303u) << 4);
+                // pair q: sub-block 2q + half = byte 2*(q&1) + half of the lo (q < 2) / hi words
 #pragma unroll
-                for (int q = 0; q < 4; q++) {  // sub-block 2q + half
-                    const uint32_t scw = q < 2 ? sc_lo : sc_hi, mnw = q < 2 ? mn_lo : mn_hi;
+                for (int q = 0; q < 4; q++) {
                     const uint32_t sel = 0x7440u + 2 * (q & 1) + half;
-                    d1[q] = fmaf(d, biased(scw, sel), nd);        // d * sc, exact (see qgemv_q4k.cu)
-                    m1[q] = fmaf(dmin, biased(mnw, sel), ndmin);  // dmin * m, exact
+                    d1[q] = fmaf(d, biased(q < 2 ? sc_lo : sc_hi, sel), nd);        // d * sc, exact (see qgemv_q4k.cu)
+                    m1[q] = fmaf(dmin, biased(q < 2 ? mn_lo : mn_hi, sel), ndmin);  // dmin * m, exact
                 }
             }
             const uint4 qa = *(const uint4 *)(blk + 16 + 32 * pp), qb = *(const uint4 *)(blk + 32 + 32 * pp);
-            if (pp == 3) {  // last read of this block's packed bytes
+            if (NT == 2 ? pp == 3 : pp >= 2) {  // this thread's last read of the block's packed bytes
                 __syncwarp();
                 if (lane == 0) mbar_arrive(raw_empty + r);
             }
             const float sd = pp == 0 ? d1[0] : pp == 1 ? d1[1] : pp == 2 ? d1[2] : d1[3];
             const float nm = -(pp == 0 ? m1[0] : pp == 1 ? m1[1] : pp == 2 ? m1[2] : m1[3]);
+            const uint64_t sd2 = pack2(sd, sd), nm2 = pack2(nm, nm), unbias = pack2(-8388608.0f, -8388608.0f);
             uint32_t v[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+            if (half) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] >>= 4;
+            }
             if (!mbar_wait(empty + s, (u & 1) ^ 1)) { healthy = false; break; }
-            uint8_t *dst = stage0 + s * C::STAGE_BYTES + row * 128;
+            uint8_t *dst = stage0 + s * C::STAGE_BYTES + sub * B_BYTES + row * 128;
 #pragma unroll
             for (int c = 0; c < 4; c++) {  // 16-byte chunk = 8 consecutive k = two packed words
                 uint32_t o[4];
 #pragma unroll
                 for (int w = 0; w < 2; w++) {
-                    const uint32_t t = (half ? (v[2 * c + w] >> 4) : v[2 * c + w]) & 0x0F0F0F0Fu;
-                    const float e0 = fmaf(sd, biased(t, 0x7440u) - 8388608.0f, nm);
-                    const float e1 = fmaf(sd, biased(t, 0x7441u) - 8388608.0f, nm);
-                    const float e2 = fmaf(sd, biased(t, 0x7442u) - 8388608.0f, nm);
-                    const float e3 = fmaf(sd, biased(t, 0x7443u) - 8388608.0f, nm);
-                    __nv_bfloat162 lo = __floats2bfloat162_rn(e0, e1), hi = __floats2bfloat162_rn(e2, e3);
-                    o[2 * w] = *(uint32_t *)&lo;
-                    o[2 * w + 1] = *(uint32_t *)&hi;
+                    const uint32_t t = v[2 * c + w] & 0x0F0F0F0Fu;
+                    // y = sd * q - m1 with one rounding, two elements per instruction
+                    const uint64_t q01 = add2(pack2(biased(t, 0x7440u), biased(t, 0x7441u)), unbias);
+                    const uint64_t q23 = add2(pack2(biased(t, 0x7442u), biased(t, 0x7443u)), unbias);
+                    o[2 * w] = to_bf16x2(fma2(sd2, q01, nm2));
+                    o[2 * w + 1] = to_bf16x2(fma2(sd2, q23, nm2));
                 }
                 const int chunk = (4 * half + c) ^ (row & 7);
                 *(uint4 *)(dst + 16 * chunk) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -230,16 +285,18 @@ qgemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (!healthy && lane == 0 && p.status) atomicOr(p.status, 8);
 
         // ---------------- epilogue: TMEM lane = weight row, column = activation row
-        if (healthy && mbar_wait(acc_full, 0)) {
+        if (NT == 1 && grp != 0) {
+            // with one accumulator the second group has no epilogue share
+        } else if (healthy && mbar_wait(acc_full, 0)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int quarter = warp & 3;  // the TMEM lanes this warp may read
-            const uint32_t n = n0 + 32 * quarter + lane;
+            const uint32_t n = n0 + sub * TN + 32 * quarter + lane;
             constexpr int COLS = MT / 2;   // each half of the epilogue warps takes half of the columns
             const int cbase = half * COLS;
 #pragma unroll 1
             for (int c0 = 0; c0 < COLS; c0 += 32) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(cbase + c0);
+                const uint32_t taddr = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(sub * MT + cbase + c0);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
                     "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
@@ -271,7 +328,7 @@ qgemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)MT) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(MT * NT)) : "memory");
     }
 }
 
@@ -302,21 +359,24 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int MT>
+template <int MT, int NT>
 static cudaError_t launch_mt(const GemmTcArgs &a, const CUtensorMap &mw, const CUtensorMap &ma, cudaStream_t stream) {
-    auto kern = qgemm_q4k_tc_kernel<MT>;
+    auto kern = qgemm_q4k_tc_kernel<MT, NT>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT>::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT, NT>::SMEM);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    dim3 grid((a.n + TN - 1) / TN, (a.rows + MT - 1) / MT);
-    kern<<<grid, THREADS, Cfg<MT>::SMEM, stream>>>(mw, ma, a);
+    dim3 grid((a.n + TN * NT - 1) / (TN * NT), (a.rows + MT - 1) / MT);
+    kern<<<grid, THREADS, Cfg<MT, NT>::SMEM, stream>>>(mw, ma, a);
     return cudaGetLastError();
 }
 
 }  // namespace tc
+
+static int g_tc_wide = -1;  // tuning: -1 choose, 0 never, 1 always use two accumulators at MT = 256
+void qgemm_tc_set_wide(int v) { g_tc_wide = v; }
 
 bool qgemm_tc_supported(int fmt, const GemmTcArgs &a) {
     return fmt == FMT_Q4K && a.k % QK == 0 && a.k >= QK && a.rows >= 1 && ((uintptr_t)a.w & 15) == 0 && tc::encode_fn() != nullptr;
@@ -356,10 +416,11 @@ cudaError_t launch_qgemm_tc(const GemmTcArgs &a, void *a_bf16_scratch, int sm_co
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
+    const bool wide = g_tc_wide >= 0 ? g_tc_wide != 0 : (a.rows > 128 && a.n >= 2 * TN);
     switch (mt) {
-        case 64: return launch_mt<64>(a, mw, ma, stream);
-        case 128: return launch_mt<128>(a, mw, ma, stream);
-        default: return launch_mt<256>(a, mw, ma, stream);
+        case 64: return launch_mt<64, 1>(a, mw, ma, stream);
+        case 128: return launch_mt<128, 1>(a, mw, ma, stream);
+        default: return wide ? launch_mt<256, 2>(a, mw, ma, stream) : launch_mt<256, 1>(a, mw, ma, stream);
     }
 }
 
