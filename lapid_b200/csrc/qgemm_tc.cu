@@ -416,7 +416,17 @@ cudaError_t launch_qgemm_tc(const GemmTcArgs &a, void *a_bf16_scratch, int sm_co
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    const bool wide = g_tc_wide >= 0 ? g_tc_wide != 0 : (a.rows > 128 && a.n >= 2 * TN);
+    // One or two accumulators per CTA at MT = 256: the 256x256 tile halves the activation traffic
+    // but there are half as many tiles; take the shape with the shorter modelled time (waves of
+    // tiles over the SMs times the measured cost of a k-step of each shape).
+    bool wide = a.rows > 128 && a.n >= 2 * TN;
+    if (wide) {
+        const uint64_t mt_tiles = (a.rows + 255) / 256;
+        const uint64_t t1 = ((a.n + TN - 1) / TN) * mt_tiles, t2 = ((a.n + 2 * TN - 1) / (2 * TN)) * mt_tiles;
+        const uint64_t w1 = (t1 + sm_count - 1) / sm_count, w2 = (t2 + sm_count - 1) / sm_count;
+        wide = w2 * 26 <= w1 * 15;
+    }
+    if (g_tc_wide >= 0) wide = g_tc_wide != 0;
     switch (mt) {
         case 64: return launch_mt<64, 1>(a, mw, ma, stream);
         case 128: return launch_mt<128, 1>(a, mw, ma, stream);
