@@ -190,6 +190,29 @@ LAPID_B200_API lapid_b200_status lapid_b200_from_ggml_blocks(lapid_b200_device *
                                               uint64_t src_bytes, uint64_t rows, uint64_t cols,
                                               lapid_b200_buffer *dst);
 
+/* ---- decode without allocation ------------------------------------------------------------ */
+/* This entry point has no counterpart in the reference. It exists for hosts that may not allocate
+ * device memory when they need a matvec (an engine that gave all device memory to its own arena at
+ * start-up, a loop with a fixed memory budget, a plug-in living under another runtime's
+ * allocator): it makes no cudaMalloc / cudaFree or other allocating call on any path, because the
+ * quantized activations go to an array inside the library image instead of a grown scratch block.
+ *
+ *   out[r, j] = sum_k a[r, k] * dequant(w)[j, k]     r < rows (1..8), j < n, k % 256 == 0
+ *
+ * a (rows x k f32, contiguous), w (Q4_K [n, k], 16-byte aligned, w_bytes readable) and out
+ * (rows x n f32, contiguous) are DEVICE pointers on device `ordinal`, owned by the caller; the work
+ * is queued on `cuda_stream` (NULL = the legacy default stream) and not waited for. Same arithmetic
+ * as a MatMul launch with batch*m <= 8 through lapid_b200_execute.
+ * Limits and rules: rows * k <= 65536 (the array holds LAPID_B200_STATIC_SCRATCH_BYTES; a larger
+ * request fails with "too_large"); every GPU that loads the library carries the array until exit;
+ * all calls on a GPU share it and it keeps the previous call's contents (nothing in it needs
+ * clearing), so calls that can overlap on the GPU race -- keep them on one stream or order them
+ * with events; the first call on a GPU also looks up the array's address and configures the
+ * kernels, so make it before any stream capture. */
+#define LAPID_B200_STATIC_SCRATCH_BYTES 86016u
+LAPID_B200_API lapid_b200_status lapid_b200_gemv_q4k_static(int32_t ordinal, void *cuda_stream, const float *a, const void *w,
+                                                            uint64_t w_bytes, float *out, uint32_t rows, uint32_t n, uint32_t k);
+
 #ifdef __cplusplus
 }
 #endif

@@ -25,6 +25,7 @@ SOURCES = {
     "qgemv_q4k.cu": [],
     "qgemm_f32.cu": [],
     "qgemm_tc.cu": [],
+    "noalloc.cu": [],
     "backend.cc": ["-x", "cu"],
 }
 

@@ -583,6 +583,12 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
 
 }  // namespace
 
+namespace lb {
+// For entry points defined in other files: records the error for lapid_b200_last_error() and
+// returns its status code.
+int32_t report_error(const char *code, const std::string &message) { return record(Error{code, message}); }
+}  // namespace lb
+
 // ================================================================== extern "C"
 extern "C" {
 
