@@ -1,0 +1,194 @@
+"""Tensor parallelism for the quantized projections of a decoder layer (one process per GPU).
+
+The reference has no multi-GPU code at all, so there is no interface to mirror; the parity statement
+is "the sum of the shards' results equals the unsharded result".
+
+* Column-parallel (q, k, v, gate, up): rank r owns weight rows ``[r*n/p, (r+1)*n/p)``. Rows of a
+  lapid-quant matrix are independent block runs, so a shard is a byte range (K formats) or a pair of
+  plane slices (Int8). No communication; the outputs stay sharded and feed the row-parallel op.
+* Row-parallel (o, down): rank r owns columns ``[r*k/p, (r+1)*k/p)``; ``k/p`` must be a multiple of
+  256 (32 for Int8) so shards are whole blocks, bit-identical to the unsharded ones. Shards are
+  repacked once, at load, into a contiguous ``[n, k/p]`` matrix. Every rank produces a partial
+  ``[M, n]`` f32 result and the partials are summed by an all-reduce.
+
+Everything here works on numpy arrays (tests, CPU ranks over gloo) and on CUDA torch tensors.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+INT8, Q4_K, Q6_K = 4, 6, 8
+_BLOCK = {Q4_K: (256, 144), Q6_K: (256, 210)}
+
+
+def _align(x: int, a: int = 256) -> int:
+    return (x + a - 1) // a * a
+
+
+def layout_total(fmt: int, n: int, k: int) -> int:
+    if fmt in _BLOCK:
+        be, bb = _BLOCK[fmt]
+        return _align(n * (k // be) * bb)
+    return _align(_align(n * k) + n * (k // 32) * 2)
+
+
+def _is_torch(x) -> bool:
+    return type(x).__module__.startswith("torch")
+
+
+def _zeros_like_bytes(x, nbytes: int):
+    if _is_torch(x):
+        import torch
+        return torch.zeros(nbytes, dtype=torch.uint8, device=x.device)
+    return np.zeros(nbytes, dtype=np.uint8)
+
+
+def _pack(parts, total: int, like):
+    """Concatenate byte pieces at their offsets into a zero-padded buffer of `total` bytes."""
+    out = _zeros_like_bytes(like, total)
+    for off, piece in parts:
+        flat = piece.reshape(-1)
+        out[off:off + flat.shape[0]] = flat
+    return out
+
+
+def check_divisible(fmt: int, n: int, k: int, world: int, kind: str) -> None:
+    if kind == "column":
+        if n % world:
+            raise ValueError(f"column-parallel: n = {n} is not divisible by {world} ranks")
+    else:
+        unit = 32 if fmt == INT8 else 256
+        if k % (world * unit):
+            raise ValueError(f"row-parallel: k = {k} must be a multiple of {world} x {unit}")
+
+
+def shard_rows(fmt: int, q, n: int, k: int, rank: int, world: int):
+    """Column-parallel shard: the quantized matrix of weight rows [rank*n/world, (rank+1)*n/world)."""
+    check_divisible(fmt, n, k, world, "column")
+    nl = n // world
+    r0 = rank * nl
+    if fmt in _BLOCK:
+        be, bb = _BLOCK[fmt]
+        rb = (k // be) * bb
+        return _pack([(0, q[r0 * rb:(r0 + nl) * rb])], layout_total(fmt, nl, k), q), nl
+    so = _align(n * k)
+    kg = k // 32
+    quants = q[r0 * k:(r0 + nl) * k]
+    scales = q[so + r0 * kg * 2: so + (r0 + nl) * kg * 2]
+    return _pack([(0, quants), (_align(nl * k), scales)], layout_total(fmt, nl, k), q), nl
+
+
+def shard_cols(fmt: int, q, n: int, k: int, rank: int, world: int):
+    """Row-parallel shard: columns [rank*k/world, (rank+1)*k/world) of every weight row, repacked
+    into a contiguous [n, k/world] lapid-quant matrix (whole blocks, bytes unchanged)."""
+    check_divisible(fmt, n, k, world, "row")
+    kl = k // world
+    if fmt in _BLOCK:
+        be, bb = _BLOCK[fmt]
+        nb, nbl = k // be, kl // be
+        blocks = q[:n * nb * bb].reshape(n, nb, bb)[:, rank * nbl:(rank + 1) * nbl, :]
+        blocks = blocks.contiguous() if _is_torch(blocks) else np.ascontiguousarray(blocks)
+        return _pack([(0, blocks)], layout_total(fmt, n, kl), q), kl
+    so = _align(n * k)
+    kg, kgl = k // 32, kl // 32
+    quants = q[:n * k].reshape(n, k)[:, rank * kl:(rank + 1) * kl]
+    scales = q[so:so + n * kg * 2].reshape(n, kg, 2)[:, rank * kgl:(rank + 1) * kgl, :]
+    if _is_torch(q):
+        quants, scales = quants.contiguous(), scales.contiguous()
+    else:
+        quants, scales = np.ascontiguousarray(quants), np.ascontiguousarray(scales)
+    return _pack([(0, quants), (_align(n * kl), scales)], layout_total(fmt, n, kl), q), kl
+
+
+# ---------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class LayerShape:
+    """Projection shapes of one Llama-architecture decoder layer."""
+    d_model: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    ffn: int
+
+    def projections(self):
+        """(name, n, k, parallel kind) in execution order."""
+        d, kv = self.d_model, self.n_kv_heads * self.head_dim
+        return [("q", self.n_heads * self.head_dim, d, "column"), ("k", kv, d, "column"), ("v", kv, d, "column"),
+                ("o", d, self.n_heads * self.head_dim, "row"), ("gate", self.ffn, d, "column"),
+                ("up", self.ffn, d, "column"), ("down", d, self.ffn, "row")]
+
+
+LLAMA3_8B = LayerShape(4096, 32, 8, 128, 14336)
+LLAMA_70B = LayerShape(8192, 64, 8, 128, 28672)
+
+
+def use_more_bits(i: int, n_layers: int) -> bool:
+    """Which layers get the wider format in a Q4_K_M-style mix
+    (crates/lapid-convert/src/policy.rs:154-157): the first and last eighth and every third between."""
+    return i < n_layers // 8 or i >= 7 * n_layers // 8 or (i - n_layers // 8) % 3 == 2
+
+
+def q4km_format(name: str, layer: int, n_layers: int) -> int:
+    """Q6_K for attn_v and for ffn_down in the `use_more_bits` layers, Q4_K elsewhere."""
+    if name == "v":
+        return Q6_K
+    if name == "down" and use_more_bits(layer, n_layers):
+        return Q6_K
+    return Q4_K
+
+
+def local_shape(name: str, n: int, k: int, kind: str, world: int):
+    return (n // world, k) if kind == "column" else (n, k // world)
+
+
+class TpLayer:
+    """One decoder layer's quantized projections on this rank.
+
+    `matmul(fmt, x, w, n, k)` is injected: the CUDA backend on a GPU rank, the CPU oracle in the
+    gloo tests. `all_reduce(t)` sums a partial result over the ranks in place (identity at world 1).
+    The attention mixing itself is outside this path: q's output feeds o directly, which keeps the
+    dependency chain and the sharding (q's columns are o's k shard) of the real layer.
+    """
+
+    def __init__(self, shape: LayerShape, weights: dict, formats: dict, world: int, matmul, all_reduce, ops):
+        self.shape, self.w, self.fmt, self.world = shape, weights, formats, world
+        self.matmul, self.all_reduce, self.ops = matmul, all_reduce, ops
+        self.dims = {name: local_shape(name, n, k, kind, world) for name, n, k, kind in shape.projections()}
+
+    def _mm(self, name, x):
+        n, k = self.dims[name]
+        return self.matmul(self.fmt[name], x, self.w[name], n, k)
+
+    def forward(self, h):
+        ops = self.ops
+        x = ops.rms_normalise(h)
+        q = self._mm("q", x)
+        self._mm("k", x)
+        self._mm("v", x)
+        o = self._mm("o", q)                      # partial sums over this rank's k shard
+        self.all_reduce(o)
+        h = ops.add(h, o)
+        x = ops.rms_normalise(h)
+        g = self._mm("gate", x)
+        u = self._mm("up", x)
+        d = self._mm("down", ops.silu_mul(g, u))  # partial
+        self.all_reduce(d)
+        return ops.add(h, d)
+
+
+class NumpyOps:
+    @staticmethod
+    def rms_normalise(x):
+        x = np.asarray(x, np.float32)
+        return (x / np.sqrt((x.astype(np.float64) ** 2).mean(axis=-1, keepdims=True) + 1e-6)).astype(np.float32)
+
+    @staticmethod
+    def add(a, b):
+        return (np.asarray(a, np.float32) + np.asarray(b, np.float32)).astype(np.float32)
+
+    @staticmethod
+    def silu_mul(g, u):
+        g = np.asarray(g, np.float64)
+        return (g / (1.0 + np.exp(-g)) * np.asarray(u, np.float64)).astype(np.float32)
