@@ -192,3 +192,90 @@ class NumpyOps:
     def silu_mul(g, u):
         g = np.asarray(g, np.float64)
         return (g / (1.0 + np.exp(-g)) * np.asarray(u, np.float64)).astype(np.float32)
+
+
+class TorchOps:
+    """The few elementwise steps between projections, on CUDA tensors (plumbing, not the product)."""
+
+    @staticmethod
+    def rms_normalise(x):
+        import torch
+        return x * torch.rsqrt(x.float().pow(2).mean(dim=-1, keepdim=True) + 1e-6)
+
+    @staticmethod
+    def add(a, b):
+        return a + b
+
+    @staticmethod
+    def silu_mul(g, u):
+        import torch
+        return torch.nn.functional.silu(g) * u
+
+
+class GpuTpLayers:
+    """A stack of decoder layers' projections on one GPU rank, driven through the C ABI.
+
+    Buffers are allocated once (torch tensors wrapped as library buffers); a token step queues, per
+    layer, four launch lists -- [q, k, v], [o], [gate, up], [down] -- on the current torch stream with
+    `execute_async`, the elementwise steps with torch, and the two all-reduces of the row-parallel
+    outputs with NCCL through torch.distributed. The whole step can be captured in a CUDA graph.
+    """
+
+    def __init__(self, backend, shape: LayerShape, world: int, rank: int, m: int, weights: list, formats: list,
+                 group=None):
+        import torch
+        from .backend import matmul_launch
+        self.be, self.shape, self.world, self.rank, self.m, self.group = backend, shape, world, rank, m, group
+        dev = weights[0]["q"].device
+        d = shape.d_model
+        proj = {name: local_shape(name, n, k, kind, world) for name, n, k, kind in shape.projections()}
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.h = torch.zeros(m, d, **f32)
+        self.x = torch.zeros(m, d, **f32)
+        self.outs = {name: torch.zeros(m, proj[name][0], **f32) for name in proj}
+        self.act = torch.zeros(m, proj["gate"][0], **f32)
+        torch.cuda.synchronize(dev)
+        wrap = backend.wrap_tensor
+        self._keep = []
+        self.steps = []
+        for w, f in zip(weights, formats):
+            bufs = [wrap(self.x), wrap(self.outs["q"]), wrap(self.act)]                 # 0 x, 1 q_out, 2 act
+            order = ["q", "k", "v", "o", "gate", "up", "down"]
+            bufs += [wrap(w[n_]) for n_ in order]                                       # 3..9 weights
+            bufs += [wrap(self.outs[n_]) for n_ in order]                               # 10..16 outputs
+            idx = {n_: i for i, n_ in enumerate(order)}
+
+            def launch(name, a_id):
+                n, k = proj[name]
+                return matmul_launch(f[name], m, n, k, inputs=(a_id, 3 + idx[name]), output=10 + idx[name])
+
+            lists = [[launch("q", 0), launch("k", 0), launch("v", 0)], [launch("o", 1)],
+                     [launch("gate", 0), launch("up", 0)], [launch("down", 2)]]
+            backend.prepare([l for ls in lists for l in ls])
+            self.steps.append([backend.packed(ls, bufs) for ls in lists])
+            self._keep.append(bufs)
+
+    def all_reduce(self, t):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, group=self.group)
+
+    def token(self, n_layers: int):
+        """Queues `n_layers` layer steps (cycling over the distinct weight sets) on the current stream."""
+        ops = TorchOps
+        h = self.h
+        for i in range(n_layers):
+            qkv, o, gu, down = self.steps[i % len(self.steps)]
+            self.x.copy_(ops.rms_normalise(h))
+            qkv()
+            o()
+            self.all_reduce(self.outs["o"])
+            h = h + self.outs["o"]
+            self.x.copy_(ops.rms_normalise(h))
+            gu()
+            self.act.copy_(ops.silu_mul(self.outs["gate"], self.outs["up"]))
+            down()
+            self.all_reduce(self.outs["down"])
+            h = h + self.outs["down"]
+        self.h_out = h
+        return h
