@@ -303,8 +303,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # the e2e outputs must be the resident path's outputs for the same activations
     be.set_stream(stream.cuda_stream)
 
+    # ---- 70B-shaped layer stack, tensor-parallel over the ranks (all ranks take part)
+    tp_obj = None
+    if not args.no_tp:
+        try:
+            tp_obj = measure_tp70b(be, stream, dev, rank, world, quantized)
+        except Exception as e:  # reported, never fatal for the headline line
+            tp_obj = {"error": f"{type(e).__name__}: {e}"[:300]}
+
     if rank != 0:
         return
+
+    prefill_rows = None
+    if world == 1 and not args.no_prefill:
+        prefill_rows = measure_prefill(be, stream, dev, base)
 
     # ---- per-case timing over cold copies (rank 0, N = 1 only): the kbench method scaled to B200's L2
     case_rows = []
@@ -377,9 +389,126 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     }
     if case_rows:
         line["cases"] = case_rows
+    if prefill_rows:
+        line["prefill"] = prefill_rows
+    if tp_obj:
+        line["tp70b"] = tp_obj
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(cases, fmt)
     print(json.dumps(line), flush=True)
+
+
+def _event_time(stream, fn, reps, warm=2):
+    import torch
+    with torch.cuda.stream(stream):
+        for _ in range(warm):
+            fn()
+        stream.synchronize()
+        ts = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            fn()
+            e1.record(stream)
+            stream.synchronize()
+            ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def measure_prefill(be, stream, dev, base):
+    """Prefill Q4_K GEMM (tcgen05): M in {64, 512, 2048} on the gate/up and down shapes; five weight
+    copies are cycled (165 MB > L2). TFLOP/s = 2*M*N*K / time, against the measured bf16 peaks."""
+    import torch
+    from lapid_b200.backend import matmul_launch
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        burst, sustained = float(pk["bf16_tflops"]), float(pk["bf16_tflops_sustained"])
+    except Exception:
+        burst, sustained = 1590.0, 1400.0
+    rows = []
+    for (n, k) in [(14336, 4096), (4096, 14336)]:
+        copies = 5
+        pool = base[(n, k)].repeat(copies).view(copies, -1)
+        for m in (64, 512, 2048):
+            a = torch.randn(m * k, device=dev)
+            o = torch.zeros(m * n, device=dev)
+            torch.cuda.synchronize()
+            bufs = [be.wrap_tensor(a), be.wrap_tensor(o)] + [be.wrap_tensor(pool[c]) for c in range(copies)]
+            ls = [matmul_launch(6, m, n, k, inputs=(0, 2 + c), output=1) for c in range(copies)]
+            be.prepare(ls)
+            ms = _event_time(stream, be.packed(ls, bufs), 5) / copies
+            tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+            rows.append({"fmt": "q4_k", "m": m, "n": n, "k": k, "us": round(ms * 1e3, 1), "tflops": round(tf, 1),
+                         "frac_burst": round(tf / burst, 4), "frac_sustained": round(tf / sustained, 4),
+                         "operands": "bf16 (f32 accumulate in TMEM)"})
+        del pool
+    return rows
+
+
+def measure_tp70b(be, stream, dev, rank, world, quantized):
+    """Llama-70B-shaped layer stack (80 layers: d_model 8192, 64/8 heads of 128, FFN 28672), Q4_K_M-style
+    mix (Q6_K for attn_v and for ffn_down in half of the layers), tensor-parallel over `world` ranks:
+    column-parallel q/k/v/gate/up, row-parallel o/down with an NCCL all-reduce. Eight distinct layer
+    weight sets are cycled so the weights always come from HBM. One token = 80 layers, one CUDA graph."""
+    import torch
+    import torch.distributed as dist
+    from lapid_b200 import tp
+    shape, n_layers, n_sets = tp.LLAMA_70B, 80, 8
+    weights, formats, wbytes = [], [], 0
+    for s_ in range(n_sets):
+        w, f = {}, {}
+        for i, (name, n, k, kind) in enumerate(shape.projections()):
+            fmt = tp.Q6_K if name == "v" or (name == "down" and s_ % 2 == 1) else tp.Q4_K
+            nl, kl = tp.local_shape(name, n, k, kind, world)
+            # random-init weights: a shard of a random matrix is a random matrix of the shard's shape
+            w[name] = quantized(fmt, nl, kl, 5000 + 97 * rank + 10 * s_ + i)
+            f[name] = fmt
+            wbytes += w[name].numel()
+        weights.append(w)
+        formats.append(f)
+    token_bytes = wbytes * n_layers // n_sets
+    out = {"layers": n_layers, "weight_sets_cycled": n_sets, "weight_bytes_per_token_per_gpu": token_bytes,
+           "collective": "nccl all_reduce (f32 sum) after o and down" if world > 1 else "none", "tp": world}
+    for m, key in ((1, "decode_b1"), (512, "prefill_m512")):
+        layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats)
+        layers.h.normal_()
+        torch.cuda.synchronize()
+        run = lambda: layers.token(n_layers)
+        graph = None
+        with torch.cuda.stream(stream):
+            run()
+        stream.synchronize()
+        if m == 1:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    be.set_stream(torch.cuda.current_stream().cuda_stream)
+                    run()
+                be.set_stream(stream.cuda_stream)
+                run = graph.replay
+            except Exception as e:
+                out["graph_error"] = str(e)[:200]
+                be.set_stream(stream.cuda_stream)
+                run = lambda: layers.token(n_layers)
+        if world > 1:
+            dist.barrier()
+        ms = _event_time(stream, run, 5 if m == 1 else 3, warm=2 if m == 1 else 1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        row = {"ms_per_token_step": round(ms, 4), "tok_s": round(m / (ms * 1e-3), 2), "cuda_graph": graph is not None}
+        if m == 1:
+            row["hbm_gbs_per_gpu"] = round(token_bytes / (ms * 1e-3) / 1e9, 1)
+        else:
+            fl = 2.0 * m * sum(n * k for _, n, k, _ in shape.projections()) * n_layers
+            row["tflops_total"] = round(fl / (ms * 1e-3) / 1e12, 1)
+        out[key] = row
+        del layers, graph
+        torch.cuda.empty_cache()
+    return out
 
 
 def cpu_baseline(cases, fmt):
@@ -418,6 +547,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cases", action="store_true", help="skip the per-case breakdown")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM rows")
+    ap.add_argument("--no-tp", action="store_true", help="skip the 70B-shaped tensor-parallel layer stack")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
