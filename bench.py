@@ -469,10 +469,20 @@ def measure_tp70b(be, stream, dev, rank, world, quantized):
         weights.append(w)
         formats.append(f)
     token_bytes = wbytes * n_layers // n_sets
-    out = {"layers": n_layers, "weight_sets_cycled": n_sets, "weight_bytes_per_token_per_gpu": token_bytes,
-           "collective": "nccl all_reduce (f32 sum) after o and down" if world > 1 else "none", "tp": world}
-    for m, key in ((1, "decode_b1"), (512, "prefill_m512")):
-        layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats)
+    out = {"layers": n_layers, "weight_sets_cycled": n_sets, "weight_bytes_per_token_per_gpu": token_bytes, "tp": world,
+           "collective": ("decode: the library's one-shot all-reduce over peer-mapped memory (2 per layer); "
+                          "prefill: nccl all_reduce") if world > 1 else "none"}
+    peer = None
+    if world > 1:
+        try:
+            peer = tp.PeerAllReduce(be, rank, world, dev)
+        except Exception as e:
+            out["peer_all_reduce_error"] = f"{type(e).__name__}: {e}"[:200]
+    variants = [(1, "decode_b1", peer), (512, "prefill_m512", peer)]
+    if world > 1 and peer is not None:
+        variants.insert(1, (1, "decode_b1_nccl", None))  # the library collective, for comparison
+    for m, key, reducer in variants:
+        layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats, peer_all_reduce=reducer)
         layers.h.normal_()
         torch.cuda.synchronize()
         run = lambda: layers.token(n_layers)

@@ -190,6 +190,26 @@ LAPID_B200_API lapid_b200_status lapid_b200_from_ggml_blocks(lapid_b200_device *
                                               uint64_t src_bytes, uint64_t rows, uint64_t cols,
                                               lapid_b200_buffer *dst);
 
+/* ---- tensor parallelism (no counterpart in the reference, which has no multi-GPU code) -------- */
+/* One-shot all-reduce (f32 sum, in place) of a row-parallel projection's partial results over up to
+ * 8 GPUs of one NVLink domain, through peer-mapped memory instead of a library collective.
+ * The caller (one process per GPU) allocates, on every rank, one zero-filled buffer of
+ * lapid_b200_tp_comm_bytes(world, max_elems) bytes that every peer can address ("symmetric
+ * memory": cuMemMap / IPC mappings, e.g. torch.distributed._symmetric_memory), and passes the
+ * `world` base addresses as mapped on THIS GPU, its own at index `rank`. All ranks must issue the
+ * same sequence of all-reduce calls. Sums are formed in rank order on every rank, so the result is
+ * bit-identical on all ranks. Waits on peers are bounded (status "backend" at the next execute). */
+typedef struct lapid_b200_tp_comm lapid_b200_tp_comm;
+LAPID_B200_API uint64_t lapid_b200_tp_comm_bytes(int32_t world, uint64_t max_elems);
+LAPID_B200_API lapid_b200_status lapid_b200_tp_comm_create(lapid_b200_device *dev, int32_t rank, int32_t world,
+                                                           void *const *peer_bases, uint64_t max_elems,
+                                                           lapid_b200_tp_comm **out);
+LAPID_B200_API void lapid_b200_tp_comm_free(lapid_b200_tp_comm *comm);
+/* Queues the all-reduce of `count` f32 (multiple of 4, <= max_elems) at element `offset` of `data`
+ * on the device's stream; returns without waiting. */
+LAPID_B200_API lapid_b200_status lapid_b200_tp_all_reduce(lapid_b200_tp_comm *comm, lapid_b200_buffer *data,
+                                                          uint64_t offset, uint64_t count);
+
 /* ---- decode without allocation ------------------------------------------------------------ */
 /* This entry point has no counterpart in the reference. It exists for hosts that may not allocate
  * device memory when they need a matvec (an engine that gave all device memory to its own arena at

@@ -26,6 +26,7 @@ SOURCES = {
     "qgemm_f32.cu": [],
     "qgemm_tc.cu": [],
     "noalloc.cu": [],
+    "tp_allreduce.cu": [],
     "backend.cc": ["-x", "cu"],
 }
 

@@ -583,6 +583,11 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
 
 }  // namespace
 
+struct lapid_b200_tp_comm {
+    lapid_b200_device *dev = nullptr;  // retained
+    lb::TpAllReduceArgs args{};
+};
+
 namespace lb {
 // For entry points defined in other files: records the error for lapid_b200_last_error() and
 // returns its status code.
@@ -877,6 +882,64 @@ lapid_b200_status lapid_b200_from_ggml_blocks(lapid_b200_device *dev, int32_t fo
             dev->launches++;
         }
         cuda_check(cudaStreamSynchronize(dev->stream), "from_ggml_blocks");
+    });
+}
+
+uint64_t lapid_b200_tp_comm_bytes(int32_t world, uint64_t max_elems) {
+    return world > 0 ? lb::tp_comm_bytes(world, max_elems) : 0;
+}
+
+lapid_b200_status lapid_b200_tp_comm_create(lapid_b200_device *dev, int32_t rank, int32_t world, void *const *peer_bases,
+                                            uint64_t max_elems, lapid_b200_tp_comm **out) {
+    return guard([&] {
+        need(dev);
+        if (!out || !peer_bases) fail("invalid_argument", "out or peer_bases is NULL");
+        if (world < 1 || world > lb::TP_MAX_RANKS || rank < 0 || rank >= world)
+            fail("invalid_argument", "tp: rank " + std::to_string(rank) + " of " + std::to_string(world) + " (at most " +
+                                         std::to_string(lb::TP_MAX_RANKS) + " ranks)");
+        if (max_elems == 0 || max_elems % 4) fail("invalid_argument", "tp: max_elems must be a positive multiple of 4");
+        auto *c = new lapid_b200_tp_comm();
+        for (int i = 0; i < world; i++) {
+            if (!peer_bases[i] || ((uintptr_t)peer_bases[i] & 15)) {
+                delete c;
+                fail("invalid_argument", "tp: peer base " + std::to_string(i) + " is NULL or not 16-byte aligned");
+            }
+            c->args.peer[i] = peer_bases[i];
+        }
+        c->args.rank = rank;
+        c->args.world = world;
+        c->args.max_elems = max_elems;
+        c->args.status = dev->status_dev;
+        dev->refs.fetch_add(1);
+        c->dev = dev;
+        *out = c;
+    });
+}
+
+void lapid_b200_tp_comm_free(lapid_b200_tp_comm *comm) {
+    if (!comm) return;
+    device_release(comm->dev);
+    delete comm;
+}
+
+lapid_b200_status lapid_b200_tp_all_reduce(lapid_b200_tp_comm *comm, lapid_b200_buffer *data, uint64_t offset, uint64_t count) {
+    return guard([&] {
+        if (!comm) fail("invalid_argument", "comm is NULL");
+        need(data, "data");
+        if (data->dev != comm->dev) fail("wrong_backend", "tp: data belongs to another device");
+        if (count % 4 || count > comm->args.max_elems)
+            fail("invalid_launch", "tp: count " + std::to_string(count) + " must be a multiple of 4 and <= " + std::to_string(comm->args.max_elems));
+        if (offset % 4 || offset + count > data->bytes / 4)
+            fail("out_of_bounds", "tp: [" + std::to_string(offset) + ", " + std::to_string(offset + count) + ") exceeds the buffer's " +
+                                      std::to_string(data->bytes / 4) + " elements");
+        lapid_b200_device *dev = comm->dev;
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        lb::TpAllReduceArgs a = comm->args;
+        a.data = (float *)data->ptr + offset;
+        a.count = count;
+        cuda_check(lb::launch_tp_all_reduce(a, dev->stream), "tp all-reduce launch");
+        dev->launches++;
     });
 }
 

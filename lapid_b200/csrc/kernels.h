@@ -107,4 +107,17 @@ size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t k);  // bf16 copy of the a
 cudaError_t launch_qgemm_tc(const GemmTcArgs &args, void *a_bf16_scratch, int sm_count, cudaStream_t stream);
 void qgemm_tc_set_wide(int v);  // tuning: -1 choose, 0 / 1 force one / two accumulators per CTA
 
+// ---- tp_allreduce.cu: one-shot all-reduce over peer-mapped memory
+constexpr int TP_MAX_RANKS = 8;
+struct TpAllReduceArgs {
+    void *peer[TP_MAX_RANKS];  // every rank's symmetric buffer as mapped on this GPU; peer[rank] is this rank's own
+    int rank, world;
+    uint64_t max_elems;        // f32 capacity of one slot
+    float *data;               // local partial, replaced by the sum
+    uint64_t count;            // multiple of 4, <= max_elems
+    int *status;
+};
+size_t tp_comm_bytes(int world, uint64_t max_elems);
+cudaError_t launch_tp_all_reduce(const TpAllReduceArgs &args, cudaStream_t stream);
+
 }  // namespace lb

@@ -212,6 +212,45 @@ class TorchOps:
         return torch.nn.functional.silu(g) * u
 
 
+class PeerAllReduce:
+    """The library's one-shot all-reduce over peer-mapped memory (`lapid_b200_tp_all_reduce`).
+
+    torch's symmetric-memory allocator supplies the buffer that every rank can address (plumbing);
+    the kernel that moves and sums the data is the library's own. Used for decode-sized results;
+    larger ones (prefill) stay on NCCL, whose ring moves 2x the data instead of world x.
+    """
+
+    def __init__(self, backend, rank: int, world: int, device, group=None, max_elems: int = 65536):
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        from . import _lib
+        self.backend, self.max_elems, self._lib = backend, max_elems, _lib
+        lib = _lib.lib()
+        nbytes = int(lib.lapid_b200_tp_comm_bytes(world, max_elems))
+        self.mem = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm.rendezvous(self.mem, group if group is not None else dist.group.WORLD)
+        self.mem.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+        ptrs = (C.c_void_p * world)(*[int(p) for p in self.handle.buffer_ptrs])
+        h = C.c_void_p()
+        _lib.check(lib.lapid_b200_tp_comm_create(backend._h, rank, world, ptrs, max_elems, C.byref(h)))
+        self._h = h
+
+    def fits(self, numel: int) -> bool:
+        return numel % 4 == 0 and numel <= self.max_elems
+
+    def __call__(self, buf, numel: int) -> None:
+        self._lib.check(self._lib.lib().lapid_b200_tp_all_reduce(self._h, buf._h, 0, numel))
+
+    def close(self):
+        if self._h:
+            self._lib.lib().lapid_b200_tp_comm_free(self._h)
+            self._h = None
+
+
 class GpuTpLayers:
     """A stack of decoder layers' projections on one GPU rank, driven through the C ABI.
 
@@ -222,10 +261,11 @@ class GpuTpLayers:
     """
 
     def __init__(self, backend, shape: LayerShape, world: int, rank: int, m: int, weights: list, formats: list,
-                 group=None):
+                 group=None, peer_all_reduce=None):
         import torch
         from .backend import matmul_launch
         self.be, self.shape, self.world, self.rank, self.m, self.group = backend, shape, world, rank, m, group
+        self.peer = peer_all_reduce
         dev = weights[0]["q"].device
         d = shape.d_model
         proj = {name: local_shape(name, n, k, kind, world) for name, n, k, kind in shape.projections()}
@@ -236,6 +276,7 @@ class GpuTpLayers:
         self.act = torch.zeros(m, proj["gate"][0], **f32)
         torch.cuda.synchronize(dev)
         wrap = backend.wrap_tensor
+        self.out_bufs = {name: wrap(self.outs[name]) for name in ("o", "down")}
         self._keep = []
         self.steps = []
         for w, f in zip(weights, formats):
@@ -255,8 +296,13 @@ class GpuTpLayers:
             self.steps.append([backend.packed(ls, bufs) for ls in lists])
             self._keep.append(bufs)
 
-    def all_reduce(self, t):
-        if self.world > 1:
+    def all_reduce(self, name):
+        if self.world == 1:
+            return
+        t = self.outs[name]
+        if self.peer is not None and self.peer.fits(t.numel()):
+            self.peer(self.out_bufs[name], t.numel())
+        else:
             import torch.distributed as dist
             dist.all_reduce(t, group=self.group)
 
@@ -269,13 +315,13 @@ class GpuTpLayers:
             self.x.copy_(ops.rms_normalise(h))
             qkv()
             o()
-            self.all_reduce(self.outs["o"])
+            self.all_reduce("o")
             h = h + self.outs["o"]
             self.x.copy_(ops.rms_normalise(h))
             gu()
             self.act.copy_(ops.silu_mul(self.outs["gate"], self.outs["up"]))
             down()
-            self.all_reduce(self.outs["down"])
+            self.all_reduce("down")
             h = h + self.outs["down"]
         self.h_out = h
         return h

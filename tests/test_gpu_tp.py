@@ -26,7 +26,7 @@ def _build(be, tp, O, quant, torch, rank, world, dev, n_sets):
     return shape, weights, formats
 
 
-def _worker(rank, world, port, m, out_path):
+def _worker(rank, world, port, m, out_path, peer):
     import torch
     import torch.distributed as dist
     import lapid_b200 as lp
@@ -43,9 +43,10 @@ def _worker(rank, world, port, m, out_path):
         stream = torch.cuda.Stream(device=dev)
         be.set_stream(stream.cuda_stream)
         results = []
+        reducer = tp.PeerAllReduce(be, rank, world, dev) if peer else None
         for w_ in ((world, rank), (1, 0)):
             shape, weights, formats = _build(be, tp, O, quant, torch, w_[1], w_[0], dev, 2)
-            layers = tp.GpuTpLayers(be, shape, w_[0], w_[1], m, weights, formats)
+            layers = tp.GpuTpLayers(be, shape, w_[0], w_[1], m, weights, formats, peer_all_reduce=reducer)
             layers.h.copy_(torch.from_numpy(O.normal(99, m * shape.d_model).reshape(m, -1)).to(dev))
             torch.cuda.synchronize(dev)
             with torch.cuda.stream(stream):
@@ -57,6 +58,11 @@ def _worker(rank, world, port, m, out_path):
                 out = layers.token(3)
             stream.synchronize()
             results.append(np.concatenate([first_o.reshape(-1), out.cpu().numpy().reshape(-1)]))
+        if peer:  # the one-shot all-reduce gives every rank the same bits
+            mine = torch.from_numpy(results[0]).to(dev)
+            other = mine.clone()
+            dist.broadcast(other, src=0)
+            assert torch.equal(mine, other)
         if rank == 0:
             np.save(out_path, np.stack(results))
         dist.barrier()
@@ -64,8 +70,9 @@ def _worker(rank, world, port, m, out_path):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("peer", [False, True])
 @pytest.mark.parametrize("m", [1, 4])
-def test_two_gpu_layer_stack_matches_one_gpu(tmp_path, m):
+def test_two_gpu_layer_stack_matches_one_gpu(tmp_path, m, peer):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -74,7 +81,7 @@ def test_two_gpu_layer_stack_matches_one_gpu(tmp_path, m):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     out_path = str(tmp_path / "out.npy")
-    mp.spawn(_worker, args=(2, port, m, out_path), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, m, out_path, peer), nprocs=2, join=True)
     sharded, single = np.load(out_path)
     n_o = m * SHAPE_ARGS[0]
 
