@@ -226,6 +226,7 @@ struct Plan {
     lapid_b200_layout wl{};
     size_t scratch = 0;  // bytes of activation scratch the launch needs
     bool fast = false;   // specialised Q4_K GEMV (activations as 336-byte records)
+    bool fast_i8 = false;  // specialised Int8 GEMV (activations as planes)
     bool tc = false;     // tensor-core GEMM (needs a bf16 copy of the activations in the scratch)
 };
 
@@ -288,8 +289,8 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
         size_t sc = align_up((uint64_t)p.rows * (l.k / 32) * 4, 256);
         size_t rec = align_up((uint64_t)p.rows * ((l.k + 255) / 256) * lb::REC, 256);  // record layout of the fast path
         p.scratch = qa + 2 * sc > rec ? qa + 2 * sc : rec;
-        p.fast = dev.gemv_fast && l.b_dtype == LAPID_B200_DTYPE_Q4_K && l.k % 256 == 0 && l.k >= 256 &&
-                 (size_t)p.rows * (l.k / 256) * lb::REC <= 150 * 1024;
+        p.fast = dev.gemv_fast && lb::qgemv_kq_fast_shape_ok(l.b_dtype, p.rows, (uint32_t)l.k);
+        p.fast_i8 = dev.gemv_fast && l.b_dtype == LAPID_B200_DTYPE_INT8 && lb::qgemv_i8_fast_shape_ok(p.rows, (uint32_t)l.k);
     } else {
         p.tc = !dev.gemm_f32 && l.b_dtype == LAPID_B200_DTYPE_Q4_K && l.k % 256 == 0 && l.k >= 256;
         if (p.tc) p.scratch = align_up(lb::qgemm_tc_scratch_bytes(p.rows, (uint32_t)l.k), 256);
@@ -400,7 +401,8 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             dev.launches++;
             slot->done = true;
         }
-        if (slot->records) cuda_check(lb::launch_qgemv_q4k_fast(g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        else if (p.fast_i8 && ((uintptr_t)g.w & 15) == 0) cuda_check(lb::launch_qgemv_i8_fast(g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
         else cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
         dev.launches++;
         return;

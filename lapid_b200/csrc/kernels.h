@@ -68,7 +68,13 @@ cudaError_t qgemv_init();
 // Reads the activations as 336-byte records (ActQuantArgs::records) from args.qa.
 bool qgemv_q4k_fast_supported(const GemvArgs &args);
 cudaError_t launch_qgemv_q4k_fast(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
-void qgemv_q4k_fast_set_cta_cap(int cap);  // tuning: at most this many CTAs per SM (0 = as many as fit)
+bool qgemv_kq_fast_supported(int fmt, const GemvArgs &args);  // Q4_K, and Q6_K when K % 2048 == 0
+bool qgemv_kq_fast_shape_ok(int fmt, uint32_t rows, uint32_t k);  // same, without the pointer checks
+cudaError_t launch_qgemv_kq_fast(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+void qgemv_q4k_fast_set_cta_cap(int cap);
+// ---- qgemv_i8.cu: fast path for Int8 planes (K % 512 == 0); reads the activation planes
+bool qgemv_i8_fast_shape_ok(uint32_t rows, uint32_t k);
+cudaError_t launch_qgemv_i8_fast(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);  // tuning: at most this many CTAs per SM (0 = as many as fit)
 
 // out[bt, i, j] = 0 (+ extra) for the k == 0 case (crates/lapid-cpu/src/matmul/mod.rs:237-247).
 cudaError_t launch_fill_zero_k(const GemvArgs &args, cudaStream_t stream);

@@ -1,4 +1,4 @@
-// Q4_K decode GEMV, fast path for 1..8 activation rows (arithmetic: see qgemv.cu; this file only
+// Q4_K and Q6_K decode GEMV, fast path for 1..8 activation rows (arithmetic: see qgemv.cu; this file only
 // changes how the work is laid out on the machine).
 //
 //  * Weights reach the SM through per-warp rings of shared-memory stages filled by the bulk-copy
@@ -27,8 +27,11 @@
 
 namespace lb {
 
-constexpr int STAGE_BYTES = 32 * Q4K_BYTES;  // 4608
-constexpr int BAR_BYTES = 256;               // warps * STAGES * 8 <= 256
+template <int FMT> struct Blk {
+    static constexpr int BYTES = FMT == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES;
+    static constexpr int STAGE = 32 * BYTES;  // 4608 / 6720: one bulk copy, a multiple of 16 bytes
+};
+constexpr int BAR_BYTES = 256;  // warps * STAGES * 8 <= 256
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -92,16 +95,41 @@ __device__ __forceinline__ float pair_dot(const uint32_t (&v)[8], const uint32_t
     return acc;
 }
 
-// REGACT: one activation row whose super-block index per lane never changes (K/256 <= G): the
-// lane keeps its 336-byte activation record in registers for the whole kernel.
+// `n` words starting at a 2-byte aligned shared address (Q6_K blocks are 210 bytes long, so every
+// other block of a stage starts in the middle of a word): aligned loads plus a funnel shift.
+template <int N> __device__ __forceinline__ void lds_words_align2(const uint8_t *p, uint32_t (&w)[N]) {
+    const uint32_t *q = (const uint32_t *)((uintptr_t)p & ~(uintptr_t)3);
+    const uint32_t sh = ((uint32_t)(uintptr_t)p & 2u) * 8u;
+    uint32_t prev = q[0];
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        const uint32_t nxt = q[i + 1];
+        w[i] = __funnelshift_r(prev, nxt, sh);
+        prev = nxt;
+    }
+}
+
+// One 32-element Q6_K sub-block pair member against one activation group: two 16-element halves
+// with their own int8 scales, v = sc0*dot0 + sc1*dot1 (crates/lapid-cpu/src/kquant.rs:224-233).
+__device__ __forceinline__ float q6_group(const uint32_t (&q)[8], const uint32_t (&a)[8], float sc0, float sc1) {
+    int d0 = 0, d1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        d0 = __dp4a((int)q[i], (int)a[i], d0);
+        d1 = __dp4a((int)q[i + 4], (int)a[i + 4], d1);
+    }
+    return fmaf(sc1, (float)d1, sc0 * (float)d0);
+}
+
 // Warps per CTA: small CTAs for one or two rows (many CTAs per SM, so that one slot can be left to
 // the next kernel), larger ones beyond, where the activation records are the bigger share of the
 // shared memory and are better amortised over more warps.
 template <int M> struct Shape { static constexpr int WARPS = M <= 2 ? 4 : 8, MIN_CTAS = M <= 2 ? 5 : 2; };
 
-template <int M, int G, bool REGACT>
-__global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_q4k_fast_kernel(GemvArgs p) {
+template <int FMT, int M, int G>
+__global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_kq_fast_kernel(GemvArgs p) {
     constexpr int STAGES = 2;
+    constexpr int BB = Blk<FMT>::BYTES, STAGE_BYTES = Blk<FMT>::STAGE;
     constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -141,8 +169,8 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
                 first = row0 * nblk + pit * 32;
                 count = min(32u, nblk - pit * 32);
             }
-            mbar_expect_tx(bars + pslot, count * Q4K_BYTES);
-            bulk_g2s(ring + (size_t)pslot * STAGE_BYTES, p.w + (uint64_t)first * Q4K_BYTES, count * Q4K_BYTES, bars + pslot);
+            mbar_expect_tx(bars + pslot, count * BB);
+            bulk_g2s(ring + (size_t)pslot * STAGE_BYTES, p.w + (uint64_t)first * BB, count * BB, bars + pslot);
         }
         pslot ^= 1;
         if (++pit == iters) {
@@ -156,15 +184,7 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    uint32_t ra[REGACT ? 80 : 1];
-    if constexpr (REGACT) {
-        const uint4 *src = (const uint4 *)((const uint8_t *)p.qa + (size_t)min((uint32_t)gl, nblk - 1) * REC);
-#pragma unroll
-        for (int i = 0; i < 20; i++) {
-            const uint4 t = __ldg(src + i);
-            ra[4 * i] = t.x; ra[4 * i + 1] = t.y; ra[4 * i + 2] = t.z; ra[4 * i + 3] = t.w;
-        }
-    } else {
+    {
         const uint32_t chunks = p.rows * nblk * (REC / 16);
         const uint8_t *src = (const uint8_t *)p.qa;
         for (uint32_t c = threadIdx.x; c < chunks; c += FAST_THREADS)
@@ -188,32 +208,25 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             }
             const uint32_t b = it * G + gl;
             if (healthy && row < n && b < nblk && gl < nblk) {
-                const uint8_t *blk = ring + (size_t)cslot * STAGE_BYTES + (size_t)(iters == 1 ? sub * nblk + gl : gl) * Q4K_BYTES;
-                const uint4 h = *(const uint4 *)blk;
-                const float d = half_bits_to_float(h.x & 0xffff), dmin = half_bits_to_float(h.x >> 16);
-                const float nd = d * -8388608.0f, ndmin = dmin * -8388608.0f;
-                const uint32_t w0 = h.y, w1 = h.z, w2 = h.w;
-                // bytes: sc_lo = scales 0..3, sc_hi = scales 4..7, likewise the mins
-                const uint32_t sc_lo = w0 & 0x3F3F3F3Fu, mn_lo = w1 & 0x3F3F3F3Fu;
-                const uint32_t sc_hi = (w2 & 0x0F0F0F0Fu) | (((w0 >> 6) & 0x03030303u) << 4);
-                const uint32_t mn_hi = ((w2 >> 4) & 0x0F0F0F0Fu) | (((w1 >> 6) & 0x03030303u) << 4);
+                const uint8_t *blk = ring + (size_t)cslot * STAGE_BYTES + (size_t)(iters == 1 ? sub * nblk + gl : gl) * BB;
+                if constexpr (FMT == FMT_Q4K) {
+                    const uint4 h = *(const uint4 *)blk;
+                    const float d = half_bits_to_float(h.x & 0xffff), dmin = half_bits_to_float(h.x >> 16);
+                    const float nd = d * -8388608.0f, ndmin = dmin * -8388608.0f;
+                    const uint32_t w0 = h.y, w1 = h.z, w2 = h.w;
+                    // bytes: sc_lo = scales 0..3, sc_hi = scales 4..7, likewise the mins
+                    const uint32_t sc_lo = w0 & 0x3F3F3F3Fu, mn_lo = w1 & 0x3F3F3F3Fu;
+                    const uint32_t sc_hi = (w2 & 0x0F0F0F0Fu) | (((w0 >> 6) & 0x03030303u) << 4);
+                    const uint32_t mn_hi = ((w2 >> 4) & 0x0F0F0F0Fu) | (((w1 >> 6) & 0x03030303u) << 4);
 #pragma unroll
-                for (int pp = 0; pp < 4; pp++) {
-                    const uint32_t scw = pp < 2 ? sc_lo : sc_hi, mnw = pp < 2 ? mn_lo : mn_hi;
-                    const uint32_t sel0 = 0x7440u + 2 * (pp & 1), sel1 = sel0 + 1;  // {byte, 0, 0, 0x4B}
-                    const float s0 = scale_byte(scw, sel0, d, nd), m0 = scale_byte(mnw, sel0, dmin, ndmin);
-                    // the high nibbles are used as 16*q: fold the exact factor 1/16 into their scale
-                    const float s1 = scale_byte(scw, sel1, d, nd) * 0.0625f, m1 = scale_byte(mnw, sel1, dmin, ndmin);
-                    const uint4 qa_ = *(const uint4 *)(blk + 16 + 32 * pp), qb_ = *(const uint4 *)(blk + 32 + 32 * pp);
-                    const uint32_t v[8] = {qa_.x, qa_.y, qa_.z, qa_.w, qb_.x, qb_.y, qb_.z, qb_.w};
-                    if constexpr (REGACT) {
-                        const uint32_t al[8] = {ra[20 * pp], ra[20 * pp + 1], ra[20 * pp + 2], ra[20 * pp + 3],
-                                                ra[20 * pp + 4], ra[20 * pp + 5], ra[20 * pp + 6], ra[20 * pp + 7]};
-                        const uint32_t ah[8] = {ra[20 * pp + 8], ra[20 * pp + 9], ra[20 * pp + 10], ra[20 * pp + 11],
-                                                ra[20 * pp + 12], ra[20 * pp + 13], ra[20 * pp + 14], ra[20 * pp + 15]};
-                        acc[0] = pair_dot(v, al, ah, s0, m0, s1, m1, __uint_as_float(ra[20 * pp + 16]), __uint_as_float(ra[20 * pp + 17]),
-                                          __uint_as_float(ra[20 * pp + 18]), __uint_as_float(ra[20 * pp + 19]), acc[0]);
-                    } else {
+                    for (int pp = 0; pp < 4; pp++) {
+                        const uint32_t scw = pp < 2 ? sc_lo : sc_hi, mnw = pp < 2 ? mn_lo : mn_hi;
+                        const uint32_t sel0 = 0x7440u + 2 * (pp & 1), sel1 = sel0 + 1;  // {byte, 0, 0, 0x4B}
+                        const float s0 = scale_byte(scw, sel0, d, nd), m0 = scale_byte(mnw, sel0, dmin, ndmin);
+                        // the high nibbles are used as 16*q: fold the exact factor 1/16 into their scale
+                        const float s1 = scale_byte(scw, sel1, d, nd) * 0.0625f, m1 = scale_byte(mnw, sel1, dmin, ndmin);
+                        const uint4 qa_ = *(const uint4 *)(blk + 16 + 32 * pp), qb_ = *(const uint4 *)(blk + 32 + 32 * pp);
+                        const uint32_t v[8] = {qa_.x, qa_.y, qa_.z, qa_.w, qb_.x, qb_.y, qb_.z, qb_.w};
 #pragma unroll
                         for (int r = 0; r < M; r++) {
                             const uint4 *rec = (const uint4 *)(acts + ((size_t)r * nblk + b) * REC + 80 * pp);
@@ -222,6 +235,41 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
                             const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
                             acc[r] = pair_dot(v, al, ah, s0, m0, s1, m1, __uint_as_float(sc.x), __uint_as_float(sc.y),
                                               __uint_as_float(sc.z), __uint_as_float(sc.w), acc[r]);
+                        }
+                    }
+                } else {
+                    // Q6_K: ql[128] | qh[64] | int8 sc[16] | f16 d; the block is only 2-byte aligned
+                    const float d = half_bits_to_float((uint32_t)blk[208] | ((uint32_t)blk[209] << 8));
+#pragma unroll
+                    for (int nh = 0; nh < 2; nh++) {  // the two 128-element halves
+                        uint32_t ql[16], qh[8], scw[2];
+                        lds_words_align2<16>(blk + 64 * nh, ql);
+                        lds_words_align2<8>(blk + 128 + 32 * nh, qh);
+                        lds_words_align2<2>(blk + 192 + 8 * nh, scw);
+#pragma unroll
+                        for (int j = 0; j < 2; j++) {  // record pair 2*nh + j: sub-blocks w = 2j (ql bytes 0..31) and 2j+1 (32..63)
+                            const int pp = 2 * nh + j;
+                            uint32_t q0[8], q1[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const uint32_t lo0 = (ql[i] >> (4 * j)) & 0x0F0F0F0Fu, lo1 = (ql[8 + i] >> (4 * j)) & 0x0F0F0F0Fu;
+                                const uint32_t hi0 = ((qh[i] >> (4 * j)) & 0x03030303u) << 4, hi1 = ((qh[i] >> (4 * j + 2)) & 0x03030303u) << 4;
+                                q0[i] = __vsub4(lo0 | hi0, 0x20202020u);  // signed quants -32..31
+                                q1[i] = __vsub4(lo1 | hi1, 0x20202020u);
+                            }
+                            const float s00 = (float)(int8_t)(scw[j] & 0xff), s01 = (float)(int8_t)((scw[j] >> 8) & 0xff);
+                            const float s10 = (float)(int8_t)((scw[j] >> 16) & 0xff), s11 = (float)(int8_t)(scw[j] >> 24);
+#pragma unroll
+                            for (int r = 0; r < M; r++) {
+                                const uint4 *rec = (const uint4 *)(acts + ((size_t)r * nblk + b) * REC + 80 * pp);
+                                const uint4 a0 = rec[0], a1 = rec[1], a2 = rec[2], a3 = rec[3], sc = rec[4];
+                                const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                                const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+                                float a_ = acc[r];
+                                a_ = fmaf(d * __uint_as_float(sc.x), q6_group(q0, al, s00, s01), a_);
+                                a_ = fmaf(d * __uint_as_float(sc.y), q6_group(q1, ah, s10, s11), a_);
+                                acc[r] = a_;
+                            }
                         }
                     }
                 }
@@ -249,11 +297,11 @@ static int g_cta_cap = 0;  // 0 = as many CTAs per SM as fit; set through qgemv_
 
 void qgemv_q4k_fast_set_cta_cap(int cap) { g_cta_cap = cap; }
 
-template <int M, int G, bool REGACT>
+template <int FMT, int M, int G>
 static cudaError_t launch_fast(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t stream) {
-    auto kern = qgemv_q4k_fast_kernel<M, G, REGACT>;
+    auto kern = qgemv_kq_fast_kernel<FMT, M, G>;
     constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
-    const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * STAGE_BYTES + (REGACT ? 0 : (size_t)a.rows * (a.k / QK) * REC);
+    const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * Blk<FMT>::STAGE + (size_t)a.rows * (a.k / QK) * REC;
     static size_t configured = 0, occ_smem = 0;
     static int ctas_per_sm = 0;
     if (smem > configured) {
@@ -292,30 +340,51 @@ static cudaError_t launch_fast(const GemvArgs &a, int sm_count, bool pdl, cudaSt
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
-template <int M> static cudaError_t launch_fast_g(const GemvArgs &a, int sm, bool pdl, cudaStream_t s) {
+template <int FMT, int M> static cudaError_t launch_fast_g(const GemvArgs &a, int sm, bool pdl, cudaStream_t s) {
     const uint32_t nblk = a.k / QK;
-    if (nblk <= 8) return launch_fast<M, 8, false>(a, sm, pdl, s);
-    if (nblk <= 16) return launch_fast<M, 16, false>(a, sm, pdl, s);
-    return launch_fast<M, 32, false>(a, sm, pdl, s);
+    if (nblk <= 8) return launch_fast<FMT, M, 8>(a, sm, pdl, s);
+    if (nblk <= 16) return launch_fast<FMT, M, 16>(a, sm, pdl, s);
+    return launch_fast<FMT, M, 32>(a, sm, pdl, s);
 }
 
-bool qgemv_q4k_fast_supported(const GemvArgs &a) {
-    return a.rows >= 1 && a.rows <= 8 && a.k % QK == 0 && a.k >= QK &&
-           (size_t)a.rows * (a.k / QK) * REC <= 150 * 1024 && ((uintptr_t)a.w & 15) == 0;
+// Q6_K stages must start on a 16-byte boundary for the bulk copy: 8 blocks = 1680 bytes, so the
+// fast path takes K that are multiples of 2048 (every model shape in practice); other K use the
+// generic kernel.
+bool qgemv_kq_fast_shape_ok(int fmt, uint32_t rows, uint32_t k) {
+    if (fmt != FMT_Q4K && fmt != FMT_Q6K) return false;
+    if (rows < 1 || rows > 8 || k % QK != 0 || k < QK) return false;
+    if (fmt == FMT_Q6K && (k / QK) % 8 != 0) return false;
+    const size_t warps = rows <= 2 ? 4 : 8;
+    const size_t stage = 32 * (size_t)(fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+    return BAR_BYTES + warps * 2 * stage + (size_t)rows * (k / QK) * REC <= 227 * 1024;
+}
+
+bool qgemv_kq_fast_supported(int fmt, const GemvArgs &a) {
+    return qgemv_kq_fast_shape_ok(fmt, a.rows, a.k) && ((uintptr_t)a.w & 15) == 0;
+}
+
+bool qgemv_q4k_fast_supported(const GemvArgs &a) { return qgemv_kq_fast_supported(FMT_Q4K, a); }
+
+template <int FMT> static cudaError_t launch_fmt(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
+    switch (a.rows) {
+        case 1: return launch_fast_g<FMT, 1>(a, sm_count, pdl, s);
+        case 2: return launch_fast_g<FMT, 2>(a, sm_count, pdl, s);
+        case 3: return launch_fast_g<FMT, 3>(a, sm_count, pdl, s);
+        case 4: return launch_fast_g<FMT, 4>(a, sm_count, pdl, s);
+        case 5: return launch_fast_g<FMT, 5>(a, sm_count, pdl, s);
+        case 6: return launch_fast_g<FMT, 6>(a, sm_count, pdl, s);
+        case 7: return launch_fast_g<FMT, 7>(a, sm_count, pdl, s);
+        case 8: return launch_fast_g<FMT, 8>(a, sm_count, pdl, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_qgemv_kq_fast(int fmt, const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
+    return fmt == FMT_Q6K ? launch_fmt<FMT_Q6K>(a, sm_count, pdl, s) : launch_fmt<FMT_Q4K>(a, sm_count, pdl, s);
 }
 
 cudaError_t launch_qgemv_q4k_fast(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
-    switch (a.rows) {
-        case 1: return launch_fast_g<1>(a, sm_count, pdl, s);
-        case 2: return launch_fast_g<2>(a, sm_count, pdl, s);
-        case 3: return launch_fast_g<3>(a, sm_count, pdl, s);
-        case 4: return launch_fast_g<4>(a, sm_count, pdl, s);
-        case 5: return launch_fast_g<5>(a, sm_count, pdl, s);
-        case 6: return launch_fast_g<6>(a, sm_count, pdl, s);
-        case 7: return launch_fast_g<7>(a, sm_count, pdl, s);
-        case 8: return launch_fast_g<8>(a, sm_count, pdl, s);
-        default: return cudaErrorInvalidValue;
-    }
+    return launch_fmt<FMT_Q4K>(a, sm_count, pdl, s);
 }
 
 }  // namespace lb
