@@ -140,7 +140,7 @@ def run_reference(args, rank: int, world: int):
     for m in MS:
         for kk in (4096, 14336):
             xs[(m, kk)] = rng.standard_normal(m * kk, dtype=np.float32)
-    cases = [(m, n, k) for (n, k, _) in SHAPES for m in MS]
+    cases = [(m, n, k) for m in MS for (n, k, _) in SHAPES]  # layer order: the projections of one batch size follow each other
     step_bytes = sum(algo_bytes(fmt, m, n, k) for (m, n, k) in cases)
 
     def step():
@@ -205,7 +205,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         return out
 
     fmt = 6
-    cases = [(m, n, k) for (n, k, _) in SHAPES for m in MS]
+    cases = [(m, n, k) for m in MS for (n, k, _) in SHAPES]  # layer order: the projections of one batch size follow each other
     base = {(n, k): quantized(fmt, n, k, 100 + i) for i, (n, k, _) in enumerate(SHAPES)}
     # one distinct weight copy per launch; packed activations and outputs
     a_off, o_off, ao, oo = [], [], 0, 0

@@ -23,6 +23,7 @@ SOURCES = {
     "actquant.cu": ["-fmad=false"],
     "qgemv.cu": [],
     "qgemv_q4k.cu": [],
+    "qgemv_q4k_mma.cu": [],
     "qgemv_i8.cu": [],
     "qgemm_f32.cu": [],
     "qgemm_tc.cu": [],

@@ -31,7 +31,18 @@ __device__ __forceinline__ void quantize_group(const ActQuantArgs &p, uint32_t r
     int sum = q;
 #pragma unroll
     for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (p.records) {
+    if (p.records == 2) {
+        // tiles of the tensor-core decode kernel: per super-block [sub-block][row][32] quants, then
+        // [row pair][sub-block][2] group scales and the same for d * sum(q)
+        const uint32_t sb = g & 7;
+        uint8_t *blk = (uint8_t *)p.qa + (uint64_t)(g >> 3) * (256 * p.rows + 512);
+        blk[(sb * p.rows + r) * 32 + lane] = (uint8_t)(int8_t)q;
+        if (lane == 0) {
+            float *sc = (float *)(blk + 256 * p.rows) + ((r >> 1) * 8 + sb) * 2 + (r & 1);
+            sc[0] = d;
+            sc[64] = xmul(d, (float)sum);
+        }
+    } else if (p.records) {
         uint8_t *rec = (uint8_t *)p.qa + ((uint64_t)r * (p.k / QK) + (g >> 3)) * REC + 80 * ((g & 7) >> 1);
         rec[32 * (g & 1) + lane] = (uint8_t)(int8_t)q;
         if (lane == 0) {

@@ -150,6 +150,8 @@ struct lapid_b200_device {
     uint32_t gemv_max_rows = 8;
     bool act_reuse = true;  // share / hoist activation pre-passes inside one launch list
     bool gemv_fast = true;   // specialised GEMV kernels where the shape allows; off = generic kernel only
+    bool gemv_group = true;  // consecutive independent K-quant decode launches of one list share a kernel
+    uint32_t gemv_mma_rows = 4;  // Q4_K decode launches with at least this many rows use the int8 tensor-core kernel; 0 = never
     bool gemm_f32 = false;  // true: rows > gemv_max_rows always take the exact-f32 GEMM instead of the tensor cores
 
     void make_current() const { cuda_check(cudaSetDevice(ordinal), "cudaSetDevice"); }
@@ -225,7 +227,9 @@ struct Plan {
     uint32_t rows = 0;
     lapid_b200_layout wl{};
     size_t scratch = 0;  // bytes of activation scratch the launch needs
-    bool fast = false;   // specialised Q4_K GEMV (activations as 336-byte records)
+    bool fast = false;   // specialised Q4_K / Q6_K GEMV (activations as 336-byte records)
+    bool mma = false;    // Q4_K GEMV on the int8 tensor-core instruction (activations as tiles)
+    int records() const { return mma ? 2 : fast ? 1 : 0; }  // ActQuantArgs::records
     bool fast_i8 = false;  // specialised Int8 GEMV (activations as planes)
     bool tc = false;     // tensor-core GEMM (needs a bf16 copy of the activations in the scratch)
 };
@@ -242,6 +246,55 @@ struct ActSlot {
     bool same(const ActSlot &o) const {
         return ptr == o.ptr && off == o.off && bs == o.bs && rs == o.rs && rows == o.rows && m == o.m && k == o.k &&
                records == o.records;
+    }
+};
+
+// Decode launches of one list that wait to go out as one grouped kernel: same format, rows and k,
+// and none of them reads or overwrites what another one writes, so running them side by side
+// gives what running them in order gives.
+struct PendingGroup {
+    struct Range {
+        const char *lo, *hi;
+        bool hits(const Range &o) const { return lo < o.hi && o.lo < hi; }
+    };
+    int fmt = 0, mode = 0;  // mode: ActQuantArgs::records of the members (1 = dp4a kernel, 2 = tensor-core kernel)
+    lb::GemvGroup g{};
+    std::vector<Range> writes, reads;
+
+    bool accepts(int f, int md, const lb::GemvArgs &a, const Range &out, const Range *in, int n_in) {
+        if (g.count == 0) return true;
+        if (g.count == lb::GEMV_GROUP_MAX || f != fmt || md != mode || a.rows != g.item[0].rows || a.k != g.item[0].k) return false;
+        for (const Range &w : writes) {
+            if (w.hits(out)) return false;
+            for (int i = 0; i < n_in; i++)
+                if (w.hits(in[i])) return false;
+        }
+        for (const Range &r : reads)
+            if (r.hits(out)) return false;
+        g.item[g.count] = a;
+        g.count++;
+        bool fits = md == 2 ? lb::qgemv_q4k_mma_group_fits(g) : lb::qgemv_kq_group_smem(f, g) <= 227 * 1024;
+        g.count--;
+        return fits;
+    }
+    void add(int f, int md, const lb::GemvArgs &a, const Range &out, const Range *in, int n_in) {
+        fmt = f;
+        mode = md;
+        g.item[g.count++] = a;
+        writes.push_back(out);
+        for (int i = 0; i < n_in; i++) reads.push_back(in[i]);
+    }
+    void flush(lapid_b200_device &dev) {
+        if (g.count == 0) return;
+        int count = g.count;
+        g.count = 0;  // also when the launch fails: the list is abandoned then
+        writes.clear();
+        reads.clear();
+        lb::GemvGroup out = g;
+        out.count = count;
+        if (mode == 2) cuda_check(lb::launch_qgemv_q4k_mma(out, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        else cuda_check(lb::launch_qgemv_kq_group(fmt, out, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        dev.launches++;
     }
 };
 
@@ -291,6 +344,12 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
         p.scratch = qa + 2 * sc > rec ? qa + 2 * sc : rec;
         p.fast = dev.gemv_fast && lb::qgemv_kq_fast_shape_ok(l.b_dtype, p.rows, (uint32_t)l.k);
         p.fast_i8 = dev.gemv_fast && l.b_dtype == LAPID_B200_DTYPE_INT8 && lb::qgemv_i8_fast_shape_ok(p.rows, (uint32_t)l.k);
+        p.mma = dev.gemv_fast && dev.gemv_mma_rows > 0 && p.rows >= dev.gemv_mma_rows && l.b_dtype == LAPID_B200_DTYPE_Q4_K &&
+                lb::qgemv_q4k_mma_shape_ok(p.rows, (uint32_t)l.k);
+        if (p.mma) {
+            size_t tiles = align_up(lb::qgemv_q4k_mma_act_bytes(p.rows, (uint32_t)l.k), 256);
+            if (tiles > p.scratch) p.scratch = tiles;
+        }
     } else {
         p.tc = !dev.gemm_f32 && l.b_dtype == LAPID_B200_DTYPE_Q4_K && l.k % 256 == 0 && l.k >= 256;
         if (p.tc) p.scratch = align_up(lb::qgemm_tc_scratch_bytes(p.rows, (uint32_t)l.k), 256);
@@ -299,7 +358,7 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
 }
 
 void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_buffer *const *buffers, size_t n_buffers,
-                ActSlot *slot) {
+                ActSlot *slot, PendingGroup *pend = nullptr) {
     Plan p = plan_launch(dev, l);
     auto get = [&](uint32_t id) -> lapid_b200_buffer * {
         if (id >= n_buffers || !buffers[id])
@@ -354,6 +413,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
     g.m = (uint32_t)l.m;
     g.n = (uint32_t)l.n;
     g.k = (uint32_t)l.k;
+    if (pend && !(p.gemv && !p.zero_k)) pend->flush(dev);  // anything but a decode launch ends the group
     if (p.zero_k) {
         cuda_check(lb::launch_fill_zero_k(g, dev.stream), "fill launch");
         dev.launches++;
@@ -368,7 +428,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         ActSlot local;
         if (!slot) {  // not planned by the caller: a private slot at the start of the scratch
             dev.ensure_scratch(p.scratch);
-            local.records = p.fast ? 1 : 0;
+            local.records = p.records();
             slot = &local;
         }
         char *base = (char *)dev.scratch + slot->offset;
@@ -396,12 +456,34 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         g.a_bs = q.a_bs;
         g.a_rs = q.a_rs;
         g.status = dev.status_dev;
+        if (pend && slot->records) {
+            using Range = PendingGroup::Range;
+            const char *ob = (const char *)out->ptr;
+            Range wr{ob + 4 * l.out.offset, ob + 4 * last};
+            Range in[3];
+            int n_in = 0;
+            for (int i = 0; i < l.n_inputs; i++) in[n_in++] = Range{(const char *)ins[i]->ptr, (const char *)ins[i]->ptr + ins[i]->bytes};
+            if (!pend->accepts(l.b_dtype, slot->records, g, wr, in, n_in)) pend->flush(dev);
+            if (!slot->done) {  // its input is not written by a pending launch (checked above), so it may run first
+                cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl, dev.stream), "act_quant launch");
+                dev.launches++;
+                slot->done = true;
+            }
+            pend->add(l.b_dtype, slot->records, g, wr, in, n_in);
+            return;
+        }
+        if (pend) pend->flush(dev);
         if (!slot->done) {
             cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl, dev.stream), "act_quant launch");
             dev.launches++;
             slot->done = true;
         }
-        if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        if (slot->records == 2) {
+            lb::GemvGroup one{};
+            one.count = 1;
+            one.item[0] = g;
+            cuda_check(lb::launch_qgemv_q4k_mma(one, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        } else if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
         else if (p.fast_i8 && ((uintptr_t)g.w & 15) == 0) cuda_check(lb::launch_qgemv_i8_fast(g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
         else cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
         dev.launches++;
@@ -496,7 +578,7 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
                 key.rows = p.rows;
                 key.m = (uint32_t)l.m;
                 key.k = (uint32_t)l.k;
-                key.records = p.fast ? 1 : 0;
+                key.records = p.records();
                 bool clean = true;  // nothing in the list so far wrote the buffer A lives in
                 for (const Range &w : written)
                     if ((const char *)ab->ptr < w.hi && w.lo < (const char *)ab->ptr + ab->bytes) clean = false;
@@ -572,7 +654,15 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
         }
         flush();
     }
-    for (size_t i = 0; i < n; i++) run_launch(*dev, launches[i], buffers, nbuf, slot_of[i] >= 0 ? &slots[slot_of[i]] : nullptr);
+    PendingGroup pend;
+    PendingGroup *pp = dev->gemv_group ? &pend : nullptr;
+    try {
+        for (size_t i = 0; i < n; i++) run_launch(*dev, launches[i], buffers, nbuf, slot_of[i] >= 0 ? &slots[slot_of[i]] : nullptr, pp);
+    } catch (...) {
+        pend.flush(*dev);  // the launches before the rejected one still run, as they would one by one
+        throw;
+    }
+    pend.flush(*dev);
     if (wait) {
         cuda_check(cudaStreamSynchronize(dev->stream), "cudaStreamSynchronize");
         if (*dev->status_host != 0) {
@@ -693,6 +783,14 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             else fail("invalid_argument", "gemv must be \"fast\" or \"generic\"");
         } else if (k == "act_reuse") {
             dev->act_reuse = v != "0";
+        } else if (k == "gemv_group") {
+            dev->gemv_group = v != "0";
+        } else if (k == "gemv_mma_rows") {
+            int r = std::atoi(value);
+            if (r < 0 || r > 8) fail("invalid_argument", "gemv_mma_rows must be in 0..8");
+            dev->gemv_mma_rows = (uint32_t)r;
+        } else if (k == "gemv_mma_config") {
+            lb::qgemv_q4k_mma_set_config(std::atoi(value));
         } else if (k == "gemv_ctas_per_sm") {
             lb::qgemv_q4k_fast_set_cta_cap(std::atoi(value));
         } else if (k == "gemm_wide") {

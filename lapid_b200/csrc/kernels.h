@@ -68,6 +68,25 @@ cudaError_t qgemv_init();
 // Reads the activations as 336-byte records (ActQuantArgs::records) from args.qa.
 bool qgemv_q4k_fast_supported(const GemvArgs &args);
 cudaError_t launch_qgemv_q4k_fast(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+// Up to GEMV_GROUP_MAX independent projections with the same format, rows and k in one launch.
+constexpr int GEMV_GROUP_MAX = 6;
+struct GemvGroup {
+    GemvArgs item[GEMV_GROUP_MAX];
+    uint32_t task_end[GEMV_GROUP_MAX];  // filled by the launcher
+    uint32_t act_off[GEMV_GROUP_MAX];   // shared-memory offset of each item's activation records
+    uint8_t act_copy[GEMV_GROUP_MAX];   // 0 when an earlier item of the group has the same activations
+    int count;
+    uint32_t act_bytes;
+};
+size_t qgemv_kq_group_smem(int fmt, GemvGroup &group);  // dynamic shared memory the group would need
+cudaError_t launch_qgemv_kq_group(int fmt, GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream);
+// Q4_K decode on the warp-level int8 tensor-core instruction (4..8 rows pay off); activations as
+// tiles (ActQuantArgs::records == 2).
+bool qgemv_q4k_mma_shape_ok(uint32_t rows, uint32_t k);
+size_t qgemv_q4k_mma_act_bytes(uint32_t rows, uint32_t k);
+bool qgemv_q4k_mma_group_fits(GemvGroup &group);
+cudaError_t launch_qgemv_q4k_mma(GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream);
+void qgemv_q4k_mma_set_config(int index);  // -1 = pick by shared-memory fit
 bool qgemv_kq_fast_supported(int fmt, const GemvArgs &args);  // Q4_K, and Q6_K when K % 2048 == 0
 bool qgemv_kq_fast_shape_ok(int fmt, uint32_t rows, uint32_t k);  // same, without the pointer checks
 cudaError_t launch_qgemv_kq_fast(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);

@@ -127,7 +127,7 @@ __device__ __forceinline__ float q6_group(const uint32_t (&q)[8], const uint32_t
 template <int M> struct Shape { static constexpr int WARPS = M <= 2 ? 4 : 8, MIN_CTAS = M <= 2 ? 5 : 2; };
 
 template <int FMT, int M, int G>
-__global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_kq_fast_kernel(GemvArgs p) {
+__global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_kq_fast_kernel(GemvGroup grp) {
     constexpr int STAGES = 2;
     constexpr int BB = Blk<FMT>::BYTES, STAGE_BYTES = Blk<FMT>::STAGE;
     constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
@@ -135,9 +135,18 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int RPW = 32 / G;
     const int sub = lane / G, gl = lane % G;
-    const uint32_t n = p.n, nblk = p.k / QK;
+    // A launch covers up to GEMV_GROUP_MAX independent projections with the same format, row count
+    // and K (q/k/v, gate/up): their tasks (32/G weight rows each) form one list, so the weight
+    // stream does not stop between them and small matrices share one launch.
+    const uint32_t nblk = grp.item[0].k / QK;
     const uint32_t iters = (nblk + G - 1) / G;
-    const uint32_t tasks = (n + RPW - 1) / RPW;
+    const uint32_t tasks = grp.task_end[grp.count - 1];
+    auto locate = [&](uint32_t t, uint32_t &local) -> int {
+        int i = 0;
+        while (t >= grp.task_end[i]) i++;
+        local = t - (i ? grp.task_end[i - 1] : 0);
+        return i;
+    };
     // CTA c owns tasks [t_lo, t_hi); its warps take them round-robin
     const uint32_t t_lo = (uint32_t)(((uint64_t)tasks * blockIdx.x) / gridDim.x);
     const uint32_t t_hi = (uint32_t)(((uint64_t)tasks * (blockIdx.x + 1)) / gridDim.x);
@@ -160,7 +169,10 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     auto issue = [&]() {
         if (pt >= t_hi) return;
         if (lane == 0) {
-            const uint32_t row0 = pt * RPW;
+            uint32_t local;
+            const int item = locate(pt, local);
+            const uint32_t n = grp.item[item].n;
+            const uint32_t row0 = local * RPW;
             uint32_t first, count;
             if (iters == 1) {
                 first = row0 * nblk;
@@ -170,7 +182,7 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
                 count = min(32u, nblk - pit * 32);
             }
             mbar_expect_tx(bars + pslot, count * BB);
-            bulk_g2s(ring + (size_t)pslot * STAGE_BYTES, p.w + (uint64_t)first * BB, count * BB, bars + pslot);
+            bulk_g2s(ring + (size_t)pslot * STAGE_BYTES, grp.item[item].w + (uint64_t)first * BB, count * BB, bars + pslot);
         }
         pslot ^= 1;
         if (++pit == iters) {
@@ -185,10 +197,14 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     {
-        const uint32_t chunks = p.rows * nblk * (REC / 16);
-        const uint8_t *src = (const uint8_t *)p.qa;
-        for (uint32_t c = threadIdx.x; c < chunks; c += FAST_THREADS)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(acts + 16 * c)), "l"(src + 16 * (size_t)c) : "memory");
+        const uint32_t chunks = M * nblk * (REC / 16);
+        for (int i = 0; i < grp.count; i++) {
+            if (!grp.act_copy[i]) continue;  // same activations as an earlier projection of the group
+            const uint8_t *src = (const uint8_t *)grp.item[i].qa;
+            uint8_t *dst = acts + grp.act_off[i];
+            for (uint32_t c = threadIdx.x; c < chunks; c += FAST_THREADS)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst + 16 * c)), "l"(src + 16 * (size_t)c) : "memory");
+        }
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
@@ -198,13 +214,18 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     bool healthy = true;
     uint32_t cslot = 0, cpar = 0;
     for (uint32_t t = t_lo + warp; t < t_hi; t += FAST_WARPS) {
-        const uint32_t row = t * RPW + sub;
+        uint32_t local;
+        const int item = locate(t, local);
+        const GemvArgs &p = grp.item[item];
+        const uint32_t n = p.n;
+        const uint8_t *iacts = acts + grp.act_off[item];
+        const uint32_t row = local * RPW + sub;
 #pragma unroll
         for (int r = 0; r < M; r++) acc[r] = 0.0f;
         for (uint32_t it = 0; it < iters; it++) {
             if (healthy && !mbar_wait(bars + cslot, cpar)) {
                 healthy = false;
-                if (lane == 0 && p.status) atomicOr(p.status, 1);
+                if (lane == 0 && grp.item[0].status) atomicOr(grp.item[0].status, 1);
             }
             const uint32_t b = it * G + gl;
             if (healthy && row < n && b < nblk && gl < nblk) {
@@ -229,7 +250,7 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
                         const uint32_t v[8] = {qa_.x, qa_.y, qa_.z, qa_.w, qb_.x, qb_.y, qb_.z, qb_.w};
 #pragma unroll
                         for (int r = 0; r < M; r++) {
-                            const uint4 *rec = (const uint4 *)(acts + ((size_t)r * nblk + b) * REC + 80 * pp);
+                            const uint4 *rec = (const uint4 *)(iacts + ((size_t)r * nblk + b) * REC + 80 * pp);
                             const uint4 a0 = rec[0], a1 = rec[1], a2 = rec[2], a3 = rec[3], sc = rec[4];
                             const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
                             const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
@@ -261,7 +282,7 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
                             const float s10 = (float)(int8_t)((scw[j] >> 16) & 0xff), s11 = (float)(int8_t)(scw[j] >> 24);
 #pragma unroll
                             for (int r = 0; r < M; r++) {
-                                const uint4 *rec = (const uint4 *)(acts + ((size_t)r * nblk + b) * REC + 80 * pp);
+                                const uint4 *rec = (const uint4 *)(iacts + ((size_t)r * nblk + b) * REC + 80 * pp);
                                 const uint4 a0 = rec[0], a1 = rec[1], a2 = rec[2], a3 = rec[3], sc = rec[4];
                                 const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
                                 const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
@@ -298,31 +319,42 @@ static int g_cta_cap = 0;  // 0 = as many CTAs per SM as fit; set through qgemv_
 void qgemv_q4k_fast_set_cta_cap(int cap) { g_cta_cap = cap; }
 
 template <int FMT, int M, int G>
-static cudaError_t launch_fast(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t stream) {
+static cudaError_t launch_fast(GemvGroup &g, int sm_count, bool pdl, cudaStream_t stream) {
     auto kern = qgemv_kq_fast_kernel<FMT, M, G>;
     constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
-    const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * Blk<FMT>::STAGE + (size_t)a.rows * (a.k / QK) * REC;
-    static size_t configured = 0, occ_smem = 0;
-    static int ctas_per_sm = 0;
+    constexpr int RPW = 32 / G;
+    uint32_t tasks = 0;
+    for (int i = 0; i < g.count; i++) {
+        tasks += (g.item[i].n + RPW - 1) / RPW;
+        g.task_end[i] = tasks;
+    }
+    const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * Blk<FMT>::STAGE + g.act_bytes;
+    static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         configured = smem;
     }
-    if (ctas_per_sm == 0 || occ_smem != smem) {
+    // resident CTAs per SM for this shared-memory size (a handful of sizes occur: remember them)
+    static size_t occ_key[8];
+    static int occ_val[8], occ_n = 0;
+    int ctas_per_sm = 0;
+    for (int i = 0; i < occ_n; i++)
+        if (occ_key[i] == smem) ctas_per_sm = occ_val[i];
+    if (ctas_per_sm == 0) {
         int occ = 0;
         cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, FAST_THREADS, smem);
         if (e != cudaSuccess) return e;
         ctas_per_sm = occ > 0 ? occ : 1;
-        occ_smem = smem;
+        const int slot = occ_n < 8 ? occ_n++ : 7;
+        occ_key[slot] = smem;
+        occ_val[slot] = ctas_per_sm;
     }
     // Leave one CTA slot per SM to the next kernel of the stream: under programmatic dependent
     // launch its CTAs move in while this kernel still runs and fill their rings, so the weight
     // stream does not stop at the kernel boundary.
     int per_sm = ctas_per_sm >= 4 ? ctas_per_sm - 1 : ctas_per_sm;
     if (g_cta_cap > 0) per_sm = g_cta_cap < ctas_per_sm ? g_cta_cap : ctas_per_sm;
-    constexpr int RPW = 32 / G;
-    const uint32_t tasks = (a.n + RPW - 1) / RPW;
     // every SM gets the same number of CTAs and every CTA the same share of the tasks
     uint32_t grid = (uint32_t)sm_count * (uint32_t)per_sm;
     const uint32_t useful = (tasks + FAST_WARPS - 1) / FAST_WARPS;
@@ -337,11 +369,11 @@ static cudaError_t launch_fast(const GemvArgs &a, int sm_count, bool pdl, cudaSt
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, a);
+    return cudaLaunchKernelEx(&cfg, kern, g);
 }
 
-template <int FMT, int M> static cudaError_t launch_fast_g(const GemvArgs &a, int sm, bool pdl, cudaStream_t s) {
-    const uint32_t nblk = a.k / QK;
+template <int FMT, int M> static cudaError_t launch_fast_g(GemvGroup &a, int sm, bool pdl, cudaStream_t s) {
+    const uint32_t nblk = a.item[0].k / QK;
     if (nblk <= 8) return launch_fast<FMT, M, 8>(a, sm, pdl, s);
     if (nblk <= 16) return launch_fast<FMT, M, 16>(a, sm, pdl, s);
     return launch_fast<FMT, M, 32>(a, sm, pdl, s);
@@ -365,8 +397,8 @@ bool qgemv_kq_fast_supported(int fmt, const GemvArgs &a) {
 
 bool qgemv_q4k_fast_supported(const GemvArgs &a) { return qgemv_kq_fast_supported(FMT_Q4K, a); }
 
-template <int FMT> static cudaError_t launch_fmt(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
-    switch (a.rows) {
+template <int FMT> static cudaError_t launch_fmt(GemvGroup &a, int sm_count, bool pdl, cudaStream_t s) {
+    switch (a.item[0].rows) {
         case 1: return launch_fast_g<FMT, 1>(a, sm_count, pdl, s);
         case 2: return launch_fast_g<FMT, 2>(a, sm_count, pdl, s);
         case 3: return launch_fast_g<FMT, 3>(a, sm_count, pdl, s);
@@ -379,12 +411,47 @@ template <int FMT> static cudaError_t launch_fmt(const GemvArgs &a, int sm_count
     }
 }
 
+// Shared memory the activation records of a group need; distinct sources only.
+static void plan_group_acts(GemvGroup &g) {
+    const uint32_t bytes = g.item[0].rows * (g.item[0].k / QK) * REC;
+    g.act_bytes = 0;
+    for (int i = 0; i < g.count; i++) {
+        g.act_copy[i] = 1;
+        for (int j = 0; j < i; j++)
+            if (g.item[j].qa == g.item[i].qa) {
+                g.act_off[i] = g.act_off[j];
+                g.act_copy[i] = 0;
+                break;
+            }
+        if (g.act_copy[i]) {
+            g.act_off[i] = g.act_bytes;
+            g.act_bytes += bytes;
+        }
+    }
+}
+
+size_t qgemv_kq_group_smem(int fmt, GemvGroup &g) {
+    plan_group_acts(g);
+    const size_t warps = g.item[0].rows <= 2 ? 4 : 8;
+    const size_t stage = 32 * (size_t)(fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+    return BAR_BYTES + warps * 2 * stage + g.act_bytes;
+}
+
+cudaError_t launch_qgemv_kq_group(int fmt, GemvGroup &g, int sm_count, bool pdl, cudaStream_t s) {
+    if (g.count < 1 || g.count > GEMV_GROUP_MAX) return cudaErrorInvalidValue;
+    plan_group_acts(g);
+    return fmt == FMT_Q6K ? launch_fmt<FMT_Q6K>(g, sm_count, pdl, s) : launch_fmt<FMT_Q4K>(g, sm_count, pdl, s);
+}
+
 cudaError_t launch_qgemv_kq_fast(int fmt, const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
-    return fmt == FMT_Q6K ? launch_fmt<FMT_Q6K>(a, sm_count, pdl, s) : launch_fmt<FMT_Q4K>(a, sm_count, pdl, s);
+    GemvGroup g{};
+    g.count = 1;
+    g.item[0] = a;
+    return launch_qgemv_kq_group(fmt, g, sm_count, pdl, s);
 }
 
 cudaError_t launch_qgemv_q4k_fast(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
-    return launch_fmt<FMT_Q4K>(a, sm_count, pdl, s);
+    return launch_qgemv_kq_fast(FMT_Q4K, a, sm_count, pdl, s);
 }
 
 }  // namespace lb

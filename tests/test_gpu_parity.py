@@ -192,6 +192,32 @@ def test_gemv_reference_test_shapes(be, oracle, fmt, name):
         assert rel_l2(got, f64) <= 2e-2  # the reference's own bound for its int8-activation path
 
 
+@pytest.mark.parametrize("config", [-1, 0, 1, 2])
+def test_gemv_q4k_tensor_core_decode_kernel(be, oracle, config):
+    """The int8 tensor-core decode kernel (default for 4..8 rows) against the oracle and against the
+    dp4a kernel, for every tile configuration, ragged n, odd super-block counts and a bias."""
+    be.set_option("gemv_mma_config", str(config))
+    try:
+        seed = 900
+        for (m, n, k, bias) in [(4, 77, 256, False), (5, 100, 768, True), (8, 513, 4096, False), (7, 33, 14336, True),
+                                (8, 16, 512, False), (6, 1, 1280, False), (3, 40, 2048, False)]:
+            seed += 1
+            w = O.normal(seed, n * k, 0.05)
+            qb = oracle.quantize(O.Q4_K, w, n, k)
+            a = O.normal(seed + 50, m * k)
+            bv = O.normal(seed + 70, n) if bias else None
+            want, _ = oracle.matmul(O.Q4_K, a, qb, n, k, m=m, bias=bv)
+            be.set_option("gemv_mma_rows", "3")
+            got = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, bias=bv)
+            be.set_option("gemv_mma_rows", "0")
+            ref = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, bias=bv)
+            assert max_rel(got, want) <= 2e-5, (m, n, k)
+            assert max_rel(got, ref) <= 2e-5, (m, n, k)
+    finally:
+        be.set_option("gemv_mma_rows", "4")
+        be.set_option("gemv_mma_config", "-1")
+
+
 def test_gemv_int8_k_not_multiple_of_256(be, oracle):
     for (m, n, k) in [(2, 40, 96), (1, 7, 32), (4, 33, 2080)]:
         w = O.normal(3, n * k, 0.1)
@@ -418,6 +444,7 @@ def test_activation_sharing_and_hoisting(be, oracle):
           matmul_launch(lp.DType.Q4K, 1, k, k, inputs=(5, 4), output=0),   # overwrites x with W4 . out_q
           matmul_launch(lp.DType.Q4K, 1, k, k, inputs=(0, 1), output=8)]   # must see the new x
     be.prepare(ls)
+    be.set_option("gemv_group", "0")
     for opt in ("1", "0"):
         be.set_option("act_reuse", opt)
         bufs[0].write(0, x)
@@ -437,3 +464,54 @@ def test_activation_sharing_and_hoisting(be, oracle):
         # 5 GEMVs; pre-passes: one shared by q/k/v (hoisted), one for out_q, one for the rewritten x
         assert launched == (8 if opt == "1" else 10)
     be.set_option("act_reuse", "1")
+    be.set_option("gemv_group", "1")
+
+
+@pytest.mark.parametrize("fmt,ofmt", [(lp.DType.Q4K, O.Q4_K), (lp.DType.Q6K, O.Q6_K)])
+@pytest.mark.parametrize("m", [1, 3, 8])
+def test_grouped_decode_launches(be, oracle, fmt, ofmt, m):
+    """Consecutive independent decode launches with the same format, rows and k go out as one
+    kernel; the results are those of the launches run one by one, bit for bit, and a launch that
+    reads or overwrites what a pending one writes is never merged with it."""
+    k = 2048
+    ns = [512, 136, 77, 1024, 256]
+    ws = [oracle.quantize(ofmt, O.normal(50 + i, n * k, 0.05), n, k) for i, n in enumerate(ns)]
+    wd = oracle.quantize(ofmt, O.normal(60, k * k, 0.05), k, k)   # consumes a [m, k] output
+    x = O.normal(70, m * k)
+    y = O.normal(71, m * k)
+    bias = O.normal(72, ns[1])
+    # 0 x, 1 y, 2..6 weights, 7 wd, 8 bias, 9 packed outputs, 10 out of the dependent launch, 11 [m,k] scratch
+    total = sum(m * n for n in ns)
+    bufs = [be.upload(x), be.upload(y)] + [be.upload(w) for w in ws] + [be.upload(wd), be.upload(bias),
+            be.alloc(total * 4), be.alloc(m * k * 4), be.alloc(m * k * 4)]
+    offs = np.cumsum([0] + [m * n for n in ns])
+    ls = []
+    for i, n in enumerate(ns):
+        ls.append(matmul_launch(fmt, m, n, k, inputs=(0 if i != 3 else 1, 2 + i), output=9, out=MatView(int(offs[i]), m * n, n),
+                                bias_input=8 if i == 1 else None))
+    ls.append(matmul_launch(fmt, m, k, k, inputs=(0, 7), output=11))    # independent: same group or next
+    ls.append(matmul_launch(fmt, m, k, k, inputs=(11, 7), output=10))   # reads the launch before it: new group
+    ls.append(matmul_launch(fmt, m, k, k, inputs=(10, 7), output=11))   # overwrites its own producer's input
+    be.prepare(ls)
+    res = {}
+    for opt in ("0", "1"):
+        be.set_option("gemv_group", opt)
+        for b in (9, 10, 11):
+            bufs[b].write(0, np.zeros(bufs[b].nbytes // 4, np.float32))
+        be.take_launch_count()
+        be.execute(ls, bufs)
+        res[opt] = (be.take_launch_count(), [bufs[b].download().view(np.float32).copy() for b in (9, 10, 11)])
+    be.set_option("gemv_group", "1")
+    for a, b in zip(res["0"][1], res["1"][1]):
+        assert np.array_equal(a, b)
+    assert res["1"][0] < res["0"][0]
+    # and against the oracle
+    got = res["1"][1][0]
+    for i, n in enumerate(ns):
+        want, _ = oracle.matmul(ofmt, x if i != 3 else y, ws[i], n, k, m=m, bias=bias if i == 1 else None)
+        assert max_rel(got[offs[i]:offs[i + 1]], want) <= 2e-5
+    h1, _ = oracle.matmul(ofmt, x, wd, k, k, m=m)
+    h2, _ = oracle.matmul(ofmt, h1, wd, k, k, m=m)
+    h3, _ = oracle.matmul(ofmt, res["1"][1][1], wd, k, k, m=m)
+    assert max_rel(res["1"][1][1], h2) <= 1e-3   # second hop: int8 rounding of a slightly different input
+    assert max_rel(res["1"][1][2], h3) <= 2e-5
