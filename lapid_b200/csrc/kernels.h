@@ -80,7 +80,7 @@ struct GemvGroup {
 };
 size_t qgemv_kq_group_smem(int fmt, GemvGroup &group);  // dynamic shared memory the group would need
 cudaError_t launch_qgemv_kq_group(int fmt, GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream);
-// Q4_K decode on the warp-level int8 tensor-core instruction (4..8 rows pay off); activations as
+// Q4_K decode on the warp-level int8 tensor-core instruction (3..8 rows pay off); activations as
 // tiles (ActQuantArgs::records == 2).
 bool qgemv_q4k_mma_shape_ok(uint32_t rows, uint32_t k);
 size_t qgemv_q4k_mma_act_bytes(uint32_t rows, uint32_t k);

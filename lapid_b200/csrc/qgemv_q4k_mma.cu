@@ -1,8 +1,8 @@
-// Q4_K decode GEMV for 4..8 activation rows on the warp-level int8 tensor-core instruction
+// Q4_K decode GEMV for 3..8 activation rows on the warp-level int8 tensor-core instruction
 // (arithmetic: see qgemv.cu; the integer dot products are the same, only the order of the f32
 // sums over sub-blocks and k-chunks differs).
 //
-// With four or more activation rows the dp4a kernel is bound by instruction issue, not by
+// With three or more activation rows the dp4a kernel is bound by instruction issue, not by
 // memory: every weight byte is multiplied M times by scalar-per-lane instructions. Here one
 // `mma.sync.m16n8k32.u8.s8` covers 16 weight rows x 32 k x 8 activation rows, so the integer
 // work per weight byte no longer grows with M; what is left is the f32 scaling of each
@@ -72,14 +72,37 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 
 // 16 weight rows (unsigned bytes) x 32 k x 8 activation rows (signed bytes). The accumulators
 // start at the bit pattern of 1.5 * 2^23: the integer dot product (|dot| < 2^22) lands in the
-// mantissa, so the result reinterpreted as f32 is 12582912 + dot and one exact subtraction
+// mantissa, so the result reinterpreted as f32 is 12582912 + dot and one exact addition
 // replaces the int -> float conversion.
 constexpr float MAGIC = 12582912.0f;
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0x4B400000));
+}
+
+// Two f32 lanes in one 64-bit register pair (Blackwell's packed f32 instructions).
+__device__ __forceinline__ uint64_t pack2i(int lo, int hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
 }
 
 __device__ __forceinline__ float scale_byte(uint32_t w, uint32_t sel, float d, float neg_d23) {
@@ -167,6 +190,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) qgemv_q4k_mma_kernel(const __gr
 
     const uint32_t colq = (uint32_t)gq < M ? gq : 0;        // activation row of this lane's B fragment
     const uint32_t cp = (uint32_t)(2 * t4) < M ? t4 : 0;    // activation row pair of this lane's C fragment
+    const uint64_t neg_magic = pack2(-MAGIC, -MAGIC);
     bool healthy = true;
     uint32_t cslot = 0, cpar = 0, par = 0;
     for (uint32_t t = t_lo; t < t_hi; t++, par ^= 1) {
@@ -225,13 +249,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) qgemv_q4k_mma_kernel(const __gr
                         if (b >= nb) break;
                         const uint8_t *ab = iacts + (size_t)(2 * it + b) * ABLK;
                         const float4 *dsp = (const float4 *)(ab + 256 * M + cp * 64);
-                        float4 dav[4], bsv[4];
+                        ulonglong2 dav[4];  // {da[c0], da[c1]} of sub-blocks 2i, 2i + 1
+                        float4 bsv[4];
 #pragma unroll
                         for (int i = 0; i < 4; i++) {
-                            dav[i] = dsp[i];
+                            dav[i] = ((const ulonglong2 *)dsp)[i];
                             bsv[i] = dsp[16 + i];
                         }
-                        const float *da = (const float *)dav, *bs = (const float *)bsv;  // [sub-block][2]
+                        const float *bs = (const float *)bsv;  // [sub-block][2]
                         float4 wv[TILES][2][4];  // [tile][row half][W1 0..3, W1 4..7, W2 0..3, W2 4..7]
 #pragma unroll
                         for (int tl = 0; tl < TILES; tl++)
@@ -254,14 +279,21 @@ __global__ void __launch_bounds__(WARPS * 32, 1) qgemv_q4k_mma_kernel(const __gr
                                 int cl[4], ch[4];
                                 mma_u8s8(cl, wa.x & 0x0F0F0F0Fu, wb.x & 0x0F0F0F0Fu, wa.y & 0x0F0F0F0Fu, wb.y & 0x0F0F0F0Fu, blo.x, blo.y);
                                 mma_u8s8(ch, wa.x & 0xF0F0F0F0u, wb.x & 0xF0F0F0F0u, wa.y & 0xF0F0F0F0u, wb.y & 0xF0F0F0F0u, bhi.x, bhi.y);
+                                // int -> f32 and the activation scale on packed f32x2: the two outputs
+                                // of a row are one register pair, and so are their activation scales
+                                float gl[4], gh[4];
+                                unpack2(mul2(add2(pack2i(cl[0], cl[1]), neg_magic), dav[j].x), gl[0], gl[1]);
+                                unpack2(mul2(add2(pack2i(cl[2], cl[3]), neg_magic), dav[j].x), gl[2], gl[3]);
+                                unpack2(mul2(add2(pack2i(ch[0], ch[1]), neg_magic), dav[j].y), gh[0], gh[1]);
+                                unpack2(mul2(add2(pack2i(ch[2], ch[3]), neg_magic), dav[j].y), gh[2], gh[3]);
 #pragma unroll
                                 for (int i = 0; i < 4; i++) {
                                     const float *w = (const float *)wv[tl][i >> 1];
                                     const int c = i & 1;
                                     float a = acc[tl][i];
-                                    a = fmaf((__int_as_float(cl[i]) - MAGIC) * da[(2 * j) * 2 + c], w[2 * j], a);
+                                    a = fmaf(gl[i], w[2 * j], a);
                                     a = fmaf(w[8 + 2 * j], bs[(2 * j) * 2 + c], a);
-                                    a = fmaf((__int_as_float(ch[i]) - MAGIC) * da[(2 * j + 1) * 2 + c], w[2 * j + 1], a);
+                                    a = fmaf(gh[i], w[2 * j + 1], a);
                                     a = fmaf(w[8 + 2 * j + 1], bs[(2 * j + 1) * 2 + c], a);
                                     acc[tl][i] = a;
                                 }
@@ -333,6 +365,9 @@ static void plan_acts(GemvGroup &g) {
 
 static int pick_config(size_t act_bytes) {
     if (g_force_config >= 0) return fixed_smem(CONFIGS[g_force_config]) + act_bytes <= 227 * 1024 ? g_force_config : -1;
+    // small activation tiles: three of the small CTAs per SM beat one large one (more tiles in
+    // flight, shorter barriers); otherwise the largest layout that fits
+    if (3 * (fixed_smem(CONFIGS[2]) + act_bytes + 1024) <= 227 * 1024) return 2;
     for (int i = 0; i < (int)(sizeof(CONFIGS) / sizeof(CONFIGS[0])); i++)
         if (fixed_smem(CONFIGS[i]) + act_bytes <= 227 * 1024) return i;
     return -1;

@@ -194,7 +194,7 @@ def test_gemv_reference_test_shapes(be, oracle, fmt, name):
 
 @pytest.mark.parametrize("config", [-1, 0, 1, 2])
 def test_gemv_q4k_tensor_core_decode_kernel(be, oracle, config):
-    """The int8 tensor-core decode kernel (default for 4..8 rows) against the oracle and against the
+    """The int8 tensor-core decode kernel (default for 3..8 rows) against the oracle and against the
     dp4a kernel, for every tile configuration, ragged n, odd super-block counts and a bias."""
     be.set_option("gemv_mma_config", str(config))
     try:
@@ -214,7 +214,7 @@ def test_gemv_q4k_tensor_core_decode_kernel(be, oracle, config):
             assert max_rel(got, want) <= 2e-5, (m, n, k)
             assert max_rel(got, ref) <= 2e-5, (m, n, k)
     finally:
-        be.set_option("gemv_mma_rows", "4")
+        be.set_option("gemv_mma_rows", "3")
         be.set_option("gemv_mma_config", "-1")
 
 
