@@ -151,7 +151,7 @@ struct lapid_b200_device {
     bool act_reuse = true;  // share / hoist activation pre-passes inside one launch list
     bool gemv_fast = true;   // specialised GEMV kernels where the shape allows; off = generic kernel only
     bool gemv_group = true;  // consecutive independent K-quant decode launches of one list share a kernel
-    uint32_t gemv_mma_rows = 3;  // Q4_K decode launches with at least this many rows use the int8 tensor-core kernel; 0 = never
+    uint32_t gemv_mma_rows = 2;  // Q4_K decode launches with at least this many rows use the int8 tensor-core kernel; 0 = never
     bool gemm_f32 = false;  // true: rows > gemv_max_rows always take the exact-f32 GEMM instead of the tensor cores
 
     void make_current() const { cuda_check(cudaSetDevice(ordinal), "cudaSetDevice"); }

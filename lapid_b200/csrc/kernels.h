@@ -70,17 +70,19 @@ bool qgemv_q4k_fast_supported(const GemvArgs &args);
 cudaError_t launch_qgemv_q4k_fast(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // Up to GEMV_GROUP_MAX independent projections with the same format, rows and k in one launch.
 constexpr int GEMV_GROUP_MAX = 6;
-struct GemvGroup {
-    GemvArgs item[GEMV_GROUP_MAX];
-    uint32_t task_end[GEMV_GROUP_MAX];  // filled by the launcher
-    uint32_t act_off[GEMV_GROUP_MAX];   // shared-memory offset of each item's activation records
-    uint8_t act_copy[GEMV_GROUP_MAX];   // 0 when an earlier item of the group has the same activations
+template <int N> struct GemvGroupT {
+    GemvArgs item[N];
+    uint32_t task_end[N];  // filled by the launcher
+    uint32_t act_off[N];   // shared-memory offset of each item's activation records
+    uint8_t act_copy[N];   // 0 when an earlier item of the group has the same activations
     int count;
     uint32_t act_bytes;
 };
+using GemvGroup = GemvGroupT<GEMV_GROUP_MAX>;
+using GemvSingle = GemvGroupT<1>;  // what a lone launch passes to the kernel: a sixth of the parameter bytes
 size_t qgemv_kq_group_smem(int fmt, GemvGroup &group);  // dynamic shared memory the group would need
 cudaError_t launch_qgemv_kq_group(int fmt, GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream);
-// Q4_K decode on the warp-level int8 tensor-core instruction (3..8 rows pay off); activations as
+// Q4_K decode on the warp-level int8 tensor-core instruction (2..8 rows pay off); activations as
 // tiles (ActQuantArgs::records == 2).
 bool qgemv_q4k_mma_shape_ok(uint32_t rows, uint32_t k);
 size_t qgemv_q4k_mma_act_bytes(uint32_t rows, uint32_t k);

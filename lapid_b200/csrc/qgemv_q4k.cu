@@ -126,8 +126,8 @@ __device__ __forceinline__ float q6_group(const uint32_t (&q)[8], const uint32_t
 // shared memory and are better amortised over more warps.
 template <int M> struct Shape { static constexpr int WARPS = M <= 2 ? 4 : 8, MIN_CTAS = M <= 2 ? 5 : 2; };
 
-template <int FMT, int M, int G>
-__global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_kq_fast_kernel(GemvGroup grp) {
+template <int FMT, int M, int G, int NG>
+__global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_kq_fast_kernel(GemvGroupT<NG> grp) {
     constexpr int STAGES = 2;
     constexpr int BB = Blk<FMT>::BYTES, STAGE_BYTES = Blk<FMT>::STAGE;
     constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
@@ -142,6 +142,10 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     const uint32_t iters = (nblk + G - 1) / G;
     const uint32_t tasks = grp.task_end[grp.count - 1];
     auto locate = [&](uint32_t t, uint32_t &local) -> int {
+        if constexpr (NG == 1) {
+            local = t;
+            return 0;
+        }
         int i = 0;
         while (t >= grp.task_end[i]) i++;
         local = t - (i ? grp.task_end[i - 1] : 0);
@@ -318,9 +322,9 @@ static int g_cta_cap = 0;  // 0 = as many CTAs per SM as fit; set through qgemv_
 
 void qgemv_q4k_fast_set_cta_cap(int cap) { g_cta_cap = cap; }
 
-template <int FMT, int M, int G>
-static cudaError_t launch_fast(GemvGroup &g, int sm_count, bool pdl, cudaStream_t stream) {
-    auto kern = qgemv_kq_fast_kernel<FMT, M, G>;
+template <int FMT, int M, int G, int NG>
+static cudaError_t launch_fast_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cudaStream_t stream) {
+    auto kern = qgemv_kq_fast_kernel<FMT, M, G, NG>;
     constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
     constexpr int RPW = 32 / G;
     uint32_t tasks = 0;
@@ -370,6 +374,18 @@ static cudaError_t launch_fast(GemvGroup &g, int sm_count, bool pdl, cudaStream_
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, g);
+}
+
+template <int FMT, int M, int G>
+static cudaError_t launch_fast(GemvGroup &g, int sm_count, bool pdl, cudaStream_t stream) {
+    if (g.count > 1) return launch_fast_n<FMT, M, G, GEMV_GROUP_MAX>(g, sm_count, pdl, stream);
+    GemvSingle one;
+    one.item[0] = g.item[0];
+    one.act_off[0] = g.act_off[0];
+    one.act_copy[0] = g.act_copy[0];
+    one.count = 1;
+    one.act_bytes = g.act_bytes;
+    return launch_fast_n<FMT, M, G, 1>(one, sm_count, pdl, stream);
 }
 
 template <int FMT, int M> static cudaError_t launch_fast_g(GemvGroup &a, int sm, bool pdl, cudaStream_t s) {

@@ -1,8 +1,8 @@
-// Q4_K decode GEMV for 3..8 activation rows on the warp-level int8 tensor-core instruction
+// Q4_K decode GEMV for 2..8 activation rows on the warp-level int8 tensor-core instruction
 // (arithmetic: see qgemv.cu; the integer dot products are the same, only the order of the f32
 // sums over sub-blocks and k-chunks differs).
 //
-// With three or more activation rows the dp4a kernel is bound by instruction issue, not by
+// With several activation rows the dp4a kernel is bound by instruction issue, not by
 // memory: every weight byte is multiplied M times by scalar-per-lane instructions. Here one
 // `mma.sync.m16n8k32.u8.s8` covers 16 weight rows x 32 k x 8 activation rows, so the integer
 // work per weight byte no longer grows with M; what is left is the f32 scaling of each
@@ -111,12 +111,13 @@ __device__ __forceinline__ float scale_byte(uint32_t w, uint32_t sel, float d, f
 
 __host__ __device__ constexpr uint32_t act_block_bytes(uint32_t rows) { return 256 * rows + 512; }
 
-struct WeightMaps {
-    CUtensorMap m[GEMV_GROUP_MAX];  // packed weights of each member: [n rows][k/256 * 36 words], box 72 words x 16*TILES rows
+template <int NG> struct WeightMapsT {
+    CUtensorMap m[NG];  // packed weights of each member: [n rows][k/256 * 36 words], box 72 words x 16*TILES rows
 };
 
-template <int WARPS, int TILES>
-__global__ void __launch_bounds__(WARPS * 32, 1) qgemv_q4k_mma_kernel(const __grid_constant__ WeightMaps maps, GemvGroup grp) {
+template <int WARPS, int TILES, int NG>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG> grp) {
     constexpr int THREADS = WARPS * 32;
     constexpr int RPT = 16 * TILES;           // weight rows per tile
     constexpr int STAGE = RPT * ROWB;         // bytes per ring stage
@@ -130,6 +131,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) qgemv_q4k_mma_kernel(const __gr
     const uint32_t ABLK = act_block_bytes(M);
     const uint32_t tasks = grp.task_end[grp.count - 1];
     auto locate = [&](uint32_t t, uint32_t &local) -> int {
+        if constexpr (NG == 1) {
+            local = t;
+            return 0;
+        }
         int i = 0;
         while (t >= grp.task_end[i]) i++;
         local = t - (i ? grp.task_end[i - 1] : 0);
@@ -425,17 +430,17 @@ static bool weight_map(const GemvArgs &a, uint32_t box_rows, CUtensorMap &out) {
     return true;
 }
 
-template <int WARPS, int TILES>
-static cudaError_t launch_cfg(GemvGroup &g, int sm_count, bool pdl, cudaStream_t stream) {
-    auto kern = qgemv_q4k_mma_kernel<WARPS, TILES>;
+template <int WARPS, int TILES, int NG>
+static cudaError_t launch_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cudaStream_t stream) {
+    auto kern = qgemv_q4k_mma_kernel<WARPS, TILES, NG>;
     uint32_t tasks = 0;
-    WeightMaps maps;
+    WeightMapsT<NG> maps;
     for (int i = 0; i < g.count; i++) {
         tasks += (g.item[i].n + 16 * TILES - 1) / (16 * TILES);
         g.task_end[i] = tasks;
         if (!weight_map(g.item[i], 16 * TILES, maps.m[i])) return cudaErrorNotSupported;
     }
-    for (int i = g.count; i < GEMV_GROUP_MAX; i++) maps.m[i] = maps.m[0];
+    for (int i = g.count; i < NG; i++) maps.m[i] = maps.m[0];
     const size_t smem = fixed_smem(Config{WARPS, TILES}) + g.act_bytes;
     static size_t configured = 0;
     if (smem > configured) {
@@ -457,6 +462,18 @@ static cudaError_t launch_cfg(GemvGroup &g, int sm_count, bool pdl, cudaStream_t
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, maps, g);
+}
+
+template <int WARPS, int TILES>
+static cudaError_t launch_cfg(GemvGroup &g, int sm_count, bool pdl, cudaStream_t stream) {
+    if (g.count > 1) return launch_n<WARPS, TILES, GEMV_GROUP_MAX>(g, sm_count, pdl, stream);
+    GemvSingle one;  // a lone launch passes a sixth of the parameter bytes
+    one.item[0] = g.item[0];
+    one.act_off[0] = g.act_off[0];
+    one.act_copy[0] = g.act_copy[0];
+    one.count = 1;
+    one.act_bytes = g.act_bytes;
+    return launch_n<WARPS, TILES, 1>(one, sm_count, pdl, stream);
 }
 
 }  // namespace mm

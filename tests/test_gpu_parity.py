@@ -207,14 +207,14 @@ def test_gemv_q4k_tensor_core_decode_kernel(be, oracle, config):
             a = O.normal(seed + 50, m * k)
             bv = O.normal(seed + 70, n) if bias else None
             want, _ = oracle.matmul(O.Q4_K, a, qb, n, k, m=m, bias=bv)
-            be.set_option("gemv_mma_rows", "3")
+            be.set_option("gemv_mma_rows", "2")
             got = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, bias=bv)
             be.set_option("gemv_mma_rows", "0")
             ref = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, bias=bv)
             assert max_rel(got, want) <= 2e-5, (m, n, k)
             assert max_rel(got, ref) <= 2e-5, (m, n, k)
     finally:
-        be.set_option("gemv_mma_rows", "3")
+        be.set_option("gemv_mma_rows", "2")
         be.set_option("gemv_mma_config", "-1")
 
 
