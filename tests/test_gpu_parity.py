@@ -199,7 +199,7 @@ def test_gemv_q4k_tensor_core_decode_kernel(be, oracle, config):
     be.set_option("gemv_mma_config", str(config))
     try:
         seed = 900
-        for (m, n, k, bias) in [(4, 77, 256, False), (5, 100, 768, True), (8, 513, 4096, False), (7, 33, 14336, True),
+        for (m, n, k, bias) in [(2, 130, 1024, False), (4, 77, 256, False), (5, 100, 768, True), (8, 513, 4096, False), (7, 33, 14336, True),
                                 (8, 16, 512, False), (6, 1, 1280, False), (3, 40, 2048, False)]:
             seed += 1
             w = O.normal(seed, n * k, 0.05)
