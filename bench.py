@@ -318,6 +318,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     prefill_rows = None
     if world == 1 and not args.no_prefill:
         prefill_rows = measure_prefill(be, stream, dev, base)
+    stack_obj = None
+    if world == 1 and not args.no_stack:
+        try:
+            stack_obj = measure_stack8b(be, stream, dev, quantized, peak)
+        except Exception as e:  # reported, never fatal for the headline line
+            stack_obj = {"error": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.empty_cache()
 
     # ---- per-case timing over cold copies (rank 0, N = 1 only): the kbench method scaled to B200's L2
     case_rows = []
@@ -407,6 +414,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         line["cases"] = case_rows
     if prefill_rows:
         line["prefill"] = prefill_rows
+    if stack_obj:
+        line["stack8b"] = stack_obj
     if tp_obj:
         line["tp70b"] = tp_obj
     if world == 1 and not args.no_cpu:
@@ -473,6 +482,79 @@ def measure_prefill(be, stream, dev, base):
                          "operands": "bf16 (f32 accumulate in TMEM)"})
         del pool
     return rows
+
+
+def measure_stack8b(be, stream, dev, quantized, peak):
+    """Every quantized projection of one decode token through a 32-layer Llama-3-8B-shaped stack plus
+    the output head, as ONE launch list through the C ABI (225 MatMul launches, batch 1 and 8).
+
+    Q4_K_M-style mix: Q6_K for attn_v, for ffn_down in the `use_more_bits` layers and for the head,
+    Q4_K elsewhere. The projections are chained by real data (x -> q,k,v; q_out -> o; o_out -> gate,
+    up; gate_out -> down -> next layer's x), so every launch but the first waits for its producer;
+    attention mixing, normalisation and the SwiGLU product are not part of this path. All 4.6 GB of
+    weights are distinct and resident; a token streams each of them once.
+    """
+    import torch
+    from lapid_b200 import tp
+    from lapid_b200.backend import matmul_launch
+    shape, n_layers, vocab = tp.LLAMA3_8B, 32, 128256
+    d = shape.d_model
+    weights, formats, token_bytes = [], [], 0
+    for i in range(n_layers):
+        f = {name: tp.q4km_format(name, i, n_layers) for name, _, _, _ in shape.projections()}
+        w = {name: quantized(f[name], n, k, 4000 + 8 * i + j) for j, (name, n, k, _) in enumerate(shape.projections())}
+        token_bytes += sum(t.numel() for t in w.values())
+        weights.append(w)
+        formats.append(f)
+    head = quantized(8, vocab, d, 4999)
+    token_bytes += head.numel()
+    out = {"layers": n_layers, "head_rows": vocab, "weight_bytes_per_token": token_bytes,
+           "launches_per_token": 7 * n_layers + 1,
+           "ceiling_tok_s_b1": round(peak * 1e9 / token_bytes, 1)}
+    for m in (1, 8):
+        bufs, launches, keep = [], [], []
+
+        def buf(t):
+            keep.append(t)
+            bufs.append(be.wrap_tensor(t))
+            return len(bufs) - 1
+
+        g = torch.Generator(device=dev)
+        g.manual_seed(5000 + m)
+        x = buf(torch.randn(m * d, device=dev, generator=g))
+        dims = {name: (n, k) for name, n, k, _ in shape.projections()}
+        for i in range(n_layers):
+            wid = {name: buf(weights[i][name]) for name in dims}
+            oid = {name: buf(torch.zeros(m * dims[name][0], device=dev)) for name in dims}
+            src = {"q": x, "k": x, "v": x, "o": oid["q"], "gate": oid["o"], "up": oid["o"], "down": oid["gate"]}
+            for name in ("q", "k", "v", "o", "gate", "up", "down"):
+                n, k = dims[name]
+                launches.append(matmul_launch(formats[i][name], m, n, k, inputs=(src[name], wid[name]), output=oid[name]))
+            x = oid["down"]
+        logits = buf(torch.zeros(m * vocab, device=dev))
+        launches.append(matmul_launch(8, m, vocab, d, inputs=(x, buf(head)), output=logits))
+        torch.cuda.synchronize()
+        be.prepare(launches)
+        run = be.packed(launches, bufs)
+        be.take_launch_count()
+        with torch.cuda.stream(stream):
+            run()
+        stream.synchronize()
+        kernels = be.take_launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            be.set_stream(torch.cuda.current_stream().cuda_stream)
+            run()
+        be.set_stream(stream.cuda_stream)
+        ms = _event_time(stream, graph.replay, 7, warm=3)
+        finite = bool(torch.isfinite(keep[-2]).all().item())
+        out[f"decode_b{m}"] = {"ms_per_token_step": round(ms, 4), "tok_s": round(m / (ms * 1e-3), 1),
+                               "hbm_gbs": round(token_bytes / (ms * 1e-3) / 1e9, 1),
+                               "frac_of_measured_hbm": round(token_bytes / (ms * 1e-3) / 1e9 / peak, 4),
+                               "kernels_per_token": kernels, "logits_finite": finite}
+        del graph, run, bufs, keep, launches
+        torch.cuda.empty_cache()
+    return out
 
 
 def measure_tp70b(be, stream, dev, rank, world, quantized):
@@ -587,6 +669,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM rows")
     ap.add_argument("--no-tp", action="store_true", help="skip the 70B-shaped tensor-parallel layer stack")
+    ap.add_argument("--no-stack", action="store_true", help="skip the 32-layer 8B-shaped projection stack")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
