@@ -210,6 +210,23 @@ LAPID_B200_API void lapid_b200_tp_comm_free(lapid_b200_tp_comm *comm);
 LAPID_B200_API lapid_b200_status lapid_b200_tp_all_reduce(lapid_b200_tp_comm *comm, lapid_b200_buffer *data,
                                                           uint64_t offset, uint64_t count);
 
+/* ---- the steps between the projections of a layer ------------------------------------------- */
+/* Not part of the quantized-matmul path: two small kernels so that a layer-stack measurement is not
+ * dominated by a framework's elementwise launches. Queued on the device's stream, not waited for.
+ *
+ * lapid_b200_rms_norm: lapid's Kernel::RmsNorm (crates/lapid-compiler/src/ir.rs:407-409, CPU
+ *   crates/lapid-cpu/src/rows.rs:118-156) with the residual add that precedes it folded in:
+ *     h = x (+ residual);  out = h * rsqrt(mean(h*h) + eps) (* weight);  sum_out = h   (if given)
+ *   x, residual, sum_out, out: [rows, cols] f32 contiguous; weight: [cols] f32. residual, weight and
+ *   sum_out may be NULL. cols: multiple of 4, at most 16384. sum_out may be x or residual (in place).
+ * lapid_b200_silu_mul: out = gate / (1 + exp(-gate)) * up over `count` f32 (multiple of 4), the SwiGLU
+ *   product (crates/lapid-nn/src/mlp.rs:84), an Elementwise kernel in lapid. out may be gate or up. */
+LAPID_B200_API lapid_b200_status lapid_b200_rms_norm(lapid_b200_device *dev, lapid_b200_buffer *x, lapid_b200_buffer *residual,
+                                                     lapid_b200_buffer *weight, lapid_b200_buffer *sum_out,
+                                                     lapid_b200_buffer *out, uint64_t rows, uint64_t cols, float eps);
+LAPID_B200_API lapid_b200_status lapid_b200_silu_mul(lapid_b200_device *dev, lapid_b200_buffer *gate, lapid_b200_buffer *up,
+                                                     lapid_b200_buffer *out, uint64_t count);
+
 /* ---- decode without allocation ------------------------------------------------------------ */
 /* This entry point has no counterpart in the reference. It exists for hosts that may not allocate
  * device memory when they need a matvec (an engine that gave all device memory to its own arena at

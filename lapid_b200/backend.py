@@ -260,6 +260,16 @@ class Backend:
         run.keep = (arr, bufs, list(buffers))
         return run
 
+    # ---- the steps between projections (queued on the device's stream, not waited for)
+    def rms_norm(self, x: Buffer, out: Buffer, rows: int, cols: int, eps: float = 1e-6, residual: Optional[Buffer] = None,
+                 weight: Optional[Buffer] = None, sum_out: Optional[Buffer] = None) -> None:
+        """``out = h * rsqrt(mean(h*h) + eps) (* weight)`` with ``h = x (+ residual)``; ``sum_out`` receives h."""
+        h = lambda b: b._h if b is not None else None
+        check(_lib.lib().lapid_b200_rms_norm(self._h, x._h, h(residual), h(weight), h(sum_out), out._h, rows, cols, eps))
+
+    def silu_mul(self, gate: Buffer, up: Buffer, out: Buffer, count: int) -> None:
+        check(_lib.lib().lapid_b200_silu_mul(self._h, gate._h, up._h, out._h, count))
+
     def take_launch_count(self) -> int:
         return int(_lib.lib().lapid_b200_take_launch_count(self._h))
 

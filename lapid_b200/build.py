@@ -28,6 +28,7 @@ SOURCES = {
     "qgemm_f32.cu": [],
     "qgemm_tc.cu": [],
     "noalloc.cu": [],
+    "glue.cu": [],
     "tp_allreduce.cu": [],
     "backend.cc": ["-x", "cu"],
 }

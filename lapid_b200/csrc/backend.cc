@@ -1043,4 +1043,64 @@ lapid_b200_status lapid_b200_tp_all_reduce(lapid_b200_tp_comm *comm, lapid_b200_
     });
 }
 
+// ---- the steps between projections (glue.cu); queued on the device's stream, not waited for
+lapid_b200_status lapid_b200_rms_norm(lapid_b200_device *dev, lapid_b200_buffer *x, lapid_b200_buffer *residual,
+                                      lapid_b200_buffer *weight, lapid_b200_buffer *sum_out, lapid_b200_buffer *out,
+                                      uint64_t rows, uint64_t cols, float eps) {
+    return guard([&] {
+        need(dev);
+        need(x, "x");
+        need(out, "out");
+        if (rows >= (1ull << 31) || !lb::rms_norm_shape_ok((uint32_t)(cols < (1ull << 31) ? cols : 0)))
+            fail("invalid_launch", "rms_norm: cols must be a multiple of 4 in 4..16384, got " + std::to_string(cols));
+        const uint64_t bytes = rows * cols * 4;
+        auto check = [&](lapid_b200_buffer *b, const char *what, uint64_t want) {
+            if (!b) return;
+            if (b->dev != dev) fail("wrong_backend", std::string("rms_norm: ") + what + " belongs to another device");
+            if (b->bytes < want) fail("out_of_bounds", std::string("rms_norm ") + what + ": needs " + std::to_string(want) + " bytes, buffer has " + std::to_string(b->bytes));
+            if ((uintptr_t)b->ptr & 15) fail("invalid_launch", std::string("rms_norm: ") + what + " must be 16-byte aligned");
+        };
+        check(x, "x", bytes);
+        check(residual, "residual", bytes);
+        check(weight, "weight", cols * 4);
+        check(sum_out, "sum_out", bytes);
+        check(out, "out", bytes);
+        if (out == x || out == residual || (sum_out && sum_out == out)) fail("buffer_aliasing", "rms_norm: out aliases an input or sum_out");
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        lb::RmsNormArgs a{};
+        a.x = (const float *)x->ptr;
+        a.residual = residual ? (const float *)residual->ptr : nullptr;
+        a.weight = weight ? (const float *)weight->ptr : nullptr;
+        a.sum_out = sum_out ? (float *)sum_out->ptr : nullptr;
+        a.out = (float *)out->ptr;
+        a.rows = (uint32_t)rows;
+        a.cols = (uint32_t)cols;
+        a.eps = eps;
+        cuda_check(lb::launch_rms_norm(a, dev->pdl, dev->stream), "rms_norm launch");
+        dev->launches++;
+    });
+}
+
+lapid_b200_status lapid_b200_silu_mul(lapid_b200_device *dev, lapid_b200_buffer *gate, lapid_b200_buffer *up,
+                                      lapid_b200_buffer *out, uint64_t count) {
+    return guard([&] {
+        need(dev);
+        need(gate, "gate");
+        need(up, "up");
+        need(out, "out");
+        if (count % 4) fail("invalid_launch", "silu_mul: count must be a multiple of 4, got " + std::to_string(count));
+        for (lapid_b200_buffer *b : {gate, up, out}) {
+            if (b->dev != dev) fail("wrong_backend", "silu_mul: a buffer belongs to another device");
+            if (b->bytes < count * 4) fail("out_of_bounds", "silu_mul: needs " + std::to_string(count * 4) + " bytes, a buffer has " + std::to_string(b->bytes));
+            if ((uintptr_t)b->ptr & 15) fail("invalid_launch", "silu_mul: buffers must be 16-byte aligned");
+        }
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        cuda_check(lb::launch_silu_mul((const float *)gate->ptr, (const float *)up->ptr, (float *)out->ptr, count, dev->sm_count,
+                                       dev->pdl, dev->stream), "silu_mul launch");
+        dev->launches++;
+    });
+}
+
 }  // extern "C"

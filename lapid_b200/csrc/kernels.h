@@ -134,6 +134,21 @@ size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t k);  // bf16 copy of the a
 cudaError_t launch_qgemm_tc(const GemmTcArgs &args, void *a_bf16_scratch, int sm_count, cudaStream_t stream);
 void qgemm_tc_set_wide(int v);  // tuning: -1 choose, 0 / 1 force one / two accumulators per CTA
 
+
+// ---- glue.cu: the row / elementwise steps between the projections of a layer (not on the matmul path)
+struct RmsNormArgs {
+    const float *x;         // [rows, cols]
+    const float *residual;  // [rows, cols] added to x first, or nullptr
+    const float *weight;    // [cols], or nullptr for a weight-less normalise
+    float *sum_out;         // [rows, cols] receives x + residual, or nullptr
+    float *out;             // [rows, cols]
+    uint32_t rows, cols;
+    float eps;
+};
+bool rms_norm_shape_ok(uint32_t cols);  // multiple of 4, at most 16384
+cudaError_t launch_rms_norm(const RmsNormArgs &args, bool pdl, cudaStream_t stream);
+cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint64_t n, int sm_count, bool pdl, cudaStream_t stream);
+
 // ---- tp_allreduce.cu: one-shot all-reduce over peer-mapped memory
 constexpr int TP_MAX_RANKS = 8;
 struct TpAllReduceArgs {

@@ -256,8 +256,9 @@ class GpuTpLayers:
 
     Buffers are allocated once (torch tensors wrapped as library buffers); a token step queues, per
     layer, four launch lists -- [q, k, v], [o], [gate, up], [down] -- on the current torch stream with
-    `execute_async`, the elementwise steps with torch, and the two all-reduces of the row-parallel
-    outputs with NCCL through torch.distributed. The whole step can be captured in a CUDA graph.
+    `execute_async`, the normalise / residual / SwiGLU steps with the library's two glue kernels, and
+    the two all-reduces of the row-parallel outputs with the library's peer all-reduce (or NCCL
+    through torch.distributed). The whole step can be captured in a CUDA graph.
     """
 
     def __init__(self, backend, shape: LayerShape, world: int, rank: int, m: int, weights: list, formats: list,
@@ -277,6 +278,11 @@ class GpuTpLayers:
         torch.cuda.synchronize(dev)
         wrap = backend.wrap_tensor
         self.out_bufs = {name: wrap(self.outs[name]) for name in ("o", "down")}
+        self.hw = torch.zeros(m, d, **f32)
+        torch.cuda.synchronize(dev)
+        self._glue = {"h": wrap(self.h), "hw": wrap(self.hw), "x": wrap(self.x), "o": self.out_bufs["o"],
+                      "down": self.out_bufs["down"], "gate": wrap(self.outs["gate"]), "up": wrap(self.outs["up"]),
+                      "act": wrap(self.act)}
         self._keep = []
         self.steps = []
         for w, f in zip(weights, formats):
@@ -307,21 +313,26 @@ class GpuTpLayers:
             dist.all_reduce(t, group=self.group)
 
     def token(self, n_layers: int):
-        """Queues `n_layers` layer steps (cycling over the distinct weight sets) on the current stream."""
-        ops = TorchOps
-        h = self.h
+        """Queues `n_layers` layer steps (cycling over the distinct weight sets) on the current stream.
+
+        Between the projections only the library's two glue kernels run: `rms_norm` (with the
+        residual add folded in) and `silu_mul`. The residual stream of the token starts from `self.h`
+        (left untouched, so a captured graph replays the same token) and ends in `self.h_out`."""
+        be, m, d = self.be, self.m, self.shape.d_model
+        w = self._glue
+        be.rms_norm(w["h"], w["x"], m, d)                                       # x = norm(h)
+        res = w["h"]
         for i in range(n_layers):
             qkv, o, gu, down = self.steps[i % len(self.steps)]
-            self.x.copy_(ops.rms_normalise(h))
             qkv()
             o()
             self.all_reduce("o")
-            h = h + self.outs["o"]
-            self.x.copy_(ops.rms_normalise(h))
+            be.rms_norm(w["o"], w["x"], m, d, residual=res, sum_out=w["hw"])     # h' = h + o;    x = norm(h')
+            res = w["hw"]
             gu()
-            self.act.copy_(ops.silu_mul(self.outs["gate"], self.outs["up"]))
+            be.silu_mul(w["gate"], w["up"], w["act"], self.act.numel())
             down()
             self.all_reduce("down")
-            h = h + self.outs["down"]
-        self.h_out = h
-        return h
+            be.rms_norm(w["down"], w["x"], m, d, residual=res, sum_out=w["hw"])  # h'' = h' + down; x = norm(h'') for the next layer
+        self.h_out = self.hw
+        return self.hw

@@ -254,6 +254,40 @@ def test_gemv_special_activations(be, oracle):
     assert max_rel(got, want) <= 2e-5
 
 
+def test_glue_kernels_rms_norm_and_silu_mul(be):
+    """The two steps between projections against f64: rms_norm as lapid-cpu's own test does
+    (crates/lapid-cpu/src/tests.rs:246-258, bound 1e-4 there; 1e-5 here), with the residual add, the
+    optional weight and the in-place residual stream; silu(gate) * up."""
+    rng = np.random.default_rng(7)
+    for rows, cols in [(1, 4096), (3, 8192), (8, 16384), (2, 260), (5, 4)]:
+        x = rng.standard_normal((rows, cols), dtype=np.float32) * 3
+        r = rng.standard_normal((rows, cols), dtype=np.float32)
+        w = rng.standard_normal(cols, dtype=np.float32)
+        bx, br, bw, bo, bs = be.upload(x), be.upload(r), be.upload(w), be.alloc(rows * cols * 4), be.alloc(rows * cols * 4)
+        for res, wt, so in [(None, None, None), (br, None, bs), (br, bw, br), (None, bw, None)]:
+            br.write(0, r)
+            be.rms_norm(bx, bo, rows, cols, 1e-6, residual=res, weight=wt, sum_out=so)
+            be.synchronize()
+            h = x.astype(np.float64) + (r if res is not None else 0)
+            want = h / np.sqrt((h ** 2).mean(axis=1, keepdims=True) + 1e-6) * (w if wt is not None else 1)
+            got = bo.download().view(np.float32).reshape(rows, cols)
+            assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+            if so is not None:
+                assert np.array_equal(so.download().view(np.float32).reshape(rows, cols), (x + r).astype(np.float32))
+    g = rng.standard_normal(4096 * 3, dtype=np.float32) * 4
+    u = rng.standard_normal(4096 * 3, dtype=np.float32)
+    g[:4] = [0.0, -100.0, 100.0, -1e-20]
+    bg, bu = be.upload(g), be.upload(u)
+    be.silu_mul(bg, bu, bg, g.size)   # in place over gate
+    be.synchronize()
+    want = g.astype(np.float64) / (1 + np.exp(-g.astype(np.float64))) * u
+    got = bg.download().view(np.float32)
+    assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+    with pytest.raises(lp.LapidError) as e:
+        be.rms_norm(bg, bu, 1, 4098)
+    assert e.value.code == "invalid_launch"
+
+
 # ------------------------------------------------------------------ exact-f32 GEMM path
 @pytest.mark.parametrize("fmt,name", FMTS)
 def test_gemm_f32_bit_exact_vs_oracle(be, oracle, fmt, name):
