@@ -1038,7 +1038,7 @@ lapid_b200_status lapid_b200_tp_all_reduce(lapid_b200_tp_comm *comm, lapid_b200_
         lb::TpAllReduceArgs a = comm->args;
         a.data = (float *)data->ptr + offset;
         a.count = count;
-        cuda_check(lb::launch_tp_all_reduce(a, dev->stream), "tp all-reduce launch");
+        cuda_check(lb::launch_tp_all_reduce(a, dev->pdl, dev->stream), "tp all-reduce launch");
         dev->launches++;
     });
 }

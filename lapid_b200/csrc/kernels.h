@@ -160,6 +160,6 @@ struct TpAllReduceArgs {
     int *status;
 };
 size_t tp_comm_bytes(int world, uint64_t max_elems);
-cudaError_t launch_tp_all_reduce(const TpAllReduceArgs &args, cudaStream_t stream);
+cudaError_t launch_tp_all_reduce(const TpAllReduceArgs &args, bool pdl, cudaStream_t stream);
 
 }  // namespace lb
