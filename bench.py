@@ -580,19 +580,23 @@ def measure_tp70b(be, stream, dev, rank, world, quantized):
         formats.append(f)
     token_bytes = wbytes * n_layers // n_sets
     out = {"layers": n_layers, "weight_sets_cycled": n_sets, "weight_bytes_per_token_per_gpu": token_bytes, "tp": world,
-           "collective": ("decode: the library's one-shot all-reduce over peer-mapped memory (2 per layer); "
-                          "prefill: nccl all_reduce") if world > 1 else "none"}
+           "collective": ("decode: partials pushed over peer-mapped memory from the GEMV epilogue and summed by the "
+                          "following rms_norm (2 per layer, no kernel of their own); prefill: nccl all_reduce") if world > 1 else "none"}
     peer = None
     if world > 1:
         try:
             peer = tp.PeerAllReduce(be, rank, world, dev)
         except Exception as e:
             out["peer_all_reduce_error"] = f"{type(e).__name__}: {e}"[:200]
-    variants = [(1, "decode_b1", peer), (512, "prefill_m512", peer)]
+    # decode_b1: the row-parallel GEMVs push their partials from their epilogue and the following
+    # rms_norm sums them (no all-reduce kernel); _allreduce_kernel: the library's stand-alone one-shot
+    # all-reduce; _nccl: the library collective, for comparison
+    variants = [(1, "decode_b1", peer, True), (512, "prefill_m512", peer, False)]
     if world > 1 and peer is not None:
-        variants.insert(1, (1, "decode_b1_nccl", None))  # the library collective, for comparison
-    for m, key, reducer in variants:
-        layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats, peer_all_reduce=reducer)
+        variants.insert(1, (1, "decode_b1_allreduce_kernel", peer, False))
+        variants.insert(2, (1, "decode_b1_nccl", None, False))
+    for m, key, reducer, fused in variants:
+        layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats, peer_all_reduce=reducer, fused=fused)
         layers.h.normal_()
         torch.cuda.synchronize()
         run = lambda: layers.token(n_layers)

@@ -210,6 +210,23 @@ LAPID_B200_API void lapid_b200_tp_comm_free(lapid_b200_tp_comm *comm);
 LAPID_B200_API lapid_b200_status lapid_b200_tp_all_reduce(lapid_b200_tp_comm *comm, lapid_b200_buffer *data,
                                                           uint64_t offset, uint64_t count);
 
+/* The all-reduce of a decode step without a kernel of its own: the row-parallel projection hands its
+ * partial to every rank from the GEMV's epilogue, and the normalisation that follows polls and sums
+ * the ranks' partials itself (in rank order: bit-identical on every rank).
+ *   lapid_b200_tp_matmul_push: ONE decode MatMul launch (batch*m in 1..8, contiguous output view,
+ *     rows*n a multiple of 4 and <= max_elems). Launches that take a K-quant fast kernel push from
+ *     the kernel; others run as usual and a small kernel publishes their output buffer. The output
+ *     buffer of a pushing launch is not written.
+ *   lapid_b200_tp_rms_norm: lapid_b200_rms_norm (below) with x = the sum over ranks of the partials of
+ *     the push in progress, [rows, cols] row-major; closes the call. Every push must be followed by
+ *     exactly one lapid_b200_tp_rms_norm on every rank before the next push or all-reduce on this
+ *     comm. */
+LAPID_B200_API lapid_b200_status lapid_b200_tp_matmul_push(lapid_b200_tp_comm *comm, const lapid_b200_launch *launch,
+                                                           lapid_b200_buffer *const *buffers, size_t n_buffers);
+LAPID_B200_API lapid_b200_status lapid_b200_tp_rms_norm(lapid_b200_tp_comm *comm, lapid_b200_buffer *residual,
+                                                        lapid_b200_buffer *weight, lapid_b200_buffer *sum_out,
+                                                        lapid_b200_buffer *out, uint64_t rows, uint64_t cols, float eps);
+
 /* ---- the steps between the projections of a layer ------------------------------------------- */
 /* Not part of the quantized-matmul path: two small kernels so that a layer-stack measurement is not
  * dominated by a framework's elementwise launches. Queued on the device's stream, not waited for.

@@ -79,6 +79,8 @@ SYMBOLS = {
     "lapid_b200_tp_comm_create": (C.c_int32, [P, C.c_int32, C.c_int32, C.POINTER(P), C.c_uint64, C.POINTER(P)]),
     "lapid_b200_tp_comm_free": (None, [P]),
     "lapid_b200_tp_all_reduce": (C.c_int32, [P, P, C.c_uint64, C.c_uint64]),
+    "lapid_b200_tp_matmul_push": (C.c_int32, [P, P, P, C.c_size_t]),
+    "lapid_b200_tp_rms_norm": (C.c_int32, [P, P, P, P, P, C.c_uint64, C.c_uint64, C.c_float]),
     "lapid_b200_rms_norm": (C.c_int32, [P, P, P, P, P, P, C.c_uint64, C.c_uint64, C.c_float]),
     "lapid_b200_silu_mul": (C.c_int32, [P, P, P, P, C.c_uint64]),
     "lapid_b200_gemv_q4k_static": (C.c_int32, [C.c_int32, P, P, P, C.c_uint64, P, C.c_uint32, C.c_uint32, C.c_uint32]),

@@ -357,8 +357,10 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
     return p;
 }
 
+// `tp` not null: a launch that takes one of the K-quant fast decode kernels hands its result to the
+// tensor-parallel group from its epilogue instead of storing it (`*pushed` says whether it did).
 void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_buffer *const *buffers, size_t n_buffers,
-                ActSlot *slot, PendingGroup *pend = nullptr) {
+                ActSlot *slot, PendingGroup *pend = nullptr, const lb::TpPushTable *tp = nullptr, bool *pushed = nullptr) {
     Plan p = plan_launch(dev, l);
     auto get = [&](uint32_t id) -> lapid_b200_buffer * {
         if (id >= n_buffers || !buffers[id])
@@ -477,6 +479,10 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl, dev.stream), "act_quant launch");
             dev.launches++;
             slot->done = true;
+        }
+        if (tp && slot->records) {
+            g.tp = tp;
+            *pushed = true;
         }
         if (slot->records == 2) {
             lb::GemvGroup one{};
@@ -1010,6 +1016,21 @@ lapid_b200_status lapid_b200_tp_comm_create(lapid_b200_device *dev, int32_t rank
         c->args.world = world;
         c->args.max_elems = max_elems;
         c->args.status = dev->status_dev;
+        // the table the pushing kernels read, at the start of this rank's own buffer
+        lb::TpPushTable table{};
+        for (int i = 0; i < world; i++) table.peer[i] = peer_bases[i];
+        table.max_elems = max_elems;
+        table.rank = rank;
+        table.world = world;
+        {
+            std::lock_guard<std::mutex> lock(dev->mu);
+            dev->make_current();
+            cudaError_t e = cudaMemcpy(peer_bases[rank], &table, sizeof(table), cudaMemcpyHostToDevice);
+            if (e != cudaSuccess) {
+                delete c;
+                cuda_check(e, "cudaMemcpy(tp table)");
+            }
+        }
         dev->refs.fetch_add(1);
         c->dev = dev;
         *out = c;
@@ -1039,6 +1060,76 @@ lapid_b200_status lapid_b200_tp_all_reduce(lapid_b200_tp_comm *comm, lapid_b200_
         a.data = (float *)data->ptr + offset;
         a.count = count;
         cuda_check(lb::launch_tp_all_reduce(a, dev->pdl, dev->stream), "tp all-reduce launch");
+        dev->launches++;
+    });
+}
+
+// One decode MatMul launch whose result goes to the group: from the GEMV's own epilogue where the
+// launch takes a K-quant fast kernel, else through its output buffer and a publishing kernel.
+lapid_b200_status lapid_b200_tp_matmul_push(lapid_b200_tp_comm *comm, const lapid_b200_launch *launch,
+                                            lapid_b200_buffer *const *buffers, size_t n_buffers) {
+    return guard([&] {
+        if (!comm) fail("invalid_argument", "comm is NULL");
+        if (!launch) fail("invalid_argument", "launch is NULL");
+        if (n_buffers && !buffers) fail("invalid_argument", "buffers is NULL");
+        lapid_b200_device *dev = comm->dev;
+        const lapid_b200_launch &l = *launch;
+        const uint64_t count = l.batch * l.m * l.n;
+        if (l.kind != LAPID_B200_KERNEL_MATMUL || l.batch * l.m > 8 || l.batch * l.m == 0)
+            fail("invalid_launch", "tp push: a decode MatMul launch (1..8 rows) is required");
+        if (count % 4 || count > comm->args.max_elems)
+            fail("invalid_launch", "tp push: rows*n = " + std::to_string(count) + " must be a multiple of 4 and <= " + std::to_string(comm->args.max_elems));
+        if (l.out.offset != 0 || l.out.row_stride != l.n || (l.batch > 1 && l.out.batch_stride != l.m * l.n))
+            fail("invalid_launch", "tp push: the output view must be contiguous");
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        bool pushed = false;
+        run_launch(*dev, l, buffers, n_buffers, nullptr, nullptr, (const lb::TpPushTable *)comm->args.peer[comm->args.rank], &pushed);
+        if (!pushed) {
+            lb::TpAllReduceArgs a = comm->args;
+            a.data = (float *)buffers[l.output]->ptr;
+            a.count = count;
+            a.push_only = 1;
+            cuda_check(lb::launch_tp_all_reduce(a, dev->pdl, dev->stream), "tp push launch");
+            dev->launches++;
+        }
+    });
+}
+
+// rms_norm whose x is the sum of what the ranks pushed for the call in progress; closes the call.
+lapid_b200_status lapid_b200_tp_rms_norm(lapid_b200_tp_comm *comm, lapid_b200_buffer *residual, lapid_b200_buffer *weight,
+                                         lapid_b200_buffer *sum_out, lapid_b200_buffer *out, uint64_t rows, uint64_t cols, float eps) {
+    return guard([&] {
+        if (!comm) fail("invalid_argument", "comm is NULL");
+        need(out, "out");
+        lapid_b200_device *dev = comm->dev;
+        if (rows == 0 || rows > 8 || !lb::rms_norm_shape_ok((uint32_t)(cols < (1ull << 31) ? cols : 0)) || rows * cols > comm->args.max_elems)
+            fail("invalid_launch", "tp rms_norm: rows in 1..8, cols a multiple of 4 up to 16384, rows*cols <= " + std::to_string(comm->args.max_elems));
+        const uint64_t bytes = rows * cols * 4;
+        auto check = [&](lapid_b200_buffer *b, const char *what, uint64_t want) {
+            if (!b) return;
+            if (b->dev != dev) fail("wrong_backend", std::string("tp rms_norm: ") + what + " belongs to another device");
+            if (b->bytes < want) fail("out_of_bounds", std::string("tp rms_norm ") + what + ": needs " + std::to_string(want) + " bytes, buffer has " + std::to_string(b->bytes));
+            if ((uintptr_t)b->ptr & 15) fail("invalid_launch", std::string("tp rms_norm: ") + what + " must be 16-byte aligned");
+        };
+        check(residual, "residual", bytes);
+        check(weight, "weight", cols * 4);
+        check(sum_out, "sum_out", bytes);
+        check(out, "out", bytes);
+        if (out == residual || (sum_out && sum_out == out)) fail("buffer_aliasing", "tp rms_norm: out aliases residual or sum_out");
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        lb::RmsNormArgs a{};
+        a.tp = (const lb::TpPushTable *)comm->args.peer[comm->args.rank];
+        a.status = dev->status_dev;
+        a.residual = residual ? (const float *)residual->ptr : nullptr;
+        a.weight = weight ? (const float *)weight->ptr : nullptr;
+        a.sum_out = sum_out ? (float *)sum_out->ptr : nullptr;
+        a.out = (float *)out->ptr;
+        a.rows = (uint32_t)rows;
+        a.cols = (uint32_t)cols;
+        a.eps = eps;
+        cuda_check(lb::launch_rms_norm(a, dev->pdl, dev->stream), "tp rms_norm launch");
         dev->launches++;
     });
 }

@@ -9,12 +9,20 @@
 //   silu_mul   out = silu(gate) * up = gate / (1 + exp(-gate)) * up                   elementwise
 //              the SwiGLU product (crates/lapid-nn/src/mlp.rs:84), an Elementwise kernel in lapid
 //
-// Both are memory-trivial (tens of KB at decode sizes) and latency-bound: one block per row with
-// 128-bit accesses and a single block reduction, programmatic dependent launch like the GEMVs.
+// Both are memory-trivial (tens of KB at decode sizes) and latency-bound: 128-bit accesses, a row
+// is split over a thread-block cluster of up to 8 CTAs whose partial sums of squares meet through
+// distributed shared memory (so a single decode row still spreads over 8 SMs -- which matters most
+// when the row is the sum of the tensor-parallel ranks' partials, polled from the hand-off slots),
+// programmatic dependent launch like the GEMVs.
 // They are not part of the quantized-matmul path; f32 results, not bit-matched to lapid-cpu (the
 // order of the sum of squares differs): the tests hold them to 1e-5 relative against f64.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "kernels.h"
+#include "tp_ll.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace lb {
 
@@ -25,16 +33,55 @@ __global__ void __launch_bounds__(GLUE_THREADS) rms_norm_kernel(RmsNormArgs p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float partial[GLUE_THREADS / 32];
-    const uint32_t row = blockIdx.x, n4 = p.cols / 4;
+    __shared__ float cta_ss;
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t parts = cluster.num_blocks(), part = cluster.block_rank();
+    const uint32_t row = blockIdx.x / parts, n4 = p.cols / 4;
+    const uint32_t per = (n4 + parts - 1) / parts, c_lo = part * per, c_hi = min(n4, c_lo + per);  // this CTA's float4 columns
+    // tensor-parallel input: x = sum over ranks (in rank order) of the partials they pushed for the
+    // call in progress, polled pair by pair from this rank's own slots (protocol: tp_allreduce.cu)
+    uint32_t epoch = 0;
+    const uint8_t *slots = nullptr;
+    size_t slot_bytes = 0;
+    bool ok = true;
+    if (p.tp) {
+        epoch = tp_current_epoch(p.tp);
+        slot_bytes = (size_t)p.tp->max_elems * 8;
+        slots = (const uint8_t *)p.tp->peer[p.tp->rank] + TP_HEADER + (size_t)(epoch & 1) * p.tp->world * slot_bytes +
+                (size_t)row * p.cols * 8;
+    }
     const float4 *x = (const float4 *)(p.x + (size_t)row * p.cols);
     const float4 *res = p.residual ? (const float4 *)(p.residual + (size_t)row * p.cols) : nullptr;
     float4 v[GLUE_MAX_VEC];
     float ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < GLUE_MAX_VEC; i++) {
-        const uint32_t c = threadIdx.x + i * GLUE_THREADS;
-        if (c < n4) {
-            float4 a = x[c];
+        const uint32_t c = c_lo + threadIdx.x + i * GLUE_THREADS;
+        if (c < c_hi) {
+            float4 a;
+            if (p.tp) {
+                a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int q = 0; q < p.tp->world; q++) {
+                    const uint8_t *src = slots + (size_t)q * slot_bytes + (size_t)c * 32;
+                    uint4 lo = ld_pairs(src), hi = ld_pairs(src + 16);
+                    for (uint32_t spin = 0; ok && (lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch); spin++) {
+                        if (spin >= TP_SPIN_LIMIT) {
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(20);
+                        lo = ld_pairs(src);
+                        hi = ld_pairs(src + 16);
+                    }
+                    const float4 v = make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x), __uint_as_float(hi.z));
+                    a.x = q ? a.x + v.x : v.x;
+                    a.y = q ? a.y + v.y : v.y;
+                    a.z = q ? a.z + v.z : v.z;
+                    a.w = q ? a.w + v.w : v.w;
+                }
+            } else {
+                a = x[c];
+            }
             if (res) {
                 const float4 b = res[c];
                 a.x += b.x;
@@ -54,11 +101,17 @@ __global__ void __launch_bounds__(GLUE_THREADS) rms_norm_kernel(RmsNormArgs p) {
     float tot = 0.0f;
 #pragma unroll
     for (int w = 0; w < GLUE_THREADS / 32; w++) tot += partial[w];
+    if (parts > 1) {  // every CTA of the row adds the partial sums in the same order
+        if (threadIdx.x == 0) cta_ss = tot;
+        cluster.sync();
+        tot = 0.0f;
+        for (uint32_t r = 0; r < parts; r++) tot += *cluster.map_shared_rank(&cta_ss, r);
+    }
     const float rstd = 1.0f / sqrtf(tot * (1.0f / (float)p.cols) + p.eps);
 #pragma unroll
     for (int i = 0; i < GLUE_MAX_VEC; i++) {
-        const uint32_t c = threadIdx.x + i * GLUE_THREADS;
-        if (c < n4) {
+        const uint32_t c = c_lo + threadIdx.x + i * GLUE_THREADS;
+        if (c < c_hi) {
             float4 a = v[i];
             a.x *= rstd;
             a.y *= rstd;
@@ -72,6 +125,18 @@ __global__ void __launch_bounds__(GLUE_THREADS) rms_norm_kernel(RmsNormArgs p) {
                 a.w *= g.w;
             }
             ((float4 *)(p.out + (size_t)row * p.cols))[c] = a;
+        }
+    }
+    if (parts > 1) cluster.sync();  // no CTA leaves while a neighbour may still read its partial sum
+    if (p.tp) {  // the last CTA to finish closes the call
+        if (!ok && p.status) atomicOr(p.status, 64);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t *epoch_ctr = (uint32_t *)((uint8_t *)p.tp->peer[p.tp->rank] + 256), *done_ctr = epoch_ctr + 1;
+            if (atomicAdd(done_ctr, 1u) == gridDim.x - 1) {
+                *done_ctr = 0;
+                *(volatile uint32_t *)epoch_ctr = epoch;
+            }
         }
     }
 }
@@ -90,15 +155,27 @@ __global__ void __launch_bounds__(GLUE_THREADS) silu_mul_kernel(const float *gat
     }
 }
 
-static void pdl_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, unsigned grid, bool pdl, cudaStream_t stream) {
+static void pdl_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, unsigned grid, bool pdl, cudaStream_t stream,
+                       unsigned cluster = 1) {
     cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(GLUE_THREADS);
     cfg.stream = stream;
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    int n = 0;
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        n++;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = n;
 }
 
 bool rms_norm_shape_ok(uint32_t cols) { return cols >= 4 && cols % 4 == 0 && cols <= GLUE_THREADS * GLUE_MAX_VEC * 4; }
@@ -106,9 +183,10 @@ bool rms_norm_shape_ok(uint32_t cols) { return cols >= 4 && cols % 4 == 0 && col
 cudaError_t launch_rms_norm(const RmsNormArgs &a, bool pdl, cudaStream_t stream) {
     if (a.rows == 0) return cudaSuccess;
     if (!rms_norm_shape_ok(a.cols)) return cudaErrorInvalidValue;
+    const unsigned parts = a.cols >= 4096 ? 8 : a.cols >= 2048 ? 4 : a.cols >= 1024 ? 2 : 1;
     cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attr[1];
-    pdl_config(cfg, attr, a.rows, pdl, stream);
+    cudaLaunchAttribute attr[2];
+    pdl_config(cfg, attr, a.rows * parts, pdl, stream, parts);
     return cudaLaunchKernelEx(&cfg, rms_norm_kernel, a);
 }
 
@@ -117,7 +195,7 @@ cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint
     if (n % 4) return cudaErrorInvalidValue;
     const uint64_t n4 = n / 4, want = (n4 + GLUE_THREADS - 1) / GLUE_THREADS, cap = (uint64_t)sm_count * 8;
     cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     pdl_config(cfg, attr, (unsigned)(want < cap ? want : cap), pdl, stream);
     return cudaLaunchKernelEx(&cfg, silu_mul_kernel, gate, up, out, n4);
 }

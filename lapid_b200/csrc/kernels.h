@@ -42,6 +42,15 @@ struct ActQuantBatch {
 cudaError_t launch_act_quant_batch(const ActQuantBatch &batch, int sm_count, bool pdl, cudaStream_t stream);
 
 // ---- qgemv.cu
+// What a kernel needs to hand its result to the other ranks of a tensor-parallel group (see
+// tp_allreduce.cu): lives in device memory, at the start of this rank's symmetric buffer.
+constexpr int TP_MAX_RANKS = 8;
+struct TpPushTable {
+    void *peer[TP_MAX_RANKS];  // every rank's symmetric buffer as mapped on this GPU; peer[rank] is this rank's own
+    uint64_t max_elems;        // value capacity of one slot
+    int32_t rank, world;
+};
+
 struct GemvArgs {
     const uint8_t *w;       // quantized [n, k] matrix in lapid-quant layout
     uint64_t w_bytes;       // bytes readable behind `w`
@@ -58,6 +67,8 @@ struct GemvArgs {
     uint64_t ex_off;
     int64_t ex_s0, ex_s1, ex_s2;
     uint32_t rows, m, n, k;
+    const TpPushTable *tp;  // not nullptr (K-quant fast kernels only): the result, row-major [rows, n], goes to slot[rank] of every
+                            // rank's buffer as {value, epoch} pairs instead of to `out`
 };
 // rows in 1..8. Returns cudaErrorInvalidValue for an unsupported combination.
 cudaError_t launch_qgemv(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
@@ -137,6 +148,8 @@ void qgemm_tc_set_wide(int v);  // tuning: -1 choose, 0 / 1 force one / two accu
 
 // ---- glue.cu: the row / elementwise steps between the projections of a layer (not on the matmul path)
 struct RmsNormArgs {
+    const TpPushTable *tp;  // not nullptr: x is the sum over ranks of what they pushed for the current call (x is ignored)
+    int *status;
     const float *x;         // [rows, cols]
     const float *residual;  // [rows, cols] added to x first, or nullptr
     const float *weight;    // [cols], or nullptr for a weight-less normalise
@@ -150,7 +163,6 @@ cudaError_t launch_rms_norm(const RmsNormArgs &args, bool pdl, cudaStream_t stre
 cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint64_t n, int sm_count, bool pdl, cudaStream_t stream);
 
 // ---- tp_allreduce.cu: one-shot all-reduce over peer-mapped memory
-constexpr int TP_MAX_RANKS = 8;
 struct TpAllReduceArgs {
     void *peer[TP_MAX_RANKS];  // every rank's symmetric buffer as mapped on this GPU; peer[rank] is this rank's own
     int rank, world;
@@ -158,6 +170,7 @@ struct TpAllReduceArgs {
     float *data;               // local partial, replaced by the sum
     uint64_t count;            // multiple of 4, <= max_elems
     int *status;
+    int push_only;             // 1: publish `data` to every rank's slots and return; the reader (tp rms_norm) sums and closes the call
 };
 size_t tp_comm_bytes(int world, uint64_t max_elems);
 cudaError_t launch_tp_all_reduce(const TpAllReduceArgs &args, bool pdl, cudaStream_t stream);

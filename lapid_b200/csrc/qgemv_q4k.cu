@@ -24,6 +24,7 @@
 //    word and the kernel runs to its end (with a wrong result that the host then rejects).
 #include "common.cuh"
 #include "kernels.h"
+#include "tp_ll.cuh"
 
 namespace lb {
 
@@ -200,6 +201,8 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
+    __shared__ TpPushCtx tp_ctx;  // only the first member of a launch may push (tensor-parallel launches are never grouped)
+    if (grp.item[0].tp && threadIdx.x == 0) tp_push_ctx_load(&tp_ctx, grp.item[0].tp);
     {
         const uint32_t chunks = M * nblk * (REC / 16);
         for (int i = 0; i < grp.count; i++) {
@@ -312,7 +315,8 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             if (gl == 0 && row < n) {
                 const uint32_t bt = r / p.m, i = r % p.m;
                 if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
-                p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
+                if (p.tp) tp_push_value(&tp_ctx, (uint64_t)r * n + row, v);  // row-parallel partial: to every rank
+                else p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
             }
         }
     }

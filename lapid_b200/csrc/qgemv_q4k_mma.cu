@@ -34,6 +34,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tp_ll.cuh"
 
 namespace lb {
 namespace mm {
@@ -179,6 +180,8 @@ qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
+    __shared__ TpPushCtx tp_ctx;  // only the first member of a launch may push (tensor-parallel launches are never grouped)
+    if (grp.item[0].tp && threadIdx.x == 0) tp_push_ctx_load(&tp_ctx, grp.item[0].tp);
     {
         const uint32_t chunks = nblk * ABLK / 16;
         for (int i = 0; i < grp.count; i++) {
@@ -332,7 +335,8 @@ qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
             if (row < p.n && r < M) {
                 const uint32_t bt = r / p.m, ri = r % p.m;
                 if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
-                p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = v;
+                if (p.tp) tp_push_value(&tp_ctx, (uint64_t)r * p.n + row, v);  // row-parallel partial: to every rank
+                else p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = v;
             }
         }
     }

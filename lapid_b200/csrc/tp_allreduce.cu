@@ -4,7 +4,7 @@
 // token that needs two calls per layer) dominates tensor-parallel decode.
 //
 // Every rank owns one "symmetric" buffer, mapped into every peer's address space:
-//     [0, 256)      unused
+//     [0, 256)      TpPushTable: the peers' addresses, for kernels that hand over their result themselves
 //     [256, 512)    epoch, done  u32: this rank's call counter and its CTA-completion counter
 //     [512, ...)    slots[parity][src][max_elems]  of {f32 value, u32 epoch} pairs
 // Every value travels with its own flag: a slot element is an 8-byte pair {value, epoch of the
@@ -27,21 +27,15 @@
 // without a full drain. A poll that gives up sets a status bit and the kernel still terminates.
 #include "common.cuh"
 #include "kernels.h"
+#include "tp_ll.cuh"
 
 namespace lb {
 
-constexpr uint32_t TP_HEADER = 512;
-constexpr uint32_t TP_SPIN_LIMIT = 1u << 21;
-
-__device__ __forceinline__ void st_pairs(void *p, float a, float b, uint32_t epoch) {
-    asm volatile("st.volatile.global.v4.b32 [%0], {%1, %2, %3, %2};" ::"l"(p), "r"(__float_as_uint(a)), "r"(epoch), "r"(__float_as_uint(b))
-                 : "memory");
-}
-__device__ __forceinline__ uint4 ld_pairs(const void *p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-}
+// The same protocol has two more users: a decode GEMV can push its result straight from its
+// epilogue (qgemv_q4k.cu, qgemv_q4k_mma.cu: GemvArgs::tp) and the normalisation that follows a
+// row-parallel projection can poll and sum the slots itself (glue.cu: RmsNormArgs::tp), so that the
+// all-reduce of a decode step costs no kernel of its own. `push_only` below is the fallback
+// producer for launches whose kernel has no pushing epilogue.
 
 __global__ void __launch_bounds__(256) tp_all_reduce_kernel(TpAllReduceArgs a) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -63,6 +57,7 @@ __global__ void __launch_bounds__(256) tp_all_reduce_kernel(TpAllReduceArgs a) {
         for (int q = 0; q < a.world; q++)
             st_pairs((uint8_t *)a.peer[q] + TP_HEADER + ((size_t)parity * a.world + a.rank) * slot_bytes + (size_t)i * 16, v.x, v.y, epoch);
     }
+    if (a.push_only) return;  // the reader closes the call (bumps the epoch)
     // ---- poll and reduce in rank order
     bool ok = true;
     const uint8_t *base = mine + TP_HEADER + (size_t)parity * a.world * slot_bytes;

@@ -245,10 +245,31 @@ class PeerAllReduce:
     def __call__(self, buf, numel: int) -> None:
         self._lib.check(self._lib.lib().lapid_b200_tp_all_reduce(self._h, buf._h, 0, numel))
 
+    def pushing(self, launch, buffers):
+        """A zero-argument callable that queues `launch` (one decode MatMul) so that its result goes
+        to every rank's slots from the GEMV's own epilogue (`lapid_b200_tp_matmul_push`); follow it
+        with `rms_norm`, which sums the ranks' partials while it normalises."""
+        arr, bufs = self.backend._pack([launch], buffers)
+        fn, check, h, nb = self._lib.lib().lapid_b200_tp_matmul_push, self._lib.check, self._h, len(buffers)
+
+        def run():
+            check(fn(h, arr, bufs, nb))
+        run.keep = (arr, bufs, list(buffers))
+        return run
+
+    def rms_norm(self, out, rows: int, cols: int, eps: float = 1e-6, residual=None, weight=None, sum_out=None) -> None:
+        """`Backend.rms_norm` with x = the sum over ranks of the push in progress (`lapid_b200_tp_rms_norm`)."""
+        h = lambda b: b._h if b is not None else None
+        self._lib.check(self._lib.lib().lapid_b200_tp_rms_norm(self._h, h(residual), h(weight), h(sum_out), out._h, rows, cols, eps))
+
     def close(self):
         if self._h:
             self._lib.lib().lapid_b200_tp_comm_free(self._h)
             self._h = None
+
+
+def d_model_of(shape) -> int:
+    return shape.d_model
 
 
 class GpuTpLayers:
@@ -262,11 +283,14 @@ class GpuTpLayers:
     """
 
     def __init__(self, backend, shape: LayerShape, world: int, rank: int, m: int, weights: list, formats: list,
-                 group=None, peer_all_reduce=None):
+                 group=None, peer_all_reduce=None, fused: bool = False):
         import torch
         from .backend import matmul_launch
         self.be, self.shape, self.world, self.rank, self.m, self.group = backend, shape, world, rank, m, group
         self.peer = peer_all_reduce
+        # fused: the row-parallel GEMVs push their partials from their epilogue and the following
+        # rms_norm sums them: the all-reduce has no kernel of its own
+        self.fused = bool(fused and peer_all_reduce is not None and world > 1 and peer_all_reduce.fits(m * d_model_of(shape)))
         dev = weights[0]["q"].device
         d = shape.d_model
         proj = {name: local_shape(name, n, k, kind, world) for name, n, k, kind in shape.projections()}
@@ -299,7 +323,11 @@ class GpuTpLayers:
             lists = [[launch("q", 0), launch("k", 0), launch("v", 0)], [launch("o", 1)],
                      [launch("gate", 0), launch("up", 0)], [launch("down", 2)]]
             backend.prepare([l for ls in lists for l in ls])
-            self.steps.append([backend.packed(ls, bufs) for ls in lists])
+            step = [backend.packed(ls, bufs) for ls in lists]
+            if self.fused:
+                step[1] = self.peer.pushing(lists[1][0], bufs)
+                step[3] = self.peer.pushing(lists[3][0], bufs)
+            self.steps.append(step)
             self._keep.append(bufs)
 
     def all_reduce(self, name):
@@ -326,13 +354,19 @@ class GpuTpLayers:
             qkv, o, gu, down = self.steps[i % len(self.steps)]
             qkv()
             o()
-            self.all_reduce("o")
-            be.rms_norm(w["o"], w["x"], m, d, residual=res, sum_out=w["hw"])     # h' = h + o;    x = norm(h')
+            if self.fused:
+                self.peer.rms_norm(w["x"], m, d, residual=res, sum_out=w["hw"])
+            else:
+                self.all_reduce("o")
+                be.rms_norm(w["o"], w["x"], m, d, residual=res, sum_out=w["hw"])     # h' = h + o;    x = norm(h')
             res = w["hw"]
             gu()
             be.silu_mul(w["gate"], w["up"], w["act"], self.act.numel())
             down()
-            self.all_reduce("down")
-            be.rms_norm(w["down"], w["x"], m, d, residual=res, sum_out=w["hw"])  # h'' = h' + down; x = norm(h'') for the next layer
+            if self.fused:
+                self.peer.rms_norm(w["x"], m, d, residual=res, sum_out=w["hw"])
+            else:
+                self.all_reduce("down")
+                be.rms_norm(w["down"], w["x"], m, d, residual=res, sum_out=w["hw"])  # h'' = h' + down; x = norm(h'') for the next layer
         self.h_out = self.hw
         return self.hw

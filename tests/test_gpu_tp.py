@@ -44,6 +44,22 @@ def _worker(rank, world, port, m, out_path, peer):
         be.set_stream(stream.cuda_stream)
         results = []
         reducer = tp.PeerAllReduce(be, rank, world, dev) if peer else None
+        if peer:
+            # the fused hand-off (GEMV epilogue pushes, rms_norm sums) adds the same numbers in the same
+            # order as the stand-alone all-reduce kernel: the residual stream must match bit for bit
+            shape, weights, formats = _build(be, tp, O, quant, torch, rank, world, dev, 2)
+            outs = []
+            for fused in (False, True):
+                layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats, peer_all_reduce=reducer, fused=fused)
+                assert layers.fused == fused
+                layers.h.copy_(torch.from_numpy(O.normal(99, m * shape.d_model).reshape(m, -1)).to(dev))
+                torch.cuda.synchronize(dev)
+                with torch.cuda.stream(stream):
+                    out = layers.token(4).clone()
+                stream.synchronize()
+                outs.append(out)
+                be.synchronize()
+            assert torch.equal(outs[0], outs[1])
         for w_ in ((world, rank), (1, 0)):
             shape, weights, formats = _build(be, tp, O, quant, torch, w_[1], w_[0], dev, 2)
             layers = tp.GpuTpLayers(be, shape, w_[0], w_[1], m, weights, formats, peer_all_reduce=reducer)
