@@ -317,7 +317,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     prefill_rows = None
     if world == 1 and not args.no_prefill:
-        prefill_rows = measure_prefill(be, stream, dev, base)
+        prefill_rows = measure_prefill(be, stream, dev, base, quantized)
     stack_obj = None
     if world == 1 and not args.no_stack:
         try:
@@ -453,9 +453,10 @@ def _event_time(stream, fn, reps, warm=2):
     return ts[len(ts) // 2]
 
 
-def measure_prefill(be, stream, dev, base):
-    """Prefill Q4_K GEMM (tcgen05): M in {64, 512, 2048} on the gate/up and down shapes; five weight
-    copies are cycled (165 MB > L2). TFLOP/s = 2*M*N*K / time, against the measured bf16 peaks."""
+def measure_prefill(be, stream, dev, base, quantized):
+    """Prefill GEMM (tcgen05): Q4_K at M in {64, 512, 2048} and Q6_K at M in {512, 2048} on the gate/up
+    and down shapes; five weight copies are cycled (165 MB > L2). TFLOP/s = 2*M*N*K / time, against
+    the measured bf16 peaks."""
     import torch
     from lapid_b200.backend import matmul_launch
     try:
@@ -465,19 +466,20 @@ def measure_prefill(be, stream, dev, base):
     except Exception:
         burst, sustained = 1590.0, 1400.0
     rows = []
-    for (n, k) in [(14336, 4096), (4096, 14336)]:
+    for fmt, (n, k) in [(f, s) for f in (6, 8) for s in [(14336, 4096), (4096, 14336)]]:
         copies = 5
-        pool = base[(n, k)].repeat(copies).view(copies, -1)
-        for m in (64, 512, 2048):
+        wq = base[(n, k)] if fmt == 6 else quantized(8, n, k, 700 + n)
+        pool = wq.repeat(copies).view(copies, -1)
+        for m in ((64, 512, 2048) if fmt == 6 else (512, 2048)):
             a = torch.randn(m * k, device=dev)
             o = torch.zeros(m * n, device=dev)
             torch.cuda.synchronize()
             bufs = [be.wrap_tensor(a), be.wrap_tensor(o)] + [be.wrap_tensor(pool[c]) for c in range(copies)]
-            ls = [matmul_launch(6, m, n, k, inputs=(0, 2 + c), output=1) for c in range(copies)]
+            ls = [matmul_launch(fmt, m, n, k, inputs=(0, 2 + c), output=1) for c in range(copies)]
             be.prepare(ls)
             ms = _event_time(stream, be.packed(ls, bufs), 5) / copies
             tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
-            rows.append({"fmt": "q4_k", "m": m, "n": n, "k": k, "us": round(ms * 1e3, 1), "tflops": round(tf, 1),
+            rows.append({"fmt": FMT_NAMES[fmt], "m": m, "n": n, "k": k, "us": round(ms * 1e3, 1), "tflops": round(tf, 1),
                          "frac_burst": round(tf / burst, 4), "frac_sustained": round(tf / sustained, 4),
                          "operands": "bf16 (f32 accumulate in TMEM)"})
         del pool

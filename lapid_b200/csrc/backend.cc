@@ -351,7 +351,8 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
             if (tiles > p.scratch) p.scratch = tiles;
         }
     } else {
-        p.tc = !dev.gemm_f32 && l.b_dtype == LAPID_B200_DTYPE_Q4_K && l.k % 256 == 0 && l.k >= 256;
+        p.tc = !dev.gemm_f32 && l.k % 256 == 0 && l.k >= 256 &&
+               (l.b_dtype == LAPID_B200_DTYPE_Q4_K || (l.b_dtype == LAPID_B200_DTYPE_Q6_K && (l.k / 256) % 8 == 0));
         if (p.tc) p.scratch = align_up(lb::qgemm_tc_scratch_bytes(p.rows, (uint32_t)l.k), 256);
     }
     return p;
@@ -520,7 +521,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             size_t off = 0;
             if (slot) off = slot->offset;
             else dev.ensure_scratch(p.scratch);
-            cuda_check(lb::launch_qgemm_tc(t, (char *)dev.scratch + off, dev.sm_count, dev.stream), "qgemm_tc launch");
+            cuda_check(lb::launch_qgemm_tc(l.b_dtype, t, (char *)dev.scratch + off, dev.sm_count, dev.stream), "qgemm_tc launch");
             dev.launches += 2;
             return;
         }

@@ -37,7 +37,7 @@ namespace tc {
 
 constexpr int TN = 128;            // weight rows per tile
 constexpr int KS = 64;             // k per stage
-constexpr int RAW_BYTES = TN * Q4K_BYTES;  // 18432
+constexpr int Q6K_BOX = 224;       // Q6_K: bytes staged per row and super-block (210 from a 2-byte aligned start, see below)
 constexpr int B_BYTES = TN * 128;  // bf16 weight tile of one stage
 constexpr int THREADS = 608;       // 19 warps
 constexpr int DEQ_WARPS = 16;      // two groups of eight: even and odd k-steps
@@ -47,11 +47,13 @@ constexpr uint32_t SPIN_LIMIT = 1u << 24;
 // MT activation rows x (NT * 128) weight rows per CTA. NT = 2 keeps two accumulators (all 512
 // columns of tensor memory at MT = 256) so that one activation tile feeds twice the weights: the
 // bf16 activation tile is the larger part of what an SM pulls from L2 per k-step.
-template <int MT, int NT> struct Cfg {
+template <int FMT, int MT, int NT> struct Cfg {
     static constexpr int STAGES = NT == 2 ? 2 : (MT == 256 ? 3 : 4);
     static constexpr int A_BYTES = MT * 128;
     static constexpr int W_BYTES = NT * B_BYTES;
     static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
+    static constexpr int ROW_BYTES = FMT == FMT_Q4K ? Q4K_BYTES : Q6K_BOX;  // packed bytes staged per row and super-block
+    static constexpr int RAW_BYTES = TN * ROW_BYTES;                         // one 128-row sub-tile: 18432 / 28672
     static constexpr int RAW = NT * RAW_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * RAW + 256 /*barriers*/ + 1024 /*alignment slack*/;
 };
@@ -94,6 +96,11 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t r;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
@@ -132,10 +139,11 @@ __device__ __forceinline__ void mma_commit(uint64_t *bar) {
 // f32 bits of (2^23 + byte `sel` of w): the byte planted in the mantissa by one PRMT
 __device__ __forceinline__ float biased(uint32_t w, uint32_t sel) { return __uint_as_float(__byte_perm(w, 0x4B000000u, sel)); }
 
-template <int MT, int NT>
+template <int FMT, int MT, int NT>
 __global__ void __launch_bounds__(THREADS, 1)
-qgemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, GemmTcArgs p) {
-    using C = Cfg<MT, NT>;
+qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, GemmTcArgs p) {
+    using C = Cfg<FMT, MT, NT>;
+    constexpr int RAW_BYTES = C::RAW_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *stage0 = smem;
@@ -193,7 +201,8 @@ qgemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 mbar_expect_tx(raw_full + r, C::RAW);
 #pragma unroll
                 for (int t = 0; t < NT; t++)
-                    tma_load_2d(raw0 + r * C::RAW + t * RAW_BYTES, &map_w, (int)(b * Q4K_BYTES), (int)(n0 + t * TN), raw_full + r);
+                    tma_load_2d(raw0 + r * C::RAW + t * RAW_BYTES, &map_w,
+                                FMT == FMT_Q4K ? (int)(b * Q4K_BYTES) : (int)((b * Q6K_BYTES) & ~15u), (int)(n0 + t * TN), raw_full + r);
             }
             if (!healthy && p.status) atomicOr(p.status, 32);
         }
@@ -230,6 +239,48 @@ qgemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         for (uint32_t ks = (NT == 2 ? 0 : grp); ks < ksteps && healthy; ks += (NT == 2 ? 1 : 2)) {
             const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
             const uint32_t b = ks >> 2, pp = ks & 3, r = b & 1, ur = b >> 1;
+            if constexpr (FMT == FMT_Q6K) {
+                // Q6_K (NT = 1): a super-block is ql[128] | qh[64] | int8 sc[16] | f16 d = 210 bytes, so it
+                // starts on a 2-byte boundary only; the copy starts at the 16-byte boundary below it and
+                // takes 224 bytes per row. 16 lanes share one weight row of the k-step: lane j expands the
+                // four weights 4j..4j+3 of its 64 (16-bit shared loads, conflict-free along the row), a
+                // warp does two rows per pass and 16 rows per k-step.
+                //   k-step pp of the block: half nh = pp >> 1 of the 256, nibble hi = pp & 1; the first 32
+                //   weights come from ql[64 nh + l], the second 32 from ql[64 nh + 32 + l]; the two high
+                //   bits from qh[32 nh + l] >> 2 * (2 hi + h); scale sc[8 nh + 2 (2 hi + h) + l / 16]
+                //   (crates/lapid-quant/src/kquant.rs:375-396). d * sc * (q - 32) is exact in f32.
+                if (pp < 2 && !mbar_wait(raw_full + r, ur & 1)) { healthy = false; break; }
+                if (!mbar_wait(empty + s, (u & 1) ^ 1)) { healthy = false; break; }
+                const uint32_t j = lane & 15, h = j >> 3, jj = j & 7, nh = pp >> 1, hi = pp & 1;
+                const uint32_t skew = (b * Q6K_BYTES) & 15u;
+                const uint64_t unbias32 = pack2(-8388640.0f, -8388640.0f);  // -(2^23 + 32)
+#pragma unroll 2
+                for (int pass = 0; pass < 8; pass++) {
+                    const int rw = 16 * dw + 2 * pass + (lane >> 4);
+                    const uint8_t *blk = raw0 + r * C::RAW + rw * Q6K_BOX + skew;
+                    const uint16_t *ql = (const uint16_t *)(blk + 64 * nh + 32 * h + 4 * jj);
+                    const uint16_t *qh = (const uint16_t *)(blk + 128 + 32 * nh + 4 * jj);
+                    const uint32_t wl = (uint32_t)ql[0] | ((uint32_t)ql[1] << 16), wh = (uint32_t)qh[0] | ((uint32_t)qh[1] << 16);
+                    const uint32_t q = ((wl >> (4 * hi)) & 0x0F0F0F0Fu) | (((wh >> (2 * (2 * hi + h))) & 0x03030303u) << 4);
+                    const float sc = (float)(int)*(const int8_t *)(blk + 192 + 8 * nh + 2 * (2 * hi + h) + (jj >> 2));
+                    const float sd = half_bits_to_float(*(const uint16_t *)(blk + 208)) * sc;
+                    const uint64_t sd2 = pack2(sd, sd);
+                    const uint64_t q01 = add2(pack2(biased(q, 0x7440u), biased(q, 0x7441u)), unbias32);
+                    const uint64_t q23 = add2(pack2(biased(q, 0x7442u), biased(q, 0x7443u)), unbias32);
+                    const uint32_t o0 = to_bf16x2(mul2(sd2, q01)), o1 = to_bf16x2(mul2(sd2, q23));
+                    uint8_t *dst = stage0 + s * C::STAGE_BYTES + rw * 128;
+                    const int chunk = (int)(j >> 1) ^ (rw & 7);
+                    *(uint2 *)(dst + 16 * chunk + 8 * (j & 1)) = make_uint2(o0, o1);
+                }
+                if (pp >= 2) {  // this warp's last read of the block's packed bytes
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(raw_empty + r);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_b + s);
+                continue;
+            }
             const uint8_t *blk = raw0 + r * C::RAW + sub * RAW_BYTES + row * Q4K_BYTES;
             if (NT == 2 ? pp == 0 : pp < 2) {  // first k-step of this thread in the block
                 if (!mbar_wait(raw_full + r, ur & 1)) { healthy = false; break; }
@@ -359,17 +410,17 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int MT, int NT>
+template <int FMT, int MT, int NT>
 static cudaError_t launch_mt(const GemmTcArgs &a, const CUtensorMap &mw, const CUtensorMap &ma, cudaStream_t stream) {
-    auto kern = qgemm_q4k_tc_kernel<MT, NT>;
+    auto kern = qgemm_tc_kernel<FMT, MT, NT>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MT, NT>::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<FMT, MT, NT>::SMEM);
         if (e != cudaSuccess) return e;
         configured = true;
     }
     dim3 grid((a.n + TN * NT - 1) / (TN * NT), (a.rows + MT - 1) / MT);
-    kern<<<grid, THREADS, Cfg<MT, NT>::SMEM, stream>>>(mw, ma, a);
+    kern<<<grid, THREADS, Cfg<FMT, MT, NT>::SMEM, stream>>>(mw, ma, a);
     return cudaGetLastError();
 }
 
@@ -379,12 +430,14 @@ static int g_tc_wide = -1;  // tuning: -1 choose, 0 never, 1 always use two accu
 void qgemm_tc_set_wide(int v) { g_tc_wide = v; }
 
 bool qgemm_tc_supported(int fmt, const GemmTcArgs &a) {
-    return fmt == FMT_Q4K && a.k % QK == 0 && a.k >= QK && a.rows >= 1 && ((uintptr_t)a.w & 15) == 0 && tc::encode_fn() != nullptr;
+    if (a.k % QK != 0 || a.k < QK || a.rows < 1 || ((uintptr_t)a.w & 15) != 0 || tc::encode_fn() == nullptr) return false;
+    // Q6_K: a row of the packed matrix must be a multiple of 16 bytes for the tensor map (K a multiple of 2048)
+    return fmt == FMT_Q4K || (fmt == FMT_Q6K && (a.k / QK) % 8 == 0);
 }
 
 size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t k) { return (size_t)rows * k * 2; }
 
-cudaError_t launch_qgemm_tc(const GemmTcArgs &a, void *a_bf16_scratch, int sm_count, cudaStream_t stream) {
+cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, int sm_count, cudaStream_t stream) {
     using namespace tc;
     if (a.rows == 0 || a.n == 0) return cudaSuccess;
     EncodeTiledFn enc = encode_fn();
@@ -398,10 +451,11 @@ cudaError_t launch_qgemm_tc(const GemmTcArgs &a, void *a_bf16_scratch, int sm_co
     if (ce != cudaSuccess) return ce;
 
     CUtensorMap mw, ma;
-    {   // packed weights as bytes: [n rows][row_bytes], box = one 144-byte block of 128 rows
-        cuuint64_t dims[2] = {(cuuint64_t)(a.k / QK) * Q4K_BYTES, a.n};
-        cuuint64_t strides[1] = {(cuuint64_t)(a.k / QK) * Q4K_BYTES};
-        cuuint32_t box[2] = {Q4K_BYTES, TN};
+    {   // packed weights as bytes: [n rows][row_bytes], box = one 144-byte block (Q6_K: 224 bytes around one) of 128 rows
+        const uint32_t blk_bytes = fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES;
+        cuuint64_t dims[2] = {(cuuint64_t)(a.k / QK) * blk_bytes, a.n};
+        cuuint64_t strides[1] = {(cuuint64_t)(a.k / QK) * blk_bytes};
+        cuuint32_t box[2] = {fmt == FMT_Q4K ? (cuuint32_t)Q4K_BYTES : (cuuint32_t)Q6K_BOX, TN};
         cuuint32_t es[2] = {1, 1};
         if (enc(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)a.w, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -419,6 +473,13 @@ cudaError_t launch_qgemm_tc(const GemmTcArgs &a, void *a_bf16_scratch, int sm_co
     // One or two accumulators per CTA at MT = 256: the 256x256 tile halves the activation traffic
     // but there are half as many tiles; take the shape with the shorter modelled time (waves of
     // tiles over the SMs times the measured cost of a k-step of each shape).
+    if (fmt == FMT_Q6K) {  // the larger staged blocks leave room for one accumulator tile only
+        switch (mt) {
+            case 64: return launch_mt<FMT_Q6K, 64, 1>(a, mw, ma, stream);
+            case 128: return launch_mt<FMT_Q6K, 128, 1>(a, mw, ma, stream);
+            default: return launch_mt<FMT_Q6K, 256, 1>(a, mw, ma, stream);
+        }
+    }
     bool wide = a.rows > 128 && a.n >= 2 * TN;
     if (wide) {
         const uint64_t mt_tiles = (a.rows + 255) / 256;
@@ -428,9 +489,9 @@ cudaError_t launch_qgemm_tc(const GemmTcArgs &a, void *a_bf16_scratch, int sm_co
     }
     if (g_tc_wide >= 0) wide = g_tc_wide != 0;
     switch (mt) {
-        case 64: return launch_mt<64, 1>(a, mw, ma, stream);
-        case 128: return launch_mt<128, 1>(a, mw, ma, stream);
-        default: return wide ? launch_mt<256, 2>(a, mw, ma, stream) : launch_mt<256, 1>(a, mw, ma, stream);
+        case 64: return launch_mt<FMT_Q4K, 64, 1>(a, mw, ma, stream);
+        case 128: return launch_mt<FMT_Q4K, 128, 1>(a, mw, ma, stream);
+        default: return wide ? launch_mt<FMT_Q4K, 256, 2>(a, mw, ma, stream) : launch_mt<FMT_Q4K, 256, 1>(a, mw, ma, stream);
     }
 }
 

@@ -321,24 +321,32 @@ def bf16_round(x):
     return u.astype(np.uint32).view(np.float32)
 
 
-def test_gemm_tensor_core_q4k(be, oracle):
-    """bf16 tensor-core prefill: stated bounds vs lapid-cpu's f32 path are rel_l2 <= 4e-3 and
-    max_rel <= 2e-2 (both operands rounded to bf16, 2^-9 each; the reference allows 2e-3 for its
-    f16 tensor-core kernel, crates/lapid-cuda/src/kquant_tests.rs:191-192). Against the same
-    product computed from bf16-rounded operands the result must agree to summation-order noise."""
+@pytest.mark.parametrize("fmt,ofmt", [(lp.DType.Q4K, O.Q4_K), (lp.DType.Q6K, O.Q6_K)])
+def test_gemm_tensor_core(be, oracle, fmt, ofmt):
+    """bf16 tensor-core prefill (Q4_K; Q6_K when K is a multiple of 2048): stated bounds vs lapid-cpu's
+    f32 path are rel_l2 <= 4e-3 and max_rel <= 2e-2 (both operands rounded to bf16, 2^-9 each; the
+    reference allows 2e-3 for its f16 tensor-core kernel, crates/lapid-cuda/src/kquant_tests.rs:191-192).
+    Against the same product computed from bf16-rounded operands the result must agree to
+    summation-order noise."""
     seed = 90
-    for (batch, m, n, k, pad, epi) in [(1, 64, 256, 512, 0, False), (1, 20, 45, 256, 3, False), (1, 130, 70, 512, 0, True),
-                                       (1, 33, 300, 1024, 0, False), (2, 137, 300, 2048, 8, True), (1, 9, 128, 256, 0, False),
-                                       (1, 512, 1024, 4096, 0, False), (1, 300, 130, 14336, 0, False)]:
+    q4 = [(1, 64, 256, 512, 0, False), (1, 20, 45, 256, 3, False), (1, 130, 70, 512, 0, True),
+          (1, 33, 300, 1024, 0, False), (2, 137, 300, 2048, 8, True), (1, 9, 128, 256, 0, False),
+          (1, 512, 1024, 4096, 0, False), (1, 300, 130, 14336, 0, False)]
+    q6 = [(1, 64, 256, 2048, 0, False), (1, 20, 45, 2048, 3, False), (1, 130, 70, 4096, 0, True),
+          (2, 137, 300, 2048, 8, True), (1, 9, 128, 2048, 0, False), (1, 512, 1024, 4096, 0, False),
+          (1, 300, 130, 14336, 0, False), (1, 257, 129, 6144, 0, False)]
+    for (batch, m, n, k, pad, epi) in (q4 if fmt == lp.DType.Q4K else q6):
         seed += 1
         big = n * k > 200000
         w = O.normal(seed, n * k, 0.02) if big else rnd(n * k, seed)
-        qb = oracle.quantize(O.Q4_K, w, n, k)
+        qb = oracle.quantize(ofmt, w, n, k)
         rs = k + pad
         a = O.normal(seed + 7, batch * m * rs) if big else rnd(batch * m * rs, seed + 7)
         bias = rnd(n, seed + 9) if epi else None
-        got = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, batch=batch, a_row_stride=rs, bias=bias).reshape(batch * m, n)
-        deq = oracle.dequantize(O.Q4_K, qb, n, k)
+        be.take_launch_count()
+        got = run_matmul(be, fmt, a, qb, m, n, k, batch=batch, a_row_stride=rs, bias=bias).reshape(batch * m, n)
+        assert be.take_launch_count() == 2   # bf16 copy of the activations + the tensor-core kernel
+        deq = oracle.dequantize(ofmt, qb, n, k)
         av = a.reshape(batch * m, rs)[:, :k]
         b64 = bias.astype(np.float64) if epi else 0.0
         exact = av.astype(np.float64) @ deq.astype(np.float64).T + b64
@@ -348,9 +356,9 @@ def test_gemm_tensor_core_q4k(be, oracle):
         assert rel_l2(got, rounded) <= 2e-5, (m, n, k, rel_l2(got, rounded))
     if True:  # the exact path still answers for the same launch when asked
         be.set_option("gemm", "f32")
-        got = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, batch=batch, a_row_stride=rs)
+        got = run_matmul(be, fmt, a, qb, m, n, k, batch=batch, a_row_stride=rs)
         be.set_option("gemm", "tc")
-        want, _ = oracle.matmul(O.Q4_K, a, qb, n, k, batch=batch, m=m, a_view=(0, m * rs, rs))
+        want, _ = oracle.matmul(ofmt, a, qb, n, k, batch=batch, m=m, a_view=(0, m * rs, rs), fma=True)
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
