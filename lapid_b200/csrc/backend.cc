@@ -273,7 +273,8 @@ struct PendingGroup {
             if (r.hits(out)) return false;
         g.item[g.count] = a;
         g.count++;
-        bool fits = md == 2 ? lb::qgemv_q4k_mma_group_fits(g) : lb::qgemv_kq_group_smem(f, g) <= 227 * 1024;
+        bool fits = md != 2 ? lb::qgemv_kq_group_smem(f, g) <= 227 * 1024 - 256
+                            : f == LAPID_B200_DTYPE_Q6_K ? lb::qgemv_q6k_mma_group_fits(g) : lb::qgemv_q4k_mma_group_fits(g);
         g.count--;
         return fits;
     }
@@ -292,7 +293,8 @@ struct PendingGroup {
         reads.clear();
         lb::GemvGroup out = g;
         out.count = count;
-        if (mode == 2) cuda_check(lb::launch_qgemv_q4k_mma(out, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        if (mode == 2 && fmt == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(out, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        else if (mode == 2) cuda_check(lb::launch_qgemv_q4k_mma(out, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
         else cuda_check(lb::launch_qgemv_kq_group(fmt, out, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
         dev.launches++;
     }
@@ -344,8 +346,10 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
         p.scratch = qa + 2 * sc > rec ? qa + 2 * sc : rec;
         p.fast = dev.gemv_fast && lb::qgemv_kq_fast_shape_ok(l.b_dtype, p.rows, (uint32_t)l.k);
         p.fast_i8 = dev.gemv_fast && l.b_dtype == LAPID_B200_DTYPE_INT8 && lb::qgemv_i8_fast_shape_ok(p.rows, (uint32_t)l.k);
-        p.mma = dev.gemv_fast && dev.gemv_mma_rows > 0 && p.rows >= dev.gemv_mma_rows && l.b_dtype == LAPID_B200_DTYPE_Q4_K &&
-                lb::qgemv_q4k_mma_shape_ok(p.rows, (uint32_t)l.k);
+        // (Q6_K pays more per weight for unpacking: its tensor-core kernel wins one row later than Q4_K's)
+        p.mma = dev.gemv_fast && dev.gemv_mma_rows > 0 &&
+                ((l.b_dtype == LAPID_B200_DTYPE_Q4_K && p.rows >= dev.gemv_mma_rows && lb::qgemv_q4k_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
+                 (l.b_dtype == LAPID_B200_DTYPE_Q6_K && p.rows > dev.gemv_mma_rows && lb::qgemv_q6k_mma_shape_ok(p.rows, (uint32_t)l.k)));
         if (p.mma) {
             size_t tiles = align_up(lb::qgemv_q4k_mma_act_bytes(p.rows, (uint32_t)l.k), 256);
             if (tiles > p.scratch) p.scratch = tiles;
@@ -489,7 +493,8 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             lb::GemvGroup one{};
             one.count = 1;
             one.item[0] = g;
-            cuda_check(lb::launch_qgemv_q4k_mma(one, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+            if (l.b_dtype == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(one, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+            else cuda_check(lb::launch_qgemv_q4k_mma(one, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
         } else if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
         else if (p.fast_i8 && ((uintptr_t)g.w & 15) == 0) cuda_check(lb::launch_qgemv_i8_fast(g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
         else cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");

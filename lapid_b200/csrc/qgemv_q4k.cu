@@ -408,7 +408,7 @@ bool qgemv_kq_fast_shape_ok(int fmt, uint32_t rows, uint32_t k) {
     if (fmt == FMT_Q6K && (k / QK) % 8 != 0) return false;
     const size_t warps = rows <= 2 ? 4 : 8;
     const size_t stage = 32 * (size_t)(fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
-    return BAR_BYTES + warps * 2 * stage + (size_t)rows * (k / QK) * REC <= 227 * 1024;
+    return BAR_BYTES + warps * 2 * stage + (size_t)rows * (k / QK) * REC <= 227 * 1024 - 256;
 }
 
 bool qgemv_kq_fast_supported(int fmt, const GemvArgs &a) {

@@ -373,12 +373,12 @@ static void plan_acts(GemvGroup &g) {
 }
 
 static int pick_config(size_t act_bytes) {
-    if (g_force_config >= 0) return fixed_smem(CONFIGS[g_force_config]) + act_bytes <= 227 * 1024 ? g_force_config : -1;
+    if (g_force_config >= 0) return fixed_smem(CONFIGS[g_force_config]) + act_bytes <= 227 * 1024 - 256 ? g_force_config : -1;
     // small activation tiles: three of the small CTAs per SM beat one large one (more tiles in
     // flight, shorter barriers); otherwise the largest layout that fits
     if (3 * (fixed_smem(CONFIGS[2]) + act_bytes + 1024) <= 227 * 1024) return 2;
     for (int i = 0; i < (int)(sizeof(CONFIGS) / sizeof(CONFIGS[0])); i++)
-        if (fixed_smem(CONFIGS[i]) + act_bytes <= 227 * 1024) return i;
+        if (fixed_smem(CONFIGS[i]) + act_bytes <= 227 * 1024 - 256) return i;
     return -1;
 }
 

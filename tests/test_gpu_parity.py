@@ -218,6 +218,30 @@ def test_gemv_q4k_tensor_core_decode_kernel(be, oracle, config):
         be.set_option("gemv_mma_config", "-1")
 
 
+def test_gemv_q6k_tensor_core_decode_kernel(be, oracle):
+    """The Q6_K int8 tensor-core decode kernel (2..8 rows, K a multiple of 2048) against the oracle and
+    against the dp4a kernel: ragged n, every row count, bias, and the 2-byte block alignment cases
+    (every block of a row starts at a different offset from a 16-byte boundary)."""
+    try:
+        seed = 950
+        for (m, n, k, bias) in [(2, 130, 2048, False), (3, 77, 2048, True), (4, 513, 4096, False), (5, 100, 6144, False),
+                                (6, 1, 2048, False), (7, 33, 14336, True), (8, 300, 4096, False), (8, 16, 14336, False)]:
+            seed += 1
+            w = O.normal(seed, n * k, 0.05)
+            qb = oracle.quantize(O.Q6_K, w, n, k)
+            a = O.normal(seed + 50, m * k)
+            bv = O.normal(seed + 70, n) if bias else None
+            want, _ = oracle.matmul(O.Q6_K, a, qb, n, k, m=m, bias=bv)
+            be.set_option("gemv_mma_rows", "1")   # Q6_K takes the kernel from one row above the option
+            got = run_matmul(be, lp.DType.Q6K, a, qb, m, n, k, bias=bv)
+            be.set_option("gemv_mma_rows", "0")
+            ref = run_matmul(be, lp.DType.Q6K, a, qb, m, n, k, bias=bv)
+            assert max_rel(got, want) <= 2e-5, (m, n, k)
+            assert max_rel(got, ref) <= 2e-5, (m, n, k)
+    finally:
+        be.set_option("gemv_mma_rows", "2")
+
+
 def test_gemv_int8_k_not_multiple_of_256(be, oracle):
     for (m, n, k) in [(2, 40, 96), (1, 7, 32), (4, 33, 2080)]:
         w = O.normal(3, n * k, 0.1)
