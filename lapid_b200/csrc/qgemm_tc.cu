@@ -28,6 +28,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstring>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -191,6 +193,36 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             }
             if (!healthy && p.status) atomicOr(p.status, 2);
         }
+    } else if (warp == 18 && FMT == FMT_Q6K && ((nblk * Q6K_BYTES) & 15u) != 0) {
+        // ---------------- packed Q6_K weights whose rows are not a multiple of 16 bytes (K not a
+        // multiple of 2048, e.g. the K/8 shard of a row-parallel projection): no tensor map can
+        // describe them, so every lane copies rows of the tile with the plain bulk copy, each from
+        // the 16-byte boundary below its block (the consumers compute the same per-row offset)
+        const uint32_t rows_valid = min((uint32_t)TN, p.n > n0 ? p.n - n0 : 0u);
+        const uint64_t pitch = (uint64_t)nblk * Q6K_BYTES;
+        const uint64_t end16 = ((uint64_t)(uintptr_t)p.w + (uint64_t)p.n * pitch + 15) & ~(uint64_t)15;  // never read past the matrix's last 16-byte line
+        auto copy_of = [&](uint32_t rr, uint32_t b, uint64_t &src) -> uint32_t {
+            src = ((uint64_t)(uintptr_t)p.w + (uint64_t)(n0 + rr) * pitch + (uint64_t)b * Q6K_BYTES) & ~(uint64_t)15;
+            return (uint32_t)min((uint64_t)Q6K_BOX, end16 - src);
+        };
+        for (uint32_t b = 0; b < nblk && healthy; b++) {
+            const uint32_t r = b & 1, ur = b >> 1;
+            if (!mbar_wait(raw_empty + r, (ur & 1) ^ 1, 64)) { healthy = false; break; }
+            if (lane == 0 && rows_valid) {
+                uint64_t src;
+                mbar_expect_tx(raw_full + r, (rows_valid - 1) * Q6K_BOX + copy_of(rows_valid - 1, b, src));  // only the last row can be short
+            }
+            __syncwarp();
+            for (uint32_t rr = lane; rr < rows_valid; rr += 32) {
+                uint64_t src;
+                const uint32_t bytes = copy_of(rr, b, src);
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 s32(raw0 + r * C::RAW + rr * Q6K_BOX)),
+                             "l"(src), "r"(bytes), "r"(s32(raw_full + r))
+                             : "memory");
+            }
+        }
+        if (!healthy && lane == 0 && p.status) atomicOr(p.status, 32);
     } else if (warp == 18) {
         // ---------------- TMA producer, packed weights: one super-block of every row of the tile
         // per copy, a whole super-block (four k-steps) ahead of the dequantizing warps
@@ -252,11 +284,14 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 if (pp < 2 && !mbar_wait(raw_full + r, ur & 1)) { healthy = false; break; }
                 if (!mbar_wait(empty + s, (u & 1) ^ 1)) { healthy = false; break; }
                 const uint32_t j = lane & 15, h = j >> 3, jj = j & 7, nh = pp >> 1, hi = pp & 1;
-                const uint32_t skew = (b * Q6K_BYTES) & 15u;
+                const uint64_t pitch = (uint64_t)nblk * Q6K_BYTES, wbase = (uint64_t)(uintptr_t)p.w + (uint64_t)b * Q6K_BYTES;
                 const uint64_t unbias32 = pack2(-8388640.0f, -8388640.0f);  // -(2^23 + 32)
 #pragma unroll 2
                 for (int pass = 0; pass < 8; pass++) {
                     const int rw = 16 * dw + 2 * pass + (lane >> 4);
+                    // where the block starts inside its 224 staged bytes: the distance of its address from
+                    // the 16-byte boundary below it (the same for every row when the row pitch is a multiple of 16)
+                    const uint32_t skew = (uint32_t)((wbase + (uint64_t)(n0 + rw) * pitch) & 15u);
                     const uint8_t *blk = raw0 + r * C::RAW + rw * Q6K_BOX + skew;
                     const uint16_t *ql = (const uint16_t *)(blk + 64 * nh + 32 * h + 4 * jj);
                     const uint16_t *qh = (const uint16_t *)(blk + 128 + 32 * nh + 4 * jj);
@@ -431,8 +466,7 @@ void qgemm_tc_set_wide(int v) { g_tc_wide = v; }
 
 bool qgemm_tc_supported(int fmt, const GemmTcArgs &a) {
     if (a.k % QK != 0 || a.k < QK || a.rows < 1 || ((uintptr_t)a.w & 15) != 0 || tc::encode_fn() == nullptr) return false;
-    // Q6_K: a row of the packed matrix must be a multiple of 16 bytes for the tensor map (K a multiple of 2048)
-    return fmt == FMT_Q4K || (fmt == FMT_Q6K && (a.k / QK) % 8 == 0);
+    return fmt == FMT_Q4K || fmt == FMT_Q6K;
 }
 
 size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t k) { return (size_t)rows * k * 2; }
@@ -457,9 +491,13 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
         cuuint64_t strides[1] = {(cuuint64_t)(a.k / QK) * blk_bytes};
         cuuint32_t box[2] = {fmt == FMT_Q4K ? (cuuint32_t)Q4K_BYTES : (cuuint32_t)Q6K_BOX, TN};
         cuuint32_t es[2] = {1, 1};
-        if (enc(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)a.w, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        if (strides[0] % 16 != 0) {
+            // Q6_K with K not a multiple of 2048: no tensor map for the weights (the kernel copies rows itself)
+            std::memset(&mw, 0, sizeof(mw));
+        } else if (enc(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)a.w, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
             return cudaErrorInvalidValue;
+        }
     }
     {   // bf16 activations [rows][k], box = 64 k (128 bytes, swizzled) x MT rows
         cuuint64_t dims[2] = {a.k, a.rows};

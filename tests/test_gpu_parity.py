@@ -358,7 +358,9 @@ def test_gemm_tensor_core(be, oracle, fmt, ofmt):
           (1, 512, 1024, 4096, 0, False), (1, 300, 130, 14336, 0, False)]
     q6 = [(1, 64, 256, 2048, 0, False), (1, 20, 45, 2048, 3, False), (1, 130, 70, 4096, 0, True),
           (2, 137, 300, 2048, 8, True), (1, 9, 128, 2048, 0, False), (1, 512, 1024, 4096, 0, False),
-          (1, 300, 130, 14336, 0, False), (1, 257, 129, 6144, 0, False)]
+          (1, 300, 130, 14336, 0, False), (1, 257, 129, 6144, 0, False),
+          # K not a multiple of 2048: rows are not 16-byte multiples, the kernel copies them one by one
+          (1, 64, 256, 512, 0, False), (1, 33, 300, 1024, 0, True), (1, 140, 131, 3584, 0, False), (1, 9, 5, 256, 0, False)]
     for (batch, m, n, k, pad, epi) in (q4 if fmt == lp.DType.Q4K else q6):
         seed += 1
         big = n * k > 200000
