@@ -104,7 +104,7 @@ void qgemv_q4k_mma_set_config(int index);  // -1 = pick by shared-memory fit
 bool qgemv_q6k_mma_shape_ok(uint32_t rows, uint32_t k);
 bool qgemv_q6k_mma_group_fits(GemvGroup &group);
 cudaError_t launch_qgemv_q6k_mma(GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream);
-bool qgemv_kq_fast_supported(int fmt, const GemvArgs &args);  // Q4_K, and Q6_K when K % 2048 == 0
+bool qgemv_kq_fast_supported(int fmt, const GemvArgs &args);  // Q4_K and Q6_K, K % 256 == 0
 bool qgemv_kq_fast_shape_ok(int fmt, uint32_t rows, uint32_t k);  // same, without the pointer checks
 cudaError_t launch_qgemv_kq_fast(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 void qgemv_q4k_fast_set_cta_cap(int cap);

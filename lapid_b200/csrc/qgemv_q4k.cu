@@ -30,7 +30,10 @@ namespace lb {
 
 template <int FMT> struct Blk {
     static constexpr int BYTES = FMT == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES;
-    static constexpr int STAGE = 32 * BYTES;  // 4608 / 6720: one bulk copy, a multiple of 16 bytes
+    // 32 blocks by one bulk copy. Q4_K: 4608 bytes, always 16-byte aligned. Q6_K: 6720 bytes that may
+    // start anywhere on a 2-byte boundary: the copy starts at the 16-byte boundary below and is up to
+    // 16 bytes longer; the consumers add the same offset.
+    static constexpr int STAGE = FMT == FMT_Q4K ? 32 * BYTES : 32 * BYTES + 16;
 };
 constexpr int BAR_BYTES = 256;  // warps * STAGES * 8 <= 256
 
@@ -186,8 +189,11 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
                 first = row0 * nblk + pit * 32;
                 count = min(32u, nblk - pit * 32);
             }
-            mbar_expect_tx(bars + pslot, count * BB);
-            bulk_g2s(ring + (size_t)pslot * STAGE_BYTES, grp.item[item].w + (uint64_t)first * BB, count * BB, bars + pslot);
+            const uint8_t *src = grp.item[item].w + (uint64_t)first * BB;
+            const uint32_t skew = (uint32_t)((uintptr_t)src & 15u);  // 0 for Q4_K
+            const uint32_t bytes = (skew + count * BB + 15u) & ~15u;
+            mbar_expect_tx(bars + pslot, bytes);
+            bulk_g2s(ring + (size_t)pslot * STAGE_BYTES, src - skew, bytes, bars + pslot);
         }
         pslot ^= 1;
         if (++pit == iters) {
@@ -236,7 +242,10 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             }
             const uint32_t b = it * G + gl;
             if (healthy && row < n && b < nblk && gl < nblk) {
-                const uint8_t *blk = ring + (size_t)cslot * STAGE_BYTES + (size_t)(iters == 1 ? sub * nblk + gl : gl) * BB;
+                // the stage starts at the 16-byte boundary below its first block (Q6_K; see Blk)
+                const uint32_t first_blk = iters == 1 ? local * RPW * nblk : local * RPW * nblk + it * 32;
+                const uint32_t skew = FMT == FMT_Q4K ? 0u : (uint32_t)(((uintptr_t)p.w + (uint64_t)first_blk * BB) & 15u);
+                const uint8_t *blk = ring + (size_t)cslot * STAGE_BYTES + skew + (size_t)(iters == 1 ? sub * nblk + gl : gl) * BB;
                 if constexpr (FMT == FMT_Q4K) {
                     const uint4 h = *(const uint4 *)blk;
                     const float d = half_bits_to_float(h.x & 0xffff), dmin = half_bits_to_float(h.x >> 16);
@@ -399,15 +408,12 @@ template <int FMT, int M> static cudaError_t launch_fast_g(GemvGroup &a, int sm,
     return launch_fast<FMT, M, 32>(a, sm, pdl, s);
 }
 
-// Q6_K stages must start on a 16-byte boundary for the bulk copy: 8 blocks = 1680 bytes, so the
-// fast path takes K that are multiples of 2048 (every model shape in practice); other K use the
-// generic kernel.
+// Any K that is a multiple of 256, as long as the rings and the activation records fit in shared memory.
 bool qgemv_kq_fast_shape_ok(int fmt, uint32_t rows, uint32_t k) {
     if (fmt != FMT_Q4K && fmt != FMT_Q6K) return false;
     if (rows < 1 || rows > 8 || k % QK != 0 || k < QK) return false;
-    if (fmt == FMT_Q6K && (k / QK) % 8 != 0) return false;
     const size_t warps = rows <= 2 ? 4 : 8;
-    const size_t stage = 32 * (size_t)(fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+    const size_t stage = fmt == FMT_Q4K ? Blk<FMT_Q4K>::STAGE : Blk<FMT_Q6K>::STAGE;
     return BAR_BYTES + warps * 2 * stage + (size_t)rows * (k / QK) * REC <= 227 * 1024 - 256;
 }
 
@@ -453,7 +459,7 @@ static void plan_group_acts(GemvGroup &g) {
 size_t qgemv_kq_group_smem(int fmt, GemvGroup &g) {
     plan_group_acts(g);
     const size_t warps = g.item[0].rows <= 2 ? 4 : 8;
-    const size_t stage = 32 * (size_t)(fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+    const size_t stage = fmt == FMT_Q4K ? Blk<FMT_Q4K>::STAGE : Blk<FMT_Q6K>::STAGE;
     return BAR_BYTES + warps * 2 * stage + g.act_bytes;
 }
 

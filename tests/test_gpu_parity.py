@@ -242,6 +242,23 @@ def test_gemv_q6k_tensor_core_decode_kernel(be, oracle):
         be.set_option("gemv_mma_rows", "2")
 
 
+def test_gemv_q6k_any_block_count(be, oracle):
+    """Q6_K rows whose byte length is not a multiple of 16 (K not a multiple of 2048: every stage of
+    the bulk-copy ring then starts at a different offset from a 16-byte boundary)."""
+    seed = 980
+    for (m, n, k) in [(1, 77, 256), (1, 300, 3584), (2, 65, 768), (4, 130, 7168), (8, 33, 3584), (1, 9, 9216), (3, 258, 1280)]:
+        seed += 1
+        qb = oracle.quantize(O.Q6_K, O.normal(seed, n * k, 0.05), n, k)
+        a = O.normal(seed + 50, m * k)
+        want, _ = oracle.matmul(O.Q6_K, a, qb, n, k, m=m)
+        got = run_matmul(be, lp.DType.Q6K, a, qb, m, n, k)
+        assert max_rel(got, want) <= 2e-5, (m, n, k)
+        be.set_option("gemv", "generic")
+        ref = run_matmul(be, lp.DType.Q6K, a, qb, m, n, k)
+        be.set_option("gemv", "fast")
+        assert max_rel(got, ref) <= 2e-5, (m, n, k)
+
+
 def test_gemv_int8_k_not_multiple_of_256(be, oracle):
     for (m, n, k) in [(2, 40, 96), (1, 7, 32), (4, 33, 2080)]:
         w = O.normal(3, n * k, 0.1)
