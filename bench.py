@@ -429,7 +429,7 @@ def gemv_kernel_name(fmt: int, m: int) -> str:
         return "qgemv_q4k_mma_kernel" if m >= 2 else "qgemv_kq_fast_kernel<q4_k>"
     if fmt == 8:
         return "qgemv_q6k_mma_kernel" if m >= 3 else "qgemv_kq_fast_kernel<q6_k>"
-    return "qgemv_i8_fast_kernel"
+    return "qgemv_i8_mma_kernel" if m >= 2 else "qgemv_i8_fast_kernel"
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch / algorithmic bytes of that launch, from

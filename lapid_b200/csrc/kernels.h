@@ -100,6 +100,9 @@ size_t qgemv_q4k_mma_act_bytes(uint32_t rows, uint32_t k);
 bool qgemv_q4k_mma_group_fits(GemvGroup &group);
 cudaError_t launch_qgemv_q4k_mma(GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream);
 void qgemv_q4k_mma_set_config(int index);  // -1 = pick by shared-memory fit
+// Int8 planes on the same instruction (K a multiple of 512); same activation tiles.
+bool qgemv_i8_mma_shape_ok(uint32_t rows, uint32_t k);
+cudaError_t launch_qgemv_i8_mma(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // Its Q6_K sibling (K a multiple of 2048); same activation tiles.
 bool qgemv_q6k_mma_shape_ok(uint32_t rows, uint32_t k);
 bool qgemv_q6k_mma_group_fits(GemvGroup &group);
