@@ -50,7 +50,7 @@ constexpr uint32_t SPIN_LIMIT = 1u << 24;
 // columns of tensor memory at MT = 256) so that one activation tile feeds twice the weights: the
 // bf16 activation tile is the larger part of what an SM pulls from L2 per k-step.
 template <int FMT, int MT, int NT> struct Cfg {
-    static constexpr int STAGES = NT == 2 ? 2 : (MT == 256 ? 3 : 4);
+    static constexpr int STAGES = (NT == 2 || MT == 512) ? 2 : (MT == 256 ? 3 : 4);
     static constexpr int A_BYTES = MT * 128;
     static constexpr int W_BYTES = NT * B_BYTES;
     static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
@@ -189,7 +189,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
                 if (!mbar_wait(empty + s, (u & 1) ^ 1, 64)) { healthy = false; break; }
                 mbar_expect_tx(full_a + s, C::A_BYTES);
-                tma_load_2d(stage0 + s * C::STAGE_BYTES + C::W_BYTES, &map_a, (int)(ks * KS), (int)m0, full_a + s);
+#pragma unroll
+                for (int h = 0; h < (MT + 255) / 256; h++)  // a box holds at most 256 rows
+                    tma_load_2d(stage0 + s * C::STAGE_BYTES + C::W_BYTES + h * 256 * 128, &map_a, (int)(ks * KS), (int)(m0 + 256 * h),
+                                full_a + s);
             }
             if (!healthy && p.status) atomicOr(p.status, 2);
         }
@@ -242,7 +245,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // ---------------- MMA issuer
         if (lane == 0) {
             // D f32, A and B bf16, both K-major, M = 128, N = MT
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
+            constexpr int MMA_N = MT > 256 ? 256 : MT;  // an instruction takes at most 256 columns: MT = 512 issues two
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MMA_N >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
             for (uint32_t ks = 0; ks < ksteps && healthy; ks++) {
                 const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
                 if (!mbar_wait(full_a + s, u & 1, 32) || !mbar_wait(full_b + s, u & 1, 32)) { healthy = false; break; }
@@ -252,8 +256,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 for (int t = 0; t < NT; t++)
 #pragma unroll
                     for (int kk = 0; kk < KS / 16; kk++)
-                        mma_bf16(tmem_base + t * MT, smem_desc(wt + t * B_BYTES + kk * 32), smem_desc(at + kk * 32), idesc,
-                                 (ks | kk) ? 1u : 0u);
+#pragma unroll
+                        for (int h = 0; h < MT / MMA_N; h++)
+                            mma_bf16(tmem_base + t * MT + h * MMA_N, smem_desc(wt + t * B_BYTES + kk * 32),
+                                     smem_desc(at + h * MMA_N * 128 + kk * 32), idesc, (ks | kk) ? 1u : 0u);
                 mma_commit(empty + s);  // the stage may be refilled once these MMAs have read it
             }
             mma_commit(acc_full);
@@ -462,7 +468,9 @@ static cudaError_t launch_mt(const GemmTcArgs &a, const CUtensorMap &mw, const C
 }  // namespace tc
 
 static int g_tc_wide = -1;  // tuning: -1 choose, 0 never, 1 always use two accumulators at MT = 256
+static int g_tc_tall = -1;  // tuning: -1 choose, 0 never, 1 always use 512-row activation tiles above 256 rows
 void qgemm_tc_set_wide(int v) { g_tc_wide = v; }
+void qgemm_tc_set_tall(int v) { g_tc_tall = v; }
 
 bool qgemm_tc_supported(int fmt, const GemmTcArgs &a) {
     if (a.k % QK != 0 || a.k < QK || a.rows < 1 || ((uintptr_t)a.w & 15) != 0 || tc::encode_fn() == nullptr) return false;
@@ -502,7 +510,7 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
     {   // bf16 activations [rows][k], box = 64 k (128 bytes, swizzled) x MT rows
         cuuint64_t dims[2] = {a.k, a.rows};
         cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};
-        cuuint32_t box[2] = {KS, mt};
+        cuuint32_t box[2] = {KS, mt > 256 ? 256u : mt};
         cuuint32_t es[2] = {1, 1};
         if (enc(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_bf16_scratch, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -511,6 +519,20 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
     // One or two accumulators per CTA at MT = 256: the 256x256 tile halves the activation traffic
     // but there are half as many tiles; take the shape with the shorter modelled time (waves of
     // tiles over the SMs times the measured cost of a k-step of each shape).
+    // 512 activation rows per CTA (all 512 columns of tensor memory for one 128-row weight tile): every
+    // dequantized weight feeds twice the tensor-core work of the 256-row tiles. A k-step of such a
+    // CTA measured 1.6x the time of a 256-row one, so it pays when it saves more than that in waves
+    // of tiles over the SMs. Q6_K only: for Q4_K the two-accumulator 256x256 tile is the better way
+    // to the same reuse (it also halves the activation traffic), measured faster in every case.
+    bool tall = false;
+    if (a.rows > 256 && fmt == FMT_Q6K) {
+        const uint64_t nt = (a.n + TN - 1) / TN;
+        const uint64_t w256 = (nt * ((a.rows + 255) / 256) + sm_count - 1) / sm_count;
+        const uint64_t w512 = (nt * ((a.rows + 511) / 512) + sm_count - 1) / sm_count;
+        tall = w512 * 16 < w256 * 10;
+    }
+    if (g_tc_tall >= 0) tall = g_tc_tall != 0 && a.rows > 256;
+    if (tall) return fmt == FMT_Q6K ? launch_mt<FMT_Q6K, 512, 1>(a, mw, ma, stream) : launch_mt<FMT_Q4K, 512, 1>(a, mw, ma, stream);
     if (fmt == FMT_Q6K) {  // the larger staged blocks leave room for one accumulator tile only
         switch (mt) {
             case 64: return launch_mt<FMT_Q6K, 64, 1>(a, mw, ma, stream);

@@ -384,8 +384,17 @@ def bf16_round(x):
     return u.astype(np.uint32).view(np.float32)
 
 
+@pytest.mark.parametrize("tall", ["-1", "1"])
 @pytest.mark.parametrize("fmt,ofmt", [(lp.DType.Q4K, O.Q4_K), (lp.DType.Q6K, O.Q6_K)])
-def test_gemm_tensor_core(be, oracle, fmt, ofmt):
+def test_gemm_tensor_core(be, oracle, fmt, ofmt, tall):
+    be.set_option("gemm_tall", tall)   # "1": 512 activation rows per CTA wherever a launch has more than 256 rows
+    try:
+        _gemm_tensor_core_cases(be, oracle, fmt, ofmt, tall == "1")
+    finally:
+        be.set_option("gemm_tall", "-1")
+
+
+def _gemm_tensor_core_cases(be, oracle, fmt, ofmt, tall_only):
     """bf16 tensor-core prefill (Q4_K; Q6_K when K is a multiple of 2048): stated bounds vs lapid-cpu's
     f32 path are rel_l2 <= 4e-3 and max_rel <= 2e-2 (both operands rounded to bf16, 2^-9 each; the
     reference allows 2e-3 for its f16 tensor-core kernel, crates/lapid-cuda/src/kquant_tests.rs:191-192).
@@ -394,7 +403,7 @@ def test_gemm_tensor_core(be, oracle, fmt, ofmt):
     seed = 90
     q4 = [(1, 64, 256, 512, 0, False), (1, 20, 45, 256, 3, False), (1, 130, 70, 512, 0, True),
           (1, 33, 300, 1024, 0, False), (2, 137, 300, 2048, 8, True), (1, 9, 128, 256, 0, False),
-          (1, 512, 1024, 4096, 0, False), (1, 300, 130, 14336, 0, False)]
+          (1, 512, 1024, 4096, 0, False), (1, 300, 130, 14336, 0, False), (1, 700, 200, 512, 0, True)]
     q6 = [(1, 64, 256, 2048, 0, False), (1, 20, 45, 2048, 3, False), (1, 130, 70, 4096, 0, True),
           (2, 137, 300, 2048, 8, True), (1, 9, 128, 2048, 0, False), (1, 512, 1024, 4096, 0, False),
           (1, 300, 130, 14336, 0, False), (1, 257, 129, 6144, 0, False),
@@ -402,6 +411,8 @@ def test_gemm_tensor_core(be, oracle, fmt, ofmt):
           (1, 64, 256, 512, 0, False), (1, 33, 300, 1024, 0, True), (1, 140, 131, 3584, 0, False), (1, 9, 5, 256, 0, False)]
     for (batch, m, n, k, pad, epi) in (q4 if fmt == lp.DType.Q4K else q6):
         seed += 1
+        if tall_only and batch * m <= 256:
+            continue
         big = n * k > 200000
         w = O.normal(seed, n * k, 0.02) if big else rnd(n * k, seed)
         qb = oracle.quantize(ofmt, w, n, k)
