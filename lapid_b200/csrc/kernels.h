@@ -79,6 +79,22 @@ cudaError_t qgemv_init();
 // Reads the activations as 336-byte records (ActQuantArgs::records) from args.qa.
 bool qgemv_q4k_fast_supported(const GemvArgs &args);
 cudaError_t launch_qgemv_q4k_fast(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+// The largest dynamic shared-memory size a kernel has been opted in to, per device of the process
+// (cudaFuncSetAttribute is a per-device setting). Used as a function-local static by the launchers.
+struct DynamicSmemOptIn {
+    size_t have[64] = {};
+    cudaError_t raise(const void *kernel, size_t bytes) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+        if (bytes <= have[dev]) return cudaSuccess;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e == cudaSuccess) have[dev] = bytes;
+        return e;
+    }
+};
+
 // Up to GEMV_GROUP_MAX independent projections with the same format, rows and k in one launch.
 constexpr int GEMV_GROUP_MAX = 6;
 template <int N> struct GemvGroupT {

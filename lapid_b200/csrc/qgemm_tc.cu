@@ -454,12 +454,8 @@ static EncodeTiledFn encode_fn() {
 template <int FMT, int MT, int NT>
 static cudaError_t launch_mt(const GemmTcArgs &a, const CUtensorMap &mw, const CUtensorMap &ma, cudaStream_t stream) {
     auto kern = qgemm_tc_kernel<FMT, MT, NT>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<FMT, MT, NT>::SMEM);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static DynamicSmemOptIn opted;
+    if (cudaError_t e = opted.raise((const void *)kern, Cfg<FMT, MT, NT>::SMEM); e != cudaSuccess) return e;
     dim3 grid((a.n + TN * NT - 1) / (TN * NT), (a.rows + MT - 1) / MT);
     kern<<<grid, THREADS, Cfg<FMT, MT, NT>::SMEM, stream>>>(mw, ma, a);
     return cudaGetLastError();

@@ -368,11 +368,11 @@ static cudaError_t launch_one(const GemvArgs &a, int sm_count, bool pdl, cudaStr
     constexpr size_t smem = (size_t)WARPS * STAGES * C * Geo<FMT>::SPAN;
     static_assert(smem <= 227 * 1024, "ring does not fit in shared memory");
     static int ctas_per_sm = 0;  // same for every device of the supported kind
+    static DynamicSmemOptIn opted;
+    if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
     if (ctas_per_sm == 0) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
         int occ = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, WARPS * 32, smem);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, WARPS * 32, smem);
         if (e != cudaSuccess) return e;
         ctas_per_sm = occ > 0 ? occ : 1;
     }

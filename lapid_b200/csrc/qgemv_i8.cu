@@ -153,13 +153,10 @@ template <int M> static cudaError_t launch_m(const GemvArgs &a, int sm_count, bo
     auto kern = qgemv_i8_fast_kernel<M>;
     constexpr int WARPS = Shape<M>::WARPS;
     const size_t smem = BAR_BYTES + (size_t)WARPS * 2 * STAGE + (size_t)a.rows * a.k + (size_t)a.rows * (a.k / GROUP) * 4;
-    static size_t configured = 0, occ_smem = 0;
+    static size_t occ_smem = 0;
     static int ctas_per_sm = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = smem;
-    }
+    static DynamicSmemOptIn opted;
+    if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
     if (ctas_per_sm == 0 || occ_smem != smem) {
         int occ = 0;
         cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, WARPS * 32, smem);

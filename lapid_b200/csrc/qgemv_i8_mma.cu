@@ -173,12 +173,8 @@ static size_t smem_bytes(int warps, uint32_t rows, uint32_t k) {
 template <int WARPS> static cudaError_t launch_w(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t stream) {
     auto kern = qgemv_i8_mma_kernel<WARPS>;
     const size_t smem = smem_bytes(WARPS, a.rows, a.k);
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = smem;
-    }
+    static DynamicSmemOptIn opted;
+    if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
     const uint32_t tasks = (a.n + 15) / 16;
     uint32_t per_sm = (uint32_t)((227 * 1024) / (smem + 1024));
     if (per_sm < 1) per_sm = 1;

@@ -346,12 +346,8 @@ static cudaError_t launch_fast_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cuda
         g.task_end[i] = tasks;
     }
     const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * Blk<FMT>::STAGE + g.act_bytes;
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = smem;
-    }
+    static DynamicSmemOptIn opted;
+    if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
     // resident CTAs per SM for this shared-memory size (a handful of sizes occur: remember them)
     static size_t occ_key[8];
     static int occ_val[8], occ_n = 0;

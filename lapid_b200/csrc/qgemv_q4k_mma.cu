@@ -446,12 +446,8 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cudaStrea
     }
     for (int i = g.count; i < NG; i++) maps.m[i] = maps.m[0];
     const size_t smem = fixed_smem(Config{WARPS, TILES}) + g.act_bytes;
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = smem;
-    }
+    static DynamicSmemOptIn opted;
+    if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
     const uint32_t per_sm = (uint32_t)((227 * 1024) / (smem + 1024));  // shared memory is what limits residency
     uint32_t grid = (uint32_t)sm_count * (per_sm ? per_sm : 1);
     if (grid > tasks) grid = tasks;

@@ -115,3 +115,31 @@ def test_two_gpu_layer_stack_matches_one_gpu(tmp_path, m, peer):
     diff = (sharded[n_o:] - single[n_o:]).astype(np.float64)
     assert np.sqrt((diff ** 2).sum() / (single[n_o:].astype(np.float64) ** 2).sum()) <= 1e-2
     assert max_rel(sharded[n_o:], single[n_o:]) <= 3e-2
+
+
+def test_two_devices_in_one_process():
+    """Per-device kernel settings (the dynamic shared-memory opt-in) are made on every device a
+    process uses: the same launches on GPU 0 and then GPU 1 of one process give the same bits."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import lapid_b200 as lp
+    from lapid_b200.backend import matmul_launch
+    from oracle import oracle as O
+    o = O.load()
+    outs = []
+    for ordinal in (0, 1):
+        be = lp.Backend(ordinal)
+        res = []
+        for fmt, ofmt in ((lp.DType.Q4K, O.Q4_K), (lp.DType.Q6K, O.Q6_K), (lp.DType.Int8, O.INT8)):
+            n, k = 300, 2048
+            qb = o.quantize(ofmt, O.normal(int(fmt), n * k, 0.05), n, k)
+            for m in (1, 4, 40):
+                a = O.normal(60 + m, m * k)
+                bufs = [be.upload(a), be.upload(qb), be.alloc(m * n * 4)]
+                be.execute([matmul_launch(fmt, m, n, k)], bufs)
+                res.append(bufs[2].download().view(np.float32).copy())
+        outs.append(res)
+        be.close()
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
