@@ -305,6 +305,23 @@ def test_config1_full_size_matvec(be, oracle, fmt, name):
     assert max_rel(got, want) <= 2e-5
 
 
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_config2_full_size_shapes(be, oracle, fmt, name):
+    """The benchmark's decode sweep at its full sizes -- the four Llama-3-8B-shaped projections,
+    M = 1 and 8 (dp4a and tensor-core decode kernels) -- against the oracle on the same seeded
+    inputs (W seed 100 + shape index, x seed 200 + M). The weights are quantized on the device
+    (byte-identical to the oracle's quantizer, see above and test_quantize_byte_exact)."""
+    for si, (n, k) in enumerate([(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]):
+        qb = quant.quantize(be, fmt, O.normal(100 + si, n * k, 0.02), n, k)
+        for m in (1, 8):
+            x = O.normal(200 + m, m * k)
+            want, path = oracle.matmul(int(fmt), x, qb, n, k, m=m)
+            assert path == "int8_act"
+            got = run_matmul(be, fmt, x, qb, m, n, k)
+            assert max_rel(got, want) <= 1e-3, (name, n, k, m)
+            assert max_rel(got, want) <= 2e-5, (name, n, k, m)
+
+
 def test_gemv_special_activations(be, oracle):
     n, k = 64, 512
     qb = oracle.quantize(O.Q4_K, O.normal(5, n * k, 0.02), n, k)
