@@ -455,6 +455,26 @@ def _gemm_tensor_core_cases(be, oracle, fmt, ofmt, tall_only):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("fmt", [lp.DType.Q4K, lp.DType.Q6K])
+def test_config3_full_size_prefill(be, fmt):
+    """The prefill benchmark's full sizes (M = 2048 and 64 on 14336 x 4096 and 4096 x 14336): the
+    tensor-core result against the exact-f32 kernel of the same library on the same inputs -- which is
+    bit-identical to the oracle wherever the oracle is run (test_gemm_f32_bit_exact_vs_oracle) -- within
+    the bound stated for bf16 operands."""
+    for si, (n, k) in enumerate([(14336, 4096), (4096, 14336)]):
+        qb = quant.quantize(be, fmt, O.normal(100 + si + 2, n * k, 0.02), n, k)
+        for m in (2048, 64):
+            a = O.normal(300 + m, m * k)
+            got = run_matmul(be, fmt, a, qb, m, n, k)
+            be.set_option("gemm", "f32")
+            try:
+                exact = run_matmul(be, fmt, a, qb, m, n, k)
+            finally:
+                be.set_option("gemm", "tc")
+            assert rel_l2(got, exact) <= 4e-3, (n, k, m, rel_l2(got, exact))
+            assert max_rel(got, exact) <= 2e-2, (n, k, m, max_rel(got, exact))
+
+
 def test_gemm_tensor_core_strided_output(be, oracle):
     k, n, off, batch, m = 256, 40, 7, 3, 30
     a = rnd(batch * m * k, 100)
