@@ -809,6 +809,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             lb::qgemv_q4k_fast_set_cta_cap(std::atoi(value));
         } else if (k == "gemm_wide") {
             lb::qgemm_tc_set_wide(std::atoi(value));
+        } else if (k == "gemm_pair") {
+            lb::qgemm_tc_set_pair(std::atoi(value));
         } else if (k == "gemm_tall") {
             lb::qgemm_tc_set_tall(std::atoi(value));
         } else if (k == "gemm") {

@@ -49,9 +49,12 @@ constexpr uint32_t SPIN_LIMIT = 1u << 24;
 // MT activation rows x (NT * 128) weight rows per CTA. NT = 2 keeps two accumulators (all 512
 // columns of tensor memory at MT = 256) so that one activation tile feeds twice the weights: the
 // bf16 activation tile is the larger part of what an SM pulls from L2 per k-step.
-template <int FMT, int MT, int NT> struct Cfg {
-    static constexpr int STAGES = (NT == 2 || MT == 512) ? 2 : (MT == 256 ? 3 : 4);
-    static constexpr int A_BYTES = MT * 128;
+// PAIR: two CTAs of a cluster run as one `cta_group::2` tensor-core unit: each dequantizes its own
+// 128*NT weight rows and loads only HALF of the activation tile (the instruction reads both CTAs'
+// halves), which halves the activation traffic from L2 and leaves room for a third stage.
+template <int FMT, int MT, int NT, bool PAIR = false> struct Cfg {
+    static constexpr int STAGES = PAIR ? 3 : ((NT == 2 || MT == 512) ? 2 : (MT == 256 ? 3 : 4));
+    static constexpr int A_BYTES = (PAIR ? MT / 2 : MT) * 128;
     static constexpr int W_BYTES = NT * B_BYTES;
     static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
     static constexpr int ROW_BYTES = FMT == FMT_Q4K ? Q4K_BYTES : Q6K_BOX;  // packed bytes staged per row and super-block
@@ -137,14 +140,52 @@ __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t da, uint64_t 
 __device__ __forceinline__ void mma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
 }
+// ---- the same for a pair of CTAs (`cta_group::2`); `cluster_addr` may name a barrier of either CTA
+__device__ __forceinline__ void mma_bf16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+// the shared::cluster address of `p` in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t cluster_addr_of(const void *p, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(s32(p)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// bounded wait with cluster-scope acquire: the arrival comes from the other CTA of the pair
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, uint32_t sleep_ns = 0) {
+    for (uint32_t spin = 0; spin < SPIN_LIMIT; spin++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(s32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (sleep_ns) __nanosleep(sleep_ns);
+    }
+    return false;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 // f32 bits of (2^23 + byte `sel` of w): the byte planted in the mantissa by one PRMT
 __device__ __forceinline__ float biased(uint32_t w, uint32_t sel) { return __uint_as_float(__byte_perm(w, 0x4B000000u, sel)); }
 
-template <int FMT, int MT, int NT>
+template <int FMT, int MT, int NT, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, GemmTcArgs p) {
-    using C = Cfg<FMT, MT, NT>;
+    using C = Cfg<FMT, MT, NT, PAIR>;
     constexpr int RAW_BYTES = C::RAW_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -154,6 +195,9 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     uint64_t *full_a = bars, *full_b = bars + C::STAGES, *empty = bars + 2 * C::STAGES;
     uint64_t *raw_full = bars + 3 * C::STAGES, *raw_empty = raw_full + 2, *acc_full = raw_full + 4;
     uint32_t *tmem_slot = (uint32_t *)(acc_full + 1);
+    uint64_t *peer_ready = acc_full + 2;  // PAIR, leader CTA: the other CTA's operands of a stage are in place
+    uint32_t cta_rank = 0;
+    if constexpr (PAIR) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta_rank));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n0 = blockIdx.x * (TN * NT), m0 = blockIdx.y * MT;
@@ -170,14 +214,22 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             mbar_init(raw_empty + r, DEQ_WARPS);
         }
         mbar_init(acc_full, 1);
+        if constexpr (PAIR)
+            for (int s = 0; s < C::STAGES; s++) mbar_init(peer_ready + s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"((uint32_t)(MT * NT)) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {  // the same warp of both CTAs: a pair-wide allocation of the same columns
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"((uint32_t)(MT * NT)) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"((uint32_t)(MT * NT)) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // both CTAs' barriers exist before either one signals the other
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     bool healthy = true;
@@ -189,10 +241,14 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
                 if (!mbar_wait(empty + s, (u & 1) ^ 1, 64)) { healthy = false; break; }
                 mbar_expect_tx(full_a + s, C::A_BYTES);
+                if constexpr (PAIR) {  // this CTA's half of the activation tile
+                    tma_load_2d(stage0 + s * C::STAGE_BYTES + C::W_BYTES, &map_a, (int)(ks * KS), (int)(m0 + (MT / 2) * cta_rank), full_a + s);
+                } else {
 #pragma unroll
-                for (int h = 0; h < (MT + 255) / 256; h++)  // a box holds at most 256 rows
-                    tma_load_2d(stage0 + s * C::STAGE_BYTES + C::W_BYTES + h * 256 * 128, &map_a, (int)(ks * KS), (int)(m0 + 256 * h),
-                                full_a + s);
+                    for (int h = 0; h < (MT + 255) / 256; h++)  // a box holds at most 256 rows
+                        tma_load_2d(stage0 + s * C::STAGE_BYTES + C::W_BYTES + h * 256 * 128, &map_a, (int)(ks * KS), (int)(m0 + 256 * h),
+                                    full_a + s);
+                }
             }
             if (!healthy && p.status) atomicOr(p.status, 2);
         }
@@ -240,6 +296,43 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                                 FMT == FMT_Q4K ? (int)(b * Q4K_BYTES) : (int)((b * Q6K_BYTES) & ~15u), (int)(n0 + t * TN), raw_full + r);
             }
             if (!healthy && p.status) atomicOr(p.status, 32);
+        }
+    } else if (warp == 1 && PAIR) {
+        // ---------------- MMA issuer of a CTA pair. The leader (rank 0) issues for both CTAs: M = 256
+        // (128 weight rows from each CTA's tile), N = MT (each CTA holds MT / 2 activation rows), the
+        // accumulators land in each CTA's own tensor memory. The other CTA's issuer warp only reports
+        // when its operands of a stage are in place. Completion is committed to both CTAs' barriers.
+        if (lane == 0) {
+            const uint32_t peer = cta_rank ^ 1;
+            if (cta_rank == 0) {
+                constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT >> 3) << 17) | ((uint32_t)((2 * TN) >> 4) << 24);
+                for (uint32_t ks = 0; ks < ksteps && healthy; ks++) {
+                    const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
+                    if (!mbar_wait(full_a + s, u & 1, 32) || !mbar_wait(full_b + s, u & 1, 32) || !mbar_wait_cluster(peer_ready + s, u & 1, 32)) {
+                        healthy = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t wt = s32(stage0 + s * C::STAGE_BYTES), at = wt + C::W_BYTES;
+#pragma unroll
+                    for (int t = 0; t < NT; t++)
+#pragma unroll
+                        for (int kk = 0; kk < KS / 16; kk++)
+                            mma_bf16_pair(tmem_base + t * MT, smem_desc(wt + t * B_BYTES + kk * 32), smem_desc(at + kk * 32), idesc, (ks | kk) ? 1u : 0u);
+                    mma_commit_pair(s32(empty + s));
+                    mma_commit_pair(cluster_addr_of(empty + s, peer));
+                }
+                mma_commit_pair(s32(acc_full));
+                mma_commit_pair(cluster_addr_of(acc_full, peer));
+                if (!healthy && p.status) atomicOr(p.status, 4);
+            } else {
+                for (uint32_t ks = 0; ks < ksteps && healthy; ks++) {
+                    const uint32_t s = ks % C::STAGES, u = ks / C::STAGES;
+                    if (!mbar_wait(full_a + s, u & 1, 32) || !mbar_wait(full_b + s, u & 1, 32)) { healthy = false; break; }
+                    mbar_arrive_cluster(cluster_addr_of(peer_ready + s, peer));
+                }
+                if (!healthy && p.status) atomicOr(p.status, 4);
+            }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer
@@ -400,14 +493,31 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (n < p.n) {
+                    // (batch, row) of the chunk's first activation row by one division, then by stepping
+                    const uint32_t mfirst = m0 + cbase + c0;
+                    uint32_t bt = mfirst / p.m, i = mfirst % p.m;
+                    float *orow = p.out + p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + n;
+                    const float *erow = p.extra ? p.extra + p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)n * p.ex_s2 : nullptr;
+                    if (!erow && i + 32 <= p.m && mfirst + 32 <= p.rows) {  // the common case: 32 whole rows of one batch entry, no epilogue term
+#pragma unroll
+                        for (int j = 0; j < 32; j++) orow[(uint64_t)j * p.out_rs] = __uint_as_float(r[j]);
+                        continue;
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
-                        const uint32_t m = m0 + cbase + c0 + j;
-                        if (m < p.rows) {
-                            const uint32_t bt = m / p.m, i = m % p.m;
+                        if (mfirst + j < p.rows) {
                             float v = __uint_as_float(r[j]);
-                            if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)n * p.ex_s2];
-                            p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + n] = v;
+                            if (erow) v += *erow;
+                            *orow = v;
+                        }
+                        if (++i == p.m) {  // next batch entry
+                            i = 0;
+                            bt++;
+                            orow = p.out + p.out_off + (uint64_t)bt * p.out_bs + n;
+                            if (erow) erow = p.extra + p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)n * p.ex_s2;
+                        } else {
+                            orow += p.out_rs;
+                            if (erow) erow += p.ex_s1;
                         }
                     }
                 }
@@ -418,9 +528,13 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // neither CTA releases the pair's tensor memory (or exits) while the other still uses it
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(MT * NT)) : "memory");
+        if constexpr (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(MT * NT)) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(MT * NT)) : "memory");
     }
 }
 
@@ -451,20 +565,39 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int FMT, int MT, int NT>
+template <int FMT, int MT, int NT, bool PAIR = false>
 static cudaError_t launch_mt(const GemmTcArgs &a, const CUtensorMap &mw, const CUtensorMap &ma, cudaStream_t stream) {
-    auto kern = qgemm_tc_kernel<FMT, MT, NT>;
+    auto kern = qgemm_tc_kernel<FMT, MT, NT, PAIR>;
+    using C = Cfg<FMT, MT, NT, PAIR>;
     static DynamicSmemOptIn opted;
-    if (cudaError_t e = opted.raise((const void *)kern, Cfg<FMT, MT, NT>::SMEM); e != cudaSuccess) return e;
+    if (cudaError_t e = opted.raise((const void *)kern, C::SMEM); e != cudaSuccess) return e;
     dim3 grid((a.n + TN * NT - 1) / (TN * NT), (a.rows + MT - 1) / MT);
-    kern<<<grid, THREADS, Cfg<FMT, MT, NT>::SMEM, stream>>>(mw, ma, a);
-    return cudaGetLastError();
+    if (!PAIR) {
+        kern<<<grid, THREADS, C::SMEM, stream>>>(mw, ma, a);
+        return cudaGetLastError();
+    }
+    grid.x = (grid.x + 1) & ~1u;  // whole pairs: a CTA past the last weight row works on zero fill and stores nothing
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, mw, ma, a);
 }
 
 }  // namespace tc
 
 static int g_tc_wide = -1;  // tuning: -1 choose, 0 never, 1 always use two accumulators at MT = 256
 static int g_tc_tall = -1;  // tuning: -1 choose, 0 never, 1 always use 512-row activation tiles above 256 rows
+static int g_tc_pair = 0;   // tuning: 1 = CTA pairs (cta_group::2) for the two-accumulator Q4_K tile
+void qgemm_tc_set_pair(int v) { g_tc_pair = v; }
 void qgemm_tc_set_wide(int v) { g_tc_wide = v; }
 void qgemm_tc_set_tall(int v) { g_tc_tall = v; }
 
@@ -488,6 +621,8 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
     cudaError_t ce = cudaGetLastError();
     if (ce != cudaSuccess) return ce;
 
+    // CTA pairs: Q4_K, more than 128 rows (256-row activation tiles), at least two 256-row weight tiles
+    const bool pair = g_tc_pair > 0 && fmt == FMT_Q4K && a.rows > 128 && a.n >= 4 * TN;
     CUtensorMap mw, ma;
     {   // packed weights as bytes: [n rows][row_bytes], box = one 144-byte block (Q6_K: 224 bytes around one) of 128 rows
         const uint32_t blk_bytes = fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES;
@@ -506,7 +641,7 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
     {   // bf16 activations [rows][k], box = 64 k (128 bytes, swizzled) x MT rows
         cuuint64_t dims[2] = {a.k, a.rows};
         cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};
-        cuuint32_t box[2] = {KS, mt > 256 ? 256u : mt};
+        cuuint32_t box[2] = {KS, pair ? 128u : (mt > 256 ? 256u : mt)};
         cuuint32_t es[2] = {1, 1};
         if (enc(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_bf16_scratch, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -544,6 +679,7 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
         wide = w2 * 26 <= w1 * 15;
     }
     if (g_tc_wide >= 0) wide = g_tc_wide != 0;
+    if (pair) return launch_mt<FMT_Q4K, 256, 2, true>(a, mw, ma, stream);
     switch (mt) {
         case 64: return launch_mt<FMT_Q4K, 64, 1>(a, mw, ma, stream);
         case 128: return launch_mt<FMT_Q4K, 128, 1>(a, mw, ma, stream);

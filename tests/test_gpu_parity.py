@@ -475,6 +475,28 @@ def test_config3_full_size_prefill(be, fmt):
             assert max_rel(got, exact) <= 2e-2, (n, k, m, max_rel(got, exact))
 
 
+def test_gemm_tensor_core_cta_pairs(be, oracle):
+    """Q4_K prefill with two CTAs per tensor-core unit (`cta_group::2`): the same bounds as the
+    single-CTA kernel and, since the products and the f32 accumulation order per output are the same,
+    the same bits."""
+    seed = 400
+    for (m, n, k, epi) in [(512, 1024, 4096, False), (300, 1000, 1024, True), (260, 700, 512, False), (1000, 512, 2048, False)]:
+        seed += 1
+        qb = oracle.quantize(O.Q4_K, O.normal(seed, n * k, 0.02), n, k)
+        a = O.normal(seed + 7, m * k)
+        bias = rnd(n, seed + 9) if epi else None
+        be.set_option("gemm_pair", "1")
+        try:
+            got = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, bias=bias).reshape(m, n)
+        finally:
+            be.set_option("gemm_pair", "0")
+        ref = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, bias=bias).reshape(m, n)
+        deq = oracle.dequantize(O.Q4_K, qb, n, k)
+        rounded = bf16_round(a.reshape(m, k)).astype(np.float64) @ bf16_round(deq).astype(np.float64).T + (bias.astype(np.float64) if epi else 0.0)
+        assert rel_l2(got, rounded) <= 2e-5, (m, n, k, rel_l2(got, rounded))
+        assert np.array_equal(got, ref), (m, n, k)
+
+
 def test_gemm_tensor_core_strided_output(be, oracle):
     k, n, off, batch, m = 256, 40, 7, 3, 30
     a = rnd(batch * m * k, 100)
