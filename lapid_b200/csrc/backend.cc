@@ -357,7 +357,7 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
         }
     } else {
         p.tc = !dev.gemm_f32 && l.k % 256 == 0 && l.k >= 256 && (l.b_dtype == LAPID_B200_DTYPE_Q4_K || l.b_dtype == LAPID_B200_DTYPE_Q6_K);
-        if (p.tc) p.scratch = align_up(lb::qgemm_tc_scratch_bytes(p.rows, (uint32_t)l.k), 256);
+        if (p.tc) p.scratch = align_up(lb::qgemm_tc_scratch_bytes(p.rows, (uint32_t)l.n, (uint32_t)l.k, dev.sm_count), 256);
     }
     return p;
 }
@@ -528,8 +528,9 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             size_t off = 0;
             if (slot) off = slot->offset;
             else dev.ensure_scratch(p.scratch);
-            cuda_check(lb::launch_qgemm_tc(l.b_dtype, t, (char *)dev.scratch + off, dev.sm_count, dev.stream), "qgemm_tc launch");
-            dev.launches += 2;
+            int launched = 0;
+            cuda_check(lb::launch_qgemm_tc(l.b_dtype, t, (char *)dev.scratch + off, dev.sm_count, dev.stream, &launched), "qgemm_tc launch");
+            dev.launches += launched;
             return;
         }
     }
@@ -809,6 +810,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             lb::qgemv_q4k_fast_set_cta_cap(std::atoi(value));
         } else if (k == "gemm_wide") {
             lb::qgemm_tc_set_wide(std::atoi(value));
+        } else if (k == "gemm_splitk") {
+            lb::qgemm_tc_set_splitk(std::atoi(value));
         } else if (k == "gemm_pair") {
             lb::qgemm_tc_set_pair(std::atoi(value));
         } else if (k == "gemm_tall") {

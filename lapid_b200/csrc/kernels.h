@@ -162,10 +162,12 @@ struct GemmTcArgs {
     int64_t ex_s0, ex_s1, ex_s2;
     uint32_t rows, m, n, k;
     int *status;
+    float *partial;  // split-K launches: [splits][rows][n] partial sums in the scratch; nullptr otherwise
 };
 bool qgemm_tc_supported(int fmt, const GemmTcArgs &args);
-size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t k);  // bf16 copy of the activations
-cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &args, void *a_bf16_scratch, int sm_count, cudaStream_t stream);
+size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t n, uint32_t k, int sm_count);  // bf16 copy of the activations + split-K partial sums
+void qgemm_tc_set_splitk(int v);  // tuning: -1 choose, 0 / 1 never, n > 1 always n ways
+cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &args, void *a_bf16_scratch, int sm_count, cudaStream_t stream, int *launched);
 void qgemm_tc_set_wide(int v);  // tuning: -1 choose, 0 / 1 force one / two accumulators per CTA
 void qgemm_tc_set_pair(int v);  // tuning: 1 = CTA pairs (cta_group::2) for the two-accumulator Q4_K tile
 void qgemm_tc_set_tall(int v);  // tuning: -1 choose, 0 / 1 never / always 512 activation rows per CTA above 256 rows

@@ -201,7 +201,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n0 = blockIdx.x * (TN * NT), m0 = blockIdx.y * MT;
-    const uint32_t nblk = p.k / QK, ksteps = p.k / KS;
+    // split-K: CTA z of gridDim.z takes the super-blocks [kb0, kb0 + nblk) of K and writes a partial tile
+    const uint32_t nblk_total = p.k / QK, per_split = (nblk_total + gridDim.z - 1) / gridDim.z;
+    const uint32_t kb0 = blockIdx.z * per_split;
+    const uint32_t nblk = min(per_split, nblk_total - kb0), ksteps = nblk * (QK / KS);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) {
@@ -242,26 +245,26 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 if (!mbar_wait(empty + s, (u & 1) ^ 1, 64)) { healthy = false; break; }
                 mbar_expect_tx(full_a + s, C::A_BYTES);
                 if constexpr (PAIR) {  // this CTA's half of the activation tile
-                    tma_load_2d(stage0 + s * C::STAGE_BYTES + C::W_BYTES, &map_a, (int)(ks * KS), (int)(m0 + (MT / 2) * cta_rank), full_a + s);
+                    tma_load_2d(stage0 + s * C::STAGE_BYTES + C::W_BYTES, &map_a, (int)(kb0 * QK + ks * KS), (int)(m0 + (MT / 2) * cta_rank), full_a + s);
                 } else {
 #pragma unroll
                     for (int h = 0; h < (MT + 255) / 256; h++)  // a box holds at most 256 rows
-                        tma_load_2d(stage0 + s * C::STAGE_BYTES + C::W_BYTES + h * 256 * 128, &map_a, (int)(ks * KS), (int)(m0 + 256 * h),
+                        tma_load_2d(stage0 + s * C::STAGE_BYTES + C::W_BYTES + h * 256 * 128, &map_a, (int)(kb0 * QK + ks * KS), (int)(m0 + 256 * h),
                                     full_a + s);
                 }
             }
             if (!healthy && p.status) atomicOr(p.status, 2);
         }
-    } else if (warp == 18 && FMT == FMT_Q6K && ((nblk * Q6K_BYTES) & 15u) != 0) {
+    } else if (warp == 18 && FMT == FMT_Q6K && ((nblk_total * Q6K_BYTES) & 15u) != 0) {
         // ---------------- packed Q6_K weights whose rows are not a multiple of 16 bytes (K not a
         // multiple of 2048, e.g. the K/8 shard of a row-parallel projection): no tensor map can
         // describe them, so every lane copies rows of the tile with the plain bulk copy, each from
         // the 16-byte boundary below its block (the consumers compute the same per-row offset)
         const uint32_t rows_valid = min((uint32_t)TN, p.n > n0 ? p.n - n0 : 0u);
-        const uint64_t pitch = (uint64_t)nblk * Q6K_BYTES;
+        const uint64_t pitch = (uint64_t)nblk_total * Q6K_BYTES;
         const uint64_t end16 = ((uint64_t)(uintptr_t)p.w + (uint64_t)p.n * pitch + 15) & ~(uint64_t)15;  // never read past the matrix's last 16-byte line
         auto copy_of = [&](uint32_t rr, uint32_t b, uint64_t &src) -> uint32_t {
-            src = ((uint64_t)(uintptr_t)p.w + (uint64_t)(n0 + rr) * pitch + (uint64_t)b * Q6K_BYTES) & ~(uint64_t)15;
+            src = ((uint64_t)(uintptr_t)p.w + (uint64_t)(n0 + rr) * pitch + (uint64_t)(kb0 + b) * Q6K_BYTES) & ~(uint64_t)15;
             return (uint32_t)min((uint64_t)Q6K_BOX, end16 - src);
         };
         for (uint32_t b = 0; b < nblk && healthy; b++) {
@@ -293,7 +296,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                 for (int t = 0; t < NT; t++)
                     tma_load_2d(raw0 + r * C::RAW + t * RAW_BYTES, &map_w,
-                                FMT == FMT_Q4K ? (int)(b * Q4K_BYTES) : (int)((b * Q6K_BYTES) & ~15u), (int)(n0 + t * TN), raw_full + r);
+                                FMT == FMT_Q4K ? (int)((kb0 + b) * Q4K_BYTES) : (int)(((kb0 + b) * Q6K_BYTES) & ~15u), (int)(n0 + t * TN),
+                                raw_full + r);
             }
             if (!healthy && p.status) atomicOr(p.status, 32);
         }
@@ -383,7 +387,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 if (pp < 2 && !mbar_wait(raw_full + r, ur & 1)) { healthy = false; break; }
                 if (!mbar_wait(empty + s, (u & 1) ^ 1)) { healthy = false; break; }
                 const uint32_t j = lane & 15, h = j >> 3, jj = j & 7, nh = pp >> 1, hi = pp & 1;
-                const uint64_t pitch = (uint64_t)nblk * Q6K_BYTES, wbase = (uint64_t)(uintptr_t)p.w + (uint64_t)b * Q6K_BYTES;
+                const uint64_t pitch = (uint64_t)nblk_total * Q6K_BYTES, wbase = (uint64_t)(uintptr_t)p.w + (uint64_t)(kb0 + b) * Q6K_BYTES;
                 const uint64_t unbias32 = pack2(-8388640.0f, -8388640.0f);  // -(2^23 + 32)
 #pragma unroll 2
                 for (int pass = 0; pass < 8; pass++) {
@@ -492,7 +496,13 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < p.n) {
+                if (n < p.n && p.partial) {  // split-K: this CTA's partial sums, [split][row][n]; summed by a second kernel
+                    const uint32_t mfirst = m0 + cbase + c0;
+                    float *prow = p.partial + ((size_t)blockIdx.z * p.rows + mfirst) * p.n + n;
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (mfirst + j < p.rows) prow[(size_t)j * p.n] = __uint_as_float(r[j]);
+                } else if (n < p.n) {
                     // (batch, row) of the chunk's first activation row by one division, then by stepping
                     const uint32_t mfirst = m0 + cbase + c0;
                     uint32_t bt = mfirst / p.m, i = mfirst % p.m;
@@ -538,6 +548,19 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     }
 }
 
+// split-K second pass: out[m, n] = sum over the splits (in order) of their partial tiles (+ extra)
+__global__ void __launch_bounds__(256) splitk_sum_kernel(GemmTcArgs p, uint32_t splits) {
+    const uint64_t total = (uint64_t)p.rows * p.n;
+    for (uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t m = (uint32_t)(e / p.n), n = (uint32_t)(e % p.n);
+        float v = p.partial[e];
+        for (uint32_t z = 1; z < splits; z++) v += p.partial[(size_t)z * total + e];
+        const uint32_t bt = m / p.m, i = m % p.m;
+        if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)n * p.ex_s2];
+        p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + n] = v;
+    }
+}
+
 // f32 activation rows (any row stride) -> contiguous bf16 [rows, k]
 __global__ void __launch_bounds__(256) a_to_bf16_kernel(GemmTcArgs p, __nv_bfloat16 *dst) {
     const uint64_t total = (uint64_t)p.rows * p.k / 2;
@@ -566,12 +589,12 @@ static EncodeTiledFn encode_fn() {
 }
 
 template <int FMT, int MT, int NT, bool PAIR = false>
-static cudaError_t launch_mt(const GemmTcArgs &a, const CUtensorMap &mw, const CUtensorMap &ma, cudaStream_t stream) {
+static cudaError_t launch_mt(const GemmTcArgs &a, const CUtensorMap &mw, const CUtensorMap &ma, cudaStream_t stream, uint32_t splits = 1) {
     auto kern = qgemm_tc_kernel<FMT, MT, NT, PAIR>;
     using C = Cfg<FMT, MT, NT, PAIR>;
     static DynamicSmemOptIn opted;
     if (cudaError_t e = opted.raise((const void *)kern, C::SMEM); e != cudaSuccess) return e;
-    dim3 grid((a.n + TN * NT - 1) / (TN * NT), (a.rows + MT - 1) / MT);
+    dim3 grid((a.n + TN * NT - 1) / (TN * NT), (a.rows + MT - 1) / MT, splits);
     if (!PAIR) {
         kern<<<grid, THREADS, C::SMEM, stream>>>(mw, ma, a);
         return cudaGetLastError();
@@ -606,11 +629,38 @@ bool qgemm_tc_supported(int fmt, const GemmTcArgs &a) {
     return fmt == FMT_Q4K || fmt == FMT_Q6K;
 }
 
-size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t k) { return (size_t)rows * k * 2; }
+// How many ways K is split: only when the tiles would leave more than half of the SMs idle, never
+// below two super-blocks per split, never more partial-sum scratch than SPLITK_SCRATCH_MAX.
+constexpr size_t SPLITK_SCRATCH_MAX = (size_t)256 << 20;
+static int g_tc_splitk = -1;  // tuning: -1 choose, 0/1 never, n > 1 always n (where K allows)
+void qgemm_tc_set_splitk(int v) { g_tc_splitk = v; }
+static uint32_t splitk_ways(uint32_t rows, uint32_t n, uint32_t k, int sm_count) {
+    const uint32_t mt = rows <= 64 ? 64 : (rows <= 128 ? 128 : 256);
+    const uint64_t tiles = (uint64_t)((n + tc::TN - 1) / tc::TN) * ((rows + mt - 1) / mt);
+    const uint32_t nblk = k / QK;
+    uint32_t ways = 1;
+    if (g_tc_splitk > 1) ways = (uint32_t)g_tc_splitk;
+    else if (g_tc_splitk < 0 && sm_count > 0 && tiles * 2 <= (uint64_t)sm_count) ways = (uint32_t)((uint64_t)sm_count / tiles);
+    if (ways > nblk / 2) ways = nblk / 2;
+    if (ways > 16) ways = 16;
+    while (ways > 1 && (size_t)ways * rows * n * 4 > SPLITK_SCRATCH_MAX) ways--;
+    // every split must own at least one super-block
+    while (ways > 1 && (uint64_t)(ways - 1) * ((nblk + ways - 1) / ways) >= nblk) ways--;
+    return ways < 1 ? 1 : ways;
+}
 
-cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, int sm_count, cudaStream_t stream) {
+// bf16 copy of the activations, then (16-byte aligned) the partial sums of a split-K launch
+size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t n, uint32_t k, int sm_count) {
+    const size_t a_bytes = ((size_t)rows * k * 2 + 255) & ~(size_t)255;
+    const uint32_t ways = splitk_ways(rows, n, k, sm_count);
+    return a_bytes + (ways > 1 ? (size_t)ways * rows * n * 4 : 0);
+}
+
+cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, int sm_count, cudaStream_t stream, int *launched) {
     using namespace tc;
+    *launched = 0;
     if (a.rows == 0 || a.n == 0) return cudaSuccess;
+    *launched = 2;  // the bf16 copy of the activations + the GEMM (+ the split-K sum)
     EncodeTiledFn enc = encode_fn();
     if (!enc) return cudaErrorNotSupported;
     const uint32_t mt = a.rows <= 64 ? 64 : (a.rows <= 128 ? 128 : 256);
@@ -646,6 +696,26 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
         if (enc(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_bf16_scratch, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
+    }
+    // Too few tiles for the SMs (small n: a tensor-parallel shard, a few prefill rows on a narrow
+    // matrix): split K over gridDim.z, partial tiles into the scratch, summed in order by a second kernel.
+    const uint32_t ways = splitk_ways(a.rows, a.n, a.k, sm_count);
+    if (ways > 1 && !pair) {
+        GemmTcArgs b = a;
+        b.partial = (float *)((char *)a_bf16_scratch + (((size_t)a.rows * a.k * 2 + 255) & ~(size_t)255));
+        cudaError_t e;
+        if (fmt == FMT_Q6K)
+            e = mt == 64 ? launch_mt<FMT_Q6K, 64, 1>(b, mw, ma, stream, ways)
+                         : mt == 128 ? launch_mt<FMT_Q6K, 128, 1>(b, mw, ma, stream, ways) : launch_mt<FMT_Q6K, 256, 1>(b, mw, ma, stream, ways);
+        else
+            e = mt == 64 ? launch_mt<FMT_Q4K, 64, 1>(b, mw, ma, stream, ways)
+                         : mt == 128 ? launch_mt<FMT_Q4K, 128, 1>(b, mw, ma, stream, ways) : launch_mt<FMT_Q4K, 256, 1>(b, mw, ma, stream, ways);
+        if (e != cudaSuccess) return e;
+        const uint64_t total = (uint64_t)a.rows * a.n;
+        const unsigned sgrid = (unsigned)((total + 255) / 256 > (uint64_t)sm_count * 8 ? (uint64_t)sm_count * 8 : (total + 255) / 256);
+        splitk_sum_kernel<<<sgrid, 256, 0, stream>>>(b, ways);
+        *launched = 3;
+        return cudaGetLastError();
     }
     // One or two accumulators per CTA at MT = 256: the 256x256 tile halves the activation traffic
     // but there are half as many tiles; take the shape with the shorter modelled time (waves of

@@ -438,7 +438,7 @@ def _gemm_tensor_core_cases(be, oracle, fmt, ofmt, tall_only):
         bias = rnd(n, seed + 9) if epi else None
         be.take_launch_count()
         got = run_matmul(be, fmt, a, qb, m, n, k, batch=batch, a_row_stride=rs, bias=bias).reshape(batch * m, n)
-        assert be.take_launch_count() == 2   # bf16 copy of the activations + the tensor-core kernel
+        assert be.take_launch_count() in (2, 3)   # bf16 copy of the activations + the tensor-core kernel (+ the split-K sum)
         deq = oracle.dequantize(ofmt, qb, n, k)
         av = a.reshape(batch * m, rs)[:, :k]
         b64 = bias.astype(np.float64) if epi else 0.0
@@ -485,16 +485,44 @@ def test_gemm_tensor_core_cta_pairs(be, oracle):
         qb = oracle.quantize(O.Q4_K, O.normal(seed, n * k, 0.02), n, k)
         a = O.normal(seed + 7, m * k)
         bias = rnd(n, seed + 9) if epi else None
+        be.set_option("gemm_splitk", "0")   # same k order in both runs
         be.set_option("gemm_pair", "1")
         try:
             got = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, bias=bias).reshape(m, n)
+            be.set_option("gemm_pair", "0")
+            ref = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, bias=bias).reshape(m, n)
         finally:
             be.set_option("gemm_pair", "0")
-        ref = run_matmul(be, lp.DType.Q4K, a, qb, m, n, k, bias=bias).reshape(m, n)
+            be.set_option("gemm_splitk", "-1")
         deq = oracle.dequantize(O.Q4_K, qb, n, k)
         rounded = bf16_round(a.reshape(m, k)).astype(np.float64) @ bf16_round(deq).astype(np.float64).T + (bias.astype(np.float64) if epi else 0.0)
         assert rel_l2(got, rounded) <= 2e-5, (m, n, k, rel_l2(got, rounded))
         assert np.array_equal(got, ref), (m, n, k)
+
+
+def test_gemm_tensor_core_split_k(be, oracle):
+    """Few output tiles (small n): K is split over several CTAs per tile and the partial tiles are
+    summed in a fixed order by a second kernel. Same bounds; forced split counts including ones that
+    do not divide the number of super-blocks; strided output and bias go through the sum kernel."""
+    seed = 500
+    for fmt, ofmt in ((lp.DType.Q4K, O.Q4_K), (lp.DType.Q6K, O.Q6_K)):
+        for (m, n, k, ways, epi) in [(64, 256, 4096, -1, False), (300, 130, 14336, -1, True), (40, 100, 1792, 3, False),
+                                     (512, 1024, 4096, 5, True), (20, 45, 1024, 16, False)]:
+            seed += 1
+            qb = oracle.quantize(ofmt, O.normal(seed, n * k, 0.02), n, k)
+            a = O.normal(seed + 7, m * k)
+            bias = rnd(n, seed + 9) if epi else None
+            be.set_option("gemm_splitk", str(ways))
+            try:
+                be.take_launch_count()
+                got = run_matmul(be, fmt, a, qb, m, n, k, bias=bias).reshape(m, n)
+                launched = be.take_launch_count()
+            finally:
+                be.set_option("gemm_splitk", "-1")
+            assert launched == 3, (m, n, k, ways)
+            deq = oracle.dequantize(ofmt, qb, n, k)
+            rounded = bf16_round(a.reshape(m, k)).astype(np.float64) @ bf16_round(deq).astype(np.float64).T + (bias.astype(np.float64) if epi else 0.0)
+            assert rel_l2(got, rounded) <= 2e-5, (m, n, k, ways, rel_l2(got, rounded))
 
 
 def test_gemm_tensor_core_strided_output(be, oracle):
