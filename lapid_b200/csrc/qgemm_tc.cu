@@ -561,15 +561,28 @@ __global__ void __launch_bounds__(256) splitk_sum_kernel(GemmTcArgs p, uint32_t 
     }
 }
 
-// f32 activation rows (any row stride) -> contiguous bf16 [rows, k]
-__global__ void __launch_bounds__(256) a_to_bf16_kernel(GemmTcArgs p, __nv_bfloat16 *dst) {
-    const uint64_t total = (uint64_t)p.rows * p.k / 2;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t e = 2 * i;
-        const uint32_t r = (uint32_t)(e / p.k), c = (uint32_t)(e % p.k);
-        const float *src = p.a + p.a_off + (uint64_t)(r / p.m) * p.a_bs + (uint64_t)(r % p.m) * p.a_rs + c;
-        ((__nv_bfloat162 *)dst)[i] = __floats2bfloat162_rn(src[0], src[1]);
+// f32 activation rows (any row stride) -> contiguous bf16 [rows, k]: blockIdx.y = row (one division per
+// thread, not per element), a thread converts eight consecutive elements (k is a multiple of 256);
+// VEC: the rows are 16-byte aligned, so the loads are 128-bit.
+template <bool VEC> __global__ void __launch_bounds__(256) a_to_bf16_kernel(GemmTcArgs p, __nv_bfloat16 *dst) {
+  for (uint32_t r = blockIdx.y; r < p.rows; r += gridDim.y) {
+    const float *src = p.a + p.a_off + (uint64_t)(r / p.m) * p.a_bs + (uint64_t)(r % p.m) * p.a_rs;
+    uint4 *out = (uint4 *)(dst + (size_t)r * p.k);
+    for (uint32_t c8 = blockIdx.x * blockDim.x + threadIdx.x; c8 < p.k / 8; c8 += gridDim.x * blockDim.x) {
+        float v[8];
+        if constexpr (VEC) {
+            const float4 lo = ((const float4 *)src)[2 * c8], hi = ((const float4 *)src)[2 * c8 + 1];
+            v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w, v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = src[8 * c8 + i];
+        }
+        __nv_bfloat162 o[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) o[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        out[c8] = *(const uint4 *)o;
     }
+  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -665,9 +678,12 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
     if (!enc) return cudaErrorNotSupported;
     const uint32_t mt = a.rows <= 64 ? 64 : (a.rows <= 128 ? 128 : 256);
 
-    uint64_t half_elems = (uint64_t)a.rows * a.k / 2;
-    unsigned cgrid = (unsigned)((half_elems + 255) / 256 > (uint64_t)sm_count * 8 ? (uint64_t)sm_count * 8 : (half_elems + 255) / 256);
-    a_to_bf16_kernel<<<cgrid, 256, 0, stream>>>(a, (__nv_bfloat16 *)a_bf16_scratch);
+    {
+        const dim3 cgrid((a.k / 8 + 255) / 256, a.rows < 65535u ? a.rows : 65535u);
+        const bool vec = ((uintptr_t)a.a & 15) == 0 && a.a_off % 4 == 0 && a.a_bs % 4 == 0 && a.a_rs % 4 == 0;
+        if (vec) a_to_bf16_kernel<true><<<cgrid, 256, 0, stream>>>(a, (__nv_bfloat16 *)a_bf16_scratch);
+        else a_to_bf16_kernel<false><<<cgrid, 256, 0, stream>>>(a, (__nv_bfloat16 *)a_bf16_scratch);
+    }
     cudaError_t ce = cudaGetLastError();
     if (ce != cudaSuccess) return ce;
 
