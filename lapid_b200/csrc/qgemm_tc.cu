@@ -11,7 +11,7 @@
 // One CTA computes a 128 (weight rows) x MT (activation rows, 64/128/256) output tile, K in steps
 // of 64 (one Q4_K "pair": 32 bytes of quants = two 32-element sub-blocks):
 //   warp 0     one lane drives TMA for the activations: per k-step a 128-byte swizzled 2-D copy
-//              of the bf16 activation tile (`cp.async.bulk.tensor.2d`, no multicast)
+//              of the bf16 activation tile (`cp.async.bulk.tensor.2d`, each CTA loads its own copy)
 //   warp 18    one lane drives TMA for the weights: per super-block a 2-D tensor-map copy of the
 //              tile rows' packed 144-byte blocks, one super-block ahead of its consumers
 //   warp 1     allocates tensor memory; one lane issues `tcgen05.mma` (M=128, N=MT, K=16, four
