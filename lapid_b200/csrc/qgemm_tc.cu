@@ -1,28 +1,38 @@
 // Prefill GEMM on the 5th-generation tensor cores: out[m, n] = sum_k A[m, k] * dequant(W)[n, k] for
-// Q4_K weights, bf16 operands, f32 accumulation in tensor memory.
+// Q4_K and Q6_K weights, bf16 operands, f32 accumulation in tensor memory.
 //
 // Reference semantics: lapid-cpu's path for more than 8 rows multiplies f32 activations by the
 // dequantized f32 weights (crates/lapid-cpu/src/matmul/qdeq.rs:57-123); lapid-cuda's tensor-core
 // kernel rounds both operands to f16 (crates/lapid-cuda/src/codegen/kquant.rs:335-519). Here both
-// operands are rounded to bf16 (weights: bf16 of lapid-quant's f32 value d1*q - m1, computed with
-// one fused multiply-add), products are exact and sums are f32, so the result differs from the
-// f32 reference by the operand rounding only (2^-9 relative per operand).
+// operands are rounded to bf16 (weights: bf16 of lapid-quant's f32 value -- Q4_K d1*q - m1 computed
+// with one fused multiply-add, Q6_K d*sc*(q-32), exact in f32), products are exact and sums are
+// f32, so the result differs from the f32 reference by the operand rounding only (2^-9 relative
+// per operand).
 //
-// One CTA computes a 128 (weight rows) x MT (activation rows, 64/128/256) output tile, K in steps
-// of 64 (one Q4_K "pair": 32 bytes of quants = two 32-element sub-blocks):
+// One CTA computes a 128*NT (weight rows) x MT (activation rows, 64/128/256/512) output tile, K in
+// steps of 64 (one Q4_K "pair": 32 bytes of quants = two 32-element sub-blocks):
 //   warp 0     one lane drives TMA for the activations: per k-step a 128-byte swizzled 2-D copy
 //              of the bf16 activation tile (`cp.async.bulk.tensor.2d`, each CTA loads its own copy)
 //   warp 18    one lane drives TMA for the weights: per super-block a 2-D tensor-map copy of the
-//              tile rows' packed 144-byte blocks, one super-block ahead of its consumers
+//              tile rows' packed blocks (144 bytes; Q6_K: 224 bytes around the 2-byte aligned 210),
+//              one super-block ahead of its consumers; Q6_K rows that are not 16-byte multiples
+//              are copied row by row with the plain bulk copy by all lanes of the warp
 //   warp 1     allocates tensor memory; one lane issues `tcgen05.mma` (M=128, N=MT, K=16, four
-//              per k-step) on shared-memory descriptors and commits to mbarriers
-//   warps 2-17 dequantize: thread (row, half) expands one 32-element sub-block per k-step from
-//              the staged packed bytes to bf16 and stores it in the 128-byte-swizzled K-major
-//              layout the tensor core reads (warps 2-9 the even k-steps, 10-17 the odd ones);
-//              afterwards warps 2-9 are the epilogue: `tcgen05.ld` 32 lanes x 32 columns at a
-//              time, optional `+ extra`, coalesced f32 stores
+//              per k-step and accumulator) on shared-memory descriptors and commits to mbarriers
+//   warps 2-17 dequantize to bf16 into the 128-byte-swizzled K-major layout the tensor core reads.
+//              Q4_K: thread (row, half) expands one 32-element sub-block per k-step (NT = 1: warps
+//              2-9 the even k-steps, 10-17 the odd ones; NT = 2: the two groups own the two 128-row
+//              sub-tiles). Q6_K: 16 lanes share a row, lane = four weights. Afterwards warps 2-9
+//              (NT = 2: all) are the epilogue: `tcgen05.ld` 32 lanes x 32 columns at a time,
+//              optional `+ extra`, coalesced f32 stores
 // The weight tile is the M side of the MMA and the activations the N side, so 64 prefill rows
 // use a 128x64 instruction at full rate instead of padding to 128 rows.
+// Tile shapes: NT = 2 at MT = 256 (two accumulators, all 512 columns of tensor memory) halves the
+// activation traffic per flop; MT = 512 with NT = 1 halves the dequantization per flop instead
+// (chosen for Q6_K by waves of tiles over the SMs). Launches with too few tiles for the SMs split K
+// over gridDim.z: partial tiles go to a scratch area and a second kernel sums them in order.
+// PAIR (off by default): two CTAs of a cluster as one `cta_group::2` unit, each loading half of the
+// activation tile; measured slower than the single-CTA 256x256 tile.
 // Every mbarrier wait is bounded: a wait that gives up sets a bit in the host-visible status
 // word, the roles fall through to the end, tensor memory is released and the kernel returns.
 #include <cuda.h>
