@@ -75,7 +75,7 @@ cudaError_t launch_qgemv(int fmt, const GemvArgs &args, int sm_count, bool pdl, 
 // Opt in to the dynamic shared memory the GEMV variants need; once per device.
 cudaError_t qgemv_init();
 
-// ---- qgemv_q4k.cu: fast path for Q4_K with 1..4 rows
+// ---- qgemv_q4k.cu: dp4a fast path for Q4_K and Q6_K, 1..8 rows (the default for one row)
 // Reads the activations as 336-byte records (ActQuantArgs::records) from args.qa.
 bool qgemv_q4k_fast_supported(const GemvArgs &args);
 cudaError_t launch_qgemv_q4k_fast(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
