@@ -132,6 +132,13 @@ typedef struct lapid_b200_view3 {
 } lapid_b200_view3;
 
 #define LAPID_B200_KERNEL_MATMUL 2 /* position of MatMul in `enum Kernel`, ir.rs:395-414 */
+/* Kernel::Gather (ir.rs:284-300, CPU crates/lapid-cpu/src/rows.rs:164-215): out[i, :] = dequant(table[ids[i], :]),
+ * the embedding lookup from a quantized table. In a launch of this kind: b_dtype = table dtype (F32,
+ * INT8, Q4_K, Q6_K), out_dtype F32, k = rows of the table, n = cols, m = count, batch 1;
+ * inputs = {table [k, n] in lapid-quant layout, indices i32 [m] contiguous}, n_inputs 2; output f32
+ * [m, n] contiguous (the views are not used). An index outside [0, k) makes execute fail with
+ * "index_out_of_range" after the launch sequence ran; the kernel does not read out of bounds. */
+#define LAPID_B200_KERNEL_GATHER 3
 
 /* Fused epilogues (MatMulSpec.epilogue, ir.rs:234-247). The reference accepts any expression;
  * this backend accepts the two shapes lapid's lowering emits for projections
@@ -140,7 +147,7 @@ typedef struct lapid_b200_view3 {
 #define LAPID_B200_EPILOGUE_ADD 1
 
 typedef struct lapid_b200_launch {
-    int32_t kind;         /* LAPID_B200_KERNEL_MATMUL */
+    int32_t kind;         /* LAPID_B200_KERNEL_MATMUL (the fields below describe it) or LAPID_B200_KERNEL_GATHER (see above) */
     int32_t a_dtype;      /* MatMulSpec.a_dtype: F32 */
     int32_t b_dtype;      /* MatMulSpec.b_dtype: INT8 | Q4_K | Q6_K */
     int32_t out_dtype;    /* MatMulSpec.out_dtype: F32 */

@@ -14,5 +14,6 @@ There is no CPU fallback anywhere: importing works without a GPU (so the library
 can be checked), but every device call fails with ``device_unavailable`` / ``cuda_unavailable``.
 """
 from ._lib import LapidError, abi_version, lib, library_path  # noqa: F401
-from .backend import (Backend, Buffer, DType, Epilogue, Launch, MatMulDims, MatMulSpec, MatView, View)  # noqa: F401
+from .backend import (Backend, Buffer, DType, Epilogue, Launch, MatMulDims, MatMulSpec, MatView, View,  # noqa: F401
+                      gather_launch, matmul_launch)
 from . import quant  # noqa: F401

@@ -126,6 +126,14 @@ def matmul_launch(b_dtype: DType, m: int, n: int, k: int, *, batch: int = 1, a_r
     return Launch(spec, dims, ins, output)
 
 
+def gather_launch(table_dtype: DType, rows: int, cols: int, count: int, *, inputs=(0, 1), output=2) -> Launch:
+    """``Kernel::Gather`` (ir.rs:284-300): ``out[i, :] = dequant(table[ids[i], :])`` for a table of
+    ``rows x cols`` (f32 or a lapid-quant matrix) and ``count`` i32 indices; inputs = (table, indices)."""
+    spec = MatMulSpec(b_dtype=DType(table_dtype))
+    dims = MatMulDims(1, count, cols, rows, a=MatView(), b=MatView(), out=MatView.contiguous(count, cols))
+    return Launch(spec, dims, tuple(inputs), output, kind=3)
+
+
 class Buffer:
     """``DeviceData``: a reference-counted device buffer handle."""
 

@@ -364,8 +364,57 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
 
 // `tp` not null: a launch that takes one of the K-quant fast decode kernels hands its result to the
 // tensor-parallel group from its epilogue instead of storing it (`*pushed` says whether it did).
+// Kernel::Gather: out[i, :] = dequant(table[ids[i], :]).
+void check_gather(const lapid_b200_launch &l) {
+    const bool quant = is_quant(l.b_dtype);
+    if (!quant && l.b_dtype != LAPID_B200_DTYPE_F32)
+        fail("unsupported_dtype", "b200 gather: table dtype " + std::to_string(l.b_dtype) + " (want f32, int8, q4_k or q6_k)");
+    if (l.out_dtype != LAPID_B200_DTYPE_F32) fail("unsupported_dtype", "b200 gather: out must be f32");
+    if (l.n_inputs != 2) fail("invalid_launch", "expected 2 inputs, got " + std::to_string(l.n_inputs));
+    if (l.batch != 1) fail("invalid_launch", "b200 gather: batch must be 1");
+    const uint64_t lim = 1ull << 31;
+    if (l.m >= lim || l.n >= lim || l.k >= lim) fail("too_large", "b200 gather: dimensions exceed 32-bit indexing");
+}
+
+void run_gather(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_buffer *const *buffers, size_t n_buffers) {
+    check_gather(l);
+    auto get = [&](uint32_t id) -> lapid_b200_buffer * {
+        if (id >= n_buffers || !buffers[id])
+            fail("invalid_launch", "buffer id " + std::to_string(id) + " out of range (" + std::to_string(n_buffers) + " buffers)");
+        if (buffers[id]->dev != &dev) fail("wrong_backend", "buffer " + std::to_string(id) + " belongs to another device");
+        return buffers[id];
+    };
+    lapid_b200_buffer *out = get(l.output), *table = get(l.inputs[0]), *ids = get(l.inputs[1]);
+    if (table->ptr == out->ptr || ids->ptr == out->ptr) fail("buffer_aliasing", "gather: an input buffer is the output buffer");
+    const uint64_t rows = l.k, cols = l.n, count = l.m;
+    if (count == 0 || cols == 0) return;
+    if (ids->bytes / 4 < count) fail("out_of_bounds", "gather indices: need " + std::to_string(count) + " i32, buffer holds " + std::to_string(ids->bytes / 4));
+    if (out->bytes / 4 < count * cols)
+        fail("out_of_bounds", "gather output: need " + std::to_string(count * cols) + " f32, buffer holds " + std::to_string(out->bytes / 4));
+    uint64_t scales_offset = 0;
+    int fmt = -1;
+    if (is_quant(l.b_dtype)) {
+        lapid_b200_layout wl = layout_of(l.b_dtype, rows, cols);
+        if (table->bytes < wl.scales_offset + wl.scales_bytes)
+            fail("out_of_bounds", "gather: quantized [" + std::to_string(rows) + ", " + std::to_string(cols) + "] needs " +
+                                      std::to_string(wl.total) + " bytes, buffer has " + std::to_string(table->bytes));
+        scales_offset = wl.scales_offset;
+        fmt = l.b_dtype;
+    } else if (table->bytes / 4 < rows * cols) {
+        fail("out_of_bounds", "gather table: need " + std::to_string(rows * cols) + " f32, buffer holds " + std::to_string(table->bytes / 4));
+    }
+    cuda_check(lb::launch_gather(fmt, table->ptr, scales_offset, (const int32_t *)ids->ptr, rows, cols, count, (float *)out->ptr,
+                                 dev.status_dev, dev.sm_count, dev.stream), "gather launch");
+    dev.launches++;
+}
+
 void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_buffer *const *buffers, size_t n_buffers,
                 ActSlot *slot, PendingGroup *pend = nullptr, const lb::TpPushTable *tp = nullptr, bool *pushed = nullptr) {
+    if (l.kind == LAPID_B200_KERNEL_GATHER) {
+        if (pend) pend->flush(dev);
+        run_gather(dev, l, buffers, n_buffers);
+        return;
+    }
     Plan p = plan_launch(dev, l);
     auto get = [&](uint32_t id) -> lapid_b200_buffer * {
         if (id >= n_buffers || !buffers[id])
@@ -580,6 +629,16 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
         int last = -1;  // most recent slot, reusable by a non-hoisted launch
         for (size_t i = 0; i < n; i++) {
             const lapid_b200_launch &l = launches[i];
+            if (l.kind == LAPID_B200_KERNEL_GATHER) {  // no scratch of its own; its output counts as written
+                lapid_b200_buffer *gb = l.output < nbuf ? buffers[l.output] : nullptr;
+                if (gb) {
+                    written.push_back({(const char *)gb->ptr, (const char *)gb->ptr + gb->bytes});
+                    if (last >= 0 && !slots[last].hoisted && (const char *)slots[last].ptr >= (const char *)gb->ptr &&
+                        (const char *)slots[last].ptr < (const char *)gb->ptr + gb->bytes)
+                        last = -1;
+                }
+                continue;
+            }
             if (l.kind != LAPID_B200_KERNEL_MATMUL || !is_quant(l.b_dtype)) break;  // run_launch reports it
             Plan p = plan_launch(*dev, l);
             lapid_b200_buffer *ab = l.n_inputs > 0 && l.inputs[0] < nbuf ? buffers[l.inputs[0]] : nullptr;
@@ -683,6 +742,7 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
         if (*dev->status_host != 0) {
             int st = *dev->status_host;
             *dev->status_host = 0;
+            if (st == 128) fail("index_out_of_range", "gather: an index is outside the table's rows; the rows of such indices were not written");
             fail("backend", "a device-side wait gave up (status " + std::to_string(st) + "); the results of this call are invalid");
         }
     }
@@ -913,7 +973,10 @@ lapid_b200_status lapid_b200_prepare(lapid_b200_device *dev, const lapid_b200_la
         std::lock_guard<std::mutex> lock(dev->mu);
         dev->make_current();
         size_t scratch = 0;  // every decode launch may get its own slot (see execute)
-        for (size_t i = 0; i < n; i++) scratch += plan_launch(*dev, launches[i]).scratch;
+        for (size_t i = 0; i < n; i++) {
+            if (launches[i].kind == LAPID_B200_KERNEL_GATHER) check_gather(launches[i]);
+            else scratch += plan_launch(*dev, launches[i]).scratch;
+        }
         dev->ensure_scratch(scratch);
     });
 }

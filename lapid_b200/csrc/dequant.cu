@@ -13,35 +13,66 @@
 
 namespace lb {
 
+// element e (0..255) of the Q4_K super-block at b
+__device__ __forceinline__ float q4k_element(const uint8_t *b, int e) {
+    int j = e >> 6, h = (e >> 5) & 1, l = e & 31;
+    float d = half_bits_to_float(b[0] | (b[1] << 8));
+    float dmin = half_bits_to_float(b[2] | (b[3] << 8));
+    int sc, mn;
+    scale_min_k4(2 * j + h, b + 4, sc, mn);
+    float d1 = xmul(d, (float)sc);
+    float m1 = xmul(dmin, (float)mn);
+    int q = (b[16 + 32 * j + l] >> (4 * h)) & 15;
+    return xsub(xmul(d1, (float)q), m1);
+}
+// element e (0..255) of the Q6_K super-block at b
+__device__ __forceinline__ float q6k_element(const uint8_t *b, int e) {
+    int n = e >> 7, w = (e >> 5) & 3, l = e & 31;
+    float d = half_bits_to_float(b[208] | (b[209] << 8));
+    int lo = (b[64 * n + 32 * (w & 1) + l] >> (4 * (w >> 1))) & 15;
+    int hi = (b[128 + 32 * n + l] >> (2 * w)) & 3;
+    int q = (lo | (hi << 4)) - 32;
+    int sc = (int8_t)b[192 + 8 * n + 2 * w + (l >> 4)];
+    return xmul(xmul(d, (float)sc), (float)q);
+}
+
 __global__ void __launch_bounds__(256) dequant_q4k_kernel(const uint8_t *__restrict__ src, float *__restrict__ dst,
                                                           uint64_t n_blocks) {
-    for (uint64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x) {
-        const uint8_t *b = src + blk * Q4K_BYTES;
-        int e = threadIdx.x;
-        int j = e >> 6, h = (e >> 5) & 1, l = e & 31;
-        float d = half_bits_to_float(b[0] | (b[1] << 8));
-        float dmin = half_bits_to_float(b[2] | (b[3] << 8));
-        int sc, mn;
-        scale_min_k4(2 * j + h, b + 4, sc, mn);
-        float d1 = xmul(d, (float)sc);
-        float m1 = xmul(dmin, (float)mn);
-        int q = (b[16 + 32 * j + l] >> (4 * h)) & 15;
-        dst[blk * QK + e] = xsub(xmul(d1, (float)q), m1);
-    }
+    for (uint64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x)
+        dst[blk * QK + threadIdx.x] = q4k_element(src + blk * Q4K_BYTES, threadIdx.x);
 }
 
 __global__ void __launch_bounds__(256) dequant_q6k_kernel(const uint8_t *__restrict__ src, float *__restrict__ dst,
                                                           uint64_t n_blocks) {
-    for (uint64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x) {
-        const uint8_t *b = src + blk * Q6K_BYTES;
-        int e = threadIdx.x;
-        int n = e >> 7, w = (e >> 5) & 3, l = e & 31;
-        float d = half_bits_to_float(b[208] | (b[209] << 8));
-        int lo = (b[64 * n + 32 * (w & 1) + l] >> (4 * (w >> 1))) & 15;
-        int hi = (b[128 + 32 * n + l] >> (2 * w)) & 3;
-        int q = (lo | (hi << 4)) - 32;
-        int sc = (int8_t)b[192 + 8 * n + 2 * w + (l >> 4)];
-        dst[blk * QK + e] = xmul(xmul(d, (float)sc), (float)q);
+    for (uint64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x)
+        dst[blk * QK + threadIdx.x] = q6k_element(src + blk * Q6K_BYTES, threadIdx.x);
+}
+
+// Gather: out[i, :] = dequant(table[ids[i], :]) (lapid's Kernel::Gather, crates/lapid-compiler/src/ir.rs:284-300;
+// CPU: crates/lapid-cpu/src/rows.rs:164-215 -- the embedding lookup from a quantized table). One CTA
+// per (output row, 256 columns); an index outside [0, rows) is not read: the row is skipped and bit
+// 128 of the host-visible status word reports it ("index_out_of_range" after the launch sequence).
+template <int FMT>
+__global__ void __launch_bounds__(256) gather_kernel(const uint8_t *__restrict__ table, uint64_t scales_offset,
+                                                     const int32_t *__restrict__ ids, uint64_t rows, uint64_t cols, uint64_t count,
+                                                     float *__restrict__ out, int *status) {
+    const uint64_t per_row = (cols + 255) / 256;
+    for (uint64_t u = blockIdx.x; u < count * per_row; u += gridDim.x) {
+        const uint64_t i = u / per_row, c = (u % per_row) * 256 + threadIdx.x;
+        const int64_t r = ids[i];
+        if (r < 0 || (uint64_t)r >= rows) {
+            if (threadIdx.x == 0 && status) atomicOr(status, 128);
+            continue;
+        }
+        if (c >= cols) continue;
+        float v;
+        if (FMT == FMT_Q4K) v = q4k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q4K_BYTES, (int)(c % QK));
+        else if (FMT == FMT_Q6K) v = q6k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q6K_BYTES, (int)(c % QK));
+        else if (FMT == FMT_INT8)
+            v = xmul((float)((const int8_t *)table)[(uint64_t)r * cols + c],
+                     half_bits_to_float(((const uint16_t *)(table + scales_offset))[((uint64_t)r * cols + c) >> 5]));
+        else v = ((const float *)table)[(uint64_t)r * cols + c];
+        out[i * cols + c] = v;
     }
 }
 
@@ -89,6 +120,19 @@ cudaError_t launch_dequantize(int fmt, const void *src, uint64_t rows, uint64_t 
         dequant_int8_kernel<<<grid_for((n + 255) / 256, sm_count), 256, 0, stream>>>(
             (const int8_t *)p, (const uint16_t *)(p + scales_offset), dst, n);
     }
+    return cudaGetLastError();
+}
+
+// fmt < 0: plain f32 table
+cudaError_t launch_gather(int fmt, const void *table, uint64_t scales_offset, const int32_t *ids, uint64_t rows, uint64_t cols,
+                          uint64_t count, float *out, int *status, int sm_count, cudaStream_t stream) {
+    if (count == 0 || cols == 0) return cudaSuccess;
+    const int grid = grid_for(count * ((cols + 255) / 256), sm_count);
+    const uint8_t *t = (const uint8_t *)table;
+    if (fmt == FMT_Q4K) gather_kernel<FMT_Q4K><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
+    else if (fmt == FMT_Q6K) gather_kernel<FMT_Q6K><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
+    else if (fmt == FMT_INT8) gather_kernel<FMT_INT8><<<grid, 256, 0, stream>>>(t, scales_offset, ids, rows, cols, count, out, status);
+    else gather_kernel<-1><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
     return cudaGetLastError();
 }
 

@@ -6,6 +6,8 @@
 namespace lb {
 
 // ---- dequant.cu
+cudaError_t launch_gather(int fmt, const void *table, uint64_t scales_offset, const int32_t *ids, uint64_t rows, uint64_t cols,
+                          uint64_t count, float *out, int *status, int sm_count, cudaStream_t stream);  // fmt < 0: f32 table
 cudaError_t launch_dequantize(int fmt, const void *src, uint64_t rows, uint64_t cols, uint64_t scales_offset,
                               float *dst, int sm_count, cudaStream_t stream);
 cudaError_t launch_q8_0_to_planes(const void *blocks, void *dst, uint64_t scales_offset, uint64_t n_groups,

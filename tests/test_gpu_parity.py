@@ -561,6 +561,52 @@ def test_strided_output_view_and_bias(be, oracle):
     assert max_rel(run_matmul(be, lp.DType.Q6K, a, qb, m, n, k, bias=bias), want) <= 2e-5
 
 
+@pytest.mark.parametrize("fmt,name", FMTS + [(lp.DType.F32, "f32")])
+def test_gather_rows_from_a_quantized_table(be, oracle, fmt, name):
+    """Kernel::Gather (the embedding lookup): out[i, :] = dequant(table[ids[i], :]), bit-identical to the
+    oracle's dequantization of the same rows (the reference's own check: crates/lapid-cpu/src/tests.rs,
+    gather against dequantized rows); repeated and unordered indices; an index outside the table fails
+    with index_out_of_range and leaves the device usable."""
+    from lapid_b200.backend import gather_launch
+    rows, cols, count = 300, 1024, 37
+    w = O.normal(31, rows * cols, 0.05)
+    if fmt == lp.DType.F32:
+        table, deq = w.view(np.uint8), w.reshape(rows, cols)
+    else:
+        table = oracle.quantize(int(fmt), w, rows, cols)
+        deq = oracle.dequantize(int(fmt), table, rows, cols).reshape(rows, cols)
+    ids = np.array([0, 299, 5, 5, 17] + list(np.random.default_rng(3).integers(0, rows, count - 5)), np.int32)
+    bufs = [be.upload(table), be.upload(ids.view(np.uint8)), be.alloc(count * cols * 4)]
+    l = gather_launch(fmt, rows, cols, count)
+    be.prepare([l])
+    be.execute([l], bufs)
+    got = bufs[2].download().view(np.float32).reshape(count, cols)
+    assert np.array_equal(got.view(np.uint32), deq[ids].astype(np.float32).view(np.uint32))
+    # a gathered row feeds a projection in the same launch list (embedding -> first matmul)
+    if fmt != lp.DType.F32:
+        n = 64
+        qb = oracle.quantize(O.Q4_K, O.normal(32, n * cols, 0.05), n, cols)
+        bufs2 = bufs + [be.upload(qb), be.alloc(2 * n * 4)]
+        l2 = matmul_launch(lp.DType.Q4K, 2, n, cols, inputs=(2, 3), output=4)
+        be.execute([gather_launch(fmt, rows, cols, 2), l2], bufs2)
+        want, _ = oracle.matmul(O.Q4_K, deq[ids[:2]].reshape(-1), qb, n, cols, m=2)
+        assert max_rel(bufs2[4].download().view(np.float32), want) <= 2e-5
+    bad = ids.copy()
+    bad[7] = rows
+    bufs[1].write(0, bad.view(np.uint8))
+    with pytest.raises(lp.LapidError) as e:
+        be.execute([l], bufs)
+    assert e.value.code == "index_out_of_range"
+    bad[7] = -1
+    bufs[1].write(0, bad.view(np.uint8))
+    with pytest.raises(lp.LapidError) as e:
+        be.execute([l], bufs)
+    assert e.value.code == "index_out_of_range"
+    bufs[1].write(0, ids.view(np.uint8))
+    be.execute([l], bufs)   # still usable
+    assert np.array_equal(bufs[2].download().view(np.float32).reshape(count, cols), got)
+
+
 def test_zero_sized_launches(be, oracle):
     qb = oracle.quantize(O.Q4_K, O.normal(1, 4 * 256, 0.02), 4, 256)
     out = run_matmul(be, lp.DType.Q4K, np.zeros(1, np.float32), qb[:256], 2, 4, 0, out=np.full(8, 9.0, np.float32))
@@ -594,7 +640,7 @@ def test_launch_validation_codes(be, oracle):
     assert code(dc.replace(ok, inputs=(0, 1, 1))) == "invalid_launch"       # 3 inputs without an epilogue
     assert code(dc.replace(ok, inputs=(0, 7))) == "invalid_launch"          # BufId out of range
     assert code(dc.replace(ok, inputs=(2, 1))) == "buffer_aliasing"         # input is the output
-    assert code(dc.replace(ok, kind=3)) == "unsupported"
+    assert code(dc.replace(ok, kind=4)) == "unsupported"
     # the device stays usable after every rejected launch
     be.execute([ok], bufs)
     want, _ = oracle.matmul(O.Q4_K, a, qb, n, k, m=m)
