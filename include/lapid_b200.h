@@ -139,6 +139,16 @@ typedef struct lapid_b200_view3 {
  * [m, n] contiguous (the views are not used). An index outside [0, k) makes execute fail with
  * "index_out_of_range" after the launch sequence ran; the kernel does not read out of bounds. */
 #define LAPID_B200_KERNEL_GATHER 3
+/* Kernel::MatMulId (ir.rs:425-443, CPU crates/lapid-cpu/src/moe.rs:21-120): the mixture-of-experts matmul
+ * out[t, s, :] = W[ids[t, s]] x[t] over a stack of e quantized matrices [n, k], each a lapid-quant matrix at
+ * byte offset expert * layout(n, k).total. In a launch of this kind: b_dtype = w dtype (INT8, Q4_K, Q6_K),
+ * a_dtype and out_dtype F32, m = t (tokens), batch = r (slots per token), b.batch_stride = e, n, k;
+ * inputs = {x f32 [t, k] contiguous, w, ids i32 [t, r] contiguous}, n_inputs 3; output f32 [t, r, n]
+ * contiguous (the other view fields are not used). t <= 8 uses the int8-activation arithmetic of the decode
+ * path for every pair, more tokens the prefill arithmetic (as lapid-cpu: float activations when t > 8,
+ * moe.rs:107-109). An id outside [0, e) makes execute fail with "index_out_of_range" after the launch
+ * sequence ran; the kernels do not read out of bounds. */
+#define LAPID_B200_KERNEL_MATMUL_ID 4
 
 /* Fused epilogues (MatMulSpec.epilogue, ir.rs:234-247). The reference accepts any expression;
  * this backend accepts the two shapes lapid's lowering emits for projections
@@ -147,7 +157,7 @@ typedef struct lapid_b200_view3 {
 #define LAPID_B200_EPILOGUE_ADD 1
 
 typedef struct lapid_b200_launch {
-    int32_t kind;         /* LAPID_B200_KERNEL_MATMUL (the fields below describe it) or LAPID_B200_KERNEL_GATHER (see above) */
+    int32_t kind;         /* LAPID_B200_KERNEL_MATMUL (the fields below describe it), LAPID_B200_KERNEL_GATHER or LAPID_B200_KERNEL_MATMUL_ID (see above) */
     int32_t a_dtype;      /* MatMulSpec.a_dtype: F32 */
     int32_t b_dtype;      /* MatMulSpec.b_dtype: INT8 | Q4_K | Q6_K */
     int32_t out_dtype;    /* MatMulSpec.out_dtype: F32 */

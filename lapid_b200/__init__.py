@@ -15,5 +15,5 @@ can be checked), but every device call fails with ``device_unavailable`` / ``cud
 """
 from ._lib import LapidError, abi_version, lib, library_path  # noqa: F401
 from .backend import (Backend, Buffer, DType, Epilogue, Launch, MatMulDims, MatMulSpec, MatView, View,  # noqa: F401
-                      gather_launch, matmul_launch)
+                      gather_launch, matmul_id_launch, matmul_launch)
 from . import quant  # noqa: F401

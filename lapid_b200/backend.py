@@ -134,6 +134,15 @@ def gather_launch(table_dtype: DType, rows: int, cols: int, count: int, *, input
     return Launch(spec, dims, tuple(inputs), output, kind=3)
 
 
+def matmul_id_launch(w_dtype: DType, t: int, r: int, e: int, n: int, k: int, *, inputs=(0, 1, 2), output=3) -> Launch:
+    """``Kernel::MatMulId`` (ir.rs:425-443): ``out[t, s, :] = W[ids[t, s]] @ x[t]`` over a stack of ``e``
+    quantized matrices ``[n, k]`` (each ``layout(n, k).total`` bytes); inputs = (x f32 [t, k], w, ids i32 [t, r]),
+    output f32 [t, r, n]."""
+    spec = MatMulSpec(b_dtype=DType(w_dtype))
+    dims = MatMulDims(r, t, n, k, a=MatView.contiguous(t, k), b=MatView(0, e, k), out=MatView.contiguous(t * r, n))
+    return Launch(spec, dims, tuple(inputs), output, kind=4)
+
+
 class Buffer:
     """``DeviceData``: a reference-counted device buffer handle."""
 

@@ -31,6 +31,7 @@ SOURCES = {
     "qgemm_tc.cu": [],
     "noalloc.cu": [],
     "glue.cu": [],
+    "moe.cu": [],
     "tp_allreduce.cu": [],
     "backend.cc": ["-x", "cu"],
 }

@@ -408,11 +408,180 @@ void run_gather(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
     dev.launches++;
 }
 
+// Kernel::MatMulId (ir.rs:425-443): out[t, s, :] = W[ids[t, s]] x[t]. In the launch: m = t, batch = r (slots per
+// token), b.batch_stride = e (matrices in the stack), n, k; inputs = {x, w, ids}.
+struct MoePlan {
+    bool noop = false, zero_k = false;
+    bool decode = false;  // t <= gemv_max_rows: int8-activation arithmetic, one one-row GEMV per pair
+    bool fast = false;    // decode: the K-quant kernel with bulk-copy rings (activations as records)
+    bool tc = false;      // above decode sizes: tensor cores (else the exact f32 kernel)
+    uint32_t mt = 64;     // activation rows per tile of the grouped GEMM
+    uint64_t t = 0, r = 0, e = 0;
+    lapid_b200_layout wl{};
+    size_t route_bytes = 0, scratch = 0;
+};
+
+MoePlan plan_matmul_id(const lapid_b200_device &dev, const lapid_b200_launch &l) {
+    MoePlan p;
+    if (!is_quant(l.b_dtype))
+        fail("unsupported_dtype", "b200 matmul_id: w dtype " + std::to_string(l.b_dtype) + " (want int8, q4_k or q6_k)");
+    if (l.a_dtype != LAPID_B200_DTYPE_F32 || l.out_dtype != LAPID_B200_DTYPE_F32)
+        fail("unsupported_dtype", "b200 matmul_id: x and out must be f32");
+    if (l.epilogue != LAPID_B200_EPILOGUE_NONE) fail("unsupported", "b200 matmul_id: no epilogue");
+    if (l.n_inputs != 3) fail("invalid_launch", "expected 3 inputs (x, w, ids), got " + std::to_string(l.n_inputs));
+    p.t = l.m;
+    p.r = l.batch;
+    p.e = l.b.batch_stride;
+    const uint64_t lim = 1ull << 31;
+    if (p.t >= lim || p.r >= lim || p.e >= lim || l.n >= lim || l.k >= lim || p.t * p.r >= lim || p.t * p.r * l.n >= (1ull << 40))
+        fail("too_large", "b200 matmul_id: dimensions exceed 32-bit indexing");
+    if (p.t * p.r * l.n == 0) {
+        p.noop = true;
+        return p;
+    }
+    if (l.k == 0) {
+        p.zero_k = true;
+        return p;
+    }
+    p.wl = layout_of(l.b_dtype, l.n, l.k);
+    p.decode = p.t <= dev.gemv_max_rows;
+    if (p.decode) {
+        if (p.t * p.r > 65535) fail("too_large", "b200 matmul_id: more than 65535 (token, slot) pairs in a decode-sized launch");
+        p.fast = dev.gemv_fast && lb::qgemv_kq_moe_shape_ok(l.b_dtype, (uint32_t)p.t, (uint32_t)l.k);
+        size_t qa = align_up(p.t * l.k, 256), sc = align_up(p.t * (l.k / 32) * 4, 256);
+        size_t rec = align_up(p.t * ((l.k + 255) / 256) * lb::REC, 256);
+        p.scratch = p.fast ? rec : qa + 2 * sc;
+    } else {
+        p.tc = !dev.gemm_f32 && lb::qgemm_tc_moe_supported(l.b_dtype, p.e, l.n, l.k, nullptr);
+        if (p.tc) {
+            const uint64_t avg = p.t * p.r / (p.e ? p.e : 1);
+            p.mt = avg <= 64 ? 64 : avg <= 160 ? 128 : 256;
+        }
+        if ((uint64_t)lb::moe_max_tiles(p.t * p.r, p.e, p.mt) * p.mt >= lim) fail("too_large", "b200 matmul_id: tile space exceeds 32-bit indexing");
+        p.route_bytes = lb::moe_route_bytes(p.t * p.r, p.e, p.mt);
+        p.scratch = p.route_bytes;
+        if (p.tc) p.scratch += align_up((uint64_t)lb::moe_max_tiles(p.t * p.r, p.e, p.mt) * p.mt * l.k * 2, 256);
+    }
+    return p;
+}
+
+void run_matmul_id(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_buffer *const *buffers, size_t n_buffers,
+                   const ActSlot *slot) {
+    MoePlan p = plan_matmul_id(dev, l);
+    auto get = [&](uint32_t id) -> lapid_b200_buffer * {
+        if (id >= n_buffers || !buffers[id])
+            fail("invalid_launch", "buffer id " + std::to_string(id) + " out of range (" + std::to_string(n_buffers) + " buffers)");
+        if (buffers[id]->dev != &dev) fail("wrong_backend", "buffer " + std::to_string(id) + " belongs to another device");
+        return buffers[id];
+    };
+    lapid_b200_buffer *out = get(l.output), *x = get(l.inputs[0]), *w = get(l.inputs[1]), *ids = get(l.inputs[2]);
+    if (x->ptr == out->ptr || w->ptr == out->ptr || ids->ptr == out->ptr)
+        fail("buffer_aliasing", "matmul_id: an input buffer is the output buffer");
+    if (p.noop) return;
+    const uint64_t pairs = p.t * p.r;
+    if (ids->bytes / 4 < pairs || x->bytes / 4 < p.t * l.k || out->bytes / 4 < pairs * l.n)
+        fail("out_of_bounds", "b200 matmul_id: buffers too small for t=" + std::to_string(p.t) + " r=" + std::to_string(p.r) +
+                                  " n=" + std::to_string(l.n) + " k=" + std::to_string(l.k));
+    if (p.zero_k) {
+        cuda_check(cudaMemsetAsync(out->ptr, 0, pairs * l.n * 4, dev.stream), "memset");
+        return;
+    }
+    if (p.e == 0) fail("invalid_launch", "b200 matmul_id: the expert stack is empty");
+    if (w->bytes < p.e * p.wl.total)
+        fail("out_of_bounds", "b200 matmul_id: expert stack holds " + std::to_string(w->bytes) + " < " + std::to_string(p.e * p.wl.total) + " bytes");
+    if (((uintptr_t)w->ptr & 15) != 0 || ((uintptr_t)x->ptr & 15) != 0) fail("invalid_launch", "b200 matmul_id: x and w must be 16-byte aligned");
+    size_t off = 0;
+    if (slot) off = slot->offset;
+    else dev.ensure_scratch(p.scratch);
+    char *base = (char *)dev.scratch + off;
+    if (p.decode) {
+        size_t qa_b = align_up(p.t * l.k, 256), sc_b = align_up(p.t * (l.k / 32) * 4, 256);
+        lb::ActQuantArgs q{};
+        q.a = (const float *)x->ptr;
+        q.a_rs = l.k;
+        q.rows = (uint32_t)p.t;
+        q.m = (uint32_t)p.t;
+        q.k = (uint32_t)l.k;
+        q.qa = (int8_t *)base;
+        q.da = (float *)(base + qa_b);
+        q.bs = l.b_dtype == LAPID_B200_DTYPE_Q4_K ? (float *)(base + qa_b + sc_b) : nullptr;
+        q.records = p.fast ? 1 : 0;
+        cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl, dev.stream), "act_quant launch");
+        lb::GemvArgs g{};
+        g.w = (const uint8_t *)w->ptr;
+        g.w_bytes = w->bytes;
+        g.scales_offset = p.wl.scales_offset;
+        g.qa = q.qa;
+        g.da = q.da;
+        g.bs = q.bs;
+        g.status = dev.status_dev;
+        g.out = (float *)out->ptr;
+        g.out_rs = l.n;
+        g.rows = (uint32_t)p.t;
+        g.m = (uint32_t)p.t;
+        g.n = (uint32_t)l.n;
+        g.k = (uint32_t)l.k;
+        g.ids = (const int32_t *)ids->ptr;
+        g.id_stride = p.wl.total;
+        g.id_r = (uint32_t)p.r;
+        g.id_e = (uint32_t)p.e;
+        if (p.fast) cuda_check(lb::launch_qgemv_kq_moe(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "matmul_id launch");
+        else cuda_check(lb::launch_qgemv_moe(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "matmul_id launch");
+        dev.launches += 2;
+        return;
+    }
+    lb::MoeRouteArgs route{};
+    lb::moe_route_layout(base, pairs, p.e, p.mt, route);
+    route.ids = (const int32_t *)ids->ptr;
+    route.status = dev.status_dev;
+    cuda_check(lb::launch_moe_route(route, dev.pdl, dev.stream), "matmul_id route launch");
+    dev.launches++;
+    const uint32_t rows = route.max_tiles * route.mt;
+    if (p.tc && lb::qgemm_tc_moe_supported(l.b_dtype, p.e, l.n, l.k, w->ptr) && p.wl.total == p.wl.qs_bytes) {
+        void *a_bf16 = base + p.route_bytes;
+        cuda_check(lb::launch_moe_gather_bf16((const float *)x->ptr, route, (uint32_t)p.r, (uint32_t)l.k, a_bf16, dev.stream), "matmul_id gather launch");
+        lb::GemmTcArgs t{};
+        t.w = (const uint8_t *)w->ptr;
+        t.out = (float *)out->ptr;
+        t.rows = rows;
+        t.m = rows;
+        t.n = (uint32_t)l.n;
+        t.k = (uint32_t)l.k;
+        t.status = dev.status_dev;
+        t.tile_expert = route.tile_expert;
+        t.row_pair = route.row_pair;
+        cuda_check(lb::launch_qgemm_tc_moe(l.b_dtype, t, (uint32_t)p.e, p.mt, a_bf16, dev.stream), "matmul_id gemm launch");
+        dev.launches += 2;
+        return;
+    }
+    lb::GemmF32Args f{};
+    f.w = (const uint8_t *)w->ptr;
+    f.scales_offset = p.wl.scales_offset;
+    f.a = (const float *)x->ptr;
+    f.a_rs = l.k;
+    f.out = (float *)out->ptr;
+    f.rows = rows;
+    f.m = rows;
+    f.n = (uint32_t)l.n;
+    f.k = (uint32_t)l.k;
+    f.tile_expert = route.tile_expert;
+    f.row_pair = route.row_pair;
+    f.id_stride = p.wl.total;
+    f.id_r = (uint32_t)p.r;
+    cuda_check(lb::launch_qgemm_f32(l.b_dtype, f, dev.stream), "matmul_id gemm launch");
+    dev.launches++;
+}
+
 void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_buffer *const *buffers, size_t n_buffers,
                 ActSlot *slot, PendingGroup *pend = nullptr, const lb::TpPushTable *tp = nullptr, bool *pushed = nullptr) {
     if (l.kind == LAPID_B200_KERNEL_GATHER) {
         if (pend) pend->flush(dev);
         run_gather(dev, l, buffers, n_buffers);
+        return;
+    }
+    if (l.kind == LAPID_B200_KERNEL_MATMUL_ID) {
+        if (pend) pend->flush(dev);
+        run_matmul_id(dev, l, buffers, n_buffers, slot);
         return;
     }
     Plan p = plan_launch(dev, l);
@@ -639,6 +808,21 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
                 }
                 continue;
             }
+            if (l.kind == LAPID_B200_KERNEL_MATMUL_ID && is_quant(l.b_dtype)) {  // a scratch slot of its own; its output counts as written
+                ActSlot sl;
+                sl.offset = scratch_total;
+                scratch_total += plan_matmul_id(*dev, l).scratch;
+                slots.push_back(sl);
+                slot_of[i] = (int)slots.size() - 1;
+                lapid_b200_buffer *gb = l.output < nbuf ? buffers[l.output] : nullptr;
+                if (gb) {
+                    written.push_back({(const char *)gb->ptr, (const char *)gb->ptr + gb->bytes});
+                    if (last >= 0 && !slots[last].hoisted && (const char *)slots[last].ptr >= (const char *)gb->ptr &&
+                        (const char *)slots[last].ptr < (const char *)gb->ptr + gb->bytes)
+                        last = -1;
+                }
+                continue;
+            }
             if (l.kind != LAPID_B200_KERNEL_MATMUL || !is_quant(l.b_dtype)) break;  // run_launch reports it
             Plan p = plan_launch(*dev, l);
             lapid_b200_buffer *ab = l.n_inputs > 0 && l.inputs[0] < nbuf ? buffers[l.inputs[0]] : nullptr;
@@ -742,7 +926,7 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
         if (*dev->status_host != 0) {
             int st = *dev->status_host;
             *dev->status_host = 0;
-            if (st == 128) fail("index_out_of_range", "gather: an index is outside the table's rows; the rows of such indices were not written");
+            if (st == 128) fail("index_out_of_range", "an index of a gather or an expert id of a matmul_id is out of range; the rows it selects were not computed");
             fail("backend", "a device-side wait gave up (status " + std::to_string(st) + "); the results of this call are invalid");
         }
     }
@@ -975,6 +1159,7 @@ lapid_b200_status lapid_b200_prepare(lapid_b200_device *dev, const lapid_b200_la
         size_t scratch = 0;  // every decode launch may get its own slot (see execute)
         for (size_t i = 0; i < n; i++) {
             if (launches[i].kind == LAPID_B200_KERNEL_GATHER) check_gather(launches[i]);
+            else if (launches[i].kind == LAPID_B200_KERNEL_MATMUL_ID) scratch += plan_matmul_id(*dev, launches[i]).scratch;
             else scratch += plan_launch(*dev, launches[i]).scratch;
         }
         dev->ensure_scratch(scratch);

@@ -71,9 +71,17 @@ struct GemvArgs {
     uint32_t rows, m, n, k;
     const TpPushTable *tp;  // not nullptr (K-quant fast kernels only): the result, row-major [rows, n], goes to slot[rank] of every
                             // rank's buffer as {value, epoch} pairs instead of to `out`
+    // Expert-indexed launches (launch_qgemv_kq_moe only): `w` is a stack of `id_e` matrices [n, k], `id_stride` bytes
+    // apart; ids[t, id_r] (i32) picks the matrix of each (token, slot) pair; rows = tokens; out is [rows, id_r, n].
+    const int32_t *ids;
+    uint64_t id_stride;
+    uint32_t id_r, id_e;
+    uint32_t id_pairs;      // launch_qgemv_moe (generic kernel): tokens * id_r, one grid row each; `rows` is 1 there
 };
 // rows in 1..8. Returns cudaErrorInvalidValue for an unsupported combination.
 cudaError_t launch_qgemv(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+// Expert-indexed form of the same kernel for every format and K (args.ids set; args.rows = tokens, 1..8).
+cudaError_t launch_qgemv_moe(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // Opt in to the dynamic shared memory the GEMV variants need; once per device.
 cudaError_t qgemv_init();
 
@@ -129,6 +137,10 @@ bool qgemv_kq_fast_supported(int fmt, const GemvArgs &args);  // Q4_K and Q6_K, 
 bool qgemv_kq_fast_shape_ok(int fmt, uint32_t rows, uint32_t k);  // same, without the pointer checks
 cudaError_t launch_qgemv_kq_fast(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 void qgemv_q4k_fast_set_cta_cap(int cap);
+// Kernel::MatMulId at decode sizes (1..8 tokens): every (token, slot) pair is a one-row GEMV against the
+// matrix its expert id selects; a bad id sets status bit 128 (and reads expert 0 instead).
+bool qgemv_kq_moe_shape_ok(int fmt, uint32_t tokens, uint32_t k);
+cudaError_t launch_qgemv_kq_moe(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // ---- qgemv_i8.cu: fast path for Int8 planes (K % 512 == 0); reads the activation planes
 bool qgemv_i8_fast_shape_ok(uint32_t rows, uint32_t k);
 cudaError_t launch_qgemv_i8_fast(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);  // tuning: at most this many CTAs per SM (0 = as many as fit)
@@ -149,6 +161,11 @@ struct GemmF32Args {
     uint64_t ex_off;
     int64_t ex_s0, ex_s1, ex_s2;
     uint32_t rows, m, n, k;
+    // Expert-indexed launches (moe.cu): rows = the tile space (64-row tiles), w = the expert stack
+    const int32_t *tile_expert;  // nullptr for an ordinary launch
+    const int32_t *row_pair;
+    uint64_t id_stride;          // bytes between the experts' matrices
+    uint32_t id_r;               // slots per token: pair p reads activation row p / id_r, writes output row p
 };
 cudaError_t launch_qgemm_f32(int fmt, const GemmF32Args &args, cudaStream_t stream);
 
@@ -165,15 +182,37 @@ struct GemmTcArgs {
     uint32_t rows, m, n, k;
     int *status;
     float *partial;  // split-K launches: [splits][rows][n] partial sums in the scratch; nullptr otherwise
+    // Expert-indexed launches (launch_qgemm_tc_moe): rows = the tile space, n = rows of ONE expert's matrix
+    const int32_t *tile_expert;  // nullptr for an ordinary launch
+    const int32_t *row_pair;
 };
 bool qgemm_tc_supported(int fmt, const GemmTcArgs &args);
 size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t n, uint32_t k, int sm_count);  // bf16 copy of the activations + split-K partial sums
 void qgemm_tc_set_splitk(int v);  // tuning: -1 choose, 0 / 1 never, n > 1 always n ways
 cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &args, void *a_bf16_scratch, int sm_count, cudaStream_t stream, int *launched);
+// Kernel::MatMulId on the tensor cores: `a_bf16` holds the activation rows in tile-space order (moe.cu), the
+// weights are a dense stack of `experts` matrices [n, k] (no padding between them), mt in {64, 128, 256}.
+bool qgemm_tc_moe_supported(int fmt, uint64_t experts, uint64_t n, uint64_t k, const void *w);
+cudaError_t launch_qgemm_tc_moe(int fmt, const GemmTcArgs &args, uint32_t experts, uint32_t mt, void *a_bf16, cudaStream_t stream);
 void qgemm_tc_set_wide(int v);  // tuning: -1 choose, 0 / 1 force one / two accumulators per CTA
 void qgemm_tc_set_pair(int v);  // tuning: 1 = CTA pairs (cta_group::2) for the two-accumulator Q4_K tile
 void qgemm_tc_set_tall(int v);  // tuning: -1 choose, 0 / 1 never / always 512 activation rows per CTA above 256 rows
 
+
+// ---- moe.cu: device-side grouping of (token, slot) pairs by expert for Kernel::MatMulId
+struct MoeRouteArgs {
+    const int32_t *ids;  // [pairs]
+    uint32_t pairs, experts, mt, max_tiles;
+    int32_t *counts, *cursor, *offsets;  // [experts] each
+    int32_t *tile_expert;                // [max_tiles]
+    int32_t *row_pair;                   // [max_tiles * mt]
+    int *status;
+};
+uint32_t moe_max_tiles(uint64_t pairs, uint64_t experts, uint32_t mt);
+size_t moe_route_bytes(uint64_t pairs, uint64_t experts, uint32_t mt);
+void moe_route_layout(void *scratch, uint64_t pairs, uint64_t experts, uint32_t mt, MoeRouteArgs &args);  // fills all but ids and status
+cudaError_t launch_moe_route(const MoeRouteArgs &args, bool pdl, cudaStream_t stream);
+cudaError_t launch_moe_gather_bf16(const float *x, const MoeRouteArgs &route, uint32_t r, uint32_t k, void *dst, cudaStream_t stream);
 
 // ---- glue.cu: the row / elementwise steps between the projections of a layer (not on the matmul path)
 struct RmsNormArgs {

@@ -5,6 +5,12 @@
 // bit-identical to it. This is the reference-exact path for more than 8 activation rows; the
 // tensor-core kernel is the fast one.
 //
+// Expert-indexed launches (Kernel::MatMulId above decode sizes) run through the same kernel: the
+// activation tiles are runs of (token, slot) pairs grouped by expert (moe.cu), a tile looks up its
+// expert's matrix, rows are gathered and scattered through the pair table. Every output is still
+// the in-order FMA sum over k, i.e. what lapid-cpu's per-expert matmul gives
+// (crates/lapid-cpu/src/moe.rs:80-118 with float_act, :109).
+//
 // CUDA-core kernel: 64x64 output tile per CTA, 4x4 register tile per thread, k in steps of one
 // 32-element group; the W tile is expanded into shared memory once per step (so each weight is
 // dequantized once per 64 activation rows) and A is staged beside it.
@@ -55,6 +61,11 @@ template <int FMT> __global__ void __launch_bounds__(256) qgemm_f32_kernel(GemmF
     __shared__ float Bs[BK][BN + PADF];
     const int tid = threadIdx.x;
     const uint32_t row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
+    if (p.tile_expert) {  // expert-indexed launch (moe.cu): this activation tile multiplies one expert's matrix
+        const int32_t e = p.tile_expert[blockIdx.y];
+        if (e < 0) return;
+        p.w += (uint64_t)e * p.id_stride;
+    }
     const int ty = tid >> 4, tx = tid & 15;
     float acc[4][4];
 #pragma unroll
@@ -65,7 +76,12 @@ template <int FMT> __global__ void __launch_bounds__(256) qgemm_f32_kernel(GemmF
     const int lr = tid >> 2, part = tid & 3;  // loader role: tile row / weight row, 8-element part
     const uint32_t arow = row0 + lr;
     const float *aptr = nullptr;
-    if (arow < p.rows) aptr = p.a + p.a_off + (uint64_t)(arow / p.m) * p.a_bs + (uint64_t)(arow % p.m) * p.a_rs;
+    if (p.tile_expert) {
+        const int32_t pair = p.row_pair[arow];
+        if (pair >= 0) aptr = p.a + p.a_off + (uint64_t)((uint32_t)pair / p.id_r) * p.a_rs;
+    } else if (arow < p.rows) {
+        aptr = p.a + p.a_off + (uint64_t)(arow / p.m) * p.a_bs + (uint64_t)(arow % p.m) * p.a_rs;
+    }
     const uint32_t wrow = col0 + lr;
 
     for (uint32_t k0 = 0; k0 < p.k; k0 += BK) {
@@ -100,6 +116,16 @@ template <int FMT> __global__ void __launch_bounds__(256) qgemm_f32_kernel(GemmF
     for (int i = 0; i < 4; i++) {
         uint32_t r = row0 + ty * 4 + i;
         if (r >= p.rows) continue;
+        if (p.tile_expert) {
+            const int32_t pair = p.row_pair[r];
+            if (pair < 0) continue;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint32_t col = col0 + tx * 4 + j;
+                if (col < p.n) p.out[p.out_off + (uint64_t)pair * p.n + col] = acc[i][j];
+            }
+            continue;
+        }
         uint32_t bt = r / p.m, ii = r % p.m;
 #pragma unroll
         for (int j = 0; j < 4; j++) {

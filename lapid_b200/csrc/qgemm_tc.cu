@@ -211,6 +211,15 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n0 = blockIdx.x * (TN * NT), m0 = blockIdx.y * MT;
+    // Expert-indexed launch (Kernel::MatMulId, moe.cu): the activation tiles are runs of (token, slot)
+    // pairs grouped by expert; the weights are the dense stack [experts * n, k], so a tile's weight
+    // rows start at expert * n. Tiles past the last used one have no expert.
+    uint32_t wrow0 = 0;
+    if (p.tile_expert) {
+        const int32_t e = p.tile_expert[blockIdx.y];
+        if (e < 0) return;  // before any barrier or tensor-memory allocation
+        wrow0 = (uint32_t)e * p.n;
+    }
     // split-K: CTA z of gridDim.z takes the super-blocks [kb0, kb0 + nblk) of K and writes a partial tile
     const uint32_t nblk_total = p.k / QK, per_split = (nblk_total + gridDim.z - 1) / gridDim.z;
     const uint32_t kb0 = blockIdx.z * per_split;
@@ -306,7 +315,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                 for (int t = 0; t < NT; t++)
                     tma_load_2d(raw0 + r * C::RAW + t * RAW_BYTES, &map_w,
-                                FMT == FMT_Q4K ? (int)((kb0 + b) * Q4K_BYTES) : (int)(((kb0 + b) * Q6K_BYTES) & ~15u), (int)(n0 + t * TN),
+                                FMT == FMT_Q4K ? (int)((kb0 + b) * Q4K_BYTES) : (int)(((kb0 + b) * Q6K_BYTES) & ~15u), (int)(wrow0 + n0 + t * TN),
                                 raw_full + r);
             }
             if (!healthy && p.status) atomicOr(p.status, 32);
@@ -506,7 +515,16 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < p.n && p.partial) {  // split-K: this CTA's partial sums, [split][row][n]; summed by a second kernel
+                if (p.row_pair) {  // expert-indexed: tile-space row -> (token, slot) pair = output row; padding rows have none
+                    const uint32_t mfirst = m0 + cbase + c0;
+                    if (n < p.n) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int32_t pair = p.row_pair[mfirst + j];
+                            if (pair >= 0) p.out[p.out_off + (uint64_t)pair * p.n + n] = __uint_as_float(r[j]);
+                        }
+                    }
+                } else if (n < p.n && p.partial) {  // split-K: this CTA's partial sums, [split][row][n]; summed by a second kernel
                     const uint32_t mfirst = m0 + cbase + c0;
                     float *prow = p.partial + ((size_t)blockIdx.z * p.rows + mfirst) * p.n + n;
 #pragma unroll
@@ -677,6 +695,46 @@ size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t n, uint32_t k, int sm_coun
     const size_t a_bytes = ((size_t)rows * k * 2 + 255) & ~(size_t)255;
     const uint32_t ways = splitk_ways(rows, n, k, sm_count);
     return a_bytes + (ways > 1 ? (size_t)ways * rows * n * 4 : 0);
+}
+
+bool qgemm_tc_moe_supported(int fmt, uint64_t experts, uint64_t n, uint64_t k, const void *w) {
+    if (fmt != FMT_Q4K && fmt != FMT_Q6K) return false;
+    if (k % QK != 0 || k < QK || ((uintptr_t)w & 15) != 0 || tc::encode_fn() == nullptr) return false;
+    const uint64_t pitch = k / QK * (fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+    // one tensor map over all experts' rows: rows of 16-byte multiples, no padding between the matrices
+    return pitch % 16 == 0 && (n * pitch) % 256 == 0 && experts * n < (1ull << 31);
+}
+
+cudaError_t launch_qgemm_tc_moe(int fmt, const GemmTcArgs &a, uint32_t experts, uint32_t mt, void *a_bf16, cudaStream_t stream) {
+    using namespace tc;
+    if (a.rows == 0 || a.n == 0) return cudaSuccess;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc || !a.tile_expert || !a.row_pair || a.rows % mt != 0) return cudaErrorInvalidValue;
+    CUtensorMap mw, ma;
+    {
+        const uint32_t blk_bytes = fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES;
+        cuuint64_t dims[2] = {(cuuint64_t)(a.k / QK) * blk_bytes, (cuuint64_t)experts * a.n};
+        cuuint64_t strides[1] = {(cuuint64_t)(a.k / QK) * blk_bytes};
+        cuuint32_t box[2] = {fmt == FMT_Q4K ? (cuuint32_t)Q4K_BYTES : (cuuint32_t)Q6K_BOX, TN};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)a.w, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    {
+        cuuint64_t dims[2] = {a.k, a.rows};
+        cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};
+        cuuint32_t box[2] = {KS, mt};
+        cuuint32_t es[2] = {1, 1};
+        if (enc(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_bf16, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    if (fmt == FMT_Q6K)
+        return mt == 64 ? launch_mt<FMT_Q6K, 64, 1>(a, mw, ma, stream)
+                        : mt == 128 ? launch_mt<FMT_Q6K, 128, 1>(a, mw, ma, stream) : mt == 256 ? launch_mt<FMT_Q6K, 256, 1>(a, mw, ma, stream) : cudaErrorInvalidValue;
+    return mt == 64 ? launch_mt<FMT_Q4K, 64, 1>(a, mw, ma, stream)
+                    : mt == 128 ? launch_mt<FMT_Q4K, 128, 1>(a, mw, ma, stream) : mt == 256 ? launch_mt<FMT_Q4K, 256, 1>(a, mw, ma, stream) : cudaErrorInvalidValue;
 }
 
 cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, int sm_count, cudaStream_t stream, int *launched) {

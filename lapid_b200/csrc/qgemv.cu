@@ -90,6 +90,22 @@ __global__ void __launch_bounds__(WARPS * 32) qgemv_kernel(GemvArgs p) {
     constexpr int SPAN = Geo<FMT>::SPAN;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint8_t *ring = smem + (size_t)warp * (STAGES * C * SPAN);
+    if (p.ids) {
+        // Expert-indexed launch (Kernel::MatMulId at decode sizes): grid row y is one (token, slot)
+        // pair, a one-row GEMV of the token's activations against the matrix its id selects. The
+        // ids come from the kernel before this one, so nothing is staged ahead of it.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        const uint32_t pair = blockIdx.y, token = pair / p.id_r;
+        const int32_t id = p.ids[pair];
+        const bool bad = id < 0 || (uint32_t)id >= p.id_e;
+        if (bad && p.status && threadIdx.x == 0) atomicOr(p.status, 128);
+        p.w += bad ? 0 : (uint64_t)id * p.id_stride;
+        p.w_bytes = p.id_stride;
+        p.qa += (uint64_t)token * p.k;
+        p.da += (uint64_t)token * (p.k / GROUP);
+        if (p.bs) p.bs += (uint64_t)token * (p.k / GROUP);
+        p.out_off += (uint64_t)pair * p.n;
+    }
 
     const uint32_t k = p.k, n = p.n;
     const uint32_t kg = k / GROUP;
@@ -381,6 +397,10 @@ static cudaError_t launch_one(const GemvArgs &a, int sm_count, bool pdl, cudaStr
     uint32_t cap = (uint32_t)sm_count * (uint32_t)ctas_per_sm;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(want < cap ? want : cap);
+    if (a.ids) {  // one grid row per (token, slot) pair; the rows share the resident slots
+        const uint32_t share = cap / a.id_pairs > 0 ? cap / a.id_pairs : 1;
+        cfg.gridDim = dim3(want < share ? want : share, a.id_pairs);
+    }
     cfg.blockDim = dim3(WARPS * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -423,6 +443,17 @@ cudaError_t launch_qgemv(int fmt, const GemvArgs &args, int sm_count, bool pdl, 
         case FMT_INT8: return launch_fmt<FMT_INT8>(args, sm_count, pdl, stream);
         default: return cudaErrorInvalidValue;
     }
+}
+
+cudaError_t launch_qgemv_moe(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream) {
+    if (!args.ids || args.id_r == 0 || args.id_e == 0 || args.rows < 1 || args.rows > 8 || ((uintptr_t)args.w & 15) || (args.id_stride & 15))
+        return cudaErrorInvalidValue;
+    if ((uint64_t)args.rows * args.id_r > 65535) return cudaErrorInvalidValue;  // grid rows
+    GemvArgs one = args;
+    one.id_pairs = args.rows * args.id_r;
+    one.rows = 1;
+    one.m = 1;
+    return launch_qgemv(fmt, one, sm_count, pdl, stream);
 }
 
 cudaError_t qgemv_init() { return cudaSuccess; }

@@ -130,8 +130,13 @@ __device__ __forceinline__ float q6_group(const uint32_t (&q)[8], const uint32_t
 // shared memory and are better amortised over more warps.
 template <int M> struct Shape { static constexpr int WARPS = M <= 2 ? 4 : 8, MIN_CTAS = M <= 2 ? 5 : 2; };
 
-template <int FMT, int M, int G, int NG>
+// MOE (Kernel::MatMulId at decode sizes; M == 1, NG == 1): the weight operand is a stack of matrices and
+// every (token, slot) pair is a one-row GEMV against the matrix its expert id selects. The pairs'
+// tasks form one list (a task never straddles two pairs), the activation records of all tokens
+// sit in shared memory and a task reads the records of its pair's token.
+template <int FMT, int M, int G, int NG, bool MOE = false>
 __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_kq_fast_kernel(GemvGroupT<NG> grp) {
+    static_assert(!MOE || (M == 1 && NG == 1), "expert-indexed launches are one-row, one-item launches");
     constexpr int STAGES = 2;
     constexpr int BB = Blk<FMT>::BYTES, STAGE_BYTES = Blk<FMT>::STAGE;
     constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
@@ -145,6 +150,14 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     const uint32_t nblk = grp.item[0].k / QK;
     const uint32_t iters = (nblk + G - 1) / G;
     const uint32_t tasks = grp.task_end[grp.count - 1];
+    const uint32_t tpp = MOE ? (grp.item[0].n + RPW - 1) / RPW : 0;  // tasks per (token, slot) pair
+    // the matrix of a pair; an id outside the stack is reported and replaced by 0
+    auto expert_matrix = [&](uint32_t pair) -> const uint8_t * {
+        const int32_t id = grp.item[0].ids[pair];
+        const bool bad = id < 0 || (uint32_t)id >= grp.item[0].id_e;
+        if (bad && grp.item[0].status) atomicOr(grp.item[0].status, 128);
+        return grp.item[0].w + (bad ? 0 : (uint64_t)id * grp.item[0].id_stride);
+    };
     auto locate = [&](uint32_t t, uint32_t &local) -> int {
         if constexpr (NG == 1) {
             local = t;
@@ -180,6 +193,11 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             uint32_t local;
             const int item = locate(pt, local);
             const uint32_t n = grp.item[item].n;
+            const uint8_t *wbase = grp.item[item].w;
+            if constexpr (MOE) {
+                wbase = expert_matrix(local / tpp);
+                local %= tpp;
+            }
             const uint32_t row0 = local * RPW;
             uint32_t first, count;
             if (iters == 1) {
@@ -189,7 +207,7 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
                 first = row0 * nblk + pit * 32;
                 count = min(32u, nblk - pit * 32);
             }
-            const uint8_t *src = grp.item[item].w + (uint64_t)first * BB;
+            const uint8_t *src = wbase + (uint64_t)first * BB;
             const uint32_t skew = (uint32_t)((uintptr_t)src & 15u);  // 0 for Q4_K
             const uint32_t bytes = (skew + count * BB + 15u) & ~15u;
             mbar_expect_tx(bars + pslot, bytes);
@@ -201,16 +219,21 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             pt += FAST_WARPS;
         }
     };
+    if constexpr (MOE) {  // the expert ids come from the kernel before this one: nothing can be fetched ahead of it
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
     issue();
     issue();
-
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if constexpr (!MOE) {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
 
     __shared__ TpPushCtx tp_ctx;  // only the first member of a launch may push (tensor-parallel launches are never grouped)
     if (grp.item[0].tp && threadIdx.x == 0) tp_push_ctx_load(&tp_ctx, grp.item[0].tp);
     {
-        const uint32_t chunks = M * nblk * (REC / 16);
+        const uint32_t chunks = (MOE ? grp.item[0].rows : M) * nblk * (REC / 16);
         for (int i = 0; i < grp.count; i++) {
             if (!grp.act_copy[i]) continue;  // same activations as an earlier projection of the group
             const uint8_t *src = (const uint8_t *)grp.item[i].qa;
@@ -232,6 +255,14 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
         const GemvArgs &p = grp.item[item];
         const uint32_t n = p.n;
         const uint8_t *iacts = acts + grp.act_off[item];
+        const uint8_t *wbase = p.w;
+        uint32_t pair = 0;
+        if constexpr (MOE) {
+            pair = local / tpp;
+            local %= tpp;
+            wbase = expert_matrix(pair);
+            iacts += (size_t)(pair / p.id_r) * nblk * REC;  // the records of the pair's token
+        }
         const uint32_t row = local * RPW + sub;
 #pragma unroll
         for (int r = 0; r < M; r++) acc[r] = 0.0f;
@@ -244,7 +275,7 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             if (healthy && row < n && b < nblk && gl < nblk) {
                 // the stage starts at the 16-byte boundary below its first block (Q6_K; see Blk)
                 const uint32_t first_blk = iters == 1 ? local * RPW * nblk : local * RPW * nblk + it * 32;
-                const uint32_t skew = FMT == FMT_Q4K ? 0u : (uint32_t)(((uintptr_t)p.w + (uint64_t)first_blk * BB) & 15u);
+                const uint32_t skew = FMT == FMT_Q4K ? 0u : (uint32_t)(((uintptr_t)wbase + (uint64_t)first_blk * BB) & 15u);
                 const uint8_t *blk = ring + (size_t)cslot * STAGE_BYTES + skew + (size_t)(iters == 1 ? sub * nblk + gl : gl) * BB;
                 if constexpr (FMT == FMT_Q4K) {
                     const uint4 h = *(const uint4 *)blk;
@@ -324,7 +355,8 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             if (gl == 0 && row < n) {
                 const uint32_t bt = r / p.m, i = r % p.m;
                 if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
-                if (p.tp) tp_push_value(&tp_ctx, (uint64_t)r * n + row, v);  // row-parallel partial: to every rank
+                if constexpr (MOE) p.out[p.out_off + (uint64_t)pair * n + row] = v;
+                else if (p.tp) tp_push_value(&tp_ctx, (uint64_t)r * n + row, v);  // row-parallel partial: to every rank
                 else p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
             }
         }
@@ -335,14 +367,14 @@ static int g_cta_cap = 0;  // 0 = as many CTAs per SM as fit; set through qgemv_
 
 void qgemv_q4k_fast_set_cta_cap(int cap) { g_cta_cap = cap; }
 
-template <int FMT, int M, int G, int NG>
+template <int FMT, int M, int G, int NG, bool MOE = false>
 static cudaError_t launch_fast_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cudaStream_t stream) {
-    auto kern = qgemv_kq_fast_kernel<FMT, M, G, NG>;
+    auto kern = qgemv_kq_fast_kernel<FMT, M, G, NG, MOE>;
     constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
     constexpr int RPW = 32 / G;
     uint32_t tasks = 0;
     for (int i = 0; i < g.count; i++) {
-        tasks += (g.item[i].n + RPW - 1) / RPW;
+        tasks += (g.item[i].n + RPW - 1) / RPW * (MOE ? g.item[i].rows * g.item[i].id_r : 1);
         g.task_end[i] = tasks;
     }
     const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * Blk<FMT>::STAGE + g.act_bytes;
@@ -463,6 +495,36 @@ cudaError_t launch_qgemv_kq_group(int fmt, GemvGroup &g, int sm_count, bool pdl,
     if (g.count < 1 || g.count > GEMV_GROUP_MAX) return cudaErrorInvalidValue;
     plan_group_acts(g);
     return fmt == FMT_Q6K ? launch_fmt<FMT_Q6K>(g, sm_count, pdl, s) : launch_fmt<FMT_Q4K>(g, sm_count, pdl, s);
+}
+
+bool qgemv_kq_moe_shape_ok(int fmt, uint32_t tokens, uint32_t k) {
+    if (fmt != FMT_Q4K && fmt != FMT_Q6K) return false;
+    if (tokens < 1 || tokens > 8 || k % QK != 0 || k < QK) return false;
+    const size_t stage = fmt == FMT_Q4K ? Blk<FMT_Q4K>::STAGE : Blk<FMT_Q6K>::STAGE;
+    return BAR_BYTES + (size_t)Shape<1>::WARPS * 2 * stage + (size_t)tokens * (k / QK) * REC <= 227 * 1024 - 256;
+}
+
+template <int FMT, int G> static cudaError_t launch_moe_g(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
+    GemvSingle one{};
+    one.item[0] = a;
+    one.act_copy[0] = 1;
+    one.count = 1;
+    one.act_bytes = a.rows * (a.k / QK) * REC;
+    return launch_fast_n<FMT, 1, G, 1, true>(one, sm_count, pdl, s);
+}
+
+template <int FMT> static cudaError_t launch_moe(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
+    const uint32_t nblk = a.k / QK;
+    if (nblk <= 8) return launch_moe_g<FMT, 8>(a, sm_count, pdl, s);
+    if (nblk <= 16) return launch_moe_g<FMT, 16>(a, sm_count, pdl, s);
+    return launch_moe_g<FMT, 32>(a, sm_count, pdl, s);
+}
+
+cudaError_t launch_qgemv_kq_moe(int fmt, const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
+    if (!qgemv_kq_moe_shape_ok(fmt, a.rows, a.k) || !a.ids || a.id_r == 0 || a.id_e == 0 || ((uintptr_t)a.w & 15) || (a.id_stride & 15))
+        return cudaErrorInvalidValue;
+    if ((uint64_t)a.rows * a.id_r * ((a.n + 3) / 4) >= (1ull << 31)) return cudaErrorInvalidValue;  // 32-bit task index
+    return fmt == FMT_Q6K ? launch_moe<FMT_Q6K>(a, sm_count, pdl, s) : launch_moe<FMT_Q4K>(a, sm_count, pdl, s);
 }
 
 cudaError_t launch_qgemv_kq_fast(int fmt, const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {

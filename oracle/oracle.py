@@ -220,6 +220,37 @@ class Oracle:
         return out, {0: "int8_act", 1: "f32_act"}.get(path.value, "none")
 
 
+    def matmul_id(self, fmt: int, x: np.ndarray, w: np.ndarray, ids: np.ndarray, t: int, r: int, e: int, n: int, k: int):
+        """``Kernel::MatMulId`` as lapid-cpu runs it (crates/lapid-cpu/src/moe.rs:21-120): the (token, slot)
+        pairs are grouped by expert, every used expert runs ONE ordinary matmul over its gathered token
+        rows -- with float activations for every expert when t > 8 (:107-109), else by its own row count
+        -- and the result rows are scattered back. ``w`` is the stack of ``e`` matrices, ``layout(n, k).total``
+        bytes each. Returns out [t, r, n]."""
+        out = np.zeros((t * r, n), dtype=np.float32)
+        if t * r * n == 0:
+            return out.reshape(t, r, n)
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)[: t * k].reshape(t, k)
+        ids = np.ascontiguousarray(ids, dtype=np.int32).reshape(-1)
+        if ids.size < t * r:
+            raise OracleError("out_of_bounds", "matmul_id: ids too small")
+        by_expert: list[list[int]] = [[] for _ in range(e)]
+        for i, ex in enumerate(ids[: t * r]):
+            if ex < 0 or ex >= e:
+                raise OracleError("index_out_of_range", f"matmul_id: expert id {ex} at position {i} out of range for {e} experts")
+            by_expert[int(ex)].append(i)
+        one = self.layout(fmt, n, k).total
+        w = np.ascontiguousarray(w, dtype=np.uint8).reshape(-1)
+        if w.size < e * one:
+            raise OracleError("out_of_bounds", "matmul_id: expert stack too small")
+        for ex, rows in enumerate(by_expert):
+            if not rows:
+                continue
+            a = x[[i // r for i in rows]]
+            res, _ = self.matmul(fmt, a, w[ex * one:(ex + 1) * one], n, k, m=len(rows), force_f32_act=t > 8)
+            out[rows] = res.reshape(len(rows), n)
+        return out.reshape(t, r, n)
+
+
 _cache: dict[bool, Oracle] = {}
 
 

@@ -607,6 +607,98 @@ def test_gather_rows_from_a_quantized_table(be, oracle, fmt, name):
     assert np.array_equal(bufs[2].download().view(np.float32).reshape(count, cols), got)
 
 
+def _expert_stack(oracle, fmt, e, n, k, seed):
+    one = oracle.layout(int(fmt), n, k).total
+    stack = np.zeros(e * one, np.uint8)
+    for x in range(e):
+        q = oracle.quantize(int(fmt), O.normal(seed + x, n * k, 0.05), n, k)
+        stack[x * one:x * one + q.size] = q
+    return stack
+
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("t,r,e,n,k", [(1, 2, 5, 24, 512), (1, 4, 8, 200, 1024), (3, 2, 4, 64, 256), (8, 8, 16, 96, 2048),
+                                       (2, 3, 6, 40, 4096 + 512)])
+def test_matmul_id_decode(be, oracle, fmt, name, t, r, e, n, k):
+    """Kernel::MatMulId at decode sizes (t <= 8): every (token, slot) pair is the int8-activation GEMV of the
+    token's row against the matrix of its expert -- what lapid-cpu computes per used expert
+    (crates/lapid-cpu/src/moe.rs:80-118; its test crates/lapid-cpu/src/tests.rs:350-383 uses the same id pattern)."""
+    from lapid_b200.backend import matmul_id_launch
+    stack = _expert_stack(oracle, fmt, e, n, k, 50)
+    x = O.normal(70, t * k, 1.0)
+    ids = np.array([(i * 7 + i // r) % e for i in range(t * r)], np.int32)
+    want = oracle.matmul_id(int(fmt), x, stack, ids, t, r, e, n, k)
+    bufs = [be.upload(x), be.upload(stack), be.upload(ids.view(np.uint8)), be.alloc(t * r * n * 4)]
+    l = matmul_id_launch(fmt, t, r, e, n, k)
+    be.prepare([l])
+    be.execute([l], bufs)
+    got = bufs[3].download().view(np.float32).reshape(t, r, n)
+    assert max_rel(got, want) <= 2e-5
+    for gemv in ("generic", "fast"):   # the any-shape kernel gives the same
+        be.set_option("gemv", gemv)
+        be.execute([l], bufs)
+        assert max_rel(bufs[3].download().view(np.float32).reshape(t, r, n), want) <= 2e-5
+    bad = ids.copy()
+    bad[-1] = e
+    bufs[2].write(0, bad.view(np.uint8))
+    with pytest.raises(lp.LapidError) as err:
+        be.execute([l], bufs)
+    assert err.value.code == "index_out_of_range"
+    bufs[2].write(0, ids.view(np.uint8))
+    be.execute([l], bufs)
+    assert max_rel(bufs[3].download().view(np.float32).reshape(t, r, n), want) <= 2e-5
+
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("t,r,e,n,k", [(40, 3, 5, 24, 512), (70, 2, 4, 200, 256), (300, 4, 8, 136, 1024), (9, 1, 3, 64, 256)])
+def test_matmul_id_prefill_exact(be, oracle, fmt, name, t, r, e, n, k):
+    """t > 8: float activations for every expert (moe.rs:107-109). With gemm=f32 the grouped exact kernel
+    is bit-identical to the oracle's per-expert f32 matmul, whatever tile a pair lands in."""
+    from lapid_b200.backend import matmul_id_launch
+    stack = _expert_stack(oracle, fmt, e, n, k, 90)
+    x = O.normal(71, t * k, 1.0)
+    ids = np.array([(i * 7 + i // r) % e for i in range(t * r)], np.int32)
+    if e > 4:
+        ids[ids == 1] = 2        # an expert nobody uses
+    want = oracle.matmul_id(int(fmt), x, stack, ids, t, r, e, n, k)
+    bufs = [be.upload(x), be.upload(stack), be.upload(ids.view(np.uint8)), be.alloc(t * r * n * 4)]
+    l = matmul_id_launch(fmt, t, r, e, n, k)
+    be.set_option("gemm", "f32")
+    try:
+        for _ in range(2):
+            be.execute([l], bufs)
+            got = bufs[3].download().view(np.float32).reshape(t, r, n)
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        bad = ids.copy()
+        bad[3] = -2
+        bufs[2].write(0, bad.view(np.uint8))
+        with pytest.raises(lp.LapidError) as err:
+            be.execute([l], bufs)
+        assert err.value.code == "index_out_of_range"
+    finally:
+        be.set_option("gemm", "tc")
+
+
+@pytest.mark.parametrize("fmt,name", [(lp.DType.Q4K, "q4_k"), (lp.DType.Q6K, "q6_k")])
+@pytest.mark.parametrize("t,r,e,n,k", [(64, 2, 4, 256, 2048), (200, 4, 8, 384, 4096), (1024, 2, 4, 128, 2048)])
+def test_matmul_id_prefill_tensor_core(be, oracle, fmt, name, t, r, e, n, k):
+    """The same launch on the tensor cores (bf16 operands): the bounds of the dense prefill kernel
+    against the exact result."""
+    from lapid_b200.backend import matmul_id_launch
+    stack = _expert_stack(oracle, fmt, e, n, k, 110)
+    x = O.normal(72, t * k, 1.0)
+    rng = np.random.default_rng(5)
+    ids = np.stack([rng.permutation(e)[:r] for _ in range(t)]).astype(np.int32).reshape(-1)
+    want = oracle.matmul_id(int(fmt), x, stack, ids, t, r, e, n, k)
+    bufs = [be.upload(x), be.upload(stack), be.upload(ids.view(np.uint8)), be.alloc(t * r * n * 4)]
+    l = matmul_id_launch(fmt, t, r, e, n, k)
+    be.take_launch_count()
+    be.execute([l], bufs)
+    assert be.take_launch_count() == 3        # route, gather to bf16, grouped tensor-core GEMM
+    got = bufs[3].download().view(np.float32).reshape(t, r, n)
+    assert rel_l2(got, want) <= 4e-3 and max_rel(got, want) <= 2e-2
+
+
 def test_zero_sized_launches(be, oracle):
     qb = oracle.quantize(O.Q4_K, O.normal(1, 4 * 256, 0.02), 4, 256)
     out = run_matmul(be, lp.DType.Q4K, np.zeros(1, np.float32), qb[:256], 2, 4, 0, out=np.full(8, 9.0, np.float32))
@@ -640,7 +732,7 @@ def test_launch_validation_codes(be, oracle):
     assert code(dc.replace(ok, inputs=(0, 1, 1))) == "invalid_launch"       # 3 inputs without an epilogue
     assert code(dc.replace(ok, inputs=(0, 7))) == "invalid_launch"          # BufId out of range
     assert code(dc.replace(ok, inputs=(2, 1))) == "buffer_aliasing"         # input is the output
-    assert code(dc.replace(ok, kind=4)) == "unsupported"
+    assert code(dc.replace(ok, kind=9)) == "unsupported"
     # the device stays usable after every rejected launch
     be.execute([ok], bufs)
     want, _ = oracle.matmul(O.Q4_K, a, qb, n, k, m=m)

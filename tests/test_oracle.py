@@ -343,6 +343,32 @@ def test_strided_output_view_and_validation(oracle):
     assert out.size == 8 and not out.any()
 
 
+@pytest.mark.parametrize("fmt,k", [(INT8, 96), (Q4_K, 256), (Q6_K, 512)])
+def test_matmul_id_matches_dequantized_f64(oracle, fmt, k):
+    """`matmul_id_quant` (crates/lapid-cpu/src/tests.rs:350-383) for the three formats of this path:
+    5 experts of [24, k], decode-sized (int8 activations, 2e-2) and prefill-sized (exact, 1e-5) launches
+    against the f64 product with the dequantized matrices, same id pattern; bad ids are refused."""
+    e, n = 5, 24
+    one = oracle.layout(fmt, n, k).total
+    stack = np.zeros(e * one, np.uint8)
+    wf = []
+    for x in range(e):
+        q = oracle.quantize(fmt, O.normal(9 + x, n * k, 0.1), n, k)
+        stack[x * one:x * one + q.size] = q
+        wf.append(oracle.dequantize(fmt, q, n, k).reshape(n, k).astype(np.float64))
+    for t, r in [(1, 2), (40, 3)]:
+        x = O.normal(33, t * k, 1.0).reshape(t, k)
+        ids = np.array([(i * 7 + i // r) % e for i in range(t * r)], np.int32)
+        want = np.stack([wf[ids[i]] @ x[i // r].astype(np.float64) for i in range(t * r)]).astype(np.float32)
+        got = oracle.matmul_id(fmt, x, stack, ids, t, r, e, n, k).reshape(t * r, n)
+        err = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want)
+        assert err < (2e-2 if t * r <= 8 else 1e-5), (fmt, t, r, err)
+    with pytest.raises(O.OracleError) as ex:
+        oracle.matmul_id(fmt, x, stack, np.full(t * r, e, np.int32), t, r, e, n, k)
+    assert ex.value.code == "index_out_of_range"
+    assert oracle.matmul_id(fmt, x, stack, ids, 0, r, e, n, k).size == 0
+
+
 def test_seeded_generator_is_counter_based():
     a = O.normal(3, 1000, 0.02)
     b = O.normal(3, 400, 0.02, start=600)
