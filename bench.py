@@ -326,6 +326,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             stack_obj = {"error": f"{type(e).__name__}: {e}"[:300]}
         torch.cuda.empty_cache()
 
+    moe_rows = None
+    if world == 1 and not args.no_moe:
+        try:
+            moe_rows = measure_moe(be, stream, dev, quantized, peak)
+        except Exception as e:  # reported, never fatal for the headline line
+            moe_rows = {"error": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.empty_cache()
+
     # ---- per-case timing over cold copies (rank 0, N = 1 only): the kbench method scaled to B200's L2
     case_rows = []
     roof = None
@@ -416,6 +424,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         line["prefill"] = prefill_rows
     if stack_obj:
         line["stack8b"] = stack_obj
+    if moe_rows:
+        line["matmul_id"] = moe_rows
     if tp_obj:
         line["tp70b"] = tp_obj
     if world == 1 and not args.no_cpu:
@@ -485,6 +495,70 @@ def measure_prefill(be, stream, dev, base, quantized):
                          "frac_burst": round(tf / burst, 4), "frac_sustained": round(tf / sustained, 4),
                          "operands": "bf16 (f32 accumulate in TMEM)"})
         del pool
+    return rows
+
+
+def measure_moe(be, stream, dev, quantized, peak):
+    """Kernel::MatMulId (the mixture-of-experts matmul) on two expert-stack shapes, Q4_K: 8 experts of
+    14336 x 4096 with 2 slots per token, and 128 experts of 768 x 2048 with 8 slots. Decode launches
+    (int8-activation arithmetic) report algorithmic GB/s = (routed experts' bytes + activations + outputs)
+    / time, prefill launches (device-side routing + grouped tcgen05 GEMM) report TFLOP/s = 2 * pairs * n * k
+    / time. Several copies of the stack (or disjoint id sets) are cycled so that weights come from HBM."""
+    import torch
+    from lapid_b200.backend import matmul_id_launch
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            burst = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        burst = 1590.0
+    rows = []
+    for tag, e, r, n, k, copies in (("8x[14336,4096] top-2", 8, 2, 14336, 4096, 2), ("128x[768,2048] top-8", 128, 8, 768, 2048, 5)):
+        one = weight_bytes(6, n, k)
+        stack = quantized(6, e * n, k, 900 + e)          # K-quant stacks are dense: [e*n, k] quantized as one matrix
+        pool = stack.repeat(copies).view(copies, -1)
+        for t in (1, 4, 512):
+            pairs = t * r
+            g = torch.Generator(device="cpu")
+            g.manual_seed(17 * t + e)
+            x = torch.randn(t * k, device=dev)
+            out = torch.zeros(pairs * n, device=dev)
+            sets = 4
+            id_sets = []
+            for s_ in range(sets):       # distinct experts per token; decode sets are disjoint where the stack allows
+                rows_ = [((torch.randperm(e, generator=g)[:r] if t > 1 else (torch.arange(r) + s_ * r) % e)) for _ in range(t)]
+                id_sets.append(torch.stack(rows_).to(torch.int32).reshape(-1).to(dev))
+            torch.cuda.synchronize()
+            bufs = [be.wrap_tensor(x), be.wrap_tensor(out)] + [be.wrap_tensor(pool[c]) for c in range(copies)] + \
+                   [be.wrap_tensor(i_) for i_ in id_sets]
+            ls = [matmul_id_launch(6, t, r, e, n, k, inputs=(0, 2 + (j % copies), 2 + copies + (j % sets)), output=1)
+                  for j in range(copies * sets)]
+            be.prepare(ls)
+            run = be.packed(ls, bufs)
+            be.take_launch_count()
+            with torch.cuda.stream(stream):
+                run()
+            stream.synchronize()
+            kernels = be.take_launch_count() // len(ls)
+            graph = torch.cuda.CUDAGraph()   # decode-sized launches are shorter than a host-side launch
+            with torch.cuda.graph(graph, stream=stream):
+                be.set_stream(torch.cuda.current_stream().cuda_stream)
+                run()
+            be.set_stream(stream.cuda_stream)
+            ms = _event_time(stream, graph.replay, 5) / len(ls)
+            del graph, run
+            used = min(pairs, e) if t > 1 else r
+            row = {"stack": tag, "fmt": "q4_k", "t": t, "r": r, "us": round(ms * 1e3, 2), "kernels_per_launch": kernels}
+            if t <= 8:
+                b = used * one + 4 * t * k + 4 * pairs * n
+                row.update({"path": "decode (int8 activations)", "gbs": round(b / (ms * 1e-3) / 1e9, 1),
+                            "frac_of_measured_hbm": round(b / (ms * 1e-3) / 1e9 / peak, 4)})
+            else:
+                tf = 2.0 * pairs * n * k / (ms * 1e-3) / 1e12
+                row.update({"path": "prefill (routed, bf16 tensor cores)", "tflops": round(tf, 1), "frac_burst": round(tf / burst, 4)})
+            rows.append(row)
+            del bufs, ls
+        del pool, stack
+        torch.cuda.empty_cache()
     return rows
 
 
@@ -677,6 +751,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM rows")
     ap.add_argument("--no-tp", action="store_true", help="skip the 70B-shaped tensor-parallel layer stack")
+    ap.add_argument("--no-moe", action="store_true", help="skip the MatMulId (mixture-of-experts) measurements")
     ap.add_argument("--no-stack", action="store_true", help="skip the 32-layer 8B-shaped projection stack")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -455,7 +455,9 @@ MoePlan plan_matmul_id(const lapid_b200_device &dev, const lapid_b200_launch &l)
         p.tc = !dev.gemm_f32 && lb::qgemm_tc_moe_supported(l.b_dtype, p.e, l.n, l.k, nullptr);
         if (p.tc) {
             const uint64_t avg = p.t * p.r / (p.e ? p.e : 1);
-            p.mt = avg <= 64 ? 64 : avg <= 160 ? 128 : 256;
+            // the grouped GEMM is bound by dequantization, which is paid once per (weight tile, activation tile):
+            // prefer the tile that holds an expert's expected rows (plus the spread of a random routing) in one piece
+            p.mt = avg <= 48 ? 64 : avg <= 100 ? 128 : 256;
         }
         if ((uint64_t)lb::moe_max_tiles(p.t * p.r, p.e, p.mt) * p.mt >= lim) fail("too_large", "b200 matmul_id: tile space exceeds 32-bit indexing");
         p.route_bytes = lb::moe_route_bytes(p.t * p.r, p.e, p.mt);
