@@ -669,12 +669,14 @@ def measure_tp70b(be, stream, dev, rank, world, quantized):
     # decode_b1: the row-parallel GEMVs push their partials from their epilogue and the following
     # rms_norm sums them (no all-reduce kernel); _allreduce_kernel: the library's stand-alone one-shot
     # all-reduce; _nccl: the library collective, for comparison
-    variants = [(1, "decode_b1", peer, True), (512, "prefill_m512", peer, False)]
+    # _prepass: the same stack with a quantizing pre-pass kernel in front of every projection group instead
+    # of the rms_norm / silu_mul kernels writing the quantized operand themselves
+    variants = [(1, "decode_b1", peer, True, True), (1, "decode_b1_prepass", peer, True, False), (512, "prefill_m512", peer, False, True)]
     if world > 1 and peer is not None:
-        variants.insert(1, (1, "decode_b1_allreduce_kernel", peer, False))
-        variants.insert(2, (1, "decode_b1_nccl", None, False))
-    for m, key, reducer, fused in variants:
-        layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats, peer_all_reduce=reducer, fused=fused)
+        variants.insert(2, (1, "decode_b1_allreduce_kernel", peer, False, True))
+        variants.insert(3, (1, "decode_b1_nccl", None, False, True))
+    for m, key, reducer, fused, fuse_act in variants:
+        layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats, peer_all_reduce=reducer, fused=fused, fuse_act=fuse_act)
         layers.h.normal_()
         torch.cuda.synchronize()
         run = lambda: layers.token(n_layers)

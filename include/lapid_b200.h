@@ -62,6 +62,9 @@ typedef int32_t lapid_b200_status;
 #define LAPID_B200_DTYPE_INT8 4
 #define LAPID_B200_DTYPE_Q4_K 6
 #define LAPID_B200_DTYPE_Q6_K 8
+/* Not a lapid dtype: as a launch's a_dtype it says that input 0 is an activation operand already
+ * quantized for this launch by lapid_b200_rms_norm_act / lapid_b200_silu_mul_act (see there). */
+#define LAPID_B200_DTYPE_ACT_Q8 100
 
 typedef struct lapid_b200_device lapid_b200_device;
 typedef struct lapid_b200_buffer lapid_b200_buffer;
@@ -158,7 +161,7 @@ typedef struct lapid_b200_view3 {
 
 typedef struct lapid_b200_launch {
     int32_t kind;         /* LAPID_B200_KERNEL_MATMUL (the fields below describe it), LAPID_B200_KERNEL_GATHER or LAPID_B200_KERNEL_MATMUL_ID (see above) */
-    int32_t a_dtype;      /* MatMulSpec.a_dtype: F32 */
+    int32_t a_dtype;      /* MatMulSpec.a_dtype: F32 (or LAPID_B200_DTYPE_ACT_Q8, see above) */
     int32_t b_dtype;      /* MatMulSpec.b_dtype: INT8 | Q4_K | Q6_K */
     int32_t out_dtype;    /* MatMulSpec.out_dtype: F32 */
     int32_t b_transposed; /* must be 1 for a quantized B */
@@ -260,6 +263,32 @@ LAPID_B200_API lapid_b200_status lapid_b200_rms_norm(lapid_b200_device *dev, lap
                                                      lapid_b200_buffer *out, uint64_t rows, uint64_t cols, float eps);
 LAPID_B200_API lapid_b200_status lapid_b200_silu_mul(lapid_b200_device *dev, lapid_b200_buffer *gate, lapid_b200_buffer *up,
                                                      lapid_b200_buffer *out, uint64_t count);
+
+/* ---- producers that quantize for the projection that follows (RMSNorm + activation-quant prologue) */
+/* A decode launch (batch*m <= 8) multiplies int8-quantized activation rows; by default `execute` makes
+ * them from the f32 operand with a small pre-pass kernel per distinct operand. The `_act` forms of the
+ * glue kernels write their result in that quantized form as well (same arithmetic, bit for bit), and a
+ * launch with a_dtype = LAPID_B200_DTYPE_ACT_Q8 and input 0 = that buffer skips its pre-pass.
+ *   lapid_b200_act_layout: for a decode MatMul launch (a_dtype F32 or ACT_Q8), the layout code its kernel
+ *     reads and the bytes of the quantized operand; fails with "invalid_launch" for other launches.
+ *     Launches with the same (layout, batch*m, k) can share one quantized operand (q/k/v; gate/up).
+ *   *_act: as the plain forms, plus `qact` (>= the bytes above, 16-byte aligned) written in `layout`;
+ *     rows*cols of the producer = batch*m and k of the consumer; cols a multiple of 256 (rms_norm:
+ *     up to 16384 and cols/32 a multiple of its cluster size, which holds for multiples of 1024).
+ *     qact NULL: exactly the plain form. */
+LAPID_B200_API lapid_b200_status lapid_b200_act_layout(lapid_b200_device *dev, const lapid_b200_launch *launch, int32_t *layout,
+                                                       uint64_t *bytes);
+LAPID_B200_API lapid_b200_status lapid_b200_rms_norm_act(lapid_b200_device *dev, lapid_b200_buffer *x, lapid_b200_buffer *residual,
+                                                         lapid_b200_buffer *weight, lapid_b200_buffer *sum_out,
+                                                         lapid_b200_buffer *out, uint64_t rows, uint64_t cols, float eps,
+                                                         lapid_b200_buffer *qact, int32_t layout);
+LAPID_B200_API lapid_b200_status lapid_b200_tp_rms_norm_act(lapid_b200_tp_comm *comm, lapid_b200_buffer *residual,
+                                                            lapid_b200_buffer *weight, lapid_b200_buffer *sum_out,
+                                                            lapid_b200_buffer *out, uint64_t rows, uint64_t cols, float eps,
+                                                            lapid_b200_buffer *qact, int32_t layout);
+LAPID_B200_API lapid_b200_status lapid_b200_silu_mul_act(lapid_b200_device *dev, lapid_b200_buffer *gate, lapid_b200_buffer *up,
+                                                         lapid_b200_buffer *out, uint64_t rows, uint64_t cols,
+                                                         lapid_b200_buffer *qact, int32_t layout);
 
 /* ---- decode without allocation ------------------------------------------------------------ */
 /* This entry point has no counterpart in the reference. It exists for hosts that may not allocate

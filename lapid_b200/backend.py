@@ -27,6 +27,7 @@ class DType(enum.IntEnum):
     Int8 = 4
     Q4K = 6
     Q6K = 8
+    ACT_Q8 = 100  # not a lapid dtype: an activation operand quantized by its producer (LAPID_B200_DTYPE_ACT_Q8)
 
 
 class Epilogue(enum.IntEnum):
@@ -114,11 +115,13 @@ class Launch:
 
 
 def matmul_launch(b_dtype: DType, m: int, n: int, k: int, *, batch: int = 1, a_row_stride: Optional[int] = None,
-                  inputs=(0, 1), output=2, bias_input: Optional[int] = None, out: Optional[MatView] = None) -> Launch:
+                  inputs=(0, 1), output=2, bias_input: Optional[int] = None, out: Optional[MatView] = None,
+                  a_quantized: bool = False) -> Launch:
     """The launch lapid lowers ``x.matmul_t(w)`` to: contiguous A (or padded rows), quantized
-    transposed B, contiguous f32 output (the `mm` helper of kbench_tests.rs:86-107)."""
+    transposed B, contiguous f32 output (the `mm` helper of kbench_tests.rs:86-107).
+    ``a_quantized``: input 0 is the quantized operand a producer wrote for this launch (``Backend.act_layout``)."""
     rs = a_row_stride if a_row_stride is not None else k
-    spec = MatMulSpec(b_dtype=DType(b_dtype), extra_dtypes=(DType.F32,) if bias_input is not None else (),
+    spec = MatMulSpec(a_dtype=DType.ACT_Q8 if a_quantized else DType.F32, b_dtype=DType(b_dtype), extra_dtypes=(DType.F32,) if bias_input is not None else (),
                       epilogue=Epilogue.ADD if bias_input is not None else Epilogue.NONE)
     dims = MatMulDims(batch, m, n, k, a=MatView(0, m * rs, rs), b=MatView(0, 0, k), out=out or MatView.contiguous(m, n),
                       extra_views=(View(0, (0, 0, 1)),) if bias_input is not None else ())
@@ -279,13 +282,26 @@ class Backend:
 
     # ---- the steps between projections (queued on the device's stream, not waited for)
     def rms_norm(self, x: Buffer, out: Buffer, rows: int, cols: int, eps: float = 1e-6, residual: Optional[Buffer] = None,
-                 weight: Optional[Buffer] = None, sum_out: Optional[Buffer] = None) -> None:
-        """``out = h * rsqrt(mean(h*h) + eps) (* weight)`` with ``h = x (+ residual)``; ``sum_out`` receives h."""
+                 weight: Optional[Buffer] = None, sum_out: Optional[Buffer] = None, qact: Optional[Buffer] = None,
+                 layout: int = 0) -> None:
+        """``out = h * rsqrt(mean(h*h) + eps) (* weight)`` with ``h = x (+ residual)``; ``sum_out`` receives h.
+        ``qact``: also written as the quantized activation operand (``act_layout``) of the launches that read ``out``."""
         h = lambda b: b._h if b is not None else None
-        check(_lib.lib().lapid_b200_rms_norm(self._h, x._h, h(residual), h(weight), h(sum_out), out._h, rows, cols, eps))
+        check(_lib.lib().lapid_b200_rms_norm_act(self._h, x._h, h(residual), h(weight), h(sum_out), out._h, rows, cols, eps,
+                                                 h(qact), layout))
 
-    def silu_mul(self, gate: Buffer, up: Buffer, out: Buffer, count: int) -> None:
-        check(_lib.lib().lapid_b200_silu_mul(self._h, gate._h, up._h, out._h, count))
+    def silu_mul(self, gate: Buffer, up: Buffer, out: Buffer, count: int, *, rows: int = 1, qact: Optional[Buffer] = None,
+                 layout: int = 0) -> None:
+        """``out = silu(gate) * up`` over ``count`` f32 (``rows`` rows of ``count // rows``); ``qact`` as in ``rms_norm``."""
+        check(_lib.lib().lapid_b200_silu_mul_act(self._h, gate._h, up._h, out._h, rows, count // rows,
+                                                 qact._h if qact is not None else None, layout))
+
+    def act_layout(self, launch: "Launch") -> tuple:
+        """``(layout, bytes)`` of the quantized activation operand a decode launch reads (``lapid_b200_act_layout``)."""
+        lay, nbytes = C.c_int32(0), C.c_uint64(0)
+        c = launch.to_c()
+        check(_lib.lib().lapid_b200_act_layout(self._h, C.byref(c), C.byref(lay), C.byref(nbytes)))
+        return int(lay.value), int(nbytes.value)
 
     def take_launch_count(self) -> int:
         return int(_lib.lib().lapid_b200_take_launch_count(self._h))

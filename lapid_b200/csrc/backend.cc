@@ -311,7 +311,7 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
     if (l.kind != LAPID_B200_KERNEL_MATMUL) fail("unsupported", "kernel kind " + std::to_string(l.kind) + " is not MatMul");
     if (!is_quant(l.b_dtype))
         fail("unsupported_dtype", "b200 matmul: b dtype " + std::to_string(l.b_dtype) + " (want int8, q4_k or q6_k)");
-    if (l.a_dtype != LAPID_B200_DTYPE_F32 || l.out_dtype != LAPID_B200_DTYPE_F32)
+    if ((l.a_dtype != LAPID_B200_DTYPE_F32 && l.a_dtype != LAPID_B200_DTYPE_ACT_Q8) || l.out_dtype != LAPID_B200_DTYPE_F32)
         fail("unsupported_dtype", "b200 matmul: a and out must be f32");
     if (l.epilogue != LAPID_B200_EPILOGUE_NONE && l.epilogue != LAPID_B200_EPILOGUE_ADD)
         fail("unsupported", "b200 matmul: epilogue " + std::to_string(l.epilogue));
@@ -339,6 +339,9 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
         fail("shape_mismatch", "b200 matmul: quantized B row stride " + std::to_string(l.b.row_stride) + ", expected k = " +
                                    std::to_string(l.k));
     p.gemv = p.rows <= dev.gemv_max_rows;
+    if (l.a_dtype == LAPID_B200_DTYPE_ACT_Q8 && (!p.gemv || l.k % 256 != 0))
+        fail("invalid_launch", "b200 matmul: a quantized activation operand needs batch*m <= " + std::to_string(dev.gemv_max_rows) +
+                                   " and k a multiple of 256");
     if (p.gemv) {
         size_t qa = align_up((uint64_t)p.rows * l.k, 256);
         size_t sc = align_up((uint64_t)p.rows * (l.k / 32) * 4, 256);
@@ -360,6 +363,33 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
         if (p.tc) p.scratch = align_up(lb::qgemm_tc_scratch_bytes(p.rows, (uint32_t)l.n, (uint32_t)l.k, dev.sm_count), 256);
     }
     return p;
+}
+
+// The quantized activation operand of a decode launch inside `base`: planes, records or tiles.
+lb::ActOut act_out_at(void *base, int records, uint32_t rows, uint32_t k) {
+    lb::ActOut o{};
+    o.qa = (int8_t *)base;
+    o.da = (float *)((char *)base + lb::act_plane_bytes(rows, k));
+    o.bs = (float *)((char *)base + lb::act_plane_bytes(rows, k) + lb::act_scale_bytes(rows, k));
+    o.records = records;
+    o.rows = rows;
+    o.k = k;
+    return o;
+}
+
+// What the `_act` producers need to know about the buffer they fill.
+lb::ActOut act_out_checked(lapid_b200_device *dev, lapid_b200_buffer *qact, int32_t layout, uint64_t rows, uint64_t cols, const char *who) {
+    lb::ActOut o{};
+    if (!qact) return o;
+    if (qact->dev != dev) fail("wrong_backend", std::string(who) + ": qact belongs to another device");
+    if (layout < 0 || layout > 2) fail("invalid_argument", std::string(who) + ": layout must be 0, 1 or 2");
+    if (rows == 0 || rows > 8 || cols % 256 != 0 || cols == 0 || cols >= (1ull << 31))
+        fail("invalid_launch", std::string(who) + ": a quantized copy needs rows in 1..8 and cols a multiple of 256");
+    const size_t planes = lb::act_plane_bytes((uint32_t)rows, (uint32_t)cols) + 2 * lb::act_scale_bytes((uint32_t)rows, (uint32_t)cols);
+    const size_t need_b = layout == 0 ? planes : layout == 1 ? rows * (cols / 256) * lb::REC : lb::qgemv_q4k_mma_act_bytes((uint32_t)rows, (uint32_t)cols);
+    if (qact->bytes < need_b) fail("out_of_bounds", std::string(who) + " qact: needs " + std::to_string(need_b) + " bytes, buffer has " + std::to_string(qact->bytes));
+    if ((uintptr_t)qact->ptr & 15) fail("invalid_launch", std::string(who) + ": qact must be 16-byte aligned");
+    return act_out_at(qact->ptr, layout, (uint32_t)rows, (uint32_t)cols);
 }
 
 // `tp` not null: a launch that takes one of the K-quant fast decode kernels hands its result to the
@@ -605,7 +635,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
     uint64_t last = l.out.offset + (l.batch - 1) * l.out.batch_stride + (l.m - 1) * l.out.row_stride + l.n;
     if (out_elems < last)
         fail("out_of_bounds", "b200 matmul: output holds " + std::to_string(out_elems) + " < " + std::to_string(last) + " elements");
-    if (l.k > 0) {
+    if (l.k > 0 && l.a_dtype != LAPID_B200_DTYPE_ACT_Q8) {
         uint64_t alast = l.a.offset + (l.batch - 1) * l.a.batch_stride + (l.m - 1) * l.a.row_stride + l.k;
         if (ins[0]->bytes / 4 < alast)
             fail("out_of_bounds", "b200 matmul a: view reaches element " + std::to_string(alast) + ", buffer holds " +
@@ -653,12 +683,24 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
 
     if (p.gemv) {
         ActSlot local;
-        if (!slot) {  // not planned by the caller: a private slot at the start of the scratch
-            dev.ensure_scratch(p.scratch);
+        char *base = nullptr;
+        if (l.a_dtype == LAPID_B200_DTYPE_ACT_Q8) {  // quantized by its producer (the `_act` glue kernels): no pre-pass
+            if (ins[0]->bytes < p.scratch)
+                fail("out_of_bounds", "b200 matmul: quantized activation operand needs " + std::to_string(p.scratch) + " bytes, buffer has " +
+                                          std::to_string(ins[0]->bytes));
+            if ((uintptr_t)ins[0]->ptr & 15) fail("invalid_launch", "b200 matmul: quantized activation operand must be 16-byte aligned");
             local.records = p.records();
+            local.done = true;
             slot = &local;
+            base = (char *)ins[0]->ptr;
+        } else {
+            if (!slot) {  // not planned by the caller: a private slot at the start of the scratch
+                dev.ensure_scratch(p.scratch);
+                local.records = p.records();
+                slot = &local;
+            }
+            base = (char *)dev.scratch + slot->offset;
         }
-        char *base = (char *)dev.scratch + slot->offset;
         size_t qa_b = align_up((uint64_t)p.rows * l.k, 256), sc_b = align_up((uint64_t)p.rows * (l.k / 32) * 4, 256);
         lb::ActQuantArgs q{};
         q.a = (const float *)ins[0]->ptr;
@@ -678,7 +720,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         g.qa = q.qa;
         g.da = q.da;
         g.bs = q.bs;
-        g.a = q.a;
+        g.a = l.a_dtype == LAPID_B200_DTYPE_ACT_Q8 ? nullptr : q.a;
         g.a_off = q.a_off;
         g.a_bs = q.a_bs;
         g.a_rs = q.a_rs;
@@ -829,7 +871,7 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
             Plan p = plan_launch(*dev, l);
             lapid_b200_buffer *ab = l.n_inputs > 0 && l.inputs[0] < nbuf ? buffers[l.inputs[0]] : nullptr;
             lapid_b200_buffer *ob = l.output < nbuf ? buffers[l.output] : nullptr;
-            if (p.gemv && ab) {
+            if (p.gemv && ab && l.a_dtype != LAPID_B200_DTYPE_ACT_Q8) {
                 ActSlot key;
                 key.ptr = ab->ptr;
                 key.off = l.a.offset;
@@ -1364,6 +1406,12 @@ lapid_b200_status lapid_b200_tp_matmul_push(lapid_b200_tp_comm *comm, const lapi
 // rms_norm whose x is the sum of what the ranks pushed for the call in progress; closes the call.
 lapid_b200_status lapid_b200_tp_rms_norm(lapid_b200_tp_comm *comm, lapid_b200_buffer *residual, lapid_b200_buffer *weight,
                                          lapid_b200_buffer *sum_out, lapid_b200_buffer *out, uint64_t rows, uint64_t cols, float eps) {
+    return lapid_b200_tp_rms_norm_act(comm, residual, weight, sum_out, out, rows, cols, eps, nullptr, 0);
+}
+
+lapid_b200_status lapid_b200_tp_rms_norm_act(lapid_b200_tp_comm *comm, lapid_b200_buffer *residual, lapid_b200_buffer *weight,
+                                             lapid_b200_buffer *sum_out, lapid_b200_buffer *out, uint64_t rows, uint64_t cols, float eps,
+                                             lapid_b200_buffer *qact, int32_t layout) {
     return guard([&] {
         if (!comm) fail("invalid_argument", "comm is NULL");
         need(out, "out");
@@ -1394,6 +1442,8 @@ lapid_b200_status lapid_b200_tp_rms_norm(lapid_b200_tp_comm *comm, lapid_b200_bu
         a.rows = (uint32_t)rows;
         a.cols = (uint32_t)cols;
         a.eps = eps;
+        a.q = act_out_checked(dev, qact, layout, rows, cols, "tp rms_norm");
+        if (qact && !lb::rms_norm_quant_ok((uint32_t)cols)) fail("invalid_launch", "tp rms_norm: cols " + std::to_string(cols) + " cannot be quantized in the kernel");
         cuda_check(lb::launch_rms_norm(a, dev->pdl, dev->stream), "tp rms_norm launch");
         dev->launches++;
     });
@@ -1403,6 +1453,12 @@ lapid_b200_status lapid_b200_tp_rms_norm(lapid_b200_tp_comm *comm, lapid_b200_bu
 lapid_b200_status lapid_b200_rms_norm(lapid_b200_device *dev, lapid_b200_buffer *x, lapid_b200_buffer *residual,
                                       lapid_b200_buffer *weight, lapid_b200_buffer *sum_out, lapid_b200_buffer *out,
                                       uint64_t rows, uint64_t cols, float eps) {
+    return lapid_b200_rms_norm_act(dev, x, residual, weight, sum_out, out, rows, cols, eps, nullptr, 0);
+}
+
+lapid_b200_status lapid_b200_rms_norm_act(lapid_b200_device *dev, lapid_b200_buffer *x, lapid_b200_buffer *residual,
+                                          lapid_b200_buffer *weight, lapid_b200_buffer *sum_out, lapid_b200_buffer *out,
+                                          uint64_t rows, uint64_t cols, float eps, lapid_b200_buffer *qact, int32_t layout) {
     return guard([&] {
         need(dev);
         need(x, "x");
@@ -1433,6 +1489,8 @@ lapid_b200_status lapid_b200_rms_norm(lapid_b200_device *dev, lapid_b200_buffer 
         a.rows = (uint32_t)rows;
         a.cols = (uint32_t)cols;
         a.eps = eps;
+        a.q = act_out_checked(dev, qact, layout, rows, cols, "rms_norm");
+        if (qact && !lb::rms_norm_quant_ok((uint32_t)cols)) fail("invalid_launch", "rms_norm: cols " + std::to_string(cols) + " cannot be quantized in the kernel");
         cuda_check(lb::launch_rms_norm(a, dev->pdl, dev->stream), "rms_norm launch");
         dev->launches++;
     });
@@ -1440,6 +1498,26 @@ lapid_b200_status lapid_b200_rms_norm(lapid_b200_device *dev, lapid_b200_buffer 
 
 lapid_b200_status lapid_b200_silu_mul(lapid_b200_device *dev, lapid_b200_buffer *gate, lapid_b200_buffer *up,
                                       lapid_b200_buffer *out, uint64_t count) {
+    return lapid_b200_silu_mul_act(dev, gate, up, out, 1, count, nullptr, 0);
+}
+
+lapid_b200_status lapid_b200_act_layout(lapid_b200_device *dev, const lapid_b200_launch *launch, int32_t *layout, uint64_t *bytes) {
+    return guard([&] {
+        need(dev);
+        if (!launch || !layout || !bytes) fail("invalid_argument", "launch, layout or bytes is NULL");
+        if (launch->kind != LAPID_B200_KERNEL_MATMUL) fail("invalid_launch", "act_layout: not a MatMul launch");
+        Plan p = plan_launch(*dev, *launch);
+        if (!p.gemv || p.noop || p.zero_k || launch->k % 256 != 0)
+            fail("invalid_launch", "act_layout: the launch does not take a quantized activation operand (batch*m <= " +
+                                       std::to_string(dev->gemv_max_rows) + ", k a multiple of 256)");
+        *layout = p.records();
+        *bytes = p.scratch;
+    });
+}
+
+lapid_b200_status lapid_b200_silu_mul_act(lapid_b200_device *dev, lapid_b200_buffer *gate, lapid_b200_buffer *up,
+                                          lapid_b200_buffer *out, uint64_t rows, uint64_t cols, lapid_b200_buffer *qact, int32_t layout) {
+    const uint64_t count = rows * cols;
     return guard([&] {
         need(dev);
         need(gate, "gate");
@@ -1453,8 +1531,9 @@ lapid_b200_status lapid_b200_silu_mul(lapid_b200_device *dev, lapid_b200_buffer 
         }
         std::lock_guard<std::mutex> lock(dev->mu);
         dev->make_current();
-        cuda_check(lb::launch_silu_mul((const float *)gate->ptr, (const float *)up->ptr, (float *)out->ptr, count, dev->sm_count,
-                                       dev->pdl, dev->stream), "silu_mul launch");
+        lb::ActOut q = act_out_checked(dev, qact, layout, rows, cols, "silu_mul");
+        cuda_check(lb::launch_silu_mul((const float *)gate->ptr, (const float *)up->ptr, (float *)out->ptr, count, (uint32_t)(qact ? cols : 0), q,
+                                       dev->sm_count, dev->pdl, dev->stream), "silu_mul launch");
         dev->launches++;
     });
 }

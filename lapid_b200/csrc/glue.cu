@@ -18,6 +18,7 @@
 // order of the sum of squares differs): the tests hold them to 1e-5 relative against f64.
 #include <cooperative_groups.h>
 
+#include "actquant.cuh"
 #include "common.cuh"
 #include "kernels.h"
 #include "tp_ll.cuh"
@@ -111,8 +112,10 @@ __global__ void __launch_bounds__(GLUE_THREADS) rms_norm_kernel(RmsNormArgs p) {
 #pragma unroll
     for (int i = 0; i < GLUE_MAX_VEC; i++) {
         const uint32_t c = c_lo + threadIdx.x + i * GLUE_THREADS;
-        if (c < c_hi) {
-            float4 a = v[i];
+        const bool active = c < c_hi;
+        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (active) {
+            a = v[i];
             a.x *= rstd;
             a.y *= rstd;
             a.z *= rstd;
@@ -126,6 +129,9 @@ __global__ void __launch_bounds__(GLUE_THREADS) rms_norm_kernel(RmsNormArgs p) {
             }
             ((float4 *)(p.out + (size_t)row * p.cols))[c] = a;
         }
+        // the same values as the int8 operand of the GEMVs that read `out` (warp-uniform branch: whole warps of
+        // the CTA's column range take it together, lanes past the range pass active = false)
+        if (p.q.qa && c_lo + (threadIdx.x & ~31u) + i * GLUE_THREADS < c_hi) act_quant_quad(p.q, active, row, 4 * c, a);
     }
     if (parts > 1) cluster.sync();  // no CTA leaves while a neighbour may still read its partial sum
     if (p.tp) {  // the last CTA to finish closes the call
@@ -141,17 +147,24 @@ __global__ void __launch_bounds__(GLUE_THREADS) rms_norm_kernel(RmsNormArgs p) {
     }
 }
 
-__global__ void __launch_bounds__(GLUE_THREADS) silu_mul_kernel(const float *gate, const float *up, float *out, uint64_t n4) {
+__global__ void __launch_bounds__(GLUE_THREADS) silu_mul_kernel(const float *gate, const float *up, float *out, uint64_t n4, uint32_t cols4,
+                                                                ActOut q) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (uint64_t i = (uint64_t)blockIdx.x * GLUE_THREADS + threadIdx.x; i < n4; i += (uint64_t)gridDim.x * GLUE_THREADS) {
-        const float4 g = ((const float4 *)gate)[i], u = ((const float4 *)up)[i];
-        float4 o;
-        o.x = g.x / (1.0f + expf(-g.x)) * u.x;
-        o.y = g.y / (1.0f + expf(-g.y)) * u.y;
-        o.z = g.z / (1.0f + expf(-g.z)) * u.z;
-        o.w = g.w / (1.0f + expf(-g.w)) * u.w;
-        ((float4 *)out)[i] = o;
+    // whole warps iterate together (the quantized copy needs every lane of a warp in the call)
+    for (uint64_t base = (uint64_t)blockIdx.x * GLUE_THREADS + (threadIdx.x & ~31u); base < n4; base += (uint64_t)gridDim.x * GLUE_THREADS) {
+        const uint64_t i = base + (threadIdx.x & 31u);
+        const bool active = i < n4;
+        float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (active) {
+            const float4 g = ((const float4 *)gate)[i], u = ((const float4 *)up)[i];
+            o.x = g.x / (1.0f + expf(-g.x)) * u.x;
+            o.y = g.y / (1.0f + expf(-g.y)) * u.y;
+            o.z = g.z / (1.0f + expf(-g.z)) * u.z;
+            o.w = g.w / (1.0f + expf(-g.w)) * u.w;
+            ((float4 *)out)[i] = o;
+        }
+        if (q.qa) act_quant_quad(q, active, (uint32_t)(i / cols4), 4 * (uint32_t)(i % cols4), o);
     }
 }
 
@@ -180,24 +193,32 @@ static void pdl_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, unsig
 
 bool rms_norm_shape_ok(uint32_t cols) { return cols >= 4 && cols % 4 == 0 && cols <= GLUE_THREADS * GLUE_MAX_VEC * 4; }
 
+static unsigned rms_norm_parts(uint32_t cols) { return cols >= 4096 ? 8 : cols >= 2048 ? 4 : cols >= 1024 ? 2 : 1; }
+
+// every CTA of the cluster gets whole 32-element groups, in whole blocks of the quantized layouts
+bool rms_norm_quant_ok(uint32_t cols) { return rms_norm_shape_ok(cols) && cols % QK == 0 && (cols / 4) % (8 * rms_norm_parts(cols)) == 0; }
+
 cudaError_t launch_rms_norm(const RmsNormArgs &a, bool pdl, cudaStream_t stream) {
     if (a.rows == 0) return cudaSuccess;
     if (!rms_norm_shape_ok(a.cols)) return cudaErrorInvalidValue;
-    const unsigned parts = a.cols >= 4096 ? 8 : a.cols >= 2048 ? 4 : a.cols >= 1024 ? 2 : 1;
+    if (a.q.qa && (!rms_norm_quant_ok(a.cols) || a.q.k != a.cols || a.q.rows != a.rows)) return cudaErrorInvalidValue;
+    const unsigned parts = rms_norm_parts(a.cols);
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[2];
     pdl_config(cfg, attr, a.rows * parts, pdl, stream, parts);
     return cudaLaunchKernelEx(&cfg, rms_norm_kernel, a);
 }
 
-cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint64_t n, int sm_count, bool pdl, cudaStream_t stream) {
+cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint64_t n, uint32_t cols, const ActOut &q, int sm_count,
+                            bool pdl, cudaStream_t stream) {
     if (n == 0) return cudaSuccess;
     if (n % 4) return cudaErrorInvalidValue;
+    if (q.qa && (cols == 0 || cols % QK != 0 || n % cols != 0 || q.k != cols || (uint64_t)q.rows * cols != n)) return cudaErrorInvalidValue;
     const uint64_t n4 = n / 4, want = (n4 + GLUE_THREADS - 1) / GLUE_THREADS, cap = (uint64_t)sm_count * 8;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[2];
     pdl_config(cfg, attr, (unsigned)(want < cap ? want : cap), pdl, stream);
-    return cudaLaunchKernelEx(&cfg, silu_mul_kernel, gate, up, out, n4);
+    return cudaLaunchKernelEx(&cfg, silu_mul_kernel, gate, up, out, n4, q.qa ? cols / 4 : 1u, q);
 }
 
 }  // namespace lb

@@ -33,6 +33,18 @@ struct ActQuantArgs {
     int records;
 };
 constexpr int REC = 336;
+// Where a producing kernel (glue.cu) leaves its result as the quantized operand of the decode GEMV that
+// follows: the same layouts as ActQuantArgs (records 0: planes qa / da / bs; 1: records; 2: tiles, both at qa).
+struct ActOut {
+    int8_t *qa;  // nullptr: no quantized copy
+    float *da;
+    float *bs;
+    int records;
+    uint32_t rows, k;
+};
+// Bytes of a quantized activation operand and where its planes start (records == 0).
+inline size_t act_plane_bytes(uint32_t rows, uint32_t k) { return (((size_t)rows * k + 255) & ~(size_t)255); }
+inline size_t act_scale_bytes(uint32_t rows, uint32_t k) { return (((size_t)rows * (k / 32) * 4 + 255) & ~(size_t)255); }
 cudaError_t launch_act_quant(const ActQuantArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // Up to ACT_BATCH_MAX operands in one launch; group_end[i] = running total of 32-groups.
 constexpr int ACT_BATCH_MAX = 24;
@@ -225,10 +237,14 @@ struct RmsNormArgs {
     float *out;             // [rows, cols]
     uint32_t rows, cols;
     float eps;
+    ActOut q;               // q.qa set: `out` also goes out as a quantized activation operand (cols % 256 == 0)
 };
 bool rms_norm_shape_ok(uint32_t cols);  // multiple of 4, at most 16384
 cudaError_t launch_rms_norm(const RmsNormArgs &args, bool pdl, cudaStream_t stream);
-cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint64_t n, int sm_count, bool pdl, cudaStream_t stream);
+bool rms_norm_quant_ok(uint32_t cols);  // the row splits over the cluster in whole 32-element groups
+// silu(gate) * up over [rows, cols] (q.qa set: also as a quantized activation operand; cols % 32 == 0)
+cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint64_t n, uint32_t cols, const ActOut &q, int sm_count,
+                            bool pdl, cudaStream_t stream);
 
 // ---- tp_allreduce.cu: one-shot all-reduce over peer-mapped memory
 struct TpAllReduceArgs {

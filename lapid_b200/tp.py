@@ -257,10 +257,12 @@ class PeerAllReduce:
         run.keep = (arr, bufs, list(buffers))
         return run
 
-    def rms_norm(self, out, rows: int, cols: int, eps: float = 1e-6, residual=None, weight=None, sum_out=None) -> None:
-        """`Backend.rms_norm` with x = the sum over ranks of the push in progress (`lapid_b200_tp_rms_norm`)."""
+    def rms_norm(self, out, rows: int, cols: int, eps: float = 1e-6, residual=None, weight=None, sum_out=None, qact=None,
+                 layout: int = 0) -> None:
+        """`Backend.rms_norm` with x = the sum over ranks of the push in progress (`lapid_b200_tp_rms_norm_act`)."""
         h = lambda b: b._h if b is not None else None
-        self._lib.check(self._lib.lib().lapid_b200_tp_rms_norm(self._h, h(residual), h(weight), h(sum_out), out._h, rows, cols, eps))
+        self._lib.check(self._lib.lib().lapid_b200_tp_rms_norm_act(self._h, h(residual), h(weight), h(sum_out), out._h, rows, cols, eps,
+                                                                   h(qact), layout))
 
     def close(self):
         if self._h:
@@ -283,7 +285,7 @@ class GpuTpLayers:
     """
 
     def __init__(self, backend, shape: LayerShape, world: int, rank: int, m: int, weights: list, formats: list,
-                 group=None, peer_all_reduce=None, fused: bool = False):
+                 group=None, peer_all_reduce=None, fused: bool = False, fuse_act: bool = True):
         import torch
         from .backend import matmul_launch
         self.be, self.shape, self.world, self.rank, self.m, self.group = backend, shape, world, rank, m, group
@@ -309,19 +311,46 @@ class GpuTpLayers:
                       "act": wrap(self.act)}
         self._keep = []
         self.steps = []
+        # fuse_act: the glue kernels also write x and act as the quantized operand of the decode GEMVs that
+        # read them (no pre-pass kernel in front of q/k/v, gate/up and down); per layer, the layout of the
+        # phase's first projection is used, a projection that wants another one keeps the f32 operand
+        self.fuse_act = bool(fuse_act and m <= 8)
+        self.qx = torch.zeros(2 * m * d + 2 * d + 4096, dtype=torch.uint8, device=dev)
+        self.qact = torch.zeros(2 * m * proj["gate"][0] + 2 * proj["gate"][0] + 4096, dtype=torch.uint8, device=dev)
+        torch.cuda.synchronize(dev)
+        self._glue["qx"], self._glue["qact"] = wrap(self.qx), wrap(self.qact)
+        self.act_layouts = []   # per weight set: layout codes for (q/k/v phase, gate/up phase, down), None = not fused
         for w, f in zip(weights, formats):
             bufs = [wrap(self.x), wrap(self.outs["q"]), wrap(self.act)]                 # 0 x, 1 q_out, 2 act
             order = ["q", "k", "v", "o", "gate", "up", "down"]
             bufs += [wrap(w[n_]) for n_ in order]                                       # 3..9 weights
             bufs += [wrap(self.outs[n_]) for n_ in order]                               # 10..16 outputs
+            bufs += [wrap(self.qx), wrap(self.qact)]                                    # 17 quantized x, 18 quantized act
             idx = {n_: i for i, n_ in enumerate(order)}
 
-            def launch(name, a_id):
+            def launch(name, a_id, quantized=False):
                 n, k = proj[name]
-                return matmul_launch(f[name], m, n, k, inputs=(a_id, 3 + idx[name]), output=10 + idx[name])
+                return matmul_launch(f[name], m, n, k, inputs=(a_id, 3 + idx[name]), output=10 + idx[name], a_quantized=quantized)
 
-            lists = [[launch("q", 0), launch("k", 0), launch("v", 0)], [launch("o", 1)],
-                     [launch("gate", 0), launch("up", 0)], [launch("down", 2)]]
+            def layout_of(name, holder):
+                if not self.fuse_act:
+                    return None
+                try:
+                    lay, nbytes = backend.act_layout(launch(name, 0))
+                except Exception:
+                    return None
+                return lay if nbytes <= holder.numel() else None
+
+            def phase(names, f32_id, q_id, holder):
+                lay = layout_of(names[0], holder)
+                ls = [launch(n_, q_id, True) if lay is not None and layout_of(n_, holder) == lay else launch(n_, f32_id) for n_ in names]
+                return lay, ls
+
+            lay_qkv, l_qkv = phase(["q", "k", "v"], 0, 17, self.qx)
+            lay_gu, l_gu = phase(["gate", "up"], 0, 17, self.qx)
+            lay_down, l_down = phase(["down"], 2, 18, self.qact)
+            self.act_layouts.append((lay_qkv, lay_gu, lay_down))
+            lists = [l_qkv, [launch("o", 1)], l_gu, l_down]
             backend.prepare([l for ls in lists for l in ls])
             step = [backend.packed(ls, bufs) for ls in lists]
             if self.fused:
@@ -348,25 +377,32 @@ class GpuTpLayers:
         (left untouched, so a captured graph replays the same token) and ends in `self.h_out`."""
         be, m, d = self.be, self.m, self.shape.d_model
         w = self._glue
-        be.rms_norm(w["h"], w["x"], m, d)                                       # x = norm(h)
+        sets = len(self.steps)
+
+        def q_of(layout, holder):   # keyword arguments that make a glue call write the quantized operand too
+            return {} if layout is None else {"qact": w[holder], "layout": layout}
+
+        be.rms_norm(w["h"], w["x"], m, d, **q_of(self.act_layouts[0][0], "qx"))  # x = norm(h)
         res = w["h"]
         for i in range(n_layers):
-            qkv, o, gu, down = self.steps[i % len(self.steps)]
+            qkv, o, gu, down = self.steps[i % sets]
+            lay_gu, lay_down = self.act_layouts[i % sets][1:]
+            lay_next = self.act_layouts[(i + 1) % sets][0]
             qkv()
             o()
             if self.fused:
-                self.peer.rms_norm(w["x"], m, d, residual=res, sum_out=w["hw"])
+                self.peer.rms_norm(w["x"], m, d, residual=res, sum_out=w["hw"], **q_of(lay_gu, "qx"))
             else:
                 self.all_reduce("o")
-                be.rms_norm(w["o"], w["x"], m, d, residual=res, sum_out=w["hw"])     # h' = h + o;    x = norm(h')
+                be.rms_norm(w["o"], w["x"], m, d, residual=res, sum_out=w["hw"], **q_of(lay_gu, "qx"))    # h' = h + o;    x = norm(h')
             res = w["hw"]
             gu()
-            be.silu_mul(w["gate"], w["up"], w["act"], self.act.numel())
+            be.silu_mul(w["gate"], w["up"], w["act"], self.act.numel(), rows=m, **q_of(lay_down, "qact"))
             down()
             if self.fused:
-                self.peer.rms_norm(w["x"], m, d, residual=res, sum_out=w["hw"])
+                self.peer.rms_norm(w["x"], m, d, residual=res, sum_out=w["hw"], **q_of(lay_next, "qx"))
             else:
                 self.all_reduce("down")
-                be.rms_norm(w["down"], w["x"], m, d, residual=res, sum_out=w["hw"])  # h'' = h' + down; x = norm(h'') for the next layer
+                be.rms_norm(w["down"], w["x"], m, d, residual=res, sum_out=w["hw"], **q_of(lay_next, "qx"))  # h'' = h' + down; x = norm(h'') for the next layer
         self.h_out = self.hw
         return self.hw

@@ -607,6 +607,49 @@ def test_gather_rows_from_a_quantized_table(be, oracle, fmt, name):
     assert np.array_equal(bufs[2].download().view(np.float32).reshape(count, cols), got)
 
 
+@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("m", [1, 2, 4, 8])
+def test_glue_kernels_quantize_for_the_next_projection(be, oracle, fmt, name, m):
+    """rms_norm / silu_mul with a quantized copy of their result: a launch that reads that copy (a_dtype
+    ACT_Q8, no pre-pass kernel) gives bit for bit what the same launch gives from the f32 result, in each
+    of the three operand layouts; the f32 result itself is unchanged."""
+    n, k = 96, 2048
+    qb = oracle.quantize(int(fmt), O.normal(5, n * k, 0.05), n, k)
+    x = O.normal(6, m * k, 1.0)
+    x[3] = 0.0
+    res = O.normal(7, m * k, 0.5)
+    wgt = (1.0 + 0.1 * O.normal(8, k, 1.0)).astype(np.float32)
+    plain = matmul_launch(fmt, m, n, k, inputs=(0, 1), output=2)
+    fused = matmul_launch(fmt, m, n, k, inputs=(3, 1), output=2, a_quantized=True)
+    layout, nbytes = be.act_layout(plain)
+    assert be.act_layout(fused) == (layout, nbytes)
+    bx, bres, bw = be.upload(x), be.upload(res), be.upload(wgt)
+    for producer in ("rms_norm", "silu_mul"):
+        normed, normed2, qact = be.alloc(m * k * 4), be.alloc(m * k * 4), be.alloc(nbytes)
+        if producer == "rms_norm":
+            be.rms_norm(bx, normed, m, k, residual=bres, weight=bw)
+            be.rms_norm(bx, normed2, m, k, residual=bres, weight=bw, qact=qact, layout=layout)
+        else:
+            be.silu_mul(bx, bres, normed, m * k, rows=m)
+            be.silu_mul(bx, bres, normed2, m * k, rows=m, qact=qact, layout=layout)
+        a = normed.download()
+        assert np.array_equal(a, normed2.download())
+        out = be.alloc(m * n * 4)
+        be.take_launch_count()
+        be.execute([plain], [normed, be.upload(qb), out])
+        want = out.download().copy()
+        assert be.take_launch_count() == 2
+        out.write(0, np.zeros(m * n * 4, np.uint8))
+        be.execute([fused], [normed, be.upload(qb), out, qact])
+        assert be.take_launch_count() == 1          # no pre-pass
+        assert np.array_equal(out.download(), want)
+    with pytest.raises(lp.LapidError):              # a prefill-sized launch takes no quantized operand
+        be.prepare([matmul_launch(fmt, 16, n, k, a_quantized=True)])
+    with pytest.raises(lp.LapidError) as e:
+        be.execute([fused], [normed, be.upload(qb), out, be.alloc(64)])
+    assert e.value.code == "out_of_bounds"
+
+
 def _expert_stack(oracle, fmt, e, n, k, seed):
     one = oracle.layout(int(fmt), n, k).total
     stack = np.zeros(e * one, np.uint8)

@@ -49,8 +49,9 @@ def _worker(rank, world, port, m, out_path, peer):
             # order as the stand-alone all-reduce kernel: the residual stream must match bit for bit
             shape, weights, formats = _build(be, tp, O, quant, torch, rank, world, dev, 2)
             outs = []
-            for fused in (False, True):
-                layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats, peer_all_reduce=reducer, fused=fused)
+            for fused, fuse_act in ((False, False), (True, False), (True, True), (False, True)):
+                layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats, peer_all_reduce=reducer, fused=fused,
+                                        fuse_act=fuse_act)
                 assert layers.fused == fused
                 layers.h.copy_(torch.from_numpy(O.normal(99, m * shape.d_model).reshape(m, -1)).to(dev))
                 torch.cuda.synchronize(dev)
@@ -59,7 +60,7 @@ def _worker(rank, world, port, m, out_path, peer):
                 stream.synchronize()
                 outs.append(out)
                 be.synchronize()
-            assert torch.equal(outs[0], outs[1])
+            assert all(torch.equal(outs[0], o_) for o_ in outs[1:])
         for w_ in ((world, rank), (1, 0)):
             shape, weights, formats = _build(be, tp, O, quant, torch, w_[1], w_[0], dev, 2)
             layers = tp.GpuTpLayers(be, shape, w_[0], w_[1], m, weights, formats, peer_all_reduce=reducer)
@@ -84,6 +85,37 @@ def _worker(rank, world, port, m, out_path, peer):
         dist.barrier()
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("m", [1, 2, 4])
+def test_layer_stack_with_activations_quantized_by_their_producers(m):
+    """One GPU: the layer stack whose rms_norm / silu_mul kernels also write the quantized operand of the
+    projections that follow gives the same residual stream, bit for bit, as the stack with a pre-pass
+    kernel in front of every projection group, with fewer kernels."""
+    import torch
+    import lapid_b200 as lp
+    from lapid_b200 import quant, tp
+    from oracle import oracle as O
+    dev = torch.device("cuda", 0)
+    be = lp.Backend(0)
+    stream = torch.cuda.Stream(device=dev)
+    be.set_stream(stream.cuda_stream)
+    shape, weights, formats = _build(be, tp, O, quant, torch, 0, 1, dev, 2)
+    outs, kernels = [], []
+    for fuse_act in (False, True):
+        layers = tp.GpuTpLayers(be, shape, 1, 0, m, weights, formats, fuse_act=fuse_act)
+        layers.h.copy_(torch.from_numpy(O.normal(99, m * shape.d_model).reshape(m, -1)).to(dev))
+        torch.cuda.synchronize(dev)
+        be.take_launch_count()
+        with torch.cuda.stream(stream):
+            out = layers.token(4).clone()
+        stream.synchronize()
+        be.synchronize()
+        kernels.append(be.take_launch_count())
+        outs.append(out)
+        assert any(l is not None for ls in layers.act_layouts for l in ls) == fuse_act
+    assert torch.isfinite(outs[0]).all() and torch.equal(outs[0], outs[1])
+    assert kernels[1] <= kernels[0] - 4 * 2      # at least the gate/up and down pre-passes of every layer are gone
 
 
 @pytest.mark.parametrize("peer", [False, True])
