@@ -42,12 +42,14 @@
 
 #define LO_FMT_INT8 4
 #define LO_FMT_Q4K 6
+#define LO_FMT_Q5K 7
 #define LO_FMT_Q6K 8
 
 #define GROUP 32
 #define ALIGN 256
 #define QK 256
 #define Q4K_BYTES 144
+#define Q5K_BYTES 176
 #define Q6K_BYTES 210
 
 /* ------------------------------------------------------------------ bit helpers */
@@ -112,12 +114,15 @@ static inline int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ?
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 static int block_elems(int fmt) { return fmt == LO_FMT_INT8 ? GROUP : QK; }
-static int block_bytes(int fmt) { return fmt == LO_FMT_Q4K ? Q4K_BYTES : (fmt == LO_FMT_Q6K ? Q6K_BYTES : 0); }
+static int block_bytes(int fmt) {
+    return fmt == LO_FMT_Q4K ? Q4K_BYTES : (fmt == LO_FMT_Q5K ? Q5K_BYTES : (fmt == LO_FMT_Q6K ? Q6K_BYTES : 0));
+}
+static int is_kfmt(int fmt) { return fmt == LO_FMT_Q4K || fmt == LO_FMT_Q5K || fmt == LO_FMT_Q6K; }
 
 /* out = {qs_offset, qs_bytes, scales_offset, scales_bytes, total}; returns 0, or -1 on a bad
  * format / cols not a multiple of the block. */
 int lo_layout(int fmt, size_t rows, size_t cols, size_t out[5]) {
-    if (fmt != LO_FMT_INT8 && fmt != LO_FMT_Q4K && fmt != LO_FMT_Q6K) return -1;
+    if (fmt != LO_FMT_INT8 && !is_kfmt(fmt)) return -1;
     size_t be = (size_t)block_elems(fmt);
     if (cols % be != 0) return -1;
     if (block_bytes(fmt) != 0) {
@@ -213,9 +218,10 @@ static inline void scale_min_k4(int j, const uint8_t *q, uint8_t *sc, uint8_t *m
     }
 }
 
-/* kquant.rs:188-260 */
-void lo_quantize_q4k_block(const float *x, uint8_t *out) {
-    uint8_t L[QK], Laux[32];
+/* kquant.rs:186-247: the shared first half of the Q4_K / Q5_K quantizers: per-32 scales and mins,
+ * the packed 6-bit scales, d / dmin in head[0..4], and the final quants L (0..nmax) per element. */
+static void quantize_k45(const float *x, int nmax, float rmin, int nstep, uint8_t *head, uint8_t *L) {
+    uint8_t Laux[32];
     float weights[32], scales[8], mins[8];
     float max_scale = 0.0f, max_min = 0.0f;
     for (int j = 0; j < 8; j++) {
@@ -225,7 +231,7 @@ void lo_quantize_q4k_block(const float *x, uint8_t *out) {
         float av_x = sqrtf(sum_x2 / 32.0f);
         for (int l = 0; l < 32; l++) weights[l] = av_x + fabsf(xs[l]);
         float m;
-        float s = make_qkx2(32, xs, weights, 15, L + 32 * j, Laux, -1.0f, 0.1f, 20, &m);
+        float s = make_qkx2(32, xs, weights, nmax, L + 32 * j, Laux, rmin, 0.1f, nstep, &m);
         scales[j] = s;
         mins[j] = m;
         if (s > max_scale) max_scale = s;
@@ -233,7 +239,7 @@ void lo_quantize_q4k_block(const float *x, uint8_t *out) {
     }
     float inv_scale = max_scale > 0.0f ? 63.0f / max_scale : 0.0f;
     float inv_min = max_min > 0.0f ? 63.0f / max_min : 0.0f;
-    uint8_t *sc = out + 4;
+    uint8_t *sc = head + 4;
     memset(sc, 0, 12);
     for (int j = 0; j < 8; j++) {
         /* the C original stores nearest_int() in a uint8_t before MIN(63, .) */
@@ -250,9 +256,9 @@ void lo_quantize_q4k_block(const float *x, uint8_t *out) {
             sc[j] |= (uint8_t)((lm >> 4) << 6);
         }
     }
-    wr_h(out, 0, max_scale / 63.0f);
-    wr_h(out, 2, max_min / 63.0f);
-    float d_all = rd_h(out, 0), dmin_all = rd_h(out, 2);
+    wr_h(head, 0, max_scale / 63.0f);
+    wr_h(head, 2, max_min / 63.0f);
+    float d_all = rd_h(head, 0), dmin_all = rd_h(head, 2);
     for (int j = 0; j < 8; j++) {
         uint8_t s, m;
         scale_min_k4(j, sc, &s, &m);
@@ -261,12 +267,43 @@ void lo_quantize_q4k_block(const float *x, uint8_t *out) {
         float dm = dmin_all * (float)m;
         for (int ii = 0; ii < 32; ii++) {
             int q = nearest_int((x[32 * j + ii] + dm) / d);
-            L[32 * j + ii] = (uint8_t)clampi(q, 0, 15);
+            L[32 * j + ii] = (uint8_t)clampi(q, 0, nmax);
         }
     }
+}
+
+/* kquant.rs:250-260 */
+void lo_quantize_q4k_block(const float *x, uint8_t *out) {
+    uint8_t L[QK];
+    quantize_k45(x, 15, -1.0f, 20, out, L);
     uint8_t *qs = out + 16;
     for (int k = 0; k < 4; k++)
         for (int i = 0; i < 32; i++) qs[32 * k + i] = (uint8_t)(L[64 * k + i] | (L[64 * k + i + 32] << 4));
+}
+
+/* kquant.rs:263-287: as Q4_K with 5-bit quants; the fifth bits of the 8 sub-blocks share qh[32] */
+void lo_quantize_q5k_block(const float *x, uint8_t *out) {
+    uint8_t L[QK];
+    quantize_k45(x, 31, -0.5f, 15, out, L);
+    uint8_t *qh = out + 16, *ql = out + 48;
+    memset(qh, 0, 32);
+    uint8_t m1 = 1, m2 = 2;
+    for (int k = 0; k < 4; k++) {
+        for (int j = 0; j < 32; j++) {
+            uint8_t l1 = L[64 * k + j], l2 = L[64 * k + j + 32];
+            if (l1 > 15) {
+                l1 -= 16;
+                qh[j] |= m1;
+            }
+            if (l2 > 15) {
+                l2 -= 16;
+                qh[j] |= m2;
+            }
+            ql[32 * k + j] = (uint8_t)(l1 | (l2 << 4));
+        }
+        m1 <<= 2;
+        m2 <<= 2;
+    }
 }
 
 /* ------------------------------------------------------------------ Q6_K quantizer */
@@ -383,6 +420,27 @@ void lo_dequantize_q4k_block(const uint8_t *b, float *y) {
     }
 }
 
+/* kquant.rs:355-373 */
+void lo_dequantize_q5k_block(const uint8_t *b, float *y) {
+    float d = rd_h(b, 0), mn = rd_h(b, 2);
+    const uint8_t *scales = b + 4, *qh = b + 16, *qs = b + 48;
+    for (int j = 0; j < 4; j++) {
+        const uint8_t *q = qs + 32 * j;
+        uint8_t u1 = (uint8_t)(1u << (2 * j)), u2 = (uint8_t)(2u << (2 * j));
+        uint8_t s1, m1, s2, m2;
+        scale_min_k4(2 * j, scales, &s1, &m1);
+        scale_min_k4(2 * j + 1, scales, &s2, &m2);
+        float d1 = d * (float)s1, mm1 = mn * (float)m1;
+        float d2 = d * (float)s2, mm2 = mn * (float)m2;
+        float *o = y + 64 * j;
+        for (int l = 0; l < 32; l++) {
+            int h1 = (qh[l] & u1) ? 16 : 0, h2 = (qh[l] & u2) ? 16 : 0;
+            o[l] = d1 * (float)((q[l] & 0xF) + h1) - mm1;
+            o[l + 32] = d2 * (float)((q[l] >> 4) + h2) - mm2;
+        }
+    }
+}
+
 /* kquant.rs:376-396 */
 void lo_dequantize_q6k_block(const uint8_t *b, float *y) {
     float d = rd_h(b, 208);
@@ -433,12 +491,13 @@ int lo_quantize(int fmt, const float *data, size_t rows, size_t cols, uint8_t *o
     size_t L[5];
     if (cols == 0 || lo_layout(fmt, rows, cols, L) != 0) return -1;
     memset(out, 0, L[4]);
-    if (fmt == LO_FMT_Q4K || fmt == LO_FMT_Q6K) {
+    if (is_kfmt(fmt)) {
         size_t nb = rows * cols / QK;
         size_t bb = (size_t)block_bytes(fmt);
 #pragma omp parallel for schedule(static)
         for (long long i = 0; i < (long long)nb; i++) {
             if (fmt == LO_FMT_Q4K) lo_quantize_q4k_block(data + (size_t)i * QK, out + (size_t)i * bb);
+            else if (fmt == LO_FMT_Q5K) lo_quantize_q5k_block(data + (size_t)i * QK, out + (size_t)i * bb);
             else lo_quantize_q6k_block(data + (size_t)i * QK, out + (size_t)i * bb);
         }
         return 0;
@@ -456,11 +515,12 @@ int lo_quantize(int fmt, const float *data, size_t rows, size_t cols, uint8_t *o
 int lo_dequantize_row(int fmt, const uint8_t *bytes, size_t rows, size_t cols, size_t row, float *out) {
     size_t L[5];
     if (cols == 0 || lo_layout(fmt, rows, cols, L) != 0 || row >= rows) return -1;
-    if (fmt == LO_FMT_Q4K || fmt == LO_FMT_Q6K) {
+    if (is_kfmt(fmt)) {
         size_t nb = cols / QK, bb = (size_t)block_bytes(fmt);
         const uint8_t *rb = bytes + row * nb * bb;
         for (size_t b = 0; b < nb; b++) {
             if (fmt == LO_FMT_Q4K) lo_dequantize_q4k_block(rb + b * bb, out + b * QK);
+            else if (fmt == LO_FMT_Q5K) lo_dequantize_q5k_block(rb + b * bb, out + b * QK);
             else lo_dequantize_q6k_block(rb + b * bb, out + b * QK);
         }
         return 0;
@@ -549,6 +609,18 @@ static void unpack_block(int fmt, const uint8_t *b, int8_t *out) {
             }
         return;
     }
+    if (fmt == LO_FMT_Q5K) {
+        const uint8_t *qh = b + 16, *qs = b + 48;
+        for (int j = 0; j < 4; j++) {
+            uint8_t u1 = (uint8_t)(1u << (2 * j)), u2 = (uint8_t)(2u << (2 * j));
+            for (int l = 0; l < 32; l++) {
+                uint8_t x = qs[j * 32 + l];
+                out[j * 64 + l] = (int8_t)((x & 0xF) + ((qh[l] & u1) ? 16 : 0));
+                out[j * 64 + 32 + l] = (int8_t)((x >> 4) + ((qh[l] & u2) ? 16 : 0));
+            }
+        }
+        return;
+    }
     for (int n = 0; n < 2; n++) {
         const uint8_t *ql = b + n * 64, *qh = b + 128 + n * 32;
         int8_t *o = out + n * 128;
@@ -581,7 +653,7 @@ static void kcol(int fmt, const uint8_t *wrow, size_t k, size_t rows, const int8
         unpack_block(fmt, b, q);
         float s[8], m[8];
         float d6 = 0.0f;
-        if (fmt == LO_FMT_Q4K) { /* kquant.rs:36-46 */
+        if (fmt == LO_FMT_Q4K || fmt == LO_FMT_Q5K) { /* kquant.rs:36-46 */
             float d = rd_h(b, 0), dmin = rd_h(b, 2);
             for (int j = 0; j < 8; j++) {
                 uint8_t sc, mn;
@@ -679,7 +751,7 @@ int lo_matmul(int fmt, const float *a, size_t a_len, lo_view av, const uint8_t *
         float *bs = (float *)malloc(rows * kg * sizeof(float));
         for (size_t r = 0; r < rows; r++) {
             const float *x = a + av.offset + (r / m) * av.batch_stride + (r % m) * av.row_stride;
-            lo_quantize_row_sums(x, k, qa + r * k, sa + r * kg, fmt == LO_FMT_Q4K ? bs + r * kg : NULL);
+            lo_quantize_row_sums(x, k, qa + r * k, sa + r * kg, (fmt == LO_FMT_Q4K || fmt == LO_FMT_Q5K) ? bs + r * kg : NULL);  /* quant.rs:101 */
         }
         size_t bb = (size_t)block_bytes(fmt);
 #pragma omp parallel for schedule(static)

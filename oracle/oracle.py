@@ -27,8 +27,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "lapid_oracle.c")
 
 # dtype codes shared with crates/lapid-c/src/lib.rs:37-60
-INT8, Q4_K, Q6_K = 4, 6, 8
-FORMATS = {"int8": INT8, "q4_k": Q4_K, "q6_k": Q6_K}
+INT8, Q4_K, Q5_K, Q6_K = 4, 6, 7, 8
+FORMATS = {"int8": INT8, "q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K}
+BLOCK_BYTES = {Q4_K: 144, Q5_K: 176, Q6_K: 210}
 
 ERRORS = {1: "invalid_launch", 2: "shape_mismatch", 3: "out_of_bounds", 4: "unsupported_dtype"}
 
@@ -108,6 +109,8 @@ class Oracle:
         lib.lo_quantize_q6k_block.argtypes = [C.c_void_p, C.c_void_p]
         lib.lo_dequantize_q4k_block.argtypes = [C.c_void_p, C.c_void_p]
         lib.lo_dequantize_q6k_block.argtypes = [C.c_void_p, C.c_void_p]
+        lib.lo_quantize_q5k_block.argtypes = [C.c_void_p, C.c_void_p]
+        lib.lo_dequantize_q5k_block.argtypes = [C.c_void_p, C.c_void_p]
         lib.lo_matmul.argtypes = [C.c_int, C.c_void_p, sz, _View, C.c_void_p, sz, sz, sz, C.c_void_p, C.c_void_p, sz,
                                   _View, sz, sz, sz, sz, C.c_int, C.c_int, C.POINTER(C.c_int)]
         lib.lo_num_threads.restype = C.c_int
@@ -170,14 +173,16 @@ class Oracle:
     def quantize_block(self, fmt: int, x: np.ndarray) -> np.ndarray:
         x = np.ascontiguousarray(x, dtype=np.float32)
         assert x.size == 256
-        out = np.empty(144 if fmt == Q4_K else 210, dtype=np.uint8)
-        (self.lib.lo_quantize_q4k_block if fmt == Q4_K else self.lib.lo_quantize_q6k_block)(x.ctypes.data, out.ctypes.data)
+        out = np.empty(BLOCK_BYTES[fmt], dtype=np.uint8)
+        {Q4_K: self.lib.lo_quantize_q4k_block, Q5_K: self.lib.lo_quantize_q5k_block,
+         Q6_K: self.lib.lo_quantize_q6k_block}[fmt](x.ctypes.data, out.ctypes.data)
         return out
 
     def dequantize_block(self, fmt: int, b: np.ndarray) -> np.ndarray:
         b = np.ascontiguousarray(b, dtype=np.uint8)
         out = np.empty(256, dtype=np.float32)
-        (self.lib.lo_dequantize_q4k_block if fmt == Q4_K else self.lib.lo_dequantize_q6k_block)(b.ctypes.data, out.ctypes.data)
+        {Q4_K: self.lib.lo_dequantize_q4k_block, Q5_K: self.lib.lo_dequantize_q5k_block,
+         Q6_K: self.lib.lo_dequantize_q6k_block}[fmt](b.ctypes.data, out.ctypes.data)
         return out
 
     # ---- lapid-cpu surface

@@ -19,7 +19,7 @@ import pytest
 from oracle import oracle as O
 from tests.refgen import make_blocks, noise, rnd
 
-INT8, Q4_K, Q6_K = O.INT8, O.Q4_K, O.Q6_K
+INT8, Q4_K, Q5_K, Q6_K = O.INT8, O.Q4_K, O.Q5_K, O.Q6_K
 
 
 def rel_err(got, want):
@@ -70,7 +70,7 @@ def test_layout_sizes(oracle):
     assert (l.qs_bytes, l.scales_offset, l.scales_bytes, l.total) == (32, 256, 2, 512)
     l = oracle.layout(INT8, 768, 768)
     assert l.scales_offset == 768 * 768 and l.total % 256 == 0
-    for fmt, bb in ((Q4_K, 144), (Q6_K, 210)):
+    for fmt, bb in ((Q4_K, 144), (Q5_K, 176), (Q6_K, 210)):
         l = oracle.layout(fmt, 3, 512)
         assert (l.qs_offset, l.qs_bytes, l.scales_offset, l.scales_bytes) == (0, 3 * 2 * bb, 3 * 2 * bb, 0)
         assert l.total == (3 * 2 * bb + 255) // 256 * 256
@@ -118,7 +118,7 @@ def test_round_trip_error_bounds_int8(oracle):
 def test_k_formats(oracle):
     rows, cols = 3, 512
     x = noise(rows * cols, 11, 2.0)
-    for fmt, tol, bb in ((Q4_K, 0.25, 144), (Q6_K, 0.06, 210)):
+    for fmt, tol, bb in ((Q4_K, 0.25, 144), (Q5_K, 0.12, 176), (Q6_K, 0.06, 210)):
         q = oracle.quantize(fmt, x, rows, cols)
         l = oracle.layout(fmt, rows, cols)
         assert q.size == l.total and l.qs_bytes == rows * 2 * bb
@@ -146,14 +146,14 @@ def test_round_trip_relative_error(oracle):
     x = noise(256, 3)
     x[17] = 4.0
     rms = np.sqrt((x.astype(np.float64) ** 2).mean())
-    for fmt, tol in ((Q4_K, 0.08), (Q6_K, 0.02)):
+    for fmt, tol in ((Q4_K, 0.08), (Q5_K, 0.04), (Q6_K, 0.02)):
         y = oracle.dequantize_block(fmt, oracle.quantize_block(fmt, x))
         err = np.sqrt(((x - y).astype(np.float64) ** 2).mean())
         assert err / rms < tol
 
 
 def test_zeros_and_constants(oracle):
-    for fmt in (Q4_K, Q6_K):
+    for fmt in (Q4_K, Q5_K, Q6_K):
         for c in (0.0, 1.0, -2.5):
             b = oracle.quantize_block(fmt, np.full(256, c, dtype=np.float32))
             y = oracle.dequantize_block(fmt, b)
@@ -167,12 +167,12 @@ gguf = pytest.importorskip("gguf")
 
 def _gguf_deq(fmt, blocks):
     from gguf import quants
-    t = {Q4_K: gguf.GGMLQuantizationType.Q4_K, Q6_K: gguf.GGMLQuantizationType.Q6_K,
+    t = {Q4_K: gguf.GGMLQuantizationType.Q4_K, Q5_K: gguf.GGMLQuantizationType.Q5_K, Q6_K: gguf.GGMLQuantizationType.Q6_K,
          INT8: gguf.GGMLQuantizationType.Q8_0}[fmt]
     return quants.dequantize(blocks, t)
 
 
-@pytest.mark.parametrize("fmt,bb,d_off,dm_off", [(Q4_K, 144, 0, 2), (Q6_K, 210, 208, None)])
+@pytest.mark.parametrize("fmt,bb,d_off,dm_off", [(Q4_K, 144, 0, 2), (Q5_K, 176, 0, 2), (Q6_K, 210, 208, None)])
 def test_dequant_bit_exact_vs_independent_dequantizer(oracle, fmt, bb, d_off, dm_off):
     """`dequant_matches_ggml`: random valid blocks decode to the same f32 bits as an independent
     implementation of GGUF's K-quant dequantizers."""
@@ -196,12 +196,12 @@ def test_quantized_bytes_decode_identically_elsewhere(oracle):
     """Bytes produced by the oracle's quantizers are valid GGUF blocks: the independent dequantizer
     reads them to the same values the oracle does (cross-checks packing order and scale packing)."""
     x = O.normal(3, 16 * 1024, 0.02)
-    for fmt, bb in ((Q4_K, 144), (Q6_K, 210)):
+    for fmt, bb in ((Q4_K, 144), (Q5_K, 176), (Q6_K, 210)):
         q = oracle.quantize(fmt, x, 16, 1024)
         mine = oracle.dequantize(fmt, q, 16, 1024)
         other = _gguf_deq(fmt, q[:16 * 4 * bb].reshape(64, bb)).reshape(16, 1024).astype(np.float32)
         assert np.array_equal(mine.view(np.uint32), other.view(np.uint32))
-        assert rel_err(mine, x) < (0.08 if fmt == Q4_K else 0.02)
+        assert rel_err(mine, x) < {Q4_K: 0.08, Q5_K: 0.04, Q6_K: 0.02}[fmt]
 
 
 def test_int8_bytes_match_independent_q8_0_quantizer(oracle):
@@ -238,7 +238,7 @@ def test_quantize_row_roundtrip(oracle):
 def test_tiles_match_dequant_reference(oracle):
     rows, n, k = 5, 6, 512
     x = np.array([((i * 37 % 101) - 50.0) * 0.013 for i in range(rows * k)], dtype=np.float32).reshape(rows, k)
-    for fmt, bb, d_off, dm_off in ((Q4_K, 144, 0, 2), (Q6_K, 210, 208, None)):
+    for fmt, bb, d_off, dm_off in ((Q4_K, 144, 0, 2), (Q5_K, 176, 0, 2), (Q6_K, 210, 208, None)):
         raw = make_blocks(bb, n * k // 256, 11, d_off, dm_off)
         w = np.concatenate([raw, np.zeros((-raw.size) % 256, np.uint8)])
         deq = oracle.dequantize(fmt, w, n, k)
@@ -275,7 +275,7 @@ def test_int8_tile_matches_dequant_reference(oracle):
 # ------------------------------------------------------------------ lapid-cpu: whole launches
 def test_kquant_matmul_matches_dequantized_f32(oracle):
     seed = 50
-    for fmt in (Q4_K, Q6_K):
+    for fmt in (Q4_K, Q5_K, Q6_K):
         for (m, n, k, pad) in [(1, 37, 512, 0), (3, 20, 256, 4), (6, 9, 256, 0), (20, 45, 256, 3), (130, 70, 512, 0),
                                (33, 300, 1024, 0)]:
             seed += 1
@@ -343,7 +343,7 @@ def test_strided_output_view_and_validation(oracle):
     assert out.size == 8 and not out.any()
 
 
-@pytest.mark.parametrize("fmt,k", [(INT8, 96), (Q4_K, 256), (Q6_K, 512)])
+@pytest.mark.parametrize("fmt,k", [(INT8, 96), (Q4_K, 256), (Q5_K, 256), (Q6_K, 512)])
 def test_matmul_id_matches_dequantized_f64(oracle, fmt, k):
     """`matmul_id_quant` (crates/lapid-cpu/src/tests.rs:350-383) for the three formats of this path:
     5 experts of [24, k], decode-sized (int8 activations, 2e-2) and prefill-sized (exact, 1e-5) launches
