@@ -26,6 +26,7 @@ class DType(enum.IntEnum):
     I32 = 3
     Int8 = 4
     Q4K = 6
+    Q5K = 7
     Q6K = 8
     ACT_Q8 = 100  # not a lapid dtype: an activation operand quantized by its producer (LAPID_B200_DTYPE_ACT_Q8)
 

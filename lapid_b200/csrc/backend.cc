@@ -99,9 +99,14 @@ void cuda_check(cudaError_t e, const char *what) {
 }
 
 // ------------------------------------------------------------------ layout (lapid-quant lib.rs:84-125)
-bool is_quant(int32_t dt) { return dt == LAPID_B200_DTYPE_INT8 || dt == LAPID_B200_DTYPE_Q4_K || dt == LAPID_B200_DTYPE_Q6_K; }
+bool is_quant(int32_t dt) {
+    return dt == LAPID_B200_DTYPE_INT8 || dt == LAPID_B200_DTYPE_Q4_K || dt == LAPID_B200_DTYPE_Q5_K || dt == LAPID_B200_DTYPE_Q6_K;
+}
+bool has_min_term(int32_t dt) { return dt == LAPID_B200_DTYPE_Q4_K || dt == LAPID_B200_DTYPE_Q5_K; }  // the decode tiles need d * sum(q) per activation group
 uint64_t block_elems(int32_t dt) { return dt == LAPID_B200_DTYPE_INT8 ? 32 : 256; }
-uint64_t block_bytes(int32_t dt) { return dt == LAPID_B200_DTYPE_Q4_K ? 144 : (dt == LAPID_B200_DTYPE_Q6_K ? 210 : 0); }
+uint64_t block_bytes(int32_t dt) {
+    return dt == LAPID_B200_DTYPE_Q4_K ? 144 : dt == LAPID_B200_DTYPE_Q5_K ? 176 : dt == LAPID_B200_DTYPE_Q6_K ? 210 : 0;
+}
 uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
 lapid_b200_layout layout_of(int32_t fmt, uint64_t rows, uint64_t cols) {
@@ -310,7 +315,7 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
     Plan p;
     if (l.kind != LAPID_B200_KERNEL_MATMUL) fail("unsupported", "kernel kind " + std::to_string(l.kind) + " is not MatMul");
     if (!is_quant(l.b_dtype))
-        fail("unsupported_dtype", "b200 matmul: b dtype " + std::to_string(l.b_dtype) + " (want int8, q4_k or q6_k)");
+        fail("unsupported_dtype", "b200 matmul: b dtype " + std::to_string(l.b_dtype) + " (want int8, q4_k, q5_k or q6_k)");
     if ((l.a_dtype != LAPID_B200_DTYPE_F32 && l.a_dtype != LAPID_B200_DTYPE_ACT_Q8) || l.out_dtype != LAPID_B200_DTYPE_F32)
         fail("unsupported_dtype", "b200 matmul: a and out must be f32");
     if (l.epilogue != LAPID_B200_EPILOGUE_NONE && l.epilogue != LAPID_B200_EPILOGUE_ADD)
@@ -398,7 +403,7 @@ lb::ActOut act_out_checked(lapid_b200_device *dev, lapid_b200_buffer *qact, int3
 void check_gather(const lapid_b200_launch &l) {
     const bool quant = is_quant(l.b_dtype);
     if (!quant && l.b_dtype != LAPID_B200_DTYPE_F32)
-        fail("unsupported_dtype", "b200 gather: table dtype " + std::to_string(l.b_dtype) + " (want f32, int8, q4_k or q6_k)");
+        fail("unsupported_dtype", "b200 gather: table dtype " + std::to_string(l.b_dtype) + " (want f32, int8, q4_k, q5_k or q6_k)");
     if (l.out_dtype != LAPID_B200_DTYPE_F32) fail("unsupported_dtype", "b200 gather: out must be f32");
     if (l.n_inputs != 2) fail("invalid_launch", "expected 2 inputs, got " + std::to_string(l.n_inputs));
     if (l.batch != 1) fail("invalid_launch", "b200 gather: batch must be 1");
@@ -454,7 +459,7 @@ struct MoePlan {
 MoePlan plan_matmul_id(const lapid_b200_device &dev, const lapid_b200_launch &l) {
     MoePlan p;
     if (!is_quant(l.b_dtype))
-        fail("unsupported_dtype", "b200 matmul_id: w dtype " + std::to_string(l.b_dtype) + " (want int8, q4_k or q6_k)");
+        fail("unsupported_dtype", "b200 matmul_id: w dtype " + std::to_string(l.b_dtype) + " (want int8, q4_k, q5_k or q6_k)");
     if (l.a_dtype != LAPID_B200_DTYPE_F32 || l.out_dtype != LAPID_B200_DTYPE_F32)
         fail("unsupported_dtype", "b200 matmul_id: x and out must be f32");
     if (l.epilogue != LAPID_B200_EPILOGUE_NONE) fail("unsupported", "b200 matmul_id: no epilogue");
@@ -536,7 +541,7 @@ void run_matmul_id(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b20
         q.k = (uint32_t)l.k;
         q.qa = (int8_t *)base;
         q.da = (float *)(base + qa_b);
-        q.bs = l.b_dtype == LAPID_B200_DTYPE_Q4_K ? (float *)(base + qa_b + sc_b) : nullptr;
+        q.bs = has_min_term(l.b_dtype) ? (float *)(base + qa_b + sc_b) : nullptr;
         q.records = p.fast ? 1 : 0;
         cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl, dev.stream), "act_quant launch");
         lb::GemvArgs g{};
@@ -712,14 +717,14 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         q.k = (uint32_t)l.k;
         q.qa = (int8_t *)base;
         q.da = (float *)(base + qa_b);
-        q.bs = l.b_dtype == LAPID_B200_DTYPE_Q4_K ? (float *)(base + qa_b + sc_b) : nullptr;
+        q.bs = (float *)(base + qa_b + sc_b);  // written for every format (a later launch may share the slot); read by Q4_K / Q5_K
         q.records = slot->records;
         g.w = (const uint8_t *)ins[1]->ptr;
         g.w_bytes = ins[1]->bytes;
         g.scales_offset = p.wl.scales_offset;
         g.qa = q.qa;
         g.da = q.da;
-        g.bs = q.bs;
+        g.bs = has_min_term(l.b_dtype) ? q.bs : nullptr;
         g.a = l.a_dtype == LAPID_B200_DTYPE_ACT_Q8 ? nullptr : q.a;
         g.a_off = q.a_off;
         g.a_bs = q.a_bs;

@@ -10,11 +10,13 @@ namespace lb {
 
 constexpr int FMT_INT8 = 4;  // lapid dtype codes (crates/lapid-c/src/lib.rs:37-60)
 constexpr int FMT_Q4K = 6;
+constexpr int FMT_Q5K = 7;
 constexpr int FMT_Q6K = 8;
 
 constexpr int GROUP = 32;
 constexpr int QK = 256;
 constexpr int Q4K_BYTES = 144;
+constexpr int Q5K_BYTES = 176;  // Q4_K's header, then the fifth bits qh[32], then the nibbles qs[128]
 constexpr int Q6K_BYTES = 210;
 
 // Separately rounded IEEE operations. nvcc fuses a*b+c into an FMA unless told otherwise; the

@@ -1,6 +1,7 @@
 // Dequantization to f32, bit-identical to lapid-quant, and the GGUF -> lapid layout conversion.
 //
 //   dequantize_q4k   crates/lapid-quant/src/kquant.rs:337-352   y = (d*sc)*q - (dmin*m)
+//   dequantize_q5k   crates/lapid-quant/src/kquant.rs:355-373   y = (d*sc)*(q + 16*h) - (dmin*m)
 //   dequantize_q6k   crates/lapid-quant/src/kquant.rs:376-396   y = (d*sc)*(q-32)
 //   Int8 rows        crates/lapid-quant/src/imp.rs:143-148      y = f32(q) * f32(d)
 //   from_ggml_blocks crates/lapid-quant/src/imp.rs:171-200
@@ -25,6 +26,18 @@ __device__ __forceinline__ float q4k_element(const uint8_t *b, int e) {
     int q = (b[16 + 32 * j + l] >> (4 * h)) & 15;
     return xsub(xmul(d1, (float)q), m1);
 }
+// element e (0..255) of the Q5_K super-block at b: Q4_K's arithmetic with a fifth bit from qh
+__device__ __forceinline__ float q5k_element(const uint8_t *b, int e) {
+    int j = e >> 6, h = (e >> 5) & 1, l = e & 31;
+    float d = half_bits_to_float(b[0] | (b[1] << 8));
+    float dmin = half_bits_to_float(b[2] | (b[3] << 8));
+    int sc, mn;
+    scale_min_k4(2 * j + h, b + 4, sc, mn);
+    float d1 = xmul(d, (float)sc);
+    float m1 = xmul(dmin, (float)mn);
+    int q = ((b[48 + 32 * j + l] >> (4 * h)) & 15) + (((b[16 + l] >> (2 * j + h)) & 1) << 4);
+    return xsub(xmul(d1, (float)q), m1);
+}
 // element e (0..255) of the Q6_K super-block at b
 __device__ __forceinline__ float q6k_element(const uint8_t *b, int e) {
     int n = e >> 7, w = (e >> 5) & 3, l = e & 31;
@@ -40,6 +53,12 @@ __global__ void __launch_bounds__(256) dequant_q4k_kernel(const uint8_t *__restr
                                                           uint64_t n_blocks) {
     for (uint64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x)
         dst[blk * QK + threadIdx.x] = q4k_element(src + blk * Q4K_BYTES, threadIdx.x);
+}
+
+__global__ void __launch_bounds__(256) dequant_q5k_kernel(const uint8_t *__restrict__ src, float *__restrict__ dst,
+                                                          uint64_t n_blocks) {
+    for (uint64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x)
+        dst[blk * QK + threadIdx.x] = q5k_element(src + blk * Q5K_BYTES, threadIdx.x);
 }
 
 __global__ void __launch_bounds__(256) dequant_q6k_kernel(const uint8_t *__restrict__ src, float *__restrict__ dst,
@@ -67,6 +86,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t *__restrict__
         if (c >= cols) continue;
         float v;
         if (FMT == FMT_Q4K) v = q4k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q4K_BYTES, (int)(c % QK));
+        else if (FMT == FMT_Q5K) v = q5k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q5K_BYTES, (int)(c % QK));
         else if (FMT == FMT_Q6K) v = q6k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q6K_BYTES, (int)(c % QK));
         else if (FMT == FMT_INT8)
             v = xmul((float)((const int8_t *)table)[(uint64_t)r * cols + c],
@@ -113,6 +133,8 @@ cudaError_t launch_dequantize(int fmt, const void *src, uint64_t rows, uint64_t 
     if (n == 0) return cudaSuccess;
     if (fmt == FMT_Q4K) {
         dequant_q4k_kernel<<<grid_for(n / QK, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n / QK);
+    } else if (fmt == FMT_Q5K) {
+        dequant_q5k_kernel<<<grid_for(n / QK, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n / QK);
     } else if (fmt == FMT_Q6K) {
         dequant_q6k_kernel<<<grid_for(n / QK, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n / QK);
     } else {
@@ -130,6 +152,7 @@ cudaError_t launch_gather(int fmt, const void *table, uint64_t scales_offset, co
     const int grid = grid_for(count * ((cols + 255) / 256), sm_count);
     const uint8_t *t = (const uint8_t *)table;
     if (fmt == FMT_Q4K) gather_kernel<FMT_Q4K><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
+    else if (fmt == FMT_Q5K) gather_kernel<FMT_Q5K><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
     else if (fmt == FMT_Q6K) gather_kernel<FMT_Q6K><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
     else if (fmt == FMT_INT8) gather_kernel<FMT_INT8><<<grid, 256, 0, stream>>>(t, scales_offset, ids, rows, cols, count, out, status);
     else gather_kernel<-1><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);

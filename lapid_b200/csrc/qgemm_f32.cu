@@ -36,6 +36,18 @@ __device__ __forceinline__ void dequant8(const GemmF32Args &p, uint32_t row, uin
             int q = (b[16 + 32 * j + l0 + i] >> (4 * h)) & 15;
             y[i] = xsub(xmul(d1, (float)q), m1);
         }
+    } else if constexpr (FMT == FMT_Q5K) {
+        const uint8_t *b = p.w + ((uint64_t)row * (p.k / QK) + k0 / QK) * Q5K_BYTES;
+        uint32_t e = k0 % QK, j = e >> 6, h = (e >> 5) & 1, l0 = e & 31;
+        float d = half_bits_to_float(b[0] | (b[1] << 8)), dmin = half_bits_to_float(b[2] | (b[3] << 8));
+        int sc, mn;
+        scale_min_k4(2 * j + h, b + 4, sc, mn);
+        float d1 = xmul(d, (float)sc), m1 = xmul(dmin, (float)mn);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            int q = ((b[48 + 32 * j + l0 + i] >> (4 * h)) & 15) + (((b[16 + l0 + i] >> (2 * j + h)) & 1) << 4);
+            y[i] = xsub(xmul(d1, (float)q), m1);
+        }
     } else if constexpr (FMT == FMT_Q6K) {
         const uint8_t *b = p.w + ((uint64_t)row * (p.k / QK) + k0 / QK) * Q6K_BYTES;
         uint32_t e = k0 % QK, nh = e >> 7, w = (e >> 5) & 3, l0 = e & 31;
@@ -144,6 +156,7 @@ cudaError_t launch_qgemm_f32(int fmt, const GemmF32Args &a, cudaStream_t stream)
     if (grid.y > 65535) return cudaErrorInvalidValue;
     switch (fmt) {
         case FMT_Q4K: qgemm_f32_kernel<FMT_Q4K><<<grid, 256, 0, stream>>>(a); break;
+        case FMT_Q5K: qgemm_f32_kernel<FMT_Q5K><<<grid, 256, 0, stream>>>(a); break;
         case FMT_Q6K: qgemm_f32_kernel<FMT_Q6K><<<grid, 256, 0, stream>>>(a); break;
         case FMT_INT8: qgemm_f32_kernel<FMT_INT8><<<grid, 256, 0, stream>>>(a); break;
         default: return cudaErrorInvalidValue;

@@ -32,6 +32,7 @@ constexpr int STAGE_BLOCKS = 8;   // super-blocks (256 elements) per stage and w
 
 template <int FMT> struct Geo;
 template <> struct Geo<FMT_Q4K> { static constexpr int SPAN = STAGE_BLOCKS * Q4K_BYTES + 16; };
+template <> struct Geo<FMT_Q5K> { static constexpr int SPAN = STAGE_BLOCKS * Q5K_BYTES + 16; };
 template <> struct Geo<FMT_Q6K> { static constexpr int SPAN = STAGE_BLOCKS * Q6K_BYTES + 16; };
 // Int8: 2048 quant bytes (+16) then 64 f16 scales (+16)
 template <> struct Geo<FMT_INT8> {
@@ -133,7 +134,7 @@ __global__ void __launch_bounds__(WARPS * 32) qgemv_kernel(GemvArgs p) {
                 warp_copy_span(slot + c * SPAN + Geo<FMT_INT8>::QSPAN, p.w,
                                p.scales_offset + ((uint64_t)row * kg + g0) * 2, ng * 2, p.w_bytes, lane);
             } else {
-                constexpr int BB = FMT == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES;
+                constexpr int BB = FMT == FMT_Q4K ? Q4K_BYTES : FMT == FMT_Q5K ? Q5K_BYTES : Q6K_BYTES;
                 uint32_t b0 = st * STAGE_BLOCKS;
                 uint32_t nb = min((uint32_t)STAGE_BLOCKS, nblk - b0);
                 warp_copy_span(slot + c * SPAN, p.w, ((uint64_t)row * nblk + b0) * BB, nb * BB, p.w_bytes, lane);
@@ -171,16 +172,19 @@ __global__ void __launch_bounds__(WARPS * 32) qgemv_kernel(GemvArgs p) {
         const uint8_t *slot = ring + (size_t)(it % STAGES) * (C * SPAN);
         const uint32_t blk = st * STAGE_BLOCKS + blk_l;  // super-block along k
 
-        if constexpr (FMT == FMT_Q4K) {
+        if constexpr (FMT == FMT_Q4K || FMT == FMT_Q5K) {
+            // Q5_K is Q4_K with a fifth bit per weight: bit s of qh[l] (32 bytes behind the header) belongs to
+            // element 32 s + l, and the nibbles follow at byte 48 (crates/lapid-quant/src/kquant.rs:355-373)
+            constexpr int BB = FMT == FMT_Q5K ? Q5K_BYTES : Q4K_BYTES, QS = FMT == FMT_Q5K ? 48 : 16;
             if (blk < nblk) {
                 uint32_t wlo[C][8], whi[C][8];
                 float s0[C], m0[C], s1[C], m1[C];
 #pragma unroll
                 for (int c = 0; c < C; c++) {
-                    const uint8_t *b = slot + c * SPAN + blk_l * Q4K_BYTES;  // 16-byte aligned: 144 = 9*16
+                    const uint8_t *b = slot + c * SPAN + blk_l * BB;  // 16-byte aligned: 144 = 9*16, 176 = 11*16
                     uint4 h = *(const uint4 *)b;
-                    uint4 q0 = *(const uint4 *)(b + 16 + 32 * pr);
-                    uint4 q1 = *(const uint4 *)(b + 32 + 32 * pr);
+                    uint4 q0 = *(const uint4 *)(b + QS + 32 * pr);
+                    uint4 q1 = *(const uint4 *)(b + QS + 16 + 32 * pr);
                     float d = half_bits_to_float(h.x & 0xffff), dmin = half_bits_to_float(h.x >> 16);
                     int sc0, mn0, sc1, mn1;
                     scale_min_pair(pr, h.y, h.z, h.w, sc0, mn0, sc1, mn1);
@@ -193,6 +197,15 @@ __global__ void __launch_bounds__(WARPS * 32) qgemv_kernel(GemvArgs p) {
                     for (int i = 0; i < 8; i++) {
                         wlo[c][i] = v[i] & 0x0F0F0F0Fu;
                         whi[c][i] = (v[i] >> 4) & 0x0F0F0F0Fu;
+                    }
+                    if constexpr (FMT == FMT_Q5K) {
+                        uint4 h0 = *(const uint4 *)(b + 16), h1 = *(const uint4 *)(b + 32);
+                        uint32_t hq[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            wlo[c][i] |= ((hq[i] >> (2 * pr)) & 0x01010101u) << 4;
+                            whi[c][i] |= ((hq[i] >> (2 * pr + 1)) & 0x01010101u) << 4;
+                        }
                     }
                 }
 #pragma unroll
@@ -439,6 +452,7 @@ cudaError_t launch_qgemv(int fmt, const GemvArgs &args, int sm_count, bool pdl, 
     if (args.n == 0 || args.rows == 0) return cudaSuccess;
     switch (fmt) {
         case FMT_Q4K: return launch_fmt<FMT_Q4K>(args, sm_count, pdl, stream);
+        case FMT_Q5K: return launch_fmt<FMT_Q5K>(args, sm_count, pdl, stream);
         case FMT_Q6K: return launch_fmt<FMT_Q6K>(args, sm_count, pdl, stream);
         case FMT_INT8: return launch_fmt<FMT_INT8>(args, sm_count, pdl, stream);
         default: return cudaErrorInvalidValue;

@@ -1,6 +1,7 @@
 // Weight quantizers on the device, byte-identical to lapid-quant's reference quantizers.
 //
 //   Q4_K  crates/lapid-quant/src/kquant.rs:42-121 (make_qkx2_quants), :188-260
+//   Q5_K  the same search with 5-bit levels (nmax 31, rmin -0.5, 15 steps), :263-287
 //   Q6_K  crates/lapid-quant/src/kquant.rs:124-174 (make_qx_quants, rmse_type 1), :290-334
 //   Int8  crates/lapid-quant/src/imp.rs:24-40, :95-115
 //
@@ -18,9 +19,9 @@ namespace lb {
 __device__ __forceinline__ int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
 
 // Asymmetric (scale, min) search for one 32-value sub-block; L receives the chosen levels.
-__device__ float make_qkx2_32(const float *x, const float *w, uint8_t *L, uint8_t *Laux, float &the_min) {
-    const int n = 32, nmax = 15, nstep = 20;
-    const float rmin = -1.0f, rdelta = 0.1f;
+template <int FMT> __device__ float make_qkx2_32(const float *x, const float *w, uint8_t *L, uint8_t *Laux, float &the_min) {
+    const int n = 32, nmax = FMT == FMT_Q5K ? 31 : 15, nstep = FMT == FMT_Q5K ? 15 : 20;
+    const float rmin = FMT == FMT_Q5K ? -0.5f : -1.0f, rdelta = 0.1f;
     float mn = x[0], mx = x[0];
     float sum_w = w[0];
     float sum_x = xmul(sum_w, x[0]);
@@ -83,8 +84,10 @@ __device__ float make_qkx2_32(const float *x, const float *w, uint8_t *L, uint8_
 
 constexpr int Q4_BLOCKS_PER_CTA = 32;  // 8 threads per super-block, 256 threads
 
+template <int FMT>
 __global__ void __launch_bounds__(256) quantize_q4k_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst,
                                                            uint64_t n_blocks) {
+    constexpr int BB = FMT == FMT_Q5K ? Q5K_BYTES : Q4K_BYTES, NMAX = FMT == FMT_Q5K ? 31 : 15;
     __shared__ uint8_t sL[Q4_BLOCKS_PER_CTA][QK];
     const int tid = threadIdx.x;
     const int lb_ = tid >> 3;  // super-block within the CTA
@@ -107,7 +110,7 @@ __global__ void __launch_bounds__(256) quantize_q4k_kernel(const float *__restri
             for (int i = 0; i < 32; i++) sum_x2 = xadd(sum_x2, xmul(x[i], x[i]));
             float av_x = __fsqrt_rn(xdiv(sum_x2, 32.0f));
             for (int i = 0; i < 32; i++) w[i] = xadd(av_x, fabsf(x[i]));
-            scale = make_qkx2_32(x, w, L, Laux, mn);
+            scale = make_qkx2_32<FMT>(x, w, L, Laux, mn);
         }
         // the eight threads of a super-block are eight consecutive lanes: exchange by shuffle
         float scales[8], mins[8];
@@ -139,11 +142,11 @@ __global__ void __launch_bounds__(256) quantize_q4k_kernel(const float *__restri
             float d = xmul(__half2float(dh), (float)ls[j]);
             if (d != 0.0f) {
                 float dm = xmul(__half2float(mh), (float)lm[j]);
-                for (int i = 0; i < 32; i++) L[i] = (uint8_t)clampi(nearest_int(xdiv(xadd(x[i], dm), d)), 0, 15);
+                for (int i = 0; i < 32; i++) L[i] = (uint8_t)clampi(nearest_int(xdiv(xadd(x[i], dm), d)), 0, NMAX);
             }
             for (int i = 0; i < 32; i++) sL[lb_][32 * j + i] = L[i];
             if (j == 0) {
-                uint8_t *out = dst + blk * Q4K_BYTES;
+                uint8_t *out = dst + blk * BB;
                 unsigned short dbits = __half_as_ushort(dh), mbits = __half_as_ushort(mh);
                 out[0] = dbits & 0xff; out[1] = dbits >> 8;
                 out[2] = mbits & 0xff; out[3] = mbits >> 8;
@@ -169,7 +172,19 @@ __global__ void __launch_bounds__(256) quantize_q4k_kernel(const float *__restri
             uint64_t gb = base + b;
             if (gb < n_blocks) {
                 int k = t >> 5, i = t & 31;
-                dst[gb * Q4K_BYTES + 16 + t] = sL[b][64 * k + i] | (sL[b][64 * k + 32 + i] << 4);
+                dst[gb * BB + (FMT == FMT_Q5K ? 48 : 16) + t] = (sL[b][64 * k + i] & 15) | ((sL[b][64 * k + 32 + i] & 15) << 4);
+            }
+        }
+        if constexpr (FMT == FMT_Q5K) {  // the fifth bits: bit s of qh[i] belongs to element 32 s + i
+            for (int o = tid; o < Q4_BLOCKS_PER_CTA * 32; o += 256) {
+                int b = o >> 5, i = o & 31;
+                uint64_t gb = base + b;
+                if (gb < n_blocks) {
+                    uint8_t h = 0;
+#pragma unroll
+                    for (int sblk = 0; sblk < 8; sblk++) h |= (uint8_t)((sL[b][32 * sblk + i] >> 4) << sblk);
+                    dst[gb * BB + 16 + i] = h;
+                }
             }
         }
         __syncthreads();
@@ -360,7 +375,10 @@ cudaError_t launch_quantize(int fmt, const float *src, uint64_t rows, uint64_t c
     uint64_t cap = (uint64_t)sm_count * 8;
     if (fmt == FMT_Q4K) {
         uint64_t nb = n / QK, ctas = (nb + Q4_BLOCKS_PER_CTA - 1) / Q4_BLOCKS_PER_CTA;
-        quantize_q4k_kernel<<<(int)(ctas < cap ? ctas : cap), 256, 0, stream>>>(src, (uint8_t *)dst, nb);
+        quantize_q4k_kernel<FMT_Q4K><<<(int)(ctas < cap ? ctas : cap), 256, 0, stream>>>(src, (uint8_t *)dst, nb);
+    } else if (fmt == FMT_Q5K) {
+        uint64_t nb = n / QK, ctas = (nb + Q4_BLOCKS_PER_CTA - 1) / Q4_BLOCKS_PER_CTA;
+        quantize_q4k_kernel<FMT_Q5K><<<(int)(ctas < cap ? ctas : cap), 256, 0, stream>>>(src, (uint8_t *)dst, nb);
     } else if (fmt == FMT_Q6K) {
         uint64_t nb = n / QK, ctas = (nb + Q6_BLOCKS_PER_CTA - 1) / Q6_BLOCKS_PER_CTA;
         quantize_q6k_kernel<<<(int)(ctas < cap ? ctas : cap), 256, 0, stream>>>(src, (uint8_t *)dst, nb);

@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import argparse
 
-FMTS = {"int8": 4, "q4_k": 6, "q6_k": 8}
+FMTS = {"int8": 4, "q4_k": 6, "q5_k": 7, "q6_k": 8}
 
 
 def main() -> None:

@@ -1,11 +1,11 @@
 """Regenerates ``tests/golden/golden.npz`` from the CPU oracle (``python tests/golden/make_golden.py``).
 
 The reference cannot be built in this environment (no Rust toolchain) and checks in no golden
-bytes for Q4_K / Q6_K, so these vectors are outputs of the oracle restatement, itself pinned by
+bytes for the K formats, so these vectors are outputs of the oracle restatement, itself pinned by
 the reference's known-answer and property tests (tests/test_oracle.py). They freeze those
 outputs: any later change of the oracle or of the CUDA path that moves a byte shows up here.
 
-Contents, per format f in (int8, q4_k, q6_k), with W = normal(seed 10+f, [24, 512], 0.02),
+Contents, per format f in (int8, q4_k, q5_k, q6_k), with W = normal(seed 10+f, [24, 512], 0.02),
 X3 = normal(seed 20, [3, 512]), X12 = normal(seed 21, [12, 512]):
   w_<f>     quantized bytes of W             (lapid_quant::quantize)
   deq_<f>   f32 bits of dequantize(w)        (lapid_quant::dequantize), as uint32

@@ -20,7 +20,7 @@ from tests.refgen import make_blocks, rnd
 
 pytestmark = pytest.mark.gpu
 
-FMTS = [(lp.DType.Int8, "int8"), (lp.DType.Q4K, "q4_k"), (lp.DType.Q6K, "q6_k")]
+FMTS = [(lp.DType.Int8, "int8"), (lp.DType.Q4K, "q4_k"), (lp.DType.Q5K, "q5_k"), (lp.DType.Q6K, "q6_k")]
 
 
 @pytest.fixture(scope="module")
@@ -96,7 +96,7 @@ def test_dequantize_bit_exact_random_blocks(be, oracle, fmt, name):
         sc = (rng.standard_normal(rows * cols // 32) * 0.01).astype(np.float16)
         qb[l.scales_offset:l.scales_offset + l.scales_bytes] = sc.view(np.uint8)
     else:
-        bb, d_off, dm_off = (144, 0, 2) if fmt == lp.DType.Q4K else (210, 208, None)
+        bb, d_off, dm_off = {lp.DType.Q4K: (144, 0, 2), lp.DType.Q5K: (176, 0, 2), lp.DType.Q6K: (210, 208, None)}[fmt]
         raw = make_blocks(bb, rows * cols // 256, 7, d_off, dm_off)
         b2 = raw.reshape(-1, bb)
         ds = np.array([0.01, 0.25, 3e-5, -0.02, 6e-8, 1.5, 0.003, 7.0], np.float16).view(np.uint8).reshape(8, 2)
