@@ -10,8 +10,8 @@
  * rounded IEEE operation in the order the reference writes it: build with -ffp-contract=off.
  *
  *   storage contract ............ crates/lapid-quant/src/lib.rs:27-125
- *   Q4_K / Q6_K quantizers ...... crates/lapid-quant/src/kquant.rs:25-334
- *   Q4_K / Q6_K dequantizers .... crates/lapid-quant/src/kquant.rs:337-396
+ *   Q4_K / Q5_K / Q6_K quantizers  crates/lapid-quant/src/kquant.rs:25-334
+ *   ... and dequantizers ........ crates/lapid-quant/src/kquant.rs:337-396
  *   Int8 (GGUF Q8_0 as planes) .. crates/lapid-quant/src/imp.rs:24-40, :73-116, :143-200
  *   f32 -> f16 .................. `half` 2.7.1 f16::from_f32 (Cargo.lock:1188), IEEE round to
  *                                 nearest even; not vendored in the reference tree, so restated
@@ -26,9 +26,9 @@
  *                                 crates/lapid-cpu/src/matmul/kernels.rs:29-46, :95-119
  *   dispatch and validation ..... crates/lapid-cpu/src/matmul/mod.rs:45, :165-262
  *
- * Parity status: Int8 bytes are pinned by the reference's known-answer vector; Q4_K / Q6_K
+ * Parity status: Int8 bytes are pinned by the reference's known-answer vector; Q4_K / Q5_K / Q6_K
  * dequantization is pinned bit-for-bit against an independent third-party dequantizer (the
- * `gguf` Python package) in the tests; Q4_K / Q6_K *quantizer bytes* are pinned only by the
+ * `gguf` Python package) in the tests; K-format *quantizer bytes* are pinned only by the
  * reference's property tests (round-trip error bounds, constants, zeros) because the reference
  * checks in no golden bytes for them: quantizer byte parity is "parity unpinned".
  */
