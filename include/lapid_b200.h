@@ -103,7 +103,10 @@ LAPID_B200_API lapid_b200_status lapid_b200_device_synchronize(lapid_b200_device
  *   "gemv"          = "fast" (default) | "generic": specialised decode kernels where the shape allows;
  *   "act_reuse"     = "1" (default) | "0": share and hoist activation pre-passes inside a launch list;
  *   "pdl"           = "1" (default) | "0": programmatic dependent launch between the kernels of
- *                     a launch sequence (weights are staged while the producer still runs). */
+ *                     a launch sequence (weights are staged while the producer still runs);
+ *   "early_acts"    = "1" (default) | "0": decode launches whose activations were quantized by the
+ *                     pre-pass at the head of the list read them, and compute their first results, before
+ *                     the kernel in front of them has finished (they still write only after it has). */
 LAPID_B200_API lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const char *key, const char *value);
 
 /* ---- buffers (Backend::alloc / upload / write / download, backend.rs:17-50) ------------- */

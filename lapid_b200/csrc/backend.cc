@@ -153,6 +153,18 @@ struct lapid_b200_device {
     int *status_dev = nullptr;
     bool pdl = true;
     uint32_t gemv_max_rows = 8;
+    // Inside one execute list: kernels launched since the batched activation pre-pass at its head, -1 when the list
+    // has none. The first kernel after that pre-pass is launched fully serialised (no programmatic dependent
+    // launch), so every later kernel of the list starts after the pre-pass has completed and may read its
+    // results before its own dependency wait (GemvArgs::early).
+    int after_hoist = -1;
+    bool early_acts = true;  // option "early_acts"
+    bool pdl_launch() {
+        const bool p = pdl && after_hoist != 0;
+        if (after_hoist >= 0) after_hoist++;
+        return p;
+    }
+    bool early_ok(bool hoisted) const { return early_acts && pdl && hoisted && after_hoist >= 1; }
     bool act_reuse = true;  // share / hoist activation pre-passes inside one launch list
     bool gemv_fast = true;   // specialised GEMV kernels where the shape allows; off = generic kernel only
     bool gemv_group = true;  // consecutive independent K-quant decode launches of one list share a kernel
@@ -298,9 +310,12 @@ struct PendingGroup {
         reads.clear();
         lb::GemvGroup out = g;
         out.count = count;
-        if (mode == 2 && fmt == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(out, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
-        else if (mode == 2) cuda_check(lb::launch_qgemv_q4k_mma(out, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
-        else cuda_check(lb::launch_qgemv_kq_group(fmt, out, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+        const bool early = dev.early_ok(true);  // members carry early = 1 when their activations came from the pre-pass at the head
+        for (int i = 0; i < count; i++) out.item[i].early = early ? out.item[i].early : 0;
+        const bool pdl = dev.pdl_launch();
+        if (mode == 2 && fmt == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(out, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        else if (mode == 2) cuda_check(lb::launch_qgemv_q4k_mma(out, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        else cuda_check(lb::launch_qgemv_kq_group(fmt, out, dev.sm_count, pdl, dev.stream), "qgemv launch");
         dev.launches++;
     }
 };
@@ -543,7 +558,7 @@ void run_matmul_id(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b20
         q.da = (float *)(base + qa_b);
         q.bs = has_min_term(l.b_dtype) ? (float *)(base + qa_b + sc_b) : nullptr;
         q.records = p.fast ? 1 : 0;
-        cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl, dev.stream), "act_quant launch");
+        cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl_launch(), dev.stream), "act_quant launch");
         lb::GemvArgs g{};
         g.w = (const uint8_t *)w->ptr;
         g.w_bytes = w->bytes;
@@ -562,8 +577,9 @@ void run_matmul_id(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b20
         g.id_stride = p.wl.total;
         g.id_r = (uint32_t)p.r;
         g.id_e = (uint32_t)p.e;
-        if (p.fast) cuda_check(lb::launch_qgemv_kq_moe(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "matmul_id launch");
-        else cuda_check(lb::launch_qgemv_moe(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "matmul_id launch");
+        const bool pdl = dev.pdl_launch();
+        if (p.fast) cuda_check(lb::launch_qgemv_kq_moe(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "matmul_id launch");
+        else cuda_check(lb::launch_qgemv_moe(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "matmul_id launch");
         dev.launches += 2;
         return;
     }
@@ -571,7 +587,7 @@ void run_matmul_id(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b20
     lb::moe_route_layout(base, pairs, p.e, p.mt, route);
     route.ids = (const int32_t *)ids->ptr;
     route.status = dev.status_dev;
-    cuda_check(lb::launch_moe_route(route, dev.pdl, dev.stream), "matmul_id route launch");
+    cuda_check(lb::launch_moe_route(route, dev.pdl_launch(), dev.stream), "matmul_id route launch");
     dev.launches++;
     const uint32_t rows = route.max_tiles * route.mt;
     if (p.tc && lb::qgemm_tc_moe_supported(l.b_dtype, p.e, l.n, l.k, w->ptr) && p.wl.total == p.wl.qs_bytes) {
@@ -739,16 +755,17 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             for (int i = 0; i < l.n_inputs; i++) in[n_in++] = Range{(const char *)ins[i]->ptr, (const char *)ins[i]->ptr + ins[i]->bytes};
             if (!pend->accepts(l.b_dtype, slot->records, g, wr, in, n_in)) pend->flush(dev);
             if (!slot->done) {  // its input is not written by a pending launch (checked above), so it may run first
-                cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl, dev.stream), "act_quant launch");
+                cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl_launch(), dev.stream), "act_quant launch");
                 dev.launches++;
                 slot->done = true;
             }
+            g.early = slot->hoisted ? 1 : 0;  // gated again when the group goes out
             pend->add(l.b_dtype, slot->records, g, wr, in, n_in);
             return;
         }
         if (pend) pend->flush(dev);
         if (!slot->done) {
-            cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl, dev.stream), "act_quant launch");
+            cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl_launch(), dev.stream), "act_quant launch");
             dev.launches++;
             slot->done = true;
         }
@@ -756,17 +773,19 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             g.tp = tp;
             *pushed = true;
         }
+        g.early = dev.early_ok(slot->hoisted) ? 1 : 0;
+        const bool pdl = dev.pdl_launch();
         if (slot->records == 2 && l.b_dtype == LAPID_B200_DTYPE_INT8) {
-            cuda_check(lb::launch_qgemv_i8_mma(g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+            cuda_check(lb::launch_qgemv_i8_mma(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         } else if (slot->records == 2) {
             lb::GemvGroup one{};
             one.count = 1;
             one.item[0] = g;
-            if (l.b_dtype == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(one, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
-            else cuda_check(lb::launch_qgemv_q4k_mma(one, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
-        } else if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
-        else if (p.fast_i8 && ((uintptr_t)g.w & 15) == 0) cuda_check(lb::launch_qgemv_i8_fast(g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
-        else cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, dev.pdl, dev.stream), "qgemv launch");
+            if (l.b_dtype == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(one, dev.sm_count, pdl, dev.stream), "qgemv launch");
+            else cuda_check(lb::launch_qgemv_q4k_mma(one, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        } else if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        else if (p.fast_i8 && ((uintptr_t)g.w & 15) == 0) cuda_check(lb::launch_qgemv_i8_fast(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        else cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         dev.launches++;
         return;
     }
@@ -925,6 +944,11 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
         }
     }
     dev->ensure_scratch(scratch_total);
+    struct HoistScope {  // after_hoist is meaningful inside this list only
+        lapid_b200_device *d;
+        explicit HoistScope(lapid_b200_device *dev_) : d(dev_) { d->after_hoist = -1; }
+        ~HoistScope() { d->after_hoist = -1; }
+    } hoist_scope(dev);
     {
         lb::ActQuantBatch batch;
         batch.count = 0;
@@ -933,6 +957,7 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
             if (batch.count == 0) return;
             cuda_check(lb::launch_act_quant_batch(batch, dev->sm_count, dev->pdl, dev->stream), "act_quant launch");
             dev->launches++;
+            dev->after_hoist = 0;
             batch.count = 0;
             groups = 0;
         };
@@ -1081,6 +1106,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
         std::string k = key, v = value;
         if (k == "pdl") {
             dev->pdl = v != "0";
+        } else if (k == "early_acts") {
+            dev->early_acts = v != "0";
         } else if (k == "gemv_max_rows") {
             int r = std::atoi(value);
             if (r < 0 || r > 8) fail("invalid_argument", "gemv_max_rows must be in 0..8");

@@ -89,6 +89,11 @@ struct GemvArgs {
     uint64_t id_stride;
     uint32_t id_r, id_e;
     uint32_t id_pairs;      // launch_qgemv_moe (generic kernel): tokens * id_r, one grid row each; `rows` is 1 there
+    // 1: everything the kernel READS (weights, quantized activations) was complete before the kernel in front of it
+    // in the stream started, so under programmatic dependent launch it may read and compute without waiting for that
+    // kernel and only has to wait before it WRITES. Set by the host for launches whose activations were quantized by
+    // the pre-pass at the head of an execute list, when a fully serialised launch lies in between. Kernels may ignore it.
+    uint32_t early;
 };
 // rows in 1..8. Returns cudaErrorInvalidValue for an unsupported combination.
 cudaError_t launch_qgemv(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);

@@ -36,6 +36,8 @@ template <int FMT> struct Blk {
     static constexpr int STAGE = FMT == FMT_Q4K ? 32 * BYTES : 32 * BYTES + 16;
 };
 constexpr int BAR_BYTES = 256;  // warps * STAGES * 8 <= 256
+// room behind the activation records for results parked in early mode: 4 warps * (16 / M) tasks * up to 4 rows * M floats
+__host__ __device__ constexpr size_t pend_bytes(int rows) { return rows <= 2 ? (size_t)4 * 16 * 4 * 4 : 0; }
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -143,6 +145,8 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int RPW = 32 / G;
+    constexpr bool DEFER = M <= 2 && !MOE;  // park results instead of waiting at the first store (early mode)
+    constexpr int PEND_MAX = 16 / M;
     const int sub = lane / G, gl = lane % G;
     // A launch covers up to GEMV_GROUP_MAX independent projections with the same format, row count
     // and K (q/k/v, gate/up): their tasks (32/G weight rows each) form one list, so the weight
@@ -225,14 +229,10 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     }
     issue();
     issue();
-    if constexpr (!MOE) {
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-    }
-
-    __shared__ TpPushCtx tp_ctx;  // only the first member of a launch may push (tensor-parallel launches are never grouped)
-    if (grp.item[0].tp && threadIdx.x == 0) tp_push_ctx_load(&tp_ctx, grp.item[0].tp);
-    {
+    // early (GemvArgs::early): the activations are older than the kernel in front of this one, so they are
+    // fetched, and the first results computed, while that kernel still runs; only the stores wait for it
+    const bool early = !MOE && grp.item[0].early != 0 && grp.item[0].tp == nullptr;
+    auto copy_acts = [&]() {
         const uint32_t chunks = (MOE ? grp.item[0].rows : M) * nblk * (REC / 16);
         for (int i = 0; i < grp.count; i++) {
             if (!grp.act_copy[i]) continue;  // same activations as an earlier projection of the group
@@ -242,9 +242,41 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst + 16 * c)), "l"(src + 16 * (size_t)c) : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
+    };
+    if (early) copy_acts();
+    if constexpr (!MOE) {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        if (!early) asm volatile("griddepcontrol.wait;" ::: "memory");
     }
+    bool waited = !early;
+
+    __shared__ TpPushCtx tp_ctx;  // only the first member of a launch may push (tensor-parallel launches are never grouped)
+    if (grp.item[0].tp && threadIdx.x == 0) tp_push_ctx_load(&tp_ctx, grp.item[0].tp);
+    if (!early) copy_acts();
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    // results parked while the kernel in front still runs (early mode, one or two rows): [task][row of the task][M]
+    float *pend = (float *)(acts + grp.act_bytes) + warp * (PEND_MAX * RPW * M);
+    uint32_t npend = 0, pend_first = 0;
+    auto flush_pending = [&]() {
+        for (uint32_t q = 0; q < npend; q++) {
+            uint32_t local;
+            const int item = locate(pend_first + q * FAST_WARPS, local);
+            const GemvArgs &p = grp.item[item];
+            const uint32_t row = local * RPW + sub;
+            if (gl == 0 && row < p.n) {
+#pragma unroll
+                for (int r = 0; r < M; r++) {
+                    float v = pend[(q * RPW + sub) * M + r];
+                    const uint32_t bt = r / p.m, i = r % p.m;
+                    if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
+                    p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
+                }
+            }
+        }
+        npend = 0;
+    };
 
     float acc[M];
     bool healthy = true;
@@ -347,6 +379,28 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             cslot ^= 1;
             if (cslot == 0) cpar ^= 1;
         }
+        if (DEFER && !waited) {
+            // early mode: the kernel in front still runs, so nothing may be written yet. Park the task's results
+            // in shared memory and go on computing; the stores follow once that kernel has completed.
+            if (npend == 0) pend_first = t;
+#pragma unroll
+            for (int r = 0; r < M; r++) {
+                float v = acc[r];
+#pragma unroll
+                for (int o = G / 2; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (gl == 0) pend[(npend * RPW + sub) * M + r] = v;
+            }
+            if (++npend == PEND_MAX) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                waited = true;
+                flush_pending();
+            }
+            continue;
+        }
+        if (!waited) {  // nothing is written before the kernel in front has completed
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            waited = true;
+        }
 #pragma unroll
         for (int r = 0; r < M; r++) {
             float v = acc[r];
@@ -361,6 +415,12 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             }
         }
     }
+    // a warp without a task still may not let its CTA (and with it the grid) end before the kernel in front
+    // has: later kernels take this grid's completion as the completion of everything before it
+    if (!waited) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if constexpr (DEFER) flush_pending();
+    }
 }
 
 static int g_cta_cap = 0;  // 0 = as many CTAs per SM as fit; set through qgemv_q4k_fast_set_cta_cap
@@ -373,11 +433,14 @@ static cudaError_t launch_fast_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cuda
     constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
     constexpr int RPW = 32 / G;
     uint32_t tasks = 0;
+    uint32_t early = 1;
     for (int i = 0; i < g.count; i++) {
         tasks += (g.item[i].n + RPW - 1) / RPW * (MOE ? g.item[i].rows * g.item[i].id_r : 1);
         g.task_end[i] = tasks;
+        early &= g.item[i].early;
     }
-    const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * Blk<FMT>::STAGE + g.act_bytes;
+    g.item[0].early = pdl ? early : 0;  // the kernel looks at the first member only
+    const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * Blk<FMT>::STAGE + g.act_bytes + pend_bytes(M);
     static DynamicSmemOptIn opted;
     if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
     // resident CTAs per SM for this shared-memory size (a handful of sizes occur: remember them)
@@ -399,6 +462,11 @@ static cudaError_t launch_fast_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cuda
     // launch its CTAs move in while this kernel still runs and fill their rings, so the weight
     // stream does not stop at the kernel boundary.
     int per_sm = ctas_per_sm >= 4 ? ctas_per_sm - 1 : ctas_per_sm;
+    // Early mode with parked results (one or two rows): a kernel computes all of its tasks without waiting
+    // for the kernel in front, so consecutive launches run side by side as long as each leaves room for
+    // the next ones. One small CTA per SM and kernel (two for two rows) measured best: up to five
+    // kernels share an SM and the weight stream never stops at a kernel boundary.
+    if (g.item[0].early && M <= 2 && !MOE) per_sm = M == 1 ? 1 : (ctas_per_sm < 2 ? ctas_per_sm : 2);
     if (g_cta_cap > 0) per_sm = g_cta_cap < ctas_per_sm ? g_cta_cap : ctas_per_sm;
     // every SM gets the same number of CTAs and every CTA the same share of the tasks
     uint32_t grid = (uint32_t)sm_count * (uint32_t)per_sm;
@@ -442,7 +510,7 @@ bool qgemv_kq_fast_shape_ok(int fmt, uint32_t rows, uint32_t k) {
     if (rows < 1 || rows > 8 || k % QK != 0 || k < QK) return false;
     const size_t warps = rows <= 2 ? 4 : 8;
     const size_t stage = fmt == FMT_Q4K ? Blk<FMT_Q4K>::STAGE : Blk<FMT_Q6K>::STAGE;
-    return BAR_BYTES + warps * 2 * stage + (size_t)rows * (k / QK) * REC <= 227 * 1024 - 256;
+    return BAR_BYTES + warps * 2 * stage + (size_t)rows * (k / QK) * REC + pend_bytes((int)rows) <= 227 * 1024 - 256;
 }
 
 bool qgemv_kq_fast_supported(int fmt, const GemvArgs &a) {
@@ -488,7 +556,7 @@ size_t qgemv_kq_group_smem(int fmt, GemvGroup &g) {
     plan_group_acts(g);
     const size_t warps = g.item[0].rows <= 2 ? 4 : 8;
     const size_t stage = fmt == FMT_Q4K ? Blk<FMT_Q4K>::STAGE : Blk<FMT_Q6K>::STAGE;
-    return BAR_BYTES + warps * 2 * stage + g.act_bytes;
+    return BAR_BYTES + warps * 2 * stage + g.act_bytes + pend_bytes((int)g.item[0].rows);
 }
 
 cudaError_t launch_qgemv_kq_group(int fmt, GemvGroup &g, int sm_count, bool pdl, cudaStream_t s) {
@@ -501,7 +569,7 @@ bool qgemv_kq_moe_shape_ok(int fmt, uint32_t tokens, uint32_t k) {
     if (fmt != FMT_Q4K && fmt != FMT_Q6K) return false;
     if (tokens < 1 || tokens > 8 || k % QK != 0 || k < QK) return false;
     const size_t stage = fmt == FMT_Q4K ? Blk<FMT_Q4K>::STAGE : Blk<FMT_Q6K>::STAGE;
-    return BAR_BYTES + (size_t)Shape<1>::WARPS * 2 * stage + (size_t)tokens * (k / QK) * REC <= 227 * 1024 - 256;
+    return BAR_BYTES + (size_t)Shape<1>::WARPS * 2 * stage + (size_t)tokens * (k / QK) * REC + pend_bytes(1) <= 227 * 1024 - 256;
 }
 
 template <int FMT, int G> static cudaError_t launch_moe_g(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {

@@ -177,12 +177,10 @@ qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
     issue();
     issue();
 
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    __shared__ TpPushCtx tp_ctx;  // only the first member of a launch may push (tensor-parallel launches are never grouped)
-    if (grp.item[0].tp && threadIdx.x == 0) tp_push_ctx_load(&tp_ctx, grp.item[0].tp);
-    {
+    // early (GemvArgs::early): the activations are older than the kernel in front of this one, so they are
+    // fetched, and the first tile computed, while that kernel still runs; only the stores wait for it
+    const bool early = grp.item[0].early != 0 && grp.item[0].tp == nullptr;
+    auto copy_acts = [&]() {
         const uint32_t chunks = nblk * ABLK / 16;
         for (int i = 0; i < grp.count; i++) {
             if (!grp.act_copy[i]) continue;
@@ -192,9 +190,17 @@ qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst + 16 * c)), "l"(src + 16 * (size_t)c) : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
-    }
+    };
+    if (early) copy_acts();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!early) asm volatile("griddepcontrol.wait;" ::: "memory");
+    bool waited = !early;
+
+    __shared__ TpPushCtx tp_ctx;  // only the first member of a launch may push (tensor-parallel launches are never grouped)
+    if (grp.item[0].tp && threadIdx.x == 0) tp_push_ctx_load(&tp_ctx, grp.item[0].tp);
+    if (!early) copy_acts();
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
 
     const uint32_t colq = (uint32_t)gq < M ? gq : 0;        // activation row of this lane's B fragment
     const uint32_t cp = (uint32_t)(2 * t4) < M ? t4 : 0;    // activation row pair of this lane's C fragment
@@ -324,6 +330,10 @@ qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
 #pragma unroll
             for (int i = 0; i < 4; i++) mine[(tl * 4 + i) * 32 + lane] = acc[tl][i];
         __syncthreads();  // the buffer of the other parity is free again once every warp got here
+        if (!waited) {    // nothing is written before the kernel in front has completed
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            waited = true;
+        }
         for (uint32_t e = threadIdx.x; e < (uint32_t)ELEMS; e += THREADS) {
             const float *src = red + (size_t)par * WARPS * ELEMS + e;
             float v = src[0];
@@ -340,6 +350,7 @@ qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
             }
         }
     }
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");  // a CTA without a tile must not let the grid end early
 }
 
 struct Config {
@@ -444,6 +455,9 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cudaStrea
         g.task_end[i] = tasks;
         if (!weight_map(g.item[i], 16 * TILES, maps.m[i])) return cudaErrorNotSupported;
     }
+    uint32_t early = pdl ? 1 : 0;
+    for (int i = 0; i < g.count; i++) early &= g.item[i].early;
+    g.item[0].early = early;  // the kernel looks at the first member only
     for (int i = g.count; i < NG; i++) maps.m[i] = maps.m[0];
     const size_t smem = fixed_smem(Config{WARPS, TILES}) + g.act_bytes;
     static DynamicSmemOptIn opted;
