@@ -438,7 +438,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 def gemv_kernel_name(fmt: int, m: int) -> str:
     """The kernel a decode launch of `m` rows takes with the library's default options."""
     if fmt == 6:
-        return "qgemv_q4k_mma_kernel" if m >= 2 else "qgemv_kq_fast_kernel<q4_k>"
+        return "qgemv_q4k_mma_kernel" if m >= 3 else "qgemv_kq_fast_kernel<q4_k>"  # (two rows: the tensor-core kernel when the operand is produced inside the list)
     if fmt == 8:
         return "qgemv_q6k_mma_kernel" if m >= 3 else "qgemv_kq_fast_kernel<q6_k>"
     if fmt == 7:

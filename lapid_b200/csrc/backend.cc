@@ -908,6 +908,11 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
                 bool clean = true;  // nothing in the list so far wrote the buffer A lives in
                 for (const Range &w : written)
                     if ((const char *)ab->ptr < w.hi && w.lo < (const char *)ab->ptr + ab->bytes) clean = false;
+                // two rows of Q4_K whose activations come from the pre-pass at the head: the dp4a kernel overlaps
+                // with the kernels around it (GemvArgs::early) and beats the tensor-core kernel there
+                if (clean && dev->act_reuse && dev->early_acts && dev->pdl && p.rows == 2 && p.mma && p.fast &&
+                    l.b_dtype == LAPID_B200_DTYPE_Q4_K)
+                    key.records = 1;
                 int found = -1;
                 if (dev->act_reuse) {
                     if (clean) {

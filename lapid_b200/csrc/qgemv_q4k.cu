@@ -136,16 +136,18 @@ template <int M> struct Shape { static constexpr int WARPS = M <= 2 ? 4 : 8, MIN
 // every (token, slot) pair is a one-row GEMV against the matrix its expert id selects. The pairs'
 // tasks form one list (a task never straddles two pairs), the activation records of all tokens
 // sit in shared memory and a task reads the records of its pair's token.
-template <int FMT, int M, int G, int NG, bool MOE = false>
+// EARLY (one or two rows; GemvArgs::early of every member): see below.
+template <int FMT, int M, int G, int NG, bool MOE = false, bool EARLY = false>
 __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_kq_fast_kernel(GemvGroupT<NG> grp) {
     static_assert(!MOE || (M == 1 && NG == 1), "expert-indexed launches are one-row, one-item launches");
+    static_assert(!EARLY || (M <= 2 && !MOE), "early mode is built for one and two rows");
     constexpr int STAGES = 2;
     constexpr int BB = Blk<FMT>::BYTES, STAGE_BYTES = Blk<FMT>::STAGE;
     constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr int RPW = 32 / G;
-    constexpr bool DEFER = M <= 2 && !MOE;  // park results instead of waiting at the first store (early mode)
+    constexpr bool DEFER = EARLY;  // park results instead of waiting at the first store
     constexpr int PEND_MAX = 16 / M;
     const int sub = lane / G, gl = lane % G;
     // A launch covers up to GEMV_GROUP_MAX independent projections with the same format, row count
@@ -231,7 +233,7 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     issue();
     // early (GemvArgs::early): the activations are older than the kernel in front of this one, so they are
     // fetched, and the first results computed, while that kernel still runs; only the stores wait for it
-    const bool early = !MOE && grp.item[0].early != 0 && grp.item[0].tp == nullptr;
+    constexpr bool early = EARLY;
     auto copy_acts = [&]() {
         const uint32_t chunks = (MOE ? grp.item[0].rows : M) * nblk * (REC / 16);
         for (int i = 0; i < grp.count; i++) {
@@ -427,20 +429,22 @@ static int g_cta_cap = 0;  // 0 = as many CTAs per SM as fit; set through qgemv_
 
 void qgemv_q4k_fast_set_cta_cap(int cap) { g_cta_cap = cap; }
 
-template <int FMT, int M, int G, int NG, bool MOE = false>
+template <int FMT, int M, int G, int NG, bool MOE = false, bool EARLY = false>
 static cudaError_t launch_fast_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cudaStream_t stream) {
-    auto kern = qgemv_kq_fast_kernel<FMT, M, G, NG, MOE>;
+    if constexpr (!EARLY && !MOE && M <= 2) {  // every member early, no tensor-parallel push: the early instantiation
+        bool early = pdl;
+        for (int i = 0; i < g.count; i++) early = early && g.item[i].early != 0 && g.item[i].tp == nullptr;
+        if (early) return launch_fast_n<FMT, M, G, NG, MOE, true>(g, sm_count, pdl, stream);
+    }
+    auto kern = qgemv_kq_fast_kernel<FMT, M, G, NG, MOE, EARLY>;
     constexpr int FAST_WARPS = Shape<M>::WARPS, FAST_THREADS = FAST_WARPS * 32;
     constexpr int RPW = 32 / G;
     uint32_t tasks = 0;
-    uint32_t early = 1;
     for (int i = 0; i < g.count; i++) {
         tasks += (g.item[i].n + RPW - 1) / RPW * (MOE ? g.item[i].rows * g.item[i].id_r : 1);
         g.task_end[i] = tasks;
-        early &= g.item[i].early;
     }
-    g.item[0].early = pdl ? early : 0;  // the kernel looks at the first member only
-    const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * Blk<FMT>::STAGE + g.act_bytes + pend_bytes(M);
+    const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * Blk<FMT>::STAGE + g.act_bytes + (EARLY ? pend_bytes(M) : 0);
     static DynamicSmemOptIn opted;
     if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
     // resident CTAs per SM for this shared-memory size (a handful of sizes occur: remember them)
@@ -466,7 +470,7 @@ static cudaError_t launch_fast_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cuda
     // for the kernel in front, so consecutive launches run side by side as long as each leaves room for
     // the next ones. One small CTA per SM and kernel (two for two rows) measured best: up to five
     // kernels share an SM and the weight stream never stops at a kernel boundary.
-    if (g.item[0].early && M <= 2 && !MOE) per_sm = M == 1 ? 1 : (ctas_per_sm < 2 ? ctas_per_sm : 2);
+    if (EARLY) per_sm = M == 1 ? 1 : (ctas_per_sm < 2 ? ctas_per_sm : 2);
     if (g_cta_cap > 0) per_sm = g_cta_cap < ctas_per_sm ? g_cta_cap : ctas_per_sm;
     // every SM gets the same number of CTAs and every CTA the same share of the tasks
     uint32_t grid = (uint32_t)sm_count * (uint32_t)per_sm;

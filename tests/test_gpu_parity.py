@@ -614,6 +614,7 @@ def test_glue_kernels_quantize_for_the_next_projection(be, oracle, fmt, name, m)
     ACT_Q8, no pre-pass kernel) gives bit for bit what the same launch gives from the f32 result, in each
     of the three operand layouts; the f32 result itself is unchanged."""
     n, k = 96, 2048
+    be.set_option("early_acts", "0")   # keep the plain launch on the kernel act_layout describes (bit-equality below)
     qb = oracle.quantize(int(fmt), O.normal(5, n * k, 0.05), n, k)
     x = O.normal(6, m * k, 1.0)
     x[3] = 0.0
@@ -648,6 +649,45 @@ def test_glue_kernels_quantize_for_the_next_projection(be, oracle, fmt, name, m)
     with pytest.raises(lp.LapidError) as e:
         be.execute([fused], [normed, be.upload(qb), out, be.alloc(64)])
     assert e.value.code == "out_of_bounds"
+    be.set_option("early_acts", "1")
+
+
+@pytest.mark.parametrize("fmt,name", [(lp.DType.Q4K, "q4_k"), (lp.DType.Q6K, "q6_k")])
+@pytest.mark.parametrize("m", [1, 2, 8])
+def test_launches_that_run_ahead_of_their_predecessor(be, oracle, fmt, name, m):
+    """A list of decode launches that share activations quantized at its head: from the second launch on the
+    kernels read and compute before the kernel in front of them has finished and park their results
+    (GemvArgs::early). Same values as with the mode switched off, whatever the launches write to: distinct
+    buffers, the same buffer again and again, or a buffer a later launch of the list reads."""
+    n, k, copies = 520, 2048, 9
+    ws = [oracle.quantize(int(fmt), O.normal(400 + c, n * k, 0.05), n, k) for c in range(copies)]
+    x = O.normal(77, m * k, 1.0)
+    wants = [oracle.matmul(int(fmt), x, w, n, k, m=m)[0] for w in ws]
+    bufs = [be.upload(x)] + [be.upload(w) for w in ws] + [be.alloc(m * n * 4) for _ in range(copies)]
+    distinct = [matmul_launch(fmt, m, n, k, inputs=(0, 1 + c), output=1 + copies + c) for c in range(copies)]
+    same = [matmul_launch(fmt, m, n, k, inputs=(0, 1 + c), output=1 + copies) for c in range(copies)]
+    for early in ("1", "0"):
+        be.set_option("early_acts", early)
+        be.execute(distinct, bufs)                                      # (independent launches also go out in groups)
+        for c in range(copies):
+            assert max_rel(bufs[1 + copies + c].download().view(np.float32), wants[c]) <= 2e-5
+        be.take_launch_count()
+        be.execute(same, bufs)                                          # write-after-write in stream order
+        assert be.take_launch_count() == 1 + copies                     # one pre-pass at the head, then one kernel each
+        assert max_rel(bufs[1 + copies].download().view(np.float32), wants[-1]) <= 2e-5
+    be.set_option("early_acts", "1")
+    if m == 1:   # a launch that reads what an early launch wrote (k == n here would be needed: use a square pair)
+        n2 = k
+        w2 = oracle.quantize(int(fmt), O.normal(450, n2 * k, 0.05), n2, k)
+        w3 = oracle.quantize(int(fmt), O.normal(451, n * n2, 0.05), n, n2)
+        y2 = oracle.matmul(int(fmt), x, w2, n2, k, m=1)[0]
+        y3 = oracle.matmul(int(fmt), y2, w3, n, n2, m=1)[0]
+        b2 = [be.upload(x), be.upload(ws[0]), be.alloc(n * 4), be.upload(w2), be.alloc(n2 * 4), be.upload(w3), be.alloc(n * 4)]
+        chain = [matmul_launch(fmt, 1, n, k, inputs=(0, 1), output=2), matmul_launch(fmt, 1, n2, k, inputs=(0, 3), output=4),
+                 matmul_launch(fmt, 1, n, n2, inputs=(4, 5), output=6)]
+        for _ in range(3):
+            be.execute(chain, b2)
+            assert max_rel(b2[6].download().view(np.float32), y3) <= 1e-4
 
 
 def _expert_stack(oracle, fmt, e, n, k, seed):

@@ -98,6 +98,7 @@ def test_layer_stack_with_activations_quantized_by_their_producers(m):
     from oracle import oracle as O
     dev = torch.device("cuda", 0)
     be = lp.Backend(0)
+    be.set_option("early_acts", "0")   # both stacks on the same decode kernels (two-row Q4_K launches would differ otherwise)
     stream = torch.cuda.Stream(device=dev)
     be.set_stream(stream.cuda_stream)
     shape, weights, formats = _build(be, tp, O, quant, torch, 0, 1, dev, 2)
