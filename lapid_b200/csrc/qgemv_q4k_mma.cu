@@ -116,7 +116,12 @@ template <int NG> struct WeightMapsT {
     CUtensorMap m[NG];  // packed weights of each member: [n rows][k/256 * 36 words], box 72 words x 16*TILES rows
 };
 
-template <int WARPS, int TILES, int NG>
+// EARLY (GemvArgs::early of every member): the activations are older than the kernel in front of this one, so
+// the kernel reads and computes without waiting for it, parks the tiles' results in shared memory and
+// stores them after the dependency wait. Launched as ONE small CTA per SM, so that the kernels of
+// consecutive launches share the SMs and the ramp-up of one hides behind the tail of the other.
+constexpr int PEND_TILES = 8;
+template <int WARPS, int TILES, int NG, bool EARLY = false>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG> grp) {
     constexpr int THREADS = WARPS * 32;
@@ -179,7 +184,7 @@ qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
 
     // early (GemvArgs::early): the activations are older than the kernel in front of this one, so they are
     // fetched, and the first tile computed, while that kernel still runs; only the stores wait for it
-    const bool early = grp.item[0].early != 0 && grp.item[0].tp == nullptr;
+    constexpr bool early = EARLY;
     auto copy_acts = [&]() {
         const uint32_t chunks = nblk * ABLK / 16;
         for (int i = 0; i < grp.count; i++) {
@@ -201,6 +206,30 @@ qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
     if (!early) copy_acts();
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
+
+    // parked tiles (EARLY): [tile][ELEMS], each element written and later stored by the same thread
+    float *pend = (float *)(acts + grp.act_bytes);
+    uint32_t npend = 0;
+    const uint32_t pend_first = t_lo;  // the CTA's tiles are consecutive; they are parked from its first one on
+    auto flush_pending = [&]() {
+        for (uint32_t q = 0; q < npend; q++) {
+            uint32_t local;
+            const int item = locate(pend_first + q, local);
+            const GemvArgs &p = grp.item[item];
+            for (uint32_t e = threadIdx.x; e < (uint32_t)ELEMS; e += THREADS) {
+                float v = pend[q * ELEMS + e];
+                const uint32_t el = e & 31, i = (e >> 5) & 3, tl = e >> 7;
+                const uint32_t row = local * RPT + tl * 16 + (el >> 2) + ((i & 2) ? 8 : 0);
+                const uint32_t r = 2 * (el & 3) + (i & 1);
+                if (row < p.n && r < grp.item[0].rows) {
+                    const uint32_t bt = r / p.m, ri = r % p.m;
+                    if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
+                    p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = v;
+                }
+            }
+        }
+        npend = 0;
+    };
 
     const uint32_t colq = (uint32_t)gq < M ? gq : 0;        // activation row of this lane's B fragment
     const uint32_t cp = (uint32_t)(2 * t4) < M ? t4 : 0;    // activation row pair of this lane's C fragment
@@ -330,9 +359,20 @@ qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
 #pragma unroll
             for (int i = 0; i < 4; i++) mine[(tl * 4 + i) * 32 + lane] = acc[tl][i];
         __syncthreads();  // the buffer of the other parity is free again once every warp got here
-        if (!waited) {    // nothing is written before the kernel in front has completed
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            waited = true;
+        if (EARLY && !waited) {  // park the tile: nothing is written before the kernel in front has completed
+            for (uint32_t e = threadIdx.x; e < (uint32_t)ELEMS; e += THREADS) {
+                const float *src = red + (size_t)par * WARPS * ELEMS + e;
+                float v = src[0];
+#pragma unroll
+                for (int w = 1; w < WARPS; w++) v += src[(size_t)w * ELEMS];
+                pend[npend * ELEMS + e] = v;
+            }
+            if (++npend == PEND_TILES) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                waited = true;
+                flush_pending();
+            }
+            continue;
         }
         for (uint32_t e = threadIdx.x; e < (uint32_t)ELEMS; e += THREADS) {
             const float *src = red + (size_t)par * WARPS * ELEMS + e;
@@ -350,7 +390,10 @@ qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
             }
         }
     }
-    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");  // a CTA without a tile must not let the grid end early
+    if (!waited) {  // (a CTA without a tile must not let the grid end early either)
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if constexpr (EARLY) flush_pending();
+    }
 }
 
 struct Config {
@@ -359,6 +402,7 @@ struct Config {
 static const Config CONFIGS[] = {{8, 2}, {8, 1}, {4, 1}};
 static int g_force_config = -1;
 
+static size_t early_pend_bytes(int tiles) { return (size_t)PEND_TILES * 16 * tiles * 8 * 4; }
 static size_t fixed_smem(const Config &c) {
     const size_t stage = (size_t)16 * c.tiles * ROWB;
     return BAR_BYTES + (size_t)c.warps * (STAGES * stage + 32 * SC_STRIDE) + (size_t)2 * c.warps * 16 * c.tiles * 8 * 4;
@@ -445,9 +489,9 @@ static bool weight_map(const GemvArgs &a, uint32_t box_rows, CUtensorMap &out) {
     return true;
 }
 
-template <int WARPS, int TILES, int NG>
+template <int WARPS, int TILES, int NG, bool EARLY = false>
 static cudaError_t launch_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cudaStream_t stream) {
-    auto kern = qgemv_q4k_mma_kernel<WARPS, TILES, NG>;
+    auto kern = qgemv_q4k_mma_kernel<WARPS, TILES, NG, EARLY>;
     uint32_t tasks = 0;
     WeightMapsT<NG> maps;
     for (int i = 0; i < g.count; i++) {
@@ -455,14 +499,12 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cudaStrea
         g.task_end[i] = tasks;
         if (!weight_map(g.item[i], 16 * TILES, maps.m[i])) return cudaErrorNotSupported;
     }
-    uint32_t early = pdl ? 1 : 0;
-    for (int i = 0; i < g.count; i++) early &= g.item[i].early;
-    g.item[0].early = early;  // the kernel looks at the first member only
     for (int i = g.count; i < NG; i++) maps.m[i] = maps.m[0];
-    const size_t smem = fixed_smem(Config{WARPS, TILES}) + g.act_bytes;
+    const size_t smem = fixed_smem(Config{WARPS, TILES}) + g.act_bytes + (EARLY ? early_pend_bytes(TILES) : 0);
     static DynamicSmemOptIn opted;
     if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
-    const uint32_t per_sm = (uint32_t)((227 * 1024) / (smem + 1024));  // shared memory is what limits residency
+    uint32_t per_sm = (uint32_t)((227 * 1024) / (smem + 1024));  // shared memory is what limits residency
+    if (EARLY) per_sm = 1;  // the other slots belong to the launches around this one
     uint32_t grid = (uint32_t)sm_count * (per_sm ? per_sm : 1);
     if (grid > tasks) grid = tasks;
     cudaLaunchConfig_t cfg = {};
@@ -478,16 +520,16 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cudaStrea
     return cudaLaunchKernelEx(&cfg, kern, maps, g);
 }
 
-template <int WARPS, int TILES>
+template <int WARPS, int TILES, bool EARLY = false>
 static cudaError_t launch_cfg(GemvGroup &g, int sm_count, bool pdl, cudaStream_t stream) {
-    if (g.count > 1) return launch_n<WARPS, TILES, GEMV_GROUP_MAX>(g, sm_count, pdl, stream);
+    if (g.count > 1) return launch_n<WARPS, TILES, GEMV_GROUP_MAX, EARLY>(g, sm_count, pdl, stream);
     GemvSingle one;  // a lone launch passes a sixth of the parameter bytes
     one.item[0] = g.item[0];
     one.act_off[0] = g.act_off[0];
     one.act_copy[0] = g.act_copy[0];
     one.count = 1;
     one.act_bytes = g.act_bytes;
-    return launch_n<WARPS, TILES, 1>(one, sm_count, pdl, stream);
+    return launch_n<WARPS, TILES, 1, EARLY>(one, sm_count, pdl, stream);
 }
 
 }  // namespace mm
@@ -510,6 +552,12 @@ bool qgemv_q4k_mma_group_fits(GemvGroup &g) {
 cudaError_t launch_qgemv_q4k_mma(GemvGroup &g, int sm_count, bool pdl, cudaStream_t stream) {
     if (g.count < 1 || g.count > GEMV_GROUP_MAX) return cudaErrorInvalidValue;
     mm::plan_acts(g);
+    {   // every member early, no tensor-parallel push, and two of the small CTAs fit on an SM: the early instantiation
+        bool early = pdl && mm::g_force_config < 0;
+        for (int i = 0; i < g.count; i++) early = early && g.item[i].early != 0 && g.item[i].tp == nullptr;
+        const size_t smem = mm::fixed_smem(mm::CONFIGS[2]) + g.act_bytes + mm::early_pend_bytes(1);
+        if (early && 2 * (smem + 1024) <= 227 * 1024) return mm::launch_cfg<4, 1, true>(g, sm_count, pdl, stream);
+    }
     switch (mm::pick_config(g.act_bytes)) {
         case 0: return mm::launch_cfg<8, 2>(g, sm_count, pdl, stream);
         case 1: return mm::launch_cfg<8, 1>(g, sm_count, pdl, stream);
