@@ -47,7 +47,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     return false;
 }
 
-template <int M> __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_i8_fast_kernel(GemvArgs p) {
+// EARLY (one row; GemvArgs::early): the activations are older than the kernel in front of this one, so the
+// kernel reads and computes without waiting for it, parks its results in shared memory and stores them
+// after the dependency wait; launched as one CTA per SM so that consecutive launches share the SMs
+// (see qgemv_q4k.cu).
+constexpr int PEND_ROWS = 32;  // parked results per warp
+template <int M, bool EARLY = false>
+__global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_i8_fast_kernel(GemvArgs p) {
+    static_assert(!EARLY || M == 1, "early mode is built for one row");
     constexpr int WARPS = Shape<M>::WARPS, THREADS = WARPS * 32, STAGES = 2;
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -88,7 +95,21 @@ template <int M> __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M
     issue();
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if constexpr (!EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
+    bool waited = !EARLY;
+    float *pend = act_d + (size_t)p.rows * kg + warp * PEND_ROWS;  // EARLY: behind the activation scales
+    uint32_t npend = 0;
+    const uint32_t pend_first = t_lo + warp;
+    auto flush_pending = [&]() {
+        if (lane == 0)
+            for (uint32_t q = 0; q < npend; q++) {
+                const uint32_t row = pend_first + q * WARPS;
+                float v = pend[q];
+                if (p.extra) v += p.extra[p.ex_off + (int64_t)row * p.ex_s2];
+                p.out[p.out_off + row] = v;
+            }
+        npend = 0;
+    };
     {
         const uint32_t qchunks = p.rows * k / 16, dchunks = p.rows * kg / 4;
         for (uint32_t c = threadIdx.x; c < qchunks; c += THREADS)
@@ -135,6 +156,18 @@ template <int M> __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M
             cslot ^= 1;
             if (cslot == 0) cpar ^= 1;
         }
+        if (EARLY && !waited) {  // park the result: nothing is written before the kernel in front has completed
+            float v = acc[0];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) pend[npend] = v;
+            if (++npend == PEND_ROWS) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                waited = true;
+                flush_pending();
+            }
+            continue;
+        }
 #pragma unroll
         for (int r = 0; r < M; r++) {
             float v = acc[r];
@@ -147,12 +180,20 @@ template <int M> __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M
             }
         }
     }
+    if (!waited) {  // (a CTA without a row must not let the grid end before the kernel in front either)
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if constexpr (EARLY) flush_pending();
+    }
 }
 
-template <int M> static cudaError_t launch_m(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t stream) {
-    auto kern = qgemv_i8_fast_kernel<M>;
+template <int M, bool EARLY = false> static cudaError_t launch_m(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t stream) {
+    if constexpr (M == 1 && !EARLY) {
+        if (pdl && a.early && !a.tp) return launch_m<M, true>(a, sm_count, pdl, stream);
+    }
+    auto kern = qgemv_i8_fast_kernel<M, EARLY>;
     constexpr int WARPS = Shape<M>::WARPS;
-    const size_t smem = BAR_BYTES + (size_t)WARPS * 2 * STAGE + (size_t)a.rows * a.k + (size_t)a.rows * (a.k / GROUP) * 4;
+    const size_t smem = BAR_BYTES + (size_t)WARPS * 2 * STAGE + (size_t)a.rows * a.k + (size_t)a.rows * (a.k / GROUP) * 4 +
+                        (EARLY ? (size_t)WARPS * PEND_ROWS * 4 : 0);
     static size_t occ_smem = 0;
     static int ctas_per_sm = 0;
     static DynamicSmemOptIn opted;
@@ -164,7 +205,8 @@ template <int M> static cudaError_t launch_m(const GemvArgs &a, int sm_count, bo
         ctas_per_sm = occ > 0 ? occ : 1;
         occ_smem = smem;
     }
-    const int per_sm = ctas_per_sm >= 4 ? ctas_per_sm - 1 : ctas_per_sm;  // one slot for the next kernel (see qgemv_q4k.cu)
+    int per_sm = ctas_per_sm >= 4 ? ctas_per_sm - 1 : ctas_per_sm;  // one slot for the next kernel (see qgemv_q4k.cu)
+    if (EARLY) per_sm = 1;                                          // the other slots belong to the launches around this one
     uint32_t grid = (uint32_t)sm_count * (uint32_t)per_sm;
     const uint32_t useful = (a.n + WARPS - 1) / WARPS;
     if (grid > useful) grid = useful;
@@ -188,7 +230,7 @@ template <int M> static cudaError_t launch_m(const GemvArgs &a, int sm_count, bo
 bool qgemv_i8_fast_shape_ok(uint32_t rows, uint32_t k) {
     if (rows < 1 || rows > 8 || k < 512 || k % 512 != 0) return false;
     const size_t warps = rows <= 2 ? 4 : 8;
-    return i8::BAR_BYTES + warps * 2 * i8::STAGE + (size_t)rows * k + (size_t)rows * (k / GROUP) * 4 <= 227 * 1024;
+    return i8::BAR_BYTES + warps * 2 * i8::STAGE + (size_t)rows * k + (size_t)rows * (k / GROUP) * 4 + 4 * i8::PEND_ROWS * 4 <= 227 * 1024 - 1024;
 }
 
 cudaError_t launch_qgemv_i8_fast(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {

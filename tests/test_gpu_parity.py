@@ -652,7 +652,7 @@ def test_glue_kernels_quantize_for_the_next_projection(be, oracle, fmt, name, m)
     be.set_option("early_acts", "1")
 
 
-@pytest.mark.parametrize("fmt,name", [(lp.DType.Q4K, "q4_k"), (lp.DType.Q6K, "q6_k")])
+@pytest.mark.parametrize("fmt,name", [(lp.DType.Q4K, "q4_k"), (lp.DType.Q6K, "q6_k"), (lp.DType.Int8, "int8")])
 @pytest.mark.parametrize("m", [1, 2, 8])
 def test_launches_that_run_ahead_of_their_predecessor(be, oracle, fmt, name, m):
     """A list of decode launches that share activations quantized at its head: from the second launch on the
