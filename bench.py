@@ -442,7 +442,7 @@ def gemv_kernel_name(fmt: int, m: int) -> str:
     if fmt == 8:
         return "qgemv_q6k_mma_kernel" if m >= 3 else "qgemv_kq_fast_kernel<q6_k>"
     if fmt == 7:
-        return "qgemv_kernel<q5_k>"
+        return "qgemv_kq_fast_kernel<q5_k>"
     return "qgemv_i8_mma_kernel" if m >= 2 else "qgemv_i8_fast_kernel"
 
 

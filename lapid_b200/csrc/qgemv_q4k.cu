@@ -1,4 +1,4 @@
-// Q4_K and Q6_K decode GEMV, fast path for 1..8 activation rows (arithmetic: see qgemv.cu; this file only
+// Q4_K, Q5_K and Q6_K decode GEMV, fast path for 1..8 activation rows (arithmetic: see qgemv.cu; this file only
 // changes how the work is laid out on the machine).
 //
 //  * Weights reach the SM through per-warp rings of shared-memory stages filled by the bulk-copy
@@ -29,11 +29,11 @@
 namespace lb {
 
 template <int FMT> struct Blk {
-    static constexpr int BYTES = FMT == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES;
+    static constexpr int BYTES = FMT == FMT_Q4K ? Q4K_BYTES : FMT == FMT_Q5K ? Q5K_BYTES : Q6K_BYTES;
     // 32 blocks by one bulk copy. Q4_K: 4608 bytes, always 16-byte aligned. Q6_K: 6720 bytes that may
     // start anywhere on a 2-byte boundary: the copy starts at the 16-byte boundary below and is up to
     // 16 bytes longer; the consumers add the same offset.
-    static constexpr int STAGE = FMT == FMT_Q4K ? 32 * BYTES : 32 * BYTES + 16;
+    static constexpr int STAGE = FMT == FMT_Q6K ? 32 * BYTES + 16 : 32 * BYTES;  // (Q5_K: 176 = 11 * 16 bytes, aligned like Q4_K)
 };
 constexpr int BAR_BYTES = 256;  // warps * STAGES * 8 <= 256
 // room behind the activation records for results parked in early mode: 4 warps * (16 / M) tasks * up to 4 rows * M floats
@@ -93,6 +93,25 @@ __device__ __forceinline__ float pair_dot(const uint32_t (&v)[8], const uint32_t
         l1 = dp4a_us(v[i + 4] & 0x0F0F0F0Fu, al[i + 4], l1);
         h0 = dp4a_us(v[i] & 0xF0F0F0F0u, ah[i], h0);
         h1 = dp4a_us(v[i + 4] & 0xF0F0F0F0u, ah[i + 4], h1);
+    }
+    acc = fmaf(s0 * da0, (float)(l0 + l1), acc);
+    acc = fmaf(-m0, bs0, acc);
+    acc = fmaf(s1 * da1, (float)(h0 + h1), acc);
+    acc = fmaf(-m1, bs1, acc);
+    return acc;
+}
+
+// The same for Q5_K: 5-bit weights, already unpacked to bytes 0..31 (lo: sub-block 2p, hi: sub-block 2p + 1).
+__device__ __forceinline__ float pair_dot5(const uint32_t (&lo)[8], const uint32_t (&hi)[8], const uint32_t (&al)[8],
+                                           const uint32_t (&ah)[8], float s0, float m0, float s1, float m1, float da0, float da1,
+                                           float bs0, float bs1, float acc) {
+    int l0 = 0, l1 = 0, h0 = 0, h1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        l0 = dp4a_us(lo[i], al[i], l0);
+        l1 = dp4a_us(lo[i + 4], al[i + 4], l1);
+        h0 = dp4a_us(hi[i], ah[i], h0);
+        h1 = dp4a_us(hi[i + 4], ah[i + 4], h1);
     }
     acc = fmaf(s0 * da0, (float)(l0 + l1), acc);
     acc = fmaf(-m0, bs0, acc);
@@ -309,9 +328,9 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             if (healthy && row < n && b < nblk && gl < nblk) {
                 // the stage starts at the 16-byte boundary below its first block (Q6_K; see Blk)
                 const uint32_t first_blk = iters == 1 ? local * RPW * nblk : local * RPW * nblk + it * 32;
-                const uint32_t skew = FMT == FMT_Q4K ? 0u : (uint32_t)(((uintptr_t)wbase + (uint64_t)first_blk * BB) & 15u);
+                const uint32_t skew = FMT != FMT_Q6K ? 0u : (uint32_t)(((uintptr_t)wbase + (uint64_t)first_blk * BB) & 15u);
                 const uint8_t *blk = ring + (size_t)cslot * STAGE_BYTES + skew + (size_t)(iters == 1 ? sub * nblk + gl : gl) * BB;
-                if constexpr (FMT == FMT_Q4K) {
+                if constexpr (FMT == FMT_Q4K || FMT == FMT_Q5K) {
                     const uint4 h = *(const uint4 *)blk;
                     const float d = half_bits_to_float(h.x & 0xffff), dmin = half_bits_to_float(h.x >> 16);
                     const float nd = d * -8388608.0f, ndmin = dmin * -8388608.0f;
@@ -326,17 +345,33 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
                         const uint32_t sel0 = 0x7440u + 2 * (pp & 1), sel1 = sel0 + 1;  // {byte, 0, 0, 0x4B}
                         const float s0 = scale_byte(scw, sel0, d, nd), m0 = scale_byte(mnw, sel0, dmin, ndmin);
                         // the high nibbles are used as 16*q: fold the exact factor 1/16 into their scale
-                        const float s1 = scale_byte(scw, sel1, d, nd) * 0.0625f, m1 = scale_byte(mnw, sel1, dmin, ndmin);
-                        const uint4 qa_ = *(const uint4 *)(blk + 16 + 32 * pp), qb_ = *(const uint4 *)(blk + 32 + 32 * pp);
-                        const uint32_t v[8] = {qa_.x, qa_.y, qa_.z, qa_.w, qb_.x, qb_.y, qb_.z, qb_.w};
+                        constexpr int QS = FMT == FMT_Q5K ? 48 : 16;  // Q5_K: the fifth bits qh[32] sit between the header and the nibbles
+                        const float s1 = scale_byte(scw, sel1, d, nd) * (FMT == FMT_Q5K ? 1.0f : 0.0625f), m1 = scale_byte(mnw, sel1, dmin, ndmin);
+                        const uint4 qa_ = *(const uint4 *)(blk + QS + 32 * pp), qb_ = *(const uint4 *)(blk + QS + 16 + 32 * pp);
+                        uint32_t v[8] = {qa_.x, qa_.y, qa_.z, qa_.w, qb_.x, qb_.y, qb_.z, qb_.w};
+                        uint32_t vh[8];  // Q5_K: the high nibbles shifted down, with their fifth bits
+                        if constexpr (FMT == FMT_Q5K) {
+                            // bit s of qh[l] belongs to element 32 s + l: sub-blocks 2 pp (low nibbles) and 2 pp + 1
+                            const uint4 ha_ = *(const uint4 *)(blk + 16), hb_ = *(const uint4 *)(blk + 32);
+                            const uint32_t hq[8] = {ha_.x, ha_.y, ha_.z, ha_.w, hb_.x, hb_.y, hb_.z, hb_.w};
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                vh[i] = ((v[i] >> 4) & 0x0F0F0F0Fu) | (((hq[i] >> (2 * pp + 1)) & 0x01010101u) << 4);
+                                v[i] = (v[i] & 0x0F0F0F0Fu) | (((hq[i] >> (2 * pp)) & 0x01010101u) << 4);
+                            }
+                        }
 #pragma unroll
                         for (int r = 0; r < M; r++) {
                             const uint4 *rec = (const uint4 *)(iacts + ((size_t)r * nblk + b) * REC + 80 * pp);
                             const uint4 a0 = rec[0], a1 = rec[1], a2 = rec[2], a3 = rec[3], sc = rec[4];
                             const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
                             const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
-                            acc[r] = pair_dot(v, al, ah, s0, m0, s1, m1, __uint_as_float(sc.x), __uint_as_float(sc.y),
-                                              __uint_as_float(sc.z), __uint_as_float(sc.w), acc[r]);
+                            if constexpr (FMT == FMT_Q5K)
+                                acc[r] = pair_dot5(v, vh, al, ah, s0, m0, s1, m1, __uint_as_float(sc.x), __uint_as_float(sc.y),
+                                                   __uint_as_float(sc.z), __uint_as_float(sc.w), acc[r]);
+                            else
+                                acc[r] = pair_dot(v, al, ah, s0, m0, s1, m1, __uint_as_float(sc.x), __uint_as_float(sc.y),
+                                                  __uint_as_float(sc.z), __uint_as_float(sc.w), acc[r]);
                         }
                     }
                 } else {
@@ -508,12 +543,16 @@ template <int FMT, int M> static cudaError_t launch_fast_g(GemvGroup &a, int sm,
     return launch_fast<FMT, M, 32>(a, sm, pdl, s);
 }
 
+static size_t stage_bytes(int fmt) {
+    return fmt == FMT_Q4K ? Blk<FMT_Q4K>::STAGE : fmt == FMT_Q5K ? Blk<FMT_Q5K>::STAGE : Blk<FMT_Q6K>::STAGE;
+}
+
 // Any K that is a multiple of 256, as long as the rings and the activation records fit in shared memory.
 bool qgemv_kq_fast_shape_ok(int fmt, uint32_t rows, uint32_t k) {
-    if (fmt != FMT_Q4K && fmt != FMT_Q6K) return false;
+    if (fmt != FMT_Q4K && fmt != FMT_Q5K && fmt != FMT_Q6K) return false;
     if (rows < 1 || rows > 8 || k % QK != 0 || k < QK) return false;
     const size_t warps = rows <= 2 ? 4 : 8;
-    const size_t stage = fmt == FMT_Q4K ? Blk<FMT_Q4K>::STAGE : Blk<FMT_Q6K>::STAGE;
+    const size_t stage = stage_bytes(fmt);
     return BAR_BYTES + warps * 2 * stage + (size_t)rows * (k / QK) * REC + pend_bytes((int)rows) <= 227 * 1024 - 256;
 }
 
@@ -559,20 +598,21 @@ static void plan_group_acts(GemvGroup &g) {
 size_t qgemv_kq_group_smem(int fmt, GemvGroup &g) {
     plan_group_acts(g);
     const size_t warps = g.item[0].rows <= 2 ? 4 : 8;
-    const size_t stage = fmt == FMT_Q4K ? Blk<FMT_Q4K>::STAGE : Blk<FMT_Q6K>::STAGE;
+    const size_t stage = stage_bytes(fmt);
     return BAR_BYTES + warps * 2 * stage + g.act_bytes + pend_bytes((int)g.item[0].rows);
 }
 
 cudaError_t launch_qgemv_kq_group(int fmt, GemvGroup &g, int sm_count, bool pdl, cudaStream_t s) {
     if (g.count < 1 || g.count > GEMV_GROUP_MAX) return cudaErrorInvalidValue;
     plan_group_acts(g);
-    return fmt == FMT_Q6K ? launch_fmt<FMT_Q6K>(g, sm_count, pdl, s) : launch_fmt<FMT_Q4K>(g, sm_count, pdl, s);
+    return fmt == FMT_Q6K ? launch_fmt<FMT_Q6K>(g, sm_count, pdl, s)
+                          : fmt == FMT_Q5K ? launch_fmt<FMT_Q5K>(g, sm_count, pdl, s) : launch_fmt<FMT_Q4K>(g, sm_count, pdl, s);
 }
 
 bool qgemv_kq_moe_shape_ok(int fmt, uint32_t tokens, uint32_t k) {
-    if (fmt != FMT_Q4K && fmt != FMT_Q6K) return false;
+    if (fmt != FMT_Q4K && fmt != FMT_Q5K && fmt != FMT_Q6K) return false;
     if (tokens < 1 || tokens > 8 || k % QK != 0 || k < QK) return false;
-    const size_t stage = fmt == FMT_Q4K ? Blk<FMT_Q4K>::STAGE : Blk<FMT_Q6K>::STAGE;
+    const size_t stage = stage_bytes(fmt);
     return BAR_BYTES + (size_t)Shape<1>::WARPS * 2 * stage + (size_t)tokens * (k / QK) * REC + pend_bytes(1) <= 227 * 1024 - 256;
 }
 
@@ -596,7 +636,8 @@ cudaError_t launch_qgemv_kq_moe(int fmt, const GemvArgs &a, int sm_count, bool p
     if (!qgemv_kq_moe_shape_ok(fmt, a.rows, a.k) || !a.ids || a.id_r == 0 || a.id_e == 0 || ((uintptr_t)a.w & 15) || (a.id_stride & 15))
         return cudaErrorInvalidValue;
     if ((uint64_t)a.rows * a.id_r * ((a.n + 3) / 4) >= (1ull << 31)) return cudaErrorInvalidValue;  // 32-bit task index
-    return fmt == FMT_Q6K ? launch_moe<FMT_Q6K>(a, sm_count, pdl, s) : launch_moe<FMT_Q4K>(a, sm_count, pdl, s);
+    return fmt == FMT_Q6K ? launch_moe<FMT_Q6K>(a, sm_count, pdl, s)
+                          : fmt == FMT_Q5K ? launch_moe<FMT_Q5K>(a, sm_count, pdl, s) : launch_moe<FMT_Q4K>(a, sm_count, pdl, s);
 }
 
 cudaError_t launch_qgemv_kq_fast(int fmt, const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
