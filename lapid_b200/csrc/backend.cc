@@ -712,6 +712,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             if ((uintptr_t)ins[0]->ptr & 15) fail("invalid_launch", "b200 matmul: quantized activation operand must be 16-byte aligned");
             local.records = p.records();
             local.done = true;
+            local.hoisted = true;  // complete before the list began (see execute_impl)
             slot = &local;
             base = (char *)ins[0]->ptr;
         } else {
@@ -954,6 +955,11 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
         explicit HoistScope(lapid_b200_device *dev_) : d(dev_) { d->after_hoist = -1; }
         ~HoistScope() { d->after_hoist = -1; }
     } hoist_scope(dev);
+    // Operands quantized by their producer (ACT_Q8) were complete before this list began, like the results of
+    // the pre-pass at its head: with the first kernel of the list fully serialised, the later ones may read them early.
+    if (dev->early_acts && dev->pdl)
+        for (size_t i = 0; i < n; i++)
+            if (launches[i].kind == LAPID_B200_KERNEL_MATMUL && launches[i].a_dtype == LAPID_B200_DTYPE_ACT_Q8) dev->after_hoist = 0;
     {
         lb::ActQuantBatch batch;
         batch.count = 0;
@@ -962,7 +968,7 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
             if (batch.count == 0) return;
             cuda_check(lb::launch_act_quant_batch(batch, dev->sm_count, dev->pdl, dev->stream), "act_quant launch");
             dev->launches++;
-            dev->after_hoist = 0;
+            if (dev->early_acts) dev->after_hoist = 0;
             batch.count = 0;
             groups = 0;
         };
