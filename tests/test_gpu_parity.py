@@ -676,6 +676,14 @@ def test_launches_that_run_ahead_of_their_predecessor(be, oracle, fmt, name, m):
         assert be.take_launch_count() == 1 + copies                     # one pre-pass at the head, then one kernel each
         assert max_rel(bufs[1 + copies].download().view(np.float32), wants[-1]) <= 2e-5
     be.set_option("early_acts", "1")
+    # the fused `acc + bias[n]` epilogue is applied when the parked results are stored
+    bias = O.normal(78, n, 1.0)
+    bb = bufs + [be.upload(bias)]
+    biased = [matmul_launch(fmt, m, n, k, inputs=(0, 1 + c), output=1 + copies + c, bias_input=len(bb) - 1) for c in range(copies)]
+    be.execute(biased, bb)
+    for c in range(copies):
+        got = bb[1 + copies + c].download().view(np.float32).reshape(m, n)
+        assert max_rel(got, wants[c].reshape(m, n) + bias[None, :]) <= 2e-5
     if m == 1:   # a launch that reads what an early launch wrote (k == n here would be needed: use a square pair)
         n2 = k
         w2 = oracle.quantize(int(fmt), O.normal(450, n2 * k, 0.05), n2, k)
