@@ -13,6 +13,7 @@
  *   Q4_K / Q5_K / Q6_K quantizers  crates/lapid-quant/src/kquant.rs:25-334
  *   ... and dequantizers ........ crates/lapid-quant/src/kquant.rs:337-396
  *   Int8 (GGUF Q8_0 as planes) .. crates/lapid-quant/src/imp.rs:24-40, :73-116, :143-200
+ *   Int4 (nibble planes) ........ crates/lapid-quant/src/imp.rs:47-71, :148-156; crates/lapid-cpu/src/qmat.rs:97-112
  *   f32 -> f16 .................. `half` 2.7.1 f16::from_f32 (Cargo.lock:1188), IEEE round to
  *                                 nearest even; not vendored in the reference tree, so restated
  *                                 from the IEEE definition and pinned by the 0x3008 known answer
@@ -41,6 +42,7 @@
 #endif
 
 #define LO_FMT_INT8 4
+#define LO_FMT_INT4 5
 #define LO_FMT_Q4K 6
 #define LO_FMT_Q5K 7
 #define LO_FMT_Q6K 8
@@ -113,7 +115,7 @@ static inline int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ?
 /* ------------------------------------------------------------------ layout (lib.rs:27-125) */
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-static int block_elems(int fmt) { return fmt == LO_FMT_INT8 ? GROUP : QK; }
+static int block_elems(int fmt) { return (fmt == LO_FMT_INT8 || fmt == LO_FMT_INT4) ? GROUP : QK; }
 static int block_bytes(int fmt) {
     return fmt == LO_FMT_Q4K ? Q4K_BYTES : (fmt == LO_FMT_Q5K ? Q5K_BYTES : (fmt == LO_FMT_Q6K ? Q6K_BYTES : 0));
 }
@@ -122,7 +124,7 @@ static int is_kfmt(int fmt) { return fmt == LO_FMT_Q4K || fmt == LO_FMT_Q5K || f
 /* out = {qs_offset, qs_bytes, scales_offset, scales_bytes, total}; returns 0, or -1 on a bad
  * format / cols not a multiple of the block. */
 int lo_layout(int fmt, size_t rows, size_t cols, size_t out[5]) {
-    if (fmt != LO_FMT_INT8 && !is_kfmt(fmt)) return -1;
+    if (fmt != LO_FMT_INT8 && fmt != LO_FMT_INT4 && !is_kfmt(fmt)) return -1;
     size_t be = (size_t)block_elems(fmt);
     if (cols % be != 0) return -1;
     if (block_bytes(fmt) != 0) {
@@ -130,7 +132,7 @@ int lo_layout(int fmt, size_t rows, size_t cols, size_t out[5]) {
         out[0] = 0; out[1] = n; out[2] = n; out[3] = 0; out[4] = align_up(n, ALIGN);
         return 0;
     }
-    size_t qs = rows * cols;
+    size_t qs = fmt == LO_FMT_INT8 ? rows * cols : rows * cols / 2; /* Int4: two elements of one group per byte */
     size_t so = align_up(qs, ALIGN);
     size_t sb = rows * (cols / GROUP) * 2;
     out[0] = 0; out[1] = qs; out[2] = so; out[3] = sb; out[4] = align_up(so + sb, ALIGN);
@@ -485,6 +487,32 @@ static float quant_group_i8(const float *x, uint8_t *q) {
     return d;
 }
 
+/* imp.rs:47-71: Int4 group. d = (the value of largest magnitude) / -8, so that value maps to quant 0;
+ * byte j holds element j (low nibble) and element j + 16 (high nibble) as q = trunc(x/d + 8.5) in 0..15. */
+static inline uint8_t nibble_i4(float v) {
+    float t = v + 8.5f;
+    int i;
+    if (t != t) i = 0;                       /* `as i32`: NaN -> 0, saturating */
+    else if (t >= 2147483648.0f) i = 2147483647;
+    else if (t <= -2147483648.0f) i = -2147483647 - 1;
+    else i = (int)t;                          /* truncates toward zero */
+    return (uint8_t)clampi(i, 0, 15);
+}
+static float quant_group_i4(const float *x, uint8_t *q) {
+    float amax = 0.0f, mx = 0.0f;
+    for (int i = 0; i < GROUP; i++) {
+        float a = fabsf(x[i]);
+        if (amax < a) {
+            amax = a;
+            mx = x[i];
+        }
+    }
+    float d = mx == 0.0f ? 0.0f : mx / -8.0f;
+    float id = d != 0.0f ? 1.0f / d : 0.0f;
+    for (int j = 0; j < GROUP / 2; j++) q[j] = (uint8_t)(nibble_i4(x[j] * id) | (nibble_i4(x[j + GROUP / 2] * id) << 4));
+    return d;
+}
+
 /* lib.rs:131 / imp.rs:73-116. `out` holds layout.total bytes; padding is zeroed. Returns 0, or
  * -1 when the format is unknown or cols is not a positive multiple of the block length. */
 int lo_quantize(int fmt, const float *data, size_t rows, size_t cols, uint8_t *out) {
@@ -505,7 +533,8 @@ int lo_quantize(int fmt, const float *data, size_t rows, size_t cols, uint8_t *o
     size_t ng = rows * (cols / GROUP);
 #pragma omp parallel for schedule(static)
     for (long long gi = 0; gi < (long long)ng; gi++) {
-        float d = quant_group_i8(data + (size_t)gi * GROUP, out + (size_t)gi * GROUP);
+        float d = fmt == LO_FMT_INT8 ? quant_group_i8(data + (size_t)gi * GROUP, out + (size_t)gi * GROUP)
+                                     : quant_group_i4(data + (size_t)gi * GROUP, out + (size_t)gi * (GROUP / 2));
         wr_h(out, L[2] + (size_t)gi * 2, d);
     }
     return 0;
@@ -528,6 +557,14 @@ int lo_dequantize_row(int fmt, const uint8_t *bytes, size_t rows, size_t cols, s
     size_t gpr = cols / GROUP;
     for (size_t g = 0; g < gpr; g++) {
         float d = rd_h(bytes, L[2] + (row * gpr + g) * 2);
+        if (fmt == LO_FMT_INT4) { /* imp.rs:148-156 */
+            const uint8_t *b = bytes + (row * cols + g * GROUP) / 2;
+            for (int j = 0; j < GROUP / 2; j++) {
+                out[g * GROUP + j] = (float)((int)(b[j] & 0x0F) - 8) * d;
+                out[g * GROUP + j + GROUP / 2] = (float)((int)(b[j] >> 4) - 8) * d;
+            }
+            continue;
+        }
         const int8_t *q = (const int8_t *)(bytes + row * cols + g * GROUP);
         for (int t = 0; t < GROUP; t++) out[g * GROUP + t] = (float)q[t] * d;
     }
@@ -548,20 +585,21 @@ int lo_dequantize(int fmt, const uint8_t *bytes, size_t rows, size_t cols, float
 int lo_from_ggml_blocks(int fmt, const uint8_t *blocks, size_t n_bytes, size_t rows, size_t cols, uint8_t *out) {
     size_t L[5];
     if (cols == 0 || lo_layout(fmt, rows, cols, L) != 0) return -1;
-    if (fmt != LO_FMT_INT8) {
+    if (fmt != LO_FMT_INT8 && fmt != LO_FMT_INT4) {
         if (n_bytes != L[1]) return -2;
         memset(out, 0, L[4]);
         memcpy(out, blocks, L[1]);
         return 0;
     }
     size_t ng = rows * (cols / GROUP);
-    if (n_bytes != ng * 34) return -2;
+    size_t blk = fmt == LO_FMT_INT8 ? 34 : 18, payload = fmt == LO_FMT_INT8 ? GROUP : GROUP / 2; /* block_q8_0 / block_q4_0 */
+    if (n_bytes != ng * blk) return -2;
     memset(out, 0, L[4]);
     for (size_t gi = 0; gi < ng; gi++) {
-        const uint8_t *b = blocks + gi * 34;
+        const uint8_t *b = blocks + gi * blk;
         out[L[2] + gi * 2] = b[0];
         out[L[2] + gi * 2 + 1] = b[1];
-        memcpy(out + gi * GROUP, b + 2, GROUP);
+        memcpy(out + gi * payload, b + 2, payload);
     }
     return 0;
 }
@@ -684,12 +722,21 @@ static void kcol(int fmt, const uint8_t *wrow, size_t k, size_t rows, const int8
 }
 
 /* crates/lapid-cpu/src/matmul/qkernels.rs:60-84 */
-static void i8col(const uint8_t *bytes, size_t scales_off, size_t col, size_t k, size_t rows, const int8_t *qa,
+static void i8col(int fmt, const uint8_t *bytes, size_t scales_off, size_t col, size_t k, size_t rows, const int8_t *qa,
                   const float *sa, float *acc) {
     size_t kg = k / GROUP;
+    int8_t unpacked[GROUP];
     for (size_t r = 0; r < rows; r++) acc[r] = 0.0f;
     for (size_t g = 0; g < kg; g++) {
         const int8_t *bq = (const int8_t *)(bytes + col * k + g * GROUP);
+        if (fmt == LO_FMT_INT4) { /* QMat::group_i8, qmat.rs:97-112: nibbles re-centred to -8..7 */
+            const uint8_t *b = bytes + (col * k + g * GROUP) / 2;
+            for (int j = 0; j < GROUP / 2; j++) {
+                unpacked[j] = (int8_t)((int)(b[j] & 0x0F) - 8);
+                unpacked[j + GROUP / 2] = (int8_t)((int)(b[j] >> 4) - 8);
+            }
+            bq = unpacked;
+        }
         float db = rd_h(bytes, scales_off + (col * kg + g) * 2);
         for (size_t r = 0; r < rows; r++) {
             float da = sa[r * kg + g];
@@ -757,7 +804,7 @@ int lo_matmul(int fmt, const float *a, size_t a_len, lo_view av, const uint8_t *
 #pragma omp parallel for schedule(static)
         for (long long j = 0; j < (long long)n; j++) {
             float acc[8];
-            if (fmt == LO_FMT_INT8) i8col(w, L[2], (size_t)j, k, rows, qa, sa, acc);
+            if (fmt == LO_FMT_INT8 || fmt == LO_FMT_INT4) i8col(fmt, w, L[2], (size_t)j, k, rows, qa, sa, acc);
             else kcol(fmt, w + (size_t)j * (k / QK) * bb, k, rows, qa, sa, bs, acc);
             for (size_t r = 0; r < rows; r++) {
                 float v = bias ? acc[r] + bias[j] : acc[r];

@@ -27,8 +27,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "lapid_oracle.c")
 
 # dtype codes shared with crates/lapid-c/src/lib.rs:37-60
-INT8, Q4_K, Q5_K, Q6_K = 4, 6, 7, 8
-FORMATS = {"int8": INT8, "q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K}
+INT8, INT4, Q4_K, Q5_K, Q6_K = 4, 5, 6, 7, 8
+FORMATS = {"int8": INT8, "int4": INT4, "q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K}
 BLOCK_BYTES = {Q4_K: 144, Q5_K: 176, Q6_K: 210}
 
 ERRORS = {1: "invalid_launch", 2: "shape_mismatch", 3: "out_of_bounds", 4: "unsupported_dtype"}

@@ -19,7 +19,7 @@ import pytest
 from oracle import oracle as O
 from tests.refgen import make_blocks, noise, rnd
 
-INT8, Q4_K, Q5_K, Q6_K = O.INT8, O.Q4_K, O.Q5_K, O.Q6_K
+INT8, INT4, Q4_K, Q5_K, Q6_K = O.INT8, O.INT4, O.Q4_K, O.Q5_K, O.Q6_K
 
 
 def rel_err(got, want):
@@ -96,11 +96,27 @@ def test_i8_test_vector(oracle):
     assert q.size == 512
 
 
+def test_i4_test_vector(oracle):
+    """`i4_test_vector` and `i4_positive_max_maps_to_minus_eight` (crates/lapid-quant/src/imp.rs:283-304)."""
+    ramp = np.arange(32, dtype=np.float32) - 16.0
+    q = oracle.quantize(INT4, ramp, 1, 32)
+    assert q[:16].tolist() == [0x80, 0x91, 0x91, 0xa2, 0xa2, 0xb3, 0xb3, 0xc4, 0xc4, 0xd5, 0xd5, 0xe6, 0xe6, 0xf7, 0xf7, 0xf8]
+    assert q[256:258].tolist() == [0x00, 0x40]  # d = -16 / -8 = 2.0 = f16 0x4000
+    x = oracle.dequantize(INT4, q, 1, 32).reshape(-1)
+    assert (x[0], x[16], x[31]) == (-16.0, 0.0, 14.0)
+    l = oracle.layout(INT4, 1, 32)
+    assert (l.qs_bytes, l.scales_offset, l.scales_bytes, l.total) == (16, 256, 2, 512)
+    v = np.full(32, 0.5, np.float32)
+    v[3] = 4.0
+    assert oracle.dequantize(INT4, oracle.quantize(INT4, v, 1, 32), 1, 32).reshape(-1)[3] == 4.0
+
+
 def test_zero_groups(oracle):
-    q = oracle.quantize(INT8, np.zeros(64, dtype=np.float32), 2, 32)
-    l = oracle.layout(INT8, 2, 32)
-    assert not q[l.scales_offset:l.scales_offset + l.scales_bytes].any()
-    assert not oracle.dequantize(INT8, q, 2, 32).any()
+    for fmt in (INT8, INT4):
+        q = oracle.quantize(fmt, np.zeros(64, dtype=np.float32), 2, 32)
+        l = oracle.layout(fmt, 2, 32)
+        assert not q[l.scales_offset:l.scales_offset + l.scales_bytes].any()
+        assert not oracle.dequantize(fmt, q, 2, 32).any()
 
 
 def test_round_trip_error_bounds_int8(oracle):
@@ -113,6 +129,11 @@ def test_round_trip_error_bounds_int8(oracle):
     amax = np.abs(g).max(axis=2, keepdims=True)
     tol = amax / 127.0 * 0.5 + amax * 1e-3 + 1e-6
     assert (np.abs(g - y.reshape(g.shape)) <= tol).all()
+    # Int4: up to one step (the side opposite to the extreme saturates at +7), imp.rs:325-330
+    q4 = oracle.quantize(INT4, x, rows, cols)
+    assert q4.size == oracle.layout(INT4, rows, cols).total
+    y4 = oracle.dequantize(INT4, q4, rows, cols).reshape(g.shape)
+    assert (np.abs(g - y4) <= amax / 8.0 + amax * 1e-3 + 1e-6).all()
 
 
 def test_k_formats(oracle):
@@ -204,6 +225,25 @@ def test_quantized_bytes_decode_identically_elsewhere(oracle):
         assert rel_err(mine, x) < {Q4_K: 0.08, Q5_K: 0.04, Q6_K: 0.02}[fmt]
 
 
+def test_int4_planes_decode_like_q4_0_blocks(oracle):
+    """GGUF block_q4_0 (f16 d + 16 nibble bytes) -> lapid Int4 planes (`from_ggml_blocks`, imp.rs:180-199):
+    the oracle's dequantization of the planes equals the independent Q4_0 dequantizer on the blocks, bit for bit,
+    and AoS -> SoA of the oracle's own bytes is the identity."""
+    from gguf import quants
+    rows, cols = 5, 256
+    x = O.normal(19, rows * cols, 0.7)
+    ours = oracle.quantize(INT4, x, rows, cols)
+    l = oracle.layout(INT4, rows, cols)
+    ng = rows * cols // 32
+    blocks = np.empty((ng, 18), dtype=np.uint8)
+    blocks[:, :2] = ours[l.scales_offset:l.scales_offset + 2 * ng].reshape(ng, 2)
+    blocks[:, 2:] = ours[:ng * 16].reshape(ng, 16)
+    assert np.array_equal(oracle.from_ggml_blocks(INT4, blocks.reshape(-1), rows, cols), ours)
+    want = quants.dequantize(blocks, gguf.GGMLQuantizationType.Q4_0).reshape(rows, cols).astype(np.float32)
+    got = oracle.dequantize(INT4, ours, rows, cols).reshape(rows, cols)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
 def test_int8_bytes_match_independent_q8_0_quantizer(oracle):
     from gguf import quants
     rows, cols = 5, 256
@@ -292,20 +332,32 @@ def test_kquant_matmul_matches_dequantized_f32(oracle):
                 assert rel_err(got, want) <= tol, (fmt, m, n, k)
 
 
-def test_quantized_large_m_matches_dequantized_f32_int8(oracle):
-    seed = 1
+@pytest.mark.parametrize("fmt", [INT8, INT4])
+def test_quantized_large_m_matches_dequantized_f32_int8(oracle, fmt):
+    seed = 1 if fmt == INT8 else 5
     for (batch, m, n, k, pad, epi) in [(1, 9, 45, 96, 0, False), (2, 35, 70, 128, 5, True), (1, 130, 200, 256, 3, True)]:
         seed += 1
         w = rnd(n * k, seed)
-        qb = oracle.quantize(INT8, w, n, k)
-        deq = oracle.dequantize(INT8, qb, n, k).astype(np.float64)
+        qb = oracle.quantize(fmt, w, n, k)
+        deq = oracle.dequantize(fmt, qb, n, k).astype(np.float64)
         rs = k + pad
         a = rnd(batch * m * rs, seed + 7)
         bias = rnd(n, seed + 9)
         want = a.reshape(batch * m, rs)[:, :k].astype(np.float64) @ deq.T + (bias.astype(np.float64) if epi else 0.0)
-        got, path = oracle.matmul(INT8, a, qb, n, k, batch=batch, m=m, a_view=(0, m * rs, rs), bias=bias if epi else None)
+        got, path = oracle.matmul(fmt, a, qb, n, k, batch=batch, m=m, a_view=(0, m * rs, rs), bias=bias if epi else None)
         assert path == "f32_act"
         assert rel_err(got, want) <= 2e-5
+    # decode-sized launches: int8 activations against the re-centred nibbles (simd_tiles_match_scalar's reference)
+    n, k = 7, 96
+    qb = oracle.quantize(fmt, rnd(n * k, 40), n, k)
+    deq = oracle.dequantize(fmt, qb, n, k).astype(np.float64)
+    x = O.normal(41, 5 * k, 1.0).reshape(5, k)
+    got, path = oracle.matmul(fmt, x, qb, n, k, m=5)
+    assert path == "int8_act"
+    for r in range(5):
+        qa, sa, _ = oracle.quantize_row_sums(x[r], want_bs=False)
+        want = ((qa.astype(np.float64) * np.repeat(sa, 32))[None, :] * deq).sum(axis=1)
+        assert (np.abs(want - got.reshape(5, n)[r]) <= 1e-3 * np.maximum(np.abs(want), 1.0)).all()
 
 
 def test_strided_output_view_and_validation(oracle):
@@ -343,7 +395,7 @@ def test_strided_output_view_and_validation(oracle):
     assert out.size == 8 and not out.any()
 
 
-@pytest.mark.parametrize("fmt,k", [(INT8, 96), (Q4_K, 256), (Q5_K, 256), (Q6_K, 512)])
+@pytest.mark.parametrize("fmt,k", [(INT8, 96), (INT4, 96), (Q4_K, 256), (Q5_K, 256), (Q6_K, 512)])
 def test_matmul_id_matches_dequantized_f64(oracle, fmt, k):
     """`matmul_id_quant` (crates/lapid-cpu/src/tests.rs:350-383) for the three formats of this path:
     5 experts of [24, k], decode-sized (int8 activations, 2e-2) and prefill-sized (exact, 1e-5) launches
