@@ -41,7 +41,7 @@ sys.path.insert(0, ROOT)
 
 SHAPES = [(4096, 4096, "q/o"), (1024, 4096, "k/v"), (14336, 4096, "gate/up"), (4096, 14336, "down")]
 MS = [1, 2, 4, 8]
-FMT_NAMES = {4: "int8", 6: "q4_k", 7: "q5_k", 8: "q6_k"}
+FMT_NAMES = {4: "int8", 5: "int4", 6: "q4_k", 7: "q5_k", 8: "q6_k"}
 
 
 def weight_bytes(fmt: int, n: int, k: int) -> int:
@@ -51,6 +51,8 @@ def weight_bytes(fmt: int, n: int, k: int) -> int:
         b = n * k // 256 * 176
     elif fmt == 8:
         b = n * k // 256 * 210
+    elif fmt == 5:
+        b = (n * k // 2 + 255) // 256 * 256 + n * k // 32 * 2
     else:
         b = (n * k + 255) // 256 * 256 + n * k // 32 * 2
     return (b + 255) // 256 * 256
@@ -342,7 +344,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     roof_kernel, roof_traffic, roof_detail = None, None, None
     if world == 1 and not args.no_cases:
         POOL = 512 << 20
-        for f in (6, 8, 4, 7):
+        for f in (6, 8, 4, 7, 5):
             for si, (n, k, tag) in enumerate(SHAPES):
                 wq = base[(n, k)] if f == 6 else quantized(f, n, k, 300 + si)
                 wb = wq.numel()
@@ -443,6 +445,8 @@ def gemv_kernel_name(fmt: int, m: int) -> str:
         return "qgemv_q6k_mma_kernel" if m >= 3 else "qgemv_kq_fast_kernel<q6_k>"
     if fmt == 7:
         return "qgemv_kq_fast_kernel<q5_k>"
+    if fmt == 5:
+        return "qgemv_i4_kernel"
     return "qgemv_i8_mma_kernel" if m >= 2 else "qgemv_i8_fast_kernel"
 
 

@@ -60,6 +60,7 @@ typedef int32_t lapid_b200_status;
 #define LAPID_B200_DTYPE_BF16 2
 #define LAPID_B200_DTYPE_I32 3
 #define LAPID_B200_DTYPE_INT8 4
+#define LAPID_B200_DTYPE_INT4 5
 #define LAPID_B200_DTYPE_Q4_K 6
 #define LAPID_B200_DTYPE_Q5_K 7
 #define LAPID_B200_DTYPE_Q6_K 8
@@ -141,14 +142,14 @@ typedef struct lapid_b200_view3 {
 #define LAPID_B200_KERNEL_MATMUL 2 /* position of MatMul in `enum Kernel`, ir.rs:395-414 */
 /* Kernel::Gather (ir.rs:284-300, CPU crates/lapid-cpu/src/rows.rs:164-215): out[i, :] = dequant(table[ids[i], :]),
  * the embedding lookup from a quantized table. In a launch of this kind: b_dtype = table dtype (F32,
- * INT8, Q4_K, Q5_K, Q6_K), out_dtype F32, k = rows of the table, n = cols, m = count, batch 1;
+ * INT8, INT4, Q4_K, Q5_K, Q6_K), out_dtype F32, k = rows of the table, n = cols, m = count, batch 1;
  * inputs = {table [k, n] in lapid-quant layout, indices i32 [m] contiguous}, n_inputs 2; output f32
  * [m, n] contiguous (the views are not used). An index outside [0, k) makes execute fail with
  * "index_out_of_range" after the launch sequence ran; the kernel does not read out of bounds. */
 #define LAPID_B200_KERNEL_GATHER 3
 /* Kernel::MatMulId (ir.rs:425-443, CPU crates/lapid-cpu/src/moe.rs:21-120): the mixture-of-experts matmul
  * out[t, s, :] = W[ids[t, s]] x[t] over a stack of e quantized matrices [n, k], each a lapid-quant matrix at
- * byte offset expert * layout(n, k).total. In a launch of this kind: b_dtype = w dtype (INT8, Q4_K, Q5_K, Q6_K),
+ * byte offset expert * layout(n, k).total. In a launch of this kind: b_dtype = w dtype (INT8, INT4, Q4_K, Q5_K, Q6_K),
  * a_dtype and out_dtype F32, m = t (tokens), batch = r (slots per token), b.batch_stride = e, n, k;
  * inputs = {x f32 [t, k] contiguous, w, ids i32 [t, r] contiguous}, n_inputs 3; output f32 [t, r, n]
  * contiguous (the other view fields are not used). t <= 8 uses the int8-activation arithmetic of the decode
@@ -166,7 +167,7 @@ typedef struct lapid_b200_view3 {
 typedef struct lapid_b200_launch {
     int32_t kind;         /* LAPID_B200_KERNEL_MATMUL (the fields below describe it), LAPID_B200_KERNEL_GATHER or LAPID_B200_KERNEL_MATMUL_ID (see above) */
     int32_t a_dtype;      /* MatMulSpec.a_dtype: F32 (or LAPID_B200_DTYPE_ACT_Q8, see above) */
-    int32_t b_dtype;      /* MatMulSpec.b_dtype: INT8 | Q4_K | Q5_K | Q6_K */
+    int32_t b_dtype;      /* MatMulSpec.b_dtype: INT8 | INT4 | Q4_K | Q5_K | Q6_K */
     int32_t out_dtype;    /* MatMulSpec.out_dtype: F32 */
     int32_t b_transposed; /* must be 1 for a quantized B */
     int32_t epilogue;     /* LAPID_B200_EPILOGUE_* */

@@ -25,6 +25,7 @@ class DType(enum.IntEnum):
     BF16 = 2
     I32 = 3
     Int8 = 4
+    Int4 = 5
     Q4K = 6
     Q5K = 7
     Q6K = 8

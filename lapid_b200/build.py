@@ -26,6 +26,7 @@ SOURCES = {
     "qgemv_q4k_mma.cu": [],
     "qgemv_q6k_mma.cu": [],
     "qgemv_i8.cu": [],
+    "qgemv_i4.cu": [],
     "qgemv_i8_mma.cu": [],
     "qgemm_f32.cu": [],
     "qgemm_tc.cu": [],

@@ -100,10 +100,11 @@ void cuda_check(cudaError_t e, const char *what) {
 
 // ------------------------------------------------------------------ layout (lapid-quant lib.rs:84-125)
 bool is_quant(int32_t dt) {
-    return dt == LAPID_B200_DTYPE_INT8 || dt == LAPID_B200_DTYPE_Q4_K || dt == LAPID_B200_DTYPE_Q5_K || dt == LAPID_B200_DTYPE_Q6_K;
+    return dt == LAPID_B200_DTYPE_INT8 || dt == LAPID_B200_DTYPE_INT4 || dt == LAPID_B200_DTYPE_Q4_K || dt == LAPID_B200_DTYPE_Q5_K ||
+           dt == LAPID_B200_DTYPE_Q6_K;
 }
 bool has_min_term(int32_t dt) { return dt == LAPID_B200_DTYPE_Q4_K || dt == LAPID_B200_DTYPE_Q5_K; }  // the decode tiles need d * sum(q) per activation group
-uint64_t block_elems(int32_t dt) { return dt == LAPID_B200_DTYPE_INT8 ? 32 : 256; }
+uint64_t block_elems(int32_t dt) { return (dt == LAPID_B200_DTYPE_INT8 || dt == LAPID_B200_DTYPE_INT4) ? 32 : 256; }
 uint64_t block_bytes(int32_t dt) {
     return dt == LAPID_B200_DTYPE_Q4_K ? 144 : dt == LAPID_B200_DTYPE_Q5_K ? 176 : dt == LAPID_B200_DTYPE_Q6_K ? 210 : 0;
 }
@@ -128,7 +129,7 @@ lapid_b200_layout layout_of(int32_t fmt, uint64_t rows, uint64_t cols) {
         return l;
     }
     l.qs_offset = 0;
-    l.qs_bytes = rows * cols;
+    l.qs_bytes = fmt == LAPID_B200_DTYPE_INT4 ? rows * cols / 2 : rows * cols;  // Int4: two elements of a group per byte
     l.scales_offset = align_up(l.qs_bytes, 256);
     l.scales_bytes = rows * (cols / 32) * 2;
     l.total = align_up(l.scales_offset + l.scales_bytes, 256);
@@ -330,7 +331,7 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
     Plan p;
     if (l.kind != LAPID_B200_KERNEL_MATMUL) fail("unsupported", "kernel kind " + std::to_string(l.kind) + " is not MatMul");
     if (!is_quant(l.b_dtype))
-        fail("unsupported_dtype", "b200 matmul: b dtype " + std::to_string(l.b_dtype) + " (want int8, q4_k, q5_k or q6_k)");
+        fail("unsupported_dtype", "b200 matmul: b dtype " + std::to_string(l.b_dtype) + " (want int8, int4, q4_k, q5_k or q6_k)");
     if ((l.a_dtype != LAPID_B200_DTYPE_F32 && l.a_dtype != LAPID_B200_DTYPE_ACT_Q8) || l.out_dtype != LAPID_B200_DTYPE_F32)
         fail("unsupported_dtype", "b200 matmul: a and out must be f32");
     if (l.epilogue != LAPID_B200_EPILOGUE_NONE && l.epilogue != LAPID_B200_EPILOGUE_ADD)
@@ -418,7 +419,7 @@ lb::ActOut act_out_checked(lapid_b200_device *dev, lapid_b200_buffer *qact, int3
 void check_gather(const lapid_b200_launch &l) {
     const bool quant = is_quant(l.b_dtype);
     if (!quant && l.b_dtype != LAPID_B200_DTYPE_F32)
-        fail("unsupported_dtype", "b200 gather: table dtype " + std::to_string(l.b_dtype) + " (want f32, int8, q4_k, q5_k or q6_k)");
+        fail("unsupported_dtype", "b200 gather: table dtype " + std::to_string(l.b_dtype) + " (want f32, int8, int4, q4_k, q5_k or q6_k)");
     if (l.out_dtype != LAPID_B200_DTYPE_F32) fail("unsupported_dtype", "b200 gather: out must be f32");
     if (l.n_inputs != 2) fail("invalid_launch", "expected 2 inputs, got " + std::to_string(l.n_inputs));
     if (l.batch != 1) fail("invalid_launch", "b200 gather: batch must be 1");
@@ -474,7 +475,7 @@ struct MoePlan {
 MoePlan plan_matmul_id(const lapid_b200_device &dev, const lapid_b200_launch &l) {
     MoePlan p;
     if (!is_quant(l.b_dtype))
-        fail("unsupported_dtype", "b200 matmul_id: w dtype " + std::to_string(l.b_dtype) + " (want int8, q4_k, q5_k or q6_k)");
+        fail("unsupported_dtype", "b200 matmul_id: w dtype " + std::to_string(l.b_dtype) + " (want int8, int4, q4_k, q5_k or q6_k)");
     if (l.a_dtype != LAPID_B200_DTYPE_F32 || l.out_dtype != LAPID_B200_DTYPE_F32)
         fail("unsupported_dtype", "b200 matmul_id: x and out must be f32");
     if (l.epilogue != LAPID_B200_EPILOGUE_NONE) fail("unsupported", "b200 matmul_id: no epilogue");
@@ -578,7 +579,8 @@ void run_matmul_id(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b20
         g.id_r = (uint32_t)p.r;
         g.id_e = (uint32_t)p.e;
         const bool pdl = dev.pdl_launch();
-        if (p.fast) cuda_check(lb::launch_qgemv_kq_moe(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "matmul_id launch");
+        if (l.b_dtype == LAPID_B200_DTYPE_INT4) cuda_check(lb::launch_qgemv_i4(g, dev.sm_count, pdl, dev.stream), "matmul_id launch");
+        else if (p.fast) cuda_check(lb::launch_qgemv_kq_moe(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "matmul_id launch");
         else cuda_check(lb::launch_qgemv_moe(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "matmul_id launch");
         dev.launches += 2;
         return;
@@ -785,6 +787,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             if (l.b_dtype == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(one, dev.sm_count, pdl, dev.stream), "qgemv launch");
             else cuda_check(lb::launch_qgemv_q4k_mma(one, dev.sm_count, pdl, dev.stream), "qgemv launch");
         } else if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        else if (l.b_dtype == LAPID_B200_DTYPE_INT4) cuda_check(lb::launch_qgemv_i4(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (p.fast_i8 && ((uintptr_t)g.w & 15) == 0) cuda_check(lb::launch_qgemv_i8_fast(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         dev.launches++;
@@ -1322,7 +1325,7 @@ lapid_b200_status lapid_b200_from_ggml_blocks(lapid_b200_device *dev, int32_t fo
         if (!src || !dst) fail("invalid_argument", "src or dst is NULL");
         if (cols == 0) fail("invalid_launch", "quantized cols must be positive");
         lapid_b200_layout l = layout_of(format, rows, cols);
-        uint64_t want = block_bytes(format) ? l.qs_bytes : rows * (cols / 32) * 34;
+        uint64_t want = block_bytes(format) ? l.qs_bytes : rows * (cols / 32) * (format == LAPID_B200_DTYPE_INT4 ? 18 : 34);
         if (src_bytes != want || src->bytes < src_bytes)
             fail("shape_mismatch", "from_ggml_blocks: got " + std::to_string(src_bytes) + " bytes, expected " + std::to_string(want));
         if (dst->bytes < l.total)
@@ -1332,6 +1335,10 @@ lapid_b200_status lapid_b200_from_ggml_blocks(lapid_b200_device *dev, int32_t fo
         cuda_check(cudaMemsetAsync(dst->ptr, 0, l.total, dev->stream), "memset");
         if (block_bytes(format)) {
             if (want) cuda_check(cudaMemcpyAsync(dst->ptr, src->ptr, want, cudaMemcpyDeviceToDevice, dev->stream), "copy");
+        } else if (format == LAPID_B200_DTYPE_INT4) {
+            cuda_check(lb::launch_q4_0_to_planes(src->ptr, dst->ptr, l.scales_offset, rows * (cols / 32), dev->sm_count, dev->stream),
+                       "q4_0 repack launch");
+            dev->launches++;
         } else {
             cuda_check(lb::launch_q8_0_to_planes(src->ptr, dst->ptr, l.scales_offset, rows * (cols / 32), dev->sm_count, dev->stream),
                        "q8_0 repack launch");

@@ -9,6 +9,7 @@
 namespace lb {
 
 constexpr int FMT_INT8 = 4;  // lapid dtype codes (crates/lapid-c/src/lib.rs:37-60)
+constexpr int FMT_INT4 = 5;  // nibble planes: byte j of a 32-group holds element j (low) and j + 16 (high); x = (q - 8) * d
 constexpr int FMT_Q4K = 6;
 constexpr int FMT_Q5K = 7;
 constexpr int FMT_Q6K = 8;

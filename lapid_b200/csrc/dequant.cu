@@ -4,6 +4,7 @@
 //   dequantize_q5k   crates/lapid-quant/src/kquant.rs:355-373   y = (d*sc)*(q + 16*h) - (dmin*m)
 //   dequantize_q6k   crates/lapid-quant/src/kquant.rs:376-396   y = (d*sc)*(q-32)
 //   Int8 rows        crates/lapid-quant/src/imp.rs:143-148      y = f32(q) * f32(d)
+//   Int4 rows        crates/lapid-quant/src/imp.rs:148-156      y = f32(nibble - 8) * f32(d)
 //   from_ggml_blocks crates/lapid-quant/src/imp.rs:171-200
 //
 // One CTA of 256 threads expands one 256-element super-block (or eight Int8 groups); thread t
@@ -88,11 +89,44 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t *__restrict__
         if (FMT == FMT_Q4K) v = q4k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q4K_BYTES, (int)(c % QK));
         else if (FMT == FMT_Q5K) v = q5k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q5K_BYTES, (int)(c % QK));
         else if (FMT == FMT_Q6K) v = q6k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q6K_BYTES, (int)(c % QK));
-        else if (FMT == FMT_INT8)
+        else if (FMT == FMT_INT4) {
+            const uint64_t pos = (uint64_t)r * cols + c, g = pos >> 5;
+            const uint32_t e = (uint32_t)(pos & 31);
+            const uint8_t b = table[g * 16 + (e & 15)];
+            v = xmul((float)((int)((e < 16 ? b : (b >> 4)) & 15) - 8), half_bits_to_float(((const uint16_t *)(table + scales_offset))[g]));
+        } else if (FMT == FMT_INT8)
             v = xmul((float)((const int8_t *)table)[(uint64_t)r * cols + c],
                      half_bits_to_float(((const uint16_t *)(table + scales_offset))[((uint64_t)r * cols + c) >> 5]));
         else v = ((const float *)table)[(uint64_t)r * cols + c];
         out[i * cols + c] = v;
+    }
+}
+
+// element c of row-major position `pos` = r * cols + c in an Int4 plane (crates/lapid-quant/src/imp.rs:148-156)
+__device__ __forceinline__ float int4_element(const uint8_t *qs, const uint16_t *scales, uint64_t pos) {
+    const uint64_t g = pos >> 5;
+    const uint32_t e = (uint32_t)(pos & 31);
+    const uint8_t b = qs[g * 16 + (e & 15)];
+    const int q = (int)((e < 16 ? b : (b >> 4)) & 15) - 8;
+    return xmul((float)q, half_bits_to_float(scales[g]));
+}
+
+__global__ void __launch_bounds__(256) dequant_int4_kernel(const uint8_t *__restrict__ qs, const uint16_t *__restrict__ scales,
+                                                           float *__restrict__ dst, uint64_t n_elems) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_elems; i += stride) dst[i] = int4_element(qs, scales, i);
+}
+
+// GGUF block_q4_0 (f16 d + 16 nibble bytes, 18 bytes) -> nibble plane + scales plane: the same nibble order.
+__global__ void __launch_bounds__(256) q4_0_to_planes_kernel(const uint8_t *__restrict__ blocks, uint8_t *__restrict__ qs,
+                                                             uint8_t *__restrict__ scales, uint64_t n_groups) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_groups * 16; i += stride) {
+        uint64_t g = i >> 4;
+        int t = (int)(i & 15);
+        const uint8_t *b = blocks + g * 18;
+        qs[i] = b[2 + t];
+        if (t < 2) scales[g * 2 + t] = b[t];
     }
 }
 
@@ -137,6 +171,9 @@ cudaError_t launch_dequantize(int fmt, const void *src, uint64_t rows, uint64_t 
         dequant_q5k_kernel<<<grid_for(n / QK, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n / QK);
     } else if (fmt == FMT_Q6K) {
         dequant_q6k_kernel<<<grid_for(n / QK, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n / QK);
+    } else if (fmt == FMT_INT4) {
+        const uint8_t *p = (const uint8_t *)src;
+        dequant_int4_kernel<<<grid_for((n + 255) / 256, sm_count), 256, 0, stream>>>(p, (const uint16_t *)(p + scales_offset), dst, n);
     } else {
         const uint8_t *p = (const uint8_t *)src;
         dequant_int8_kernel<<<grid_for((n + 255) / 256, sm_count), 256, 0, stream>>>(
@@ -155,7 +192,17 @@ cudaError_t launch_gather(int fmt, const void *table, uint64_t scales_offset, co
     else if (fmt == FMT_Q5K) gather_kernel<FMT_Q5K><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
     else if (fmt == FMT_Q6K) gather_kernel<FMT_Q6K><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
     else if (fmt == FMT_INT8) gather_kernel<FMT_INT8><<<grid, 256, 0, stream>>>(t, scales_offset, ids, rows, cols, count, out, status);
+    else if (fmt == FMT_INT4) gather_kernel<FMT_INT4><<<grid, 256, 0, stream>>>(t, scales_offset, ids, rows, cols, count, out, status);
     else gather_kernel<-1><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_q4_0_to_planes(const void *blocks, void *dst, uint64_t scales_offset, uint64_t n_groups,
+                                  int sm_count, cudaStream_t stream) {
+    if (n_groups == 0) return cudaSuccess;
+    uint8_t *d = (uint8_t *)dst;
+    q4_0_to_planes_kernel<<<grid_for((n_groups * 16 + 255) / 256, sm_count), 256, 0, stream>>>(
+        (const uint8_t *)blocks, d, d + scales_offset, n_groups);
     return cudaGetLastError();
 }
 

@@ -12,6 +12,9 @@ cudaError_t launch_dequantize(int fmt, const void *src, uint64_t rows, uint64_t 
                               float *dst, int sm_count, cudaStream_t stream);
 cudaError_t launch_q8_0_to_planes(const void *blocks, void *dst, uint64_t scales_offset, uint64_t n_groups,
                                   int sm_count, cudaStream_t stream);
+cudaError_t launch_q4_0_to_planes(const void *blocks, void *dst, uint64_t scales_offset, uint64_t n_groups,
+                                  int sm_count, cudaStream_t stream);
+
 
 // ---- quantize.cu
 cudaError_t launch_quantize(int fmt, const float *src, uint64_t rows, uint64_t cols, uint64_t scales_offset,
@@ -99,6 +102,8 @@ struct GemvArgs {
 cudaError_t launch_qgemv(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // Expert-indexed form of the same kernel for every format and K (args.ids set; args.rows = tokens, 1..8).
 cudaError_t launch_qgemv_moe(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+// ---- qgemv_i4.cu: Int4 nibble planes, 1..8 rows (and the expert-indexed form: args.ids set, rows = tokens)
+cudaError_t launch_qgemv_i4(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // Opt in to the dynamic shared memory the GEMV variants need; once per device.
 cudaError_t qgemv_init();
 

@@ -366,6 +366,48 @@ __global__ void __launch_bounds__(256) quantize_int8_kernel(const float *__restr
     }
 }
 
+// Int4 (crates/lapid-quant/src/imp.rs:47-71): d = (the value of largest magnitude) / -8, q = trunc(x / d + 8.5)
+// clamped to 0..15, byte j = element j | element j + 16 << 4. One thread per 32-group.
+__global__ void __launch_bounds__(256) quantize_int4_kernel(const float *__restrict__ src, uint8_t *__restrict__ qs,
+                                                            uint16_t *__restrict__ scales, uint64_t n_groups) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; g < n_groups; g += stride) {
+        const float4 *xp = (const float4 *)(src + g * 32);
+        float x[32];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float4 v = xp[i];
+            x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+        }
+        float amax = 0.0f, mx = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            float a = fabsf(x[i]);
+            if (amax < a) {
+                amax = a;
+                mx = x[i];
+            }
+        }
+        float d = mx == 0.0f ? 0.0f : xdiv(mx, -8.0f);
+        float id = d != 0.0f ? xdiv(1.0f, d) : 0.0f;
+        auto nib = [&](float v) -> uint32_t {
+            float t = xadd(xmul(v, id), 8.5f);
+            int q = (t != t) ? 0 : (t >= 2147483648.0f ? 2147483647 : (t <= -2147483648.0f ? (-2147483647 - 1) : (int)t));
+            return (uint32_t)clampi(q, 0, 15);
+        };
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint32_t wv = 0;
+#pragma unroll
+            for (int t = 0; t < 4; t++) wv |= (nib(x[4 * i + t]) | (nib(x[4 * i + t + 16]) << 4)) << (8 * t);
+            packed[i] = wv;
+        }
+        *(uint4 *)(qs + g * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        scales[g] = __half_as_ushort(__float2half_rn(d));
+    }
+}
+
 cudaError_t launch_quantize(int fmt, const float *src, uint64_t rows, uint64_t cols, uint64_t scales_offset,
                             uint64_t total_bytes, void *dst, int sm_count, cudaStream_t stream) {
     cudaError_t e = cudaMemsetAsync(dst, 0, total_bytes, stream);  // padding (and gaps) are zero
@@ -382,6 +424,10 @@ cudaError_t launch_quantize(int fmt, const float *src, uint64_t rows, uint64_t c
     } else if (fmt == FMT_Q6K) {
         uint64_t nb = n / QK, ctas = (nb + Q6_BLOCKS_PER_CTA - 1) / Q6_BLOCKS_PER_CTA;
         quantize_q6k_kernel<<<(int)(ctas < cap ? ctas : cap), 256, 0, stream>>>(src, (uint8_t *)dst, nb);
+    } else if (fmt == FMT_INT4) {
+        uint64_t ng = n / GROUP, ctas = (ng + 255) / 256;
+        uint8_t *d = (uint8_t *)dst;
+        quantize_int4_kernel<<<(int)(ctas < cap ? ctas : cap), 256, 0, stream>>>(src, d, (uint16_t *)(d + scales_offset), ng);
     } else {
         uint64_t ng = n / GROUP, ctas = (ng + 255) / 256;
         uint8_t *d = (uint8_t *)dst;

@@ -20,15 +20,16 @@ ALIGN = 256
 class Format(enum.IntEnum):
     """Formats this backend implements; values are lapid-c's dtype codes."""
     Int8 = 4   # GGUF Q8_0 in lapid's plane layout
+    Int4 = 5   # GGUF Q4_0's nibbles in lapid's plane layout
     Q4K = 6
     Q5K = 7
     Q6K = 8
 
     def block_elems(self) -> int:
-        return 32 if self is Format.Int8 else 256
+        return 32 if self in (Format.Int8, Format.Int4) else 256
 
     def block_bytes(self) -> int:
-        return {Format.Int8: 0, Format.Q4K: 144, Format.Q5K: 176, Format.Q6K: 210}[self]
+        return {Format.Int8: 0, Format.Int4: 0, Format.Q4K: 144, Format.Q5K: 176, Format.Q6K: 210}[self]
 
     def is_aos(self) -> bool:
         return self.block_bytes() != 0

@@ -45,19 +45,21 @@ def test_abi_version_and_mismatch_error_json():
 
 
 def test_layout_matches_oracle_and_reference_sizes(oracle):
-    for fmt in (quant.Format.Int8, quant.Format.Q4K, quant.Format.Q6K):
-        for rows, cols in [(1, 256), (3, 512), (768, 768 if fmt == quant.Format.Int8 else 1024), (4096, 4096), (14336, 4096),
+    for fmt in (quant.Format.Int8, quant.Format.Int4, quant.Format.Q4K, quant.Format.Q5K, quant.Format.Q6K):
+        for rows, cols in [(1, 256), (3, 512), (768, 768 if fmt.block_elems() == 32 else 1024), (4096, 4096), (14336, 4096),
                            (4096, 14336), (128256, 4096)]:
             a, b = quant.layout(fmt, rows, cols), oracle.layout(int(fmt), rows, cols)
             assert (a.qs_offset, a.qs_bytes, a.scales_offset, a.scales_bytes, a.total) == \
                    (b.qs_offset, b.qs_bytes, b.scales_offset, b.scales_bytes, b.total)
     l = quant.layout(quant.Format.Int8, 1, 32)
     assert (l.qs_bytes, l.scales_offset, l.scales_bytes, l.total) == (32, 256, 2, 512)
+    l = quant.layout(quant.Format.Int4, 1, 32)
+    assert (l.qs_bytes, l.scales_offset, l.scales_bytes, l.total) == (16, 256, 2, 512)
     with pytest.raises(lp.LapidError) as e:
         quant.layout(quant.Format.Q4K, 2, 128)
     assert e.value.code == "invalid_launch" and e.value.status == 8
     with pytest.raises(lp.LapidError) as e:
-        quant.layout(5, 2, 128)  # int4: not implemented here
+        quant.layout(9, 2, 128)  # mxfp4: not implemented here
     assert e.value.code == "unsupported_dtype" and e.value.status == 3
 
 

@@ -20,7 +20,8 @@ from tests.refgen import make_blocks, rnd
 
 pytestmark = pytest.mark.gpu
 
-FMTS = [(lp.DType.Int8, "int8"), (lp.DType.Q4K, "q4_k"), (lp.DType.Q5K, "q5_k"), (lp.DType.Q6K, "q6_k")]
+FMTS = [(lp.DType.Int8, "int8"), (lp.DType.Int4, "int4"), (lp.DType.Q4K, "q4_k"), (lp.DType.Q5K, "q5_k"), (lp.DType.Q6K, "q6_k")]
+PLANES = (lp.DType.Int8, lp.DType.Int4)   # formats with 32-element groups in plane layout
 
 
 @pytest.fixture(scope="module")
@@ -88,7 +89,7 @@ def test_golden_vectors(be, oracle, fmt, name):
 @pytest.mark.parametrize("fmt,name", FMTS)
 def test_dequantize_bit_exact_random_blocks(be, oracle, fmt, name):
     rows, cols = 16, 2048
-    if fmt == lp.DType.Int8:
+    if fmt in PLANES:
         l = oracle.layout(int(fmt), rows, cols)
         rng = np.random.default_rng(3)
         qb = np.zeros(l.total, np.uint8)
@@ -146,6 +147,12 @@ def test_from_ggml_blocks(be, oracle):
     blocks[:, :2] = ours[l.scales_offset:l.scales_offset + 2 * ng].reshape(ng, 2)
     blocks[:, 2:] = ours[:ng * 32].reshape(ng, 32)
     assert np.array_equal(quant.from_ggml_blocks(be, quant.Format.Int8, blocks, rows, cols), ours)
+    ours4 = oracle.quantize(O.INT4, x, rows, cols)          # GGUF block_q4_0: f16 d + 16 nibble bytes
+    l4 = oracle.layout(O.INT4, rows, cols)
+    b4 = np.empty((ng, 18), np.uint8)
+    b4[:, :2] = ours4[l4.scales_offset:l4.scales_offset + 2 * ng].reshape(ng, 2)
+    b4[:, 2:] = ours4[:ng * 16].reshape(ng, 16)
+    assert np.array_equal(quant.from_ggml_blocks(be, quant.Format.Int4, b4, rows, cols), ours4)
     for fmt in (quant.Format.Q4K, quant.Format.Q6K):
         q = oracle.quantize(int(fmt), O.normal(8, 3 * 512, 0.02), 3, 512)
         lq = oracle.layout(int(fmt), 3, 512)
@@ -177,7 +184,7 @@ def test_gemv_reference_test_shapes(be, oracle, fmt, name):
     for (m, n, k, pad) in [(1, 37, 512, 0), (3, 20, 256, 4), (6, 9, 256, 0), (1, 36, 768, 0), (3, 36, 768, 1),
                            (2, 1030, 4096, 0), (8, 77, 14336, 0), (1, 5, 2304, 0), (4, 50, 14336, 0), (3, 40, 8192, 8),
                            (2, 3, 16384, 0), (1, 300, 28672, 0)]:
-        if fmt != lp.DType.Int8 and k % 256:
+        if fmt not in PLANES and k % 256:
             continue
         seed += 1
         w = rnd(n * k, seed) if n * k < 100000 else O.normal(seed, n * k, 0.5)
