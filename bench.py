@@ -403,6 +403,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                         "achieved": round(v["bytes"] / (v["us"] * 1e-6) / 1e9, 1),
                         "frac": round(v["bytes"] / (v["us"] * 1e-6) / 1e9 / peak, 4)} for kname, v in by_kernel.items()]
 
+        # the north star's own case, one row on the large shapes, listed beside the aggregates
+        for r in q4:
+            if r["m"] == 1 and r["n"] * r["k"] >= 4096 * 14336:
+                roof_detail.append({"kernel": r["kernel"], "case": f"M=1 {r['n']}x{r['k']}", "launches": 1, "us": r["us"],
+                                    "achieved": r["gbs"], "frac": r["frac"]})
+
     achieved = roof if roof is not None else value / world
     line = {
         "metric": "q4k_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
