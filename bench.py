@@ -480,7 +480,7 @@ def _event_time(stream, fn, reps, warm=2):
 
 
 def measure_prefill(be, stream, dev, base, quantized):
-    """Prefill GEMM (tcgen05): Q4_K at M in {64, 512, 2048} and Q6_K at M in {512, 2048} on the gate/up
+    """Prefill GEMM (tcgen05): Q4_K at M in {64, 512, 2048}, Q6_K and Q5_K at M in {512, 2048} on the gate/up
     and down shapes; five weight copies are cycled (165 MB > L2). TFLOP/s = 2*M*N*K / time, against
     the measured bf16 peaks."""
     import torch
@@ -492,9 +492,9 @@ def measure_prefill(be, stream, dev, base, quantized):
     except Exception:
         burst, sustained = 1590.0, 1400.0
     rows = []
-    for fmt, (n, k) in [(f, s) for f in (6, 8) for s in [(14336, 4096), (4096, 14336)]]:
+    for fmt, (n, k) in [(f, s) for f in (6, 8, 7) for s in [(14336, 4096), (4096, 14336)]]:
         copies = 5
-        wq = base[(n, k)] if fmt == 6 else quantized(8, n, k, 700 + n)
+        wq = base[(n, k)] if fmt == 6 else quantized(fmt, n, k, 700 + n)
         pool = wq.repeat(copies).view(copies, -1)
         for m in ((64, 512, 2048) if fmt == 6 else (512, 2048)):
             a = torch.randn(m * k, device=dev)

@@ -380,7 +380,8 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
             if (tiles > p.scratch) p.scratch = tiles;
         }
     } else {
-        p.tc = !dev.gemm_f32 && l.k % 256 == 0 && l.k >= 256 && (l.b_dtype == LAPID_B200_DTYPE_Q4_K || l.b_dtype == LAPID_B200_DTYPE_Q6_K);
+        p.tc = !dev.gemm_f32 && l.k % 256 == 0 && l.k >= 256 &&
+               (l.b_dtype == LAPID_B200_DTYPE_Q4_K || l.b_dtype == LAPID_B200_DTYPE_Q5_K || l.b_dtype == LAPID_B200_DTYPE_Q6_K);
         if (p.tc) p.scratch = align_up(lb::qgemm_tc_scratch_bytes(p.rows, (uint32_t)l.n, (uint32_t)l.k, dev.sm_count), 256);
     }
     return p;

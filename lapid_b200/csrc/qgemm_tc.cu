@@ -67,7 +67,7 @@ template <int FMT, int MT, int NT, bool PAIR = false> struct Cfg {
     static constexpr int A_BYTES = (PAIR ? MT / 2 : MT) * 128;
     static constexpr int W_BYTES = NT * B_BYTES;
     static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
-    static constexpr int ROW_BYTES = FMT == FMT_Q4K ? Q4K_BYTES : Q6K_BOX;  // packed bytes staged per row and super-block
+    static constexpr int ROW_BYTES = FMT == FMT_Q4K ? Q4K_BYTES : FMT == FMT_Q5K ? Q5K_BYTES : Q6K_BOX;  // packed bytes staged per row and super-block
     static constexpr int RAW_BYTES = TN * ROW_BYTES;                         // one 128-row sub-tile: 18432 / 28672
     static constexpr int RAW = NT * RAW_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * RAW + 256 /*barriers*/ + 1024 /*alignment slack*/;
@@ -315,7 +315,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                 for (int t = 0; t < NT; t++)
                     tma_load_2d(raw0 + r * C::RAW + t * RAW_BYTES, &map_w,
-                                FMT == FMT_Q4K ? (int)((kb0 + b) * Q4K_BYTES) : (int)(((kb0 + b) * Q6K_BYTES) & ~15u), (int)(wrow0 + n0 + t * TN),
+                                FMT == FMT_Q6K ? (int)(((kb0 + b) * Q6K_BYTES) & ~15u) : (int)((kb0 + b) * C::ROW_BYTES), (int)(wrow0 + n0 + t * TN),
                                 raw_full + r);
             }
             if (!healthy && p.status) atomicOr(p.status, 32);
@@ -438,7 +438,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 if (lane == 0) mbar_arrive(full_b + s);
                 continue;
             }
-            const uint8_t *blk = raw0 + r * C::RAW + sub * RAW_BYTES + row * Q4K_BYTES;
+            const uint8_t *blk = raw0 + r * C::RAW + sub * RAW_BYTES + row * C::ROW_BYTES;
             if (NT == 2 ? pp == 0 : pp < 2) {  // first k-step of this thread in the block
                 if (!mbar_wait(raw_full + r, ur & 1)) { healthy = false; break; }
                 const uint4 h = *(const uint4 *)blk;
@@ -456,7 +456,15 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     m1[q] = fmaf(dmin, biased(q < 2 ? mn_lo : mn_hi, sel), ndmin);  // dmin * m, exact
                 }
             }
-            const uint4 qa = *(const uint4 *)(blk + 16 + 32 * pp), qb = *(const uint4 *)(blk + 32 + 32 * pp);
+            // Q5_K: Q4_K's block with the fifth bits qh[32] between the header and the nibbles; bit s of qh[l]
+            // belongs to element 32 s + l (crates/lapid-quant/src/kquant.rs:355-373)
+            constexpr int QS = FMT == FMT_Q5K ? 48 : 16;
+            const uint4 qa = *(const uint4 *)(blk + QS + 32 * pp), qb = *(const uint4 *)(blk + QS + 16 + 32 * pp);
+            uint4 ha = make_uint4(0, 0, 0, 0), hb = ha;
+            if constexpr (FMT == FMT_Q5K) {
+                ha = *(const uint4 *)(blk + 16);
+                hb = *(const uint4 *)(blk + 32);
+            }
             if (NT == 2 ? pp == 3 : pp >= 2) {  // this thread's last read of the block's packed bytes
                 __syncwarp();
                 if (lane == 0) mbar_arrive(raw_empty + r);
@@ -469,6 +477,11 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                 for (int i = 0; i < 8; i++) v[i] >>= 4;
             }
+            if constexpr (FMT == FMT_Q5K) {
+                const uint32_t hq[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = (v[i] & 0x0F0F0F0Fu) | (((hq[i] >> (2 * pp + half)) & 0x01010101u) << 4);
+            }
             if (!mbar_wait(empty + s, (u & 1) ^ 1)) { healthy = false; break; }
             uint8_t *dst = stage0 + s * C::STAGE_BYTES + sub * B_BYTES + row * 128;
 #pragma unroll
@@ -476,7 +489,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 uint32_t o[4];
 #pragma unroll
                 for (int w = 0; w < 2; w++) {
-                    const uint32_t t = v[2 * c + w] & 0x0F0F0F0Fu;
+                    const uint32_t t = v[2 * c + w] & (FMT == FMT_Q5K ? 0x1F1F1F1Fu : 0x0F0F0F0Fu);
                     // y = sd * q - m1 with one rounding, two elements per instruction
                     const uint64_t q01 = add2(pack2(biased(t, 0x7440u), biased(t, 0x7441u)), unbias);
                     const uint64_t q23 = add2(pack2(biased(t, 0x7442u), biased(t, 0x7443u)), unbias);
@@ -667,7 +680,18 @@ void qgemm_tc_set_tall(int v) { g_tc_tall = v; }
 
 bool qgemm_tc_supported(int fmt, const GemmTcArgs &a) {
     if (a.k % QK != 0 || a.k < QK || a.rows < 1 || ((uintptr_t)a.w & 15) != 0 || tc::encode_fn() == nullptr) return false;
-    return fmt == FMT_Q4K || fmt == FMT_Q6K;
+    return fmt == FMT_Q4K || fmt == FMT_Q5K || fmt == FMT_Q6K;
+}
+
+static uint32_t tc_block_bytes(int fmt) { return fmt == FMT_Q4K ? Q4K_BYTES : fmt == FMT_Q5K ? Q5K_BYTES : Q6K_BYTES; }
+static uint32_t tc_box_bytes(int fmt) { return fmt == FMT_Q6K ? (uint32_t)tc::Q6K_BOX : tc_block_bytes(fmt); }
+// the one-accumulator tile of a format by activation rows per CTA
+template <int FMT> static cudaError_t launch_one_acc(uint32_t mt, const GemmTcArgs &a, const CUtensorMap &mw, const CUtensorMap &ma,
+                                                     cudaStream_t stream, uint32_t ways = 1) {
+    using namespace tc;
+    return mt == 64 ? launch_mt<FMT, 64, 1>(a, mw, ma, stream, ways)
+                    : mt == 128 ? launch_mt<FMT, 128, 1>(a, mw, ma, stream, ways)
+                                : mt == 256 ? launch_mt<FMT, 256, 1>(a, mw, ma, stream, ways) : cudaErrorInvalidValue;
 }
 
 // How many ways K is split: only when the tiles would leave more than half of the SMs idle, never
@@ -698,9 +722,9 @@ size_t qgemm_tc_scratch_bytes(uint32_t rows, uint32_t n, uint32_t k, int sm_coun
 }
 
 bool qgemm_tc_moe_supported(int fmt, uint64_t experts, uint64_t n, uint64_t k, const void *w) {
-    if (fmt != FMT_Q4K && fmt != FMT_Q6K) return false;
+    if (fmt != FMT_Q4K && fmt != FMT_Q5K && fmt != FMT_Q6K) return false;
     if (k % QK != 0 || k < QK || ((uintptr_t)w & 15) != 0 || tc::encode_fn() == nullptr) return false;
-    const uint64_t pitch = k / QK * (fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES);
+    const uint64_t pitch = k / QK * tc_block_bytes(fmt);
     // one tensor map over all experts' rows: rows of 16-byte multiples, no padding between the matrices
     return pitch % 16 == 0 && (n * pitch) % 256 == 0 && experts * n < (1ull << 31);
 }
@@ -712,10 +736,10 @@ cudaError_t launch_qgemm_tc_moe(int fmt, const GemmTcArgs &a, uint32_t experts, 
     if (!enc || !a.tile_expert || !a.row_pair || a.rows % mt != 0) return cudaErrorInvalidValue;
     CUtensorMap mw, ma;
     {
-        const uint32_t blk_bytes = fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES;
+        const uint32_t blk_bytes = tc_block_bytes(fmt);
         cuuint64_t dims[2] = {(cuuint64_t)(a.k / QK) * blk_bytes, (cuuint64_t)experts * a.n};
         cuuint64_t strides[1] = {(cuuint64_t)(a.k / QK) * blk_bytes};
-        cuuint32_t box[2] = {fmt == FMT_Q4K ? (cuuint32_t)Q4K_BYTES : (cuuint32_t)Q6K_BOX, TN};
+        cuuint32_t box[2] = {(cuuint32_t)tc_box_bytes(fmt), TN};
         cuuint32_t es[2] = {1, 1};
         if (enc(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)a.w, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -730,11 +754,9 @@ cudaError_t launch_qgemm_tc_moe(int fmt, const GemmTcArgs &a, uint32_t experts, 
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    if (fmt == FMT_Q6K)
-        return mt == 64 ? launch_mt<FMT_Q6K, 64, 1>(a, mw, ma, stream)
-                        : mt == 128 ? launch_mt<FMT_Q6K, 128, 1>(a, mw, ma, stream) : mt == 256 ? launch_mt<FMT_Q6K, 256, 1>(a, mw, ma, stream) : cudaErrorInvalidValue;
-    return mt == 64 ? launch_mt<FMT_Q4K, 64, 1>(a, mw, ma, stream)
-                    : mt == 128 ? launch_mt<FMT_Q4K, 128, 1>(a, mw, ma, stream) : mt == 256 ? launch_mt<FMT_Q4K, 256, 1>(a, mw, ma, stream) : cudaErrorInvalidValue;
+    if (fmt == FMT_Q6K) return launch_one_acc<FMT_Q6K>(mt, a, mw, ma, stream);
+    if (fmt == FMT_Q5K) return launch_one_acc<FMT_Q5K>(mt, a, mw, ma, stream);
+    return launch_one_acc<FMT_Q4K>(mt, a, mw, ma, stream);
 }
 
 cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, int sm_count, cudaStream_t stream, int *launched) {
@@ -759,10 +781,10 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
     const bool pair = g_tc_pair > 0 && fmt == FMT_Q4K && a.rows > 128 && a.n >= 4 * TN;
     CUtensorMap mw, ma;
     {   // packed weights as bytes: [n rows][row_bytes], box = one 144-byte block (Q6_K: 224 bytes around one) of 128 rows
-        const uint32_t blk_bytes = fmt == FMT_Q4K ? Q4K_BYTES : Q6K_BYTES;
+        const uint32_t blk_bytes = tc_block_bytes(fmt);
         cuuint64_t dims[2] = {(cuuint64_t)(a.k / QK) * blk_bytes, a.n};
         cuuint64_t strides[1] = {(cuuint64_t)(a.k / QK) * blk_bytes};
-        cuuint32_t box[2] = {fmt == FMT_Q4K ? (cuuint32_t)Q4K_BYTES : (cuuint32_t)Q6K_BOX, TN};
+        cuuint32_t box[2] = {(cuuint32_t)tc_box_bytes(fmt), TN};
         cuuint32_t es[2] = {1, 1};
         if (strides[0] % 16 != 0) {
             // Q6_K with K not a multiple of 2048: no tensor map for the weights (the kernel copies rows itself)
@@ -788,12 +810,8 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
         GemmTcArgs b = a;
         b.partial = (float *)((char *)a_bf16_scratch + (((size_t)a.rows * a.k * 2 + 255) & ~(size_t)255));
         cudaError_t e;
-        if (fmt == FMT_Q6K)
-            e = mt == 64 ? launch_mt<FMT_Q6K, 64, 1>(b, mw, ma, stream, ways)
-                         : mt == 128 ? launch_mt<FMT_Q6K, 128, 1>(b, mw, ma, stream, ways) : launch_mt<FMT_Q6K, 256, 1>(b, mw, ma, stream, ways);
-        else
-            e = mt == 64 ? launch_mt<FMT_Q4K, 64, 1>(b, mw, ma, stream, ways)
-                         : mt == 128 ? launch_mt<FMT_Q4K, 128, 1>(b, mw, ma, stream, ways) : launch_mt<FMT_Q4K, 256, 1>(b, mw, ma, stream, ways);
+        e = fmt == FMT_Q6K ? launch_one_acc<FMT_Q6K>(mt, b, mw, ma, stream, ways)
+                           : fmt == FMT_Q5K ? launch_one_acc<FMT_Q5K>(mt, b, mw, ma, stream, ways) : launch_one_acc<FMT_Q4K>(mt, b, mw, ma, stream, ways);
         if (e != cudaSuccess) return e;
         const uint64_t total = (uint64_t)a.rows * a.n;
         const unsigned sgrid = (unsigned)((total + 255) / 256 > (uint64_t)sm_count * 8 ? (uint64_t)sm_count * 8 : (total + 255) / 256);
@@ -809,6 +827,7 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
     // CTA measured 1.6x the time of a 256-row one, so it pays when it saves more than that in waves
     // of tiles over the SMs. Q6_K only: for Q4_K the two-accumulator 256x256 tile is the better way
     // to the same reuse (it also halves the activation traffic), measured faster in every case.
+    if (fmt == FMT_Q5K) return launch_one_acc<FMT_Q5K>(mt, a, mw, ma, stream);  // (one accumulator tile: no wide or tall variants built)
     bool tall = false;
     if (a.rows > 256 && fmt == FMT_Q6K) {
         const uint64_t nt = (a.n + TN - 1) / TN;

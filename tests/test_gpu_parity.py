@@ -409,7 +409,7 @@ def bf16_round(x):
 
 
 @pytest.mark.parametrize("tall", ["-1", "1"])
-@pytest.mark.parametrize("fmt,ofmt", [(lp.DType.Q4K, O.Q4_K), (lp.DType.Q6K, O.Q6_K)])
+@pytest.mark.parametrize("fmt,ofmt", [(lp.DType.Q4K, O.Q4_K), (lp.DType.Q5K, O.Q5_K), (lp.DType.Q6K, O.Q6_K)])
 def test_gemm_tensor_core(be, oracle, fmt, ofmt, tall):
     be.set_option("gemm_tall", tall)   # "1": 512 activation rows per CTA wherever a launch has more than 256 rows
     try:
@@ -512,7 +512,7 @@ def test_gemm_tensor_core_split_k(be, oracle):
     summed in a fixed order by a second kernel. Same bounds; forced split counts including ones that
     do not divide the number of super-blocks; strided output and bias go through the sum kernel."""
     seed = 500
-    for fmt, ofmt in ((lp.DType.Q4K, O.Q4_K), (lp.DType.Q6K, O.Q6_K)):
+    for fmt, ofmt in ((lp.DType.Q4K, O.Q4_K), (lp.DType.Q5K, O.Q5_K), (lp.DType.Q6K, O.Q6_K)):
         for (m, n, k, ways, epi) in [(64, 256, 4096, -1, False), (300, 130, 14336, -1, True), (40, 100, 1792, 3, False),
                                      (512, 1024, 4096, 5, True), (20, 45, 1024, 16, False)]:
             seed += 1
@@ -777,7 +777,7 @@ def test_matmul_id_prefill_exact(be, oracle, fmt, name, t, r, e, n, k):
         be.set_option("gemm", "tc")
 
 
-@pytest.mark.parametrize("fmt,name", [(lp.DType.Q4K, "q4_k"), (lp.DType.Q6K, "q6_k")])
+@pytest.mark.parametrize("fmt,name", [(lp.DType.Q4K, "q4_k"), (lp.DType.Q5K, "q5_k"), (lp.DType.Q6K, "q6_k")])
 @pytest.mark.parametrize("t,r,e,n,k", [(64, 2, 4, 256, 2048), (200, 4, 8, 384, 4096), (1024, 2, 4, 128, 2048)])
 def test_matmul_id_prefill_tensor_core(be, oracle, fmt, name, t, r, e, n, k):
     """The same launch on the tensor cores (bf16 operands): the bounds of the dense prefill kernel
