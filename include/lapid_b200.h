@@ -97,8 +97,8 @@ LAPID_B200_API lapid_b200_status lapid_b200_device_synchronize(lapid_b200_device
  * (crates/lapid-cpu/src/matmul/mod.rs:52-57, crates/lapid-cuda/src/lib.rs:13-23):
  *   "gemv_max_rows" = "0".."8" (default 8, the reference's SMALL_M, crates/lapid-cpu/src/matmul/mod.rs:45):
  *                     launches with batch*m above it take the GEMM path;
- *   "gemm"          = "tc" (default): launches above gemv_max_rows with Q4_K weights run on the tensor
- *                     cores with bf16 operands (other formats always use the exact kernel);
+ *   "gemm"          = "tc" (default): launches above gemv_max_rows with Q4_K, Q5_K or Q6_K weights (k a multiple
+ *                     of 256) run on the tensor cores with bf16 operands (INT8 and INT4 use the exact kernel);
  *                     "f32": every such launch uses the exact-f32 kernel (lapid-cpu's qdeq numerics,
  *                     bit-identical to it);
  *   "gemv"          = "fast" (default) | "generic": specialised decode kernels where the shape allows;
