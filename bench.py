@@ -129,52 +129,64 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------
+def cpu_threads() -> int:
+    """The host cores this process may use (a launcher may have set OMP_NUM_THREADS=1 for its workers)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except Exception:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_sweep(o, fmt, budget_s: float, max_steps: int, warm: int):
+    """The oracle's timed copy of lapid-cpu's decode path over the 16-GEMV sweep on this host's cores. Every
+    launch of a step has its own weight copy (16 matrices, 311 MB per step, cycled like the GPU arm's), so the
+    last-level cache does not serve the weights. Returns (GB/s, ms per step, steps, cores)."""
+    o.set_num_threads(cpu_threads())
+    rng = np.random.default_rng(0)
+    cases = [(m, n, k) for m in MS for (n, k, _) in SHAPES]
+    base = {(n, k): o.quantize(fmt, rng.standard_normal(n * k, dtype=np.float32) * np.float32(0.02), n, k) for (n, k, _) in SHAPES}
+    ws = [base[(n, k)].copy() for (m, n, k) in cases]   # distinct memory per launch
+    xs = {(m, kk): rng.standard_normal(m * kk, dtype=np.float32) for m in MS for kk in (4096, 14336)}
+    step_bytes = sum(algo_bytes(fmt, m, n, k) for (m, n, k) in cases)
+
+    def step():
+        for w, (m, n, k) in zip(ws, cases):
+            o.matmul(fmt, xs[(m, k)], w, n, k, m=m)
+
+    for _ in range(max(1, warm)):
+        step()
+    t0 = time.perf_counter()
+    done = 0
+    while done < max_steps:
+        step()
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = (time.perf_counter() - t0) / done
+    return step_bytes / dt / 1e9, dt * 1e3, done, o.num_threads()
+
+
 def run_reference(args, rank: int, world: int):
-    """CPU arm: the oracle's restatement of lapid-cpu's decode path on the same 16 GEMVs."""
+    """CPU arm: the oracle's restatement of lapid-cpu's decode path on the same 16 GEMVs, all host cores."""
     if rank != 0:
         return
     from oracle import oracle as O
     o = O.load(fast=True)
-    cores = o.num_threads()
     fmt = 6
-    rng = np.random.default_rng(0)
-    ws, xs = {}, {}
-    for (n, k, _) in SHAPES:
-        w = (rng.standard_normal(n * k, dtype=np.float32) * np.float32(0.02))
-        ws[(n, k)] = o.quantize(fmt, w, n, k)
-    for m in MS:
-        for kk in (4096, 14336):
-            xs[(m, kk)] = rng.standard_normal(m * kk, dtype=np.float32)
-    cases = [(m, n, k) for m in MS for (n, k, _) in SHAPES]  # layer order: the projections of one batch size follow each other
-    step_bytes = sum(algo_bytes(fmt, m, n, k) for (m, n, k) in cases)
-
-    def step():
-        for (m, n, k) in cases:
-            o.matmul(fmt, xs[(m, k)], ws[(n, k)], n, k, m=m)
-
-    for _ in range(max(1, min(args.warmup, 3))):
-        step()
-    steps = max(1, args.steps)
-    t0 = time.perf_counter()
-    done = 0
-    for _ in range(steps):
-        step()
-        done += 1
-        if time.perf_counter() - t0 > 120.0:  # keep the arm within minutes on slow hosts
-            break
-    dt = (time.perf_counter() - t0) / done
-    val = step_bytes / dt / 1e9
+    val, ms, done, cores = cpu_sweep(o, fmt, budget_s=120.0, max_steps=max(1, args.steps), warm=min(max(args.warmup, 1), 3))
+    cases = [(m, n, k) for m in MS for (n, k, _) in SHAPES]
     line = {
         "impl": "reference", "metric": "q4k_decode_gemv_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": done, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "steps": done, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 x q4_k -> f32", "data": "synthetic",
         "config": {"workload": "decode_gemv_sweep", "format": "q4_k", "shapes": [[n, k] for (n, k, _) in SHAPES],
                    "batch_m": MS, "launches_per_step": len(cases)},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": f"{done} full steps of the 16-GEMV sweep (weights stay in host memory/LLC)"},
+                         "sample": f"{done} full steps of the 16-GEMV sweep, one weight copy per launch (311 MB per step, no reuse inside a step)"},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "C restatement of lapid-cpu's int8-activation decode path (the Rust reference cannot be built here); "
-                "gcc -O3 -march=native, OpenMP over output columns",
+                "gcc -O3 -march=native, OpenMP over output columns on every core this process may use"
+                + (f"; ONE CPU copy of the sweep: a run on {args.gpus} GPUs streams {args.gpus} copies at once" if args.gpus > 1 else ""),
     }
     print(json.dumps(line), flush=True)
 
@@ -189,7 +201,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     be = lp.Backend(local_rank)
-    for kv in filter(None, os.environ.get("LAPID_B200_OPTS", "").split(",")):  # e.g. "pdl=0,gemv=generic"
+    for kv in list(filter(None, os.environ.get("LAPID_B200_OPTS", "").split(","))) + list(args.opt):  # e.g. "pdl=0,gemv=generic"
         key, _, val = kv.partition("=")
         be.set_option(key, val)
     stream = torch.cuda.Stream(device=dev)
@@ -305,14 +317,26 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     e2e_val = world * step_bytes / e2e_s / 1e9
-    # the e2e outputs must be the resident path's outputs for the same activations
     be.set_stream(stream.cuda_stream)
+
+    # ---- outside the timed regions: every launch of the sweep against the CPU oracle (resident path: the
+    #      outputs of the last graph replay; end-to-end path: what the last download brought back)
+    check = None
+    if rank == 0 and not args.no_check:
+        try:
+            stream.synchronize()
+            check = {"sweep": check_sweep(fmt, cases, base, acts.cpu().numpy(), outs.cpu().numpy(), a_off, o_off),
+                     "e2e": check_sweep(fmt, cases, base, h_acts.numpy(), h_out.numpy(), a_off, o_off),
+                     "bar": "max_rel = max|got - ref| / max(|ref|, rms(ref)) against the CPU oracle's int8-activation path; "
+                            "decode bar 1e-3 (tests assert 2e-5); prefill (bf16 operands) rel_l2 <= 4e-3"}
+        except Exception as e:
+            check = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     # ---- 70B-shaped layer stack, tensor-parallel over the ranks (all ranks take part)
     tp_obj = None
     if not args.no_tp:
         try:
-            tp_obj = measure_tp70b(be, stream, dev, rank, world, quantized)
+            tp_obj = measure_tp70b(be, stream, dev, rank, world, quantized, check=not args.no_check)
         except Exception as e:  # reported, never fatal for the headline line
             tp_obj = {"error": f"{type(e).__name__}: {e}"[:300]}
 
@@ -321,11 +345,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     prefill_rows = None
     if world == 1 and not args.no_prefill:
-        prefill_rows = measure_prefill(be, stream, dev, base, quantized)
+        prefill_rows = measure_prefill(be, stream, dev, base, quantized, check=not args.no_check)
     stack_obj = None
     if world == 1 and not args.no_stack:
         try:
-            stack_obj = measure_stack8b(be, stream, dev, quantized, peak)
+            stack_obj = measure_stack8b(be, stream, dev, quantized, peak, check=not args.no_check)
         except Exception as e:  # reported, never fatal for the headline line
             stack_obj = {"error": f"{type(e).__name__}: {e}"[:300]}
         torch.cuda.empty_cache()
@@ -398,7 +422,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         roof_kernel = max(by_kernel, key=lambda kname: by_kernel[kname]["us"])
         e = by_kernel[roof_kernel]
         roof = e["bytes"] / (e["us"] * 1e-6) / 1e9
-        roof_traffic = DRAM_TRAFFIC_RATIO[roof_kernel] * e["bytes"] / e["launches"]
+        ratio = DRAM_TRAFFIC_RATIO.get(roof_kernel)
+        roof_traffic = ratio * e["bytes"] / e["launches"] if ratio is not None else None
         roof_detail = [{"kernel": kname, "launches": v["launches"], "us": round(v["us"], 2),
                         "achieved": round(v["bytes"] / (v["us"] * 1e-6) / 1e9, 1),
                         "frac": round(v["bytes"] / (v["us"] * 1e-6) / 1e9 / peak, 4)} for kname, v in by_kernel.items()]
@@ -413,7 +438,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     line = {
         "metric": "q4k_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8 x q4_k -> f32", "data": "synthetic",
+        "vs_baseline": (value / published_baseline()) if published_baseline() else None, "dtype": "int8 x q4_k -> f32", "data": "synthetic",
         "config": {"workload": "decode_gemv_sweep", "format": "q4_k", "shapes": [[n, k] for (n, k, _) in SHAPES],
                    "batch_m": MS, "launches_per_step": len(cases), "weight_bytes_per_step": sum(w.numel() for w in wcopies),
                    "l2": "every launch has its own weight copy; 311 MB per step > 126 MB L2", "cuda_graph": True,
@@ -425,9 +450,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": roof_traffic, "peak_kind": peak_kind, "kernel": roof_kernel, "by_kernel": roof_detail,
                      "what": "Q4_K decode launches of the kernel with the larger time share (act-quant pre-pass included): "
-                             "algorithmic bytes / mean launch time over its cases; traffic = mean DRAM bytes per launch, "
-                             "from the ncu capture of one launch scaled by algorithmic bytes"},
+                             "algorithmic bytes / mean launch time over its cases; traffic is MODELLED, not measured in this run: "
+                             "mean algorithmic bytes per launch x the DRAM-bytes / algorithmic-bytes ratio of the ncu capture "
+                             "summarised under profiles/ (null when that kernel has no capture)"},
     }
+    if world > 1 and isinstance(tp_obj, dict) and "decode_b1" in tp_obj:
+        line["config"]["tp70b"] = {"decode_tok_s": tp_obj["decode_b1"]["tok_s"],
+                                   "decode_frac_of_hbm_ceiling": tp_obj["decode_b1"].get("frac_of_hbm_ceiling"),
+                                   "prefill_m512_tok_s": tp_obj.get("prefill_m512", {}).get("tok_s"),
+                                   "prefill_collective_share": tp_obj.get("prefill_m512", {}).get("collective_share"),
+                                   "note": "the headline value is a communication-free replica run; the tensor-parallel stack "
+                                           "with real exchanges is this object (details under tp70b)"}
     if case_rows:
         line["cases"] = case_rows
     if prefill_rows:
@@ -438,27 +471,81 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         line["matmul_id"] = moe_rows
     if tp_obj:
         line["tp70b"] = tp_obj
+    if check is not None:
+        if prefill_rows:
+            check["prefill"] = [r["check"] for r in prefill_rows if "check" in r]
+        if isinstance(stack_obj, dict) and "check" in stack_obj:
+            check["stack8b"] = stack_obj["check"]
+        if isinstance(tp_obj, dict) and "check" in tp_obj:
+            check["tp70b"] = tp_obj["check"]
+        decode = [check[kk]["max_rel"] for kk in ("sweep", "e2e", "stack8b") if isinstance(check.get(kk), dict) and "max_rel" in check[kk]]
+        check["decode_worst_max_rel"] = max(decode) if decode else None
+        check["prefill_worst_rel_l2"] = max([c["rel_l2"] for c in check.get("prefill", [])], default=None)
+        line["check"] = check
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(cases, fmt)
     print(json.dumps(line), flush=True)
 
 
 def gemv_kernel_name(fmt: int, m: int) -> str:
-    """The kernel a decode launch of `m` rows takes with the library's default options."""
+    """The kernel a decode launch of `m` rows takes with the library's default options when, as in the per-case
+    timing, its activations were quantized at the head of the launch list."""
     if fmt == 6:
-        return "qgemv_q4k_mma_kernel" if m >= 3 else "qgemv_kq_fast_kernel<q4_k>"  # (two rows: the tensor-core kernel when the operand is produced inside the list)
+        return "qgemv_kq_stream_kernel<q4_k>" if m >= 3 else "qgemv_kq_fast_kernel<q4_k>"  # (two rows: the stream kernel when the operand is produced inside the list)
     if fmt == 8:
         return "qgemv_q6k_mma_kernel" if m >= 3 else "qgemv_kq_fast_kernel<q6_k>"
     if fmt == 7:
-        return "qgemv_kq_fast_kernel<q5_k>"
+        return "qgemv_kq_stream_kernel<q5_k>" if m >= 3 else "qgemv_kq_fast_kernel<q5_k>"
     if fmt == 5:
         return "qgemv_i4_kernel"
     return "qgemv_i8_mma_kernel" if m >= 2 else "qgemv_i8_fast_kernel"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch / algorithmic bytes of that launch, from
-# the ncu captures summarised under profiles/ (weights are read once; the outputs stay in L2).
-DRAM_TRAFFIC_RATIO = {"qgemv_q4k_mma_kernel": 0.985, "qgemv_kq_fast_kernel<q4_k>": 0.9985}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch / algorithmic bytes of that launch, from the ncu
+# captures summarised under profiles/ (weights are read once; the outputs stay in L2). A kernel without a
+# capture reports no traffic.
+DRAM_TRAFFIC_RATIO = {"qgemv_kq_fast_kernel<q4_k>": 0.9985}
+
+
+def max_rel(got, ref) -> float:
+    """max |got - ref| / max(|ref|, rms(ref)): the parity tests' per-element measure."""
+    got = np.asarray(got, np.float64).reshape(-1)
+    ref = np.asarray(ref, np.float64).reshape(-1)
+    rms = float(np.sqrt((ref ** 2).mean()))
+    return float((np.abs(got - ref) / np.maximum(np.abs(ref), max(rms, 1e-30))).max())
+
+
+def rel_l2(got, ref) -> float:
+    got = np.asarray(got, np.float64).reshape(-1)
+    ref = np.asarray(ref, np.float64).reshape(-1)
+    return float(np.sqrt(((got - ref) ** 2).sum() / max((ref ** 2).sum(), 1e-30)))
+
+
+def published_baseline():
+    """BASELINE.json's published number for this metric, if it holds one (it holds none for B200)."""
+    try:
+        with open(os.path.join(ROOT, "BASELINE.json")) as f:
+            pub = json.load(f).get("published") or {}
+        v = pub.get("q4k_decode_gemv_hbm_gbs")
+        return float(v) if v else None
+    except Exception:
+        return None
+
+
+def check_sweep(fmt, cases, base, acts, outs, a_off, o_off):
+    """Every launch of the sweep against the oracle: the worst max_rel per kernel and overall."""
+    from oracle import oracle as O
+    o = O.load(fast=True)
+    o.set_num_threads(cpu_threads())
+    wh = {nk: t.cpu().numpy() for nk, t in base.items()}
+    by_kernel, worst = {}, 0.0
+    for i, (m, n, k) in enumerate(cases):
+        want, _ = o.matmul(fmt, acts[a_off[i]:a_off[i] + m * k], wh[(n, k)], n, k, m=m)
+        mr = max_rel(outs[o_off[i]:o_off[i] + m * n], want)
+        name = gemv_kernel_name(fmt, m) if m != 2 else "two rows (kernel chosen by the launch list)"
+        by_kernel[name] = max(by_kernel.get(name, 0.0), mr)
+        worst = max(worst, mr)
+    return {"launches_checked": len(cases), "max_rel": worst, "by_kernel": by_kernel}
 
 
 def _event_time(stream, fn, reps, warm=2):
@@ -479,10 +566,40 @@ def _event_time(stream, fn, reps, warm=2):
     return ts[len(ts) // 2]
 
 
-def measure_prefill(be, stream, dev, base, quantized):
+def _graph_times(be, stream, run, reps, warm=3):
+    """Captures `run` (which queues work through the library on the current stream) in a CUDA graph and
+    times `reps` replays with events: (median ms, min ms)."""
+    import torch
+    with torch.cuda.stream(stream):
+        run()   # first use of a kernel variant sets its attributes: keep that out of the capture
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        be.set_stream(torch.cuda.current_stream().cuda_stream)
+        run()
+    be.set_stream(stream.cuda_stream)
+    ts = []
+    with torch.cuda.stream(stream):
+        for _ in range(warm):
+            graph.replay()
+        stream.synchronize()
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+            ts.append(e0.elapsed_time(e1))
+    del graph
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def measure_prefill(be, stream, dev, base, quantized, check=True):
     """Prefill GEMM (tcgen05): Q4_K at M in {64, 512, 2048}, Q6_K and Q5_K at M in {512, 2048} on the gate/up
-    and down shapes; five weight copies are cycled (165 MB > L2). TFLOP/s = 2*M*N*K / time, against
-    the measured bf16 peaks."""
+    and down shapes; five weight copies are cycled (165 MB > L2) inside one CUDA graph, 12 replays: median and
+    best. TFLOP/s = 2*M*N*K / time, against the measured bf16 peaks. One Q4_K row per shape is checked
+    against the oracle's f32 path on a 128-row slice of the weights (outside the timed region)."""
     import torch
     from lapid_b200.backend import matmul_launch
     try:
@@ -503,11 +620,25 @@ def measure_prefill(be, stream, dev, base, quantized):
             bufs = [be.wrap_tensor(a), be.wrap_tensor(o)] + [be.wrap_tensor(pool[c]) for c in range(copies)]
             ls = [matmul_launch(fmt, m, n, k, inputs=(0, 2 + c), output=1) for c in range(copies)]
             be.prepare(ls)
-            ms = _event_time(stream, be.packed(ls, bufs), 5) / copies
+            med, best = _graph_times(be, stream, be.packed(ls, bufs), 12)
+            ms, ms_best = med / copies, best / copies
             tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
-            rows.append({"fmt": FMT_NAMES[fmt], "m": m, "n": n, "k": k, "us": round(ms * 1e3, 1), "tflops": round(tf, 1),
-                         "frac_burst": round(tf / burst, 4), "frac_sustained": round(tf / sustained, 4),
-                         "operands": "bf16 (f32 accumulate in TMEM)"})
+            row = {"fmt": FMT_NAMES[fmt], "m": m, "n": n, "k": k, "us": round(ms * 1e3, 1), "us_best": round(ms_best * 1e3, 1),
+                   "tflops": round(tf, 1), "tflops_best": round(2.0 * m * n * k / (ms_best * 1e-3) / 1e12, 1),
+                   "frac_burst": round(tf / burst, 4), "frac_sustained": round(tf / sustained, 4),
+                   "operands": "bf16 (f32 accumulate in TMEM)", "timing": "CUDA graph of 5 launches over 5 weight copies, 12 replays"}
+            if check and fmt == 6 and m == 512:
+                from oracle import oracle as O
+                orc = O.load(fast=True)
+                orc.set_num_threads(cpu_threads())
+                j0, rws = n // 2 + 64, 128
+                rb = k // 256 * 144
+                part = wq[j0 * rb:(j0 + rws) * rb].cpu().numpy()
+                want, _ = orc.matmul(6, a.cpu().numpy(), np.concatenate([part, np.zeros((-part.size) % 256, np.uint8)]), rws, k, m=m)
+                got = o.view(m, n)[:, j0:j0 + rws].cpu().numpy()
+                row["check"] = {"case": f"q4_k M={m} {n}x{k}, weight rows [{j0}, {j0 + rws})", "rel_l2": rel_l2(got, want),
+                                "max_rel": max_rel(got, want)}
+            rows.append(row)
         del pool
     return rows
 
@@ -576,7 +707,7 @@ def measure_moe(be, stream, dev, quantized, peak):
     return rows
 
 
-def measure_stack8b(be, stream, dev, quantized, peak):
+def measure_stack8b(be, stream, dev, quantized, peak, check=True):
     """Every quantized projection of one decode token through a 32-layer Llama-3-8B-shaped stack plus
     the output head, as ONE launch list through the C ABI (225 MatMul launches, batch 1 and 8).
 
@@ -639,17 +770,31 @@ def measure_stack8b(be, stream, dev, quantized, peak):
             run()
         be.set_stream(stream.cuda_stream)
         ms = _event_time(stream, graph.replay, 7, warm=3)
-        finite = bool(torch.isfinite(keep[-2]).all().item())
         out[f"decode_b{m}"] = {"ms_per_token_step": round(ms, 4), "tok_s": round(m / (ms * 1e-3), 1),
                                "hbm_gbs": round(token_bytes / (ms * 1e-3) / 1e9, 1),
                                "frac_of_measured_hbm": round(token_bytes / (ms * 1e-3) / 1e9 / peak, 4),
-                               "kernels_per_token": kernels, "logits_finite": finite}
+                               "kernels_per_token": kernels}
+        if check:
+            # outside the timed region: the last layer's down projection and the output head of the replayed token
+            # against the oracle, each on the input that launch actually read
+            from oracle import oracle as O
+            orc = O.load(fast=True)
+            orc.set_num_threads(cpu_threads())
+            stream.synchronize()
+            i = n_layers - 1
+            n_dn, k_dn = dims["down"]
+            gate_out, down_out, logits_t = keep[oid["gate"]], keep[oid["down"]], keep[logits]   # `keep` and `bufs` share indices
+            want_dn, _ = orc.matmul(formats[i]["down"], gate_out.cpu().numpy(), weights[i]["down"].cpu().numpy(), n_dn, k_dn, m=m)
+            want_hd, _ = orc.matmul(8, down_out.cpu().numpy(), head.cpu().numpy(), vocab, d, m=m)
+            mr = max(max_rel(down_out.cpu().numpy(), want_dn), max_rel(logits_t.cpu().numpy(), want_hd))
+            out.setdefault("check", {"what": "last layer's ffn_down and the 128256 x 4096 Q6_K head vs the oracle, batch 1 and 8", "max_rel": 0.0})
+            out["check"]["max_rel"] = max(out["check"]["max_rel"], mr)
         del graph, run, bufs, keep, launches
         torch.cuda.empty_cache()
     return out
 
 
-def measure_tp70b(be, stream, dev, rank, world, quantized):
+def measure_tp70b(be, stream, dev, rank, world, quantized, check=True):
     """Llama-70B-shaped layer stack (80 layers: d_model 8192, 64/8 heads of 128, FFN 28672), Q4_K_M-style
     mix (Q6_K for attn_v and for ffn_down in half of the layers), tensor-parallel over `world` ranks:
     column-parallel q/k/v/gate/up, row-parallel o/down with an NCCL all-reduce. Eight distinct layer
@@ -685,12 +830,16 @@ def measure_tp70b(be, stream, dev, rank, world, quantized):
     # all-reduce; _nccl: the library collective, for comparison
     # _prepass: the same stack with a quantizing pre-pass kernel in front of every projection group instead
     # of the rms_norm / silu_mul kernels writing the quantized operand themselves
-    variants = [(1, "decode_b1", peer, True, True), (1, "decode_b1_prepass", peer, True, False), (512, "prefill_m512", peer, False, True)]
+    variants = [(1, "decode_b1", peer, True, True, False), (1, "decode_b1_prepass", peer, True, False, False),
+                (512, "prefill_m512", peer, False, True, False)]
+    if world > 1:
+        variants.append((512, "prefill_m512_no_collective", peer, False, True, True))   # timing only: what the all-reduces cost
     if world > 1 and peer is not None:
-        variants.insert(2, (1, "decode_b1_allreduce_kernel", peer, False, True))
-        variants.insert(3, (1, "decode_b1_nccl", None, False, True))
-    for m, key, reducer, fused, fuse_act in variants:
-        layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats, peer_all_reduce=reducer, fused=fused, fuse_act=fuse_act)
+        variants.insert(2, (1, "decode_b1_allreduce_kernel", peer, False, True, False))
+        variants.insert(3, (1, "decode_b1_nccl", None, False, True, False))
+    for m, key, reducer, fused, fuse_act, skip in variants:
+        layers = tp.GpuTpLayers(be, shape, world, rank, m, weights, formats, peer_all_reduce=reducer, fused=fused, fuse_act=fuse_act,
+                                skip_collective=skip)
         layers.h.normal_()
         torch.cuda.synchronize()
         run = lambda: layers.token(n_layers)
@@ -698,18 +847,18 @@ def measure_tp70b(be, stream, dev, rank, world, quantized):
         with torch.cuda.stream(stream):
             run()
         stream.synchronize()
-        if m == 1:
-            try:
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=stream):
-                    be.set_stream(torch.cuda.current_stream().cuda_stream)
-                    run()
-                be.set_stream(stream.cuda_stream)
-                run = graph.replay
-            except Exception as e:
-                out["graph_error"] = str(e)[:200]
-                be.set_stream(stream.cuda_stream)
-                run = lambda: layers.token(n_layers)
+        try:   # one token = one CUDA graph (NCCL's all-reduce is captured with the rest)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                be.set_stream(torch.cuda.current_stream().cuda_stream)
+                run()
+            be.set_stream(stream.cuda_stream)
+            run = graph.replay
+        except Exception as e:
+            out["graph_error"] = str(e)[:200]
+            graph = None
+            be.set_stream(stream.cuda_stream)
+            run = lambda: layers.token(n_layers)
         if world > 1:
             dist.barrier()
         ms = _event_time(stream, run, 5 if m == 1 else 3, warm=2 if m == 1 else 1)
@@ -720,41 +869,143 @@ def measure_tp70b(be, stream, dev, rank, world, quantized):
         row = {"ms_per_token_step": round(ms, 4), "tok_s": round(m / (ms * 1e-3), 2), "cuda_graph": graph is not None}
         if m == 1:
             row["hbm_gbs_per_gpu"] = round(token_bytes / (ms * 1e-3) / 1e9, 1)
+            row["frac_of_hbm_ceiling"] = round(token_bytes / (ms * 1e-3) / 1e9 / measured_peaks()[0], 4)
         else:
             fl = 2.0 * m * sum(n * k for _, n, k, _ in shape.projections()) * n_layers
             row["tflops_total"] = round(fl / (ms * 1e-3) / 1e12, 1)
         out[key] = row
         del layers, graph
         torch.cuda.empty_cache()
+    if "prefill_m512_no_collective" in out:
+        a, b = out["prefill_m512"]["ms_per_token_step"], out["prefill_m512_no_collective"]["ms_per_token_step"]
+        out["prefill_m512"]["collective_share"] = round(max(0.0, a - b) / a, 4)
+    if check and world > 1:
+        try:
+            out["check"] = tp_check(be, stream, dev, rank, world, quantized, peer)
+        except Exception as e:
+            out["check"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     return out
 
 
+def tp_check(be, stream, dev, rank, world, quantized, peer):
+    """Tensor-parallel correctness at this world size, outside any timed region: one 70B-shaped layer whose shards
+    are cut from COMMON full matrices (every rank makes the same full matrices from the same seeds and keeps its
+    shard), run sharded on all ranks and unsharded on rank 0. `first_exchange`: h + sum over ranks of o, whose inputs
+    are the same on both sides, so only the order of f32 sums differs (bar 1e-5); `layer`: the whole layer step,
+    where those differences pass the int8 activation quantizer of the later projections (bar rel_l2 1e-2)."""
+    import torch
+    import torch.distributed as dist
+    from lapid_b200 import tp
+    shape = tp.LLAMA_70B
+    full, fmts, shard = {}, {}, {}
+    for i, (name, n, k, kind) in enumerate(shape.projections()):
+        fmts[name] = tp.Q6_K if name in ("v", "down") else tp.Q4_K
+        full[name] = quantized(fmts[name], n, k, 9000 + i)   # the same matrix on every rank
+        cut = tp.shard_rows if kind == "column" else tp.shard_cols
+        shard[name] = cut(fmts[name], full[name], n, k, rank, world)[0]
+    res = {"what": "sharded layer (all ranks) vs unsharded layer (rank 0), shards cut from common full matrices", "tp": world}
+    for m, key in ((1, "decode_b1"), (512, "prefill_m512")):
+        g = torch.Generator(device=dev)
+        g.manual_seed(77 + m)
+        h0 = torch.randn(m, shape.d_model, device=dev, generator=g)
+        got = {}
+        sharded = tp.GpuTpLayers(be, shape, world, rank, m, [shard], [fmts], peer_all_reduce=peer, fused=(m == 1), fuse_act=True)
+        for part in ("first_exchange", "layer"):
+            sharded.h.copy_(h0)
+            torch.cuda.synchronize()
+            dist.barrier()
+            with torch.cuda.stream(stream):
+                t = sharded.first_row_parallel() if part == "first_exchange" else sharded.token(1)
+            stream.synchronize()
+            got[part] = t.clone()
+        del sharded
+        dist.barrier()
+        if rank == 0:
+            single = tp.GpuTpLayers(be, shape, 1, 0, m, [full], [fmts], fuse_act=True)
+            row = {}
+            for part in ("first_exchange", "layer"):
+                single.h.copy_(h0)
+                torch.cuda.synchronize()
+                with torch.cuda.stream(stream):
+                    t = single.first_row_parallel() if part == "first_exchange" else single.token(1)
+                stream.synchronize()
+                row[part] = {"max_rel": max_rel(got[part].cpu().numpy(), t.cpu().numpy()),
+                             "rel_l2": rel_l2(got[part].cpu().numpy(), t.cpu().numpy())}
+            res[key] = row
+            del single
+        torch.cuda.empty_cache()
+        dist.barrier()
+    return res
+
+
+def run_case(args):
+    """One matmul case through the C ABI: `reps` executes of `copies` launches (each over its own weight copy, so a
+    decode launch streams from HBM), then the same list as a CUDA graph, timed with events. Prints one JSON row."""
+    import torch
+    import lapid_b200 as lp
+    from lapid_b200 import quant
+    from lapid_b200.backend import matmul_id_launch, matmul_launch
+    parts = args.case.split(",")
+    names = {v: kk for kk, v in FMT_NAMES.items()}
+    fmt, (m, n, k) = names[parts[0]], [int(x) for x in parts[1:4]]
+    copies = int(parts[4]) if len(parts) > 4 else 6
+    reps = int(parts[5]) if len(parts) > 5 else 2
+    be = lp.Backend(0)
+    for kv in list(filter(None, os.environ.get("LAPID_B200_OPTS", "").split(","))) + list(args.opt):
+        key, _, val = kv.partition("=")
+        be.set_option(key, val)
+    stream = torch.cuda.Stream()
+    be.set_stream(stream.cuda_stream)
+    e, r = args.experts, args.slots
+    one = quant.layout(fmt, n, k).total
+    stack = torch.empty((e or 1) * one, dtype=torch.uint8, device="cuda")
+    for x in range(e or 1):
+        w = torch.randn(n * k, device="cuda") * 0.02
+        torch.cuda.synchronize()
+        be.quantize_into(fmt, be.wrap_tensor(w), n, k, be.wrap_tensor(stack[x * one:(x + 1) * one]))
+    pool = stack.repeat(copies).view(copies, -1)
+    a = torch.randn(m * k, device="cuda")
+    if e:
+        g = torch.Generator()
+        g.manual_seed(1)
+        ids = torch.stack([torch.randperm(e, generator=g)[:r] for _ in range(m)]).to(torch.int32).reshape(-1).cuda()
+        o = torch.zeros(m * r * n, device="cuda")
+        torch.cuda.synchronize()
+        bufs = [be.wrap_tensor(a), be.wrap_tensor(o), be.wrap_tensor(ids)] + [be.wrap_tensor(pool[c]) for c in range(copies)]
+        launches = [matmul_id_launch(fmt, m, r, e, n, k, inputs=(0, 3 + c, 2), output=1) for c in range(copies)]
+    else:
+        o = torch.zeros(m * n, device="cuda")
+        torch.cuda.synchronize()
+        bufs = [be.wrap_tensor(a), be.wrap_tensor(o)] + [be.wrap_tensor(pool[c]) for c in range(copies)]
+        launches = [matmul_launch(fmt, m, n, k, inputs=(0, 2 + c), output=1) for c in range(copies)]
+    be.prepare(launches)
+    run = be.packed(launches, bufs)
+    be.take_launch_count()
+    with torch.cuda.stream(stream):
+        for _ in range(reps):
+            run()
+    stream.synchronize()
+    kernels = be.take_launch_count() // max(1, reps)
+    med, best = _graph_times(be, stream, run, 9)
+    us, us_best = med / copies * 1e3, best / copies * 1e3
+    row = {"case": args.case, "experts": e, "copies": copies, "reps": reps, "kernels_per_list": kernels, "us_per_launch": round(us, 3),
+           "us_per_launch_best": round(us_best, 3), "checksum": float(o.abs().sum())}
+    if not e and m <= 8:
+        peak, kind = measured_peaks()
+        gbs = algo_bytes(fmt, m, n, k) / (us * 1e-6) / 1e9
+        row.update({"gbs": round(gbs, 1), "frac_of_hbm": round(gbs / peak, 4), "peak_kind": kind})
+    elif not e:
+        row["tflops"] = round(2.0 * m * n * k / (us * 1e-6) / 1e12, 1)
+    print(json.dumps(row), flush=True)
+
+
 def cpu_baseline(cases, fmt):
-    """The oracle's timed copy on this host's cores over one full step of the same sweep."""
+    """The oracle's timed copy on this host's cores: a bounded sample (about 10 s) of full steps of the same sweep."""
     from oracle import oracle as O
     o = O.load(fast=True)
-    rng = np.random.default_rng(0)
-    ws = {}
-    for (n, k, _) in SHAPES:
-        ws[(n, k)] = o.quantize(fmt, rng.standard_normal(n * k, dtype=np.float32) * np.float32(0.02), n, k)
-    xs = {(m, kk): rng.standard_normal(m * kk, dtype=np.float32) for m in MS for kk in (4096, 14336)}
-    step_bytes = sum(algo_bytes(fmt, m, n, k) for (m, n, k) in cases)
-
-    def step():
-        for (m, n, k) in cases:
-            o.matmul(fmt, xs[(m, k)], ws[(n, k)], n, k, m=m)
-
-    step()
-    t0 = time.perf_counter()
-    done = 0
-    while done < 3 or (time.perf_counter() - t0 < 10.0 and done < 50):
-        step()
-        done += 1
-        if time.perf_counter() - t0 > 30.0:
-            break
-    dt = (time.perf_counter() - t0) / done
-    return {"value": step_bytes / dt / 1e9, "unit": "GB/s", "cores": o.num_threads(), "kind": "port",
-            "sample": f"{done} full steps of the 16-GEMV Q4_K sweep, {dt * 1e3:.1f} ms per step"}
+    val, ms, done, cores = cpu_sweep(o, fmt, budget_s=10.0, max_steps=50, warm=1)
+    return {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"{done} full steps of the 16-GEMV Q4_K sweep (one weight copy per launch), {ms:.1f} ms per step"}
 
 
 def main():
@@ -769,12 +1020,22 @@ def main():
     ap.add_argument("--no-tp", action="store_true", help="skip the 70B-shaped tensor-parallel layer stack")
     ap.add_argument("--no-moe", action="store_true", help="skip the MatMulId (mixture-of-experts) measurements")
     ap.add_argument("--no-stack", action="store_true", help="skip the 32-layer 8B-shaped projection stack")
+    ap.add_argument("--no-check", action="store_true", help="skip the result checks against the CPU oracle (they run outside the timed regions)")
+    ap.add_argument("--case", default=None, metavar="FMT,M,N,K[,COPIES[,REPS]]",
+                    help="run ONE matmul case instead of the benchmark (e.g. q4_k,8,14336,4096,6,2): REPS executes of COPIES launches, "
+                         "each over its own weight copy, then a timed CUDA-graph replay; small enough to sit under a profiler")
+    ap.add_argument("--experts", type=int, default=0, help="--case: MatMulId over a stack of this many matrices (0: a plain MatMul)")
+    ap.add_argument("--slots", type=int, default=2, help="--case with --experts: experts per token")
+    ap.add_argument("--opt", action="append", default=[], help="device option key=value (repeatable)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.case:
+        run_case(args)
         return
     if world > 1:
         import torch

@@ -283,6 +283,14 @@ LAPID_B200_API lapid_b200_status lapid_b200_silu_mul(lapid_b200_device *dev, lap
  *     qact NULL: exactly the plain form. */
 LAPID_B200_API lapid_b200_status lapid_b200_act_layout(lapid_b200_device *dev, const lapid_b200_launch *launch, int32_t *layout,
                                                        uint64_t *bytes);
+/* The pre-pass as a call of its own: `quantize_row_sums` (crates/lapid-cpu/src/matmul/quant.rs:30-89) for `rows`
+ * (1..8) contiguous f32 rows of `k` elements in `a`, written to `qact` in `layout` (0: planes -- int8 q[rows][k],
+ * then at the next multiple of 256 bytes f32 d[rows][k/32], then likewise f32 d*sum(q)[rows][k/32]; 1 and 2: the
+ * record and tile layouts of the specialised decode kernels, k a multiple of 256). Per 32-element group:
+ * amax = max|x|, d = amax/127, id = d > 0 ? 1/d : 0, q = clamp(round_half_even(x*id), -127, 127). Queued on the
+ * device's stream, not waited for. A launch with a_dtype ACT_Q8 whose lapid_b200_act_layout matches reads it. */
+LAPID_B200_API lapid_b200_status lapid_b200_quantize_activations(lapid_b200_device *dev, const lapid_b200_buffer *a, uint64_t rows,
+                                                                 uint64_t k, int32_t layout, lapid_b200_buffer *qact);
 LAPID_B200_API lapid_b200_status lapid_b200_rms_norm_act(lapid_b200_device *dev, lapid_b200_buffer *x, lapid_b200_buffer *residual,
                                                          lapid_b200_buffer *weight, lapid_b200_buffer *sum_out,
                                                          lapid_b200_buffer *out, uint64_t rows, uint64_t cols, float eps,
@@ -312,11 +320,19 @@ LAPID_B200_API lapid_b200_status lapid_b200_silu_mul_act(lapid_b200_device *dev,
  * request fails with "too_large"); every GPU that loads the library carries the array until exit;
  * all calls on a GPU share it and it keeps the previous call's contents (nothing in it needs
  * clearing), so calls that can overlap on the GPU race -- keep them on one stream or order them
- * with events; the first call on a GPU also looks up the array's address and configures the
- * kernels, so make it before any stream capture. */
+ * with events; the first call on a GPU also looks up the array's address, and the first call on a GPU
+ * with a given (rows, k) configures that kernel variant, so make those calls before any stream capture.
+ * The calling thread's current device is put back before the call returns. A device-side wait that gave
+ * up (the result is then wrong) is not reported by this call, which does not wait: read it with
+ * lapid_b200_gemv_q4k_static_status after synchronising. */
 #define LAPID_B200_STATIC_SCRATCH_BYTES 86016u
 LAPID_B200_API lapid_b200_status lapid_b200_gemv_q4k_static(int32_t ordinal, void *cuda_stream, const float *a, const void *w,
                                                             uint64_t w_bytes, float *out, uint32_t rows, uint32_t n, uint32_t k);
+/* Companion of the call above (no counterpart in the reference either): writes to *out, and clears, the word in
+ * which the static path's kernels on GPU `ordinal` record a bounded wait that gave up (0 = none since the last
+ * read; nonzero = the outputs of the calls since then are invalid). Synchronise the stream(s) those calls were
+ * queued on first. Allocates nothing. */
+LAPID_B200_API lapid_b200_status lapid_b200_gemv_q4k_static_status(int32_t ordinal, int32_t *out);
 
 #ifdef __cplusplus
 }

@@ -84,10 +84,12 @@ SYMBOLS = {
     "lapid_b200_rms_norm": (C.c_int32, [P, P, P, P, P, P, C.c_uint64, C.c_uint64, C.c_float]),
     "lapid_b200_silu_mul": (C.c_int32, [P, P, P, P, C.c_uint64]),
     "lapid_b200_act_layout": (C.c_int32, [P, P, C.POINTER(C.c_int32), C.POINTER(C.c_uint64)]),
+    "lapid_b200_quantize_activations": (C.c_int32, [P, P, C.c_uint64, C.c_uint64, C.c_int32, P]),
     "lapid_b200_rms_norm_act": (C.c_int32, [P, P, P, P, P, P, C.c_uint64, C.c_uint64, C.c_float, P, C.c_int32]),
     "lapid_b200_tp_rms_norm_act": (C.c_int32, [P, P, P, P, P, C.c_uint64, C.c_uint64, C.c_float, P, C.c_int32]),
     "lapid_b200_silu_mul_act": (C.c_int32, [P, P, P, P, C.c_uint64, C.c_uint64, P, C.c_int32]),
     "lapid_b200_gemv_q4k_static": (C.c_int32, [C.c_int32, P, P, P, C.c_uint64, P, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "lapid_b200_gemv_q4k_static_status": (C.c_int32, [C.c_int32, C.POINTER(C.c_int32)]),
 }
 
 _lib = None

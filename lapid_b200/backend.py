@@ -298,6 +298,11 @@ class Backend:
         check(_lib.lib().lapid_b200_silu_mul_act(self._h, gate._h, up._h, out._h, rows, count // rows,
                                                  qact._h if qact is not None else None, layout))
 
+    def quantize_activations(self, a: Buffer, rows: int, k: int, layout: int, qact: Buffer) -> None:
+        """``quantize_row_sums`` (crates/lapid-cpu/src/matmul/quant.rs:30-89) of ``rows`` f32 rows into ``qact`` in
+        ``layout`` (0 planes, 1 records, 2 tiles): the decode path's activation pre-pass as a call of its own."""
+        check(_lib.lib().lapid_b200_quantize_activations(self._h, a._h, rows, k, layout, qact._h))
+
     def act_layout(self, launch: "Launch") -> tuple:
         """``(layout, bytes)`` of the quantized activation operand a decode launch reads (``lapid_b200_act_layout``)."""
         lay, nbytes = C.c_int32(0), C.c_uint64(0)

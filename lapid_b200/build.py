@@ -24,6 +24,7 @@ SOURCES = {
     "qgemv.cu": [],
     "qgemv_q4k.cu": [],
     "qgemv_q4k_mma.cu": [],
+    "qgemv_kq_stream.cu": [],
     "qgemv_q6k_mma.cu": [],
     "qgemv_i8.cu": [],
     "qgemv_i4.cu": [],

@@ -170,12 +170,16 @@ struct lapid_b200_device {
     bool gemv_fast = true;   // specialised GEMV kernels where the shape allows; off = generic kernel only
     bool gemv_group = true;  // consecutive independent K-quant decode launches of one list share a kernel
     uint32_t gemv_mma_rows = 2;  // Q4_K decode launches with at least this many rows use the int8 tensor-core kernel; 0 = never
+    bool gemv_stream = true;     // Q4_K / Q5_K tensor-core decode launches take the balanced-stream kernel (qgemv_kq_stream.cu)
+    bool two_row_dp4a = true;    // two early Q4_K rows prefer the dp4a kernel (see execute_impl)
+    lb::StreamWs stream_ws{};    // workspace of that kernel: partial tiles and their counters (zero between launches)
     bool gemm_f32 = false;  // true: rows > gemv_max_rows always take the exact-f32 GEMM instead of the tensor cores
 
     void make_current() const { cuda_check(cudaSetDevice(ordinal), "cudaSetDevice"); }
     ~lapid_b200_device() {
         if (cudaSetDevice(ordinal) == cudaSuccess) {
             if (scratch) cudaFree(scratch);
+            if (stream_ws.partial) cudaFree(stream_ws.partial);
             if (status_host) cudaFreeHost(status_host);
             if (own_stream) cudaStreamDestroy(own_stream);
         }
@@ -247,6 +251,7 @@ struct Plan {
     size_t scratch = 0;  // bytes of activation scratch the launch needs
     bool fast = false;   // specialised Q4_K / Q6_K GEMV (activations as 336-byte records)
     bool mma = false;    // Q4_K GEMV on the int8 tensor-core instruction (activations as tiles)
+    bool stream = false; // ... through the balanced-stream kernel (Q4_K, Q5_K)
     int records() const { return mma ? 2 : fast ? 1 : 0; }  // ActQuantArgs::records
     bool fast_i8 = false;  // specialised Int8 GEMV (activations as planes)
     bool tc = false;     // tensor-core GEMM (needs a bf16 copy of the activations in the scratch)
@@ -275,7 +280,7 @@ struct PendingGroup {
         const char *lo, *hi;
         bool hits(const Range &o) const { return lo < o.hi && o.lo < hi; }
     };
-    int fmt = 0, mode = 0;  // mode: ActQuantArgs::records of the members (1 = dp4a kernel, 2 = tensor-core kernel)
+    int fmt = 0, mode = 0;  // kernel of the members: 1 = dp4a kernel, 2 = tensor-core kernel, 3 = balanced-stream tensor-core kernel
     lb::GemvGroup g{};
     std::vector<Range> writes, reads;
 
@@ -291,8 +296,9 @@ struct PendingGroup {
             if (r.hits(out)) return false;
         g.item[g.count] = a;
         g.count++;
-        bool fits = md != 2 ? lb::qgemv_kq_group_smem(f, g) <= 227 * 1024 - 256
-                            : f == LAPID_B200_DTYPE_Q6_K ? lb::qgemv_q6k_mma_group_fits(g) : lb::qgemv_q4k_mma_group_fits(g);
+        bool fits = md == 3 ? true  // its shared memory does not depend on the members
+                    : md != 2 ? lb::qgemv_kq_group_smem(f, g) <= 227 * 1024 - 256
+                              : f == LAPID_B200_DTYPE_Q6_K ? lb::qgemv_q6k_mma_group_fits(g) : lb::qgemv_q4k_mma_group_fits(g);
         g.count--;
         return fits;
     }
@@ -314,7 +320,8 @@ struct PendingGroup {
         const bool early = dev.early_ok(true);  // members carry early = 1 when their activations came from the pre-pass at the head
         for (int i = 0; i < count; i++) out.item[i].early = early ? out.item[i].early : 0;
         const bool pdl = dev.pdl_launch();
-        if (mode == 2 && fmt == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(out, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        if (mode == 3) cuda_check(lb::launch_qgemv_kq_stream(fmt, out, dev.stream_ws, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        else if (mode == 2 && fmt == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(out, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (mode == 2) cuda_check(lb::launch_qgemv_q4k_mma(out, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else cuda_check(lb::launch_qgemv_kq_group(fmt, out, dev.sm_count, pdl, dev.stream), "qgemv launch");
         dev.launches++;
@@ -371,8 +378,12 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
         p.fast = dev.gemv_fast && lb::qgemv_kq_fast_shape_ok(l.b_dtype, p.rows, (uint32_t)l.k);
         p.fast_i8 = dev.gemv_fast && l.b_dtype == LAPID_B200_DTYPE_INT8 && lb::qgemv_i8_fast_shape_ok(p.rows, (uint32_t)l.k);
         // (Q6_K pays more per weight for unpacking: its tensor-core kernel wins one row later than Q4_K's)
+        p.stream = dev.gemv_fast && dev.gemv_stream && dev.gemv_mma_rows > 0 &&
+                   ((l.b_dtype == LAPID_B200_DTYPE_Q4_K && p.rows >= dev.gemv_mma_rows) || (l.b_dtype == LAPID_B200_DTYPE_Q5_K && p.rows > dev.gemv_mma_rows)) &&
+                   lb::qgemv_kq_stream_shape_ok(l.b_dtype, p.rows, (uint32_t)l.n, (uint32_t)l.k);
         p.mma = dev.gemv_fast && dev.gemv_mma_rows > 0 &&
-                ((l.b_dtype == LAPID_B200_DTYPE_Q4_K && p.rows >= dev.gemv_mma_rows && lb::qgemv_q4k_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
+                (p.stream ||
+                 (l.b_dtype == LAPID_B200_DTYPE_Q4_K && p.rows >= dev.gemv_mma_rows && lb::qgemv_q4k_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
                  (l.b_dtype == LAPID_B200_DTYPE_Q6_K && p.rows > dev.gemv_mma_rows && lb::qgemv_q6k_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
                  (l.b_dtype == LAPID_B200_DTYPE_INT8 && p.rows >= dev.gemv_mma_rows && lb::qgemv_i8_mma_shape_ok(p.rows, (uint32_t)l.k)));
         if (p.mma) {
@@ -757,14 +768,15 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             Range in[3];
             int n_in = 0;
             for (int i = 0; i < l.n_inputs; i++) in[n_in++] = Range{(const char *)ins[i]->ptr, (const char *)ins[i]->ptr + ins[i]->bytes};
-            if (!pend->accepts(l.b_dtype, slot->records, g, wr, in, n_in)) pend->flush(dev);
+            const int mode = slot->records == 2 && p.stream ? 3 : slot->records;
+            if (!pend->accepts(l.b_dtype, mode, g, wr, in, n_in)) pend->flush(dev);
             if (!slot->done) {  // its input is not written by a pending launch (checked above), so it may run first
                 cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl_launch(), dev.stream), "act_quant launch");
                 dev.launches++;
                 slot->done = true;
             }
             g.early = slot->hoisted ? 1 : 0;  // gated again when the group goes out
-            pend->add(l.b_dtype, slot->records, g, wr, in, n_in);
+            pend->add(l.b_dtype, mode, g, wr, in, n_in);
             return;
         }
         if (pend) pend->flush(dev);
@@ -785,7 +797,8 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             lb::GemvGroup one{};
             one.count = 1;
             one.item[0] = g;
-            if (l.b_dtype == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(one, dev.sm_count, pdl, dev.stream), "qgemv launch");
+            if (p.stream) cuda_check(lb::launch_qgemv_kq_stream(l.b_dtype, one, dev.stream_ws, dev.sm_count, pdl, dev.stream), "qgemv launch");
+            else if (l.b_dtype == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(one, dev.sm_count, pdl, dev.stream), "qgemv launch");
             else cuda_check(lb::launch_qgemv_q4k_mma(one, dev.sm_count, pdl, dev.stream), "qgemv launch");
         } else if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (l.b_dtype == LAPID_B200_DTYPE_INT4) cuda_check(lb::launch_qgemv_i4(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
@@ -915,7 +928,7 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
                     if ((const char *)ab->ptr < w.hi && w.lo < (const char *)ab->ptr + ab->bytes) clean = false;
                 // two rows of Q4_K whose activations come from the pre-pass at the head: the dp4a kernel overlaps
                 // with the kernels around it (GemvArgs::early) and beats the tensor-core kernel there
-                if (clean && dev->act_reuse && dev->early_acts && dev->pdl && p.rows == 2 && p.mma && p.fast &&
+                if (clean && dev->two_row_dp4a && dev->act_reuse && dev->early_acts && dev->pdl && p.rows == 2 && p.mma && p.fast &&
                     l.b_dtype == LAPID_B200_DTYPE_Q4_K)
                     key.records = 1;
                 int found = -1;
@@ -1015,6 +1028,9 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
         if (*dev->status_host != 0) {
             int st = *dev->status_host;
             *dev->status_host = 0;
+            // a launch that gave up may have left slab counters of the decode workspace half counted
+            cudaMemsetAsync(dev->stream_ws.counter, 0, dev->stream_ws.counters * 4, dev->stream);
+            cudaStreamSynchronize(dev->stream);
             if (st == 128) fail("index_out_of_range", "an index of a gather or an expert id of a matmul_id is out of range; the rows it selects were not computed");
             fail("backend", "a device-side wait gave up (status " + std::to_string(st) + "); the results of this call are invalid");
         }
@@ -1073,6 +1089,12 @@ lapid_b200_status lapid_b200_device_open(int32_t ordinal, lapid_b200_device **ou
             cuda_check(cudaHostAlloc((void **)&d->status_host, sizeof(int), cudaHostAllocMapped), "cudaHostAlloc");
             *d->status_host = 0;
             cuda_check(cudaHostGetDevicePointer((void **)&d->status_dev, d->status_host, 0), "cudaHostGetDevicePointer");
+            const size_t ws_bytes = lb::qgemv_kq_stream_ws_bytes(d->sm_count, &d->stream_ws);
+            void *ws = nullptr;
+            cuda_check(cudaMalloc(&ws, ws_bytes), "cudaMalloc(decode workspace)");
+            d->stream_ws.partial = (float *)ws;
+            d->stream_ws.counter = (uint32_t *)((char *)ws + d->stream_ws.partial_floats * 4);
+            cuda_check(cudaMemset(ws, 0, ws_bytes), "cudaMemset(decode workspace)");
         } catch (...) {
             delete d;
             throw;
@@ -1139,6 +1161,14 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             int r = std::atoi(value);
             if (r < 0 || r > 8) fail("invalid_argument", "gemv_mma_rows must be in 0..8");
             dev->gemv_mma_rows = (uint32_t)r;
+        } else if (k == "gemv_stream") {
+            dev->gemv_stream = v != "0";
+        } else if (k == "gemv_stream_config") {
+            lb::qgemv_kq_stream_set_config(std::atoi(value));
+        } else if (k == "gemv_stream_ctas") {
+            lb::qgemv_kq_stream_set_ctas_per_sm(std::atoi(value));
+        } else if (k == "gemv_two_row_dp4a") {
+            dev->two_row_dp4a = v != "0";
         } else if (k == "gemv_mma_config") {
             lb::qgemv_q4k_mma_set_config(std::atoi(value));
         } else if (k == "gemv_ctas_per_sm") {
@@ -1563,6 +1593,41 @@ lapid_b200_status lapid_b200_act_layout(lapid_b200_device *dev, const lapid_b200
                                        std::to_string(dev->gemv_max_rows) + ", k a multiple of 256)");
         *layout = p.records();
         *bytes = p.scratch;
+    });
+}
+
+// The pre-pass of the decode path as a call of its own (crates/lapid-cpu/src/matmul/quant.rs:30-89).
+lapid_b200_status lapid_b200_quantize_activations(lapid_b200_device *dev, const lapid_b200_buffer *a, uint64_t rows, uint64_t k,
+                                                  int32_t layout, lapid_b200_buffer *qact) {
+    return guard([&] {
+        need(dev);
+        if (!a || !qact) fail("invalid_argument", "a or qact is NULL");
+        if (a->dev != dev || qact->dev != dev) fail("wrong_backend", "quantize_activations: a buffer belongs to another device");
+        if (rows == 0 || rows > 8 || k == 0 || k >= (1ull << 31) || k % 32 != 0 || (layout != 0 && k % 256 != 0))
+            fail("invalid_launch", "quantize_activations: rows in 1..8, k a multiple of 32 (of 256 for the record and tile layouts)");
+        if (layout < 0 || layout > 2) fail("invalid_argument", "quantize_activations: layout must be 0, 1 or 2");
+        if (a->bytes / 4 < rows * k) fail("out_of_bounds", "quantize_activations: a holds " + std::to_string(a->bytes / 4) + " < " + std::to_string(rows * k) + " elements");
+        if ((uintptr_t)a->ptr & 15) fail("invalid_launch", "quantize_activations: a must be 16-byte aligned");
+        const size_t planes = lb::act_plane_bytes((uint32_t)rows, (uint32_t)k) + 2 * lb::act_scale_bytes((uint32_t)rows, (uint32_t)k);
+        const size_t need_b = layout == 0 ? planes : layout == 1 ? rows * (k / 256) * lb::REC : lb::qgemv_q4k_mma_act_bytes((uint32_t)rows, (uint32_t)k);
+        if (qact->bytes < need_b) fail("out_of_bounds", "quantize_activations qact: needs " + std::to_string(need_b) + " bytes, buffer has " + std::to_string(qact->bytes));
+        if ((uintptr_t)qact->ptr & 15) fail("invalid_launch", "quantize_activations: qact must be 16-byte aligned");
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        const lb::ActOut o = act_out_at(qact->ptr, layout, (uint32_t)rows, (uint32_t)k);
+        lb::ActQuantArgs q{};
+        q.a = (const float *)a->ptr;
+        q.a_bs = rows * k;
+        q.a_rs = k;
+        q.rows = (uint32_t)rows;
+        q.m = (uint32_t)rows;
+        q.k = (uint32_t)k;
+        q.qa = o.qa;
+        q.da = o.da;
+        q.bs = o.bs;
+        q.records = layout;
+        cuda_check(lb::launch_act_quant(q, dev->sm_count, dev->pdl, dev->stream), "act_quant launch");
+        dev->launches++;
     });
 }
 

@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 namespace lb {
 
 // ---- dequant.cu
@@ -113,17 +115,49 @@ bool qgemv_q4k_fast_supported(const GemvArgs &args);
 cudaError_t launch_qgemv_q4k_fast(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // The largest dynamic shared-memory size a kernel has been opted in to, per device of the process
 // (cudaFuncSetAttribute is a per-device setting). Used as a function-local static by the launchers.
+// Launches may come from several host threads (one per device): the table is guarded by its own mutex.
 struct DynamicSmemOptIn {
     size_t have[64] = {};
+    std::mutex mu;
     cudaError_t raise(const void *kernel, size_t bytes) {
         int dev = 0;
         cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
         if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lock(mu);
         if (bytes <= have[dev]) return cudaSuccess;
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
         if (e == cudaSuccess) have[dev] = bytes;
         return e;
+    }
+};
+
+// Resident CTAs per SM of a kernel for a dynamic shared-memory size, remembered per (device, size); a launcher keeps
+// one as a function-local static. Thread-safe; when the table is full the answer is computed every time.
+struct OccupancyCache {
+    struct Entry {
+        int dev;
+        size_t smem;
+        int ctas;
+    };
+    Entry e[16];
+    int n = 0;
+    std::mutex mu;
+    template <class K> cudaError_t get(K kernel, int threads, size_t smem, int *out) {
+        int dev = 0;
+        if (cudaError_t err = cudaGetDevice(&dev); err != cudaSuccess) return err;
+        std::lock_guard<std::mutex> lock(mu);
+        for (int i = 0; i < n; i++)
+            if (e[i].dev == dev && e[i].smem == smem) {
+                *out = e[i].ctas;
+                return cudaSuccess;
+            }
+        int occ = 0;
+        if (cudaError_t err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, smem); err != cudaSuccess) return err;
+        if (occ < 1) occ = 1;
+        if (n < 16) e[n++] = Entry{dev, smem, occ};
+        *out = occ;
+        return cudaSuccess;
     }
 };
 
@@ -148,6 +182,20 @@ size_t qgemv_q4k_mma_act_bytes(uint32_t rows, uint32_t k);
 bool qgemv_q4k_mma_group_fits(GemvGroup &group);
 cudaError_t launch_qgemv_q4k_mma(GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream);
 void qgemv_q4k_mma_set_config(int index);  // -1 = pick by shared-memory fit
+// ---- qgemv_kq_stream.cu: Q4_K / Q5_K decode on the same instruction as one stream of equal work shares
+// (2..8 rows; any K that is a multiple of 256; same activation tiles). Spans that hold only some k-chunks
+// of a row tile meet in a workspace in global memory: `partial` (partial_floats f32) and `counter`
+// (counters u32, zero between launches); one workspace per device serves every launch of its stream.
+struct StreamWs {
+    float *partial;
+    uint32_t *counter;
+    uint64_t partial_floats, counters;
+};
+size_t qgemv_kq_stream_ws_bytes(int sm_count, StreamWs *layout);  // bytes to allocate: the partials, then the counters
+bool qgemv_kq_stream_shape_ok(int fmt, uint32_t rows, uint32_t n, uint32_t k);
+cudaError_t launch_qgemv_kq_stream(int fmt, GemvGroup &group, const StreamWs &ws, int sm_count, bool pdl, cudaStream_t stream);
+void qgemv_kq_stream_set_config(int index);     // tuning: -1 = choose
+void qgemv_kq_stream_set_ctas_per_sm(int n);    // tuning: 0 = choose
 // Int8 planes on the same instruction (K a multiple of 512); same activation tiles.
 bool qgemv_i8_mma_shape_ok(uint32_t rows, uint32_t k);
 cudaError_t launch_qgemv_i8_mma(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);

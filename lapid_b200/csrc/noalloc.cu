@@ -16,8 +16,12 @@
 //  * the array keeps what the last call left in it. Nothing in it has to start at zero: the
 //    pre-pass of a call overwrites every byte its GEMV interprets (the 16 padding bytes of a
 //    record are copied but never read as data);
-//  * the first call on a GPU looks up the array's device address and sets the kernels' attributes.
-//    Make that first call outside any stream capture; later calls only launch two kernels.
+//  * the first call on a GPU looks up the array's device address; the first call on a GPU with a given
+//    (rows, k) also sets that kernel variant's attributes and asks for its occupancy. Make those first
+//    calls outside any stream capture; later calls with the same shape only launch two kernels;
+//  * the calling thread's current device is `ordinal` while the call runs and is put back before it returns;
+//  * a device-side wait that gives up (it never should) is recorded in a second static word, which
+//    lapid_b200_gemv_q4k_static_status reads and clears.
 // No cudaMalloc, cudaFree, cudaHostAlloc or any other allocating call is made here, on any path.
 #include "../../include/lapid_b200.h"
 
@@ -38,11 +42,28 @@ constexpr size_t STATIC_SCRATCH_BYTES = LAPID_B200_STATIC_SCRATCH_BYTES;
 // Activation records of one call: rows * (k / 256) records of 336 bytes. In host code this name is
 // only a handle for cudaGetSymbolAddress; the kernels get the looked-up device address.
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+// The kernels OR a bit in here when one of their bounded waits gave up (the role the host-mapped status word
+// of a device object plays for `execute`).
+static __device__ int g_static_status;
 
 constexpr int MAX_DEVICES = 64;
 std::mutex g_mu;
 void *g_scratch_addr[MAX_DEVICES] = {};
+int *g_status_addr[MAX_DEVICES] = {};
 int g_sm_count[MAX_DEVICES] = {};
+
+// Makes `ordinal` current for the scope and puts the caller's device back afterwards.
+struct DeviceScope {
+    int prev = -1;
+    cudaError_t err;
+    explicit DeviceScope(int ordinal) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        err = cudaSetDevice(ordinal);
+    }
+    ~DeviceScope() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
 
 }  // namespace
 
@@ -67,9 +88,11 @@ extern "C" LAPID_B200_API lapid_b200_status lapid_b200_gemv_q4k_static(int32_t o
                                                      std::to_string(w_need) + " bytes, got " + std::to_string(w_bytes));
     if (((uintptr_t)w & 15) != 0) return lb::report_error("invalid_launch", "gemv_q4k_static: w must be 16-byte aligned");
 
-    cudaError_t e = cudaSetDevice(ordinal);
+    DeviceScope scope(ordinal);
+    cudaError_t e = scope.err;
     if (e != cudaSuccess) return lb::report_error("device_unavailable", std::string("gemv_q4k_static: cudaSetDevice: ") + cudaGetErrorString(e));
     void *scratch = nullptr;
+    int *status = nullptr;
     int sm_count = 0;
     {
         std::lock_guard<std::mutex> lock(g_mu);
@@ -78,13 +101,19 @@ extern "C" LAPID_B200_API lapid_b200_status lapid_b200_gemv_q4k_static(int32_t o
             e = cudaGetSymbolAddress(&ptr, g_static_scratch);
             if (e != cudaSuccess || !ptr)
                 return lb::report_error("cuda", std::string("gemv_q4k_static: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+            void *sptr = nullptr;
+            e = cudaGetSymbolAddress(&sptr, g_static_status);
+            if (e != cudaSuccess || !sptr)
+                return lb::report_error("cuda", std::string("gemv_q4k_static: cudaGetSymbolAddress(status): ") + cudaGetErrorString(e));
             int sms = 0;
             e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ordinal);
             if (e != cudaSuccess) return lb::report_error("cuda", std::string("gemv_q4k_static: ") + cudaGetErrorString(e));
             g_sm_count[ordinal] = sms;
+            g_status_addr[ordinal] = (int *)sptr;
             g_scratch_addr[ordinal] = ptr;
         }
         scratch = g_scratch_addr[ordinal];
+        status = g_status_addr[ordinal];
         sm_count = g_sm_count[ordinal];
     }
     cudaStream_t stream = (cudaStream_t)cuda_stream;
@@ -115,7 +144,7 @@ extern "C" LAPID_B200_API lapid_b200_status lapid_b200_gemv_q4k_static(int32_t o
     g.extra = nullptr;
     g.a = a;
     g.a_rs = k;
-    g.status = nullptr;
+    g.status = status;
     g.rows = rows;
     g.m = rows;
     g.n = n;
@@ -123,5 +152,31 @@ extern "C" LAPID_B200_API lapid_b200_status lapid_b200_gemv_q4k_static(int32_t o
     if (!lb::qgemv_q4k_fast_supported(g)) return lb::report_error("invalid_launch", "gemv_q4k_static: shape not supported");
     e = lb::launch_qgemv_q4k_fast(g, sm_count, false, stream);
     if (e != cudaSuccess) return lb::report_error("cuda", std::string("gemv_q4k_static: launch: ") + cudaGetErrorString(e));
+    return LAPID_B200_OK;
+}
+
+// Reads and clears the wait-timeout word of `ordinal`'s static path. Synchronise the stream(s) the calls were
+// queued on first: the copy below is ordered behind the legacy default stream only.
+extern "C" LAPID_B200_API lapid_b200_status lapid_b200_gemv_q4k_static_status(int32_t ordinal, int32_t *out) {
+    if (!out) return lb::report_error("invalid_argument", "gemv_q4k_static_status: out is NULL");
+    if (ordinal < 0 || ordinal >= MAX_DEVICES)
+        return lb::report_error("device_unavailable", "gemv_q4k_static_status: device ordinal " + std::to_string(ordinal));
+    int *addr = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        addr = g_status_addr[ordinal];
+    }
+    if (!addr) {  // no call on this GPU yet: nothing can have been recorded
+        *out = 0;
+        return LAPID_B200_OK;
+    }
+    DeviceScope scope(ordinal);
+    if (scope.err != cudaSuccess)
+        return lb::report_error("device_unavailable", std::string("gemv_q4k_static_status: cudaSetDevice: ") + cudaGetErrorString(scope.err));
+    int v = 0;
+    cudaError_t e = cudaMemcpy(&v, addr, sizeof v, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && v != 0) e = cudaMemset(addr, 0, sizeof v);
+    if (e != cudaSuccess) return lb::report_error("cuda", std::string("gemv_q4k_static_status: ") + cudaGetErrorString(e));
+    *out = v;
     return LAPID_B200_OK;
 }

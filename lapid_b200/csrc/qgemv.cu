@@ -396,15 +396,11 @@ static cudaError_t launch_one(const GemvArgs &a, int sm_count, bool pdl, cudaStr
     auto kern = qgemv_kernel<FMT, M, C, STAGES>;
     constexpr size_t smem = (size_t)WARPS * STAGES * C * Geo<FMT>::SPAN;
     static_assert(smem <= 227 * 1024, "ring does not fit in shared memory");
-    static int ctas_per_sm = 0;  // same for every device of the supported kind
     static DynamicSmemOptIn opted;
     if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
-    if (ctas_per_sm == 0) {
-        int occ = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, WARPS * 32, smem);
-        if (e != cudaSuccess) return e;
-        ctas_per_sm = occ > 0 ? occ : 1;
-    }
+    static OccupancyCache occupancy;
+    int ctas_per_sm = 1;
+    if (cudaError_t e = occupancy.get(kern, WARPS * 32, smem, &ctas_per_sm); e != cudaSuccess) return e;
     uint32_t tasks = (a.n + C - 1) / C;
     uint32_t want = (tasks + WARPS - 1) / WARPS;
     uint32_t cap = (uint32_t)sm_count * (uint32_t)ctas_per_sm;

@@ -194,17 +194,11 @@ template <int M, bool EARLY = false> static cudaError_t launch_m(const GemvArgs 
     constexpr int WARPS = Shape<M>::WARPS;
     const size_t smem = BAR_BYTES + (size_t)WARPS * 2 * STAGE + (size_t)a.rows * a.k + (size_t)a.rows * (a.k / GROUP) * 4 +
                         (EARLY ? (size_t)WARPS * PEND_ROWS * 4 : 0);
-    static size_t occ_smem = 0;
-    static int ctas_per_sm = 0;
     static DynamicSmemOptIn opted;
     if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
-    if (ctas_per_sm == 0 || occ_smem != smem) {
-        int occ = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, WARPS * 32, smem);
-        if (e != cudaSuccess) return e;
-        ctas_per_sm = occ > 0 ? occ : 1;
-        occ_smem = smem;
-    }
+    static OccupancyCache occupancy;
+    int ctas_per_sm = 1;
+    if (cudaError_t e = occupancy.get(kern, WARPS * 32, smem, &ctas_per_sm); e != cudaSuccess) return e;
     int per_sm = ctas_per_sm >= 4 ? ctas_per_sm - 1 : ctas_per_sm;  // one slot for the next kernel (see qgemv_q4k.cu)
     if (EARLY) per_sm = 1;                                          // the other slots belong to the launches around this one
     uint32_t grid = (uint32_t)sm_count * (uint32_t)per_sm;

@@ -1,0 +1,542 @@
+// Q4_K / Q5_K decode GEMV for 2..8 activation rows on the warp-level int8 tensor-core instruction,
+// organised as one stream of equal work shares (arithmetic: see qgemv.cu; the integer dot products
+// are the same, only the order of the f32 sums over sub-blocks and k-chunks differs).
+//
+//  * Unit of work: 16*TILES*WARPS weight rows x one k-chunk (two super-blocks, 512 weights per row).
+//    The units of all members of the launch, tile after tile, k-chunk after k-chunk, form one
+//    sequence; CTA b takes the contiguous span [U*b/G, U*(b+1)/G) of it, so every CTA streams the
+//    same number of bytes whatever the shape (no tail of half-empty waves, no idle SMs on matrices
+//    with few rows).
+//  * Inside a CTA one producer warp fills a ring of stages: the weights of a unit by ONE tensor-map
+//    copy (TMA: a box of rows x 288 or 352 bytes of the packed matrix; rows past the end and the missing
+//    half of an odd last k-chunk arrive as zeros) and the int8 activation tiles of the same two
+//    super-blocks by one bulk copy, both completing on the stage's mbarrier. Shared memory therefore
+//    does not grow with K, and the members of a grouped launch may read different activations.
+//  * Each consumer warp owns 16*TILES rows of the tile and keeps their 16x8 accumulators in registers
+//    over all k-chunks of its span: no cross-warp reduction, no CTA-wide barrier in the main loop. A
+//    warp releases a stage with one mbarrier arrive.
+//  * A span that covers all k-chunks of a tile stores it directly. Otherwise the warp writes its partial
+//    16x8 tiles to a workspace in global memory and bumps a counter of the slab; the warp that arrives
+//    last adds the partials in span order (so the sum does not depend on who was last) and stores.
+//    Nobody waits for anybody: there is no spin on another CTA.
+//  * Programmatic dependent launch: weights are requested before the dependency wait; a launch whose
+//    activations are older than the kernel in front of it (GemvArgs::early) also fetches them and
+//    computes before the wait. Nothing is written, and the workspace is not touched, before the kernel
+//    in front has completed, so consecutive launches can share one workspace.
+//  * Every mbarrier wait is bounded; a wait that gives up sets the host-visible status word.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "pipe.cuh"
+#include "tp_ll.cuh"
+
+namespace lb {
+namespace ks {
+
+using namespace pipe;
+
+constexpr int BAR_BYTES = 128;
+constexpr int SC_STRIDE = 80;  // decoded scales of one (row, super-block): 16 floats, padded against bank conflicts
+
+template <int FMT> struct Geo {
+    static constexpr int BLK = FMT == FMT_Q5K ? Q5K_BYTES : Q4K_BYTES;
+    static constexpr int ROWB = 2 * BLK;                 // one k-chunk of one weight row
+    static constexpr int QS = FMT == FMT_Q5K ? 48 : 16;  // offset of the nibbles inside a block
+};
+
+__host__ __device__ constexpr uint32_t act_block_bytes(uint32_t rows) { return 256 * rows + 512; }
+
+template <int NG> struct Maps {
+    CUtensorMap m[NG];  // packed weights of each member: [n rows][k/256 * BLK/4 words], box ROWB/4 words x tile rows
+};
+
+template <int FMT, int WARPS, int TILES, int STAGES, int NG>
+__global__ void __launch_bounds__((WARPS + 1) * 32, (WARPS >= 8 && STAGES <= 2) || (WARPS < 8 && STAGES <= 3) ? 2 : 1)
+qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp, StreamWs ws, uint32_t early) {
+    constexpr int BLK = Geo<FMT>::BLK, ROWB = Geo<FMT>::ROWB, QS = Geo<FMT>::QS;
+    constexpr int RPW = 16 * TILES;      // rows per consumer warp
+    constexpr int RT = RPW * WARPS;      // rows per tile
+    constexpr int WBYTES = RT * ROWB;    // weight bytes per stage
+    constexpr int EW = 128 * TILES;      // outputs of one warp per tile
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t M = grp.item[0].rows;
+    const uint32_t nblk = grp.item[0].k / QK;
+    const uint32_t C = (nblk + 1) / 2;  // k-chunks per tile
+    const uint32_t ABLK = act_block_bytes(M);
+    const uint32_t SBYTES = WBYTES + 2 * ABLK;
+    const uint32_t tiles = grp.task_end[grp.count - 1];
+    const uint64_t U = (uint64_t)tiles * C;
+    const uint32_t G = gridDim.x, b = blockIdx.x;
+    const uint32_t u_lo = (uint32_t)(U * b / G), u_hi = (uint32_t)(U * (b + 1) / G);
+    auto locate = [&](uint32_t t, uint32_t &local) -> int {
+        if constexpr (NG == 1) {
+            local = t;
+            return 0;
+        }
+        int i = 0;
+        while (t >= grp.task_end[i]) i++;
+        local = t - (i ? grp.task_end[i - 1] : 0);
+        return i;
+    };
+
+    uint64_t *full = (uint64_t *)smem, *empty = full + STAGES;
+    uint8_t *stages = smem + BAR_BYTES;
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, WARPS);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == WARPS) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0) {
+            const uint32_t nunits = u_hi - u_lo;
+            auto unit = [&](uint32_t i, int &item, uint32_t &local, uint32_t &c, uint32_t &nb) {
+                const uint32_t u = u_lo + i, gt = u / C;
+                c = u - gt * C;
+                item = locate(gt, local);
+                nb = min(2u, nblk - 2 * c);
+            };
+            auto load_w = [&](uint32_t i, uint32_t slot) {
+                int item;
+                uint32_t local, c, nb;
+                unit(i, item, local, c, nb);
+                mbar_expect_tx(full + slot, WBYTES + nb * ABLK);  // the whole box counts, zero fill included
+                tma_load_2d(stages + (size_t)slot * SBYTES, &maps.m[item], (int)(c * (ROWB / 4)), (int)(local * RT), full + slot);
+            };
+            auto load_a = [&](uint32_t i, uint32_t slot) {
+                int item;
+                uint32_t local, c, nb;
+                unit(i, item, local, c, nb);
+                bulk_g2s(stages + (size_t)slot * SBYTES + WBYTES, (const uint8_t *)grp.item[item].qa + (size_t)(2 * c) * ABLK, nb * ABLK,
+                         full + slot);
+            };
+            const uint32_t pre = nunits < (uint32_t)STAGES ? nunits : (uint32_t)STAGES;
+            for (uint32_t i = 0; i < pre; i++) load_w(i, i);
+            if (!early) asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations come from the kernel in front
+            for (uint32_t i = 0; i < pre; i++) load_a(i, i);
+            uint32_t slot = 0, phase = 0;  // phase of `empty[slot]` the next refill waits for
+            for (uint32_t i = pre; i < nunits; i++) {
+                if (!mbar_wait(empty + slot, phase)) {
+                    if (grp.item[0].status) atomicOr(grp.item[0].status, 1);
+                    break;
+                }
+                load_w(i, slot);
+                load_a(i, slot);
+                if (++slot == (uint32_t)STAGES) {
+                    slot = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+        // later kernels take this grid's completion as the completion of everything before it
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumers
+    const int gq = lane >> 2, t4 = lane & 3;
+    const uint32_t colq = (uint32_t)gq < M ? gq : 0;      // activation row of this lane's B fragment
+    const uint32_t cp = (uint32_t)(2 * t4) < M ? t4 : 0;  // activation row pair of this lane's C fragment
+    const uint64_t neg_magic = pack2(-MAGIC, -MAGIC);
+    uint8_t *scs = stages + (size_t)STAGES * SBYTES + (size_t)warp * (32 * TILES * SC_STRIDE);
+    __shared__ TpPushCtx tp_ctx[WARPS];
+    bool waited = false, healthy = true;
+    const uint32_t first_tile = u_lo / C;
+    auto owner = [&](uint64_t u) -> uint32_t { return (uint32_t)(((u + 1) * G - 1) / U); };
+
+    uint32_t u = u_lo, slot = 0, par = 0;
+    while (u < u_hi) {
+        const uint32_t gt = u / C, c0 = u - gt * C;
+        const uint32_t c1 = min(C, c0 + (u_hi - u));
+        uint32_t local;
+        const int item = locate(gt, local);
+        const GemvArgs &p = grp.item[item];
+        float acc[TILES][4];
+#pragma unroll
+        for (int tl = 0; tl < TILES; tl++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[tl][i] = 0.0f;
+
+        for (uint32_t c = c0; c < c1; c++, u++) {
+            if (healthy && !mbar_wait(full + slot, par)) {
+                healthy = false;
+                if (lane == 0 && grp.item[0].status) atomicOr(grp.item[0].status, 1);
+            }
+            const uint8_t *wst = stages + (size_t)slot * SBYTES + (size_t)warp * (RPW * ROWB);  // this warp's rows
+            const uint8_t *ast = stages + (size_t)slot * SBYTES + WBYTES;
+            const uint32_t nb = min(2u, nblk - 2 * c);
+            if (healthy) {
+                // ---- decode the 6-bit scales and mins: one lane per (row, super-block); per sub-block pair j
+                //      {d*sc[2j], d*sc[2j+1] (/16 where the high nibbles are used in place), -dmin*m[2j], -dmin*m[2j+1]}
+                auto decode = [&](uint32_t rr, uint32_t bb, uint32_t sl) {
+                    const uint4 h = *(const uint4 *)(wst + rr * ROWB + bb * BLK);
+                    const float d = half_bits_to_float(h.x & 0xffff), dmin = -half_bits_to_float(h.x >> 16);
+                    const float nd = d * -8388608.0f, ndmin = dmin * -8388608.0f;
+                    const uint32_t w0 = h.y, w1 = h.z, w2 = h.w;
+                    const uint32_t sc_lo = w0 & 0x3F3F3F3Fu, mn_lo = w1 & 0x3F3F3F3Fu;
+                    const uint32_t sc_hi = (w2 & 0x0F0F0F0Fu) | (((w0 >> 6) & 0x03030303u) << 4);
+                    const uint32_t mn_hi = ((w2 >> 4) & 0x0F0F0F0Fu) | (((w1 >> 6) & 0x03030303u) << 4);
+                    float w[16];
+#pragma unroll
+                    for (int s = 0; s < 8; s++) {
+                        const uint32_t sel = 0x7440u + (s & 3);
+                        const float sc = scale_byte(s < 4 ? sc_lo : sc_hi, sel, d, nd);
+                        w[s] = (FMT == FMT_Q4K && (s & 1)) ? sc * 0.0625f : sc;
+                        w[8 + s] = scale_byte(s < 4 ? mn_lo : mn_hi, sel, dmin, ndmin);
+                    }
+                    float4 *dst = (float4 *)(scs + sl * SC_STRIDE);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) dst[j] = make_float4(w[2 * j], w[2 * j + 1], w[8 + 2 * j], w[8 + 2 * j + 1]);
+                };
+                if constexpr (TILES == 2) {
+#pragma unroll
+                    for (uint32_t bb = 0; bb < 2; bb++)
+                        if (bb < nb) decode(lane, bb, bb * RPW + lane);
+                } else {
+                    if ((uint32_t)(lane >> 4) < nb) decode(lane & 15, lane >> 4, lane);
+                }
+                __syncwarp();
+#pragma unroll
+                for (uint32_t bb = 0; bb < 2; bb++) {
+                    if (bb >= nb) break;
+                    const uint8_t *ab = ast + (size_t)bb * ABLK;
+                    const float4 *dsp = (const float4 *)(ab + 256 * M + cp * 64);
+                    ulonglong2 dav[4];  // {da[c0], da[c1]} of sub-blocks 2i, 2i + 1
+                    float4 bsv[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        dav[i] = ((const ulonglong2 *)dsp)[i];
+                        bsv[i] = dsp[16 + i];
+                    }
+                    const float *bs = (const float *)bsv;  // [sub-block][2]
+                    uint2 qh[TILES][2];                    // Q5_K: the fifth bits of this lane's eight k positions, rows gq and gq + 8
+                    if constexpr (FMT == FMT_Q5K) {
+#pragma unroll
+                        for (int tl = 0; tl < TILES; tl++)
+#pragma unroll
+                            for (int hf = 0; hf < 2; hf++)
+                                qh[tl][hf] = *(const uint2 *)(wst + (tl * 16 + hf * 8 + gq) * ROWB + bb * BLK + 16 + 8 * t4);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const uint2 blo = *(const uint2 *)(ab + (2 * j) * (M * 32) + colq * 32 + 8 * t4);
+                        const uint2 bhi = *(const uint2 *)(ab + (2 * j + 1) * (M * 32) + colq * 32 + 8 * t4);
+#pragma unroll
+                        for (int tl = 0; tl < TILES; tl++) {
+                            const uint8_t *wrow = wst + (tl * 16 + gq) * ROWB + bb * BLK + QS + j * 32 + 8 * t4;
+                            const uint2 wa = *(const uint2 *)wrow, wb = *(const uint2 *)(wrow + 8 * ROWB);
+                            uint32_t al[4], ah[4];
+                            if constexpr (FMT == FMT_Q5K) {
+                                // bit 2j (2j + 1) of a qh byte is the fifth bit of the low (high) nibble's weight
+                                auto fifth = [](uint32_t q, int bit) { return (bit <= 4 ? q << (4 - bit) : q >> (bit - 4)) & 0x10101010u; };
+                                al[0] = (wa.x & 0x0F0F0F0Fu) | fifth(qh[tl][0].x, 2 * j);
+                                al[1] = (wb.x & 0x0F0F0F0Fu) | fifth(qh[tl][1].x, 2 * j);
+                                al[2] = (wa.y & 0x0F0F0F0Fu) | fifth(qh[tl][0].y, 2 * j);
+                                al[3] = (wb.y & 0x0F0F0F0Fu) | fifth(qh[tl][1].y, 2 * j);
+                                ah[0] = ((wa.x >> 4) & 0x0F0F0F0Fu) | fifth(qh[tl][0].x, 2 * j + 1);
+                                ah[1] = ((wb.x >> 4) & 0x0F0F0F0Fu) | fifth(qh[tl][1].x, 2 * j + 1);
+                                ah[2] = ((wa.y >> 4) & 0x0F0F0F0Fu) | fifth(qh[tl][0].y, 2 * j + 1);
+                                ah[3] = ((wb.y >> 4) & 0x0F0F0F0Fu) | fifth(qh[tl][1].y, 2 * j + 1);
+                            } else {
+                                al[0] = wa.x & 0x0F0F0F0Fu, al[1] = wb.x & 0x0F0F0F0Fu, al[2] = wa.y & 0x0F0F0F0Fu, al[3] = wb.y & 0x0F0F0F0Fu;
+                                ah[0] = wa.x & 0xF0F0F0F0u, ah[1] = wb.x & 0xF0F0F0F0u, ah[2] = wa.y & 0xF0F0F0F0u, ah[3] = wb.y & 0xF0F0F0F0u;
+                            }
+                            int cl[4], ch[4];
+                            mma_u8s8_magic(cl, al[0], al[1], al[2], al[3], blo.x, blo.y);
+                            mma_u8s8_magic(ch, ah[0], ah[1], ah[2], ah[3], bhi.x, bhi.y);
+                            // int -> f32 and the activation scale on packed f32x2: the two outputs of a
+                            // row are one register pair, and so are their activation scales
+                            float gl[4], gh[4];
+                            unpack2(mul2(add2(pack2i(cl[0], cl[1]), neg_magic), dav[j].x), gl[0], gl[1]);
+                            unpack2(mul2(add2(pack2i(cl[2], cl[3]), neg_magic), dav[j].x), gl[2], gl[3]);
+                            unpack2(mul2(add2(pack2i(ch[0], ch[1]), neg_magic), dav[j].y), gh[0], gh[1]);
+                            unpack2(mul2(add2(pack2i(ch[2], ch[3]), neg_magic), dav[j].y), gh[2], gh[3]);
+                            const uint32_t sl = bb * RPW + tl * 16 + gq;
+                            const float4 sv0 = ((const float4 *)(scs + sl * SC_STRIDE))[j];
+                            const float4 sv1 = ((const float4 *)(scs + (sl + 8) * SC_STRIDE))[j];
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const float4 sv = (i & 2) ? sv1 : sv0;
+                                const int cc = i & 1;
+                                float a = acc[tl][i];
+                                a = fmaf(gl[i], sv.x, a);
+                                a = fmaf(sv.z, bs[(2 * j) * 2 + cc], a);
+                                a = fmaf(gh[i], sv.y, a);
+                                a = fmaf(sv.w, bs[(2 * j + 1) * 2 + cc], a);
+                                acc[tl][i] = a;
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();  // every lane is done with the stage and the scale scratch
+            if (lane == 0) mbar_arrive(empty + slot);
+            if (++slot == (uint32_t)STAGES) {
+                slot = 0;
+                par ^= 1;
+            }
+        }
+
+        // ---- nothing is written, and the workspace is not touched, before the kernel in front has completed
+        if (!waited) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            waited = true;
+            if (grp.item[0].tp) {  // only the first member of a launch may push (tensor-parallel launches are never grouped)
+                if (lane == 0) tp_push_ctx_load(&tp_ctx[warp], grp.item[0].tp);
+                __syncwarp();
+            }
+        }
+        if (!healthy) continue;
+        auto store = [&](const float (&v)[TILES][4]) {
+#pragma unroll
+            for (int tl = 0; tl < TILES; tl++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t row = local * RT + warp * RPW + tl * 16 + gq + ((i & 2) ? 8 : 0);
+                    const uint32_t r = 2 * t4 + (i & 1);
+                    if (row < p.n && r < M) {
+                        float x = v[tl][i];
+                        const uint32_t bt = r / p.m, ri = r % p.m;
+                        if (p.extra) x += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
+                        if (p.tp) tp_push_value(&tp_ctx[warp], (uint64_t)r * p.n + row, x);  // row-parallel partial: to every rank
+                        else p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = x;
+                    }
+                }
+        };
+        if (c0 == 0 && c1 == C) {
+            store(acc);
+            continue;
+        }
+        // ---- this span holds only some k-chunks of the tile: leave the partial sums in the workspace; the
+        //      warp that completes the slab adds them in span order and stores
+        const uint32_t mine_slot = gt == first_tile ? 0 : 1;  // a span has at most two partial tiles: its first and its last
+        float *mine = ws.partial + (((size_t)b * 2 + mine_slot) * WARPS + warp) * EW;
+#pragma unroll
+        for (int tl = 0; tl < TILES; tl++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) __stcg(mine + (tl * 4 + i) * 32 + lane, acc[tl][i]);
+        __threadfence();
+        __syncwarp();
+        const uint32_t b_first = owner((uint64_t)gt * C), b_last = owner((uint64_t)gt * C + C - 1);
+        const uint32_t slab = gt * WARPS + warp;
+        uint32_t old = 0;
+        if (lane == 0) old = atomicAdd(ws.counter + slab, 1u);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old != b_last - b_first) continue;  // not the last one
+        __threadfence();
+        if (lane == 0) ws.counter[slab] = 0;  // ready for the next launch (which starts its fix-ups after this grid has completed)
+        float v[TILES][4];
+#pragma unroll
+        for (int tl = 0; tl < TILES; tl++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) v[tl][i] = 0.0f;
+        for (uint32_t bb = b_first; bb <= b_last; bb++) {
+            if (bb == b) {
+#pragma unroll
+                for (int tl = 0; tl < TILES; tl++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) v[tl][i] += acc[tl][i];
+                continue;
+            }
+            const uint32_t their_first = (uint32_t)(U * bb / G) / C;
+            const float *src = ws.partial + (((size_t)bb * 2 + (their_first == gt ? 0 : 1)) * WARPS + warp) * EW;
+#pragma unroll
+            for (int tl = 0; tl < TILES; tl++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) v[tl][i] += __ldcg(src + (tl * 4 + i) * 32 + lane);
+        }
+        store(v);
+    }
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// ------------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static std::mutex g_mu;  // guards the caches below: launches may come from several host threads (one per device)
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!tried) {
+        tried = true;
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// A tensor map depends only on (address, n, k, block bytes, box rows): the last few are remembered, a
+// decode loop asks for the same handful every token.
+static bool weight_map(const GemvArgs &a, uint32_t blk, uint32_t box_rows, CUtensorMap &out) {
+    struct Entry {
+        const void *w;
+        uint32_t n, k, blk, rows;
+        CUtensorMap map;
+    };
+    constexpr int CAP = 256;
+    static Entry cache[CAP];
+    static int used = 0, next = 0;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    std::lock_guard<std::mutex> lock(g_mu);
+    for (int i = 0; i < used; i++)
+        if (cache[i].w == a.w && cache[i].n == a.n && cache[i].k == a.k && cache[i].blk == blk && cache[i].rows == box_rows) {
+            out = cache[i].map;
+            return true;
+        }
+    const uint32_t nblk = a.k / QK;
+    cuuint64_t dims[2] = {(cuuint64_t)nblk * (blk / 4), a.n};
+    cuuint64_t strides[1] = {(cuuint64_t)nblk * blk};
+    cuuint32_t box[2] = {2 * blk / 4, box_rows};
+    cuuint32_t es[2] = {1, 1};
+    if (enc(&out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void *)a.w, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    Entry &e = cache[used < CAP ? used++ : (next = (next + 1) % CAP)];
+    e.w = a.w;
+    e.n = a.n;
+    e.k = a.k;
+    e.blk = blk;
+    e.rows = box_rows;
+    e.map = out;
+    return true;
+}
+
+struct Config {
+    int warps, tiles, stages;
+};
+// 0: eight warps of 16 rows, two stages (two CTAs fit on an SM: the launches around this one move in beside it)
+// 1: four warps of 32 rows (the activation fragments are shared by two row tiles), two stages
+// 2: four warps of 16 rows, three stages (half the tile: matrices with few rows)
+// 3: eight warps of 16 rows, four stages (one CTA per SM)
+static const Config CONFIGS[] = {{8, 1, 2}, {4, 2, 2}, {4, 1, 3}, {8, 1, 4}};
+constexpr int N_CONFIGS = 4;
+static int g_force_config = -1;
+static int g_ctas_per_sm = 0;  // 0 = choose
+
+static size_t smem_bytes(int fmt, const Config &c, uint32_t rows) {
+    const size_t rowb = fmt == FMT_Q5K ? Geo<FMT_Q5K>::ROWB : Geo<FMT_Q4K>::ROWB;
+    const size_t stage = (size_t)16 * c.tiles * c.warps * rowb + 2 * act_block_bytes(rows);
+    return BAR_BYTES + (size_t)c.stages * stage + (size_t)c.warps * 32 * c.tiles * SC_STRIDE;
+}
+
+template <int FMT, int WARPS, int TILES, int STAGES, int NG>
+static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
+    auto kern = qgemv_kq_stream_kernel<FMT, WARPS, TILES, STAGES, NG>;
+    constexpr uint32_t RT = 16 * TILES * WARPS;
+    const uint32_t M = g.item[0].rows, C = (g.item[0].k / QK + 1) / 2;
+    uint32_t tiles = 0;
+    Maps<NG> maps;
+    for (int i = 0; i < g.count; i++) {
+        tiles += (g.item[i].n + RT - 1) / RT;
+        g.task_end[i] = tiles;
+        if (!weight_map(g.item[i], Geo<FMT>::BLK, RT, maps.m[i])) return cudaErrorNotSupported;
+    }
+    for (int i = g.count; i < NG; i++) maps.m[i] = maps.m[0];
+    const size_t smem = smem_bytes(FMT, Config{WARPS, TILES, STAGES}, M);
+    static DynamicSmemOptIn opted;
+    if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
+    // One CTA per SM when the launch is part of a dependent-launch stream and a second CTA fits: the other slot
+    // belongs to the launches around this one, which stage their first weights (and, when early, compute)
+    // while this one still runs. Otherwise as many as fit.
+    const uint32_t fit = (uint32_t)((227 * 1024) / (smem + 1024));
+    uint32_t per_sm = fit >= 2 ? (pdl ? 1 : 2) : 1;
+    if (g_ctas_per_sm > 0) per_sm = (uint32_t)g_ctas_per_sm < fit ? (uint32_t)g_ctas_per_sm : (fit ? fit : 1);
+    const uint64_t U = (uint64_t)tiles * C;
+    uint32_t grid = (uint32_t)sm_count * per_sm;
+    if (grid > U) grid = (uint32_t)U;
+    // workspace: two partial tiles per CTA, one counter per (tile, warp)
+    if ((uint64_t)grid * 2 * RT * 8 > ws.partial_floats || (uint64_t)tiles * WARPS > ws.counters || !ws.partial || !ws.counter)
+        return cudaErrorNotSupported;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3((WARPS + 1) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, maps, g, ws, (uint32_t)(early ? 1 : 0));
+}
+
+template <int FMT, int WARPS, int TILES, int STAGES>
+static cudaError_t launch_cfg(GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
+    if (g.count > 1) return launch_n<FMT, WARPS, TILES, STAGES, GEMV_GROUP_MAX>(g, ws, sm_count, pdl, early, stream);
+    GemvSingle one;  // a lone launch passes a sixth of the parameter bytes
+    one.item[0] = g.item[0];
+    one.act_off[0] = 0;
+    one.act_copy[0] = 0;
+    one.count = 1;
+    one.act_bytes = 0;
+    return launch_n<FMT, WARPS, TILES, STAGES, 1>(one, ws, sm_count, pdl, early, stream);
+}
+
+static int pick_config(const GemvGroup &g, int sm_count) {
+    if (g_force_config >= 0) return g_force_config;
+    // few rows in total: the half-height tile gives twice the units to spread
+    uint64_t rows = 0;
+    for (int i = 0; i < g.count; i++) rows += g.item[i].n;
+    const uint64_t units = (rows + 127) / 128 * ((g.item[0].k / QK + 1) / 2);
+    return units < 2 * (uint64_t)sm_count ? 2 : 0;
+}
+
+template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
+    switch (pick_config(g, sm_count)) {
+        case 0: return launch_cfg<FMT, 8, 1, 2>(g, ws, sm_count, pdl, early, stream);
+        case 1: return launch_cfg<FMT, 4, 2, 2>(g, ws, sm_count, pdl, early, stream);
+        case 2: return launch_cfg<FMT, 4, 1, 3>(g, ws, sm_count, pdl, early, stream);
+        case 3: return launch_cfg<FMT, 8, 1, 4>(g, ws, sm_count, pdl, early, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace ks
+
+void qgemv_kq_stream_set_config(int index) { ks::g_force_config = index < 0 || index >= ks::N_CONFIGS ? -1 : index; }
+void qgemv_kq_stream_set_ctas_per_sm(int n) { ks::g_ctas_per_sm = n < 0 ? 0 : n; }
+
+size_t qgemv_kq_stream_ws_bytes(int sm_count, StreamWs *layout) {
+    // partial tiles: 2 CTAs per SM x 2 tiles x 128 rows x 8 outputs; counters: one per 16 weight rows of up to 4 M rows
+    const uint64_t partial_floats = (uint64_t)sm_count * 2 * 2 * 128 * 8;
+    const uint64_t counters = 1u << 18;
+    if (layout) {
+        layout->partial_floats = partial_floats;
+        layout->counters = counters;
+    }
+    return partial_floats * 4 + counters * 4;
+}
+
+bool qgemv_kq_stream_shape_ok(int fmt, uint32_t rows, uint32_t n, uint32_t k) {
+    if (fmt != FMT_Q4K && fmt != FMT_Q5K) return false;
+    if (rows < 1 || rows > 8 || k % QK != 0 || k < QK || !ks::encode_fn()) return false;
+    return (uint64_t)(n + 15) / 16 <= (1u << 18) / 2;  // counters (a grouped launch may hold several matrices: checked again at launch)
+}
+
+cudaError_t launch_qgemv_kq_stream(int fmt, GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, cudaStream_t stream) {
+    if (g.count < 1 || g.count > GEMV_GROUP_MAX) return cudaErrorInvalidValue;
+    bool early = pdl;  // every member early and no tensor-parallel push
+    for (int i = 0; i < g.count; i++) early = early && g.item[i].early != 0 && g.item[i].tp == nullptr;
+    return fmt == FMT_Q5K ? ks::launch_fmt<FMT_Q5K>(g, ws, sm_count, pdl, early, stream)
+                          : ks::launch_fmt<FMT_Q4K>(g, ws, sm_count, pdl, early, stream);
+}
+
+}  // namespace lb

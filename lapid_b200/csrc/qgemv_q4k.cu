@@ -482,21 +482,10 @@ static cudaError_t launch_fast_n(GemvGroupT<NG> &g, int sm_count, bool pdl, cuda
     const size_t smem = BAR_BYTES + (size_t)FAST_WARPS * 2 * Blk<FMT>::STAGE + g.act_bytes + (EARLY ? pend_bytes(M) : 0);
     static DynamicSmemOptIn opted;
     if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
-    // resident CTAs per SM for this shared-memory size (a handful of sizes occur: remember them)
-    static size_t occ_key[8];
-    static int occ_val[8], occ_n = 0;
-    int ctas_per_sm = 0;
-    for (int i = 0; i < occ_n; i++)
-        if (occ_key[i] == smem) ctas_per_sm = occ_val[i];
-    if (ctas_per_sm == 0) {
-        int occ = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, FAST_THREADS, smem);
-        if (e != cudaSuccess) return e;
-        ctas_per_sm = occ > 0 ? occ : 1;
-        const int slot = occ_n < 8 ? occ_n++ : 7;
-        occ_key[slot] = smem;
-        occ_val[slot] = ctas_per_sm;
-    }
+    // resident CTAs per SM for this shared-memory size (a handful of sizes occur: remembered per device)
+    static OccupancyCache occupancy;
+    int ctas_per_sm = 1;
+    if (cudaError_t e = occupancy.get(kern, FAST_THREADS, smem, &ctas_per_sm); e != cudaSuccess) return e;
     // Leave one CTA slot per SM to the next kernel of the stream: under programmatic dependent
     // launch its CTAs move in while this kernel still runs and fill their rings, so the weight
     // stream does not stop at the kernel boundary.

@@ -77,3 +77,65 @@ def from_ggml_blocks(backend, fmt: int, blocks: np.ndarray, rows: int, cols: int
     dst = backend.alloc(l.total)
     _lib.check(_lib.lib().lapid_b200_from_ggml_blocks(backend._h, int(fmt), src._h, blocks.size, rows, cols, dst._h))
     return dst.download()
+
+
+# ---- the quantized activation operand of the decode path (lapid_b200_quantize_activations / lapid_b200_act_layout)
+ACT_PLANES, ACT_RECORDS, ACT_TILES = 0, 1, 2
+_REC = 336
+
+
+def _up256(x: int) -> int:
+    return (x + 255) // 256 * 256
+
+
+def act_bytes(act_layout: int, rows: int, k: int) -> int:
+    """Bytes of ``rows`` quantized activation rows of ``k`` elements in ``act_layout``."""
+    if act_layout == ACT_PLANES:
+        return _up256(rows * k) + 2 * _up256(rows * (k // 32) * 4)
+    if act_layout == ACT_RECORDS:
+        return rows * (k // 256) * _REC
+    return (k // 256) * (256 * rows + 512)
+
+
+def quantize_activations(backend, x: np.ndarray, rows: int, k: int, act_layout: int) -> np.ndarray:
+    """The raw operand bytes for f32 ``x [rows, k]`` (``quantize_row_sums``, crates/lapid-cpu/src/matmul/quant.rs:30-89)."""
+    src = backend.upload(np.ascontiguousarray(x, dtype=np.float32).reshape(-1))
+    dst = backend.upload(np.zeros(act_bytes(act_layout, rows, k), np.uint8))
+    backend.quantize_activations(src, rows, k, act_layout, dst)
+    return dst.download()
+
+
+def unpack_activations(act_layout: int, raw: np.ndarray, rows: int, k: int):
+    """``(q int8 [rows, k], d f32 [rows, k/32], bs f32 [rows, k/32])`` from the raw bytes of an operand in
+    ``act_layout``: planes; 336-byte records, one per (row, 256-block): 4 x [64 quants | d d bs bs], 16 pad; or
+    tiles, one per 256-block: ``[sub-block 8][row][32]`` quants, then ``[row pair 4][sub-block 8][2]`` f32 d and
+    the same for bs."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    kg, nblk = k // 32, k // 256
+    q = np.zeros((rows, k), np.int8)
+    d = np.zeros((rows, kg), np.float32)
+    bs = np.zeros((rows, kg), np.float32)
+    if act_layout == ACT_PLANES:
+        p0, p1 = _up256(rows * k), _up256(rows * kg * 4)
+        q[:] = raw[:rows * k].view(np.int8).reshape(rows, k)
+        d[:] = raw[p0:p0 + rows * kg * 4].view(np.float32).reshape(rows, kg)
+        bs[:] = raw[p0 + p1:p0 + p1 + rows * kg * 4].view(np.float32).reshape(rows, kg)
+    elif act_layout == ACT_RECORDS:
+        rec = raw[:rows * nblk * _REC].reshape(rows, nblk, _REC)
+        for p in range(4):
+            part = rec[:, :, 80 * p:80 * p + 80]
+            for h in range(2):
+                g = 2 * p + h
+                q.reshape(rows, nblk, 8, 32)[:, :, g, :] = part[:, :, 32 * h:32 * h + 32].view(np.int8)
+                d.reshape(rows, nblk, 8)[:, :, g] = np.ascontiguousarray(part[:, :, 64 + 4 * h:68 + 4 * h]).view(np.float32)[:, :, 0]
+                bs.reshape(rows, nblk, 8)[:, :, g] = np.ascontiguousarray(part[:, :, 72 + 4 * h:76 + 4 * h]).view(np.float32)[:, :, 0]
+    else:
+        ab = 256 * rows + 512
+        blk = raw[:nblk * ab].reshape(nblk, ab)
+        qs = blk[:, :256 * rows].view(np.int8).reshape(nblk, 8, rows, 32)
+        q.reshape(rows, nblk, 8, 32)[:] = qs.transpose(2, 0, 1, 3)
+        sc = np.ascontiguousarray(blk[:, 256 * rows:]).view(np.float32).reshape(nblk, 2, 4, 8, 2)  # [d | bs][row pair][sub-block][row & 1]
+        for r in range(rows):
+            d.reshape(rows, nblk, 8)[r] = sc[:, 0, r >> 1, :, r & 1]
+            bs.reshape(rows, nblk, 8)[r] = sc[:, 1, r >> 1, :, r & 1]
+    return q, d, bs

@@ -285,11 +285,12 @@ class GpuTpLayers:
     """
 
     def __init__(self, backend, shape: LayerShape, world: int, rank: int, m: int, weights: list, formats: list,
-                 group=None, peer_all_reduce=None, fused: bool = False, fuse_act: bool = True):
+                 group=None, peer_all_reduce=None, fused: bool = False, fuse_act: bool = True, skip_collective: bool = False):
         import torch
         from .backend import matmul_launch
         self.be, self.shape, self.world, self.rank, self.m, self.group = backend, shape, world, rank, m, group
         self.peer = peer_all_reduce
+        self.skip_collective = skip_collective   # timing only: the exchanges are left out (the results are then wrong)
         # fused: the row-parallel GEMVs push their partials from their epilogue and the following
         # rms_norm sums them: the all-reduce has no kernel of its own
         self.fused = bool(fused and peer_all_reduce is not None and world > 1 and peer_all_reduce.fits(m * d_model_of(shape)))
@@ -360,7 +361,7 @@ class GpuTpLayers:
             self._keep.append(bufs)
 
     def all_reduce(self, name):
-        if self.world == 1:
+        if self.world == 1 or self.skip_collective:
             return
         t = self.outs[name]
         if self.peer is not None and self.peer.fits(t.numel()):
@@ -369,40 +370,57 @@ class GpuTpLayers:
             import torch.distributed as dist
             dist.all_reduce(t, group=self.group)
 
+    def _q_of(self, layout, holder):
+        """Keyword arguments that make a glue call write the quantized operand too."""
+        return {} if layout is None else {"qact": self._glue[holder], "layout": layout}
+
+    def _attention_half(self, i: int, res):
+        """q, k, v, then o and its exchange: hw = res + sum over ranks of o; x = norm(hw), quantized for gate / up."""
+        be, m, d, w = self.be, self.m, self.shape.d_model, self._glue
+        qkv, o, _, _ = self.steps[i % len(self.steps)]
+        lay_gu = self.act_layouts[i % len(self.steps)][1]
+        qkv()
+        o()
+        if self.fused:
+            self.peer.rms_norm(w["x"], m, d, residual=res, sum_out=w["hw"], **self._q_of(lay_gu, "qx"))
+        else:
+            self.all_reduce("o")
+            be.rms_norm(w["o"], w["x"], m, d, residual=res, sum_out=w["hw"], **self._q_of(lay_gu, "qx"))    # h' = h + o;    x = norm(h')
+
+    def _ffn_half(self, i: int):
+        """gate, up, SwiGLU, then down and its exchange: hw += sum over ranks of down; x = norm(hw) for the next layer."""
+        be, m, d, w = self.be, self.m, self.shape.d_model, self._glue
+        sets = len(self.steps)
+        _, _, gu, down = self.steps[i % sets]
+        lay_down = self.act_layouts[i % sets][2]
+        lay_next = self.act_layouts[(i + 1) % sets][0]
+        gu()
+        be.silu_mul(w["gate"], w["up"], w["act"], self.act.numel(), rows=m, **self._q_of(lay_down, "qact"))
+        down()
+        if self.fused:
+            self.peer.rms_norm(w["x"], m, d, residual=w["hw"], sum_out=w["hw"], **self._q_of(lay_next, "qx"))
+        else:
+            self.all_reduce("down")
+            be.rms_norm(w["down"], w["x"], m, d, residual=w["hw"], sum_out=w["hw"], **self._q_of(lay_next, "qx"))  # h'' = h' + down; x = norm(h'') for the next layer
+
     def token(self, n_layers: int):
         """Queues `n_layers` layer steps (cycling over the distinct weight sets) on the current stream.
 
         Between the projections only the library's two glue kernels run: `rms_norm` (with the
         residual add folded in) and `silu_mul`. The residual stream of the token starts from `self.h`
         (left untouched, so a captured graph replays the same token) and ends in `self.h_out`."""
-        be, m, d = self.be, self.m, self.shape.d_model
         w = self._glue
-        sets = len(self.steps)
-
-        def q_of(layout, holder):   # keyword arguments that make a glue call write the quantized operand too
-            return {} if layout is None else {"qact": w[holder], "layout": layout}
-
-        be.rms_norm(w["h"], w["x"], m, d, **q_of(self.act_layouts[0][0], "qx"))  # x = norm(h)
-        res = w["h"]
+        self.be.rms_norm(w["h"], w["x"], self.m, self.shape.d_model, **self._q_of(self.act_layouts[0][0], "qx"))  # x = norm(h)
         for i in range(n_layers):
-            qkv, o, gu, down = self.steps[i % sets]
-            lay_gu, lay_down = self.act_layouts[i % sets][1:]
-            lay_next = self.act_layouts[(i + 1) % sets][0]
-            qkv()
-            o()
-            if self.fused:
-                self.peer.rms_norm(w["x"], m, d, residual=res, sum_out=w["hw"], **q_of(lay_gu, "qx"))
-            else:
-                self.all_reduce("o")
-                be.rms_norm(w["o"], w["x"], m, d, residual=res, sum_out=w["hw"], **q_of(lay_gu, "qx"))    # h' = h + o;    x = norm(h')
-            res = w["hw"]
-            gu()
-            be.silu_mul(w["gate"], w["up"], w["act"], self.act.numel(), rows=m, **q_of(lay_down, "qact"))
-            down()
-            if self.fused:
-                self.peer.rms_norm(w["x"], m, d, residual=res, sum_out=w["hw"], **q_of(lay_next, "qx"))
-            else:
-                self.all_reduce("down")
-                be.rms_norm(w["down"], w["x"], m, d, residual=res, sum_out=w["hw"], **q_of(lay_next, "qx"))  # h'' = h' + down; x = norm(h'') for the next layer
+            self._attention_half(i, w["h"] if i == 0 else w["hw"])
+            self._ffn_half(i)
         self.h_out = self.hw
+        return self.hw
+
+    def first_row_parallel(self):
+        """Queues the first layer up to and including its first exchange and returns `h + sum over ranks of o`:
+        the first row-parallel result, whose inputs are the same however the layer is sharded."""
+        w = self._glue
+        self.be.rms_norm(w["h"], w["x"], self.m, self.shape.d_model, **self._q_of(self.act_layouts[0][0], "qx"))
+        self._attention_half(0, w["h"])
         return self.hw

@@ -625,7 +625,9 @@ void lo_quantize_row_sums(const float *x, size_t k, int8_t *q, float *s, float *
         int sum = 0;
         for (int t = 0; t < GROUP; t++) {
             float r = (xg[t] * id + 12582912.0f) - 12582912.0f; /* math.rs:134-136 */
-            int v = (r != r) ? 0 : (int)r;
+            /* Rust's `as i32` saturates and maps NaN to 0 (a C cast of an out-of-range float is undefined): a
+             * group of denormals has d > 0 but 1/d = inf, so r can be +-inf here */
+            int v = (r != r) ? 0 : r >= 2147483648.0f ? 2147483647 : r <= -2147483648.0f ? (-2147483647 - 1) : (int)r;
             v = clampi(v, -127, 127);
             q[g * GROUP + t] = (int8_t)v;
             sum += v;

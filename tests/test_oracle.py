@@ -183,10 +183,13 @@ def test_zeros_and_constants(oracle):
                 assert not b.any()  # kquant.rs:304-307 for Q6_K; scale 0 everywhere for Q4_K
 
 
-gguf = pytest.importorskip("gguf")
+def _gguf():
+    """The third-party package of the independent cross-checks; only the tests that use it skip without it."""
+    return pytest.importorskip("gguf")
 
 
 def _gguf_deq(fmt, blocks):
+    gguf = _gguf()
     from gguf import quants
     t = {Q4_K: gguf.GGMLQuantizationType.Q4_K, Q5_K: gguf.GGMLQuantizationType.Q5_K, Q6_K: gguf.GGMLQuantizationType.Q6_K,
          INT8: gguf.GGMLQuantizationType.Q8_0}[fmt]
@@ -229,6 +232,7 @@ def test_int4_planes_decode_like_q4_0_blocks(oracle):
     """GGUF block_q4_0 (f16 d + 16 nibble bytes) -> lapid Int4 planes (`from_ggml_blocks`, imp.rs:180-199):
     the oracle's dequantization of the planes equals the independent Q4_0 dequantizer on the blocks, bit for bit,
     and AoS -> SoA of the oracle's own bytes is the identity."""
+    gguf = _gguf()
     from gguf import quants
     rows, cols = 5, 256
     x = O.normal(19, rows * cols, 0.7)
@@ -245,6 +249,7 @@ def test_int4_planes_decode_like_q4_0_blocks(oracle):
 
 
 def test_int8_bytes_match_independent_q8_0_quantizer(oracle):
+    gguf = _gguf()
     from gguf import quants
     rows, cols = 5, 256
     x = O.normal(9, rows * cols, 0.7).reshape(rows, cols)

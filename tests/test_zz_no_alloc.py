@@ -52,6 +52,9 @@ def test_static_scratch_gemv_matches_execute_twice_in_a_row():
         assert _max_rel(got, ref) <= 2e-5
         want, _ = O.load().matmul(O.Q4_K, a, qb, n, k, m=rows)
         assert _max_rel(got, want) <= 2e-5
+        assert torch.cuda.current_device() == 0   # the call puts the thread's device back
+    word = C.c_int32(-1)
+    assert lib.lapid_b200_gemv_q4k_static_status(0, C.byref(word)) == 0 and word.value == 0   # no wait gave up
 
     # limits: rows * k beyond the static scratch, bad rows, bad k, short weights -- clear errors, no launch
     z = torch.zeros(16, device=dev)
