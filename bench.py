@@ -406,7 +406,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     us = times[len(times) // 2] * 1e3
                     gbs = algo_bytes(f, m, n, k) / (us * 1e-6) / 1e9
                     case_rows.append({"fmt": FMT_NAMES[f], "n": n, "k": k, "m": m, "us": round(us, 3),
-                                      "gbs": round(gbs, 1), "frac": round(gbs / peak, 4), "kernel": gemv_kernel_name(f, m)})
+                                      "gbs": round(gbs, 1), "frac": round(gbs / peak, 4), "kernel": gemv_kernel_name(f, m, n, k)})
                     del gr, rn, cb_, ls
                 del pool
                 torch.cuda.empty_cache()
@@ -487,11 +487,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     print(json.dumps(line), flush=True)
 
 
-def gemv_kernel_name(fmt: int, m: int) -> str:
+def gemv_kernel_name(fmt: int, m: int, n: int = 0, k: int = 0) -> str:
     """The kernel a decode launch of `m` rows takes with the library's default options when, as in the per-case
-    timing, its activations were quantized at the head of the launch list."""
+    timing, its activations were quantized at the head of the launch list (so it may run ahead of its predecessor)."""
+    units = -(-n // 128) * -(-(k // 256) // 2)   # 128-row x 512-k units of the balanced-stream kernel
     if fmt == 6:
-        return "qgemv_kq_stream_kernel<q4_k>" if m >= 3 else "qgemv_kq_fast_kernel<q4_k>"  # (two rows: the stream kernel when the operand is produced inside the list)
+        if m >= 3:
+            return "qgemv_kq_stream_kernel<q4_k>" if units >= 2 * 148 else "qgemv_q4k_mma_kernel"
+        return "qgemv_kq_fast_kernel<q4_k>"  # (two rows: a tensor-core kernel when the operand is produced inside the list)
     if fmt == 8:
         return "qgemv_q6k_mma_kernel" if m >= 3 else "qgemv_kq_fast_kernel<q6_k>"
     if fmt == 7:
@@ -504,7 +507,7 @@ def gemv_kernel_name(fmt: int, m: int) -> str:
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch / algorithmic bytes of that launch, from the ncu
 # captures summarised under profiles/ (weights are read once; the outputs stay in L2). A kernel without a
 # capture reports no traffic.
-DRAM_TRAFFIC_RATIO = {"qgemv_kq_fast_kernel<q4_k>": 0.9985}
+DRAM_TRAFFIC_RATIO = {"qgemv_q4k_mma_kernel": 0.985, "qgemv_kq_fast_kernel<q4_k>": 0.9985}
 
 
 def max_rel(got, ref) -> float:
@@ -542,7 +545,7 @@ def check_sweep(fmt, cases, base, acts, outs, a_off, o_off):
     for i, (m, n, k) in enumerate(cases):
         want, _ = o.matmul(fmt, acts[a_off[i]:a_off[i] + m * k], wh[(n, k)], n, k, m=m)
         mr = max_rel(outs[o_off[i]:o_off[i] + m * n], want)
-        name = gemv_kernel_name(fmt, m) if m != 2 else "two rows (kernel chosen by the launch list)"
+        name = "decode kernels for 3..8 rows" if m >= 3 else gemv_kernel_name(fmt, m, n, k) if m == 1 else "two rows (kernel chosen by the launch list)"
         by_kernel[name] = max(by_kernel.get(name, 0.0), mr)
         worst = max(worst, mr)
     return {"launches_checked": len(cases), "max_rel": worst, "by_kernel": by_kernel}

@@ -170,16 +170,18 @@ struct lapid_b200_device {
     bool gemv_fast = true;   // specialised GEMV kernels where the shape allows; off = generic kernel only
     bool gemv_group = true;  // consecutive independent K-quant decode launches of one list share a kernel
     uint32_t gemv_mma_rows = 2;  // Q4_K decode launches with at least this many rows use the int8 tensor-core kernel; 0 = never
-    bool gemv_stream = true;     // Q4_K / Q5_K tensor-core decode launches take the balanced-stream kernel (qgemv_kq_stream.cu)
+    // balanced-stream tensor-core decode kernel (qgemv_kq_stream.cu): 0 never; 1 (default) Q5_K always and Q4_K where
+    // it is the faster one (launch_qgemv_q4k_mma decides); 2 both formats always
+    int gemv_stream = 1;
     bool two_row_dp4a = true;    // two early Q4_K rows prefer the dp4a kernel (see execute_impl)
-    lb::StreamWs stream_ws{};    // workspace of that kernel: partial tiles and their counters (zero between launches)
+    lb::StreamWs stream_ws{};    // workspace of that kernel: partial sums in flight between CTAs (all zero between launches)
     bool gemm_f32 = false;  // true: rows > gemv_max_rows always take the exact-f32 GEMM instead of the tensor cores
 
     void make_current() const { cuda_check(cudaSetDevice(ordinal), "cudaSetDevice"); }
     ~lapid_b200_device() {
         if (cudaSetDevice(ordinal) == cudaSuccess) {
             if (scratch) cudaFree(scratch);
-            if (stream_ws.partial) cudaFree(stream_ws.partial);
+            if (stream_ws.pairs) cudaFree(stream_ws.pairs);
             if (status_host) cudaFreeHost(status_host);
             if (own_stream) cudaStreamDestroy(own_stream);
         }
@@ -322,7 +324,7 @@ struct PendingGroup {
         const bool pdl = dev.pdl_launch();
         if (mode == 3) cuda_check(lb::launch_qgemv_kq_stream(fmt, out, dev.stream_ws, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (mode == 2 && fmt == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(out, dev.sm_count, pdl, dev.stream), "qgemv launch");
-        else if (mode == 2) cuda_check(lb::launch_qgemv_q4k_mma(out, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        else if (mode == 2) cuda_check(lb::launch_qgemv_q4k_mma(out, dev.sm_count, pdl, dev.stream, dev.gemv_stream ? &dev.stream_ws : nullptr), "qgemv launch");
         else cuda_check(lb::launch_qgemv_kq_group(fmt, out, dev.sm_count, pdl, dev.stream), "qgemv launch");
         dev.launches++;
     }
@@ -378,8 +380,9 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
         p.fast = dev.gemv_fast && lb::qgemv_kq_fast_shape_ok(l.b_dtype, p.rows, (uint32_t)l.k);
         p.fast_i8 = dev.gemv_fast && l.b_dtype == LAPID_B200_DTYPE_INT8 && lb::qgemv_i8_fast_shape_ok(p.rows, (uint32_t)l.k);
         // (Q6_K pays more per weight for unpacking: its tensor-core kernel wins one row later than Q4_K's)
-        p.stream = dev.gemv_fast && dev.gemv_stream && dev.gemv_mma_rows > 0 &&
-                   ((l.b_dtype == LAPID_B200_DTYPE_Q4_K && p.rows >= dev.gemv_mma_rows) || (l.b_dtype == LAPID_B200_DTYPE_Q5_K && p.rows > dev.gemv_mma_rows)) &&
+        p.stream = dev.gemv_fast && dev.gemv_mma_rows > 0 &&
+                   ((dev.gemv_stream >= 2 && l.b_dtype == LAPID_B200_DTYPE_Q4_K && p.rows >= dev.gemv_mma_rows) ||
+                    (dev.gemv_stream >= 1 && l.b_dtype == LAPID_B200_DTYPE_Q5_K && p.rows > dev.gemv_mma_rows)) &&
                    lb::qgemv_kq_stream_shape_ok(l.b_dtype, p.rows, (uint32_t)l.n, (uint32_t)l.k);
         p.mma = dev.gemv_fast && dev.gemv_mma_rows > 0 &&
                 (p.stream ||
@@ -799,7 +802,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             one.item[0] = g;
             if (p.stream) cuda_check(lb::launch_qgemv_kq_stream(l.b_dtype, one, dev.stream_ws, dev.sm_count, pdl, dev.stream), "qgemv launch");
             else if (l.b_dtype == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(one, dev.sm_count, pdl, dev.stream), "qgemv launch");
-            else cuda_check(lb::launch_qgemv_q4k_mma(one, dev.sm_count, pdl, dev.stream), "qgemv launch");
+            else cuda_check(lb::launch_qgemv_q4k_mma(one, dev.sm_count, pdl, dev.stream, dev.gemv_stream ? &dev.stream_ws : nullptr), "qgemv launch");
         } else if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (l.b_dtype == LAPID_B200_DTYPE_INT4) cuda_check(lb::launch_qgemv_i4(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (p.fast_i8 && ((uintptr_t)g.w & 15) == 0) cuda_check(lb::launch_qgemv_i8_fast(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
@@ -1028,8 +1031,8 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
         if (*dev->status_host != 0) {
             int st = *dev->status_host;
             *dev->status_host = 0;
-            // a launch that gave up may have left slab counters of the decode workspace half counted
-            cudaMemsetAsync(dev->stream_ws.counter, 0, dev->stream_ws.counters * 4, dev->stream);
+            // a launch that gave up may have left partial sums in the decode workspace
+            cudaMemsetAsync(dev->stream_ws.pairs, 0, dev->stream_ws.n_pairs * 8, dev->stream);
             cudaStreamSynchronize(dev->stream);
             if (st == 128) fail("index_out_of_range", "an index of a gather or an expert id of a matmul_id is out of range; the rows it selects were not computed");
             fail("backend", "a device-side wait gave up (status " + std::to_string(st) + "); the results of this call are invalid");
@@ -1092,8 +1095,7 @@ lapid_b200_status lapid_b200_device_open(int32_t ordinal, lapid_b200_device **ou
             const size_t ws_bytes = lb::qgemv_kq_stream_ws_bytes(d->sm_count, &d->stream_ws);
             void *ws = nullptr;
             cuda_check(cudaMalloc(&ws, ws_bytes), "cudaMalloc(decode workspace)");
-            d->stream_ws.partial = (float *)ws;
-            d->stream_ws.counter = (uint32_t *)((char *)ws + d->stream_ws.partial_floats * 4);
+            d->stream_ws.pairs = (uint2 *)ws;
             cuda_check(cudaMemset(ws, 0, ws_bytes), "cudaMemset(decode workspace)");
         } catch (...) {
             delete d;
@@ -1162,11 +1164,15 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             if (r < 0 || r > 8) fail("invalid_argument", "gemv_mma_rows must be in 0..8");
             dev->gemv_mma_rows = (uint32_t)r;
         } else if (k == "gemv_stream") {
-            dev->gemv_stream = v != "0";
+            int r = std::atoi(value);
+            if (r < 0 || r > 2) fail("invalid_argument", "gemv_stream must be 0 (never), 1 (Q5_K) or 2 (Q4_K and Q5_K)");
+            dev->gemv_stream = r;
         } else if (k == "gemv_stream_config") {
             lb::qgemv_kq_stream_set_config(std::atoi(value));
         } else if (k == "gemv_stream_ctas") {
             lb::qgemv_kq_stream_set_ctas_per_sm(std::atoi(value));
+        } else if (k == "gemv_stream_debug") {
+            lb::qgemv_kq_stream_set_debug(std::atoi(value));
         } else if (k == "gemv_two_row_dp4a") {
             dev->two_row_dp4a = v != "0";
         } else if (k == "gemv_mma_config") {

@@ -180,22 +180,23 @@ cudaError_t launch_qgemv_kq_group(int fmt, GemvGroup &group, int sm_count, bool 
 bool qgemv_q4k_mma_shape_ok(uint32_t rows, uint32_t k);
 size_t qgemv_q4k_mma_act_bytes(uint32_t rows, uint32_t k);
 bool qgemv_q4k_mma_group_fits(GemvGroup &group);
-cudaError_t launch_qgemv_q4k_mma(GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream);
+struct StreamWs;
+cudaError_t launch_qgemv_q4k_mma(GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream, const StreamWs *ws = nullptr);
 void qgemv_q4k_mma_set_config(int index);  // -1 = pick by shared-memory fit
 // ---- qgemv_kq_stream.cu: Q4_K / Q5_K decode on the same instruction as one stream of equal work shares
 // (2..8 rows; any K that is a multiple of 256; same activation tiles). Spans that hold only some k-chunks
-// of a row tile meet in a workspace in global memory: `partial` (partial_floats f32) and `counter`
-// (counters u32, zero between launches); one workspace per device serves every launch of its stream.
+// of a row tile hand their partial sums over in a workspace in global memory: `pairs` ({f32 value, u32 flag},
+// all zero between launches); one workspace per device serves every launch of its stream.
 struct StreamWs {
-    float *partial;
-    uint32_t *counter;
-    uint64_t partial_floats, counters;
+    uint2 *pairs;
+    uint64_t n_pairs;
 };
-size_t qgemv_kq_stream_ws_bytes(int sm_count, StreamWs *layout);  // bytes to allocate: the partials, then the counters
+size_t qgemv_kq_stream_ws_bytes(int sm_count, StreamWs *layout);  // bytes to allocate (zero-filled)
 bool qgemv_kq_stream_shape_ok(int fmt, uint32_t rows, uint32_t n, uint32_t k);
 cudaError_t launch_qgemv_kq_stream(int fmt, GemvGroup &group, const StreamWs &ws, int sm_count, bool pdl, cudaStream_t stream);
 void qgemv_kq_stream_set_config(int index);     // tuning: -1 = choose
 void qgemv_kq_stream_set_ctas_per_sm(int n);    // tuning: 0 = choose
+void qgemv_kq_stream_set_debug(int v);          // measurement only: 2 = drop partial tiles (wrong results)
 // Int8 planes on the same instruction (K a multiple of 512); same activation tiles.
 bool qgemv_i8_mma_shape_ok(uint32_t rows, uint32_t k);
 cudaError_t launch_qgemv_i8_mma(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);

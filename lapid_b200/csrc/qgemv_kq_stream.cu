@@ -15,14 +15,18 @@
 //  * Each consumer warp owns 16*TILES rows of the tile and keeps their 16x8 accumulators in registers
 //    over all k-chunks of its span: no cross-warp reduction, no CTA-wide barrier in the main loop. A
 //    warp releases a stage with one mbarrier arrive.
-//  * A span that covers all k-chunks of a tile stores it directly. Otherwise the warp writes its partial
-//    16x8 tiles to a workspace in global memory and bumps a counter of the slab; the warp that arrives
-//    last adds the partials in span order (so the sum does not depend on who was last) and stores.
-//    Nobody waits for anybody: there is no spin on another CTA.
+//  * A span that covers all k-chunks of a tile stores it directly. Otherwise the span that holds the tile's
+//    first k-chunk adds up and stores, and the spans behind it hand it their partial 16x8 tiles through a
+//    workspace in global memory as {value, flag} pairs (one aligned 8-byte store each, never torn: no fence,
+//    no atomic). A contributor's share of such a tile is the first thing it computes and the collector's
+//    share the last thing, so the pairs are normally there when they are asked for; the collector's polls
+//    are bounded all the same. It sums in span order (= k order), so the result does not depend on timing,
+//    and clears the pairs it took. All CTAs of a launch are resident together (the grid never exceeds the
+//    CTAs the SMs hold), so a collector never polls a CTA that cannot run.
 //  * Programmatic dependent launch: weights are requested before the dependency wait; a launch whose
 //    activations are older than the kernel in front of it (GemvArgs::early) also fetches them and
-//    computes before the wait. Nothing is written, and the workspace is not touched, before the kernel
-//    in front has completed, so consecutive launches can share one workspace.
+//    computes its first tile before the wait. Nothing is written, and the workspace is not touched, before
+//    the kernel in front has completed, so consecutive launches share one workspace.
 //  * Every mbarrier wait is bounded; a wait that gives up sets the host-visible status word.
 #include <cuda.h>
 
@@ -40,6 +44,13 @@ using namespace pipe;
 
 constexpr int BAR_BYTES = 128;
 constexpr int SC_STRIDE = 80;  // decoded scales of one (row, super-block): 16 floats, padded against bank conflicts
+constexpr uint32_t PAIR_SPIN_LIMIT = 1u << 20;  // polls of a partial-sum pair before the kernel gives up
+
+__device__ __forceinline__ uint2 ld_pair(const void *p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
 
 template <int FMT> struct Geo {
     static constexpr int BLK = FMT == FMT_Q5K ? Q5K_BYTES : Q4K_BYTES;
@@ -122,7 +133,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
             };
             const uint32_t pre = nunits < (uint32_t)STAGES ? nunits : (uint32_t)STAGES;
             for (uint32_t i = 0; i < pre; i++) load_w(i, i);
-            if (!early) asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations come from the kernel in front
+            if (!(early & 1)) asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations come from the kernel in front
             for (uint32_t i = 0; i < pre; i++) load_a(i, i);
             uint32_t slot = 0, phase = 0;  // phase of `empty[slot]` the next refill waits for
             for (uint32_t i = pre; i < nunits; i++) {
@@ -151,7 +162,6 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
     uint8_t *scs = stages + (size_t)STAGES * SBYTES + (size_t)warp * (32 * TILES * SC_STRIDE);
     __shared__ TpPushCtx tp_ctx[WARPS];
     bool waited = false, healthy = true;
-    const uint32_t first_tile = u_lo / C;
     auto owner = [&](uint64_t u) -> uint32_t { return (uint32_t)(((u + 1) * G - 1) / U); };
 
     uint32_t u = u_lo, slot = 0, par = 0;
@@ -317,45 +327,61 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
             store(acc);
             continue;
         }
-        // ---- this span holds only some k-chunks of the tile: leave the partial sums in the workspace; the
-        //      warp that completes the slab adds them in span order and stores
-        const uint32_t mine_slot = gt == first_tile ? 0 : 1;  // a span has at most two partial tiles: its first and its last
-        float *mine = ws.partial + (((size_t)b * 2 + mine_slot) * WARPS + warp) * EW;
-#pragma unroll
-        for (int tl = 0; tl < TILES; tl++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) __stcg(mine + (tl * 4 + i) * 32 + lane, acc[tl][i]);
-        __threadfence();
-        __syncwarp();
-        const uint32_t b_first = owner((uint64_t)gt * C), b_last = owner((uint64_t)gt * C + C - 1);
-        const uint32_t slab = gt * WARPS + warp;
-        uint32_t old = 0;
-        if (lane == 0) old = atomicAdd(ws.counter + slab, 1u);
-        old = __shfl_sync(0xffffffffu, old, 0);
-        if (old != b_last - b_first) continue;  // not the last one
-        __threadfence();
-        if (lane == 0) ws.counter[slab] = 0;  // ready for the next launch (which starts its fix-ups after this grid has completed)
-        float v[TILES][4];
-#pragma unroll
-        for (int tl = 0; tl < TILES; tl++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) v[tl][i] = 0.0f;
-        for (uint32_t bb = b_first; bb <= b_last; bb++) {
-            if (bb == b) {
-#pragma unroll
-                for (int tl = 0; tl < TILES; tl++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) v[tl][i] += acc[tl][i];
-                continue;
-            }
-            const uint32_t their_first = (uint32_t)(U * bb / G) / C;
-            const float *src = ws.partial + (((size_t)bb * 2 + (their_first == gt ? 0 : 1)) * WARPS + warp) * EW;
+        if (early & 2) continue;  // measurement only (option gemv_stream_debug): partial tiles are dropped, the results are wrong
+        // ---- this span holds only some k-chunks of the tile. The span that holds the tile's first k-chunk adds
+        //      up and stores; the others hand it their partial sums through the workspace as {value, 1} pairs
+        //      (an aligned 8-byte store is never torn, so a pair whose flag is set carries its value: no fence,
+        //      no counter). Only the first segment of a span can lack its tile's head, so a CTA has one slot.
+        uint2 *mine = ws.pairs + ((size_t)b * WARPS + warp) * EW;
+        if (c0 != 0) {
 #pragma unroll
             for (int tl = 0; tl < TILES; tl++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) v[tl][i] += __ldcg(src + (tl * 4 + i) * 32 + lane);
+                for (int i = 0; i < 4; i++) st_pair(mine + (tl * 4 + i) * 32 + lane, acc[tl][i], 1u);
+            continue;
         }
-        store(v);
+        // The contributors are the spans right behind this one; theirs is the FIRST thing they compute, so their
+        // pairs are usually there already. Sum in span order = k order; take each pair and leave the slot empty
+        // for the next launch (which touches the workspace only after this grid has completed).
+        const uint32_t b_last = owner((uint64_t)gt * C + C - 1);
+        constexpr int NB = 4 / TILES, NE = 4 * TILES;  // contributors asked for at once (their loads are all in flight together)
+        for (uint32_t b0 = b + 1; b0 <= b_last && healthy; b0 += NB) {
+            uint2 v[NB][NE];
+            auto slot_of = [&](int j, int e) { return ws.pairs + ((size_t)(b0 + j) * WARPS + warp) * EW + e * 32 + lane; };
+#pragma unroll
+            for (int j = 0; j < NB; j++)
+#pragma unroll
+                for (int e = 0; e < NE; e++) v[j][e] = b0 + j <= b_last ? ld_pair(slot_of(j, e)) : make_uint2(0u, 1u);
+            for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT; spin++) {
+                bool all = true;
+#pragma unroll
+                for (int j = 0; j < NB; j++)
+#pragma unroll
+                    for (int e = 0; e < NE; e++) all = all && v[j][e].y != 0;
+                if (all) break;
+#pragma unroll
+                for (int j = 0; j < NB; j++)
+#pragma unroll
+                    for (int e = 0; e < NE; e++)
+                        if (v[j][e].y == 0) v[j][e] = ld_pair(slot_of(j, e));
+            }
+#pragma unroll
+            for (int j = 0; j < NB; j++)
+#pragma unroll
+                for (int e = 0; e < NE; e++) {
+                    if (v[j][e].y == 0) healthy = false;
+                    if (b0 + j <= b_last) {
+                        acc[e / 4][e % 4] += __uint_as_float(v[j][e].x);
+                        st_pair(slot_of(j, e), 0.0f, 0u);
+                    }
+                }
+        }
+        healthy = __all_sync(0xffffffffu, healthy);
+        if (!healthy) {
+            if (lane == 0 && grp.item[0].status) atomicOr(grp.item[0].status, 1);
+            continue;
+        }
+        store(acc);
     }
     if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
@@ -430,6 +456,7 @@ static const Config CONFIGS[] = {{8, 1, 2}, {4, 2, 2}, {4, 1, 3}, {8, 1, 4}};
 constexpr int N_CONFIGS = 4;
 static int g_force_config = -1;
 static int g_ctas_per_sm = 0;  // 0 = choose
+static int g_debug = 0;        // measurement only: 2 = drop the partial tiles (wrong results)
 
 static size_t smem_bytes(int fmt, const Config &c, uint32_t rows) {
     const size_t rowb = fmt == FMT_Q5K ? Geo<FMT_Q5K>::ROWB : Geo<FMT_Q4K>::ROWB;
@@ -453,18 +480,16 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count,
     const size_t smem = smem_bytes(FMT, Config{WARPS, TILES, STAGES}, M);
     static DynamicSmemOptIn opted;
     if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
-    // One CTA per SM when the launch is part of a dependent-launch stream and a second CTA fits: the other slot
-    // belongs to the launches around this one, which stage their first weights (and, when early, compute)
-    // while this one still runs. Otherwise as many as fit.
+    // As many CTAs per SM as fit, at most two (measured: a CTA slot left to the next launch of the stream costs
+    // more than it brings here). The grid never exceeds what the SMs hold at once: see the kernel's hand-over.
     const uint32_t fit = (uint32_t)((227 * 1024) / (smem + 1024));
-    uint32_t per_sm = fit >= 2 ? (pdl ? 1 : 2) : 1;
+    uint32_t per_sm = fit >= 2 ? 2 : 1;
     if (g_ctas_per_sm > 0) per_sm = (uint32_t)g_ctas_per_sm < fit ? (uint32_t)g_ctas_per_sm : (fit ? fit : 1);
     const uint64_t U = (uint64_t)tiles * C;
     uint32_t grid = (uint32_t)sm_count * per_sm;
     if (grid > U) grid = (uint32_t)U;
-    // workspace: two partial tiles per CTA, one counter per (tile, warp)
-    if ((uint64_t)grid * 2 * RT * 8 > ws.partial_floats || (uint64_t)tiles * WARPS > ws.counters || !ws.partial || !ws.counter)
-        return cudaErrorNotSupported;
+    // workspace: one partial tile (RT x 8 pairs) per CTA
+    if ((uint64_t)grid * RT * 8 > ws.n_pairs || !ws.pairs) return cudaErrorNotSupported;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3((WARPS + 1) * 32);
@@ -475,7 +500,7 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, maps, g, ws, (uint32_t)(early ? 1 : 0));
+    return cudaLaunchKernelEx(&cfg, kern, maps, g, ws, (uint32_t)((early ? 1 : 0) | (g_debug & 2)));
 }
 
 template <int FMT, int WARPS, int TILES, int STAGES>
@@ -490,13 +515,9 @@ static cudaError_t launch_cfg(GemvGroup &g, const StreamWs &ws, int sm_count, bo
     return launch_n<FMT, WARPS, TILES, STAGES, 1>(one, ws, sm_count, pdl, early, stream);
 }
 
-static int pick_config(const GemvGroup &g, int sm_count) {
-    if (g_force_config >= 0) return g_force_config;
-    // few rows in total: the half-height tile gives twice the units to spread
-    uint64_t rows = 0;
-    for (int i = 0; i < g.count; i++) rows += g.item[i].n;
-    const uint64_t units = (rows + 127) / 128 * ((g.item[0].k / QK + 1) / 2);
-    return units < 2 * (uint64_t)sm_count ? 2 : 0;
+static int pick_config(const GemvGroup &, int) {
+    // measured: four warps of 16 rows with three stages, two CTAs per SM, is the best layout on every shape tried
+    return g_force_config >= 0 ? g_force_config : 2;
 }
 
 template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
@@ -513,22 +534,18 @@ template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, const StreamWs &w
 
 void qgemv_kq_stream_set_config(int index) { ks::g_force_config = index < 0 || index >= ks::N_CONFIGS ? -1 : index; }
 void qgemv_kq_stream_set_ctas_per_sm(int n) { ks::g_ctas_per_sm = n < 0 ? 0 : n; }
+void qgemv_kq_stream_set_debug(int v) { ks::g_debug = v; }
 
 size_t qgemv_kq_stream_ws_bytes(int sm_count, StreamWs *layout) {
-    // partial tiles: 2 CTAs per SM x 2 tiles x 128 rows x 8 outputs; counters: one per 16 weight rows of up to 4 M rows
-    const uint64_t partial_floats = (uint64_t)sm_count * 2 * 2 * 128 * 8;
-    const uint64_t counters = 1u << 18;
-    if (layout) {
-        layout->partial_floats = partial_floats;
-        layout->counters = counters;
-    }
-    return partial_floats * 4 + counters * 4;
+    const uint64_t n_pairs = (uint64_t)sm_count * 4 * 128 * 8;  // up to 4 CTAs per SM of 128-row tiles (or 8 of 64-row ones)
+    if (layout) layout->n_pairs = n_pairs;
+    return n_pairs * 8;
 }
 
 bool qgemv_kq_stream_shape_ok(int fmt, uint32_t rows, uint32_t n, uint32_t k) {
+    (void)n;
     if (fmt != FMT_Q4K && fmt != FMT_Q5K) return false;
-    if (rows < 1 || rows > 8 || k % QK != 0 || k < QK || !ks::encode_fn()) return false;
-    return (uint64_t)(n + 15) / 16 <= (1u << 18) / 2;  // counters (a grouped launch may hold several matrices: checked again at launch)
+    return rows >= 1 && rows <= 8 && k % QK == 0 && k >= QK && ks::encode_fn() != nullptr;
 }
 
 cudaError_t launch_qgemv_kq_stream(int fmt, GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, cudaStream_t stream) {

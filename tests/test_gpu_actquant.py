@@ -128,7 +128,8 @@ def test_producers_write_what_the_prepass_writes(be, oracle, fmt, m):
         for a, b_, c in zip(mine, pre, want):
             assert np.array_equal(a.view(np.uint8), b_.view(np.uint8)) and np.array_equal(a.view(np.uint8), c.view(np.uint8)), producer
     qb = oracle.quantize(int(fmt), O.normal(63, n * k, 0.05), n, k)
-    pre_op = be.upload(quant.quantize_activations(be, x.reshape(m, k), m, k, layout))
+    pre_op = be.upload(np.zeros(nbytes, np.uint8))   # the size act_layout asks for (padded; the operand itself is act_bytes long)
+    be.quantize_activations(be.upload(x), m, k, layout, pre_op)
     outb = be.alloc(m * n * 4)
     be.execute([matmul_launch(fmt, m, n, k, inputs=(0, 1), output=2, a_quantized=True)], [pre_op, be.upload(qb), outb])
     want, _ = oracle.matmul(int(fmt), x, qb, n, k, m=m)
