@@ -70,6 +70,11 @@ def dequantize(backend, fmt: int, qbytes: np.ndarray, rows: int, cols: int) -> n
     return dst.download().view(np.float32).reshape(rows, cols)
 
 
+def from_ggml_blocks_into(backend, fmt: int, src, src_bytes: int, rows: int, cols: int, dst) -> None:
+    """``from_ggml_blocks`` between two device buffers: ``src_bytes`` of GGUF blocks in ``src`` -> lapid layout in ``dst``."""
+    _lib.check(_lib.lib().lapid_b200_from_ggml_blocks(backend._h, int(fmt), src._h, src_bytes, rows, cols, dst._h))
+
+
 def from_ggml_blocks(backend, fmt: int, blocks: np.ndarray, rows: int, cols: int) -> np.ndarray:
     blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
     l = layout(fmt, rows, cols)
