@@ -166,7 +166,8 @@ typedef struct lapid_b200_view3 {
 
 typedef struct lapid_b200_launch {
     int32_t kind;         /* LAPID_B200_KERNEL_MATMUL (the fields below describe it), LAPID_B200_KERNEL_GATHER or LAPID_B200_KERNEL_MATMUL_ID (see above) */
-    int32_t a_dtype;      /* MatMulSpec.a_dtype: F32 (or LAPID_B200_DTYPE_ACT_Q8, see above) */
+    int32_t a_dtype;      /* MatMulSpec.a_dtype: F32, F16 or BF16 -- half types are widened exactly to f32 as they are read, as
+                             lapid-cpu's load_contig does (crates/lapid-cpu/src/matmul/mod.rs:165-286) -- or LAPID_B200_DTYPE_ACT_Q8 (above) */
     int32_t b_dtype;      /* MatMulSpec.b_dtype: INT8 | INT4 | Q4_K | Q5_K | Q6_K */
     int32_t out_dtype;    /* MatMulSpec.out_dtype: F32 */
     int32_t b_transposed; /* must be 1 for a quantized B */

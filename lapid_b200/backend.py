@@ -118,12 +118,13 @@ class Launch:
 
 def matmul_launch(b_dtype: DType, m: int, n: int, k: int, *, batch: int = 1, a_row_stride: Optional[int] = None,
                   inputs=(0, 1), output=2, bias_input: Optional[int] = None, out: Optional[MatView] = None,
-                  a_quantized: bool = False) -> Launch:
+                  a_quantized: bool = False, a_dtype: DType = DType.F32) -> Launch:
     """The launch lapid lowers ``x.matmul_t(w)`` to: contiguous A (or padded rows), quantized
     transposed B, contiguous f32 output (the `mm` helper of kbench_tests.rs:86-107).
-    ``a_quantized``: input 0 is the quantized operand a producer wrote for this launch (``Backend.act_layout``)."""
+    ``a_quantized``: input 0 is the quantized operand a producer wrote for this launch (``Backend.act_layout``);
+    ``a_dtype``: F32, F16 or BF16 activations (widened exactly to f32 as they are read, like lapid-cpu's ``load_contig``)."""
     rs = a_row_stride if a_row_stride is not None else k
-    spec = MatMulSpec(a_dtype=DType.ACT_Q8 if a_quantized else DType.F32, b_dtype=DType(b_dtype), extra_dtypes=(DType.F32,) if bias_input is not None else (),
+    spec = MatMulSpec(a_dtype=DType.ACT_Q8 if a_quantized else DType(a_dtype), b_dtype=DType(b_dtype), extra_dtypes=(DType.F32,) if bias_input is not None else (),
                       epilogue=Epilogue.ADD if bias_input is not None else Epilogue.NONE)
     dims = MatMulDims(batch, m, n, k, a=MatView(0, m * rs, rs), b=MatView(0, 0, k), out=out or MatView.contiguous(m, n),
                       extra_views=(View(0, (0, 0, 1)),) if bias_input is not None else ())

@@ -17,8 +17,8 @@ namespace lb {
 // One 32-element group of one row, by one warp.
 __device__ __forceinline__ void quantize_group(const ActQuantArgs &p, uint32_t r, uint32_t g, int lane) {
     const uint32_t kg = p.k / GROUP;
-    const float *row = p.a + p.a_off + (uint64_t)(r / p.m) * p.a_bs + (uint64_t)(r % p.m) * p.a_rs;
-    float x = row[g * GROUP + lane];
+    const void *row = act_row(p.a, p.a_type, p.a_off, p.a_bs, p.a_rs, r, p.m);
+    float x = load_act(row, g * GROUP + lane, p.a_type);
     float amax = fabsf(x);
     if (!(amax == amax)) amax = 0.0f;  // f32::max ignores a NaN operand
 #pragma unroll

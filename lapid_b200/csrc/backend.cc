@@ -103,6 +103,10 @@ bool is_quant(int32_t dt) {
     return dt == LAPID_B200_DTYPE_INT8 || dt == LAPID_B200_DTYPE_INT4 || dt == LAPID_B200_DTYPE_Q4_K || dt == LAPID_B200_DTYPE_Q5_K ||
            dt == LAPID_B200_DTYPE_Q6_K;
 }
+bool is_act_float(int32_t dt) { return dt == LAPID_B200_DTYPE_F32 || dt == LAPID_B200_DTYPE_F16 || dt == LAPID_B200_DTYPE_BF16; }
+// ACT_F32 / ACT_F16 / ACT_BF16 of the kernels, and the element size, for a launch's a_dtype
+int act_type_of(int32_t dt) { return dt == LAPID_B200_DTYPE_F16 ? 1 : dt == LAPID_B200_DTYPE_BF16 ? 2 : 0; }
+uint64_t act_elem_size(int32_t dt) { return dt == LAPID_B200_DTYPE_F32 ? 4 : 2; }
 bool has_min_term(int32_t dt) { return dt == LAPID_B200_DTYPE_Q4_K || dt == LAPID_B200_DTYPE_Q5_K; }  // the decode tiles need d * sum(q) per activation group
 uint64_t block_elems(int32_t dt) { return (dt == LAPID_B200_DTYPE_INT8 || dt == LAPID_B200_DTYPE_INT4) ? 32 : 256; }
 uint64_t block_bytes(int32_t dt) {
@@ -160,6 +164,7 @@ struct lapid_b200_device {
     // results before its own dependency wait (GemvArgs::early).
     int after_hoist = -1;
     bool early_acts = true;  // option "early_acts"
+    uint32_t tp_spin_limit = 0;  // option "tp_spin_limit": polls before a tensor-parallel wait gives up (0 = the kernels' default)
     bool pdl_launch() {
         const bool p = pdl && after_hoist != 0;
         if (after_hoist >= 0) after_hoist++;
@@ -265,12 +270,13 @@ struct ActSlot {
     uint64_t off = 0, bs = 0, rs = 0;
     uint32_t rows = 0, m = 0, k = 0;
     int records = 0;
+    int a_type = 0;        // element type of the operand (ACT_F32 / ACT_F16 / ACT_BF16)
     size_t offset = 0;     // into the device scratch
     bool hoisted = false;  // quantized by the batched pre-pass at the head of the call
     bool done = false;
     bool same(const ActSlot &o) const {
         return ptr == o.ptr && off == o.off && bs == o.bs && rs == o.rs && rows == o.rows && m == o.m && k == o.k &&
-               records == o.records;
+               records == o.records && a_type == o.a_type;
     }
 };
 
@@ -341,8 +347,8 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
     if (l.kind != LAPID_B200_KERNEL_MATMUL) fail("unsupported", "kernel kind " + std::to_string(l.kind) + " is not MatMul");
     if (!is_quant(l.b_dtype))
         fail("unsupported_dtype", "b200 matmul: b dtype " + std::to_string(l.b_dtype) + " (want int8, int4, q4_k, q5_k or q6_k)");
-    if ((l.a_dtype != LAPID_B200_DTYPE_F32 && l.a_dtype != LAPID_B200_DTYPE_ACT_Q8) || l.out_dtype != LAPID_B200_DTYPE_F32)
-        fail("unsupported_dtype", "b200 matmul: a and out must be f32");
+    if ((!is_act_float(l.a_dtype) && l.a_dtype != LAPID_B200_DTYPE_ACT_Q8) || l.out_dtype != LAPID_B200_DTYPE_F32)
+        fail("unsupported_dtype", "b200 matmul: a must be f32, f16 or bf16 and out f32");
     if (l.epilogue != LAPID_B200_EPILOGUE_NONE && l.epilogue != LAPID_B200_EPILOGUE_ADD)
         fail("unsupported", "b200 matmul: epilogue " + std::to_string(l.epilogue));
     int want_inputs = l.epilogue == LAPID_B200_EPILOGUE_ADD ? 3 : 2;
@@ -675,9 +681,9 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         fail("out_of_bounds", "b200 matmul: output holds " + std::to_string(out_elems) + " < " + std::to_string(last) + " elements");
     if (l.k > 0 && l.a_dtype != LAPID_B200_DTYPE_ACT_Q8) {
         uint64_t alast = l.a.offset + (l.batch - 1) * l.a.batch_stride + (l.m - 1) * l.a.row_stride + l.k;
-        if (ins[0]->bytes / 4 < alast)
+        if (ins[0]->bytes / act_elem_size(l.a_dtype) < alast)
             fail("out_of_bounds", "b200 matmul a: view reaches element " + std::to_string(alast) + ", buffer holds " +
-                                      std::to_string(ins[0]->bytes / 4));
+                                      std::to_string(ins[0]->bytes / act_elem_size(l.a_dtype)));
     }
     const float *extra = nullptr;
     if (l.epilogue == LAPID_B200_EPILOGUE_ADD) {
@@ -742,7 +748,8 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         }
         size_t qa_b = align_up((uint64_t)p.rows * l.k, 256), sc_b = align_up((uint64_t)p.rows * (l.k / 32) * 4, 256);
         lb::ActQuantArgs q{};
-        q.a = (const float *)ins[0]->ptr;
+        q.a = ins[0]->ptr;
+        q.a_type = act_type_of(l.a_dtype);
         q.a_off = l.a.offset;
         q.a_bs = l.a.batch_stride;
         q.a_rs = l.a.row_stride;
@@ -759,7 +766,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         g.qa = q.qa;
         g.da = q.da;
         g.bs = has_min_term(l.b_dtype) ? q.bs : nullptr;
-        g.a = l.a_dtype == LAPID_B200_DTYPE_ACT_Q8 ? nullptr : q.a;
+        g.a = l.a_dtype == LAPID_B200_DTYPE_F32 ? (const float *)q.a : nullptr;
         g.a_off = q.a_off;
         g.a_bs = q.a_bs;
         g.a_rs = q.a_rs;
@@ -813,7 +820,8 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
     if (p.tc) {
         lb::GemmTcArgs t{};
         t.w = (const uint8_t *)ins[1]->ptr;
-        t.a = (const float *)ins[0]->ptr;
+        t.a = ins[0]->ptr;
+        t.a_type = act_type_of(l.a_dtype);
         t.a_off = l.a.offset;
         t.a_bs = l.a.batch_stride;
         t.a_rs = l.a.row_stride;
@@ -844,7 +852,8 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
     lb::GemmF32Args f{};
     f.w = (const uint8_t *)ins[1]->ptr;
     f.scales_offset = p.wl.scales_offset;
-    f.a = (const float *)ins[0]->ptr;
+    f.a = ins[0]->ptr;
+    f.a_type = act_type_of(l.a_dtype);
     f.a_off = l.a.offset;
     f.a_bs = l.a.batch_stride;
     f.a_rs = l.a.row_stride;
@@ -863,6 +872,19 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
     f.k = g.k;
     cuda_check(lb::launch_qgemm_f32(l.b_dtype, f, dev.stream), "qgemm_f32 launch");
     dev.launches++;
+}
+
+// After a wait on the device's stream: a kernel whose bounded wait gave up (or that met a bad index) said so in the
+// host-visible status word; the call that notices fails, clears the word and leaves the device usable.
+void check_status_word(lapid_b200_device *dev) {
+    if (*dev->status_host == 0) return;
+    int st = *dev->status_host;
+    *dev->status_host = 0;
+    // a launch that gave up may have left partial sums in the decode workspace
+    cudaMemsetAsync(dev->stream_ws.pairs, 0, dev->stream_ws.n_pairs * 8, dev->stream);
+    cudaStreamSynchronize(dev->stream);
+    if (st == 128) fail("index_out_of_range", "an index of a gather or an expert id of a matmul_id is out of range; the rows it selects were not computed");
+    fail("backend", "a device-side wait gave up (status " + std::to_string(st) + "); the results of this call are invalid");
 }
 
 void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n, lapid_b200_buffer *const *buffers,
@@ -926,6 +948,7 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
                 key.m = (uint32_t)l.m;
                 key.k = (uint32_t)l.k;
                 key.records = p.records();
+                key.a_type = act_type_of(l.a_dtype);
                 bool clean = true;  // nothing in the list so far wrote the buffer A lives in
                 for (const Range &w : written)
                     if ((const char *)ab->ptr < w.hi && w.lo < (const char *)ab->ptr + ab->bytes) clean = false;
@@ -998,7 +1021,8 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
             size_t qa_b = align_up((uint64_t)sl.rows * sl.k, 256), sc_b = align_up((uint64_t)sl.rows * (sl.k / 32) * 4, 256);
             lb::ActQuantArgs &q = batch.item[batch.count];
             q = lb::ActQuantArgs{};
-            q.a = (const float *)sl.ptr;
+            q.a = sl.ptr;
+            q.a_type = sl.a_type;
             q.a_off = sl.off;
             q.a_bs = sl.bs;
             q.a_rs = sl.rs;
@@ -1028,15 +1052,7 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
     pend.flush(*dev);
     if (wait) {
         cuda_check(cudaStreamSynchronize(dev->stream), "cudaStreamSynchronize");
-        if (*dev->status_host != 0) {
-            int st = *dev->status_host;
-            *dev->status_host = 0;
-            // a launch that gave up may have left partial sums in the decode workspace
-            cudaMemsetAsync(dev->stream_ws.pairs, 0, dev->stream_ws.n_pairs * 8, dev->stream);
-            cudaStreamSynchronize(dev->stream);
-            if (st == 128) fail("index_out_of_range", "an index of a gather or an expert id of a matmul_id is out of range; the rows it selects were not computed");
-            fail("backend", "a device-side wait gave up (status " + std::to_string(st) + "); the results of this call are invalid");
-        }
+        check_status_word(dev);
     }
 }
 
@@ -1134,6 +1150,7 @@ lapid_b200_status lapid_b200_device_synchronize(lapid_b200_device *dev) {
         std::lock_guard<std::mutex> lock(dev->mu);
         dev->make_current();
         cuda_check(cudaStreamSynchronize(dev->stream), "cudaStreamSynchronize");
+        check_status_word(dev);
     });
 }
 
@@ -1147,6 +1164,10 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             dev->pdl = v != "0";
         } else if (k == "early_acts") {
             dev->early_acts = v != "0";
+        } else if (k == "tp_spin_limit") {
+            long r = std::atol(value);
+            if (r < 0 || r > (1l << 30)) fail("invalid_argument", "tp_spin_limit must be in 0..2^30 (0 = the default)");
+            dev->tp_spin_limit = (uint32_t)r;
         } else if (k == "gemv_max_rows") {
             int r = std::atoi(value);
             if (r < 0 || r > 8) fail("invalid_argument", "gemv_max_rows must be in 0..8");
@@ -1453,6 +1474,7 @@ lapid_b200_status lapid_b200_tp_all_reduce(lapid_b200_tp_comm *comm, lapid_b200_
         lb::TpAllReduceArgs a = comm->args;
         a.data = (float *)data->ptr + offset;
         a.count = count;
+        a.spin_limit = dev->tp_spin_limit;
         cuda_check(lb::launch_tp_all_reduce(a, dev->pdl, dev->stream), "tp all-reduce launch");
         dev->launches++;
     });
@@ -1522,6 +1544,7 @@ lapid_b200_status lapid_b200_tp_rms_norm_act(lapid_b200_tp_comm *comm, lapid_b20
         lb::RmsNormArgs a{};
         a.tp = (const lb::TpPushTable *)comm->args.peer[comm->args.rank];
         a.status = dev->status_dev;
+        a.spin_limit = dev->tp_spin_limit;
         a.residual = residual ? (const float *)residual->ptr : nullptr;
         a.weight = weight ? (const float *)weight->ptr : nullptr;
         a.sum_out = sum_out ? (float *)sum_out->ptr : nullptr;
@@ -1622,7 +1645,7 @@ lapid_b200_status lapid_b200_quantize_activations(lapid_b200_device *dev, const 
         dev->make_current();
         const lb::ActOut o = act_out_at(qact->ptr, layout, (uint32_t)rows, (uint32_t)k);
         lb::ActQuantArgs q{};
-        q.a = (const float *)a->ptr;
+        q.a = a->ptr;
         q.a_bs = rows * k;
         q.a_rs = k;
         q.rows = (uint32_t)rows;

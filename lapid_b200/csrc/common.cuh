@@ -32,6 +32,21 @@ __device__ __forceinline__ float half_bits_to_float(uint32_t h) {
     return __half2float(__ushort_as_half((unsigned short)h));
 }
 
+// Activation element types of a launch (MatMulSpec.a_dtype): lapid-cpu widens f16 / bf16 rows to f32 before anything
+// else happens to them (`load_contig`, crates/lapid-cpu/src/matmul/mod.rs:165-286); both widenings are exact.
+constexpr int ACT_F32 = 0, ACT_F16 = 1, ACT_BF16 = 2;
+__host__ __device__ constexpr uint32_t act_elem_bytes(int a_type) { return a_type == ACT_F32 ? 4u : 2u; }
+// Element i of the row that starts at `row`.
+__device__ __forceinline__ float load_act(const void *row, uint64_t i, int a_type) {
+    if (a_type == ACT_F32) return ((const float *)row)[i];
+    const unsigned short h = ((const unsigned short *)row)[i];
+    return a_type == ACT_F16 ? __half2float(__ushort_as_half(h)) : __uint_as_float((uint32_t)h << 16);
+}
+// Start of row r = bt*m + i of an activation operand: base + (off + bt*bs + i*rs) elements.
+__device__ __forceinline__ const void *act_row(const void *base, int a_type, uint64_t off, uint64_t bs, uint64_t rs, uint32_t r, uint32_t m) {
+    return (const char *)base + (off + (uint64_t)(r / m) * bs + (uint64_t)(r % m) * rs) * act_elem_bytes(a_type);
+}
+
 // ggml's nearest_int (crates/lapid-quant/src/kquant.rs:25-28): round half to even through the
 // 1.5 * 2^23 offset, valid for |x| <= 4194303.
 __device__ __forceinline__ int nearest_int(float f) {

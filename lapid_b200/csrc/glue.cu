@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(GLUE_THREADS) rms_norm_kernel(RmsNormArgs p) {
                     const uint8_t *src = slots + (size_t)q * slot_bytes + (size_t)c * 32;
                     uint4 lo = ld_pairs(src), hi = ld_pairs(src + 16);
                     for (uint32_t spin = 0; ok && (lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch); spin++) {
-                        if (spin >= TP_SPIN_LIMIT) {
+                        if (spin >= (p.spin_limit ? p.spin_limit : TP_SPIN_LIMIT)) {
                             ok = false;
                             break;
                         }

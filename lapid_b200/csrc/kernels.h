@@ -27,7 +27,8 @@ cudaError_t launch_quantize(int fmt, const float *src, uint64_t rows, uint64_t c
 // qa: [rows][k] int8; da: [rows][k/32] f32 group scales; bs: [rows][k/32] f32 = da * sum(q)
 // (written only when bs != nullptr, i.e. for Q4_K weights).
 struct ActQuantArgs {
-    const float *a;
+    const void *a;          // f32, f16 or bf16 rows (a_type: ACT_F32 / ACT_F16 / ACT_BF16 of common.cuh), strides in elements
+    int a_type;
     uint64_t a_off, a_bs, a_rs;
     uint32_t rows, m, k;
     int8_t *qa;
@@ -224,7 +225,8 @@ cudaError_t launch_fill_zero_k(const GemvArgs &args, cudaStream_t stream);
 struct GemmF32Args {
     const uint8_t *w;
     uint64_t scales_offset;
-    const float *a;
+    const void *a;          // f32, f16 or bf16 rows (a_type), widened exactly to f32 as they are read
+    int a_type;
     uint64_t a_off, a_bs, a_rs;
     float *out;
     uint64_t out_off, out_bs, out_rs;
@@ -243,7 +245,8 @@ cudaError_t launch_qgemm_f32(int fmt, const GemmF32Args &args, cudaStream_t stre
 // ---- qgemm_tc.cu: tcgen05 tensor-core GEMM (Q4_K weights, bf16 operands, f32 accumulation)
 struct GemmTcArgs {
     const uint8_t *w;
-    const float *a;
+    const void *a;          // f32, f16 or bf16 rows (a_type); the kernel multiplies their bf16 roundings
+    int a_type;
     uint64_t a_off, a_bs, a_rs;
     float *out;
     uint64_t out_off, out_bs, out_rs;
@@ -289,6 +292,7 @@ cudaError_t launch_moe_gather_bf16(const float *x, const MoeRouteArgs &route, ui
 struct RmsNormArgs {
     const TpPushTable *tp;  // not nullptr: x is the sum over ranks of what they pushed for the current call (x is ignored)
     int *status;
+    uint32_t spin_limit;    // tp: polls of a peer's pair before the kernel gives up and sets status bit 64 (0 = the default)
     const float *x;         // [rows, cols]
     const float *residual;  // [rows, cols] added to x first, or nullptr
     const float *weight;    // [cols], or nullptr for a weight-less normalise
@@ -313,6 +317,7 @@ struct TpAllReduceArgs {
     float *data;               // local partial, replaced by the sum
     uint64_t count;            // multiple of 4, <= max_elems
     int *status;
+    uint32_t spin_limit;       // polls of a peer's pair before the kernel gives up and sets status bit 64 (0 = the default)
     int push_only;             // 1: publish `data` to every rank's slots and return; the reader (tp rms_norm) sums and closes the call
 };
 size_t tp_comm_bytes(int world, uint64_t max_elems);

@@ -94,19 +94,19 @@ template <int FMT> __global__ void __launch_bounds__(256) qgemm_f32_kernel(GemmF
 
     const int lr = tid >> 2, part = tid & 3;  // loader role: tile row / weight row, 8-element part
     const uint32_t arow = row0 + lr;
-    const float *aptr = nullptr;
+    const void *aptr = nullptr;
     if (p.tile_expert) {
         const int32_t pair = p.row_pair[arow];
-        if (pair >= 0) aptr = p.a + p.a_off + (uint64_t)((uint32_t)pair / p.id_r) * p.a_rs;
+        if (pair >= 0) aptr = (const char *)p.a + (p.a_off + (uint64_t)((uint32_t)pair / p.id_r) * p.a_rs) * act_elem_bytes(p.a_type);
     } else if (arow < p.rows) {
-        aptr = p.a + p.a_off + (uint64_t)(arow / p.m) * p.a_bs + (uint64_t)(arow % p.m) * p.a_rs;
+        aptr = act_row(p.a, p.a_type, p.a_off, p.a_bs, p.a_rs, arow, p.m);
     }
     const uint32_t wrow = col0 + lr;
 
     for (uint32_t k0 = 0; k0 < p.k; k0 += BK) {
         float av[8], wv[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) av[i] = aptr ? aptr[k0 + part * 8 + i] : 0.0f;
+        for (int i = 0; i < 8; i++) av[i] = aptr ? load_act(aptr, k0 + part * 8 + i, p.a_type) : 0.0f;
         if (wrow < p.n) {
             dequant8<FMT>(p, wrow, k0 + part * 8, wv);
         } else {

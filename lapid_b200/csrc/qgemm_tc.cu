@@ -607,7 +607,8 @@ __global__ void __launch_bounds__(256) splitk_sum_kernel(GemmTcArgs p, uint32_t 
 // VEC: the rows are 16-byte aligned, so the loads are 128-bit.
 template <bool VEC> __global__ void __launch_bounds__(256) a_to_bf16_kernel(GemmTcArgs p, __nv_bfloat16 *dst) {
   for (uint32_t r = blockIdx.y; r < p.rows; r += gridDim.y) {
-    const float *src = p.a + p.a_off + (uint64_t)(r / p.m) * p.a_bs + (uint64_t)(r % p.m) * p.a_rs;
+    const void *srow = act_row(p.a, p.a_type, p.a_off, p.a_bs, p.a_rs, r, p.m);
+    const float *src = (const float *)srow;  // (VEC: f32 rows only)
     uint4 *out = (uint4 *)(dst + (size_t)r * p.k);
     for (uint32_t c8 = blockIdx.x * blockDim.x + threadIdx.x; c8 < p.k / 8; c8 += gridDim.x * blockDim.x) {
         float v[8];
@@ -616,7 +617,7 @@ template <bool VEC> __global__ void __launch_bounds__(256) a_to_bf16_kernel(Gemm
             v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w, v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
         } else {
 #pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = src[8 * c8 + i];
+            for (int i = 0; i < 8; i++) v[i] = load_act(srow, 8 * c8 + i, p.a_type);
         }
         __nv_bfloat162 o[4];
 #pragma unroll
@@ -770,7 +771,7 @@ cudaError_t launch_qgemm_tc(int fmt, const GemmTcArgs &a, void *a_bf16_scratch, 
 
     {
         const dim3 cgrid((a.k / 8 + 255) / 256, a.rows < 65535u ? a.rows : 65535u);
-        const bool vec = ((uintptr_t)a.a & 15) == 0 && a.a_off % 4 == 0 && a.a_bs % 4 == 0 && a.a_rs % 4 == 0;
+        const bool vec = a.a_type == ACT_F32 && ((uintptr_t)a.a & 15) == 0 && a.a_off % 4 == 0 && a.a_bs % 4 == 0 && a.a_rs % 4 == 0;
         if (vec) a_to_bf16_kernel<true><<<cgrid, 256, 0, stream>>>(a, (__nv_bfloat16 *)a_bf16_scratch);
         else a_to_bf16_kernel<false><<<cgrid, 256, 0, stream>>>(a, (__nv_bfloat16 *)a_bf16_scratch);
     }

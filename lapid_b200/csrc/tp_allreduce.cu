@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(256) tp_all_reduce_kernel(TpAllReduceArgs a) {
     if (a.push_only) return;  // the reader closes the call (bumps the epoch)
     // ---- poll and reduce in rank order
     bool ok = true;
+    const uint32_t limit = a.spin_limit ? a.spin_limit : TP_SPIN_LIMIT;
     const uint8_t *base = mine + TP_HEADER + (size_t)parity * a.world * slot_bytes;
     for (uint32_t i = first; i < n2; i += stride) {
         float2 acc = make_float2(0.0f, 0.0f);
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(256) tp_all_reduce_kernel(TpAllReduceArgs a) {
             const uint8_t *src = base + (size_t)q * slot_bytes + (size_t)i * 16;
             uint4 v = ld_pairs(src);
             for (uint32_t spin = 0; ok && (v.y != epoch || v.w != epoch); spin++) {
-                if (spin >= TP_SPIN_LIMIT) {
+                if (spin >= limit) {
                     ok = false;
                     break;
                 }

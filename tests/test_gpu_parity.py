@@ -370,6 +370,48 @@ def test_config1_full_size_matvec(be, oracle, fmt, name):
     assert max_rel(got, want) <= 2e-5
 
 
+def _as_half(x, kind):
+    """f32 -> (bytes to upload, the f32 values those bytes widen to) for f16 / bf16 activations."""
+    if kind == lp.DType.F16:
+        h = x.astype(np.float16)
+        return h.view(np.uint8), h.astype(np.float32)
+    bits = x.astype(np.float32).view(np.uint32)
+    b16 = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)   # round to nearest even
+    return b16.view(np.uint8), (b16.astype(np.uint32) << 16).view(np.float32)
+
+
+@pytest.mark.parametrize("kind", [lp.DType.F16, lp.DType.BF16])
+@pytest.mark.parametrize("fmt,name", [(lp.DType.Q4K, "q4_k"), (lp.DType.Q5K, "q5_k"), (lp.DType.Q6K, "q6_k"), (lp.DType.Int8, "int8")])
+def test_half_precision_activations(be, oracle, fmt, name, kind):
+    """a_dtype F16 / BF16 (lapid-cpu's `load_contig`, crates/lapid-cpu/src/matmul/mod.rs:165-286): the rows are widened
+    exactly to f32 and then take the f32 path -- the decode kernels (dp4a and tensor-core), the exact f32 GEMM (bit
+    for bit) and the tensor-core GEMM, with a padded row stride and a bias."""
+    n, k, pad = 200, 1024, 8
+    qb = oracle.quantize(int(fmt), O.normal(1400, n * k, 0.05), n, k)
+    bias = O.normal(1401, n)
+    for m in (1, 4, 8, 40):
+        raw, wide = _as_half(O.normal(1410 + m, m * (k + pad)), kind)
+        want, path = oracle.matmul(int(fmt), wide, qb, n, k, m=m, a_view=(0, 0, k + pad), bias=bias, fma=True)
+        bufs = [be.upload(raw), be.upload(qb), be.alloc(m * n * 4), be.upload(bias)]
+        l = matmul_launch(fmt, m, n, k, a_row_stride=k + pad, bias_input=3, a_dtype=kind)
+        if m <= 8:
+            be.execute([l], bufs)
+            assert max_rel(bufs[2].download().view(np.float32), want) <= 2e-5, (name, m)
+        else:
+            be.set_option("gemm", "f32")
+            try:
+                be.execute([l], bufs)
+            finally:
+                be.set_option("gemm", "tc")
+            assert np.array_equal(bufs[2].download().view(np.uint32), want.view(np.uint32)), (name, m)
+            be.execute([l], bufs)
+            got = bufs[2].download().view(np.float32)
+            assert rel_l2(got, want) <= 4e-3 and max_rel(got, want) <= 2e-2
+    with pytest.raises(lp.LapidError) as e:   # the view is checked in elements of the operand's own type
+        be.execute([matmul_launch(fmt, 8, n, k, a_dtype=kind)], [be.alloc(8 * k * 2 - 2), bufs[1], bufs[2]])
+    assert e.value.code == "out_of_bounds"
+
+
 def test_gemv_special_activations(be, oracle):
     n, k = 64, 512
     qb = oracle.quantize(O.Q4_K, O.normal(5, n * k, 0.02), n, k)
@@ -982,3 +1024,42 @@ def test_grouped_decode_launches(be, oracle, fmt, ofmt, m):
     h3, _ = oracle.matmul(ofmt, res["1"][1][1], wd, k, k, m=m)
     assert max_rel(res["1"][1][1], h2) <= 1e-3   # second hop: int8 rounding of a slightly different input
     assert max_rel(res["1"][1][2], h3) <= 2e-5
+
+
+def test_a_device_side_wait_that_runs_out_is_reported(be, oracle):
+    """Failure detection without a GPU fault: a tensor-parallel all-reduce whose second "rank" never writes (its
+    buffer is a local one nobody touches) polls with a short limit (option tp_spin_limit), gives up, returns, and
+    records that in the host-visible status word. The next waiting call fails with "backend" and clears the word;
+    the device, the comm buffers and later launches work as before."""
+    import ctypes as C
+    from lapid_b200 import _lib
+    lib = _lib.lib()
+    world, max_elems, count = 2, 1024, 256
+    nbytes = int(lib.lapid_b200_tp_comm_bytes(world, max_elems))
+    mine, silent = be.upload(np.zeros(nbytes, np.uint8)), be.upload(np.zeros(nbytes, np.uint8))
+    ptrs = (C.c_void_p * world)(mine.device_ptr, silent.device_ptr)
+    comm = C.c_void_p()
+    _lib.check(lib.lapid_b200_tp_comm_create(be._h, 0, world, ptrs, max_elems, C.byref(comm)))
+    data = be.upload(np.ones(count, np.float32))
+    be.set_option("tp_spin_limit", "2000")
+    try:
+        _lib.check(lib.lapid_b200_tp_all_reduce(comm, data._h, 0, count))     # queued; the kernel gives up after 2000 polls
+        with pytest.raises(lp.LapidError) as e:
+            be.synchronize()
+        assert e.value.code == "backend" and "gave up" in e.value.message
+        be.synchronize()                                                        # the word was cleared: the device is usable
+        # the same through execute: the all-reduce in front of a launch list poisons that list's wait
+        _lib.check(lib.lapid_b200_tp_all_reduce(comm, data._h, 0, count))
+        n, k = 64, 512
+        qb = oracle.quantize(O.Q4_K, O.normal(1500, n * k, 0.05), n, k)
+        x = O.normal(1501, k)
+        bufs = [be.upload(x), be.upload(qb), be.alloc(n * 4)]
+        with pytest.raises(lp.LapidError) as e:
+            be.execute([matmul_launch(lp.DType.Q4K, 1, n, k)], bufs)
+        assert e.value.code == "backend"
+        be.execute([matmul_launch(lp.DType.Q4K, 1, n, k)], bufs)               # and the next one works
+        want, _ = oracle.matmul(O.Q4_K, x, qb, n, k, m=1)
+        assert max_rel(bufs[2].download().view(np.float32), want) <= 2e-5
+    finally:
+        be.set_option("tp_spin_limit", "0")
+        lib.lapid_b200_tp_comm_free(comm)
