@@ -29,6 +29,7 @@ class DType(enum.IntEnum):
     Q4K = 6
     Q5K = 7
     Q6K = 8
+    MXFP4 = 9
     ACT_Q8 = 100  # not a lapid dtype: an activation operand quantized by its producer (LAPID_B200_DTYPE_ACT_Q8)
 
 

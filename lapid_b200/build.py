@@ -28,6 +28,7 @@ SOURCES = {
     "qgemv_q6k_mma.cu": [],
     "qgemv_i8.cu": [],
     "qgemv_i4.cu": [],
+    "qgemv_mxfp4.cu": [],
     "qgemv_i8_mma.cu": [],
     "qgemm_f32.cu": [],
     "qgemm_tc.cu": [],

@@ -13,12 +13,14 @@ constexpr int FMT_INT4 = 5;  // nibble planes: byte j of a 32-group holds elemen
 constexpr int FMT_Q4K = 6;
 constexpr int FMT_Q5K = 7;
 constexpr int FMT_Q6K = 8;
+constexpr int FMT_MXFP4 = 9;  // ggml block_mxfp4: 32 elements in 17 bytes, e8m0 scale + e2m1 nibbles (byte j: element j low, j + 16 high)
 
 constexpr int GROUP = 32;
 constexpr int QK = 256;
 constexpr int Q4K_BYTES = 144;
 constexpr int Q5K_BYTES = 176;  // Q4_K's header, then the fifth bits qh[32], then the nibbles qs[128]
 constexpr int Q6K_BYTES = 210;
+constexpr int MXFP4_BYTES = 17;
 
 // Separately rounded IEEE operations. nvcc fuses a*b+c into an FMA unless told otherwise; the
 // reference never does ("do not simplify the arithmetic", crates/lapid-quant/src/kquant.rs:3-4),
@@ -45,6 +47,19 @@ __device__ __forceinline__ float load_act(const void *row, uint64_t i, int a_typ
 // Start of row r = bt*m + i of an activation operand: base + (off + bt*bs + i*rs) elements.
 __device__ __forceinline__ const void *act_row(const void *base, int a_type, uint64_t off, uint64_t bs, uint64_t rs, uint32_t r, uint32_t m) {
     return (const char *)base + (off + (uint64_t)(r / m) * bs + (uint64_t)(r % m) * rs) * act_elem_bytes(a_type);
+}
+
+// MXFP4 (crates/lapid-quant/src/mxfp4.rs:14-25): x = KV[nibble] * d, KV = the doubled e2m1 values
+// {0,1,2,3,4,6,8,12} and their negatives, d = 2^(e - 128) (a denormal for e < 2).
+__device__ __forceinline__ int mxfp4_kv(uint32_t nib) {
+    const uint32_t mag = (uint32_t)((0x0C08060403020100ull >> (8 * (nib & 7))) & 0xff);
+    return (nib & 8) ? -(int)mag : (int)mag;
+}
+__device__ __forceinline__ float e8m0_half(uint32_t e) { return __uint_as_float(e < 2 ? 0x00200000u << e : (e - 1) << 23); }
+// element `e` (0..31) of the block at `b`
+__device__ __forceinline__ float mxfp4_element(const uint8_t *b, uint32_t e) {
+    const uint32_t q = b[1 + (e & 15)];
+    return xmul((float)mxfp4_kv(e < 16 ? q & 15 : q >> 4), e8m0_half(b[0]));
 }
 
 // ggml's nearest_int (crates/lapid-quant/src/kquant.rs:25-28): round half to even through the

@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t *__restrict__
         if (FMT == FMT_Q4K) v = q4k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q4K_BYTES, (int)(c % QK));
         else if (FMT == FMT_Q5K) v = q5k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q5K_BYTES, (int)(c % QK));
         else if (FMT == FMT_Q6K) v = q6k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q6K_BYTES, (int)(c % QK));
+        else if (FMT == FMT_MXFP4) v = mxfp4_element(table + (((uint64_t)r * cols + c) >> 5) * MXFP4_BYTES, (uint32_t)(c & 31));
         else if (FMT == FMT_INT4) {
             const uint64_t pos = (uint64_t)r * cols + c, g = pos >> 5;
             const uint32_t e = (uint32_t)(pos & 31);
@@ -115,6 +116,12 @@ __global__ void __launch_bounds__(256) dequant_int4_kernel(const uint8_t *__rest
                                                            float *__restrict__ dst, uint64_t n_elems) {
     uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_elems; i += stride) dst[i] = int4_element(qs, scales, i);
+}
+
+__global__ void __launch_bounds__(256) dequant_mxfp4_kernel(const uint8_t *__restrict__ src, float *__restrict__ dst, uint64_t n_elems) {
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_elems; i += stride)
+        dst[i] = mxfp4_element(src + (i >> 5) * MXFP4_BYTES, (uint32_t)(i & 31));
 }
 
 // GGUF block_q4_0 (f16 d + 16 nibble bytes, 18 bytes) -> nibble plane + scales plane: the same nibble order.
@@ -171,6 +178,8 @@ cudaError_t launch_dequantize(int fmt, const void *src, uint64_t rows, uint64_t 
         dequant_q5k_kernel<<<grid_for(n / QK, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n / QK);
     } else if (fmt == FMT_Q6K) {
         dequant_q6k_kernel<<<grid_for(n / QK, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n / QK);
+    } else if (fmt == FMT_MXFP4) {
+        dequant_mxfp4_kernel<<<grid_for((n + 255) / 256, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n);
     } else if (fmt == FMT_INT4) {
         const uint8_t *p = (const uint8_t *)src;
         dequant_int4_kernel<<<grid_for((n + 255) / 256, sm_count), 256, 0, stream>>>(p, (const uint16_t *)(p + scales_offset), dst, n);
@@ -193,6 +202,7 @@ cudaError_t launch_gather(int fmt, const void *table, uint64_t scales_offset, co
     else if (fmt == FMT_Q6K) gather_kernel<FMT_Q6K><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
     else if (fmt == FMT_INT8) gather_kernel<FMT_INT8><<<grid, 256, 0, stream>>>(t, scales_offset, ids, rows, cols, count, out, status);
     else if (fmt == FMT_INT4) gather_kernel<FMT_INT4><<<grid, 256, 0, stream>>>(t, scales_offset, ids, rows, cols, count, out, status);
+    else if (fmt == FMT_MXFP4) gather_kernel<FMT_MXFP4><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
     else gather_kernel<-1><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
     return cudaGetLastError();
 }

@@ -107,6 +107,8 @@ cudaError_t launch_qgemv(int fmt, const GemvArgs &args, int sm_count, bool pdl, 
 cudaError_t launch_qgemv_moe(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // ---- qgemv_i4.cu: Int4 nibble planes, 1..8 rows (and the expert-indexed form: args.ids set, rows = tokens)
 cudaError_t launch_qgemv_i4(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+// ---- qgemv_mxfp4.cu: MXFP4 blocks, 1..8 rows (and the expert-indexed form: args.ids set, rows = tokens); reads the planes
+cudaError_t launch_qgemv_mxfp4(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // Opt in to the dynamic shared memory the GEMV variants need; once per device.
 cudaError_t qgemv_init();
 

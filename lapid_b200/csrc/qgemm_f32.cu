@@ -59,6 +59,11 @@ __device__ __forceinline__ void dequant8(const GemmF32Args &p, uint32_t row, uin
             int hi = (b[128 + 32 * nh + l0 + i] >> (2 * w)) & 3;
             y[i] = xmul(t, (float)((lo | (hi << 4)) - 32));
         }
+    } else if constexpr (FMT == FMT_MXFP4) {
+        const uint8_t *b = p.w + (((uint64_t)row * p.k + k0) / GROUP) * MXFP4_BYTES;
+        const uint32_t e = k0 % GROUP;  // 0, 8, 16 or 24
+#pragma unroll
+        for (int i = 0; i < 8; i++) y[i] = mxfp4_element(b, e + i);
     } else if constexpr (FMT == FMT_INT4) {
         const uint64_t g = ((uint64_t)row * p.k + k0) / GROUP;
         const uint32_t e = k0 % GROUP;  // 0, 8, 16 or 24: elements 16.. are the high nibbles of the same bytes
@@ -167,6 +172,7 @@ cudaError_t launch_qgemm_f32(int fmt, const GemmF32Args &a, cudaStream_t stream)
         case FMT_Q6K: qgemm_f32_kernel<FMT_Q6K><<<grid, 256, 0, stream>>>(a); break;
         case FMT_INT8: qgemm_f32_kernel<FMT_INT8><<<grid, 256, 0, stream>>>(a); break;
         case FMT_INT4: qgemm_f32_kernel<FMT_INT4><<<grid, 256, 0, stream>>>(a); break;
+        case FMT_MXFP4: qgemm_f32_kernel<FMT_MXFP4><<<grid, 256, 0, stream>>>(a); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

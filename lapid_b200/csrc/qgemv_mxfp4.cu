@@ -1,0 +1,147 @@
+// Decode GEMV over MXFP4 blocks (ggml `block_mxfp4`, crates/lapid-quant/src/mxfp4.rs: 32 elements in 17 bytes --
+// one e8m0 scale byte, then 16 bytes whose low nibbles are elements 0..15 and high nibbles elements 16..31;
+// x = KV[nibble] * 2^(e - 128) with KV the doubled e2m1 values) with lapid-cpu's int8-activation arithmetic
+// (crates/lapid-cpu/src/mxfp4.rs:38-58):
+//
+//     acc += d * da_g * f32(sum_32 qa * KV[q])          one activation group per weight block
+//
+// One warp per weight row; a lane takes every 32nd block of the row. Blocks are 17 bytes long, so they start on
+// any byte boundary: the 16 nibble bytes are fetched as aligned 32-bit words and funnel-shifted into place. A
+// nibble becomes its KV magnitude with one byte-permute (the eight magnitudes 0,1,2,3,4,6,8,12 are a two-register
+// table and the three low bits of four nibbles the selector); the sign bits split the four magnitudes into a
+// positive and a negative word, each multiplied with `dp4a` against the activation planes (served by L1/L2).
+// A straightforward streaming kernel: the format is outside the benchmark's configurations and has no
+// bulk-copy or tensor-core variant yet.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lb {
+namespace mx {
+
+constexpr int WARPS = 8;
+
+// The four nibbles in bytes of `n` (each 0..15) -> their KV magnitudes, split by sign: pos holds the magnitudes of
+// the non-negative codes, neg those of the negative ones (the other bytes are 0).
+__device__ __forceinline__ void kv_split(uint32_t n, uint32_t &pos, uint32_t &neg) {
+    const uint32_t t = n & 0x07070707u;
+    const uint32_t u = (t | (t >> 4)) & 0x00FF00FFu;  // byte 0: nibbles 0, 1; byte 2: nibbles 2, 3
+    const uint32_t sel = (u | (u >> 8)) & 0xFFFFu;    // one selector nibble per output byte
+    const uint32_t mag = __byte_perm(0x03020100u, 0x0C080604u, sel);
+    const uint32_t s = ((n >> 3) & 0x01010101u) * 0xFFu;  // 0xFF in the bytes whose code has the sign bit
+    pos = mag & ~s;
+    neg = mag & s;
+}
+
+template <int M> __global__ void __launch_bounds__(WARPS * 32) qgemv_mxfp4_kernel(GemvArgs p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t k = p.k, kg = k / GROUP;
+    if (p.ids) {
+        // Expert-indexed launch (Kernel::MatMulId at decode sizes): grid row y is one (token, slot) pair
+        const uint32_t pair = blockIdx.y, token = pair / p.id_r;
+        const int32_t id = p.ids[pair];
+        const bool bad = id < 0 || (uint32_t)id >= p.id_e;
+        if (bad && p.status && threadIdx.x == 0) atomicOr(p.status, 128);
+        p.w += bad ? 0 : (uint64_t)id * p.id_stride;
+        p.qa += (uint64_t)token * k;
+        p.da += (uint64_t)token * kg;
+        p.out_off += (uint64_t)pair * p.n;
+    }
+    for (uint32_t row = blockIdx.x * WARPS + warp; row < p.n; row += gridDim.x * WARPS) {
+        float acc[M];
+#pragma unroll
+        for (int r = 0; r < M; r++) acc[r] = 0.0f;
+        const uint8_t *wrow = p.w + (uint64_t)row * kg * MXFP4_BYTES;
+        for (uint32_t g = lane; g < kg; g += 32) {
+            const uint8_t *b = wrow + (uint64_t)g * MXFP4_BYTES;
+            const float d = e8m0_half(__ldg(b));
+            // the 16 nibble bytes b[1..16] from the aligned words around them
+            const uintptr_t q0 = (uintptr_t)(b + 1);
+            const uint32_t *wp = (const uint32_t *)(q0 & ~(uintptr_t)3);
+            const uint32_t sh = (uint32_t)(q0 & 3) * 8;
+            uint32_t raw[5];
+#pragma unroll
+            for (int i = 0; i < 4; i++) raw[i] = __ldg(wp + i);
+            raw[4] = sh ? __ldg(wp + 4) : 0u;  // (aligned blocks end with the fourth word: nothing is read behind them)
+            uint32_t lp[4], ln[4], hp[4], hn[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t w = __funnelshift_r(raw[i], raw[i + 1], sh);
+                kv_split(w & 0x0F0F0F0Fu, lp[i], ln[i]);         // elements 4i .. 4i + 3
+                kv_split((w >> 4) & 0x0F0F0F0Fu, hp[i], hn[i]);  // elements 16 + 4i ..
+            }
+#pragma unroll
+            for (int r = 0; r < M; r++) {
+                const uint4 *ap = (const uint4 *)(p.qa + (uint64_t)r * k + (uint64_t)g * GROUP);
+                const uint4 a0 = __ldg(ap), a1 = __ldg(ap + 1);
+                const float da = __ldg(p.da + (uint64_t)r * kg + g);
+                const uint32_t al[4] = {a0.x, a0.y, a0.z, a0.w}, ah[4] = {a1.x, a1.y, a1.z, a1.w};
+                int dp = 0, dn = 0;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    dp = __dp4a((int)lp[i], (int)al[i], dp);
+                    dn = __dp4a((int)ln[i], (int)al[i], dn);
+                    dp = __dp4a((int)hp[i], (int)ah[i], dp);
+                    dn = __dp4a((int)hn[i], (int)ah[i], dn);
+                }
+                acc[r] = fmaf(d * da, (float)(dp - dn), acc[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < M; r++) {
+            float v = acc[r];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) {
+                const uint32_t bt = r / p.m, i = r % p.m;
+                if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
+                p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
+            }
+        }
+    }
+}
+
+template <int M> static cudaError_t launch_m(const GemvArgs &a, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
+    const uint32_t want = (a.n + WARPS - 1) / WARPS;
+    uint32_t cap = (uint32_t)sm_count * 8;
+    if (pairs > 1) cap = cap / pairs > 0 ? cap / pairs : 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(want < cap ? want : cap, pairs);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, qgemv_mxfp4_kernel<M>, a);
+}
+
+}  // namespace mx
+
+cudaError_t launch_qgemv_mxfp4(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream) {
+    if (args.n == 0 || args.rows == 0) return cudaSuccess;
+    if (args.k % GROUP != 0 || ((uintptr_t)args.w & 3) != 0) return cudaErrorInvalidValue;
+    if (args.ids) {  // one-row GEMV per (token, slot) pair
+        if (args.id_r == 0 || args.id_e == 0 || args.rows > 8 || (uint64_t)args.rows * args.id_r > 65535 || (args.id_stride & 3))
+            return cudaErrorInvalidValue;
+        GemvArgs one = args;
+        one.rows = 1;
+        one.m = 1;
+        return mx::launch_m<1>(one, args.rows * args.id_r, sm_count, pdl, stream);
+    }
+    switch (args.rows) {
+        case 1: return mx::launch_m<1>(args, 1, sm_count, pdl, stream);
+        case 2: return mx::launch_m<2>(args, 1, sm_count, pdl, stream);
+        case 3: return mx::launch_m<3>(args, 1, sm_count, pdl, stream);
+        case 4: return mx::launch_m<4>(args, 1, sm_count, pdl, stream);
+        case 5: return mx::launch_m<5>(args, 1, sm_count, pdl, stream);
+        case 6: return mx::launch_m<6>(args, 1, sm_count, pdl, stream);
+        case 7: return mx::launch_m<7>(args, 1, sm_count, pdl, stream);
+        case 8: return mx::launch_m<8>(args, 1, sm_count, pdl, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace lb

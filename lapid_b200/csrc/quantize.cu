@@ -408,6 +408,46 @@ __global__ void __launch_bounds__(256) quantize_int4_kernel(const float *__restr
     }
 }
 
+// MXFP4 (crates/lapid-quant/src/mxfp4.rs:27-49): one warp per 32-element block, lane = element.
+//   e = u8(floor(log2(amax)) - 2 + 127) (0 for an all-zero block), d = 2^(e - 128),
+//   code = the first of the 16 values KV * d closest to x.
+// The reference takes log2 in f32 from its maths library; here it is taken in f64 and rounded to f32, which
+// gives the correctly rounded f32 logarithm (the cases where the two could differ need a logarithm within
+// 2^-29 of a rounding boundary; inputs just below a power of two, whose logarithm rounds up to the integer,
+// come out the same).
+__global__ void __launch_bounds__(256) quantize_mxfp4_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst, uint64_t n_blocks) {
+    const int lane = threadIdx.x & 31;
+    const uint64_t warps = (uint64_t)gridDim.x * (blockDim.x >> 5);
+    for (uint64_t blk = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); blk < n_blocks; blk += warps) {
+        const float x = src[blk * GROUP + lane];
+        float amax = fabsf(x);
+        if (!(amax == amax)) amax = 0.0f;  // f32::max ignores a NaN operand
+#pragma unroll
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        uint32_t e = 0;
+        if (amax > 0.0f) {
+            const float l = (float)log2((double)amax);
+            const float v = xadd(xsub(floorf(l), 2.0f), 127.0f);
+            e = v <= 0.0f ? 0u : (v >= 255.0f ? 255u : (uint32_t)v);  // `as u8` saturates
+        }
+        const float d = e8m0_half(e);
+        uint32_t best = 0;
+        float best_err = fabsf(xsub(xmul(0.0f, d), x));
+#pragma unroll
+        for (uint32_t i = 1; i < 16; i++) {
+            const float err = fabsf(xsub(xmul((float)mxfp4_kv(i), d), x));
+            if (err < best_err) {
+                best = i;
+                best_err = err;
+            }
+        }
+        const uint32_t hi = __shfl_down_sync(0xffffffffu, best, 16);
+        uint8_t *out = dst + blk * MXFP4_BYTES;
+        if (lane < 16) out[1 + lane] = (uint8_t)(best | (hi << 4));
+        if (lane == 0) out[0] = (uint8_t)e;
+    }
+}
+
 cudaError_t launch_quantize(int fmt, const float *src, uint64_t rows, uint64_t cols, uint64_t scales_offset,
                             uint64_t total_bytes, void *dst, int sm_count, cudaStream_t stream) {
     cudaError_t e = cudaMemsetAsync(dst, 0, total_bytes, stream);  // padding (and gaps) are zero
@@ -424,6 +464,9 @@ cudaError_t launch_quantize(int fmt, const float *src, uint64_t rows, uint64_t c
     } else if (fmt == FMT_Q6K) {
         uint64_t nb = n / QK, ctas = (nb + Q6_BLOCKS_PER_CTA - 1) / Q6_BLOCKS_PER_CTA;
         quantize_q6k_kernel<<<(int)(ctas < cap ? ctas : cap), 256, 0, stream>>>(src, (uint8_t *)dst, nb);
+    } else if (fmt == FMT_MXFP4) {
+        uint64_t nb = n / GROUP, ctas = (nb + 7) / 8;
+        quantize_mxfp4_kernel<<<(int)(ctas < cap ? ctas : cap), 256, 0, stream>>>(src, (uint8_t *)dst, nb);
     } else if (fmt == FMT_INT4) {
         uint64_t ng = n / GROUP, ctas = (ng + 255) / 256;
         uint8_t *d = (uint8_t *)dst;

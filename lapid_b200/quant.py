@@ -24,12 +24,13 @@ class Format(enum.IntEnum):
     Q4K = 6
     Q5K = 7
     Q6K = 8
+    MXFP4 = 9  # ggml block_mxfp4: 32 elements in 17 bytes
 
     def block_elems(self) -> int:
-        return 32 if self in (Format.Int8, Format.Int4) else 256
+        return 32 if self in (Format.Int8, Format.Int4, Format.MXFP4) else 256
 
     def block_bytes(self) -> int:
-        return {Format.Int8: 0, Format.Int4: 0, Format.Q4K: 144, Format.Q5K: 176, Format.Q6K: 210}[self]
+        return {Format.Int8: 0, Format.Int4: 0, Format.Q4K: 144, Format.Q5K: 176, Format.Q6K: 210, Format.MXFP4: 17}[self]
 
     def is_aos(self) -> bool:
         return self.block_bytes() != 0

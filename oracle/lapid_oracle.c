@@ -46,6 +46,8 @@
 #define LO_FMT_Q4K 6
 #define LO_FMT_Q5K 7
 #define LO_FMT_Q6K 8
+#define LO_FMT_MXFP4 9
+#define MXFP4_BYTES 17
 
 #define GROUP 32
 #define ALIGN 256
@@ -115,16 +117,17 @@ static inline int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ?
 /* ------------------------------------------------------------------ layout (lib.rs:27-125) */
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-static int block_elems(int fmt) { return (fmt == LO_FMT_INT8 || fmt == LO_FMT_INT4) ? GROUP : QK; }
+static int block_elems(int fmt) { return (fmt == LO_FMT_INT8 || fmt == LO_FMT_INT4 || fmt == LO_FMT_MXFP4) ? GROUP : QK; }
 static int block_bytes(int fmt) {
-    return fmt == LO_FMT_Q4K ? Q4K_BYTES : (fmt == LO_FMT_Q5K ? Q5K_BYTES : (fmt == LO_FMT_Q6K ? Q6K_BYTES : 0));
+    return fmt == LO_FMT_Q4K ? Q4K_BYTES
+                             : (fmt == LO_FMT_Q5K ? Q5K_BYTES : (fmt == LO_FMT_Q6K ? Q6K_BYTES : (fmt == LO_FMT_MXFP4 ? MXFP4_BYTES : 0)));
 }
 static int is_kfmt(int fmt) { return fmt == LO_FMT_Q4K || fmt == LO_FMT_Q5K || fmt == LO_FMT_Q6K; }
 
 /* out = {qs_offset, qs_bytes, scales_offset, scales_bytes, total}; returns 0, or -1 on a bad
  * format / cols not a multiple of the block. */
 int lo_layout(int fmt, size_t rows, size_t cols, size_t out[5]) {
-    if (fmt != LO_FMT_INT8 && fmt != LO_FMT_INT4 && !is_kfmt(fmt)) return -1;
+    if (fmt != LO_FMT_INT8 && fmt != LO_FMT_INT4 && fmt != LO_FMT_MXFP4 && !is_kfmt(fmt)) return -1;
     size_t be = (size_t)block_elems(fmt);
     if (cols % be != 0) return -1;
     if (block_bytes(fmt) != 0) {
@@ -513,12 +516,85 @@ static float quant_group_i4(const float *x, uint8_t *q) {
     return d;
 }
 
+/* ------------------------------------------------------------------ MXFP4 (crates/lapid-quant/src/mxfp4.rs) */
+/* 32 elements in 17 bytes: e (e8m0) | qs[16], byte j = element j (low nibble) | element j + 16 (high nibble);
+ * x = KV[nibble] * d with the doubled e2m1 values KV and d = 2^(e - 128). */
+static const int8_t MXFP4_KV[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12}; /* mxfp4.rs:19 */
+
+/* mxfp4.rs:22-25: d as f32 bits (a denormal for e < 2) */
+static inline float e8m0_half(uint8_t e) { return bits_f32(e < 2 ? (uint32_t)0x00200000u << e : (uint32_t)(e - 1) << 23); }
+
+/* mxfp4.rs:27-38: the first code with the smallest |KV * d - x| */
+static uint8_t mxfp4_best_index(float x, float d) {
+    uint8_t best = 0;
+    float best_err = fabsf((float)MXFP4_KV[0] * d - x);
+    for (int i = 1; i < 16; i++) {
+        float err = fabsf((float)MXFP4_KV[i] * d - x);
+        if (err < best_err) {
+            best = (uint8_t)i;
+            best_err = err;
+        }
+    }
+    return best;
+}
+
+/* mxfp4.rs:41-49. `as u8` saturates: values below 0 give 0, above 255 give 255 (NaN gives 0). */
+void lo_quantize_mxfp4_block(const float *x, uint8_t *out) {
+    float amax = 0.0f;
+    for (int i = 0; i < GROUP; i++) {
+        float a = fabsf(x[i]);
+        if (a > amax) amax = a; /* f32::max ignores a NaN operand */
+    }
+    uint8_t e = 0;
+    if (amax > 0.0f) {
+        float v = floorf(log2f(amax)) - 2.0f + 127.0f;
+        e = (v != v) ? 0 : (v <= 0.0f ? 0 : (v >= 255.0f ? 255 : (uint8_t)v));
+    }
+    float d = e8m0_half(e);
+    out[0] = e;
+    for (int j = 0; j < GROUP / 2; j++)
+        out[1 + j] = (uint8_t)(mxfp4_best_index(x[j], d) | (mxfp4_best_index(x[j + GROUP / 2], d) << 4));
+}
+
+/* mxfp4.rs:52-59 */
+void lo_dequantize_mxfp4_block(const uint8_t *b, float *y) {
+    float d = e8m0_half(b[0]);
+    for (int j = 0; j < GROUP / 2; j++) {
+        uint8_t q = b[1 + j];
+        y[j] = (float)MXFP4_KV[q & 15] * d;
+        y[j + GROUP / 2] = (float)MXFP4_KV[q >> 4] * d;
+    }
+}
+
+/* mxfp4.rs:66-84: packed e2m1 pairs (byte i = element 2i low, 2i + 1 high) + one e8m0 scale per 32 elements
+ * -> MXFP4 blocks. `out` holds rows * cols / 32 * 17 bytes. */
+void lo_mxfp4_from_e2m1_pairs(const uint8_t *packed, const uint8_t *scales, size_t rows, size_t cols, uint8_t *out) {
+    size_t nb = rows * cols / GROUP;
+    for (size_t bi = 0; bi < nb; bi++) {
+        const uint8_t *src = packed + bi * (GROUP / 2);
+        uint8_t *dst = out + bi * MXFP4_BYTES;
+        uint8_t codes[GROUP];
+        dst[0] = scales[bi];
+        for (int i = 0; i < GROUP / 2; i++) {
+            codes[2 * i] = src[i] & 15;
+            codes[2 * i + 1] = src[i] >> 4;
+        }
+        for (int j = 0; j < GROUP / 2; j++) dst[1 + j] = (uint8_t)(codes[j] | (codes[j + GROUP / 2] << 4));
+    }
+}
+
 /* lib.rs:131 / imp.rs:73-116. `out` holds layout.total bytes; padding is zeroed. Returns 0, or
  * -1 when the format is unknown or cols is not a positive multiple of the block length. */
 int lo_quantize(int fmt, const float *data, size_t rows, size_t cols, uint8_t *out) {
     size_t L[5];
     if (cols == 0 || lo_layout(fmt, rows, cols, L) != 0) return -1;
     memset(out, 0, L[4]);
+    if (fmt == LO_FMT_MXFP4) {
+        size_t nb = rows * cols / GROUP;
+#pragma omp parallel for schedule(static)
+        for (long long i = 0; i < (long long)nb; i++) lo_quantize_mxfp4_block(data + (size_t)i * GROUP, out + (size_t)i * MXFP4_BYTES);
+        return 0;
+    }
     if (is_kfmt(fmt)) {
         size_t nb = rows * cols / QK;
         size_t bb = (size_t)block_bytes(fmt);
@@ -544,6 +620,11 @@ int lo_quantize(int fmt, const float *data, size_t rows, size_t cols, uint8_t *o
 int lo_dequantize_row(int fmt, const uint8_t *bytes, size_t rows, size_t cols, size_t row, float *out) {
     size_t L[5];
     if (cols == 0 || lo_layout(fmt, rows, cols, L) != 0 || row >= rows) return -1;
+    if (fmt == LO_FMT_MXFP4) {
+        size_t nb = cols / GROUP;
+        for (size_t b = 0; b < nb; b++) lo_dequantize_mxfp4_block(bytes + (row * nb + b) * MXFP4_BYTES, out + b * GROUP);
+        return 0;
+    }
     if (is_kfmt(fmt)) {
         size_t nb = cols / QK, bb = (size_t)block_bytes(fmt);
         const uint8_t *rb = bytes + row * nb * bb;
@@ -723,6 +804,22 @@ static void kcol(int fmt, const uint8_t *wrow, size_t k, size_t rows, const int8
     }
 }
 
+/* crates/lapid-cpu/src/mxfp4.rs:27-58: one output column of the MXFP4 decode tile, acc += d * da * f32(dot) */
+static void mxcol(const uint8_t *wrow, size_t k, size_t rows, const int8_t *qa, const float *sa, float *acc) {
+    size_t kg = k / GROUP;
+    int8_t q[GROUP];
+    for (size_t r = 0; r < rows; r++) acc[r] = 0.0f;
+    for (size_t blk = 0; blk < kg; blk++) {
+        const uint8_t *b = wrow + blk * MXFP4_BYTES;
+        for (int j = 0; j < GROUP / 2; j++) {
+            q[j] = MXFP4_KV[b[1 + j] & 15];
+            q[j + GROUP / 2] = MXFP4_KV[b[1 + j] >> 4];
+        }
+        float d = e8m0_half(b[0]);
+        for (size_t r = 0; r < rows; r++) acc[r] += d * sa[r * kg + blk] * idot(qa + r * k + blk * GROUP, q, GROUP);
+    }
+}
+
 /* crates/lapid-cpu/src/matmul/qkernels.rs:60-84 */
 static void i8col(int fmt, const uint8_t *bytes, size_t scales_off, size_t col, size_t k, size_t rows, const int8_t *qa,
                   const float *sa, float *acc) {
@@ -806,7 +903,8 @@ int lo_matmul(int fmt, const float *a, size_t a_len, lo_view av, const uint8_t *
 #pragma omp parallel for schedule(static)
         for (long long j = 0; j < (long long)n; j++) {
             float acc[8];
-            if (fmt == LO_FMT_INT8 || fmt == LO_FMT_INT4) i8col(fmt, w, L[2], (size_t)j, k, rows, qa, sa, acc);
+            if (fmt == LO_FMT_MXFP4) mxcol(w + (size_t)j * kg * MXFP4_BYTES, k, rows, qa, sa, acc);
+            else if (fmt == LO_FMT_INT8 || fmt == LO_FMT_INT4) i8col(fmt, w, L[2], (size_t)j, k, rows, qa, sa, acc);
             else kcol(fmt, w + (size_t)j * (k / QK) * bb, k, rows, qa, sa, bs, acc);
             for (size_t r = 0; r < rows; r++) {
                 float v = bias ? acc[r] + bias[j] : acc[r];

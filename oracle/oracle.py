@@ -27,9 +27,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "lapid_oracle.c")
 
 # dtype codes shared with crates/lapid-c/src/lib.rs:37-60
-INT8, INT4, Q4_K, Q5_K, Q6_K = 4, 5, 6, 7, 8
-FORMATS = {"int8": INT8, "int4": INT4, "q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K}
-BLOCK_BYTES = {Q4_K: 144, Q5_K: 176, Q6_K: 210}
+INT8, INT4, Q4_K, Q5_K, Q6_K, MXFP4 = 4, 5, 6, 7, 8, 9
+FORMATS = {"int8": INT8, "int4": INT4, "q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K, "mxfp4": MXFP4}
+BLOCK_BYTES = {Q4_K: 144, Q5_K: 176, Q6_K: 210, MXFP4: 17}
 
 ERRORS = {1: "invalid_launch", 2: "shape_mismatch", 3: "out_of_bounds", 4: "unsupported_dtype"}
 
@@ -111,6 +111,10 @@ class Oracle:
         lib.lo_dequantize_q6k_block.argtypes = [C.c_void_p, C.c_void_p]
         lib.lo_quantize_q5k_block.argtypes = [C.c_void_p, C.c_void_p]
         lib.lo_dequantize_q5k_block.argtypes = [C.c_void_p, C.c_void_p]
+        lib.lo_quantize_mxfp4_block.argtypes = [C.c_void_p, C.c_void_p]
+        lib.lo_dequantize_mxfp4_block.argtypes = [C.c_void_p, C.c_void_p]
+        lib.lo_mxfp4_from_e2m1_pairs.argtypes = [C.c_void_p, C.c_void_p, sz, sz, C.c_void_p]
+        lib.lo_mxfp4_from_e2m1_pairs.restype = None
         lib.lo_matmul.argtypes = [C.c_int, C.c_void_p, sz, _View, C.c_void_p, sz, sz, sz, C.c_void_p, C.c_void_p, sz,
                                   _View, sz, sz, sz, sz, C.c_int, C.c_int, C.POINTER(C.c_int)]
         lib.lo_num_threads.restype = C.c_int
@@ -172,17 +176,26 @@ class Oracle:
 
     def quantize_block(self, fmt: int, x: np.ndarray) -> np.ndarray:
         x = np.ascontiguousarray(x, dtype=np.float32)
-        assert x.size == 256
+        assert x.size == (32 if fmt == MXFP4 else 256)
         out = np.empty(BLOCK_BYTES[fmt], dtype=np.uint8)
         {Q4_K: self.lib.lo_quantize_q4k_block, Q5_K: self.lib.lo_quantize_q5k_block,
-         Q6_K: self.lib.lo_quantize_q6k_block}[fmt](x.ctypes.data, out.ctypes.data)
+         Q6_K: self.lib.lo_quantize_q6k_block, MXFP4: self.lib.lo_quantize_mxfp4_block}[fmt](x.ctypes.data, out.ctypes.data)
         return out
 
     def dequantize_block(self, fmt: int, b: np.ndarray) -> np.ndarray:
         b = np.ascontiguousarray(b, dtype=np.uint8)
-        out = np.empty(256, dtype=np.float32)
+        out = np.empty(32 if fmt == MXFP4 else 256, dtype=np.float32)
         {Q4_K: self.lib.lo_dequantize_q4k_block, Q5_K: self.lib.lo_dequantize_q5k_block,
-         Q6_K: self.lib.lo_dequantize_q6k_block}[fmt](b.ctypes.data, out.ctypes.data)
+         Q6_K: self.lib.lo_dequantize_q6k_block, MXFP4: self.lib.lo_dequantize_mxfp4_block}[fmt](b.ctypes.data, out.ctypes.data)
+        return out
+
+    def mxfp4_from_e2m1_pairs(self, packed: np.ndarray, scales: np.ndarray, rows: int, cols: int) -> np.ndarray:
+        """`from_e2m1_pairs` (crates/lapid-quant/src/mxfp4.rs:61-84): torch-style packed e2m1 pairs + e8m0 scales -> MXFP4 blocks."""
+        packed = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1)
+        scales = np.ascontiguousarray(scales, dtype=np.uint8).reshape(-1)
+        assert cols % 32 == 0 and packed.size == rows * cols // 2 and scales.size == rows * cols // 32
+        out = np.empty(rows * cols // 32 * 17, dtype=np.uint8)
+        self.lib.lo_mxfp4_from_e2m1_pairs(packed.ctypes.data, scales.ctypes.data, C.c_size_t(rows), C.c_size_t(cols), out.ctypes.data)
         return out
 
     # ---- lapid-cpu surface

@@ -45,7 +45,7 @@ def test_abi_version_and_mismatch_error_json():
 
 
 def test_layout_matches_oracle_and_reference_sizes(oracle):
-    for fmt in (quant.Format.Int8, quant.Format.Int4, quant.Format.Q4K, quant.Format.Q5K, quant.Format.Q6K):
+    for fmt in (quant.Format.Int8, quant.Format.Int4, quant.Format.Q4K, quant.Format.Q5K, quant.Format.Q6K, quant.Format.MXFP4):
         for rows, cols in [(1, 256), (3, 512), (768, 768 if fmt.block_elems() == 32 else 1024), (4096, 4096), (14336, 4096),
                            (4096, 14336), (128256, 4096)]:
             a, b = quant.layout(fmt, rows, cols), oracle.layout(int(fmt), rows, cols)
@@ -58,8 +58,10 @@ def test_layout_matches_oracle_and_reference_sizes(oracle):
     with pytest.raises(lp.LapidError) as e:
         quant.layout(quant.Format.Q4K, 2, 128)
     assert e.value.code == "invalid_launch" and e.value.status == 8
+    l = quant.layout(quant.Format.MXFP4, 2, 128)  # 8 blocks of 17 bytes (crates/lapid-quant/src/lib.rs:62-75, :108-112)
+    assert (l.qs_bytes, l.scales_offset, l.scales_bytes, l.total) == (136, 136, 0, 256)
     with pytest.raises(lp.LapidError) as e:
-        quant.layout(9, 2, 128)  # mxfp4: not implemented here
+        quant.layout(10, 2, 256)  # iq2_xxs: the grid-based i-quants are not implemented here
     assert e.value.code == "unsupported_dtype" and e.value.status == 3
 
 

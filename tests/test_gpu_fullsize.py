@@ -23,7 +23,8 @@ from oracle import oracle as O
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]
-FMTS = [(lp.DType.Int8, "int8"), (lp.DType.Int4, "int4"), (lp.DType.Q4K, "q4_k"), (lp.DType.Q5K, "q5_k"), (lp.DType.Q6K, "q6_k")]
+FMTS = [(lp.DType.Int8, "int8"), (lp.DType.Int4, "int4"), (lp.DType.Q4K, "q4_k"), (lp.DType.Q5K, "q5_k"), (lp.DType.Q6K, "q6_k"),
+        (lp.DType.MXFP4, "mxfp4")]
 BLOCK_BYTES = {lp.DType.Q4K: 144, lp.DType.Q5K: 176, lp.DType.Q6K: 210}
 
 

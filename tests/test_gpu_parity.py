@@ -20,8 +20,10 @@ from tests.refgen import make_blocks, rnd
 
 pytestmark = pytest.mark.gpu
 
-FMTS = [(lp.DType.Int8, "int8"), (lp.DType.Int4, "int4"), (lp.DType.Q4K, "q4_k"), (lp.DType.Q5K, "q5_k"), (lp.DType.Q6K, "q6_k")]
+FMTS = [(lp.DType.Int8, "int8"), (lp.DType.Int4, "int4"), (lp.DType.Q4K, "q4_k"), (lp.DType.Q5K, "q5_k"), (lp.DType.Q6K, "q6_k"),
+        (lp.DType.MXFP4, "mxfp4")]
 PLANES = (lp.DType.Int8, lp.DType.Int4)   # formats with 32-element groups in plane layout
+GROUP32 = PLANES + (lp.DType.MXFP4,)      # formats whose K only has to be a multiple of 32
 
 
 @pytest.fixture(scope="module")
@@ -96,6 +98,10 @@ def test_dequantize_bit_exact_random_blocks(be, oracle, fmt, name):
         qb[:l.qs_bytes] = rng.integers(0, 256, l.qs_bytes, dtype=np.uint8)
         sc = (rng.standard_normal(rows * cols // 32) * 0.01).astype(np.float16)
         qb[l.scales_offset:l.scales_offset + l.scales_bytes] = sc.view(np.uint8)
+    elif fmt == lp.DType.MXFP4:   # every byte pattern is a valid block; scale bytes include 0, 1 (denormal d) and 255
+        raw = np.random.default_rng(4).integers(0, 256, rows * cols // 32 * 17, dtype=np.uint8)
+        raw.reshape(-1, 17)[:6, 0] = [0, 1, 2, 127, 254, 255]
+        qb = np.concatenate([raw, np.zeros((-raw.size) % 256, np.uint8)])
     else:
         bb, d_off, dm_off = {lp.DType.Q4K: (144, 0, 2), lp.DType.Q5K: (176, 0, 2), lp.DType.Q6K: (210, 208, None)}[fmt]
         raw = make_blocks(bb, rows * cols // 256, 7, d_off, dm_off)
@@ -122,6 +128,10 @@ def test_quantize_byte_exact(be, oracle, fmt, name):
     x[7, 300:330] = np.abs(x[7, 300:330])  # a sub-block with min > 0
     x[8, :] *= 1e-20               # values below the quantizers' epsilon
     x[9, :64] = np.linspace(-1, 1, 64, dtype=np.float32)
+    x[10, :32] = np.float32(8.0) * (1 - np.float32(2.0) ** -24)   # just below a power of two: its f32 log2 rounds up to 3
+    x[10, 32:64] = np.nextafter(np.float32(0.25), np.float32(0))
+    x[10, 64:96] = 3e-39                                            # denormals
+    x[10, 96:128] = 1e30
     want = oracle.quantize(int(fmt), x, rows, cols)
     got = quant.quantize(be, fmt, x, rows, cols)
     diff = np.flatnonzero(got != want)
@@ -184,7 +194,7 @@ def test_gemv_reference_test_shapes(be, oracle, fmt, name):
     for (m, n, k, pad) in [(1, 37, 512, 0), (3, 20, 256, 4), (6, 9, 256, 0), (1, 36, 768, 0), (3, 36, 768, 1),
                            (2, 1030, 4096, 0), (8, 77, 14336, 0), (1, 5, 2304, 0), (4, 50, 14336, 0), (3, 40, 8192, 8),
                            (2, 3, 16384, 0), (1, 300, 28672, 0)]:
-        if fmt not in PLANES and k % 256:
+        if fmt not in GROUP32 and k % 256:
             continue
         seed += 1
         w = rnd(n * k, seed) if n * k < 100000 else O.normal(seed, n * k, 0.5)

@@ -262,6 +262,47 @@ def test_int8_bytes_match_independent_q8_0_quantizer(oracle):
 
 
 # ------------------------------------------------------------------ lapid-cpu: activations, tiles
+def test_mxfp4_reference_tests_and_independent_codec(oracle):
+    """MXFP4 (crates/lapid-quant/src/mxfp4.rs): the reference's own tests `round_trip_exact_grid` and
+    `e2m1_pairs_match_blocks` (:90-113), and -- where the third-party package has the format -- its independent
+    quantizer AND dequantizer on the same data, byte for byte and bit for bit."""
+    MX = O.MXFP4
+    x = np.array([[0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0][i % 8] * (-0.25 if i % 3 == 0 else 0.25) for i in range(32)], np.float32)
+    assert np.array_equal(oracle.dequantize_block(MX, oracle.quantize_block(MX, x)), x)
+    codes = np.array([i % 16 for i in range(32)], np.uint8)
+    packed = (codes[0::2] | (codes[1::2] << 4)).astype(np.uint8)
+    y = oracle.dequantize_block(MX, oracle.mxfp4_from_e2m1_pairs(packed, np.array([127], np.uint8), 1, 32))
+    e2m1 = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+    assert all(y[i] == e2m1[c & 7] * (-1.0 if c & 8 else 1.0) for i, c in enumerate(codes))
+    l = oracle.layout(MX, 3, 96)
+    assert (l.qs_bytes, l.scales_bytes, l.total) == (3 * 3 * 17, 0, 256)
+    assert not oracle.quantize(MX, np.zeros(64, np.float32), 2, 32)[:34].any()          # an all-zero block: e = 0, codes 0
+    # a block of denormals: floor(log2(amax)) - 2 + 127 is negative and Rust's `as u8` saturates to 0 (mxfp4.rs:43);
+    # a C cast of a negative float to uint8_t is undefined (other implementations wrap to 253 here)
+    assert oracle.quantize_block(MX, np.full(32, 3e-39, np.float32))[0] == 0
+    gguf = _gguf()
+    from gguf import quants
+    if not hasattr(gguf.GGMLQuantizationType, "MXFP4"):
+        pytest.skip("this gguf package has no MXFP4")
+    rows, cols = 16, 512
+    w = O.normal(77, rows * cols, 0.7).reshape(rows, cols)
+    w[0, :32] = np.float32(8.0) * (1 - np.float32(2.0) ** -24)   # log2 rounds up to 3.0 in f32
+    w[2, :32] = 1e30
+    q = oracle.quantize(MX, w, rows, cols)
+    blocks = q[:rows * cols // 32 * 17].reshape(rows, -1)
+    assert np.array_equal(quants.quantize(w, gguf.GGMLQuantizationType.MXFP4).reshape(-1), blocks.reshape(-1))
+    deq = quants.dequantize(blocks, gguf.GGMLQuantizationType.MXFP4).astype(np.float32)
+    assert np.array_equal(deq.view(np.uint32), oracle.dequantize(MX, q, rows, cols).reshape(rows, cols).view(np.uint32))
+    # the decode tile against the dequantized product (crates/lapid-cpu/src/matmul/matmul_tests.rs:96-139, shapes with k % 256 != 0)
+    for (m, n, k) in [(1, 11, 96), (5, 7, 224), (3, 20, 256), (40, 13, 160)]:
+        wq = oracle.quantize(MX, O.normal(80 + m, n * k, 0.5), n, k)
+        a = O.normal(90 + m, m * k)
+        got, path = oracle.matmul(MX, a, wq, n, k, m=m)
+        ref = a.reshape(m, k).astype(np.float64) @ oracle.dequantize(MX, wq, n, k).reshape(n, k).astype(np.float64).T
+        err = np.sqrt(((got.reshape(m, n) - ref) ** 2).sum() / (ref ** 2).sum())
+        assert path == ("int8_act" if m <= 8 else "f32_act") and err <= (2e-2 if m <= 8 else 1e-5)
+
+
 def test_quantize_row_roundtrip(oracle):
     x = np.array([((i * 37) % 29) * 0.37 - 5.0 for i in range(64)], dtype=np.float32)
     q, s, _ = oracle.quantize_row_sums(x)
