@@ -1194,6 +1194,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             lb::qgemv_kq_stream_set_config(std::atoi(value));
         } else if (k == "gemv_stream_ctas") {
             lb::qgemv_kq_stream_set_ctas_per_sm(std::atoi(value));
+        } else if (k == "gemv_stream_early_ctas") {
+            lb::qgemv_kq_stream_set_early_ctas(std::atoi(value));
         } else if (k == "gemv_stream_debug") {
             lb::qgemv_kq_stream_set_debug(std::atoi(value));
         } else if (k == "gemv_two_row_dp4a") {

@@ -200,6 +200,7 @@ cudaError_t launch_qgemv_kq_stream(int fmt, GemvGroup &group, const StreamWs &ws
 void qgemv_kq_stream_set_config(int index);     // tuning: -1 = choose
 void qgemv_kq_stream_set_ctas_per_sm(int n);    // tuning: 0 = choose
 void qgemv_kq_stream_set_debug(int v);          // measurement only: 2 = drop partial tiles (wrong results)
+void qgemv_kq_stream_set_early_ctas(int v);     // tuning: CTAs per SM of a launch that runs ahead of its predecessor (0 = as any launch)
 // Int8 planes on the same instruction (K a multiple of 512); same activation tiles.
 bool qgemv_i8_mma_shape_ok(uint32_t rows, uint32_t k);
 cudaError_t launch_qgemv_i8_mma(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);

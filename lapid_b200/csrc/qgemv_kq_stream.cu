@@ -2,7 +2,7 @@
 // organised as one stream of equal work shares (arithmetic: see qgemv.cu; the integer dot products
 // are the same, only the order of the f32 sums over sub-blocks and k-chunks differs).
 //
-//  * Unit of work: 16*TILES*WARPS weight rows x one k-chunk (two super-blocks, 512 weights per row).
+//  * Unit of work: 16*TILES*WARPS weight rows x one k-chunk (NB = one or two super-blocks per row).
 //    The units of all members of the launch, tile after tile, k-chunk after k-chunk, form one
 //    sequence; CTA b takes the contiguous span [U*b/G, U*(b+1)/G) of it, so every CTA streams the
 //    same number of bytes whatever the shape (no tail of half-empty waves, no idle SMs on matrices
@@ -45,6 +45,7 @@ using namespace pipe;
 constexpr int BAR_BYTES = 128;
 constexpr int SC_STRIDE = 80;  // decoded scales of one (row, super-block): 16 floats, padded against bank conflicts
 constexpr uint32_t PAIR_SPIN_LIMIT = 1u << 20;  // polls of a partial-sum pair before the kernel gives up
+constexpr int HOLD = 2;                         // tiles a warp of a launch that runs ahead keeps in registers before it has to wait
 
 __device__ __forceinline__ uint2 ld_pair(const void *p) {
     uint2 v;
@@ -54,7 +55,6 @@ __device__ __forceinline__ uint2 ld_pair(const void *p) {
 
 template <int FMT> struct Geo {
     static constexpr int BLK = FMT == FMT_Q5K ? Q5K_BYTES : Q4K_BYTES;
-    static constexpr int ROWB = 2 * BLK;                 // one k-chunk of one weight row
     static constexpr int QS = FMT == FMT_Q5K ? 48 : 16;  // offset of the nibbles inside a block
 };
 
@@ -64,10 +64,11 @@ template <int NG> struct Maps {
     CUtensorMap m[NG];  // packed weights of each member: [n rows][k/256 * BLK/4 words], box ROWB/4 words x tile rows
 };
 
-template <int FMT, int WARPS, int TILES, int STAGES, int NG>
-__global__ void __launch_bounds__((WARPS + 1) * 32, (WARPS >= 8 && STAGES <= 2) || (WARPS < 8 && STAGES <= 3) ? 2 : 1)
+// NB: super-blocks per k-chunk (1 or 2). MINB: CTAs per SM the register allocation must allow.
+template <int FMT, int WARPS, int TILES, int NB, int STAGES, int MINB, int NG>
+__global__ void __launch_bounds__((WARPS + 1) * 32, MINB)
 qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp, StreamWs ws, uint32_t early) {
-    constexpr int BLK = Geo<FMT>::BLK, ROWB = Geo<FMT>::ROWB, QS = Geo<FMT>::QS;
+    constexpr int BLK = Geo<FMT>::BLK, ROWB = NB * BLK, QS = Geo<FMT>::QS;
     constexpr int RPW = 16 * TILES;      // rows per consumer warp
     constexpr int RT = RPW * WARPS;      // rows per tile
     constexpr int WBYTES = RT * ROWB;    // weight bytes per stage
@@ -76,9 +77,9 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t M = grp.item[0].rows;
     const uint32_t nblk = grp.item[0].k / QK;
-    const uint32_t C = (nblk + 1) / 2;  // k-chunks per tile
+    const uint32_t C = (nblk + NB - 1) / NB;  // k-chunks per tile
     const uint32_t ABLK = act_block_bytes(M);
-    const uint32_t SBYTES = WBYTES + 2 * ABLK;
+    const uint32_t SBYTES = WBYTES + NB * ABLK;
     const uint32_t tiles = grp.task_end[grp.count - 1];
     const uint64_t U = (uint64_t)tiles * C;
     const uint32_t G = gridDim.x, b = blockIdx.x;
@@ -115,7 +116,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
                 const uint32_t u = u_lo + i, gt = u / C;
                 c = u - gt * C;
                 item = locate(gt, local);
-                nb = min(2u, nblk - 2 * c);
+                nb = min((uint32_t)NB, nblk - NB * c);
             };
             auto load_w = [&](uint32_t i, uint32_t slot) {
                 int item;
@@ -128,7 +129,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
                 int item;
                 uint32_t local, c, nb;
                 unit(i, item, local, c, nb);
-                bulk_g2s(stages + (size_t)slot * SBYTES + WBYTES, (const uint8_t *)grp.item[item].qa + (size_t)(2 * c) * ABLK, nb * ABLK,
+                bulk_g2s(stages + (size_t)slot * SBYTES + WBYTES, (const uint8_t *)grp.item[item].qa + (size_t)(NB * c) * ABLK, nb * ABLK,
                          full + slot);
             };
             const uint32_t pre = nunits < (uint32_t)STAGES ? nunits : (uint32_t)STAGES;
@@ -159,18 +160,103 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
     const uint32_t colq = (uint32_t)gq < M ? gq : 0;      // activation row of this lane's B fragment
     const uint32_t cp = (uint32_t)(2 * t4) < M ? t4 : 0;  // activation row pair of this lane's C fragment
     const uint64_t neg_magic = pack2(-MAGIC, -MAGIC);
-    uint8_t *scs = stages + (size_t)STAGES * SBYTES + (size_t)warp * (32 * TILES * SC_STRIDE);
+    uint8_t *scs = stages + (size_t)STAGES * SBYTES + (size_t)warp * (RPW * NB * SC_STRIDE);  // one slot per (row, super-block) of a stage
     __shared__ TpPushCtx tp_ctx[WARPS];
     bool waited = false, healthy = true;
     auto owner = [&](uint64_t u) -> uint32_t { return (uint32_t)(((u + 1) * G - 1) / U); };
+
+    // One finished segment [c0, c1) of tile gt: store it, hand it to the span that collects the tile, or collect.
+    auto finish = [&](uint32_t gt, uint32_t c0, uint32_t c1, float (&acc)[TILES][4]) {
+        if (!healthy) return;
+        uint32_t local;
+        const int item = locate(gt, local);
+        const GemvArgs &p = grp.item[item];
+        auto store = [&](const float (&v)[TILES][4]) {
+#pragma unroll
+            for (int tl = 0; tl < TILES; tl++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t row = local * RT + warp * RPW + tl * 16 + gq + ((i & 2) ? 8 : 0);
+                    const uint32_t r = 2 * t4 + (i & 1);
+                    if (row < p.n && r < M) {
+                        float x = v[tl][i];
+                        const uint32_t bt = r / p.m, ri = r % p.m;
+                        if (p.extra) x += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
+                        if (p.tp) tp_push_value(&tp_ctx[warp], (uint64_t)r * p.n + row, x);  // row-parallel partial: to every rank
+                        else p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = x;
+                    }
+                }
+        };
+        if (c0 == 0 && c1 == C) {
+            store(acc);
+            return;
+        }
+        if (early & 2) return;  // measurement only (option gemv_stream_debug): partial tiles are dropped, the results are wrong
+        // ---- this span holds only some k-chunks of the tile. The span that holds the tile's first k-chunk adds
+        //      up and stores; the others hand it their partial sums through the workspace as {value, 1} pairs
+        //      (an aligned 8-byte store is never torn, so a pair whose flag is set carries its value: no fence,
+        //      no counter). Only the first segment of a span can lack its tile's head, so a CTA has one slot.
+        uint2 *mine = ws.pairs + ((size_t)b * WARPS + warp) * EW;
+        if (c0 != 0) {
+#pragma unroll
+            for (int tl = 0; tl < TILES; tl++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) st_pair(mine + (tl * 4 + i) * 32 + lane, acc[tl][i], 1u);
+            return;
+        }
+        // The contributors are the spans right behind this one; theirs is the FIRST thing they compute, so their
+        // pairs are usually there already. Sum in span order = k order; take each pair and leave the slot empty
+        // for the next launch (which touches the workspace only after this grid has completed).
+        const uint32_t b_last = owner((uint64_t)gt * C + C - 1);
+        constexpr int NBATCH = 4 / TILES, NE = 4 * TILES;  // contributors asked for at once (their loads are all in flight together)
+        for (uint32_t b0 = b + 1; b0 <= b_last && healthy; b0 += NBATCH) {
+            uint2 v[NBATCH][NE];
+            auto slot_of = [&](int j, int e) { return ws.pairs + ((size_t)(b0 + j) * WARPS + warp) * EW + e * 32 + lane; };
+#pragma unroll
+            for (int j = 0; j < NBATCH; j++)
+#pragma unroll
+                for (int e = 0; e < NE; e++) v[j][e] = b0 + j <= b_last ? ld_pair(slot_of(j, e)) : make_uint2(0u, 1u);
+            for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT; spin++) {
+                bool all = true;
+#pragma unroll
+                for (int j = 0; j < NBATCH; j++)
+#pragma unroll
+                    for (int e = 0; e < NE; e++) all = all && v[j][e].y != 0;
+                if (all) break;
+#pragma unroll
+                for (int j = 0; j < NBATCH; j++)
+#pragma unroll
+                    for (int e = 0; e < NE; e++)
+                        if (v[j][e].y == 0) v[j][e] = ld_pair(slot_of(j, e));
+            }
+#pragma unroll
+            for (int j = 0; j < NBATCH; j++)
+#pragma unroll
+                for (int e = 0; e < NE; e++) {
+                    if (v[j][e].y == 0) healthy = false;
+                    if (b0 + j <= b_last) {
+                        acc[e / 4][e % 4] += __uint_as_float(v[j][e].x);
+                        st_pair(slot_of(j, e), 0.0f, 0u);
+                    }
+                }
+        }
+        healthy = __all_sync(0xffffffffu, healthy);
+        if (!healthy) {
+            if (lane == 0 && grp.item[0].status) atomicOr(grp.item[0].status, 1);
+            return;
+        }
+        store(acc);
+    };
+
+    // parked tiles of a launch that runs ahead (a span of equal shares rarely holds more than two segments)
+    float held[HOLD][TILES][4];
+    uint32_t npark = 0;
+    const uint32_t park_u0 = u_lo;
 
     uint32_t u = u_lo, slot = 0, par = 0;
     while (u < u_hi) {
         const uint32_t gt = u / C, c0 = u - gt * C;
         const uint32_t c1 = min(C, c0 + (u_hi - u));
-        uint32_t local;
-        const int item = locate(gt, local);
-        const GemvArgs &p = grp.item[item];
         float acc[TILES][4];
 #pragma unroll
         for (int tl = 0; tl < TILES; tl++)
@@ -184,7 +270,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
             }
             const uint8_t *wst = stages + (size_t)slot * SBYTES + (size_t)warp * (RPW * ROWB);  // this warp's rows
             const uint8_t *ast = stages + (size_t)slot * SBYTES + WBYTES;
-            const uint32_t nb = min(2u, nblk - 2 * c);
+            const uint32_t nb = min((uint32_t)NB, nblk - NB * c);
             if (healthy) {
                 // ---- decode the 6-bit scales and mins: one lane per (row, super-block); per sub-block pair j
                 //      {d*sc[2j], d*sc[2j+1] (/16 where the high nibbles are used in place), -dmin*m[2j], -dmin*m[2j+1]}
@@ -208,16 +294,18 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
 #pragma unroll
                     for (int j = 0; j < 4; j++) dst[j] = make_float4(w[2 * j], w[2 * j + 1], w[8 + 2 * j], w[8 + 2 * j + 1]);
                 };
-                if constexpr (TILES == 2) {
+                if constexpr (TILES == 2) {  // a lane per row, one super-block after the other
 #pragma unroll
-                    for (uint32_t bb = 0; bb < 2; bb++)
+                    for (uint32_t bb = 0; bb < (uint32_t)NB; bb++)
                         if (bb < nb) decode(lane, bb, bb * RPW + lane);
-                } else {
+                } else if constexpr (NB == 2) {  // 16 rows x 2 super-blocks
                     if ((uint32_t)(lane >> 4) < nb) decode(lane & 15, lane >> 4, lane);
+                } else {
+                    if (lane < 16) decode(lane, 0, lane);
                 }
                 __syncwarp();
 #pragma unroll
-                for (uint32_t bb = 0; bb < 2; bb++) {
+                for (uint32_t bb = 0; bb < (uint32_t)NB; bb++) {
                     if (bb >= nb) break;
                     const uint8_t *ab = ast + (size_t)bb * ABLK;
                     const float4 *dsp = (const float4 *)(ab + 256 * M + cp * 64);
@@ -297,7 +385,20 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
             }
         }
 
-        // ---- nothing is written, and the workspace is not touched, before the kernel in front has completed
+        // ---- nothing is written, and the workspace is not touched, before the kernel in front has completed. A launch
+        //      that may run ahead (early) parks the tile and goes on computing; its stores, hand-overs and
+        //      collections follow once that kernel has completed, or when the parking space is full.
+        if ((early & 1) && !waited && healthy) {
+#pragma unroll
+            for (int q = 0; q < HOLD; q++)
+                if ((uint32_t)q == npark) {
+#pragma unroll
+                    for (int tl = 0; tl < TILES; tl++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) held[q][tl][i] = acc[tl][i];
+                }
+            if (++npark < (uint32_t)HOLD && u < u_hi) continue;
+        }
         if (!waited) {
             asm volatile("griddepcontrol.wait;" ::: "memory");
             waited = true;
@@ -305,83 +406,18 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
                 if (lane == 0) tp_push_ctx_load(&tp_ctx[warp], grp.item[0].tp);
                 __syncwarp();
             }
-        }
-        if (!healthy) continue;
-        auto store = [&](const float (&v)[TILES][4]) {
+            // the parked tiles, oldest first (the walk over the span is repeated from where parking began)
+            uint32_t uu = park_u0;
 #pragma unroll
-            for (int tl = 0; tl < TILES; tl++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t row = local * RT + warp * RPW + tl * 16 + gq + ((i & 2) ? 8 : 0);
-                    const uint32_t r = 2 * t4 + (i & 1);
-                    if (row < p.n && r < M) {
-                        float x = v[tl][i];
-                        const uint32_t bt = r / p.m, ri = r % p.m;
-                        if (p.extra) x += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
-                        if (p.tp) tp_push_value(&tp_ctx[warp], (uint64_t)r * p.n + row, x);  // row-parallel partial: to every rank
-                        else p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = x;
-                    }
-                }
-        };
-        if (c0 == 0 && c1 == C) {
-            store(acc);
-            continue;
-        }
-        if (early & 2) continue;  // measurement only (option gemv_stream_debug): partial tiles are dropped, the results are wrong
-        // ---- this span holds only some k-chunks of the tile. The span that holds the tile's first k-chunk adds
-        //      up and stores; the others hand it their partial sums through the workspace as {value, 1} pairs
-        //      (an aligned 8-byte store is never torn, so a pair whose flag is set carries its value: no fence,
-        //      no counter). Only the first segment of a span can lack its tile's head, so a CTA has one slot.
-        uint2 *mine = ws.pairs + ((size_t)b * WARPS + warp) * EW;
-        if (c0 != 0) {
-#pragma unroll
-            for (int tl = 0; tl < TILES; tl++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) st_pair(mine + (tl * 4 + i) * 32 + lane, acc[tl][i], 1u);
-            continue;
-        }
-        // The contributors are the spans right behind this one; theirs is the FIRST thing they compute, so their
-        // pairs are usually there already. Sum in span order = k order; take each pair and leave the slot empty
-        // for the next launch (which touches the workspace only after this grid has completed).
-        const uint32_t b_last = owner((uint64_t)gt * C + C - 1);
-        constexpr int NB = 4 / TILES, NE = 4 * TILES;  // contributors asked for at once (their loads are all in flight together)
-        for (uint32_t b0 = b + 1; b0 <= b_last && healthy; b0 += NB) {
-            uint2 v[NB][NE];
-            auto slot_of = [&](int j, int e) { return ws.pairs + ((size_t)(b0 + j) * WARPS + warp) * EW + e * 32 + lane; };
-#pragma unroll
-            for (int j = 0; j < NB; j++)
-#pragma unroll
-                for (int e = 0; e < NE; e++) v[j][e] = b0 + j <= b_last ? ld_pair(slot_of(j, e)) : make_uint2(0u, 1u);
-            for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT; spin++) {
-                bool all = true;
-#pragma unroll
-                for (int j = 0; j < NB; j++)
-#pragma unroll
-                    for (int e = 0; e < NE; e++) all = all && v[j][e].y != 0;
-                if (all) break;
-#pragma unroll
-                for (int j = 0; j < NB; j++)
-#pragma unroll
-                    for (int e = 0; e < NE; e++)
-                        if (v[j][e].y == 0) v[j][e] = ld_pair(slot_of(j, e));
+            for (int q = 0; q < HOLD; q++) {
+                if ((uint32_t)q >= npark) break;
+                const uint32_t pgt = uu / C, pc0 = uu - pgt * C, pc1 = min(C, pc0 + (u_hi - uu));
+                finish(pgt, pc0, pc1, held[q]);
+                uu += pc1 - pc0;
             }
-#pragma unroll
-            for (int j = 0; j < NB; j++)
-#pragma unroll
-                for (int e = 0; e < NE; e++) {
-                    if (v[j][e].y == 0) healthy = false;
-                    if (b0 + j <= b_last) {
-                        acc[e / 4][e % 4] += __uint_as_float(v[j][e].x);
-                        st_pair(slot_of(j, e), 0.0f, 0u);
-                    }
-                }
+            if (npark) continue;  // (the segment that just ended was the last parked one)
         }
-        healthy = __all_sync(0xffffffffu, healthy);
-        if (!healthy) {
-            if (lane == 0 && grp.item[0].status) atomicOr(grp.item[0].status, 1);
-            continue;
-        }
-        store(acc);
+        finish(gt, c0, c1, acc);
     }
     if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
@@ -410,10 +446,10 @@ static EncodeTiledFn encode_fn() {
 
 // A tensor map depends only on (address, n, k, block bytes, box rows): the last few are remembered, a
 // decode loop asks for the same handful every token.
-static bool weight_map(const GemvArgs &a, uint32_t blk, uint32_t box_rows, CUtensorMap &out) {
+static bool weight_map(const GemvArgs &a, uint32_t blk, uint32_t nb, uint32_t box_rows, CUtensorMap &out) {
     struct Entry {
         const void *w;
-        uint32_t n, k, blk, rows;
+        uint32_t n, k, blk, nb, rows;
         CUtensorMap map;
     };
     constexpr int CAP = 256;
@@ -423,14 +459,14 @@ static bool weight_map(const GemvArgs &a, uint32_t blk, uint32_t box_rows, CUten
     if (!enc) return false;
     std::lock_guard<std::mutex> lock(g_mu);
     for (int i = 0; i < used; i++)
-        if (cache[i].w == a.w && cache[i].n == a.n && cache[i].k == a.k && cache[i].blk == blk && cache[i].rows == box_rows) {
+        if (cache[i].w == a.w && cache[i].n == a.n && cache[i].k == a.k && cache[i].blk == blk && cache[i].nb == nb && cache[i].rows == box_rows) {
             out = cache[i].map;
             return true;
         }
     const uint32_t nblk = a.k / QK;
     cuuint64_t dims[2] = {(cuuint64_t)nblk * (blk / 4), a.n};
     cuuint64_t strides[1] = {(cuuint64_t)nblk * blk};
-    cuuint32_t box[2] = {2 * blk / 4, box_rows};
+    cuuint32_t box[2] = {nb * blk / 4, box_rows};
     cuuint32_t es[2] = {1, 1};
     if (enc(&out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void *)a.w, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -440,51 +476,63 @@ static bool weight_map(const GemvArgs &a, uint32_t blk, uint32_t box_rows, CUten
     e.n = a.n;
     e.k = a.k;
     e.blk = blk;
+    e.nb = nb;
     e.rows = box_rows;
     e.map = out;
     return true;
 }
 
 struct Config {
-    int warps, tiles, stages;
+    int warps, tiles, nb, stages;  // consumer warps, 16-row tiles per warp, super-blocks per k-chunk, ring stages
 };
-// 0: eight warps of 16 rows, two stages (two CTAs fit on an SM: the launches around this one move in beside it)
-// 1: four warps of 32 rows (the activation fragments are shared by two row tiles), two stages
-// 2: four warps of 16 rows, three stages (half the tile: matrices with few rows)
-// 3: eight warps of 16 rows, four stages (one CTA per SM)
-static const Config CONFIGS[] = {{8, 1, 2}, {4, 2, 2}, {4, 1, 3}, {8, 1, 4}};
-constexpr int N_CONFIGS = 4;
+// 0: eight warps of 16 rows, two-block chunks, two stages
+// 1: four warps of 32 rows (the activation fragments and scales are shared by two row tiles), two-block chunks, two stages
+// 2: four warps of 16 rows, two-block chunks, three stages
+// 3: eight warps of 16 rows, two-block chunks, four stages (one CTA per SM)
+// 4: four warps of 32 rows, one-block chunks, three stages (three CTAs per SM)
+// 5: four warps of 32 rows, one-block chunks, four stages
+// 6: eight warps of 32 rows, one-block chunks, two stages
+static const Config CONFIGS[] = {{8, 1, 2, 2}, {4, 2, 2, 2}, {4, 1, 2, 3}, {8, 1, 2, 4}, {4, 2, 1, 3}, {4, 2, 1, 4}, {8, 2, 1, 2}};
+constexpr int N_CONFIGS = 7;
 static int g_force_config = -1;
 static int g_ctas_per_sm = 0;  // 0 = choose
 static int g_debug = 0;        // measurement only: 2 = drop the partial tiles (wrong results)
+// CTAs per SM of a launch that runs ahead of its predecessor (0 = as for any launch). Measured: leaving slots to the
+// launches around it pays only on small matrices (4096 x 4096: 4.1 against 5.3 us at 1), where the per-warp-ring kernel
+// is used anyway; on the 33 MB shapes the warps of ONE launch finish it sooner than the same warps spread over
+// two or three launches (10.8 against 14.4 us), so the default is off.
+static int g_early_ctas = 0;
 
 static size_t smem_bytes(int fmt, const Config &c, uint32_t rows) {
-    const size_t rowb = fmt == FMT_Q5K ? Geo<FMT_Q5K>::ROWB : Geo<FMT_Q4K>::ROWB;
-    const size_t stage = (size_t)16 * c.tiles * c.warps * rowb + 2 * act_block_bytes(rows);
-    return BAR_BYTES + (size_t)c.stages * stage + (size_t)c.warps * 32 * c.tiles * SC_STRIDE;
+    const size_t rowb = (size_t)c.nb * (fmt == FMT_Q5K ? Geo<FMT_Q5K>::BLK : Geo<FMT_Q4K>::BLK);
+    const size_t stage = (size_t)16 * c.tiles * c.warps * rowb + c.nb * act_block_bytes(rows);
+    return BAR_BYTES + (size_t)c.stages * stage + (size_t)c.warps * 16 * c.tiles * c.nb * SC_STRIDE;
 }
 
-template <int FMT, int WARPS, int TILES, int STAGES, int NG>
+template <int FMT, int WARPS, int TILES, int NB, int STAGES, int MINB, int NG>
 static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
-    auto kern = qgemv_kq_stream_kernel<FMT, WARPS, TILES, STAGES, NG>;
+    auto kern = qgemv_kq_stream_kernel<FMT, WARPS, TILES, NB, STAGES, MINB, NG>;
     constexpr uint32_t RT = 16 * TILES * WARPS;
-    const uint32_t M = g.item[0].rows, C = (g.item[0].k / QK + 1) / 2;
+    const uint32_t M = g.item[0].rows, C = (g.item[0].k / QK + NB - 1) / NB;
     uint32_t tiles = 0;
     Maps<NG> maps;
     for (int i = 0; i < g.count; i++) {
         tiles += (g.item[i].n + RT - 1) / RT;
         g.task_end[i] = tiles;
-        if (!weight_map(g.item[i], Geo<FMT>::BLK, RT, maps.m[i])) return cudaErrorNotSupported;
+        if (!weight_map(g.item[i], Geo<FMT>::BLK, NB, RT, maps.m[i])) return cudaErrorNotSupported;
     }
     for (int i = g.count; i < NG; i++) maps.m[i] = maps.m[0];
-    const size_t smem = smem_bytes(FMT, Config{WARPS, TILES, STAGES}, M);
+    const size_t smem = smem_bytes(FMT, Config{WARPS, TILES, NB, STAGES}, M);
     static DynamicSmemOptIn opted;
     if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
-    // As many CTAs per SM as fit, at most two (measured: a CTA slot left to the next launch of the stream costs
-    // more than it brings here). The grid never exceeds what the SMs hold at once: see the kernel's hand-over.
+    // As many CTAs per SM as fit, at most what the kernel's register allocation allows (measured: a CTA slot left to
+    // the next launch of the stream costs more than it brings here). The grid never exceeds what the SMs hold at
+    // once: see the kernel's hand-over.
     const uint32_t fit = (uint32_t)((227 * 1024) / (smem + 1024));
-    uint32_t per_sm = fit >= 2 ? 2 : 1;
-    if (g_ctas_per_sm > 0) per_sm = (uint32_t)g_ctas_per_sm < fit ? (uint32_t)g_ctas_per_sm : (fit ? fit : 1);
+    uint32_t per_sm = fit < (uint32_t)MINB ? (fit ? fit : 1) : (uint32_t)MINB;
+    // Tuning: a launch that runs ahead of its predecessor may leave CTA slots to the launches around it.
+    if (early && fit >= 2 && g_early_ctas > 0) per_sm = (uint32_t)g_early_ctas < per_sm ? (uint32_t)g_early_ctas : per_sm;
+    if (g_ctas_per_sm > 0) per_sm = (uint32_t)g_ctas_per_sm < per_sm ? (uint32_t)g_ctas_per_sm : per_sm;
     const uint64_t U = (uint64_t)tiles * C;
     uint32_t grid = (uint32_t)sm_count * per_sm;
     if (grid > U) grid = (uint32_t)U;
@@ -503,16 +551,16 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count,
     return cudaLaunchKernelEx(&cfg, kern, maps, g, ws, (uint32_t)((early ? 1 : 0) | (g_debug & 2)));
 }
 
-template <int FMT, int WARPS, int TILES, int STAGES>
+template <int FMT, int WARPS, int TILES, int NB, int STAGES, int MINB>
 static cudaError_t launch_cfg(GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
-    if (g.count > 1) return launch_n<FMT, WARPS, TILES, STAGES, GEMV_GROUP_MAX>(g, ws, sm_count, pdl, early, stream);
+    if (g.count > 1) return launch_n<FMT, WARPS, TILES, NB, STAGES, MINB, GEMV_GROUP_MAX>(g, ws, sm_count, pdl, early, stream);
     GemvSingle one;  // a lone launch passes a sixth of the parameter bytes
     one.item[0] = g.item[0];
     one.act_off[0] = 0;
     one.act_copy[0] = 0;
     one.count = 1;
     one.act_bytes = 0;
-    return launch_n<FMT, WARPS, TILES, STAGES, 1>(one, ws, sm_count, pdl, early, stream);
+    return launch_n<FMT, WARPS, TILES, NB, STAGES, MINB, 1>(one, ws, sm_count, pdl, early, stream);
 }
 
 static int pick_config(const GemvGroup &, int) {
@@ -522,10 +570,13 @@ static int pick_config(const GemvGroup &, int) {
 
 template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
     switch (pick_config(g, sm_count)) {
-        case 0: return launch_cfg<FMT, 8, 1, 2>(g, ws, sm_count, pdl, early, stream);
-        case 1: return launch_cfg<FMT, 4, 2, 2>(g, ws, sm_count, pdl, early, stream);
-        case 2: return launch_cfg<FMT, 4, 1, 3>(g, ws, sm_count, pdl, early, stream);
-        case 3: return launch_cfg<FMT, 8, 1, 4>(g, ws, sm_count, pdl, early, stream);
+        case 0: return launch_cfg<FMT, 8, 1, 2, 2, 2>(g, ws, sm_count, pdl, early, stream);
+        case 1: return launch_cfg<FMT, 4, 2, 2, 2, 2>(g, ws, sm_count, pdl, early, stream);
+        case 2: return launch_cfg<FMT, 4, 1, 2, 3, 2>(g, ws, sm_count, pdl, early, stream);
+        case 3: return launch_cfg<FMT, 8, 1, 2, 4, 1>(g, ws, sm_count, pdl, early, stream);
+        case 4: return launch_cfg<FMT, 4, 2, 1, 3, 3>(g, ws, sm_count, pdl, early, stream);
+        case 5: return launch_cfg<FMT, 4, 2, 1, 4, 2>(g, ws, sm_count, pdl, early, stream);
+        case 6: return launch_cfg<FMT, 8, 2, 1, 2, 2>(g, ws, sm_count, pdl, early, stream);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -535,6 +586,7 @@ template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, const StreamWs &w
 void qgemv_kq_stream_set_config(int index) { ks::g_force_config = index < 0 || index >= ks::N_CONFIGS ? -1 : index; }
 void qgemv_kq_stream_set_ctas_per_sm(int n) { ks::g_ctas_per_sm = n < 0 ? 0 : n; }
 void qgemv_kq_stream_set_debug(int v) { ks::g_debug = v; }
+void qgemv_kq_stream_set_early_ctas(int v) { ks::g_early_ctas = v < 0 ? 0 : v; }
 
 size_t qgemv_kq_stream_ws_bytes(int sm_count, StreamWs *layout) {
     const uint64_t n_pairs = (uint64_t)sm_count * 4 * 128 * 8;  // up to 4 CTAs per SM of 128-row tiles (or 8 of 64-row ones)

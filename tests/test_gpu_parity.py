@@ -241,7 +241,7 @@ def test_gemv_q4k_tensor_core_decode_kernel(be, oracle, config):
 
 
 @pytest.mark.parametrize("fmt,ofmt", [(lp.DType.Q4K, O.Q4_K), (lp.DType.Q5K, O.Q5_K)])
-@pytest.mark.parametrize("config,ctas", [(-1, 0), (0, 1), (0, 2), (1, 0), (2, 0), (2, 3), (3, 0)])
+@pytest.mark.parametrize("config,ctas", [(-1, 0), (0, 1), (0, 2), (1, 0), (2, 0), (2, 1), (3, 0), (4, 0), (4, 2), (5, 0), (6, 0)])
 def test_gemv_balanced_stream_kernel(be, oracle, fmt, ofmt, config, ctas):
     """The balanced-stream tensor-core decode kernel (default for Q4_K from 2 rows, Q5_K from 3) in each of its
     tile configurations and CTA counts, against the oracle and against the dp4a kernel: tiles shared by many
