@@ -563,9 +563,14 @@ static cudaError_t launch_cfg(GemvGroup &g, const StreamWs &ws, int sm_count, bo
     return launch_n<FMT, WARPS, TILES, NB, STAGES, MINB, 1>(one, ws, sm_count, pdl, early, stream);
 }
 
-static int pick_config(const GemvGroup &, int) {
-    // measured: four warps of 16 rows with three stages, two CTAs per SM, is the best layout on every shape tried
-    return g_force_config >= 0 ? g_force_config : 2;
+static int pick_config(const GemvGroup &g, int sm_count) {
+    if (g_force_config >= 0) return g_force_config;
+    // Measured (M = 4, 8): four warps of 16 rows with three stages, two CTAs per SM, up to the 33 MB shapes; from
+    // eight 128-row units per SM on (66 MB) the 32-row warps win, whose activation fragments and scales serve
+    // two row tiles (shared-memory wavefronts, not instruction issue, bound the 16-row layout in the long run).
+    uint64_t units = 0;
+    for (int i = 0; i < g.count; i++) units += (uint64_t)((g.item[i].n + 127) / 128) * ((g.item[i].k / QK + 1) / 2);
+    return units >= 8 * (uint64_t)sm_count ? 1 : 2;
 }
 
 template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {

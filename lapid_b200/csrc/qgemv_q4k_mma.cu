@@ -566,7 +566,8 @@ cudaError_t launch_qgemv_q4k_mma(GemvGroup &g, int sm_count, bool pdl, cudaStrea
             units += (uint64_t)((g.item[i].n + 127) / 128) * ((g.item[i].k / QK + 1) / 2);
         }
         const bool cramped = mm::fixed_smem(mm::CONFIGS[1]) + g.act_bytes > 227 * 1024 - 256;
-        if (units >= 2 * (uint64_t)sm_count && (early || cramped)) return launch_qgemv_kq_stream(FMT_Q4K, g, *ws, sm_count, pdl, stream);
+        if ((units >= 2 * (uint64_t)sm_count && (early || cramped)) || units >= 8 * (uint64_t)sm_count)
+            return launch_qgemv_kq_stream(FMT_Q4K, g, *ws, sm_count, pdl, stream);
     }
     {   // every member early, no tensor-parallel push, and two of the small CTAs fit on an SM: the early instantiation
         bool early = pdl && mm::g_force_config < 0;
