@@ -32,13 +32,14 @@ __device__ __forceinline__ void quantize_group(const ActQuantArgs &p, uint32_t r
 #pragma unroll
     for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     if (p.records == 2) {
-        // tiles of the tensor-core decode kernel: per super-block [sub-block][row][32] quants, then
-        // [row pair][sub-block][2] group scales and the same for d * sum(q)
+        // tiles of the tensor-core decode kernels: per super-block [sub-block][row][32] quants, then the group scales as
+        // [sub-block pair 4][row pair 4][sub-block & 1][row & 1] (the four row pairs of a sub-block pair are 64
+        // consecutive bytes: the lanes' 128-bit reads of them hit distinct banks) and the same for d * sum(q)
         const uint32_t sb = g & 7;
         uint8_t *blk = (uint8_t *)p.qa + (uint64_t)(g >> 3) * (256 * p.rows + 512);
         blk[(sb * p.rows + r) * 32 + lane] = (uint8_t)(int8_t)q;
         if (lane == 0) {
-            float *sc = (float *)(blk + 256 * p.rows) + ((r >> 1) * 8 + sb) * 2 + (r & 1);
+            float *sc = (float *)(blk + 256 * p.rows) + (((sb >> 1) * 4 + (r >> 1)) * 2 + (sb & 1)) * 2 + (r & 1);
             sc[0] = d;
             sc[64] = xmul(d, (float)sum);
         }

@@ -45,7 +45,7 @@ __device__ __forceinline__ void act_quant_quad(const ActOut &o, bool active, uin
         uint8_t *blk = (uint8_t *)o.qa + (uint64_t)(g >> 3) * (256 * o.rows + 512);
         *(uint32_t *)(blk + (sb * o.rows + r) * 32 + e) = packed;
         if (e == 0) {
-            float *sc = (float *)(blk + 256 * o.rows) + ((r >> 1) * 8 + sb) * 2 + (r & 1);
+            float *sc = (float *)(blk + 256 * o.rows) + (((sb >> 1) * 4 + (r >> 1)) * 2 + (sb & 1)) * 2 + (r & 1);
             sc[0] = d;
             sc[64] = bsum;
         }

@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) qgemv_i8_mma_kernel(GemvArgs p)
 #pragma unroll
             for (int blk = 0; blk < 2; blk++) {  // the chunk's two 256-wide activation tiles
                 const uint8_t *ab = acts + (size_t)(2 * it + blk) * ABLK;
-                const float2 *dsp = (const float2 *)(ab + 256 * M + cp * 64);  // {da[c0], da[c1]} per group
+                const float2 *dsp = (const float2 *)(ab + 256 * M) + 2 * cp;  // {da[c0], da[c1]} of group s at [8 * (s >> 1) + (s & 1)]
                 // the f16 scales of this lane's two weight rows for the tile's eight groups
                 const uint4 sw0 = *(const uint4 *)(stage + Q_BYTES + gq * 32 + 16 * blk);
                 const uint4 sw1 = *(const uint4 *)(stage + Q_BYTES + (gq + 8) * 32 + 16 * blk);
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) qgemv_i8_mma_kernel(GemvArgs p)
                     const uint2 b = *(const uint2 *)(ab + s * (M * 32) + colq * 32 + 8 * t4);
                     int c[4];
                     mma_s8(c, a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
-                    const float2 da = dsp[s];
+                    const float2 da = dsp[8 * (s >> 1) + (s & 1)];
                     const float w0 = half_bits_to_float((s0[s >> 1] >> (16 * (s & 1))) & 0xffff);
                     const float w1 = half_bits_to_float((s1[s >> 1] >> (16 * (s & 1))) & 0xffff);
                     acc[0] = fmaf((__int_as_float(c[0]) - MAGIC) * da.x, w0, acc[0]);

@@ -308,13 +308,13 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
                 for (uint32_t bb = 0; bb < (uint32_t)NB; bb++) {
                     if (bb >= nb) break;
                     const uint8_t *ab = ast + (size_t)bb * ABLK;
-                    const float4 *dsp = (const float4 *)(ab + 256 * M + cp * 64);
+                    const float4 *dsp = (const float4 *)(ab + 256 * M) + cp;  // scales: [sub-block pair][row pair][sub-block & 1][row & 1]
                     ulonglong2 dav[4];  // {da[c0], da[c1]} of sub-blocks 2i, 2i + 1
                     float4 bsv[4];
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
-                        dav[i] = ((const ulonglong2 *)dsp)[i];
-                        bsv[i] = dsp[16 + i];
+                        dav[i] = ((const ulonglong2 *)dsp)[4 * i];
+                        bsv[i] = dsp[16 + 4 * i];
                     }
                     const float *bs = (const float *)bsv;  // [sub-block][2]
                     uint2 qh[TILES][2];                    // Q5_K: the fifth bits of this lane's eight k positions, rows gq and gq + 8

@@ -23,8 +23,8 @@
 //    the low nibbles of sub-block 2j and the high nibbles of 2j+1) and activations 8t..8t+7.
 //    High nibbles are used in place (16*q, exact factor 1/16 folded into the scale).
 //  * The pre-pass writes the int8 activations as tiles: per super-block, [sub-block][row][32]
-//    quants, then the group scales as [row pair][sub-block][2] (da) and the same for d*sum(q)
-//    (bs), so a lane's B fragment is one 64-bit load and its scales are 128-bit loads.
+//    quants, then the group scales as [sub-block pair][row pair][sub-block & 1][row & 1] (da) and the same
+//    for d*sum(q) (bs), so a lane's B fragment is one 64-bit load and its scales are conflict-free 128-bit loads.
 //  * The 6-bit scales and mins of a stage are decoded once per (row, super-block) by one lane and
 //    passed through shared memory; a thread needs them for four rows.
 //  * Every mbarrier wait is bounded; a wait that gives up sets the host-visible status word.
@@ -291,13 +291,13 @@ qgemv_q4k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
                         const uint32_t b = TILES == 2 ? ph : bb;
                         if (b >= nb) break;
                         const uint8_t *ab = iacts + (size_t)(2 * it + b) * ABLK;
-                        const float4 *dsp = (const float4 *)(ab + 256 * M + cp * 64);
+                        const float4 *dsp = (const float4 *)(ab + 256 * M) + cp;  // scales: [sub-block pair][row pair][sub-block & 1][row & 1]
                         ulonglong2 dav[4];  // {da[c0], da[c1]} of sub-blocks 2i, 2i + 1
                         float4 bsv[4];
 #pragma unroll
                         for (int i = 0; i < 4; i++) {
-                            dav[i] = ((const ulonglong2 *)dsp)[i];
-                            bsv[i] = dsp[16 + i];
+                            dav[i] = ((const ulonglong2 *)dsp)[4 * i];
+                            bsv[i] = dsp[16 + 4 * i];
                         }
                         const float *bs = (const float *)bsv;  // [sub-block][2]
                         float4 wv[TILES][2][4];  // [tile][row half][W1 0..3, W1 4..7, W2 0..3, W2 4..7]

@@ -183,7 +183,7 @@ qgemv_q6k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
             if (healthy) {
                 const uint8_t *stage = ring + (size_t)cslot * STAGE + ((it * Q6K_BYTES) & 15u);
                 const uint8_t *ab = iacts + (size_t)it * ABLK;
-                const float2 *dsp = (const float2 *)(ab + 256 * M + cp * 64);  // {da[c0], da[c1]} per sub-block
+                const float2 *dsp = (const float2 *)(ab + 256 * M) + 2 * cp;  // {da[c0], da[c1]} of sub-block s at [8 * (s >> 1) + (s & 1)]
 #pragma unroll
                 for (int tl = 0; tl < TILES; tl++) {
                     const uint8_t *b0 = stage + (tl * 16 + gq) * BOX, *b1 = b0 + 8 * BOX;  // this lane's two weight rows
@@ -227,7 +227,7 @@ qgemv_q6k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
                                 tsum[2] += sc1 * c[2];
                                 tsum[3] += sc1 * c[3];
                             }
-                            const float2 da = dsp[s];
+                            const float2 da = dsp[8 * (s >> 1) + (s & 1)];
                             blk[0] = fmaf((float)tsum[0], da.x, blk[0]);
                             blk[1] = fmaf((float)tsum[1], da.y, blk[1]);
                             blk[2] = fmaf((float)tsum[2], da.x, blk[2]);

@@ -114,8 +114,8 @@ def quantize_activations(backend, x: np.ndarray, rows: int, k: int, act_layout: 
 def unpack_activations(act_layout: int, raw: np.ndarray, rows: int, k: int):
     """``(q int8 [rows, k], d f32 [rows, k/32], bs f32 [rows, k/32])`` from the raw bytes of an operand in
     ``act_layout``: planes; 336-byte records, one per (row, 256-block): 4 x [64 quants | d d bs bs], 16 pad; or
-    tiles, one per 256-block: ``[sub-block 8][row][32]`` quants, then ``[row pair 4][sub-block 8][2]`` f32 d and
-    the same for bs."""
+    tiles, one per 256-block: ``[sub-block 8][row][32]`` quants, then f32 d as
+    ``[sub-block pair 4][row pair 4][sub-block & 1][row & 1]`` and the same for bs."""
     raw = np.ascontiguousarray(raw, dtype=np.uint8)
     kg, nblk = k // 32, k // 256
     q = np.zeros((rows, k), np.int8)
@@ -140,8 +140,8 @@ def unpack_activations(act_layout: int, raw: np.ndarray, rows: int, k: int):
         blk = raw[:nblk * ab].reshape(nblk, ab)
         qs = blk[:, :256 * rows].view(np.int8).reshape(nblk, 8, rows, 32)
         q.reshape(rows, nblk, 8, 32)[:] = qs.transpose(2, 0, 1, 3)
-        sc = np.ascontiguousarray(blk[:, 256 * rows:]).view(np.float32).reshape(nblk, 2, 4, 8, 2)  # [d | bs][row pair][sub-block][row & 1]
+        sc = np.ascontiguousarray(blk[:, 256 * rows:]).view(np.float32).reshape(nblk, 2, 4, 4, 2, 2)  # [d | bs][sub-block pair][row pair][sub-block & 1][row & 1]
         for r in range(rows):
-            d.reshape(rows, nblk, 8)[r] = sc[:, 0, r >> 1, :, r & 1]
-            bs.reshape(rows, nblk, 8)[r] = sc[:, 1, r >> 1, :, r & 1]
+            d.reshape(rows, nblk, 8)[r] = sc[:, 0, :, r >> 1, :, r & 1].reshape(nblk, 8)
+            bs.reshape(rows, nblk, 8)[r] = sc[:, 1, :, r >> 1, :, r & 1].reshape(nblk, 8)
     return q, d, bs
