@@ -507,7 +507,7 @@ def gemv_kernel_name(fmt: int, m: int, n: int = 0, k: int = 0) -> str:
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch / algorithmic bytes of that launch, from the ncu
 # captures summarised under profiles/ (weights are read once; the outputs stay in L2). A kernel without a
 # capture reports no traffic.
-DRAM_TRAFFIC_RATIO = {"qgemv_q4k_mma_kernel": 0.985, "qgemv_kq_fast_kernel<q4_k>": 0.9985}
+DRAM_TRAFFIC_RATIO = {"qgemv_kq_stream_kernel<q4_k>": 0.9935, "qgemv_q4k_mma_kernel": 0.985, "qgemv_kq_fast_kernel<q4_k>": 0.9985}
 
 
 def max_rel(got, ref) -> float:

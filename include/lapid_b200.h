@@ -197,6 +197,15 @@ LAPID_B200_API lapid_b200_status lapid_b200_execute_async(lapid_b200_device *dev
 /* Backend::take_profile (backend.rs:59-62) restricted to this path: number of kernels this
  * library launched on `dev` since the last call. */
 LAPID_B200_API uint64_t lapid_b200_take_launch_count(lapid_b200_device *dev);
+/* Diagnostics of the balanced-stream decode kernel (no counterpart in the reference): record, for the next
+ * `launches` launches of that kernel on this process, one row of 16 words per CTA -- [0] entry time (ns, global
+ * timer), then SM clock cycles at [1] entry, [2] first loads issued, [3] first data there, [4] before and [5] after
+ * the wait for the kernel in front, [6] exit; [7] exit time (ns); [8] SM; [9] work units; [10] cycles its first warp
+ * waited for data. `read` copies launches x ctas x 16 words (launch order) and says how many launches were recorded
+ * and how many CTA rows each launch has (rows of CTAs that did not exist are zero). begin(0) frees the buffer. */
+LAPID_B200_API lapid_b200_status lapid_b200_decode_trace_begin(lapid_b200_device *dev, uint32_t launches);
+LAPID_B200_API lapid_b200_status lapid_b200_decode_trace_read(lapid_b200_device *dev, uint64_t *out, uint64_t cap_words,
+                                                               uint32_t *launches, uint32_t *ctas);
 
 /* ---- lapid-quant surface (crates/lapid-quant/src/lib.rs:84-160) ---------------------------- */
 typedef struct lapid_b200_layout {

@@ -71,6 +71,8 @@ SYMBOLS = {
     "lapid_b200_execute": (C.c_int32, [P, C.POINTER(LaunchC), C.c_size_t, C.POINTER(P), C.c_size_t]),
     "lapid_b200_execute_async": (C.c_int32, [P, C.POINTER(LaunchC), C.c_size_t, C.POINTER(P), C.c_size_t]),
     "lapid_b200_take_launch_count": (C.c_uint64, [P]),
+    "lapid_b200_decode_trace_begin": (C.c_int32, [P, C.c_uint32]),
+    "lapid_b200_decode_trace_read": (C.c_int32, [P, P, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "lapid_b200_quant_layout": (C.c_int32, [C.c_int32, C.c_uint64, C.c_uint64, C.POINTER(LayoutC)]),
     "lapid_b200_dequantize": (C.c_int32, [P, C.c_int32, P, C.c_uint64, C.c_uint64, P]),
     "lapid_b200_quantize": (C.c_int32, [P, C.c_int32, P, C.c_uint64, C.c_uint64, P]),

@@ -315,6 +315,20 @@ class Backend:
     def take_launch_count(self) -> int:
         return int(_lib.lib().lapid_b200_take_launch_count(self._h))
 
+    def decode_trace_begin(self, launches: int) -> None:
+        """Record the per-CTA timeline of the next ``launches`` launches of the balanced-stream decode kernel."""
+        check(_lib.lib().lapid_b200_decode_trace_begin(self._h, launches))
+
+    def decode_trace_read(self, max_launches: int) -> np.ndarray:
+        """``[launches, ctas, 16]`` uint64 (see ``lapid_b200_decode_trace_begin`` in the header for the words)."""
+        n, ctas = C.c_uint32(0), C.c_uint32(0)
+        check(_lib.lib().lapid_b200_decode_trace_read(self._h, None, 0, C.byref(n), C.byref(ctas)))
+        rows = min(int(n.value), max_launches)
+        out = np.zeros((max(rows, 1), max(int(ctas.value), 1), 16), np.uint64)
+        if rows:
+            check(_lib.lib().lapid_b200_decode_trace_read(self._h, out.ctypes.data_as(C.c_void_p), out.size, C.byref(n), C.byref(ctas)))
+        return out[:rows]
+
     # ---- lapid-quant on the device
     def quantize_into(self, fmt: int, src: Buffer, rows: int, cols: int, dst: Buffer) -> None:
         check(_lib.lib().lapid_b200_quantize(self._h, int(fmt), src._h, rows, cols, dst._h))

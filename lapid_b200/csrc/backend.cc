@@ -1330,6 +1330,27 @@ lapid_b200_status lapid_b200_execute_async(lapid_b200_device *dev, const lapid_b
 
 uint64_t lapid_b200_take_launch_count(lapid_b200_device *dev) { return dev ? dev->launches.exchange(0) : 0; }
 
+lapid_b200_status lapid_b200_decode_trace_begin(lapid_b200_device *dev, uint32_t launches) {
+    return guard([&] {
+        need(dev);
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        cuda_check(cudaStreamSynchronize(dev->stream), "cudaStreamSynchronize");
+        cuda_check(lb::qgemv_kq_stream_trace_begin(launches, dev->sm_count), "trace buffer");
+    });
+}
+
+lapid_b200_status lapid_b200_decode_trace_read(lapid_b200_device *dev, uint64_t *out, uint64_t cap_words, uint32_t *launches, uint32_t *ctas) {
+    return guard([&] {
+        need(dev);
+        if (!launches || !ctas) fail("invalid_argument", "launches or ctas is NULL");
+        std::lock_guard<std::mutex> lock(dev->mu);
+        dev->make_current();
+        cuda_check(cudaStreamSynchronize(dev->stream), "cudaStreamSynchronize");
+        *launches = lb::qgemv_kq_stream_trace_read((unsigned long long *)out, cap_words, ctas);
+    });
+}
+
 lapid_b200_status lapid_b200_quant_layout(int32_t format, uint64_t rows, uint64_t cols, lapid_b200_layout *out) {
     return guard([&] {
         if (!out) fail("invalid_argument", "out is NULL");

@@ -194,6 +194,8 @@ struct StreamWs {
     uint2 *pairs;
     uint64_t n_pairs;
 };
+cudaError_t qgemv_kq_stream_trace_begin(uint32_t launches, int sm_count);
+uint32_t qgemv_kq_stream_trace_read(unsigned long long *out, uint64_t cap_words, uint32_t *ctas);
 size_t qgemv_kq_stream_ws_bytes(int sm_count, StreamWs *layout);  // bytes to allocate (zero-filled)
 bool qgemv_kq_stream_shape_ok(int fmt, uint32_t rows, uint32_t n, uint32_t k);
 cudaError_t launch_qgemv_kq_stream(int fmt, GemvGroup &group, const StreamWs &ws, int sm_count, bool pdl, cudaStream_t stream);

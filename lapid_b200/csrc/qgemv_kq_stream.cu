@@ -60,6 +60,26 @@ template <int FMT> struct Geo {
 
 __host__ __device__ constexpr uint32_t act_block_bytes(uint32_t rows) { return 256 * rows + 512; }
 
+// Words of a CTA's trace row (SM clock cycles unless stated)
+enum { TR_GT_ENTRY = 0 /* ns */, TR_ENTRY, TR_LOADS_ISSUED, TR_FIRST_DATA, TR_BEFORE_WAIT, TR_AFTER_WAIT, TR_EXIT, TR_GT_EXIT /* ns */,
+       TR_SM, TR_UNITS, TR_STARVED, TR_FLAG_SEEN, TRACE_WORDS = 16 };
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// What a CTA needs before its first copy can start, in one 64-byte line of the parameter space (a new launch finds
+// the constant cache cold: every further line the prologue touches costs a miss in series)
+struct alignas(64) Head {
+    uint32_t rows, nblk, chunks, tiles;  // activation rows; super-blocks per weight row; k-chunks per tile; row tiles of all members
+    uint32_t q, rem;                     // units per span: the first `rem` spans hold q + 1, the others q
+    uint32_t early, pad;
+    const int8_t *qa0;                   // activation tiles of the first member
+    uint2 *pairs;                        // hand-over workspace
+    unsigned long long *trace;           // diagnostics, or null
+};
+
 template <int NG> struct Maps {
     CUtensorMap m[NG];  // packed weights of each member: [n rows][k/256 * BLK/4 words], box ROWB/4 words x tile rows
 };
@@ -67,7 +87,7 @@ template <int NG> struct Maps {
 // NB: super-blocks per k-chunk (1 or 2). MINB: CTAs per SM the register allocation must allow.
 template <int FMT, int WARPS, int TILES, int NB, int STAGES, int MINB, int NG>
 __global__ void __launch_bounds__((WARPS + 1) * 32, MINB)
-qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp, StreamWs ws, uint32_t early) {
+qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, GemvGroupT<NG> grp) {
     constexpr int BLK = Geo<FMT>::BLK, ROWB = NB * BLK, QS = Geo<FMT>::QS;
     constexpr int RPW = 16 * TILES;      // rows per consumer warp
     constexpr int RT = RPW * WARPS;      // rows per tile
@@ -75,15 +95,17 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
     constexpr int EW = 128 * TILES;      // outputs of one warp per tile
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t M = grp.item[0].rows;
-    const uint32_t nblk = grp.item[0].k / QK;
-    const uint32_t C = (nblk + NB - 1) / NB;  // k-chunks per tile
+    const uint32_t M = head.rows, nblk = head.nblk, C = head.chunks, early = head.early;
     const uint32_t ABLK = act_block_bytes(M);
     const uint32_t SBYTES = WBYTES + NB * ABLK;
-    const uint32_t tiles = grp.task_end[grp.count - 1];
-    const uint64_t U = (uint64_t)tiles * C;
-    const uint32_t G = gridDim.x, b = blockIdx.x;
-    const uint32_t u_lo = (uint32_t)(U * b / G), u_hi = (uint32_t)(U * (b + 1) / G);
+    const uint32_t b = blockIdx.x;
+    // Equal shares: the first `rem` spans hold q + 1 units, the others q (q >= 1: the grid never exceeds the units)
+    const uint32_t q = head.q, rem = head.rem;
+    const uint32_t u_lo = b * q + min(b, rem), u_hi = u_lo + q + (b < rem ? 1u : 0u);
+    struct {
+        uint2 *pairs;
+        unsigned long long *trace;
+    } ws = {head.pairs, head.trace};
     auto locate = [&](uint32_t t, uint32_t &local) -> int {
         if constexpr (NG == 1) {
             local = t;
@@ -95,47 +117,71 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
         return i;
     };
 
+    // Timeline of this CTA for the diagnostics call (ws.trace is null unless a trace was asked for): 16 words per CTA
+    unsigned long long *trace = ws.trace ? ws.trace + (size_t)b * TRACE_WORDS : nullptr;
+    auto stamp = [&](int i) {
+        if (trace && lane == 0) trace[i] = (unsigned long long)clock64();
+    };
+    if (trace && threadIdx.x == 0) {
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        trace[TR_GT_ENTRY] = globaltimer_ns();
+        trace[TR_ENTRY] = (unsigned long long)clock64();
+        trace[TR_SM] = smid;
+        trace[TR_UNITS] = u_hi - u_lo;
+    }
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint64_t *full = (uint64_t *)smem, *empty = full + STAGES;
+    volatile uint32_t *front_done = (volatile uint32_t *)(smem + BAR_BYTES - 16);  // set once the kernel in front has completed
     uint8_t *stages = smem + BAR_BYTES;
-    if (threadIdx.x == 0) {
+    // The producer's lane sets the barriers up and asks for the first weights at once; the others meet it below.
+    auto unit = [&](uint32_t i, int &item, uint32_t &local, uint32_t &c, uint32_t &nb) {
+        const uint32_t u = u_lo + i, gt = u / C;
+        c = u - gt * C;
+        item = locate(gt, local);
+        nb = min((uint32_t)NB, nblk - NB * c);
+    };
+    auto load_w = [&](uint32_t i, uint32_t slot) {
+        int item;
+        uint32_t local, c, nb;
+        unit(i, item, local, c, nb);
+        mbar_expect_tx(full + slot, WBYTES + nb * ABLK);  // the whole box counts, zero fill included
+        tma_load_2d(stages + (size_t)slot * SBYTES, &maps.m[item], (int)(c * (ROWB / 4)), (int)(local * RT), full + slot);
+    };
+    auto load_a = [&](uint32_t i, uint32_t slot) {
+        int item;
+        uint32_t local, c, nb;
+        unit(i, item, local, c, nb);
+        const int8_t *qa = NG == 1 ? head.qa0 : grp.item[item].qa;
+        bulk_g2s(stages + (size_t)slot * SBYTES + WBYTES, (const uint8_t *)qa + (size_t)(NB * c) * ABLK, nb * ABLK, full + slot);
+    };
+    const uint32_t nunits = u_hi - u_lo;
+    const uint32_t pre = nunits < (uint32_t)STAGES ? nunits : (uint32_t)STAGES;
+    if (warp == WARPS && lane == 0) {
 #pragma unroll
         for (int s = 0; s < STAGES; s++) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, WARPS);
         }
+        *front_done = 0;
         mbar_fence_init();
+        for (uint32_t i = 0; i < pre; i++) {
+            load_w(i, i);
+            if (early & 1) load_a(i, i);  // (a launch that runs ahead: its activations are older than the kernel in front)
+        }
     }
     __syncthreads();
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == WARPS) {
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
-            const uint32_t nunits = u_hi - u_lo;
-            auto unit = [&](uint32_t i, int &item, uint32_t &local, uint32_t &c, uint32_t &nb) {
-                const uint32_t u = u_lo + i, gt = u / C;
-                c = u - gt * C;
-                item = locate(gt, local);
-                nb = min((uint32_t)NB, nblk - NB * c);
-            };
-            auto load_w = [&](uint32_t i, uint32_t slot) {
-                int item;
-                uint32_t local, c, nb;
-                unit(i, item, local, c, nb);
-                mbar_expect_tx(full + slot, WBYTES + nb * ABLK);  // the whole box counts, zero fill included
-                tma_load_2d(stages + (size_t)slot * SBYTES, &maps.m[item], (int)(c * (ROWB / 4)), (int)(local * RT), full + slot);
-            };
-            auto load_a = [&](uint32_t i, uint32_t slot) {
-                int item;
-                uint32_t local, c, nb;
-                unit(i, item, local, c, nb);
-                bulk_g2s(stages + (size_t)slot * SBYTES + WBYTES, (const uint8_t *)grp.item[item].qa + (size_t)(NB * c) * ABLK, nb * ABLK,
-                         full + slot);
-            };
-            const uint32_t pre = nunits < (uint32_t)STAGES ? nunits : (uint32_t)STAGES;
-            for (uint32_t i = 0; i < pre; i++) load_w(i, i);
-            if (!(early & 1)) asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations come from the kernel in front
-            for (uint32_t i = 0; i < pre; i++) load_a(i, i);
+            if (!(early & 1)) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations come from the kernel in front
+                *front_done = 1;
+                for (uint32_t i = 0; i < pre; i++) load_a(i, i);
+            }
+            stamp(TR_LOADS_ISSUED);
             uint32_t slot = 0, phase = 0;  // phase of `empty[slot]` the next refill waits for
             for (uint32_t i = pre; i < nunits; i++) {
                 if (!mbar_wait(empty + slot, phase)) {
@@ -149,9 +195,17 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
                     phase ^= 1;
                 }
             }
+        } else {
+            // (the idle lanes touch the parameter lines the epilogue reads, so that they are in the constant cache by then)
+            const uint32_t touch = grp.item[0].n ^ (uint32_t)(uintptr_t)grp.item[0].out ^ (uint32_t)grp.item[0].out_rs ^ grp.task_end[0];
+            asm volatile("" ::"r"(touch));
         }
-        // later kernels take this grid's completion as the completion of everything before it
+        __syncwarp();
+        // With every copy of the span requested, the warp waits for the kernel in front and tells the consumers of a
+        // launch that runs ahead that they may write now. Later kernels take this grid's completion as the completion
+        // of everything before it.
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (lane == 0) *front_done = 1;
         return;
     }
 
@@ -163,7 +217,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
     uint8_t *scs = stages + (size_t)STAGES * SBYTES + (size_t)warp * (RPW * NB * SC_STRIDE);  // one slot per (row, super-block) of a stage
     __shared__ TpPushCtx tp_ctx[WARPS];
     bool waited = false, healthy = true;
-    auto owner = [&](uint64_t u) -> uint32_t { return (uint32_t)(((u + 1) * G - 1) / U); };
+    auto owner = [&](uint32_t u) -> uint32_t { return u < rem * (q + 1) ? u / (q + 1) : rem + (u - rem * (q + 1)) / q; };
 
     // One finished segment [c0, c1) of tile gt: store it, hand it to the span that collects the tile, or collect.
     auto finish = [&](uint32_t gt, uint32_t c0, uint32_t c1, float (&acc)[TILES][4]) {
@@ -207,7 +261,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
         // The contributors are the spans right behind this one; theirs is the FIRST thing they compute, so their
         // pairs are usually there already. Sum in span order = k order; take each pair and leave the slot empty
         // for the next launch (which touches the workspace only after this grid has completed).
-        const uint32_t b_last = owner((uint64_t)gt * C + C - 1);
+        const uint32_t b_last = owner(gt * C + C - 1);
         constexpr int NBATCH = 4 / TILES, NE = 4 * TILES;  // contributors asked for at once (their loads are all in flight together)
         for (uint32_t b0 = b + 1; b0 <= b_last && healthy; b0 += NBATCH) {
             uint2 v[NBATCH][NE];
@@ -251,9 +305,20 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
     // parked tiles of a launch that runs ahead (a span of equal shares rarely holds more than two segments)
     float held[HOLD][TILES][4];
     uint32_t npark = 0;
-    const uint32_t park_u0 = u_lo;
+    auto flush_parked = [&]() {  // oldest first: the walk over the span is repeated from its start
+        uint32_t uu = u_lo;
+#pragma unroll
+        for (int qq = 0; qq < HOLD; qq++) {
+            if ((uint32_t)qq >= npark) break;
+            const uint32_t pgt = uu / C, pc0 = uu - pgt * C, pc1 = min(C, pc0 + (u_hi - uu));
+            finish(pgt, pc0, pc1, held[qq]);
+            uu += pc1 - pc0;
+        }
+        npark = 0;
+    };
 
     uint32_t u = u_lo, slot = 0, par = 0;
+    long long starved = 0;  // (trace) cycles warp 0 waited for data
     while (u < u_hi) {
         const uint32_t gt = u / C, c0 = u - gt * C;
         const uint32_t c1 = min(C, c0 + (u_hi - u));
@@ -264,9 +329,21 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
             for (int i = 0; i < 4; i++) acc[tl][i] = 0.0f;
 
         for (uint32_t c = c0; c < c1; c++, u++) {
+            // a launch that runs ahead hands its parked tiles over as soon as the kernel in front has completed
+            // (the spans that collect them are then served without a wait at their end)
+            if (npark && !waited && *front_done) {
+                waited = true;
+                if (warp == 0) stamp(TR_FLAG_SEEN);
+                flush_parked();
+            }
+            const long long t_wait = trace ? clock64() : 0;
             if (healthy && !mbar_wait(full + slot, par)) {
                 healthy = false;
                 if (lane == 0 && grp.item[0].status) atomicOr(grp.item[0].status, 1);
+            }
+            if (trace && warp == 0) {
+                starved += clock64() - t_wait;
+                if (u == u_lo) stamp(TR_FIRST_DATA);
             }
             const uint8_t *wst = stages + (size_t)slot * SBYTES + (size_t)warp * (RPW * ROWB);  // this warp's rows
             const uint8_t *ast = stages + (size_t)slot * SBYTES + WBYTES;
@@ -387,39 +464,46 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, GemvGroupT<NG> grp
 
         // ---- nothing is written, and the workspace is not touched, before the kernel in front has completed. A launch
         //      that may run ahead (early) parks the tile and goes on computing; its stores, hand-overs and
-        //      collections follow once that kernel has completed, or when the parking space is full.
+        //      collections follow once that kernel has completed (the watcher warp says so), or when the parking
+        //      space is full.
+        if (u >= u_hi && warp == 0) stamp(TR_BEFORE_WAIT);
         if ((early & 1) && !waited && healthy) {
+            if (*front_done) {
+                waited = true;
+                if (warp == 0) stamp(TR_FLAG_SEEN);
+                flush_parked();
+            } else {
 #pragma unroll
-            for (int q = 0; q < HOLD; q++)
-                if ((uint32_t)q == npark) {
+                for (int qq = 0; qq < HOLD; qq++)
+                    if ((uint32_t)qq == npark) {
 #pragma unroll
-                    for (int tl = 0; tl < TILES; tl++)
+                        for (int tl = 0; tl < TILES; tl++)
 #pragma unroll
-                        for (int i = 0; i < 4; i++) held[q][tl][i] = acc[tl][i];
-                }
-            if (++npark < (uint32_t)HOLD && u < u_hi) continue;
+                            for (int i = 0; i < 4; i++) held[qq][tl][i] = acc[tl][i];
+                    }
+                if (++npark < (uint32_t)HOLD && u < u_hi) continue;
+            }
         }
         if (!waited) {
             asm volatile("griddepcontrol.wait;" ::: "memory");
             waited = true;
+            if (warp == 0) stamp(TR_AFTER_WAIT);
             if (grp.item[0].tp) {  // only the first member of a launch may push (tensor-parallel launches are never grouped)
                 if (lane == 0) tp_push_ctx_load(&tp_ctx[warp], grp.item[0].tp);
                 __syncwarp();
             }
-            // the parked tiles, oldest first (the walk over the span is repeated from where parking began)
-            uint32_t uu = park_u0;
-#pragma unroll
-            for (int q = 0; q < HOLD; q++) {
-                if ((uint32_t)q >= npark) break;
-                const uint32_t pgt = uu / C, pc0 = uu - pgt * C, pc1 = min(C, pc0 + (u_hi - uu));
-                finish(pgt, pc0, pc1, held[q]);
-                uu += pc1 - pc0;
-            }
-            if (npark) continue;  // (the segment that just ended was the last parked one)
+            const bool parked = npark != 0;  // (then the segment that just ended is the last parked one)
+            flush_parked();
+            if (parked) continue;
         }
         finish(gt, c0, c1, acc);
     }
     if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (trace && warp == 0 && lane == 0) {
+        trace[TR_STARVED] = (unsigned long long)starved;
+        trace[TR_EXIT] = (unsigned long long)clock64();
+        trace[TR_GT_EXIT] = globaltimer_ns();
+    }
 }
 
 // ------------------------------------------------------------------------------------------ host
@@ -492,8 +576,14 @@ struct Config {
 // 4: four warps of 32 rows, one-block chunks, three stages (three CTAs per SM)
 // 5: four warps of 32 rows, one-block chunks, four stages
 // 6: eight warps of 32 rows, one-block chunks, two stages
-static const Config CONFIGS[] = {{8, 1, 2, 2}, {4, 2, 2, 2}, {4, 1, 2, 3}, {8, 1, 2, 4}, {4, 2, 1, 3}, {4, 2, 1, 4}, {8, 2, 1, 2}};
-constexpr int N_CONFIGS = 7;
+// 7: four warps of 16 rows, two-block chunks, two stages (three CTAs per SM)
+// 8: eight warps of 16 rows, one-block chunks, four stages
+// 9: six warps of 16 rows, two-block chunks, two stages
+// 10: four warps of 32 rows, one-block chunks, two stages (three CTAs per SM)
+// 11: four warps of 16 rows, one-block chunks, four stages (three CTAs per SM)
+static const Config CONFIGS[] = {{8, 1, 2, 2}, {4, 2, 2, 2}, {4, 1, 2, 3}, {8, 1, 2, 4}, {4, 2, 1, 3}, {4, 2, 1, 4},
+                                 {8, 2, 1, 2}, {4, 1, 2, 2}, {8, 1, 1, 4}, {6, 1, 2, 2}, {4, 2, 1, 2}, {4, 1, 1, 4}};
+constexpr int N_CONFIGS = 12;
 static int g_force_config = -1;
 static int g_ctas_per_sm = 0;  // 0 = choose
 static int g_debug = 0;        // measurement only: 2 = drop the partial tiles (wrong results)
@@ -502,6 +592,9 @@ static int g_debug = 0;        // measurement only: 2 = drop the partial tiles (
 // is used anyway; on the 33 MB shapes the warps of ONE launch finish it sooner than the same warps spread over
 // two or three launches (10.8 against 14.4 us), so the default is off.
 static int g_early_ctas = 0;
+// Diagnostics: a device buffer of TRACE_WORDS words per CTA for the next `g_trace_cap` launches (row = launch, in launch order)
+static unsigned long long *g_trace = nullptr;
+static uint32_t g_trace_cap = 0, g_trace_next = 0, g_trace_ctas = 0;
 
 static size_t smem_bytes(int fmt, const Config &c, uint32_t rows) {
     const size_t rowb = (size_t)c.nb * (fmt == FMT_Q5K ? Geo<FMT_Q5K>::BLK : Geo<FMT_Q4K>::BLK);
@@ -510,7 +603,7 @@ static size_t smem_bytes(int fmt, const Config &c, uint32_t rows) {
 }
 
 template <int FMT, int WARPS, int TILES, int NB, int STAGES, int MINB, int NG>
-static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
+static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count, bool pdl, bool early, int want_per_sm, cudaStream_t stream) {
     auto kern = qgemv_kq_stream_kernel<FMT, WARPS, TILES, NB, STAGES, MINB, NG>;
     constexpr uint32_t RT = 16 * TILES * WARPS;
     const uint32_t M = g.item[0].rows, C = (g.item[0].k / QK + NB - 1) / NB;
@@ -532,8 +625,10 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count,
     uint32_t per_sm = fit < (uint32_t)MINB ? (fit ? fit : 1) : (uint32_t)MINB;
     // Tuning: a launch that runs ahead of its predecessor may leave CTA slots to the launches around it.
     if (early && fit >= 2 && g_early_ctas > 0) per_sm = (uint32_t)g_early_ctas < per_sm ? (uint32_t)g_early_ctas : per_sm;
+    if (want_per_sm > 0) per_sm = (uint32_t)want_per_sm < per_sm ? (uint32_t)want_per_sm : per_sm;
     if (g_ctas_per_sm > 0) per_sm = (uint32_t)g_ctas_per_sm < per_sm ? (uint32_t)g_ctas_per_sm : per_sm;
     const uint64_t U = (uint64_t)tiles * C;
+    if (U >= (1ull << 31)) return cudaErrorNotSupported;
     uint32_t grid = (uint32_t)sm_count * per_sm;
     if (grid > U) grid = (uint32_t)U;
     // workspace: one partial tile (RT x 8 pairs) per CTA
@@ -548,40 +643,65 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, maps, g, ws, (uint32_t)((early ? 1 : 0) | (g_debug & 2)));
+    Head head = {};
+    head.rows = M;
+    head.nblk = g.item[0].k / QK;
+    head.chunks = C;
+    head.tiles = tiles;
+    head.q = (uint32_t)(U / grid);
+    head.rem = (uint32_t)(U % grid);
+    head.early = (uint32_t)((early ? 1 : 0) | (g_debug & 2));
+    head.qa0 = g.item[0].qa;
+    head.pairs = ws.pairs;
+    if (g_trace && g_trace_next < g_trace_cap && grid <= g_trace_ctas)
+        head.trace = g_trace + (size_t)(g_trace_next++) * g_trace_ctas * TRACE_WORDS;
+    return cudaLaunchKernelEx(&cfg, kern, maps, head, g);
 }
 
 template <int FMT, int WARPS, int TILES, int NB, int STAGES, int MINB>
-static cudaError_t launch_cfg(GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
-    if (g.count > 1) return launch_n<FMT, WARPS, TILES, NB, STAGES, MINB, GEMV_GROUP_MAX>(g, ws, sm_count, pdl, early, stream);
+static cudaError_t launch_cfg(GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, bool early, int per_sm, cudaStream_t stream) {
+    if (g.count > 1) return launch_n<FMT, WARPS, TILES, NB, STAGES, MINB, GEMV_GROUP_MAX>(g, ws, sm_count, pdl, early, per_sm, stream);
     GemvSingle one;  // a lone launch passes a sixth of the parameter bytes
     one.item[0] = g.item[0];
     one.act_off[0] = 0;
     one.act_copy[0] = 0;
     one.count = 1;
     one.act_bytes = 0;
-    return launch_n<FMT, WARPS, TILES, NB, STAGES, MINB, 1>(one, ws, sm_count, pdl, early, stream);
+    return launch_n<FMT, WARPS, TILES, NB, STAGES, MINB, 1>(one, ws, sm_count, pdl, early, per_sm, stream);
 }
 
-static int pick_config(const GemvGroup &g, int sm_count) {
+// Measured (M = 4, 8; early = launches that run ahead of their predecessor, as in a list over one quantized operand):
+//  * four warps of 16 rows, two-block chunks, two stages (57 KB: three CTAs fit on an SM) up to 66 MB; what counts at
+//    these sizes is that the SM is never without a CTA that computes while another starts or hands over, so three
+//    CTAs per SM -- or two with the third slot left to the next launch of the stream when the spans would
+//    otherwise fall below six units (many spans per row tile: more hand-overs than work);
+//  * from sixteen 128-row units per SM on the 32-row warps, whose activation fragments and scales serve two row tiles
+//    (shared-memory wavefronts bound the 16-row layout in the long run).
+static int pick_config(const GemvGroup &g, int sm_count, bool early, int &per_sm) {
+    per_sm = 0;
     if (g_force_config >= 0) return g_force_config;
-    // Measured (M = 4, 8): four warps of 16 rows with three stages, two CTAs per SM, up to the 33 MB shapes; from
-    // eight 128-row units per SM on (66 MB) the 32-row warps win, whose activation fragments and scales serve
-    // two row tiles (shared-memory wavefronts, not instruction issue, bound the 16-row layout in the long run).
-    uint64_t units = 0;
+    uint64_t units = 0;  // 128 rows x 512 k
     for (int i = 0; i < g.count; i++) units += (uint64_t)((g.item[i].n + 127) / 128) * ((g.item[i].k / QK + 1) / 2);
-    return units >= 8 * (uint64_t)sm_count ? 1 : 2;
+    if (units >= 16 * (uint64_t)sm_count) return 1;
+    if (early && 2 * units < 6 * 3 * (uint64_t)sm_count) per_sm = 2;  // (config 7 has 64-row tiles: twice the units)
+    return 7;
 }
 
 template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
-    switch (pick_config(g, sm_count)) {
-        case 0: return launch_cfg<FMT, 8, 1, 2, 2, 2>(g, ws, sm_count, pdl, early, stream);
-        case 1: return launch_cfg<FMT, 4, 2, 2, 2, 2>(g, ws, sm_count, pdl, early, stream);
-        case 2: return launch_cfg<FMT, 4, 1, 2, 3, 2>(g, ws, sm_count, pdl, early, stream);
-        case 3: return launch_cfg<FMT, 8, 1, 2, 4, 1>(g, ws, sm_count, pdl, early, stream);
-        case 4: return launch_cfg<FMT, 4, 2, 1, 3, 3>(g, ws, sm_count, pdl, early, stream);
-        case 5: return launch_cfg<FMT, 4, 2, 1, 4, 2>(g, ws, sm_count, pdl, early, stream);
-        case 6: return launch_cfg<FMT, 8, 2, 1, 2, 2>(g, ws, sm_count, pdl, early, stream);
+    int per_sm = 0;
+    switch (pick_config(g, sm_count, early, per_sm)) {
+        case 0: return launch_cfg<FMT, 8, 1, 2, 2, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 1: return launch_cfg<FMT, 4, 2, 2, 2, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 2: return launch_cfg<FMT, 4, 1, 2, 3, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 3: return launch_cfg<FMT, 8, 1, 2, 4, 1>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 4: return launch_cfg<FMT, 4, 2, 1, 3, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 5: return launch_cfg<FMT, 4, 2, 1, 4, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 6: return launch_cfg<FMT, 8, 2, 1, 2, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 7: return launch_cfg<FMT, 4, 1, 2, 2, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 8: return launch_cfg<FMT, 8, 1, 1, 4, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 9: return launch_cfg<FMT, 6, 1, 2, 2, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 10: return launch_cfg<FMT, 4, 2, 1, 2, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 11: return launch_cfg<FMT, 4, 1, 1, 4, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -592,6 +712,28 @@ void qgemv_kq_stream_set_config(int index) { ks::g_force_config = index < 0 || i
 void qgemv_kq_stream_set_ctas_per_sm(int n) { ks::g_ctas_per_sm = n < 0 ? 0 : n; }
 void qgemv_kq_stream_set_debug(int v) { ks::g_debug = v; }
 void qgemv_kq_stream_set_early_ctas(int v) { ks::g_early_ctas = v < 0 ? 0 : v; }
+
+// Diagnostics: record the timeline of every CTA of the next `launches` launches of this kernel (0 = stop and free).
+cudaError_t qgemv_kq_stream_trace_begin(uint32_t launches, int sm_count) {
+    if (ks::g_trace) cudaFree(ks::g_trace);
+    ks::g_trace = nullptr;
+    ks::g_trace_cap = ks::g_trace_next = 0;
+    if (!launches) return cudaSuccess;
+    ks::g_trace_ctas = (uint32_t)sm_count * 4;
+    const size_t bytes = (size_t)launches * ks::g_trace_ctas * ks::TRACE_WORDS * 8;
+    if (cudaError_t e = cudaMalloc(&ks::g_trace, bytes); e != cudaSuccess) return e;
+    ks::g_trace_cap = launches;
+    return cudaMemset(ks::g_trace, 0, bytes);
+}
+// Copies the rows recorded so far to `out` (launches x ctas x 16 words); returns the launches recorded.
+uint32_t qgemv_kq_stream_trace_read(unsigned long long *out, uint64_t cap_words, uint32_t *ctas) {
+    if (ctas) *ctas = ks::g_trace_ctas;
+    if (!ks::g_trace) return 0;
+    uint64_t words = (uint64_t)ks::g_trace_next * ks::g_trace_ctas * ks::TRACE_WORDS;
+    if (words > cap_words) words = cap_words;
+    if (out && words) cudaMemcpy(out, ks::g_trace, words * 8, cudaMemcpyDeviceToHost);
+    return ks::g_trace_next;
+}
 
 size_t qgemv_kq_stream_ws_bytes(int sm_count, StreamWs *layout) {
     const uint64_t n_pairs = (uint64_t)sm_count * 4 * 128 * 8;  // up to 4 CTAs per SM of 128-row tiles (or 8 of 64-row ones)

@@ -551,10 +551,11 @@ bool qgemv_q4k_mma_group_fits(GemvGroup &g) {
 
 // `ws` set: launches that the balanced-stream kernel (qgemv_kq_stream.cu) runs faster go there. Measured on B200
 // (M = 4 and 8, cold HBM): it wins on matrices with at least two of its 128-row units per SM when the launch may
-// run ahead of its predecessor (every member early: 10.7 / 10.9 us against 11.4 / 14.2 on 14336 x 4096 and
-// 4096 x 14336 at M = 8), and, for dependent launches, where this kernel's activation copy leaves room for only
-// four warps per SM (M = 7, 8 at K = 14336: 12.6 against 14.1 us). Smaller matrices and the other dependent
-// launches stay here: the stream kernel's hand-over of partial tiles between CTAs costs 1 to 2 us at its end.
+// run ahead of its predecessor (every member early: 8.5 / 8.2 us against 10.0 / 13.2 on 14336 x 4096 and
+// 4096 x 14336 at M = 8), and, for dependent launches, from seven rows on (M = 8: 10.2 / 11.6 against 11.3 / 13.2 us;
+// at K = 14336 this kernel's activation copy then leaves room for only four warps per SM) and from eight units
+// per SM on. Smaller matrices and the other dependent launches stay here: the stream kernel's hand-over of
+// partial tiles between CTAs costs about a microsecond at its end.
 cudaError_t launch_qgemv_q4k_mma(GemvGroup &g, int sm_count, bool pdl, cudaStream_t stream, const StreamWs *ws) {
     if (g.count < 1 || g.count > GEMV_GROUP_MAX) return cudaErrorInvalidValue;
     mm::plan_acts(g);
@@ -566,7 +567,7 @@ cudaError_t launch_qgemv_q4k_mma(GemvGroup &g, int sm_count, bool pdl, cudaStrea
             units += (uint64_t)((g.item[i].n + 127) / 128) * ((g.item[i].k / QK + 1) / 2);
         }
         const bool cramped = mm::fixed_smem(mm::CONFIGS[1]) + g.act_bytes > 227 * 1024 - 256;
-        if ((units >= 2 * (uint64_t)sm_count && (early || cramped)) || units >= 8 * (uint64_t)sm_count)
+        if ((units >= 2 * (uint64_t)sm_count && (early || cramped || g.item[0].rows >= 7)) || units >= 8 * (uint64_t)sm_count)
             return launch_qgemv_kq_stream(FMT_Q4K, g, *ws, sm_count, pdl, stream);
     }
     {   // every member early, no tensor-parallel push, and two of the small CTAs fit on an SM: the early instantiation
