@@ -883,7 +883,7 @@ void check_status_word(lapid_b200_device *dev) {
     int st = *dev->status_host;
     *dev->status_host = 0;
     // a launch that gave up may have left partial sums in the decode workspace
-    cudaMemsetAsync(dev->stream_ws.pairs, 0, dev->stream_ws.n_pairs * 8, dev->stream);
+    cudaMemsetAsync(dev->stream_ws.pairs, 0, dev->stream_ws.total_bytes, dev->stream);
     cudaStreamSynchronize(dev->stream);
     if (st == 128) fail("index_out_of_range", "an index of a gather or an expert id of a matmul_id is out of range; the rows it selects were not computed");
     fail("backend", "a device-side wait gave up (status " + std::to_string(st) + "); the results of this call are invalid");
@@ -1114,6 +1114,7 @@ lapid_b200_status lapid_b200_device_open(int32_t ordinal, lapid_b200_device **ou
             void *ws = nullptr;
             cuda_check(cudaMalloc(&ws, ws_bytes), "cudaMalloc(decode workspace)");
             d->stream_ws.pairs = (uint2 *)ws;
+            d->stream_ws.stage = (uint8_t *)ws + d->stream_ws.n_pairs * 8;
             cuda_check(cudaMemset(ws, 0, ws_bytes), "cudaMemset(decode workspace)");
         } catch (...) {
             delete d;
@@ -1196,6 +1197,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             lb::qgemv_kq_stream_set_ctas_per_sm(std::atoi(value));
         } else if (k == "gemv_stream_early_ctas") {
             lb::qgemv_kq_stream_set_early_ctas(std::atoi(value));
+        } else if (k == "gemv_stream_final_tiles") {
+            lb::qgemv_kq_stream_set_final_tiles(std::atoi(value));
         } else if (k == "gemv_stream_debug") {
             lb::qgemv_kq_stream_set_debug(std::atoi(value));
         } else if (k == "gemv_two_row_dp4a") {

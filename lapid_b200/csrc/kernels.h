@@ -184,24 +184,31 @@ bool qgemv_q4k_mma_shape_ok(uint32_t rows, uint32_t k);
 size_t qgemv_q4k_mma_act_bytes(uint32_t rows, uint32_t k);
 bool qgemv_q4k_mma_group_fits(GemvGroup &group);
 struct StreamWs;
-cudaError_t launch_qgemv_q4k_mma(GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream, const StreamWs *ws = nullptr);
+cudaError_t launch_qgemv_q4k_mma(GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream, StreamWs *ws = nullptr);
 void qgemv_q4k_mma_set_config(int index);  // -1 = pick by shared-memory fit
 // ---- qgemv_kq_stream.cu: Q4_K / Q5_K decode on the same instruction as one stream of equal work shares
-// (2..8 rows; any K that is a multiple of 256; same activation tiles). Spans that hold only some k-chunks
-// of a row tile hand their partial sums over in a workspace in global memory: `pairs` ({f32 value, u32 flag},
-// all zero between launches); one workspace per device serves every launch of its stream.
+// (2..8 rows; any K that is a multiple of 256; same activation tiles). One workspace per device serves every launch
+// of its stream (all zero between launches): `pairs` ({f32 value, u32 flag}) through which the spans of a dependent
+// launch hand partial tiles to each other, and behind it the staging regions of the launches that run ahead of their
+// predecessor (control words + partial tiles), which the launcher hands out in rotation (launches of one device are
+// serialised by its owner).
 struct StreamWs {
     uint2 *pairs;
     uint64_t n_pairs;
+    uint8_t *stage;        // STAGE_REGIONS x (control words, partial tiles)
+    uint64_t total_bytes;  // of the whole allocation, from `pairs` on
+    uint32_t next_region, next_id;
 };
+// Diagnostics: per-CTA timeline rows of the next `launches` launches (16 words per CTA; see include/lapid_b200.h)
 cudaError_t qgemv_kq_stream_trace_begin(uint32_t launches, int sm_count);
 uint32_t qgemv_kq_stream_trace_read(unsigned long long *out, uint64_t cap_words, uint32_t *ctas);
 size_t qgemv_kq_stream_ws_bytes(int sm_count, StreamWs *layout);  // bytes to allocate (zero-filled)
 bool qgemv_kq_stream_shape_ok(int fmt, uint32_t rows, uint32_t n, uint32_t k);
-cudaError_t launch_qgemv_kq_stream(int fmt, GemvGroup &group, const StreamWs &ws, int sm_count, bool pdl, cudaStream_t stream);
+cudaError_t launch_qgemv_kq_stream(int fmt, GemvGroup &group, StreamWs &ws, int sm_count, bool pdl, cudaStream_t stream);
 void qgemv_kq_stream_set_config(int index);     // tuning: -1 = choose
 void qgemv_kq_stream_set_ctas_per_sm(int n);    // tuning: 0 = choose
 void qgemv_kq_stream_set_debug(int v);          // measurement only: 2 = drop partial tiles (wrong results)
+void qgemv_kq_stream_set_final_tiles(int v);    // tuning: row tiles per finalising CTA of a launch that runs ahead (0 = choose)
 void qgemv_kq_stream_set_early_ctas(int v);     // tuning: CTAs per SM of a launch that runs ahead of its predecessor (0 = as any launch)
 // Int8 planes on the same instruction (K a multiple of 512); same activation tiles.
 bool qgemv_i8_mma_shape_ok(uint32_t rows, uint32_t k);

@@ -15,18 +15,26 @@
 //  * Each consumer warp owns 16*TILES rows of the tile and keeps their 16x8 accumulators in registers
 //    over all k-chunks of its span: no cross-warp reduction, no CTA-wide barrier in the main loop. A
 //    warp releases a stage with one mbarrier arrive.
-//  * A span that covers all k-chunks of a tile stores it directly. Otherwise the span that holds the tile's
-//    first k-chunk adds up and stores, and the spans behind it hand it their partial 16x8 tiles through a
-//    workspace in global memory as {value, flag} pairs (one aligned 8-byte store each, never torn: no fence,
-//    no atomic). A contributor's share of such a tile is the first thing it computes and the collector's
-//    share the last thing, so the pairs are normally there when they are asked for; the collector's polls
-//    are bounded all the same. It sums in span order (= k order), so the result does not depend on timing,
-//    and clears the pairs it took. All CTAs of a launch are resident together (the grid never exceeds the
-//    CTAs the SMs hold), so a collector never polls a CTA that cannot run.
-//  * Programmatic dependent launch: weights are requested before the dependency wait; a launch whose
-//    activations are older than the kernel in front of it (GemvArgs::early) also fetches them and
-//    computes its first tile before the wait. Nothing is written, and the workspace is not touched, before
-//    the kernel in front has completed, so consecutive launches share one workspace.
+//  * Programmatic dependent launch: weights are requested before the dependency wait. What happens to a finished
+//    segment of a tile depends on whether the launch may run ahead of the kernel in front of it:
+//    - A dependent launch (its activations come from that kernel) waits before it loads them, so by the time a
+//      segment is finished it may write. A span that covers all k-chunks of a tile stores it directly. Otherwise
+//      the span that holds the tile's first k-chunk adds up and stores, and the spans behind it hand it their
+//      partial 16x8 tiles through a workspace in global memory as {value, flag} pairs (one aligned 8-byte store
+//      each, never torn: no fence, no atomic). A contributor's share of such a tile is the first thing it computes
+//      and the collector's share the last thing, so the pairs are normally there when they are asked for; the
+//      collector's polls are bounded all the same. It sums in span order (= k order) and clears the pairs it took.
+//      All CTAs of a launch are resident together (the grid never exceeds the CTAs the SMs hold), so a collector
+//      never polls a CTA that cannot run.
+//    - A launch that runs ahead (GemvArgs::early: everything it reads is older than the kernel in front) must not
+//      write its output before that kernel has completed, and a CTA that waited for that would keep its place on
+//      the SM from the next launch. So its CTAs only STAGE: every segment goes to a slot (tile, piece) of a staging
+//      region in global memory that belongs to this launch alone, the warp counts itself done (fence + atomic) and
+//      leaves. The CTAs of the last F spans stay: when every warp of the launch is counted they wait for the kernel
+//      in front, add the pieces of their tiles up in k order and store them. Nobody polls for a neighbour, nobody
+//      but those F CTAs waits, and the result does not depend on timing. A staging region is claimed with a
+//      compare-and-swap on its owner word by the first CTA that gets there and released by the last finaliser, so
+//      two launches in flight never share one whatever the order in which their CTAs run.
 //  * Every mbarrier wait is bounded; a wait that gives up sets the host-visible status word.
 #include <cuda.h>
 
@@ -45,7 +53,9 @@ using namespace pipe;
 constexpr int BAR_BYTES = 128;
 constexpr int SC_STRIDE = 80;  // decoded scales of one (row, super-block): 16 floats, padded against bank conflicts
 constexpr uint32_t PAIR_SPIN_LIMIT = 1u << 20;  // polls of a partial-sum pair before the kernel gives up
-constexpr int HOLD = 2;                         // tiles a warp of a launch that runs ahead keeps in registers before it has to wait
+constexpr int STAGE_REGIONS = 8;                 // staging regions, taken in rotation by the launches that run ahead
+constexpr uint64_t STAGE_BYTES = 8ull << 20;     // pairs of one region
+constexpr int WORDS_BYTES = 256;                 // control words in front of a region (see the claim in the kernel)
 
 __device__ __forceinline__ uint2 ld_pair(const void *p) {
     uint2 v;
@@ -62,7 +72,7 @@ __host__ __device__ constexpr uint32_t act_block_bytes(uint32_t rows) { return 2
 
 // Words of a CTA's trace row (SM clock cycles unless stated)
 enum { TR_GT_ENTRY = 0 /* ns */, TR_ENTRY, TR_LOADS_ISSUED, TR_FIRST_DATA, TR_BEFORE_WAIT, TR_AFTER_WAIT, TR_EXIT, TR_GT_EXIT /* ns */,
-       TR_SM, TR_UNITS, TR_STARVED, TR_FLAG_SEEN, TRACE_WORDS = 16 };
+       TR_SM, TR_UNITS, TR_STARVED, TR_FLAG_SEEN, TR_BARS_READY, TR_FIRST_ISSUED, TR_AFTER_SYNC, TRACE_WORDS = 16 };
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -74,10 +84,14 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 struct alignas(64) Head {
     uint32_t rows, nblk, chunks, tiles;  // activation rows; super-blocks per weight row; k-chunks per tile; row tiles of all members
     uint32_t q, rem;                     // units per span: the first `rem` spans hold q + 1, the others q
-    uint32_t early, pad;
+    uint32_t early, pieces;              // early: bit 0 runs ahead (stages), bit 1 measurement only; pieces: staging slots per tile
     const int8_t *qa0;                   // activation tiles of the first member
-    uint2 *pairs;                        // hand-over workspace
+    uint2 *pairs;                        // hand-over workspace of dependent launches
     unsigned long long *trace;           // diagnostics, or null
+    // ---- second line: read at the end of a segment
+    uint2 *stage;                        // staging region of a launch that runs ahead: {value, flag} pairs
+    uint32_t *words;                     // its control words
+    uint32_t launch_id, nfinal;          // owner value; CTAs that finalise (the last spans)
 };
 
 template <int NG> struct Maps {
@@ -106,6 +120,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
         uint2 *pairs;
         unsigned long long *trace;
     } ws = {head.pairs, head.trace};
+    const uint32_t G = gridDim.x;
     auto locate = [&](uint32_t t, uint32_t &local) -> int {
         if constexpr (NG == 1) {
             local = t;
@@ -133,7 +148,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint64_t *full = (uint64_t *)smem, *empty = full + STAGES;
-    volatile uint32_t *front_done = (volatile uint32_t *)(smem + BAR_BYTES - 16);  // set once the kernel in front has completed
+    volatile uint32_t *region_ok = (volatile uint32_t *)(smem + BAR_BYTES - 16);  // the tag of this launch's pairs once the staging region is its own; ~0: the claim gave up
     uint8_t *stages = smem + BAR_BYTES;
     // The producer's lane sets the barriers up and asks for the first weights at once; the others meet it below.
     auto unit = [&](uint32_t i, int &item, uint32_t &local, uint32_t &c, uint32_t &nb) {
@@ -164,22 +179,53 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
             mbar_init(full + s, 1);
             mbar_init(empty + s, WARPS);
         }
-        *front_done = 0;
+        *region_ok = 0;
         mbar_fence_init();
+        stamp(TR_BARS_READY);
         for (uint32_t i = 0; i < pre; i++) {
             load_w(i, i);
             if (early & 1) load_a(i, i);  // (a launch that runs ahead: its activations are older than the kernel in front)
+            if (i == 0) stamp(TR_FIRST_ISSUED);
         }
     }
     __syncthreads();
+    if (warp == 0) stamp(TR_AFTER_SYNC);
 
     if (warp == WARPS) {
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
             if (!(early & 1)) {
                 asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations come from the kernel in front
-                *front_done = 1;
                 for (uint32_t i = 0; i < pre; i++) load_a(i, i);
+            } else {
+                // Claim the staging region. Control words: {owner (launch id, 0 = free), tag} as one 64-bit word, then the
+                // count of finalising warps that are done. Whoever swaps its id into a free word first takes the next tag
+                // with it -- the use counter of the region: pairs of earlier uses never match it, so slots need not be
+                // emptied; the other CTAs of the launch find the id there and take the tag. The last finalising warp
+                // frees the word again. A launch that finds the region owned by an earlier one waits for that (the earlier
+                // launch depends on nothing this one does).
+                unsigned long long *ot = (unsigned long long *)head.words;
+                uint32_t tag = 0xFFFFFFFFu;
+                for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT; spin++) {
+                    const unsigned long long r = *(volatile unsigned long long *)ot;
+                    const uint32_t o = (uint32_t)r;
+                    if (o == head.launch_id) {
+                        tag = (uint32_t)(r >> 32);
+                        break;
+                    }
+                    if (o == 0) {
+                        uint32_t next = (uint32_t)(r >> 32) + 1;
+                        if (next == 0 || next == 0xFFFFFFFFu) next = 1;
+                        if (atomicCAS(ot, r, ((unsigned long long)next << 32) | head.launch_id) == r) {
+                            tag = next;
+                            break;
+                        }
+                        continue;
+                    }
+                    __nanosleep(64);
+                }
+                if (tag == 0xFFFFFFFFu && grp.item[0].status) atomicOr(grp.item[0].status, 1);
+                *region_ok = tag;
             }
             stamp(TR_LOADS_ISSUED);
             uint32_t slot = 0, phase = 0;  // phase of `empty[slot]` the next refill waits for
@@ -197,15 +243,10 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
             }
         } else {
             // (the idle lanes touch the parameter lines the epilogue reads, so that they are in the constant cache by then)
-            const uint32_t touch = grp.item[0].n ^ (uint32_t)(uintptr_t)grp.item[0].out ^ (uint32_t)grp.item[0].out_rs ^ grp.task_end[0];
+            const uint32_t touch = grp.item[0].n ^ (uint32_t)(uintptr_t)grp.item[0].out ^ (uint32_t)grp.item[0].out_rs ^ grp.task_end[0] ^
+                                   head.launch_id;
             asm volatile("" ::"r"(touch));
         }
-        __syncwarp();
-        // With every copy of the span requested, the warp waits for the kernel in front and tells the consumers of a
-        // launch that runs ahead that they may write now. Later kernels take this grid's completion as the completion
-        // of everything before it.
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (lane == 0) *front_done = 1;
         return;
     }
 
@@ -219,30 +260,57 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
     bool waited = false, healthy = true;
     auto owner = [&](uint32_t u) -> uint32_t { return u < rem * (q + 1) ? u / (q + 1) : rem + (u - rem * (q + 1)) / q; };
 
-    // One finished segment [c0, c1) of tile gt: store it, hand it to the span that collects the tile, or collect.
-    auto finish = [&](uint32_t gt, uint32_t c0, uint32_t c1, float (&acc)[TILES][4]) {
-        if (!healthy) return;
+    // Writes a finished tile of member `item` (rows local*RT.. of it), epilogue included.
+    auto store = [&](uint32_t gt, uint32_t w, const float (&v)[TILES][4]) {  // w: the warp slice of the tile
         uint32_t local;
         const int item = locate(gt, local);
         const GemvArgs &p = grp.item[item];
-        auto store = [&](const float (&v)[TILES][4]) {
 #pragma unroll
-            for (int tl = 0; tl < TILES; tl++)
+        for (int tl = 0; tl < TILES; tl++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t row = local * RT + warp * RPW + tl * 16 + gq + ((i & 2) ? 8 : 0);
-                    const uint32_t r = 2 * t4 + (i & 1);
-                    if (row < p.n && r < M) {
-                        float x = v[tl][i];
-                        const uint32_t bt = r / p.m, ri = r % p.m;
-                        if (p.extra) x += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
-                        if (p.tp) tp_push_value(&tp_ctx[warp], (uint64_t)r * p.n + row, x);  // row-parallel partial: to every rank
-                        else p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = x;
-                    }
+            for (int i = 0; i < 4; i++) {
+                const uint32_t row = local * RT + w * RPW + tl * 16 + gq + ((i & 2) ? 8 : 0);
+                const uint32_t r = 2 * t4 + (i & 1);
+                if (row < p.n && r < M) {
+                    float x = v[tl][i];
+                    const uint32_t bt = r / p.m, ri = r % p.m;
+                    if (p.extra) x += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
+                    if (p.tp) tp_push_value(&tp_ctx[warp], (uint64_t)r * p.n + row, x);  // row-parallel partial: to every rank
+                    else p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = x;
                 }
-        };
+            }
+    };
+    constexpr int NE = 4 * TILES;  // accumulators of a lane
+    // ---- a launch that runs ahead: segment [c0, ..) of tile gt goes to its staging slot (tile, piece); the piece is
+    //      the position of this span among the spans that share the tile
+    auto stage_slot = [&](uint32_t gt, uint32_t piece, uint32_t w) {
+        return head.stage + (((size_t)gt * head.pieces + piece) * WARPS + w) * EW + lane;
+    };
+    auto region_tag = [&]() -> uint32_t {
+        uint32_t tag = *region_ok;
+        for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT && tag == 0; spin++) {
+            __nanosleep(32);
+            tag = *region_ok;
+        }
+        if (tag == 0 || tag == 0xFFFFFFFFu) {
+            healthy = false;
+            tag = 0xFFFFFFFFu;
+        }
+        return tag;
+    };
+    auto stage_out = [&](uint32_t gt, const float (&acc)[TILES][4]) {
+        const uint32_t tag = region_tag();
+        if (!healthy) return;
+        uint2 *dst = stage_slot(gt, b - owner(gt * C), warp);
+#pragma unroll
+        for (int e = 0; e < NE; e++) st_pair(dst + e * 32, acc[e / 4][e % 4], tag);
+    };
+    // ---- a dependent launch. One finished segment [c0, c1) of tile gt: store it, hand it to the span that collects
+    //      the tile, or collect.
+    auto finish = [&](uint32_t gt, uint32_t c0, uint32_t c1, float (&acc)[TILES][4]) {
+        if (!healthy) return;
         if (c0 == 0 && c1 == C) {
-            store(acc);
+            store(gt, warp, acc);
             return;
         }
         if (early & 2) return;  // measurement only (option gemv_stream_debug): partial tiles are dropped, the results are wrong
@@ -250,19 +318,17 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
         //      up and stores; the others hand it their partial sums through the workspace as {value, 1} pairs
         //      (an aligned 8-byte store is never torn, so a pair whose flag is set carries its value: no fence,
         //      no counter). Only the first segment of a span can lack its tile's head, so a CTA has one slot.
-        uint2 *mine = ws.pairs + ((size_t)b * WARPS + warp) * EW;
         if (c0 != 0) {
+            uint2 *mine = ws.pairs + ((size_t)b * WARPS + warp) * EW;
 #pragma unroll
-            for (int tl = 0; tl < TILES; tl++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) st_pair(mine + (tl * 4 + i) * 32 + lane, acc[tl][i], 1u);
+            for (int e = 0; e < NE; e++) st_pair(mine + e * 32 + lane, acc[e / 4][e % 4], 1u);
             return;
         }
         // The contributors are the spans right behind this one; theirs is the FIRST thing they compute, so their
         // pairs are usually there already. Sum in span order = k order; take each pair and leave the slot empty
         // for the next launch (which touches the workspace only after this grid has completed).
         const uint32_t b_last = owner(gt * C + C - 1);
-        constexpr int NBATCH = 4 / TILES, NE = 4 * TILES;  // contributors asked for at once (their loads are all in flight together)
+        constexpr int NBATCH = 4 / TILES;  // contributors asked for at once (their loads are all in flight together)
         for (uint32_t b0 = b + 1; b0 <= b_last && healthy; b0 += NBATCH) {
             uint2 v[NBATCH][NE];
             auto slot_of = [&](int j, int e) { return ws.pairs + ((size_t)(b0 + j) * WARPS + warp) * EW + e * 32 + lane; };
@@ -299,22 +365,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
             if (lane == 0 && grp.item[0].status) atomicOr(grp.item[0].status, 1);
             return;
         }
-        store(acc);
-    };
-
-    // parked tiles of a launch that runs ahead (a span of equal shares rarely holds more than two segments)
-    float held[HOLD][TILES][4];
-    uint32_t npark = 0;
-    auto flush_parked = [&]() {  // oldest first: the walk over the span is repeated from its start
-        uint32_t uu = u_lo;
-#pragma unroll
-        for (int qq = 0; qq < HOLD; qq++) {
-            if ((uint32_t)qq >= npark) break;
-            const uint32_t pgt = uu / C, pc0 = uu - pgt * C, pc1 = min(C, pc0 + (u_hi - uu));
-            finish(pgt, pc0, pc1, held[qq]);
-            uu += pc1 - pc0;
-        }
-        npark = 0;
+        store(gt, warp, acc);
     };
 
     uint32_t u = u_lo, slot = 0, par = 0;
@@ -329,13 +380,6 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
             for (int i = 0; i < 4; i++) acc[tl][i] = 0.0f;
 
         for (uint32_t c = c0; c < c1; c++, u++) {
-            // a launch that runs ahead hands its parked tiles over as soon as the kernel in front has completed
-            // (the spans that collect them are then served without a wait at their end)
-            if (npark && !waited && *front_done) {
-                waited = true;
-                if (warp == 0) stamp(TR_FLAG_SEEN);
-                flush_parked();
-            }
             const long long t_wait = trace ? clock64() : 0;
             if (healthy && !mbar_wait(full + slot, par)) {
                 healthy = false;
@@ -462,29 +506,12 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
             }
         }
 
-        // ---- nothing is written, and the workspace is not touched, before the kernel in front has completed. A launch
-        //      that may run ahead (early) parks the tile and goes on computing; its stores, hand-overs and
-        //      collections follow once that kernel has completed (the watcher warp says so), or when the parking
-        //      space is full.
         if (u >= u_hi && warp == 0) stamp(TR_BEFORE_WAIT);
-        if ((early & 1) && !waited && healthy) {
-            if (*front_done) {
-                waited = true;
-                if (warp == 0) stamp(TR_FLAG_SEEN);
-                flush_parked();
-            } else {
-#pragma unroll
-                for (int qq = 0; qq < HOLD; qq++)
-                    if ((uint32_t)qq == npark) {
-#pragma unroll
-                        for (int tl = 0; tl < TILES; tl++)
-#pragma unroll
-                            for (int i = 0; i < 4; i++) held[qq][tl][i] = acc[tl][i];
-                    }
-                if (++npark < (uint32_t)HOLD && u < u_hi) continue;
-            }
+        if (early & 1) {  // runs ahead: nothing is written but the staging region
+            if (healthy) stage_out(gt, acc);
+            continue;
         }
-        if (!waited) {
+        if (!waited) {  // (the producer has waited already before it asked for the activations: this returns at once)
             asm volatile("griddepcontrol.wait;" ::: "memory");
             waited = true;
             if (warp == 0) stamp(TR_AFTER_WAIT);
@@ -492,13 +519,89 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
                 if (lane == 0) tp_push_ctx_load(&tp_ctx[warp], grp.item[0].tp);
                 __syncwarp();
             }
-            const bool parked = npark != 0;  // (then the segment that just ended is the last parked one)
-            flush_parked();
-            if (parked) continue;
         }
         finish(gt, c0, c1, acc);
     }
-    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if ((early & 1) && b + head.nfinal >= G) {
+        // ---- one of the last spans. Its warps take the (tile, warp slice) items of the launch in turn, two at a time: wait
+        //      for the pieces (they are {value, tag} pairs: a pair that carries this launch's tag carries its value), add
+        //      them up in k order and -- once the kernel in front has completed -- store the result.
+        const uint32_t nfinal = head.nfinal, items = head.tiles * WARPS, stride = nfinal * WARPS;
+        const uint32_t tag = region_tag();
+        if (warp == 0) stamp(TR_FLAG_SEEN);
+        constexpr int PB = 4 / TILES;  // pieces of an item asked for at once
+        for (uint32_t it = (b - (G - nfinal)) * WARPS + warp; it < items && healthy; it += 2 * stride) {
+            uint32_t t[2], w[2], np[2];
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                const uint32_t i = it + k * stride;
+                t[k] = i / WARPS;
+                w[k] = i - t[k] * WARPS;
+                np[k] = i < items ? owner(t[k] * C + C - 1) - owner(t[k] * C) + 1 : 0;
+            }
+            float acc[2][TILES][4];
+#pragma unroll
+            for (int k = 0; k < 2; k++)
+#pragma unroll
+                for (int e = 0; e < NE; e++) acc[k][e / 4][e % 4] = 0.0f;
+            for (uint32_t p0 = 0; p0 < max(np[0], np[1]) && healthy; p0 += PB) {
+                uint2 v[2][PB][NE];
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+#pragma unroll
+                    for (int j = 0; j < PB; j++)
+#pragma unroll
+                        for (int e = 0; e < NE; e++)
+                            v[k][j][e] = p0 + j < np[k] ? ld_pair(stage_slot(t[k], p0 + j, w[k]) + e * 32) : make_uint2(0u, tag);
+                for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT; spin++) {
+                    bool all = true;
+#pragma unroll
+                    for (int k = 0; k < 2; k++)
+#pragma unroll
+                        for (int j = 0; j < PB; j++)
+#pragma unroll
+                            for (int e = 0; e < NE; e++) all = all && v[k][j][e].y == tag;
+                    if (all) break;
+#pragma unroll
+                    for (int k = 0; k < 2; k++)
+#pragma unroll
+                        for (int j = 0; j < PB; j++)
+#pragma unroll
+                            for (int e = 0; e < NE; e++)
+                                if (v[k][j][e].y != tag) v[k][j][e] = ld_pair(stage_slot(t[k], p0 + j, w[k]) + e * 32);
+                }
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+#pragma unroll
+                    for (int j = 0; j < PB; j++)
+#pragma unroll
+                        for (int e = 0; e < NE; e++) {
+                            if (v[k][j][e].y != tag) healthy = false;
+                            if (p0 + j < np[k]) acc[k][e / 4][e % 4] += __uint_as_float(v[k][j][e].x);
+                        }
+            }
+            healthy = __all_sync(0xffffffffu, healthy);
+            if (!waited) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                waited = true;
+                if (warp == 0) stamp(TR_AFTER_WAIT);
+            }
+            if (healthy && !(early & 2)) {
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+                    if (np[k]) store(t[k], w[k], acc[k]);
+            }
+        }
+        if (!healthy && lane == 0 && grp.item[0].status) atomicOr(grp.item[0].status, 1);
+        if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");  // (later kernels take this grid's completion as that of everything before it)
+        // this warp has read what it will ever read of the region; the last one to say so frees it
+        __syncwarp();
+        if (lane == 0 && atomicAdd(head.words + 2, 1u) == stride - 1) {
+            head.words[2] = 0;
+            __threadfence();
+            *(volatile uint32_t *)head.words = 0;  // (the tag stays: the next owner counts on from it)
+        }
+    }
     if (trace && warp == 0 && lane == 0) {
         trace[TR_STARVED] = (unsigned long long)starved;
         trace[TR_EXIT] = (unsigned long long)clock64();
@@ -581,9 +684,12 @@ struct Config {
 // 9: six warps of 16 rows, two-block chunks, two stages
 // 10: four warps of 32 rows, one-block chunks, two stages (three CTAs per SM)
 // 11: four warps of 16 rows, one-block chunks, four stages (three CTAs per SM)
-static const Config CONFIGS[] = {{8, 1, 2, 2}, {4, 2, 2, 2}, {4, 1, 2, 3}, {8, 1, 2, 4}, {4, 2, 1, 3}, {4, 2, 1, 4},
-                                 {8, 2, 1, 2}, {4, 1, 2, 2}, {8, 1, 1, 4}, {6, 1, 2, 2}, {4, 2, 1, 2}, {4, 1, 1, 4}};
-constexpr int N_CONFIGS = 12;
+// 12: three warps of 16 rows, two-block chunks, two stages (four CTAs per SM)
+// 13: two warps of 16 rows, two-block chunks, two stages (five CTAs per SM)
+// 14: three warps of 16 rows, two-block chunks, three stages (three CTAs per SM)
+static const Config CONFIGS[] = {{8, 1, 2, 2}, {4, 2, 2, 2}, {4, 1, 2, 3}, {8, 1, 2, 4}, {4, 2, 1, 3}, {4, 2, 1, 4}, {8, 2, 1, 2}, {4, 1, 2, 2},
+                                 {8, 1, 1, 4}, {6, 1, 2, 2}, {4, 2, 1, 2}, {4, 1, 1, 4}, {3, 1, 2, 2}, {2, 1, 2, 2}, {3, 1, 2, 3}};
+constexpr int N_CONFIGS = 15;
 static int g_force_config = -1;
 static int g_ctas_per_sm = 0;  // 0 = choose
 static int g_debug = 0;        // measurement only: 2 = drop the partial tiles (wrong results)
@@ -592,6 +698,7 @@ static int g_debug = 0;        // measurement only: 2 = drop the partial tiles (
 // is used anyway; on the 33 MB shapes the warps of ONE launch finish it sooner than the same warps spread over
 // two or three launches (10.8 against 14.4 us), so the default is off.
 static int g_early_ctas = 0;
+static int g_final_tiles = 0;  // tuning: row tiles per finalising CTA of a launch that runs ahead (0 = choose)
 // Diagnostics: a device buffer of TRACE_WORDS words per CTA for the next `g_trace_cap` launches (row = launch, in launch order)
 static unsigned long long *g_trace = nullptr;
 static uint32_t g_trace_cap = 0, g_trace_next = 0, g_trace_ctas = 0;
@@ -603,7 +710,7 @@ static size_t smem_bytes(int fmt, const Config &c, uint32_t rows) {
 }
 
 template <int FMT, int WARPS, int TILES, int NB, int STAGES, int MINB, int NG>
-static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count, bool pdl, bool early, int want_per_sm, cudaStream_t stream) {
+static cudaError_t launch_n(GemvGroupT<NG> &g, StreamWs &ws, int sm_count, bool pdl, bool early, int want_per_sm, cudaStream_t stream) {  // NOLINT
     auto kern = qgemv_kq_stream_kernel<FMT, WARPS, TILES, NB, STAGES, MINB, NG>;
     constexpr uint32_t RT = 16 * TILES * WARPS;
     const uint32_t M = g.item[0].rows, C = (g.item[0].k / QK + NB - 1) / NB;
@@ -633,6 +740,13 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count,
     if (grid > U) grid = (uint32_t)U;
     // workspace: one partial tile (RT x 8 pairs) per CTA
     if ((uint64_t)grid * RT * 8 > ws.n_pairs || !ws.pairs) return cudaErrorNotSupported;
+    // A launch that runs ahead stages its segments: at most `pieces` spans share a tile. Without room for that it runs
+    // as a dependent launch.
+    const uint32_t q = (uint32_t)(U / grid), pieces = (C + q - 1) / q + 1;
+    if (early && ((uint64_t)tiles * pieces * RT * 8 * 8 > STAGE_BYTES || !ws.stage || (g_debug & 4))) {
+        early = false;
+        for (int i = 0; i < g.count; i++) g.item[i].early = 0;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3((WARPS + 1) * 32);
@@ -648,18 +762,29 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, const StreamWs &ws, int sm_count,
     head.nblk = g.item[0].k / QK;
     head.chunks = C;
     head.tiles = tiles;
-    head.q = (uint32_t)(U / grid);
+    head.q = q;
     head.rem = (uint32_t)(U % grid);
     head.early = (uint32_t)((early ? 1 : 0) | (g_debug & 2));
+    head.pieces = pieces;
     head.qa0 = g.item[0].qa;
     head.pairs = ws.pairs;
+    if (early) {
+        uint8_t *region = ws.stage + (size_t)(ws.next_region++ % STAGE_REGIONS) * (WORDS_BYTES + STAGE_BYTES);
+        head.words = (uint32_t *)region;
+        head.stage = (uint2 *)(region + WORDS_BYTES);
+        if (++ws.next_id == 0) ws.next_id = 1;
+        head.launch_id = ws.next_id;
+        const uint32_t per = g_final_tiles > 0 ? (uint32_t)g_final_tiles : 2;  // tiles per finalising CTA
+        const uint32_t want = (tiles + per - 1) / per;
+        head.nfinal = want < grid ? want : grid;
+    }
     if (g_trace && g_trace_next < g_trace_cap && grid <= g_trace_ctas)
         head.trace = g_trace + (size_t)(g_trace_next++) * g_trace_ctas * TRACE_WORDS;
     return cudaLaunchKernelEx(&cfg, kern, maps, head, g);
 }
 
 template <int FMT, int WARPS, int TILES, int NB, int STAGES, int MINB>
-static cudaError_t launch_cfg(GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, bool early, int per_sm, cudaStream_t stream) {
+static cudaError_t launch_cfg(GemvGroup &g, StreamWs &ws, int sm_count, bool pdl, bool early, int per_sm, cudaStream_t stream) {
     if (g.count > 1) return launch_n<FMT, WARPS, TILES, NB, STAGES, MINB, GEMV_GROUP_MAX>(g, ws, sm_count, pdl, early, per_sm, stream);
     GemvSingle one;  // a lone launch passes a sixth of the parameter bytes
     one.item[0] = g.item[0];
@@ -687,7 +812,7 @@ static int pick_config(const GemvGroup &g, int sm_count, bool early, int &per_sm
     return 7;
 }
 
-template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
+template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
     int per_sm = 0;
     switch (pick_config(g, sm_count, early, per_sm)) {
         case 0: return launch_cfg<FMT, 8, 1, 2, 2, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
@@ -702,6 +827,9 @@ template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, const StreamWs &w
         case 9: return launch_cfg<FMT, 6, 1, 2, 2, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
         case 10: return launch_cfg<FMT, 4, 2, 1, 2, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
         case 11: return launch_cfg<FMT, 4, 1, 1, 4, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 12: return launch_cfg<FMT, 3, 1, 2, 2, 4>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 13: return launch_cfg<FMT, 2, 1, 2, 2, 5>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 14: return launch_cfg<FMT, 3, 1, 2, 3, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -712,6 +840,7 @@ void qgemv_kq_stream_set_config(int index) { ks::g_force_config = index < 0 || i
 void qgemv_kq_stream_set_ctas_per_sm(int n) { ks::g_ctas_per_sm = n < 0 ? 0 : n; }
 void qgemv_kq_stream_set_debug(int v) { ks::g_debug = v; }
 void qgemv_kq_stream_set_early_ctas(int v) { ks::g_early_ctas = v < 0 ? 0 : v; }
+void qgemv_kq_stream_set_final_tiles(int v) { ks::g_final_tiles = v < 0 ? 0 : v; }
 
 // Diagnostics: record the timeline of every CTA of the next `launches` launches of this kernel (0 = stop and free).
 cudaError_t qgemv_kq_stream_trace_begin(uint32_t launches, int sm_count) {
@@ -719,7 +848,7 @@ cudaError_t qgemv_kq_stream_trace_begin(uint32_t launches, int sm_count) {
     ks::g_trace = nullptr;
     ks::g_trace_cap = ks::g_trace_next = 0;
     if (!launches) return cudaSuccess;
-    ks::g_trace_ctas = (uint32_t)sm_count * 4;
+    ks::g_trace_ctas = (uint32_t)sm_count * 8;
     const size_t bytes = (size_t)launches * ks::g_trace_ctas * ks::TRACE_WORDS * 8;
     if (cudaError_t e = cudaMalloc(&ks::g_trace, bytes); e != cudaSuccess) return e;
     ks::g_trace_cap = launches;
@@ -737,8 +866,12 @@ uint32_t qgemv_kq_stream_trace_read(unsigned long long *out, uint64_t cap_words,
 
 size_t qgemv_kq_stream_ws_bytes(int sm_count, StreamWs *layout) {
     const uint64_t n_pairs = (uint64_t)sm_count * 4 * 128 * 8;  // up to 4 CTAs per SM of 128-row tiles (or 8 of 64-row ones)
-    if (layout) layout->n_pairs = n_pairs;
-    return n_pairs * 8;
+    const uint64_t total = n_pairs * 8 + (uint64_t)ks::STAGE_REGIONS * (ks::WORDS_BYTES + ks::STAGE_BYTES);
+    if (layout) {
+        layout->n_pairs = n_pairs;
+        layout->total_bytes = total;
+    }
+    return total;
 }
 
 bool qgemv_kq_stream_shape_ok(int fmt, uint32_t rows, uint32_t n, uint32_t k) {
@@ -747,7 +880,7 @@ bool qgemv_kq_stream_shape_ok(int fmt, uint32_t rows, uint32_t n, uint32_t k) {
     return rows >= 1 && rows <= 8 && k % QK == 0 && k >= QK && ks::encode_fn() != nullptr;
 }
 
-cudaError_t launch_qgemv_kq_stream(int fmt, GemvGroup &g, const StreamWs &ws, int sm_count, bool pdl, cudaStream_t stream) {
+cudaError_t launch_qgemv_kq_stream(int fmt, GemvGroup &g, StreamWs &ws, int sm_count, bool pdl, cudaStream_t stream) {
     if (g.count < 1 || g.count > GEMV_GROUP_MAX) return cudaErrorInvalidValue;
     bool early = pdl;  // every member early and no tensor-parallel push
     for (int i = 0; i < g.count; i++) early = early && g.item[i].early != 0 && g.item[i].tp == nullptr;

@@ -556,7 +556,7 @@ bool qgemv_q4k_mma_group_fits(GemvGroup &g) {
 // at K = 14336 this kernel's activation copy then leaves room for only four warps per SM) and from eight units
 // per SM on. Smaller matrices and the other dependent launches stay here: the stream kernel's hand-over of
 // partial tiles between CTAs costs about a microsecond at its end.
-cudaError_t launch_qgemv_q4k_mma(GemvGroup &g, int sm_count, bool pdl, cudaStream_t stream, const StreamWs *ws) {
+cudaError_t launch_qgemv_q4k_mma(GemvGroup &g, int sm_count, bool pdl, cudaStream_t stream, StreamWs *ws) {
     if (g.count < 1 || g.count > GEMV_GROUP_MAX) return cudaErrorInvalidValue;
     mm::plan_acts(g);
     if (ws && mm::g_force_config < 0) {
