@@ -492,9 +492,9 @@ def gemv_kernel_name(fmt: int, m: int, n: int = 0, k: int = 0) -> str:
     timing, its activations were quantized at the head of the launch list (so it may run ahead of its predecessor)."""
     units = -(-n // 128) * -(-(k // 256) // 2)   # 128-row x 512-k units of the balanced-stream kernel
     if fmt == 6:
-        if m >= 3:
+        if m >= 2:
             return "qgemv_kq_stream_kernel<q4_k>" if units >= 2 * 148 else "qgemv_q4k_mma_kernel"
-        return "qgemv_kq_fast_kernel<q4_k>"  # (two rows: a tensor-core kernel when the operand is produced inside the list)
+        return "qgemv_kq_fast_kernel<q4_k>"
     if fmt == 8:
         return "qgemv_q6k_mma_kernel" if m >= 3 else "qgemv_kq_fast_kernel<q6_k>"
     if fmt == 7:

@@ -178,7 +178,7 @@ struct lapid_b200_device {
     // balanced-stream tensor-core decode kernel (qgemv_kq_stream.cu): 0 never; 1 (default) Q5_K always and Q4_K where
     // it is the faster one (launch_qgemv_q4k_mma decides); 2 both formats always
     int gemv_stream = 1;
-    bool two_row_dp4a = true;    // two early Q4_K rows prefer the dp4a kernel (see execute_impl)
+    bool two_row_dp4a = false;    // two early Q4_K rows on the dp4a kernel (see execute_impl)
     lb::StreamWs stream_ws{};    // workspace of that kernel: partial sums in flight between CTAs (all zero between launches)
     bool gemm_f32 = false;  // true: rows > gemv_max_rows always take the exact-f32 GEMM instead of the tensor cores
 
@@ -295,6 +295,9 @@ struct PendingGroup {
     bool accepts(int f, int md, const lb::GemvArgs &a, const Range &out, const Range *in, int n_in) {
         if (g.count == 0) return true;
         if (g.count == lb::GEMV_GROUP_MAX || f != fmt || md != mode || a.rows != g.item[0].rows || a.k != g.item[0].k) return false;
+        // dp4a launches that may run ahead of their predecessor overlap on their own: measured (one row, the three K = 4096
+        // projections of an 8B layer) 17.7 us as three launches against 19.2 us as one
+        if (md == 1 && a.early && g.item[0].early) return false;
         for (const Range &w : writes) {
             if (w.hits(out)) return false;
             for (int i = 0; i < n_in; i++)
@@ -780,13 +783,13 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             int n_in = 0;
             for (int i = 0; i < l.n_inputs; i++) in[n_in++] = Range{(const char *)ins[i]->ptr, (const char *)ins[i]->ptr + ins[i]->bytes};
             const int mode = slot->records == 2 && p.stream ? 3 : slot->records;
+            g.early = slot->hoisted ? 1 : 0;  // gated again when the group goes out
             if (!pend->accepts(l.b_dtype, mode, g, wr, in, n_in)) pend->flush(dev);
             if (!slot->done) {  // its input is not written by a pending launch (checked above), so it may run first
                 cuda_check(lb::launch_act_quant(q, dev.sm_count, dev.pdl_launch(), dev.stream), "act_quant launch");
                 dev.launches++;
                 slot->done = true;
             }
-            g.early = slot->hoisted ? 1 : 0;  // gated again when the group goes out
             pend->add(l.b_dtype, mode, g, wr, in, n_in);
             return;
         }
@@ -954,8 +957,9 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
                 bool clean = true;  // nothing in the list so far wrote the buffer A lives in
                 for (const Range &w : written)
                     if ((const char *)ab->ptr < w.hi && w.lo < (const char *)ab->ptr + ab->bytes) clean = false;
-                // two rows of Q4_K whose activations come from the pre-pass at the head: the dp4a kernel overlaps
-                // with the kernels around it (GemvArgs::early) and beats the tensor-core kernel there
+                // Option (off): two rows of Q4_K whose activations come from the pre-pass at the head on the dp4a kernel.
+                // It used to beat the tensor-core kernel there; since the balanced-stream kernel the tensor-core
+                // kernels win (the sweep step of 16 launches: 76.7 against 86.3 us)
                 if (clean && dev->two_row_dp4a && dev->act_reuse && dev->early_acts && dev->pdl && p.rows == 2 && p.mma && p.fast &&
                     l.b_dtype == LAPID_B200_DTYPE_Q4_K)
                     key.records = 1;

@@ -54,7 +54,7 @@ constexpr int BAR_BYTES = 128;
 constexpr int SC_STRIDE = 80;  // decoded scales of one (row, super-block): 16 floats, padded against bank conflicts
 constexpr uint32_t PAIR_SPIN_LIMIT = 1u << 20;  // polls of a partial-sum pair before the kernel gives up
 constexpr int STAGE_REGIONS = 8;                 // staging regions, taken in rotation by the launches that run ahead
-constexpr uint64_t STAGE_BYTES = 8ull << 20;     // pairs of one region
+constexpr uint64_t STAGE_BYTES = 6ull << 20;     // partial tiles of one region
 constexpr int WORDS_BYTES = 256;                 // control words in front of a region (see the claim in the kernel)
 
 __device__ __forceinline__ uint2 ld_pair(const void *p) {
@@ -89,9 +89,9 @@ struct alignas(64) Head {
     uint2 *pairs;                        // hand-over workspace of dependent launches
     unsigned long long *trace;           // diagnostics, or null
     // ---- second line: read at the end of a segment
-    uint2 *stage;                        // staging region of a launch that runs ahead: {value, flag} pairs
+    float *stage;                        // staging region of a launch that runs ahead: partial tiles
     uint32_t *words;                     // its control words
-    uint32_t launch_id, nfinal;          // owner value; CTAs that finalise (the last spans)
+    uint32_t launch_id, nfinal;          // owner value; CTAs of the kernel that adds the pieces up
 };
 
 template <int NG> struct Maps {
@@ -148,7 +148,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint64_t *full = (uint64_t *)smem, *empty = full + STAGES;
-    volatile uint32_t *region_ok = (volatile uint32_t *)(smem + BAR_BYTES - 16);  // the tag of this launch's pairs once the staging region is its own; ~0: the claim gave up
+    volatile uint32_t *region_ok = (volatile uint32_t *)(smem + BAR_BYTES - 16);  // 1 once the staging region is this launch's own; 2: the claim gave up
     uint8_t *stages = smem + BAR_BYTES;
     // The producer's lane sets the barriers up and asks for the first weights at once; the others meet it below.
     auto unit = [&](uint32_t i, int &item, uint32_t &local, uint32_t &c, uint32_t &nb) {
@@ -198,34 +198,22 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
                 asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations come from the kernel in front
                 for (uint32_t i = 0; i < pre; i++) load_a(i, i);
             } else {
-                // Claim the staging region. Control words: {owner (launch id, 0 = free), tag} as one 64-bit word, then the
-                // count of finalising warps that are done. Whoever swaps its id into a free word first takes the next tag
-                // with it -- the use counter of the region: pairs of earlier uses never match it, so slots need not be
-                // emptied; the other CTAs of the launch find the id there and take the tag. The last finalising warp
-                // frees the word again. A launch that finds the region owned by an earlier one waits for that (the earlier
-                // launch depends on nothing this one does).
-                unsigned long long *ot = (unsigned long long *)head.words;
-                uint32_t tag = 0xFFFFFFFFu;
+                // Claim the staging region: word 0 is its owner (a launch id, 0 = free). Whoever swaps its id into a free
+                // word first owns it for the launch; the other CTAs find the id there. The kernel that adds the pieces up
+                // frees it. A launch that finds the region owned by an earlier one waits for that (the earlier launch
+                // depends on nothing this one does).
+                uint32_t ok = 2;
                 for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT; spin++) {
-                    const unsigned long long r = *(volatile unsigned long long *)ot;
-                    const uint32_t o = (uint32_t)r;
+                    uint32_t o = *(volatile uint32_t *)head.words;
+                    if (o == 0) o = atomicCAS(head.words, 0u, head.launch_id) ? *(volatile uint32_t *)head.words : head.launch_id;
                     if (o == head.launch_id) {
-                        tag = (uint32_t)(r >> 32);
+                        ok = 1;
                         break;
-                    }
-                    if (o == 0) {
-                        uint32_t next = (uint32_t)(r >> 32) + 1;
-                        if (next == 0 || next == 0xFFFFFFFFu) next = 1;
-                        if (atomicCAS(ot, r, ((unsigned long long)next << 32) | head.launch_id) == r) {
-                            tag = next;
-                            break;
-                        }
-                        continue;
                     }
                     __nanosleep(64);
                 }
-                if (tag == 0xFFFFFFFFu && grp.item[0].status) atomicOr(grp.item[0].status, 1);
-                *region_ok = tag;
+                if (ok != 1 && grp.item[0].status) atomicOr(grp.item[0].status, 1);
+                *region_ok = ok;
             }
             stamp(TR_LOADS_ISSUED);
             uint32_t slot = 0, phase = 0;  // phase of `empty[slot]` the next refill waits for
@@ -247,6 +235,9 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
                                    head.launch_id;
             asm volatile("" ::"r"(touch));
         }
+        // A launch that runs ahead: one CTA waits for the kernel in front before it leaves, so that this grid's
+        // completion still means the completion of everything before it (the others just leave).
+        if ((early & 1) && b + 1 == G) asm volatile("griddepcontrol.wait;" ::: "memory");
         return;
     }
 
@@ -283,27 +274,19 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
     constexpr int NE = 4 * TILES;  // accumulators of a lane
     // ---- a launch that runs ahead: segment [c0, ..) of tile gt goes to its staging slot (tile, piece); the piece is
     //      the position of this span among the spans that share the tile
-    auto stage_slot = [&](uint32_t gt, uint32_t piece, uint32_t w) {
-        return head.stage + (((size_t)gt * head.pieces + piece) * WARPS + w) * EW + lane;
-    };
-    auto region_tag = [&]() -> uint32_t {
-        uint32_t tag = *region_ok;
-        for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT && tag == 0; spin++) {
-            __nanosleep(32);
-            tag = *region_ok;
-        }
-        if (tag == 0 || tag == 0xFFFFFFFFu) {
-            healthy = false;
-            tag = 0xFFFFFFFFu;
-        }
-        return tag;
-    };
     auto stage_out = [&](uint32_t gt, const float (&acc)[TILES][4]) {
-        const uint32_t tag = region_tag();
-        if (!healthy) return;
-        uint2 *dst = stage_slot(gt, b - owner(gt * C), warp);
+        uint32_t ok = *region_ok;
+        for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT && ok == 0; spin++) {
+            __nanosleep(32);
+            ok = *region_ok;
+        }
+        if (ok != 1) {
+            healthy = false;
+            return;
+        }
+        float *dst = head.stage + (((size_t)gt * head.pieces + (b - owner(gt * C))) * WARPS + warp) * EW + lane;
 #pragma unroll
-        for (int e = 0; e < NE; e++) st_pair(dst + e * 32, acc[e / 4][e % 4], tag);
+        for (int e = 0; e < NE; e++) __stcg(dst + e * 32, acc[e / 4][e % 4]);
     };
     // ---- a dependent launch. One finished segment [c0, c1) of tile gt: store it, hand it to the span that collects
     //      the tile, or collect.
@@ -522,90 +505,74 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
         }
         finish(gt, c0, c1, acc);
     }
-    if ((early & 1) && b + head.nfinal >= G) {
-        // ---- one of the last spans. Its warps take the (tile, warp slice) items of the launch in turn, two at a time: wait
-        //      for the pieces (they are {value, tag} pairs: a pair that carries this launch's tag carries its value), add
-        //      them up in k order and -- once the kernel in front has completed -- store the result.
-        const uint32_t nfinal = head.nfinal, items = head.tiles * WARPS, stride = nfinal * WARPS;
-        const uint32_t tag = region_tag();
-        if (warp == 0) stamp(TR_FLAG_SEEN);
-        constexpr int PB = 4 / TILES;  // pieces of an item asked for at once
-        for (uint32_t it = (b - (G - nfinal)) * WARPS + warp; it < items && healthy; it += 2 * stride) {
-            uint32_t t[2], w[2], np[2];
-#pragma unroll
-            for (int k = 0; k < 2; k++) {
-                const uint32_t i = it + k * stride;
-                t[k] = i / WARPS;
-                w[k] = i - t[k] * WARPS;
-                np[k] = i < items ? owner(t[k] * C + C - 1) - owner(t[k] * C) + 1 : 0;
-            }
-            float acc[2][TILES][4];
-#pragma unroll
-            for (int k = 0; k < 2; k++)
-#pragma unroll
-                for (int e = 0; e < NE; e++) acc[k][e / 4][e % 4] = 0.0f;
-            for (uint32_t p0 = 0; p0 < max(np[0], np[1]) && healthy; p0 += PB) {
-                uint2 v[2][PB][NE];
-#pragma unroll
-                for (int k = 0; k < 2; k++)
-#pragma unroll
-                    for (int j = 0; j < PB; j++)
-#pragma unroll
-                        for (int e = 0; e < NE; e++)
-                            v[k][j][e] = p0 + j < np[k] ? ld_pair(stage_slot(t[k], p0 + j, w[k]) + e * 32) : make_uint2(0u, tag);
-                for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT; spin++) {
-                    bool all = true;
-#pragma unroll
-                    for (int k = 0; k < 2; k++)
-#pragma unroll
-                        for (int j = 0; j < PB; j++)
-#pragma unroll
-                            for (int e = 0; e < NE; e++) all = all && v[k][j][e].y == tag;
-                    if (all) break;
-#pragma unroll
-                    for (int k = 0; k < 2; k++)
-#pragma unroll
-                        for (int j = 0; j < PB; j++)
-#pragma unroll
-                            for (int e = 0; e < NE; e++)
-                                if (v[k][j][e].y != tag) v[k][j][e] = ld_pair(stage_slot(t[k], p0 + j, w[k]) + e * 32);
-                }
-#pragma unroll
-                for (int k = 0; k < 2; k++)
-#pragma unroll
-                    for (int j = 0; j < PB; j++)
-#pragma unroll
-                        for (int e = 0; e < NE; e++) {
-                            if (v[k][j][e].y != tag) healthy = false;
-                            if (p0 + j < np[k]) acc[k][e / 4][e % 4] += __uint_as_float(v[k][j][e].x);
-                        }
-            }
-            healthy = __all_sync(0xffffffffu, healthy);
-            if (!waited) {
-                asm volatile("griddepcontrol.wait;" ::: "memory");
-                waited = true;
-                if (warp == 0) stamp(TR_AFTER_WAIT);
-            }
-            if (healthy && !(early & 2)) {
-#pragma unroll
-                for (int k = 0; k < 2; k++)
-                    if (np[k]) store(t[k], w[k], acc[k]);
-            }
-        }
-        if (!healthy && lane == 0 && grp.item[0].status) atomicOr(grp.item[0].status, 1);
-        if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");  // (later kernels take this grid's completion as that of everything before it)
-        // this warp has read what it will ever read of the region; the last one to say so frees it
-        __syncwarp();
-        if (lane == 0 && atomicAdd(head.words + 2, 1u) == stride - 1) {
-            head.words[2] = 0;
-            __threadfence();
-            *(volatile uint32_t *)head.words = 0;  // (the tag stays: the next owner counts on from it)
-        }
-    }
     if (trace && warp == 0 && lane == 0) {
         trace[TR_STARVED] = (unsigned long long)starved;
         trace[TR_EXIT] = (unsigned long long)clock64();
         trace[TR_GT_EXIT] = globaltimer_ns();
+    }
+}
+
+// Second half of a launch that ran ahead: adds the staged pieces of every (tile, warp slice) up in k order and stores
+// the result (epilogue included). Launched right behind the stream kernel, it waits for that kernel -- and through its
+// one waiting CTA for everything before it -- so the pieces are complete and the output may be written; the stream
+// kernel's CTAs meanwhile have left their SMs to the next launch. One item per warp and round, all its pieces in flight
+// together. The last CTA frees the staging region.
+template <int WARPS, int TILES, int NG>
+__global__ void __launch_bounds__(256) qgemv_kq_finalize_kernel(const Head head, GemvGroupT<NG> grp) {
+    constexpr int RPW = 16 * TILES, RT = RPW * WARPS, EW = 128 * TILES, NE = 4 * TILES;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int lane = threadIdx.x & 31, gq = lane >> 2, t4 = lane & 3;
+    const uint32_t C = head.chunks, q = head.q, rem = head.rem, M = head.rows;
+    auto owner = [&](uint32_t u) -> uint32_t { return u < rem * (q + 1) ? u / (q + 1) : rem + (u - rem * (q + 1)) / q; };
+    // (what the loop needs of the parameters, fetched before the wait)
+    const uint32_t items = head.tiles * WARPS, wpc = blockDim.x >> 5;
+    const uint32_t touch = grp.item[0].n ^ (uint32_t)(uintptr_t)grp.item[0].out ^ grp.task_end[0];
+    asm volatile("" ::"r"(touch));
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (uint32_t it = blockIdx.x * wpc + (threadIdx.x >> 5); it < items; it += gridDim.x * wpc) {
+        const uint32_t t = it / WARPS, w = it - t * WARPS;
+        const uint32_t np = owner(t * C + C - 1) - owner(t * C) + 1;
+        const float *src = head.stage + (((size_t)t * head.pieces) * WARPS + w) * EW + lane;
+        float acc[NE];
+#pragma unroll
+        for (int e = 0; e < NE; e++) acc[e] = 0.0f;
+        for (uint32_t p0 = 0; p0 < np; p0 += 4) {
+            float v[4][NE];
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+#pragma unroll
+                for (int e = 0; e < NE; e++) v[j][e] = p0 + j < np ? __ldcg(src + (size_t)(p0 + j) * WARPS * EW + e * 32) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+#pragma unroll
+                for (int e = 0; e < NE; e++) acc[e] += v[j][e];
+        }
+        uint32_t local = t;
+        int item = 0;
+        if constexpr (NG > 1) {
+            while (t >= grp.task_end[item]) item++;
+            local = t - (item ? grp.task_end[item - 1] : 0);
+        }
+        const GemvArgs &p = grp.item[item];
+#pragma unroll
+        for (int e = 0; e < NE; e++) {
+            const int tl = e / 4, i = e % 4;
+            const uint32_t row = local * RT + w * RPW + tl * 16 + gq + ((i & 2) ? 8 : 0);
+            const uint32_t r = 2 * t4 + (i & 1);
+            if (row < p.n && r < M) {
+                float x = acc[e];
+                const uint32_t bt = r / p.m, ri = r % p.m;
+                if (p.extra) x += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
+                p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = x;
+            }
+        }
+    }
+    // the last CTA to get here frees the staging region (every read of it lies before that CTA's count)
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(head.words + 2, 1u) == gridDim.x - 1) {
+        head.words[2] = 0;
+        __threadfence();
+        *(volatile uint32_t *)head.words = 0;
     }
 }
 
@@ -743,7 +710,7 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, StreamWs &ws, int sm_count, bool 
     // A launch that runs ahead stages its segments: at most `pieces` spans share a tile. Without room for that it runs
     // as a dependent launch.
     const uint32_t q = (uint32_t)(U / grid), pieces = (C + q - 1) / q + 1;
-    if (early && ((uint64_t)tiles * pieces * RT * 8 * 8 > STAGE_BYTES || !ws.stage || (g_debug & 4))) {
+    if (early && ((uint64_t)tiles * pieces * RT * 8 * 4 > STAGE_BYTES || !ws.stage || (g_debug & 4))) {
         early = false;
         for (int i = 0; i < g.count; i++) g.item[i].early = 0;
     }
@@ -771,16 +738,23 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, StreamWs &ws, int sm_count, bool 
     if (early) {
         uint8_t *region = ws.stage + (size_t)(ws.next_region++ % STAGE_REGIONS) * (WORDS_BYTES + STAGE_BYTES);
         head.words = (uint32_t *)region;
-        head.stage = (uint2 *)(region + WORDS_BYTES);
+        head.stage = (float *)(region + WORDS_BYTES);
         if (++ws.next_id == 0) ws.next_id = 1;
         head.launch_id = ws.next_id;
-        const uint32_t per = g_final_tiles > 0 ? (uint32_t)g_final_tiles : 2;  // tiles per finalising CTA
-        const uint32_t want = (tiles + per - 1) / per;
-        head.nfinal = want < grid ? want : grid;
+        const uint32_t per = g_final_tiles > 0 ? (uint32_t)g_final_tiles : 16;  // items (tile x warp slice) per CTA of the adding-up kernel
+        head.nfinal = (tiles * WARPS + per - 1) / per;
     }
     if (g_trace && g_trace_next < g_trace_cap && grid <= g_trace_ctas)
         head.trace = g_trace + (size_t)(g_trace_next++) * g_trace_ctas * TRACE_WORDS;
-    return cudaLaunchKernelEx(&cfg, kern, maps, head, g);
+    if (cudaError_t e = cudaLaunchKernelEx(&cfg, kern, maps, head, g); e != cudaSuccess || !early) return e;
+    // the launch ran ahead: its second half (see qgemv_kq_finalize_kernel)
+    cudaLaunchConfig_t fin = {};
+    fin.gridDim = dim3(head.nfinal);
+    fin.blockDim = dim3(256);
+    fin.stream = stream;
+    fin.attrs = attr;
+    fin.numAttrs = 1;
+    return cudaLaunchKernelEx(&fin, qgemv_kq_finalize_kernel<WARPS, TILES, NG>, head, g);
 }
 
 template <int FMT, int WARPS, int TILES, int NB, int STAGES, int MINB>

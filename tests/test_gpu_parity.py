@@ -1025,7 +1025,9 @@ def test_grouped_decode_launches(be, oracle, fmt, ofmt, m):
             assert max_rel(a, b) <= 2e-6
         else:
             assert np.array_equal(a, b)
-    assert res["1"][0] < res["0"][0]
+    # the tensor-core kernels share a launch; dp4a launches that may run ahead of their predecessor (one row, operands
+    # quantized at the head of the list) overlap on their own and are left as they are
+    assert res["1"][0] < res["0"][0] if m >= 3 else res["1"][0] <= res["0"][0]
     # and against the oracle
     got = res["1"][1][0]
     for i, n in enumerate(ns):
