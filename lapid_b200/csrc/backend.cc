@@ -290,14 +290,17 @@ struct PendingGroup {
     };
     int fmt = 0, mode = 0;  // kernel of the members: 1 = dp4a kernel, 2 = tensor-core kernel, 3 = balanced-stream tensor-core kernel
     lb::GemvGroup g{};
+    bool split_early = false;  // see accepts()
     std::vector<Range> writes, reads;
 
     bool accepts(int f, int md, const lb::GemvArgs &a, const Range &out, const Range *in, int n_in) {
         if (g.count == 0) return true;
         if (g.count == lb::GEMV_GROUP_MAX || f != fmt || md != mode || a.rows != g.item[0].rows || a.k != g.item[0].k) return false;
-        // dp4a launches that may run ahead of their predecessor overlap on their own: measured (one row, the three K = 4096
-        // projections of an 8B layer) 17.7 us as three launches against 19.2 us as one
-        if (md == 1 && a.early && g.item[0].early) return false;
+        // In a long list, dp4a launches that may run ahead of their predecessor overlap on their own: measured (one row,
+        // the three K = 4096 projections of an 8B layer inside a list of 16) 17.7 us as three launches against 19.2 us
+        // as one. In a short list (q, k, v of one decoder layer) the launch boundaries weigh more: 80 layers of 70B
+        // shapes take 9.8 ms per token grouped, 10.6 ms one by one.
+        if (md == 1 && split_early && a.early && g.item[0].early) return false;
         for (const Range &w : writes) {
             if (w.hits(out)) return false;
             for (int i = 0; i < n_in; i++)
@@ -331,11 +334,12 @@ struct PendingGroup {
         const bool early = dev.early_ok(true);  // members carry early = 1 when their activations came from the pre-pass at the head
         for (int i = 0; i < count; i++) out.item[i].early = early ? out.item[i].early : 0;
         const bool pdl = dev.pdl_launch();
+        const uint64_t before = dev.stream_ws.kernels;
         if (mode == 3) cuda_check(lb::launch_qgemv_kq_stream(fmt, out, dev.stream_ws, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (mode == 2 && fmt == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(out, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (mode == 2) cuda_check(lb::launch_qgemv_q4k_mma(out, dev.sm_count, pdl, dev.stream, dev.gemv_stream ? &dev.stream_ws : nullptr), "qgemv launch");
         else cuda_check(lb::launch_qgemv_kq_group(fmt, out, dev.sm_count, pdl, dev.stream), "qgemv launch");
-        dev.launches++;
+        dev.launches += dev.stream_ws.kernels > before ? dev.stream_ws.kernels - before : 1;  // (the stream kernel may take two)
     }
 };
 
@@ -805,6 +809,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         }
         g.early = dev.early_ok(slot->hoisted) ? 1 : 0;
         const bool pdl = dev.pdl_launch();
+        const uint64_t ws_before = dev.stream_ws.kernels;
         if (slot->records == 2 && l.b_dtype == LAPID_B200_DTYPE_INT8) {
             cuda_check(lb::launch_qgemv_i8_mma(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         } else if (slot->records == 2) {
@@ -819,7 +824,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         else if (l.b_dtype == LAPID_B200_DTYPE_MXFP4) cuda_check(lb::launch_qgemv_mxfp4(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (p.fast_i8 && ((uintptr_t)g.w & 15) == 0) cuda_check(lb::launch_qgemv_i8_fast(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
-        dev.launches++;
+        dev.launches += dev.stream_ws.kernels > ws_before ? dev.stream_ws.kernels - ws_before : 1;  // (the stream kernel may take two)
         return;
     }
     if (p.tc) {
@@ -1048,6 +1053,7 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
         flush();
     }
     PendingGroup pend;
+    pend.split_early = n >= 8;
     PendingGroup *pp = dev->gemv_group ? &pend : nullptr;
     try {
         for (size_t i = 0; i < n; i++) run_launch(*dev, launches[i], buffers, nbuf, slot_of[i] >= 0 ? &slots[slot_of[i]] : nullptr, pp);

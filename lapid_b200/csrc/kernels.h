@@ -198,6 +198,7 @@ struct StreamWs {
     uint8_t *stage;        // STAGE_REGIONS x (control words, partial tiles)
     uint64_t total_bytes;  // of the whole allocation, from `pairs` on
     uint32_t next_region, next_id;
+    uint64_t kernels;      // kernels launched through this workspace so far (a launch that runs ahead takes two)
 };
 // Diagnostics: per-CTA timeline rows of the next `launches` launches (16 words per CTA; see include/lapid_b200.h)
 cudaError_t qgemv_kq_stream_trace_begin(uint32_t launches, int sm_count);

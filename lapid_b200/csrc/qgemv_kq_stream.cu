@@ -746,6 +746,7 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, StreamWs &ws, int sm_count, bool 
     }
     if (g_trace && g_trace_next < g_trace_cap && grid <= g_trace_ctas)
         head.trace = g_trace + (size_t)(g_trace_next++) * g_trace_ctas * TRACE_WORDS;
+    ws.kernels += early ? 2 : 1;
     if (cudaError_t e = cudaLaunchKernelEx(&cfg, kern, maps, head, g); e != cudaSuccess || !early) return e;
     // the launch ran ahead: its second half (see qgemv_kq_finalize_kernel)
     cudaLaunchConfig_t fin = {};
