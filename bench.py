@@ -507,7 +507,7 @@ def gemv_kernel_name(fmt: int, m: int, n: int = 0, k: int = 0) -> str:
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch / algorithmic bytes of that launch, from the ncu
 # captures summarised under profiles/ (weights are read once; the outputs stay in L2). A kernel without a
 # capture reports no traffic.
-DRAM_TRAFFIC_RATIO = {"qgemv_kq_stream_kernel<q4_k>": 0.9935, "qgemv_q4k_mma_kernel": 0.985, "qgemv_kq_fast_kernel<q4_k>": 0.9985}
+DRAM_TRAFFIC_RATIO = {"qgemv_kq_stream_kernel<q4_k>": 0.986, "qgemv_q4k_mma_kernel": 0.985, "qgemv_kq_fast_kernel<q4_k>": 0.9985}
 
 
 def max_rel(got, ref) -> float:
@@ -999,7 +999,49 @@ def run_case(args):
         row.update({"gbs": round(gbs, 1), "frac_of_hbm": round(gbs / peak, 4), "peak_kind": kind})
     elif not e:
         row["tflops"] = round(2.0 * m * n * k / (us * 1e-6) / 1e12, 1)
+    if args.trace:
+        row["timeline"] = stream_kernel_timeline(be, stream, run, copies)
     print(json.dumps(row), flush=True)
+
+
+def stream_kernel_timeline(be, stream, run, launches, mhz=1965.0):
+    """Per-CTA timeline of the balanced-stream decode kernel over one CUDA-graph replay of `run` (the library's
+    diagnostics call: `lapid_b200_decode_trace_begin` / `_read`). Microseconds; SM clock cycles are converted with the
+    maximum SM clock. Per launch: CTAs, when they entered and left (5 % / median / 95 % of the CTAs, relative to the first
+    entry of the first launch), and the means of a CTA's phases -- entry to first data, first data to the end of its
+    span (`work`), the rest (`after`: staging or hand-over, waits, stores), of which it waited for data (`starved`)."""
+    import torch
+    with torch.cuda.stream(stream):
+        run()
+    stream.synchronize()
+    be.decode_trace_begin(launches)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        be.set_stream(torch.cuda.current_stream().cuda_stream)
+        run()
+    be.set_stream(stream.cuda_stream)
+    with torch.cuda.stream(stream):
+        for _ in range(4):
+            graph.replay()
+    stream.synchronize()
+    t = be.decode_trace_read(launches).astype(np.int64)
+    be.decode_trace_begin(0)
+    del graph
+    out, base = [], None
+    pct = lambda x: [round(float(np.percentile(x, q)), 2) for q in (5, 50, 95)]
+    for i in range(t.shape[0]):
+        r = t[i]
+        r = r[r[:, 1] != 0]   # rows of CTAs that ran
+        if not len(r):
+            continue
+        base = int(r[:, 0].min()) if base is None else base
+        cyc = lambda a, b: (r[:, b] - r[:, a]) / mhz
+        out.append({"launch": i, "ctas": int(len(r)), "units_per_cta": [int(r[:, 9].min()), int(r[:, 9].max())],
+                    "entry_us": pct((r[:, 0] - base) / 1e3), "exit_us": pct((r[:, 7] - base) / 1e3), "last_exit_us": round(float((r[:, 7] - base).max()) / 1e3, 2),
+                    "mean_us": {"life": round(float(cyc(1, 6).mean()), 2), "first_data": round(float(cyc(1, 3).mean()), 2),
+                                "work": round(float(cyc(3, 4).mean()), 2), "after": round(float(cyc(4, 6).mean()), 2),
+                                "starved": round(float((r[:, 10] / mhz).mean()), 2)}})
+    return out
 
 
 def cpu_baseline(cases, fmt):
@@ -1027,6 +1069,7 @@ def main():
     ap.add_argument("--case", default=None, metavar="FMT,M,N,K[,COPIES[,REPS]]",
                     help="run ONE matmul case instead of the benchmark (e.g. q4_k,8,14336,4096,6,2): REPS executes of COPIES launches, "
                          "each over its own weight copy, then a timed CUDA-graph replay; small enough to sit under a profiler")
+    ap.add_argument("--trace", action="store_true", help="--case: add the per-CTA timeline of the balanced-stream decode kernel (one more graph replay)")
     ap.add_argument("--experts", type=int, default=0, help="--case: MatMulId over a stack of this many matrices (0: a plain MatMul)")
     ap.add_argument("--slots", type=int, default=2, help="--case with --experts: experts per token")
     ap.add_argument("--opt", action="append", default=[], help="device option key=value (repeatable)")

@@ -775,6 +775,7 @@ static cudaError_t launch_cfg(GemvGroup &g, StreamWs &ws, int sm_count, bool pdl
 //    these sizes is that the SM is never without a CTA that computes while another starts or hands over, so three
 //    CTAs per SM -- or two with the third slot left to the next launch of the stream when the spans would
 //    otherwise fall below six units (many spans per row tile: more hand-overs than work);
+//  * below two units per SM (4096 x 4096 at Q5_K: 4.8 against 6.6 us) one CTA of three stages per SM;
 //  * from sixteen 128-row units per SM on the 32-row warps, whose activation fragments and scales serve two row tiles
 //    (shared-memory wavefronts bound the 16-row layout in the long run).
 static int pick_config(const GemvGroup &g, int sm_count, bool early, int &per_sm) {
@@ -783,6 +784,10 @@ static int pick_config(const GemvGroup &g, int sm_count, bool early, int &per_sm
     uint64_t units = 0;  // 128 rows x 512 k
     for (int i = 0; i < g.count; i++) units += (uint64_t)((g.item[i].n + 127) / 128) * ((g.item[i].k / QK + 1) / 2);
     if (units >= 16 * (uint64_t)sm_count) return 1;
+    if (units < 2 * (uint64_t)sm_count) {  // small matrices (Q5_K only: Q4_K has the per-warp-ring kernel for them): one CTA of three stages per SM
+        per_sm = 1;
+        return 2;
+    }
     if (early && 2 * units < 6 * 3 * (uint64_t)sm_count) per_sm = 2;  // (config 7 has 64-row tiles: twice the units)
     return 7;
 }
