@@ -728,9 +728,13 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         dev.launches++;
         return;
     }
-    if (ins[1]->bytes < p.wl.scales_offset + p.wl.scales_bytes)
-        fail("out_of_bounds", "b200: quantized [" + std::to_string(l.n) + ", " + std::to_string(l.k) + "] needs " +
-                                  std::to_string(p.wl.total) + " bytes, buffer has " + std::to_string(ins[1]->bytes));
+    {   // the blocks themselves, to the end of their last 16-byte line (the Q6_K bulk copies fetch whole lines: 210-byte
+        // blocks end anywhere); `layout().total`, which quantize hands out, is padded further
+        const uint64_t need = align_up(p.wl.scales_offset + p.wl.scales_bytes, 16);
+        if (ins[1]->bytes < need)
+            fail("out_of_bounds", "b200: quantized [" + std::to_string(l.n) + ", " + std::to_string(l.k) + "] needs " + std::to_string(need) +
+                                      " bytes (layout total " + std::to_string(p.wl.total) + "), buffer has " + std::to_string(ins[1]->bytes));
+    }
     if (((uintptr_t)ins[1]->ptr & 15) != 0) fail("invalid_launch", "b200: quantized B must be 16-byte aligned");
 
     if (p.gemv) {
