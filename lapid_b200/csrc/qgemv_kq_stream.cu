@@ -4,7 +4,7 @@
 //
 //  * Unit of work: 16*TILES*WARPS weight rows x one k-chunk (NB = one or two super-blocks per row).
 //    The units of all members of the launch, tile after tile, k-chunk after k-chunk, form one
-//    sequence; CTA b takes the contiguous span [U*b/G, U*(b+1)/G) of it, so every CTA streams the
+//    sequence; CTA b takes a contiguous span of U/G (or one more) of them, so every CTA streams the
 //    same number of bytes whatever the shape (no tail of half-empty waves, no idle SMs on matrices
 //    with few rows).
 //  * Inside a CTA one producer warp fills a ring of stages: the weights of a unit by ONE tensor-map
@@ -29,12 +29,14 @@
 //    - A launch that runs ahead (GemvArgs::early: everything it reads is older than the kernel in front) must not
 //      write its output before that kernel has completed, and a CTA that waited for that would keep its place on
 //      the SM from the next launch. So its CTAs only STAGE: every segment goes to a slot (tile, piece) of a staging
-//      region in global memory that belongs to this launch alone, the warp counts itself done (fence + atomic) and
-//      leaves. The CTAs of the last F spans stay: when every warp of the launch is counted they wait for the kernel
-//      in front, add the pieces of their tiles up in k order and store them. Nobody polls for a neighbour, nobody
-//      but those F CTAs waits, and the result does not depend on timing. A staging region is claimed with a
-//      compare-and-swap on its owner word by the first CTA that gets there and released by the last finaliser, so
-//      two launches in flight never share one whatever the order in which their CTAs run.
+//      region in global memory that belongs to this launch alone, and the CTA leaves (one CTA of the grid waits for
+//      the kernel in front before it does, so that the grid's completion still means the completion of everything
+//      before it). A second, small kernel launched right behind (qgemv_kq_finalize_kernel) waits for this one,
+//      adds the pieces of every tile up in k order and stores them. Nobody polls for a neighbour and the result
+//      does not depend on timing. A staging region is claimed with a compare-and-swap on its owner word by the
+//      first CTA that gets there and released by the last CTA of the second kernel, so two launches in flight never
+//      share one whatever the order in which their CTAs run.
+//  * The span of CTA b: the first U mod G spans hold floor(U / G) + 1 units, the others floor(U / G).
 //  * Every mbarrier wait is bounded; a wait that gives up sets the host-visible status word.
 #include <cuda.h>
 
@@ -636,44 +638,29 @@ static bool weight_map(const GemvArgs &a, uint32_t blk, uint32_t nb, uint32_t bo
     return true;
 }
 
-struct Config {
-    int warps, tiles, nb, stages;  // consumer warps, 16-row tiles per warp, super-blocks per k-chunk, ring stages
-};
+// Layouts (consumer warps, 16-row tiles per warp, super-blocks per k-chunk, ring stages):
 // 0: eight warps of 16 rows, two-block chunks, two stages
 // 1: four warps of 32 rows (the activation fragments and scales are shared by two row tiles), two-block chunks, two stages
 // 2: four warps of 16 rows, two-block chunks, three stages
-// 3: eight warps of 16 rows, two-block chunks, four stages (one CTA per SM)
-// 4: four warps of 32 rows, one-block chunks, three stages (three CTAs per SM)
-// 5: four warps of 32 rows, one-block chunks, four stages
-// 6: eight warps of 32 rows, one-block chunks, two stages
-// 7: four warps of 16 rows, two-block chunks, two stages (three CTAs per SM)
-// 8: eight warps of 16 rows, one-block chunks, four stages
-// 9: six warps of 16 rows, two-block chunks, two stages
-// 10: four warps of 32 rows, one-block chunks, two stages (three CTAs per SM)
-// 11: four warps of 16 rows, one-block chunks, four stages (three CTAs per SM)
-// 12: three warps of 16 rows, two-block chunks, two stages (four CTAs per SM)
-// 13: two warps of 16 rows, two-block chunks, two stages (five CTAs per SM)
-// 14: three warps of 16 rows, two-block chunks, three stages (three CTAs per SM)
-static const Config CONFIGS[] = {{8, 1, 2, 2}, {4, 2, 2, 2}, {4, 1, 2, 3}, {8, 1, 2, 4}, {4, 2, 1, 3}, {4, 2, 1, 4}, {8, 2, 1, 2}, {4, 1, 2, 2},
-                                 {8, 1, 1, 4}, {6, 1, 2, 2}, {4, 2, 1, 2}, {4, 1, 1, 4}, {3, 1, 2, 2}, {2, 1, 2, 2}, {3, 1, 2, 3}};
-constexpr int N_CONFIGS = 15;
+// 3: four warps of 16 rows, two-block chunks, two stages (three CTAs per SM): the default up to 66 MB
+// 4: three warps of 16 rows, two-block chunks, two stages (four CTAs per SM)
+// (Also built and measured, never ahead: one-block chunks with three and four stages, eight warps of 32 rows, six and
+// two warps of 16 rows.)
+constexpr int N_CONFIGS = 5;
 static int g_force_config = -1;
 static int g_ctas_per_sm = 0;  // 0 = choose
 static int g_debug = 0;        // measurement only: 2 = drop the partial tiles (wrong results)
-// CTAs per SM of a launch that runs ahead of its predecessor (0 = as for any launch). Measured: leaving slots to the
-// launches around it pays only on small matrices (4096 x 4096: 4.1 against 5.3 us at 1), where the per-warp-ring kernel
-// is used anyway; on the 33 MB shapes the warps of ONE launch finish it sooner than the same warps spread over
-// two or three launches (10.8 against 14.4 us), so the default is off.
+// Tuning: CTAs per SM of a launch that runs ahead of its predecessor (0 = as pick_config says).
 static int g_early_ctas = 0;
 static int g_final_tiles = 0;  // tuning: row tiles per finalising CTA of a launch that runs ahead (0 = choose)
 // Diagnostics: a device buffer of TRACE_WORDS words per CTA for the next `g_trace_cap` launches (row = launch, in launch order)
 static unsigned long long *g_trace = nullptr;
 static uint32_t g_trace_cap = 0, g_trace_next = 0, g_trace_ctas = 0;
 
-static size_t smem_bytes(int fmt, const Config &c, uint32_t rows) {
-    const size_t rowb = (size_t)c.nb * (fmt == FMT_Q5K ? Geo<FMT_Q5K>::BLK : Geo<FMT_Q4K>::BLK);
-    const size_t stage = (size_t)16 * c.tiles * c.warps * rowb + c.nb * act_block_bytes(rows);
-    return BAR_BYTES + (size_t)c.stages * stage + (size_t)c.warps * 16 * c.tiles * c.nb * SC_STRIDE;
+static size_t smem_bytes(int fmt, int warps, int tiles, int nb, int stages, uint32_t rows) {
+    const size_t rowb = (size_t)nb * (fmt == FMT_Q5K ? Geo<FMT_Q5K>::BLK : Geo<FMT_Q4K>::BLK);
+    const size_t stage = (size_t)16 * tiles * warps * rowb + nb * act_block_bytes(rows);
+    return BAR_BYTES + (size_t)stages * stage + (size_t)warps * 16 * tiles * nb * SC_STRIDE;
 }
 
 template <int FMT, int WARPS, int TILES, int NB, int STAGES, int MINB, int NG>
@@ -689,7 +676,7 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, StreamWs &ws, int sm_count, bool 
         if (!weight_map(g.item[i], Geo<FMT>::BLK, NB, RT, maps.m[i])) return cudaErrorNotSupported;
     }
     for (int i = g.count; i < NG; i++) maps.m[i] = maps.m[0];
-    const size_t smem = smem_bytes(FMT, Config{WARPS, TILES, NB, STAGES}, M);
+    const size_t smem = smem_bytes(FMT, WARPS, TILES, NB, STAGES, M);
     static DynamicSmemOptIn opted;
     if (cudaError_t e = opted.raise((const void *)kern, smem); e != cudaSuccess) return e;
     // As many CTAs per SM as fit, at most what the kernel's register allocation allows (measured: a CTA slot left to
@@ -788,8 +775,8 @@ static int pick_config(const GemvGroup &g, int sm_count, bool early, int &per_sm
         per_sm = 1;
         return 2;
     }
-    if (early && 2 * units < 6 * 3 * (uint64_t)sm_count) per_sm = 2;  // (config 7 has 64-row tiles: twice the units)
-    return 7;
+    if (early && 2 * units < 6 * 3 * (uint64_t)sm_count) per_sm = 2;  // (64-row tiles: twice the units)
+    return 3;
 }
 
 template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, StreamWs &ws, int sm_count, bool pdl, bool early, cudaStream_t stream) {
@@ -798,18 +785,8 @@ template <int FMT> static cudaError_t launch_fmt(GemvGroup &g, StreamWs &ws, int
         case 0: return launch_cfg<FMT, 8, 1, 2, 2, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
         case 1: return launch_cfg<FMT, 4, 2, 2, 2, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
         case 2: return launch_cfg<FMT, 4, 1, 2, 3, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 3: return launch_cfg<FMT, 8, 1, 2, 4, 1>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 4: return launch_cfg<FMT, 4, 2, 1, 3, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 5: return launch_cfg<FMT, 4, 2, 1, 4, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 6: return launch_cfg<FMT, 8, 2, 1, 2, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 7: return launch_cfg<FMT, 4, 1, 2, 2, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 8: return launch_cfg<FMT, 8, 1, 1, 4, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 9: return launch_cfg<FMT, 6, 1, 2, 2, 2>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 10: return launch_cfg<FMT, 4, 2, 1, 2, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 11: return launch_cfg<FMT, 4, 1, 1, 4, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 12: return launch_cfg<FMT, 3, 1, 2, 2, 4>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 13: return launch_cfg<FMT, 2, 1, 2, 2, 5>(g, ws, sm_count, pdl, early, per_sm, stream);
-        case 14: return launch_cfg<FMT, 3, 1, 2, 3, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 3: return launch_cfg<FMT, 4, 1, 2, 2, 3>(g, ws, sm_count, pdl, early, per_sm, stream);
+        case 4: return launch_cfg<FMT, 3, 1, 2, 2, 4>(g, ws, sm_count, pdl, early, per_sm, stream);
         default: return cudaErrorInvalidValue;
     }
 }
