@@ -159,11 +159,46 @@ typedef struct lapid_b200_view3 {
  * sequence ran; the kernels do not read out of bounds. */
 #define LAPID_B200_KERNEL_MATMUL_ID 4
 
-/* Fused epilogues (MatMulSpec.epilogue, ir.rs:234-247). The reference accepts any expression;
- * this backend accepts the two shapes lapid's lowering emits for projections
- * (crates/lapid-compiler/src/lower/emit.rs:199-262): none, and `Load(0) + Load(1)`. */
+/* Fused epilogues (MatMulSpec.epilogue, ir.rs:234-247; the expression type: ir.rs:94-111). NONE and ADD
+ * (`Load(0) + Load(1)`) are the two shapes lapid's lowering emits for projections
+ * (crates/lapid-compiler/src/lower/emit.rs:199-262). EXPR is any f32 expression over Load(0) = the accumulator and
+ * Load(1) = extras[0] (n_inputs 3 when the program loads it, else 2), given in postfix order in `expr[0 .. n_expr)`:
+ * one word per node, `op | arg << 8`; LAPID_B200_EXPR_CONST is followed by a word with the constant's bits. It is what
+ * the elementwise chain behind a projection lowers to -- silu(acc) for the gate of a gated MLP, acc * extras[0] for
+ * its up projection (crates/lapid-nn/src/mlp.rs:84), so that no elementwise kernel is left between gate/up and down.
+ * At most 24 words and four values on the evaluation stack; the integer nodes of the reference's expression type
+ * (LoadBits, IntUnary, IntBinary, Convert) answer "unsupported". Decode kernels evaluate it in their stores; a
+ * prefill launch applies it to its output in place with one more kernel. Transcendental nodes are CUDA's f32
+ * functions: they agree with lapid-cpu's own polynomials to a few ulp, not bit for bit. */
 #define LAPID_B200_EPILOGUE_NONE 0
 #define LAPID_B200_EPILOGUE_ADD 1
+#define LAPID_B200_EPILOGUE_EXPR 2
+#define LAPID_B200_EXPR_WORDS 24
+#define LAPID_B200_EXPR_LOAD 1   /* arg: 0 = accumulator, 1 = extras[0] */
+#define LAPID_B200_EXPR_CONST 2  /* next word: f32 bits */
+/* UnaryOp (crates/lapid-tensor/src/op.rs:11-23), in its order, from 16 */
+#define LAPID_B200_EXPR_NEG 16
+#define LAPID_B200_EXPR_EXP 17
+#define LAPID_B200_EXPR_LOG 18
+#define LAPID_B200_EXPR_SQRT 19
+#define LAPID_B200_EXPR_RSQRT 20
+#define LAPID_B200_EXPR_RECIP 21
+#define LAPID_B200_EXPR_SIN 22
+#define LAPID_B200_EXPR_COS 23
+#define LAPID_B200_EXPR_TANH 24
+#define LAPID_B200_EXPR_ERF 25
+#define LAPID_B200_EXPR_ABS 26
+/* the float BinaryOps (op.rs:26-37), in their order, from 32: pops b then a, pushes a op b */
+#define LAPID_B200_EXPR_ADD 32
+#define LAPID_B200_EXPR_SUB 33
+#define LAPID_B200_EXPR_MUL 34
+#define LAPID_B200_EXPR_DIV 35
+#define LAPID_B200_EXPR_MAX 36
+#define LAPID_B200_EXPR_MIN 37
+#define LAPID_B200_EXPR_POW 38
+#define LAPID_B200_EXPR_CMPLT 39
+#define LAPID_B200_EXPR_CMPEQ 40
+#define LAPID_B200_EXPR_WHERE 48 /* pops b, a, cond; pushes cond != 0 ? a : b */
 
 typedef struct lapid_b200_launch {
     int32_t kind;         /* LAPID_B200_KERNEL_MATMUL (the fields below describe it), LAPID_B200_KERNEL_GATHER or LAPID_B200_KERNEL_MATMUL_ID (see above) */
@@ -173,13 +208,15 @@ typedef struct lapid_b200_launch {
     int32_t out_dtype;    /* MatMulSpec.out_dtype: F32 */
     int32_t b_transposed; /* must be 1 for a quantized B */
     int32_t epilogue;     /* LAPID_B200_EPILOGUE_* */
-    int32_t extra_dtype;  /* dtype of extras[0] when epilogue == ADD: F32 */
+    int32_t extra_dtype;  /* dtype of extras[0] when the epilogue reads it: F32 */
     int32_t n_inputs;     /* 2, or 3 with an extra */
     uint64_t batch, m, n, k;         /* MatMulDims */
     lapid_b200_matview a, b, out;    /* b: offset 0, batch_stride 0 (quantized B, ir.rs:232-233) */
     lapid_b200_view3 extra;          /* MatMulDims.extra_views[0] */
     uint32_t inputs[3];   /* BufIds: a, b, extras[0] -- indices into `buffers` of execute */
     uint32_t output;      /* BufId of the output */
+    uint32_t n_expr;      /* epilogue == EXPR: words of the program */
+    uint32_t expr[LAPID_B200_EXPR_WORDS];
 } lapid_b200_launch;
 
 /* Backend::prepare (backend.rs:51-54): validates the launches and sizes the device's scratch so

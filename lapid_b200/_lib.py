@@ -38,6 +38,7 @@ class LaunchC(C.Structure):
         ("batch", C.c_uint64), ("m", C.c_uint64), ("n", C.c_uint64), ("k", C.c_uint64),
         ("a", MatViewC), ("b", MatViewC), ("out", MatViewC), ("extra", View3C),
         ("inputs", C.c_uint32 * 3), ("output", C.c_uint32),
+        ("n_expr", C.c_uint32), ("expr", C.c_uint32 * 24),
     ]
 
 

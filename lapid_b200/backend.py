@@ -34,9 +34,10 @@ class DType(enum.IntEnum):
 
 
 class Epilogue(enum.IntEnum):
-    """The two epilogue shapes this backend accepts: none, and ``Load(0) + Load(1)``."""
+    """Epilogue kinds: none, ``Load(0) + Load(1)``, or an expression (:class:`Expr`) over the accumulator and extras[0]."""
     NONE = 0
     ADD = 1
+    EXPR = 2
 
 
 @dataclass(frozen=True)
@@ -58,15 +59,94 @@ class View:
     strides: tuple = (0, 0, 1)
 
 
+class Expr:
+    """The f32 part of the reference's epilogue expression type (crates/lapid-compiler/src/ir.rs:94-111) as a
+    postfix program for ``LAPID_B200_EPILOGUE_EXPR``: ``Expr.load(0)`` is the accumulator, ``Expr.load(1)`` extras[0];
+    unary nodes are methods (``neg exp log sqrt rsqrt recip sin cos tanh erf abs``, crates/lapid-tensor/src/op.rs:11-23),
+    binary ones operators and methods (``+ - * /``, ``max min pow lt eq``), ``Expr.where(cond, a, b)``; Python numbers
+    become constants. ``Expr.silu(x)`` and ``Expr.gelu_tanh(x)`` build what lapid-nn's activations build
+    (crates/lapid-nn/src/ops.rs:12-30)."""
+    _UN = {"neg": 16, "exp": 17, "log": 18, "sqrt": 19, "rsqrt": 20, "recip": 21, "sin": 22, "cos": 23, "tanh": 24, "erf": 25, "abs": 26}
+    _BIN = {"add": 32, "sub": 33, "mul": 34, "div": 35, "max": 36, "min": 37, "pow": 38, "lt": 39, "eq": 40}
+
+    def __init__(self, words):
+        self.words = tuple(int(w) for w in words)
+
+    @staticmethod
+    def load(i: int) -> "Expr":
+        return Expr([1 | (i << 8)])
+
+    @staticmethod
+    def const(v: float) -> "Expr":
+        return Expr([2, int(np.float32(v).view(np.uint32))])
+
+    @staticmethod
+    def _of(v) -> "Expr":
+        return v if isinstance(v, Expr) else Expr.const(v)
+
+    def _un(self, name):
+        return Expr(self.words + (Expr._UN[name],))
+
+    def _bin(self, name, other, swap=False):
+        a, b = (Expr._of(other), self) if swap else (self, Expr._of(other))
+        return Expr(a.words + b.words + (Expr._BIN[name],))
+
+    @staticmethod
+    def where(cond, a, b) -> "Expr":
+        return Expr(Expr._of(cond).words + Expr._of(a).words + Expr._of(b).words + (48,))
+
+    @staticmethod
+    def sigmoid(x: "Expr") -> "Expr":
+        return (x.neg().exp() + 1.0).recip()
+
+    @staticmethod
+    def silu(x: "Expr") -> "Expr":
+        return x * Expr.sigmoid(x)
+
+    @staticmethod
+    def gelu_tanh(x: "Expr") -> "Expr":
+        inner = (x * x * x * 0.044715 + x) * 0.7978845608028654
+        return x * 0.5 * (inner.tanh() + 1.0)
+
+    def __add__(self, o): return self._bin("add", o)
+    def __radd__(self, o): return self._bin("add", o, True)
+    def __sub__(self, o): return self._bin("sub", o)
+    def __rsub__(self, o): return self._bin("sub", o, True)
+    def __mul__(self, o): return self._bin("mul", o)
+    def __rmul__(self, o): return self._bin("mul", o, True)
+    def __truediv__(self, o): return self._bin("div", o)
+    def __rtruediv__(self, o): return self._bin("div", o, True)
+    def __neg__(self): return self._un("neg")
+    def max(self, o): return self._bin("max", o)
+    def min(self, o): return self._bin("min", o)
+    def pow(self, o): return self._bin("pow", o)
+    def lt(self, o): return self._bin("lt", o)
+    def eq(self, o): return self._bin("eq", o)
+
+    def reads_extra(self) -> bool:
+        i, n = 0, len(self.words)
+        while i < n:
+            w = self.words[i]
+            if (w & 0xff) == 1 and (w >> 8) == 1:
+                return True
+            i += 2 if (w & 0xff) == 2 else 1
+        return False
+
+
+for _name in Expr._UN:
+    setattr(Expr, _name, (lambda nm: lambda self: self._un(nm))(_name))
+
+
 @dataclass(frozen=True)
 class MatMulSpec:
-    """ir.rs:239-247. ``epilogue`` is an :class:`Epilogue` instead of an expression tree."""
+    """ir.rs:239-247. ``epilogue`` is an :class:`Epilogue`; with ``Epilogue.EXPR`` the expression is ``expr``."""
     a_dtype: DType = DType.F32
     b_dtype: DType = DType.Q4K
     b_transposed: bool = True
     extra_dtypes: tuple = ()
     out_dtype: DType = DType.F32
     epilogue: Epilogue = Epilogue.NONE
+    expr: Optional[Expr] = None
 
 
 @dataclass(frozen=True)
@@ -98,6 +178,12 @@ class Launch:
         c.a_dtype, c.b_dtype, c.out_dtype = int(s.a_dtype), int(s.b_dtype), int(s.out_dtype)
         c.b_transposed = int(bool(s.b_transposed))
         c.epilogue = int(s.epilogue)
+        if s.expr is not None:
+            if len(s.expr.words) > 24:
+                raise _lib.LapidError(8, "unsupported", f"an epilogue expression of {len(s.expr.words)} words (at most 24)")
+            c.n_expr = len(s.expr.words)
+            for i, w in enumerate(s.expr.words):
+                c.expr[i] = w
         c.extra_dtype = int(s.extra_dtypes[0]) if s.extra_dtypes else 0
         c.n_inputs = len(self.inputs)
         c.batch, c.m, c.n, c.k = d.batch, d.m, d.n, d.k
@@ -119,12 +205,22 @@ class Launch:
 
 def matmul_launch(b_dtype: DType, m: int, n: int, k: int, *, batch: int = 1, a_row_stride: Optional[int] = None,
                   inputs=(0, 1), output=2, bias_input: Optional[int] = None, out: Optional[MatView] = None,
-                  a_quantized: bool = False, a_dtype: DType = DType.F32) -> Launch:
+                  a_quantized: bool = False, a_dtype: DType = DType.F32, expr: Optional[Expr] = None, extra_input: Optional[int] = None,
+                  extra_view: Optional[View] = None) -> Launch:
     """The launch lapid lowers ``x.matmul_t(w)`` to: contiguous A (or padded rows), quantized
     transposed B, contiguous f32 output (the `mm` helper of kbench_tests.rs:86-107).
     ``a_quantized``: input 0 is the quantized operand a producer wrote for this launch (``Backend.act_layout``);
-    ``a_dtype``: F32, F16 or BF16 activations (widened exactly to f32 as they are read, like lapid-cpu's ``load_contig``)."""
+    ``a_dtype``: F32, F16 or BF16 activations (widened exactly to f32 as they are read, like lapid-cpu's ``load_contig``);
+    ``expr``: an epilogue expression; when it loads extras[0], ``extra_input`` is that buffer and ``extra_view`` its view
+    over [batch, m, n] (default: a contiguous [m, n] array)."""
     rs = a_row_stride if a_row_stride is not None else k
+    if expr is not None:
+        has = expr.reads_extra()
+        spec = MatMulSpec(a_dtype=DType.ACT_Q8 if a_quantized else DType(a_dtype), b_dtype=DType(b_dtype), extra_dtypes=(DType.F32,) if has else (),
+                          epilogue=Epilogue.EXPR, expr=expr)
+        dims = MatMulDims(batch, m, n, k, a=MatView(0, m * rs, rs), b=MatView(0, 0, k), out=out or MatView.contiguous(m, n),
+                          extra_views=((extra_view or View(0, (m * n, n, 1)),) if has else ()))
+        return Launch(spec, dims, tuple(inputs) + ((extra_input,) if has else ()), output)
     spec = MatMulSpec(a_dtype=DType.ACT_Q8 if a_quantized else DType(a_dtype), b_dtype=DType(b_dtype), extra_dtypes=(DType.F32,) if bias_input is not None else (),
                       epilogue=Epilogue.ADD if bias_input is not None else Epilogue.NONE)
     dims = MatMulDims(batch, m, n, k, a=MatView(0, m * rs, rs), b=MatView(0, 0, k), out=out or MatView.contiguous(m, n),

@@ -283,6 +283,15 @@ struct ActSlot {
 // Decode launches of one list that wait to go out as one grouped kernel: same format, rows and k,
 // and none of them reads or overwrites what another one writes, so running them side by side
 // gives what running them in order gives.
+// A decode launch whose epilogue expression its kernel did not evaluate (the kernels store the plain accumulator then):
+// one more kernel applies it in place.
+void finish_expr(lapid_b200_device &dev, const lb::GemvArgs &it) {
+    if (!it.epi.n) return;
+    cuda_check(lb::launch_epilogue_expr(it.epi, it.out, it.out_off, it.out_bs, it.out_rs, it.extra, it.ex_off, it.ex_s0, it.ex_s1, it.ex_s2,
+                                        it.rows / it.m, it.m, it.n, dev.sm_count, dev.stream), "epilogue launch");
+    dev.launches++;
+}
+
 struct PendingGroup {
     struct Range {
         const char *lo, *hi;
@@ -340,12 +349,45 @@ struct PendingGroup {
         else if (mode == 2) cuda_check(lb::launch_qgemv_q4k_mma(out, dev.sm_count, pdl, dev.stream, dev.gemv_stream ? &dev.stream_ws : nullptr), "qgemv launch");
         else cuda_check(lb::launch_qgemv_kq_group(fmt, out, dev.sm_count, pdl, dev.stream), "qgemv launch");
         dev.launches += dev.stream_ws.kernels > before ? dev.stream_ws.kernels - before : 1;  // (the stream kernel may take two)
+        for (int i = 0; i < count; i++) finish_expr(dev, out.item[i]);
     }
 };
 
 std::string dims_str(const lapid_b200_launch &l) {
     return "[" + std::to_string(l.batch) + ", " + std::to_string(l.m) + ", " + std::to_string(l.n) + ", " +
            std::to_string(l.k) + "]";
+}
+
+// The epilogue program of a launch: known nodes, a well-formed postfix order, at most four values on the stack, one
+// result. Returns whether it loads extras[0].
+bool check_expr(const lapid_b200_launch &l) {
+    if (l.n_expr == 0 || l.n_expr > LAPID_B200_EXPR_WORDS)
+        fail("invalid_launch", "b200 matmul: an epilogue expression of " + std::to_string(l.n_expr) + " words (1.." + std::to_string(LAPID_B200_EXPR_WORDS) + ")");
+    int depth = 0;
+    bool extra = false;
+    for (uint32_t i = 0; i < l.n_expr; i++) {
+        const uint32_t w = l.expr[i], op = w & 0xffu, arg = w >> 8;
+        int pops = 0;
+        if (op == LAPID_B200_EXPR_LOAD) {
+            if (arg > 1) fail("unsupported", "b200 matmul: epilogue Load(" + std::to_string(arg) + "): one extra is supported");
+            extra = extra || arg == 1;
+        } else if (op == LAPID_B200_EXPR_CONST) {
+            if (++i >= l.n_expr) fail("invalid_launch", "b200 matmul: epilogue expression ends inside a constant");
+        } else if (op >= LAPID_B200_EXPR_NEG && op <= LAPID_B200_EXPR_ABS) {
+            pops = 1;
+        } else if (op >= LAPID_B200_EXPR_ADD && op <= LAPID_B200_EXPR_CMPEQ) {
+            pops = 2;
+        } else if (op == LAPID_B200_EXPR_WHERE) {
+            pops = 3;
+        } else {
+            fail("unsupported", "b200 matmul: epilogue node " + std::to_string(op) + " (the f32 nodes of the expression type are supported)");
+        }
+        if (depth < pops) fail("invalid_launch", "b200 matmul: epilogue expression pops an empty stack at word " + std::to_string(i));
+        depth += 1 - pops;
+        if (depth > 4) fail("unsupported", "b200 matmul: epilogue expression needs more than four values on the stack");
+    }
+    if (depth != 1) fail("invalid_launch", "b200 matmul: epilogue expression leaves " + std::to_string(depth) + " values");
+    return extra;
 }
 
 // Checks that need no buffers (prepare runs these alone).
@@ -356,13 +398,13 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
         fail("unsupported_dtype", "b200 matmul: b dtype " + std::to_string(l.b_dtype) + " (want int8, int4, q4_k, q5_k, q6_k or mxfp4)");
     if ((!is_act_float(l.a_dtype) && l.a_dtype != LAPID_B200_DTYPE_ACT_Q8) || l.out_dtype != LAPID_B200_DTYPE_F32)
         fail("unsupported_dtype", "b200 matmul: a must be f32, f16 or bf16 and out f32");
-    if (l.epilogue != LAPID_B200_EPILOGUE_NONE && l.epilogue != LAPID_B200_EPILOGUE_ADD)
+    if (l.epilogue != LAPID_B200_EPILOGUE_NONE && l.epilogue != LAPID_B200_EPILOGUE_ADD && l.epilogue != LAPID_B200_EPILOGUE_EXPR)
         fail("unsupported", "b200 matmul: epilogue " + std::to_string(l.epilogue));
-    int want_inputs = l.epilogue == LAPID_B200_EPILOGUE_ADD ? 3 : 2;
+    const bool reads_extra = l.epilogue == LAPID_B200_EPILOGUE_ADD || (l.epilogue == LAPID_B200_EPILOGUE_EXPR && check_expr(l));
+    int want_inputs = reads_extra ? 3 : 2;
     if (l.n_inputs != want_inputs)
         fail("invalid_launch", "expected " + std::to_string(want_inputs) + " inputs, got " + std::to_string(l.n_inputs));
-    if (l.epilogue == LAPID_B200_EPILOGUE_ADD && l.extra_dtype != LAPID_B200_DTYPE_F32)
-        fail("unsupported_dtype", "b200 matmul: extra must be f32");
+    if (reads_extra && l.extra_dtype != LAPID_B200_DTYPE_F32) fail("unsupported_dtype", "b200 matmul: extra must be f32");
     const uint64_t lim = 1ull << 31;  // 32-bit indexing inside the kernels
     if (l.batch >= lim || l.m >= lim || l.n >= lim || l.k >= lim || l.batch * l.m >= lim)
         fail("too_large", "b200 matmul: dimensions " + dims_str(l) + " exceed 32-bit indexing");
@@ -694,7 +736,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
                                       std::to_string(ins[0]->bytes / act_elem_size(l.a_dtype)));
     }
     const float *extra = nullptr;
-    if (l.epilogue == LAPID_B200_EPILOGUE_ADD) {
+    if (l.n_inputs == 3) {  // (plan_launch has matched the count to what the epilogue reads)
         // lowest and highest element the view touches over [batch, m, n]
         int64_t lo = (int64_t)l.extra.offset, hi = (int64_t)l.extra.offset;
         const uint64_t ext[3] = {l.batch, l.m, l.n};
@@ -718,14 +760,29 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
     g.ex_s0 = l.extra.strides[0];
     g.ex_s1 = l.extra.strides[1];
     g.ex_s2 = l.extra.strides[2];
+    if (l.epilogue == LAPID_B200_EPILOGUE_EXPR) {
+        g.epi.n = l.n_expr;
+        for (uint32_t i = 0; i < l.n_expr; i++) g.epi.code[i] = l.expr[i];
+        if (tp) fail("unsupported", "b200: a row-parallel launch adds partial sums up; an epilogue expression cannot be applied to them");
+    }
     g.rows = p.rows;
     g.m = (uint32_t)l.m;
     g.n = (uint32_t)l.n;
     g.k = (uint32_t)l.k;
     if (pend && !(p.gemv && !p.zero_k)) pend->flush(dev);  // anything but a decode launch ends the group
-    if (p.zero_k) {
-        cuda_check(lb::launch_fill_zero_k(g, dev.stream), "fill launch");
+    // a prefill launch (and the k == 0 fill) with an expression stores plain results first; one more kernel applies it
+    auto expr_pass = [&]() {
+        if (!g.epi.n) return;
+        cuda_check(lb::launch_epilogue_expr(g.epi, g.out, g.out_off, g.out_bs, g.out_rs, extra, g.ex_off, g.ex_s0, g.ex_s1, g.ex_s2,
+                                            (uint32_t)l.batch, g.m, g.n, dev.sm_count, dev.stream), "epilogue launch");
         dev.launches++;
+    };
+    if (p.zero_k) {
+        lb::GemvArgs z = g;
+        if (g.epi.n) z.extra = nullptr;
+        cuda_check(lb::launch_fill_zero_k(z, dev.stream), "fill launch");
+        dev.launches++;
+        expr_pass();
         return;
     }
     {   // the blocks themselves, to the end of their last 16-byte line (the Q6_K bulk copies fetch whole lines: 210-byte
@@ -823,12 +880,14 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             if (p.stream) cuda_check(lb::launch_qgemv_kq_stream(l.b_dtype, one, dev.stream_ws, dev.sm_count, pdl, dev.stream), "qgemv launch");
             else if (l.b_dtype == LAPID_B200_DTYPE_Q6_K) cuda_check(lb::launch_qgemv_q6k_mma(one, dev.sm_count, pdl, dev.stream), "qgemv launch");
             else cuda_check(lb::launch_qgemv_q4k_mma(one, dev.sm_count, pdl, dev.stream, dev.gemv_stream ? &dev.stream_ws : nullptr), "qgemv launch");
+            g.epi.n = one.item[0].epi.n;  // (cleared when the launch evaluated its expression itself)
         } else if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (l.b_dtype == LAPID_B200_DTYPE_INT4) cuda_check(lb::launch_qgemv_i4(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (l.b_dtype == LAPID_B200_DTYPE_MXFP4) cuda_check(lb::launch_qgemv_mxfp4(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (p.fast_i8 && ((uintptr_t)g.w & 15) == 0) cuda_check(lb::launch_qgemv_i8_fast(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         dev.launches += dev.stream_ws.kernels > ws_before ? dev.stream_ws.kernels - ws_before : 1;  // (the stream kernel may take two)
+        finish_expr(dev, g);
         return;
     }
     if (p.tc) {
@@ -843,7 +902,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         t.out_off = g.out_off;
         t.out_bs = g.out_bs;
         t.out_rs = g.out_rs;
-        t.extra = extra;
+        t.extra = g.epi.n ? nullptr : extra;
         t.ex_off = g.ex_off;
         t.ex_s0 = g.ex_s0;
         t.ex_s1 = g.ex_s1;
@@ -860,6 +919,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             int launched = 0;
             cuda_check(lb::launch_qgemm_tc(l.b_dtype, t, (char *)dev.scratch + off, dev.sm_count, dev.stream, &launched), "qgemm_tc launch");
             dev.launches += launched;
+            expr_pass();
             return;
         }
     }
@@ -875,7 +935,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
     f.out_off = g.out_off;
     f.out_bs = g.out_bs;
     f.out_rs = g.out_rs;
-    f.extra = extra;
+    f.extra = g.epi.n ? nullptr : extra;
     f.ex_off = g.ex_off;
     f.ex_s0 = g.ex_s0;
     f.ex_s1 = g.ex_s1;
@@ -886,6 +946,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
     f.k = g.k;
     cuda_check(lb::launch_qgemm_f32(l.b_dtype, f, dev.stream), "qgemm_f32 launch");
     dev.launches++;
+    expr_pass();
 }
 
 // After a wait on the device's stream: a kernel whose bounded wait gave up (or that met a bad index) said so in the
@@ -1211,6 +1272,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             lb::qgemv_kq_stream_set_ctas_per_sm(std::atoi(value));
         } else if (k == "gemv_stream_early_ctas") {
             lb::qgemv_kq_stream_set_early_ctas(std::atoi(value));
+        } else if (k == "gemv_stream_big_units") {
+            lb::qgemv_kq_stream_set_big_units(std::atoi(value));
         } else if (k == "gemv_stream_final_tiles") {
             lb::qgemv_kq_stream_set_final_tiles(std::atoi(value));
         } else if (k == "gemv_stream_debug") {

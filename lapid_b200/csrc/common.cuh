@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "kernels.h"
+
 namespace lb {
 
 constexpr int FMT_INT8 = 4;  // lapid dtype codes (crates/lapid-c/src/lib.rs:37-60)
@@ -60,6 +62,40 @@ __device__ __forceinline__ float e8m0_half(uint32_t e) { return __uint_as_float(
 __device__ __forceinline__ float mxfp4_element(const uint8_t *b, uint32_t e) {
     const uint32_t q = b[1 + (e & 15)];
     return xmul((float)mxfp4_kv(e < 16 ? q & 15 : q >> 4), e8m0_half(b[0]));
+}
+
+// The epilogue expression of a launch at one output element (postfix program, see EpiProg): a four-deep stack in
+// registers, one pass over the program's words. f32 throughout; Exp, Log, Sin, Cos, Tanh, Erf and Pow are CUDA's
+// full-precision functions, Recip and Div IEEE divisions (the reference's CPU backend has polynomial versions of its
+// own: results agree to a few ulp, not bit for bit).
+__device__ __forceinline__ float epi_eval(const EpiProg &e, float acc, float extra) {
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    for (uint32_t i = 0; i < e.n; i++) {
+        const uint32_t w = e.code[i], op = w & 0xffu;
+        if (op == EPI_LOAD || op == EPI_CONST) {
+            const float v = op == EPI_CONST ? __uint_as_float(e.code[++i]) : ((w >> 8) ? extra : acc);
+            s3 = s2, s2 = s1, s1 = s0, s0 = v;
+        } else if (op < EPI_UNARY_END) {
+            const float x = s0;
+            s0 = op == EPI_NEG ? -x : op == EPI_EXP ? expf(x) : op == EPI_LOG ? logf(x) : op == EPI_SQRT ? sqrtf(x)
+               : op == EPI_RSQRT ? 1.0f / sqrtf(x) : op == EPI_RECIP ? 1.0f / x : op == EPI_SIN ? sinf(x) : op == EPI_COS ? cosf(x)
+               : op == EPI_TANH ? tanhf(x) : op == EPI_ERF ? erff(x) : fabsf(x);
+        } else if (op < EPI_BINARY_END) {
+            const float a = s1, b = s0;
+            s0 = op == EPI_ADD ? a + b : op == EPI_SUB ? a - b : op == EPI_MUL ? a * b : op == EPI_DIV ? a / b : op == EPI_MAX ? fmaxf(a, b)
+               : op == EPI_MIN ? fminf(a, b) : op == EPI_POW ? powf(a, b) : op == EPI_CMPLT ? (a < b ? 1.0f : 0.0f) : (a == b ? 1.0f : 0.0f);
+            s1 = s2, s2 = s3;
+        } else {  // EPI_WHERE: cond, a, b -> cond != 0 ? a : b
+            s0 = s2 != 0.0f ? s1 : s0;
+            s1 = s3;
+        }
+    }
+    return s0;
+}
+// What a kernel that evaluates expressions itself stores for accumulator `v` of the output element whose extra lies at index `idx`.
+template <class P> __device__ __forceinline__ float epilogue(const P &p, float v, int64_t idx) {
+    if (p.epi.n == 0) return p.extra ? v + p.extra[idx] : v;
+    return epi_eval(p.epi, v, p.extra ? p.extra[idx] : 0.0f);
 }
 
 // ggml's nearest_int (crates/lapid-quant/src/kquant.rs:25-28): round half to even through the

@@ -221,4 +221,31 @@ cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint
     return cudaLaunchKernelEx(&cfg, silu_mul_kernel, gate, up, out, n4, q.qa ? cols / 4 : 1u, q);
 }
 
+// ---- the epilogue expression of a prefill launch, applied to its output in place (the GEMM kernels store the plain
+//      accumulators first; the decode kernels evaluate the expression in their own stores)
+__global__ void __launch_bounds__(256) epilogue_expr_kernel(EpiProg prog, float *out, uint64_t out_off, uint64_t out_bs, uint64_t out_rs,
+                                                            const float *extra, uint64_t ex_off, int64_t ex_s0, int64_t ex_s1, int64_t ex_s2,
+                                                            uint32_t batch, uint32_t m, uint32_t n) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint64_t total = (uint64_t)batch * m * n;
+    for (uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t row = e / n, j = e - row * n, bt = row / m, i = row - bt * m;
+        float *o = out + out_off + bt * out_bs + i * out_rs + j;
+        const float x = extra ? extra[(int64_t)ex_off + (int64_t)bt * ex_s0 + (int64_t)i * ex_s1 + (int64_t)j * ex_s2] : 0.0f;
+        *o = epi_eval(prog, *o, x);
+    }
+}
+
+cudaError_t launch_epilogue_expr(const EpiProg &prog, float *out, uint64_t out_off, uint64_t out_bs, uint64_t out_rs, const float *extra,
+                                 uint64_t ex_off, int64_t ex_s0, int64_t ex_s1, int64_t ex_s2, uint32_t batch, uint32_t m, uint32_t n,
+                                 int sm_count, cudaStream_t stream) {
+    const uint64_t total = (uint64_t)batch * m * n;
+    if (!total || !prog.n) return cudaSuccess;
+    uint64_t blocks = (total + 255) / 256;
+    if (blocks > (uint64_t)sm_count * 16) blocks = (uint64_t)sm_count * 16;
+    epilogue_expr_kernel<<<(unsigned)blocks, 256, 0, stream>>>(prog, out, out_off, out_bs, out_rs, extra, ex_off, ex_s0, ex_s1, ex_s2, batch, m, n);
+    return cudaGetLastError();
+}
+
 }  // namespace lb

@@ -7,6 +7,26 @@
 
 namespace lb {
 
+// A fused epilogue expression (MatMulSpec.epilogue, crates/lapid-compiler/src/ir.rs:94-111 restricted to its f32 part) as
+// a postfix program over Load(0) = the accumulator and Load(1) = extras[0]: `code[i]` = op | arg << 8; EPI_CONST is
+// followed by the constant's bits. n == 0: no program (the launch's `extra`, if any, is added). Evaluated with a
+// four-deep register stack (epi_eval in common.cuh); the host checks the stack discipline before a launch.
+constexpr int EPI_WORDS = 24;
+enum : uint32_t {
+    EPI_LOAD = 1, EPI_CONST = 2,
+    EPI_NEG = 16, EPI_EXP, EPI_LOG, EPI_SQRT, EPI_RSQRT, EPI_RECIP, EPI_SIN, EPI_COS, EPI_TANH, EPI_ERF, EPI_ABS, EPI_UNARY_END,
+    EPI_ADD = 32, EPI_SUB, EPI_MUL, EPI_DIV, EPI_MAX, EPI_MIN, EPI_POW, EPI_CMPLT, EPI_CMPEQ, EPI_BINARY_END,
+    EPI_WHERE = 48,
+};
+struct EpiProg {
+    uint32_t n;
+    uint32_t code[EPI_WORDS];
+};
+// Applies `prog` to out[bt, i, j] in place (the prefill kernels run their GEMM first): rows x n elements.
+cudaError_t launch_epilogue_expr(const EpiProg &prog, float *out, uint64_t out_off, uint64_t out_bs, uint64_t out_rs, const float *extra,
+                                 uint64_t ex_off, int64_t ex_s0, int64_t ex_s1, int64_t ex_s2, uint32_t batch, uint32_t m, uint32_t n,
+                                 int sm_count, cudaStream_t stream);
+
 // ---- dequant.cu
 cudaError_t launch_gather(int fmt, const void *table, uint64_t scales_offset, const int32_t *ids, uint64_t rows, uint64_t cols,
                           uint64_t count, float *out, int *status, int sm_count, cudaStream_t stream);  // fmt < 0: f32 table
@@ -86,6 +106,9 @@ struct GemvArgs {
     const float *extra;     // epilogue `acc + extra[bt, i, j]`, nullptr for none
     uint64_t ex_off;
     int64_t ex_s0, ex_s1, ex_s2;
+    EpiProg epi;            // epi.n != 0: the epilogue is this expression over the accumulator and extra[bt, i, j] instead. A kernel
+                            // then stores the plain accumulator (the host applies the expression with one more kernel) unless
+                            // its launcher says it evaluates expressions itself (and clears epi.n in the caller's struct)
     uint32_t rows, m, n, k;
     const TpPushTable *tp;  // not nullptr (K-quant fast kernels only): the result, row-major [rows, n], goes to slot[rank] of every
                             // rank's buffer as {value, epoch} pairs instead of to `out`
@@ -210,6 +233,7 @@ void qgemv_kq_stream_set_config(int index);     // tuning: -1 = choose
 void qgemv_kq_stream_set_ctas_per_sm(int n);    // tuning: 0 = choose
 void qgemv_kq_stream_set_debug(int v);          // measurement only: 2 = drop partial tiles (wrong results)
 void qgemv_kq_stream_set_final_tiles(int v);    // tuning: row tiles per finalising CTA of a launch that runs ahead (0 = choose)
+void qgemv_kq_stream_set_big_units(int v);      // tuning: 128-row units per SM from which the 32-row warps are used
 void qgemv_kq_stream_set_early_ctas(int v);     // tuning: CTAs per SM of a launch that runs ahead of its predecessor (0 = as any launch)
 // Int8 planes on the same instruction (K a multiple of 512); same activation tiles.
 bool qgemv_i8_mma_shape_ok(uint32_t rows, uint32_t k);

@@ -354,8 +354,7 @@ __global__ void __launch_bounds__(WARPS * 32) qgemv_kernel(GemvArgs p) {
                     uint32_t col = t * C + c;
                     if (lane == 0 && col < n) {
                         uint32_t bt = r / p.m, i = r % p.m;
-                        if (p.extra)
-                            v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)col * p.ex_s2];
+                        if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)col * p.ex_s2];
                         p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + col] = v;
                     }
                 }
@@ -372,7 +371,7 @@ __global__ void fill_zero_k_kernel(GemvArgs p) {
         uint32_t r = (uint32_t)(idx / p.n), col = (uint32_t)(idx % p.n);
         uint32_t bt = r / p.m, i = r % p.m;
         float v = 0.0f;
-        if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)col * p.ex_s2];
+        if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)col * p.ex_s2];
         p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + col] = v;
     }
 }

@@ -267,7 +267,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
                 if (row < p.n && r < M) {
                     float x = v[tl][i];
                     const uint32_t bt = r / p.m, ri = r % p.m;
-                    if (p.extra) x += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
+                    if (p.extra && !p.epi.n) x += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
                     if (p.tp) tp_push_value(&tp_ctx[warp], (uint64_t)r * p.n + row, x);  // row-parallel partial: to every rank
                     else p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = x;
                 }
@@ -519,7 +519,8 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
 // one waiting CTA for everything before it -- so the pieces are complete and the output may be written; the stream
 // kernel's CTAs meanwhile have left their SMs to the next launch. One item per warp and round, all its pieces in flight
 // together. The last CTA frees the staging region.
-template <int WARPS, int TILES, int NG>
+// EXPR: a member has an epilogue expression (a variant of its own: the evaluator's code and stack stay out of the other).
+template <int WARPS, int TILES, int NG, bool EXPR>
 __global__ void __launch_bounds__(256) qgemv_kq_finalize_kernel(const Head head, GemvGroupT<NG> grp) {
     constexpr int RPW = 16 * TILES, RT = RPW * WARPS, EW = 128 * TILES, NE = 4 * TILES;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -564,7 +565,9 @@ __global__ void __launch_bounds__(256) qgemv_kq_finalize_kernel(const Head head,
             if (row < p.n && r < M) {
                 float x = acc[e];
                 const uint32_t bt = r / p.m, ri = r % p.m;
-                if (p.extra) x += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
+                const int64_t ex = (int64_t)(p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2);
+                if constexpr (EXPR) x = epilogue(p, x, ex);
+                else if (p.extra) x += p.extra[ex];
                 p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = x;
             }
         }
@@ -652,6 +655,7 @@ static int g_ctas_per_sm = 0;  // 0 = choose
 static int g_debug = 0;        // measurement only: 2 = drop the partial tiles (wrong results)
 // Tuning: CTAs per SM of a launch that runs ahead of its predecessor (0 = as pick_config says).
 static int g_early_ctas = 0;
+static int g_big_units = 16;   // tuning: 128-row units per SM from which the 32-row warps are used
 static int g_final_tiles = 0;  // tuning: row tiles per finalising CTA of a launch that runs ahead (0 = choose)
 // Diagnostics: a device buffer of TRACE_WORDS words per CTA for the next `g_trace_cap` launches (row = launch, in launch order)
 static unsigned long long *g_trace = nullptr;
@@ -742,7 +746,12 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, StreamWs &ws, int sm_count, bool 
     fin.stream = stream;
     fin.attrs = attr;
     fin.numAttrs = 1;
-    return cudaLaunchKernelEx(&fin, qgemv_kq_finalize_kernel<WARPS, TILES, NG>, head, g);
+    bool expr = false;
+    for (int i = 0; i < g.count; i++) expr = expr || g.item[i].epi.n != 0;
+    const cudaError_t e = expr ? cudaLaunchKernelEx(&fin, qgemv_kq_finalize_kernel<WARPS, TILES, NG, true>, head, g)
+                               : cudaLaunchKernelEx(&fin, qgemv_kq_finalize_kernel<WARPS, TILES, NG, false>, head, g);
+    for (int i = 0; i < g.count; i++) g.item[i].epi.n = 0;  // (the adding-up kernel has evaluated the members' expressions)
+    return e;
 }
 
 template <int FMT, int WARPS, int TILES, int NB, int STAGES, int MINB>
@@ -754,7 +763,10 @@ static cudaError_t launch_cfg(GemvGroup &g, StreamWs &ws, int sm_count, bool pdl
     one.act_copy[0] = 0;
     one.count = 1;
     one.act_bytes = 0;
-    return launch_n<FMT, WARPS, TILES, NB, STAGES, MINB, 1>(one, ws, sm_count, pdl, early, per_sm, stream);
+    const cudaError_t e = launch_n<FMT, WARPS, TILES, NB, STAGES, MINB, 1>(one, ws, sm_count, pdl, early, per_sm, stream);
+    g.item[0].epi.n = one.item[0].epi.n;  // (cleared when the launch evaluated its expression itself)
+    g.item[0].early = one.item[0].early;
+    return e;
 }
 
 // Measured (M = 4, 8; early = launches that run ahead of their predecessor, as in a list over one quantized operand):
@@ -770,7 +782,7 @@ static int pick_config(const GemvGroup &g, int sm_count, bool early, int &per_sm
     if (g_force_config >= 0) return g_force_config;
     uint64_t units = 0;  // 128 rows x 512 k
     for (int i = 0; i < g.count; i++) units += (uint64_t)((g.item[i].n + 127) / 128) * ((g.item[i].k / QK + 1) / 2);
-    if (units >= 16 * (uint64_t)sm_count) return 1;
+    if (units >= (uint64_t)g_big_units * (uint64_t)sm_count) return 1;
     if (units < 2 * (uint64_t)sm_count) {  // small matrices (Q5_K only: Q4_K has the per-warp-ring kernel for them): one CTA of three stages per SM
         per_sm = 1;
         return 2;
@@ -798,6 +810,7 @@ void qgemv_kq_stream_set_ctas_per_sm(int n) { ks::g_ctas_per_sm = n < 0 ? 0 : n;
 void qgemv_kq_stream_set_debug(int v) { ks::g_debug = v; }
 void qgemv_kq_stream_set_early_ctas(int v) { ks::g_early_ctas = v < 0 ? 0 : v; }
 void qgemv_kq_stream_set_final_tiles(int v) { ks::g_final_tiles = v < 0 ? 0 : v; }
+void qgemv_kq_stream_set_big_units(int v) { ks::g_big_units = v < 1 ? 16 : v; }
 
 // Diagnostics: record the timeline of every CTA of the next `launches` launches of this kernel (0 = stop and free).
 cudaError_t qgemv_kq_stream_trace_begin(uint32_t launches, int sm_count) {

@@ -95,7 +95,7 @@ template <int M> __global__ void __launch_bounds__(WARPS * 32) qgemv_mxfp4_kerne
             for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
             if (lane == 0) {
                 const uint32_t bt = r / p.m, i = r % p.m;
-                if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
+                if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
                 p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
             }
         }

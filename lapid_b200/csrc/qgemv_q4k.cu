@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
                 for (int r = 0; r < M; r++) {
                     float v = pend[(q * RPW + sub) * M + r];
                     const uint32_t bt = r / p.m, i = r % p.m;
-                    if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
+                    if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
                     p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
                 }
             }
@@ -445,7 +445,7 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             for (int o = G / 2; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
             if (gl == 0 && row < n) {
                 const uint32_t bt = r / p.m, i = r % p.m;
-                if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
+                if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
                 if constexpr (MOE) p.out[p.out_off + (uint64_t)pair * n + row] = v;
                 else if (p.tp) tp_push_value(&tp_ctx, (uint64_t)r * n + row, v);  // row-parallel partial: to every rank
                 else p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;

@@ -266,7 +266,7 @@ qgemv_q6k_mma_kernel(const __grid_constant__ WeightMapsT<NG> maps, GemvGroupT<NG
             const uint32_t r = 2 * (el & 3) + (i & 1);
             if (row < p.n && r < M) {
                 const uint32_t bt = r / p.m, ri = r % p.m;
-                if (p.extra) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
+                if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)ri * p.ex_s1 + (int64_t)row * p.ex_s2];
                 if (p.tp) tp_push_value(&tp_ctx, (uint64_t)r * p.n + row, v);  // row-parallel partial: to every rank
                 else p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)ri * p.out_rs + row] = v;
             }

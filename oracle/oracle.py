@@ -272,6 +272,46 @@ class Oracle:
 _cache: dict[bool, Oracle] = {}
 
 
+def epilogue(words, acc: np.ndarray, extra: np.ndarray | None = None) -> np.ndarray:
+    """The reference's epilogue expression (`Epilogue::apply`, crates/lapid-cpu/src/matmul/mod.rs:133-161, over the
+    expression type of crates/lapid-compiler/src/ir.rs:94-111, f32 nodes) evaluated element by element: `words` is the
+    postfix program of the C ABI (one word per node, op | arg << 8; 2 = constant, followed by its bits), Load(0) = `acc`,
+    Load(1) = `extra`. Every node is one f32 numpy operation (lapid-cpu has polynomial exp / erf of its own: a few ulp
+    from these)."""
+    f = np.float32
+    acc = np.asarray(acc, f)
+    st, i = [], 0
+    un = {16: np.negative, 17: np.exp, 18: np.log, 19: np.sqrt, 20: lambda x: f(1) / np.sqrt(x), 21: lambda x: f(1) / x, 22: np.sin,
+          23: np.cos, 24: np.tanh, 26: np.abs}
+    bi = {32: np.add, 33: np.subtract, 34: np.multiply, 35: np.divide, 36: np.maximum, 37: np.minimum, 38: np.power,
+          39: lambda a, b: (a < b).astype(f), 40: lambda a, b: (a == b).astype(f)}
+    with np.errstate(all="ignore"):
+        while i < len(words):
+            w = int(words[i]); op, arg = w & 0xff, w >> 8
+            if op == 1:
+                st.append(acc if arg == 0 else np.broadcast_to(np.asarray(extra, f), acc.shape))
+            elif op == 2:
+                i += 1
+                st.append(np.full(acc.shape, np.uint32(words[i]).view(f), f))
+            elif op == 25:
+                import math
+                st.append(np.vectorize(math.erf, otypes=[np.float64])(st.pop().astype(np.float64)).astype(f))
+            elif op in un:
+                st.append(un[op](st.pop()).astype(f))
+            elif op in bi:
+                b = st.pop(); a = st.pop()
+                st.append(bi[op](a, b).astype(f))
+            elif op == 48:
+                b = st.pop(); a = st.pop(); c = st.pop()
+                st.append(np.where(c != 0, a, b).astype(f))
+            else:
+                raise OracleError("unsupported", f"epilogue node {op}")
+            i += 1
+    if len(st) != 1:
+        raise OracleError("invalid_launch", f"epilogue expression leaves {len(st)} values")
+    return st[0]
+
+
 def load(fast: bool = False) -> Oracle:
     """The parity copy by default; ``fast=True`` compiles and loads the timed ``-march=native`` copy."""
     if fast not in _cache:

@@ -90,5 +90,12 @@ def test_launch_marshalling_matches_header_struct():
     assert (c.kind, c.b_dtype, c.n_inputs, c.epilogue) == (2, 8, 3, 1)
     assert (c.a.row_stride, c.a.batch_stride, c.b.row_stride, c.out.row_stride) == (260, 780, 256, 20)
     assert list(c.inputs) == [0, 1, 3] and c.output == 2 and list(c.extra.strides) == [0, 0, 1]
-    # struct size as a C compiler lays it out: 8 int32 + 4 u64 + 3*3 u64 + (u64 + 3 i64) + 4 u32
-    assert C.sizeof(_lib.LaunchC) == 32 + 32 + 72 + 32 + 16
+    # struct size as a C compiler lays it out: 8 int32 + 4 u64 + 3*3 u64 + (u64 + 3 i64) + 4 u32 + (1 + 24) u32, padded to 8
+    assert C.sizeof(_lib.LaunchC) == 32 + 32 + 72 + 32 + 16 + 104
+    # an epilogue expression: postfix words, Load(1) makes the extra the third input
+    e = lp.backend.Expr.silu(lp.backend.Expr.load(0)) * lp.backend.Expr.load(1)
+    c = lp.backend.matmul_launch(lp.DType.Q4K, 2, 64, 256, expr=e, extra_input=5).to_c()
+    assert (c.epilogue, c.n_inputs, c.n_expr, list(c.inputs)) == (2, 3, 11, [0, 1, 5])
+    assert list(c.expr)[:11] == [1, 1, 16, 17, 2, 0x3F800000, 32, 21, 34, 1 | 1 << 8, 34] and list(c.extra.strides) == [128, 64, 1]
+    c = lp.backend.matmul_launch(lp.DType.Q4K, 2, 64, 256, expr=lp.backend.Expr.load(0).tanh()).to_c()
+    assert (c.n_inputs, c.n_expr) == (2, 2)

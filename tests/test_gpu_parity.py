@@ -1127,3 +1127,79 @@ def test_a_device_side_wait_that_runs_out_is_reported(be, oracle):
     finally:
         be.set_option("tp_spin_limit", "0")
         lib.lapid_b200_tp_comm_free(comm)
+
+
+# ------------------------------------------------------------------ epilogue expressions
+def _expr_cases():
+    from lapid_b200.backend import Expr
+    acc, ext = Expr.load(0), Expr.load(1)
+    return [("silu", Expr.silu(acc), False), ("mul", acc * ext, True), ("silu_mul", Expr.silu(acc) * ext, True),
+            ("gelu_tanh", Expr.gelu_tanh(acc), False), ("relu", Expr.where(acc.lt(0.0), 0.0, acc), False),
+            ("mix", ((acc * acc + 1.0).sqrt() - ext.abs().max(0.25)).min(acc * 0.5 + 1.0), True)]
+
+
+@pytest.mark.parametrize("fmt,ofmt", [(lp.DType.Q4K, O.Q4_K), (lp.DType.Q5K, O.Q5_K), (lp.DType.Q6K, O.Q6_K), (lp.DType.Int8, O.INT8),
+                                      (lp.DType.Int4, O.INT4), (lp.DType.MXFP4, O.MXFP4)])
+def test_epilogue_expressions(be, oracle, fmt, ofmt):
+    """`MatMulSpec.epilogue` as an expression (crates/lapid-compiler/src/ir.rs:94-111, applied by
+    `Epilogue::apply`, crates/lapid-cpu/src/matmul/mod.rs:133-161): the gate / up epilogues of a gated MLP
+    (crates/lapid-nn/src/mlp.rs:84) and other f32 trees, through every decode kernel (one row, few rows, shapes that
+    take the fast, the tensor-core, the balanced-stream and the generic kernels, a list whose launches run ahead) and
+    through the prefill kernels, against the oracle's result with the expression applied by numpy. Bars: decode
+    and the exact prefill kernel max_rel 2e-5 (transcendental nodes: CUDA's f32 functions against numpy's); prefill on
+    tensor cores (bf16 operands) rel_l2 4e-3 and max_rel 5e-2 (the expression scales the operands' rounding)."""
+    shapes = [(1, 96, 2048), (2, 130, 2048), (4, 77, 4096), (8, 2500, 4096), (3, 33, 256), (8, 4096, 4096), (40, 200, 2048), (128, 256, 4096)]
+    for (name, e, has) in _expr_cases():
+        launches, bufs, wants = [], [], []
+        for i, (m, n, k) in enumerate(shapes):
+            seed = 1500 + 7 * i
+            qb = oracle.quantize(ofmt, O.normal(seed, n * k, 0.05), n, k)
+            a = O.normal(seed + 1, m * k)
+            x = (O.normal(seed + 2, m * n) * 0.5 + 0.7).astype(np.float32)
+            acc, path = oracle.matmul(ofmt, a, qb, n, k, m=m)
+            want = O.epilogue(e.words, acc.reshape(m, n), x.reshape(m, n) if has else None).reshape(-1)
+            base = len(bufs)
+            bufs += [be.upload(a), be.upload(qb), be.alloc(m * n * 4)] + ([be.upload(x)] if has else [])
+            launches.append(matmul_launch(fmt, m, n, k, inputs=(base, base + 1), output=base + 2, expr=e, extra_input=base + 3 if has else None))
+            wants.append((base + 2, want, m, path))
+        be.prepare(launches)
+        be.execute(launches, bufs)      # one list: the decode launches behind the first run ahead of their predecessors
+        for (b, want, m, path) in wants:
+            got = bufs[b].download().view(np.float32)
+            tc = path == "f32_act" and fmt in (lp.DType.Q4K, lp.DType.Q5K, lp.DType.Q6K)
+            assert max_rel(got, want) <= (5e-2 if tc else 2e-5), (name, m, max_rel(got, want))
+            assert rel_l2(got, want) <= (4e-3 if tc else 1e-5), (name, m, rel_l2(got, want))
+        for l, (b, want, m, path) in zip(launches, wants):   # and each launch alone (a dependent launch)
+            bufs[b].write(0, np.zeros(want.size, np.float32))
+            be.execute([l], bufs)
+            got = bufs[b].download().view(np.float32)
+            tc = path == "f32_act" and fmt in (lp.DType.Q4K, lp.DType.Q5K, lp.DType.Q6K)
+            assert max_rel(got, want) <= (5e-2 if tc else 2e-5), (name, m, "alone", max_rel(got, want))
+
+
+def test_epilogue_expression_is_validated(be, oracle):
+    from lapid_b200.backend import Expr
+    n, k = 64, 256
+    qb = oracle.quantize(O.Q4_K, O.normal(1600, n * k, 0.05), n, k)
+    bufs = [be.upload(O.normal(1601, k)), be.upload(qb), be.alloc(n * 4), be.upload(O.normal(1602, n))]
+
+    def run(words, extra=False):
+        l = matmul_launch(lp.DType.Q4K, 1, n, k, expr=Expr(words), extra_input=3 if extra else None)
+        with pytest.raises(lp.LapidError) as err:
+            be.execute([l], bufs)
+        return err.value.code
+
+    assert run([16]) == "invalid_launch"                     # a unary node on an empty stack
+    assert run([1, 1]) == "invalid_launch"                   # two values left
+    assert run([1, 2]) == "invalid_launch"                   # ends inside a constant
+    assert run([1, 99]) == "unsupported"                     # an unknown node
+    assert run([1 | 2 << 8]) == "unsupported"                # Load(2): one extra is supported
+    assert run([1, 1, 1, 1, 1, 32, 32, 32, 32]) == "unsupported"   # five values on the stack
+    l = matmul_launch(lp.DType.Q4K, 1, n, k, expr=Expr.load(0) * Expr.load(1), extra_input=3)
+    import dataclasses as dc
+    with pytest.raises(lp.LapidError) as err:                # the program loads the extra but the launch has two inputs
+        be.execute([dc.replace(l, inputs=(0, 1))], bufs)
+    assert err.value.code == "invalid_launch"
+    be.execute([l], bufs)                                    # and the device still works
+    acc, _ = oracle.matmul(O.Q4_K, bufs[0].download().view(np.float32), qb, n, k, m=1)
+    assert max_rel(bufs[2].download().view(np.float32), acc * bufs[3].download().view(np.float32)) <= 2e-5
