@@ -1272,6 +1272,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             lb::qgemv_kq_stream_set_ctas_per_sm(std::atoi(value));
         } else if (k == "gemv_stream_early_ctas") {
             lb::qgemv_kq_stream_set_early_ctas(std::atoi(value));
+        } else if (k == "gemv_stream_spin_limit") {
+            lb::qgemv_kq_stream_set_spin_limit(std::atoi(value));
         } else if (k == "gemv_stream_big_units") {
             lb::qgemv_kq_stream_set_big_units(std::atoi(value));
         } else if (k == "gemv_stream_final_tiles") {

@@ -233,6 +233,7 @@ void qgemv_kq_stream_set_config(int index);     // tuning: -1 = choose
 void qgemv_kq_stream_set_ctas_per_sm(int n);    // tuning: 0 = choose
 void qgemv_kq_stream_set_debug(int v);          // measurement only: 2 = drop partial tiles (wrong results)
 void qgemv_kq_stream_set_final_tiles(int v);    // tuning: row tiles per finalising CTA of a launch that runs ahead (0 = choose)
+void qgemv_kq_stream_set_spin_limit(int v);     // polls before the claim of a staging region gives up (0 = default)
 void qgemv_kq_stream_set_big_units(int v);      // tuning: 128-row units per SM from which the 32-row warps are used
 void qgemv_kq_stream_set_early_ctas(int v);     // tuning: CTAs per SM of a launch that runs ahead of its predecessor (0 = as any launch)
 // Int8 planes on the same instruction (K a multiple of 512); same activation tiles.

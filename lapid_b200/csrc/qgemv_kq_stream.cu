@@ -94,6 +94,7 @@ struct alignas(64) Head {
     float *stage;                        // staging region of a launch that runs ahead: partial tiles
     uint32_t *words;                     // its control words
     uint32_t launch_id, nfinal;          // owner value; CTAs of the kernel that adds the pieces up
+    uint32_t spin;                       // polls before a wait on the staging region gives up
 };
 
 template <int NG> struct Maps {
@@ -205,7 +206,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
                 // frees it. A launch that finds the region owned by an earlier one waits for that (the earlier launch
                 // depends on nothing this one does).
                 uint32_t ok = 2;
-                for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT; spin++) {
+                for (uint32_t spin = 0; spin < head.spin; spin++) {
                     uint32_t o = *(volatile uint32_t *)head.words;
                     if (o == 0) o = atomicCAS(head.words, 0u, head.launch_id) ? *(volatile uint32_t *)head.words : head.launch_id;
                     if (o == head.launch_id) {
@@ -278,7 +279,7 @@ qgemv_kq_stream_kernel(const __grid_constant__ Maps<NG> maps, const Head head, G
     //      the position of this span among the spans that share the tile
     auto stage_out = [&](uint32_t gt, const float (&acc)[TILES][4]) {
         uint32_t ok = *region_ok;
-        for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT && ok == 0; spin++) {
+        for (uint32_t spin = 0; spin < PAIR_SPIN_LIMIT && ok == 0; spin++) {  // (the producer's claim is what is bounded by head.spin)
             __nanosleep(32);
             ok = *region_ok;
         }
@@ -652,9 +653,11 @@ static bool weight_map(const GemvArgs &a, uint32_t blk, uint32_t nb, uint32_t bo
 constexpr int N_CONFIGS = 5;
 static int g_force_config = -1;
 static int g_ctas_per_sm = 0;  // 0 = choose
-static int g_debug = 0;        // measurement only: 2 = drop the partial tiles (wrong results)
+static int g_debug = 0;        // bits: 2 = drop the partial tiles (measurement only: wrong results); 4 = no launch runs ahead;
+                               // 8 = test hook, see launch_n
 // Tuning: CTAs per SM of a launch that runs ahead of its predecessor (0 = as pick_config says).
 static int g_early_ctas = 0;
+static int g_spin_limit = 0;   // polls before the claim of a staging region gives up (0 = PAIR_SPIN_LIMIT); tests shorten it
 static int g_big_units = 16;   // tuning: 128-row units per SM from which the 32-row warps are used
 static int g_final_tiles = 0;  // tuning: row tiles per finalising CTA of a launch that runs ahead (0 = choose)
 // Diagnostics: a device buffer of TRACE_WORDS words per CTA for the next `g_trace_cap` launches (row = launch, in launch order)
@@ -732,6 +735,11 @@ static cudaError_t launch_n(GemvGroupT<NG> &g, StreamWs &ws, int sm_count, bool 
         head.stage = (float *)(region + WORDS_BYTES);
         if (++ws.next_id == 0) ws.next_id = 1;
         head.launch_id = ws.next_id;
+        head.spin = g_spin_limit > 0 ? (uint32_t)g_spin_limit : PAIR_SPIN_LIMIT;
+        if (g_debug & 8) {  // test hook: the region looks owned by a launch that never frees it, so the claim runs out
+            static const uint32_t foreign = 0x7FFFFFFFu;
+            if (cudaError_t e = cudaMemcpyAsync(head.words, &foreign, 4, cudaMemcpyHostToDevice, stream); e != cudaSuccess) return e;
+        }
         const uint32_t per = g_final_tiles > 0 ? (uint32_t)g_final_tiles : 16;  // items (tile x warp slice) per CTA of the adding-up kernel
         head.nfinal = (tiles * WARPS + per - 1) / per;
     }
@@ -811,6 +819,7 @@ void qgemv_kq_stream_set_debug(int v) { ks::g_debug = v; }
 void qgemv_kq_stream_set_early_ctas(int v) { ks::g_early_ctas = v < 0 ? 0 : v; }
 void qgemv_kq_stream_set_final_tiles(int v) { ks::g_final_tiles = v < 0 ? 0 : v; }
 void qgemv_kq_stream_set_big_units(int v) { ks::g_big_units = v < 1 ? 16 : v; }
+void qgemv_kq_stream_set_spin_limit(int v) { ks::g_spin_limit = v < 0 ? 0 : v; }
 
 // Diagnostics: record the timeline of every CTA of the next `launches` launches of this kernel (0 = stop and free).
 cudaError_t qgemv_kq_stream_trace_begin(uint32_t launches, int sm_count) {

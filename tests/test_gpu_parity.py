@@ -1129,6 +1129,35 @@ def test_a_device_side_wait_that_runs_out_is_reported(be, oracle):
         lib.lapid_b200_tp_comm_free(comm)
 
 
+def test_a_staging_region_that_is_never_freed_is_reported(be, oracle):
+    """Failure detection without a GPU fault, balanced-stream kernel: the staging region of a launch that runs ahead
+    looks owned by a launch that never frees it (a test hook writes a foreign owner word), so the claim of every CTA
+    runs out after a short limit (option gemv_stream_spin_limit); the kernels return, the list's wait fails with
+    "backend", the workspace is cleared and the same list then runs and is right."""
+    m, n, k = 8, 2048, 4096
+    qbs = [oracle.quantize(O.Q4_K, O.normal(1700 + i, n * k, 0.05), n, k) for i in range(3)]
+    x = O.normal(1710, m * k)
+    want = oracle.matmul(O.Q4_K, x, qbs[-1], n, k, m=m)[0]
+    bufs = [be.upload(x)] + [be.upload(q) for q in qbs] + [be.alloc(m * n * 4)]
+    # (launches that overwrite each other's output are never grouped: three kernels, the last two run ahead)
+    ls = [matmul_launch(lp.DType.Q4K, m, n, k, inputs=(0, 1 + i), output=4) for i in range(3)]
+    be.set_option("gemv_stream", "2")
+    be.set_option("gemv_stream_spin_limit", "3000")
+    be.set_option("gemv_stream_debug", "8")
+    try:
+        with pytest.raises(lp.LapidError) as e:
+            be.execute(ls, bufs)
+        assert e.value.code == "backend" and "gave up" in e.value.message
+    finally:
+        be.set_option("gemv_stream_debug", "0")
+        be.set_option("gemv_stream_spin_limit", "0")
+    try:
+        be.execute(ls, bufs)
+        assert max_rel(bufs[4].download().view(np.float32), want) <= 2e-5
+    finally:
+        be.set_option("gemv_stream", "1")
+
+
 # ------------------------------------------------------------------ epilogue expressions
 def _expr_cases():
     from lapid_b200.backend import Expr
