@@ -231,9 +231,19 @@ LAPID_B200_API lapid_b200_status lapid_b200_execute(lapid_b200_device *dev, cons
  * counterpart in the reference, whose execute always waits. */
 LAPID_B200_API lapid_b200_status lapid_b200_execute_async(lapid_b200_device *dev, const lapid_b200_launch *launches,
                                            size_t n_launches, lapid_b200_buffer *const *buffers, size_t n_buffers);
-/* Backend::take_profile (backend.rs:59-62) restricted to this path: number of kernels this
- * library launched on `dev` since the last call. */
+/* Number of kernels this library launched on `dev` since the last call. */
 LAPID_B200_API uint64_t lapid_b200_take_launch_count(lapid_b200_device *dev);
+/* Backend::take_profile (backend.rs:59-62; CUDA side crates/lapid-cuda/src/execute.rs:45-76): GPU time per kernel kind
+ * -- "matmul_decode", "matmul_prefill", "gather", "matmul_id" -- accumulated since the last call while the device option
+ * "profile" is "1" (every launch of an execute list is then bracketed by events and runs on its own: nothing is
+ * grouped, and execute_async waits like execute), sorted by time, then cleared. Writes all *n entries when
+ * cap >= *n, else only sets *n so that the caller can come back with room (nothing is cleared then). */
+typedef struct lapid_b200_profile_entry {
+    char kind[24];
+    uint64_t launches;
+    double ms;
+} lapid_b200_profile_entry;
+LAPID_B200_API lapid_b200_status lapid_b200_take_profile(lapid_b200_device *dev, lapid_b200_profile_entry *entries, size_t cap, size_t *n);
 /* Diagnostics of the balanced-stream decode kernel (no counterpart in the reference): record, for the next
  * `launches` launches of that kernel on this process, one row of 16 words per CTA -- [0] entry time (ns, global
  * timer), then SM clock cycles at [1] entry, [2] first loads issued, [3] first data there, [4] before and [5] after

@@ -42,6 +42,10 @@ class LaunchC(C.Structure):
     ]
 
 
+class ProfileEntryC(C.Structure):
+    _fields_ = [("kind", C.c_char * 24), ("launches", C.c_uint64), ("ms", C.c_double)]
+
+
 class LayoutC(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("rows", "cols", "qs_offset", "qs_bytes", "scales_offset", "scales_bytes", "total")]
 
@@ -72,6 +76,7 @@ SYMBOLS = {
     "lapid_b200_execute": (C.c_int32, [P, C.POINTER(LaunchC), C.c_size_t, C.POINTER(P), C.c_size_t]),
     "lapid_b200_execute_async": (C.c_int32, [P, C.POINTER(LaunchC), C.c_size_t, C.POINTER(P), C.c_size_t]),
     "lapid_b200_take_launch_count": (C.c_uint64, [P]),
+    "lapid_b200_take_profile": (C.c_int32, [P, C.POINTER(ProfileEntryC), C.c_size_t, C.POINTER(C.c_size_t)]),
     "lapid_b200_decode_trace_begin": (C.c_int32, [P, C.c_uint32]),
     "lapid_b200_decode_trace_read": (C.c_int32, [P, P, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "lapid_b200_quant_layout": (C.c_int32, [C.c_int32, C.c_uint64, C.c_uint64, C.POINTER(LayoutC)]),

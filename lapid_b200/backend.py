@@ -411,6 +411,14 @@ class Backend:
     def take_launch_count(self) -> int:
         return int(_lib.lib().lapid_b200_take_launch_count(self._h))
 
+    def take_profile(self) -> list:
+        """``Backend::take_profile``: ``[(kind, launches, ms)]`` since the last call, by time (option ``profile`` = "1")."""
+        n = C.c_size_t(0)
+        check(_lib.lib().lapid_b200_take_profile(self._h, None, 0, C.byref(n)))
+        arr = (_lib.ProfileEntryC * max(1, n.value))()
+        check(_lib.lib().lapid_b200_take_profile(self._h, arr, len(arr), C.byref(n)))
+        return [(arr[i].kind.decode(), int(arr[i].launches), float(arr[i].ms)) for i in range(n.value)]
+
     def decode_trace_begin(self, launches: int) -> None:
         """Record the per-CTA timeline of the next ``launches`` launches of the balanced-stream decode kernel."""
         check(_lib.lib().lapid_b200_decode_trace_begin(self._h, launches))

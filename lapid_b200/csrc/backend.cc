@@ -15,6 +15,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
+#include <map>
 #include <mutex>
 #include <new>
 #include <string>
@@ -181,6 +183,11 @@ struct lapid_b200_device {
     bool two_row_dp4a = false;    // two early Q4_K rows on the dp4a kernel (see execute_impl)
     lb::StreamWs stream_ws{};    // workspace of that kernel: partial sums in flight between CTAs (all zero between launches)
     bool gemm_f32 = false;  // true: rows > gemv_max_rows always take the exact-f32 GEMM instead of the tensor cores
+    // option "profile": every launch of an execute list is bracketed by events (launches run one by one then: nothing is
+    // grouped) and its GPU time added to its kernel kind; lapid_b200_take_profile drains the totals
+    bool profile = false;
+    std::map<std::string, std::pair<uint64_t, double>> profile_by_kind;
+    std::vector<cudaEvent_t> profile_events;
 
     void make_current() const { cuda_check(cudaSetDevice(ordinal), "cudaSetDevice"); }
     ~lapid_b200_device() {
@@ -188,6 +195,7 @@ struct lapid_b200_device {
             if (scratch) cudaFree(scratch);
             if (stream_ws.pairs) cudaFree(stream_ws.pairs);
             if (status_host) cudaFreeHost(status_host);
+            for (cudaEvent_t e : profile_events) cudaEventDestroy(e);
             if (own_stream) cudaStreamDestroy(own_stream);
         }
     }
@@ -1119,16 +1127,40 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
     }
     PendingGroup pend;
     pend.split_early = n >= 8;
-    PendingGroup *pp = dev->gemv_group ? &pend : nullptr;
+    PendingGroup *pp = dev->gemv_group && !dev->profile ? &pend : nullptr;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(dev->stream, &capturing);
+    const bool profiling = dev->profile && capturing == cudaStreamCaptureStatusNone;  // (events of a capture cannot be timed)
+    if (profiling)
+        while (dev->profile_events.size() < 2 * n) {
+            cudaEvent_t e;
+            cuda_check(cudaEventCreate(&e), "cudaEventCreate");
+            dev->profile_events.push_back(e);
+        }
     try {
-        for (size_t i = 0; i < n; i++) run_launch(*dev, launches[i], buffers, nbuf, slot_of[i] >= 0 ? &slots[slot_of[i]] : nullptr, pp);
+        for (size_t i = 0; i < n; i++) {
+            if (profiling) cuda_check(cudaEventRecord(dev->profile_events[2 * i], dev->stream), "cudaEventRecord");
+            run_launch(*dev, launches[i], buffers, nbuf, slot_of[i] >= 0 ? &slots[slot_of[i]] : nullptr, pp);
+            if (profiling) cuda_check(cudaEventRecord(dev->profile_events[2 * i + 1], dev->stream), "cudaEventRecord");
+        }
     } catch (...) {
         pend.flush(*dev);  // the launches before the rejected one still run, as they would one by one
         throw;
     }
     pend.flush(*dev);
-    if (wait) {
+    if (wait || profiling) {
         cuda_check(cudaStreamSynchronize(dev->stream), "cudaStreamSynchronize");
+        if (profiling)
+            for (size_t i = 0; i < n; i++) {
+                float ms = 0.0f;
+                if (cudaEventElapsedTime(&ms, dev->profile_events[2 * i], dev->profile_events[2 * i + 1]) != cudaSuccess) continue;
+                const lapid_b200_launch &l = launches[i];
+                const char *kind = l.kind == LAPID_B200_KERNEL_GATHER ? "gather" : l.kind == LAPID_B200_KERNEL_MATMUL_ID ? "matmul_id"
+                                   : l.batch * l.m <= dev->gemv_max_rows ? "matmul_decode" : "matmul_prefill";
+                auto &e = dev->profile_by_kind[kind];
+                e.first++;
+                e.second += ms;
+            }
         check_status_word(dev);
     }
 }
@@ -1272,6 +1304,9 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             lb::qgemv_kq_stream_set_ctas_per_sm(std::atoi(value));
         } else if (k == "gemv_stream_early_ctas") {
             lb::qgemv_kq_stream_set_early_ctas(std::atoi(value));
+        } else if (k == "profile") {
+            dev->profile = v != "0";
+            if (!dev->profile) dev->profile_by_kind.clear();
         } else if (k == "gemv_stream_spin_limit") {
             lb::qgemv_kq_stream_set_spin_limit(std::atoi(value));
         } else if (k == "gemv_stream_big_units") {
@@ -1411,6 +1446,24 @@ lapid_b200_status lapid_b200_execute_async(lapid_b200_device *dev, const lapid_b
 }
 
 uint64_t lapid_b200_take_launch_count(lapid_b200_device *dev) { return dev ? dev->launches.exchange(0) : 0; }
+
+lapid_b200_status lapid_b200_take_profile(lapid_b200_device *dev, lapid_b200_profile_entry *entries, size_t cap, size_t *n) {
+    return guard([&] {
+        need(dev);
+        if (!n || (cap && !entries)) fail("invalid_argument", "n or entries is NULL");
+        std::lock_guard<std::mutex> lock(dev->mu);
+        std::vector<std::pair<std::string, std::pair<uint64_t, double>>> v(dev->profile_by_kind.begin(), dev->profile_by_kind.end());
+        std::sort(v.begin(), v.end(), [](const auto &a, const auto &b) { return a.second.second > b.second.second; });
+        *n = v.size();
+        if (cap < v.size()) return;  // (the caller asks again with room; nothing is drained)
+        for (size_t i = 0; i < v.size(); i++) {
+            std::snprintf(entries[i].kind, sizeof(entries[i].kind), "%s", v[i].first.c_str());
+            entries[i].launches = v[i].second.first;
+            entries[i].ms = v[i].second.second;
+        }
+        dev->profile_by_kind.clear();
+    });
+}
 
 lapid_b200_status lapid_b200_decode_trace_begin(lapid_b200_device *dev, uint32_t launches) {
     return guard([&] {

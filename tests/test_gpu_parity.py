@@ -1232,3 +1232,32 @@ def test_epilogue_expression_is_validated(be, oracle):
     be.execute([l], bufs)                                    # and the device still works
     acc, _ = oracle.matmul(O.Q4_K, bufs[0].download().view(np.float32), qb, n, k, m=1)
     assert max_rel(bufs[2].download().view(np.float32), acc * bufs[3].download().view(np.float32)) <= 2e-5
+
+
+def test_take_profile(be, oracle):
+    """`Backend::take_profile` (crates/lapid-compiler/src/backend.rs:59-62): with the option on, the GPU time of every
+    launch is added to its kernel kind; the call returns (kind, launches, ms) by time and clears the totals; results are
+    those of an ordinary run."""
+    n, k = 512, 2048
+    qb = oracle.quantize(O.Q4_K, O.normal(1800, n * k, 0.05), n, k)
+    a1, a64 = O.normal(1801, k), O.normal(1802, 64 * k)
+    table = oracle.quantize(O.Q6_K, O.normal(1803, 32 * 256, 0.05), 32, 256)
+    ids = np.array([3, 31, 0], np.int32)
+    bufs = [be.upload(a1), be.upload(qb), be.alloc(n * 4), be.upload(a64), be.alloc(64 * n * 4), be.upload(table), be.upload(ids), be.alloc(3 * 256 * 4)]
+    ls = [matmul_launch(lp.DType.Q4K, 1, n, k, inputs=(0, 1), output=2), matmul_launch(lp.DType.Q4K, 1, n, k, inputs=(0, 1), output=2),
+          matmul_launch(lp.DType.Q4K, 64, n, k, inputs=(3, 1), output=4), lp.backend.gather_launch(lp.DType.Q6K, 32, 256, 3, inputs=(5, 6), output=7)]
+    assert be.take_profile() == []
+    be.execute(ls, bufs)
+    assert be.take_profile() == []              # off by default
+    be.set_option("profile", "1")
+    try:
+        be.execute(ls, bufs)
+        be.execute(ls[:1], bufs)
+        prof = be.take_profile()
+        assert sorted((kind, cnt) for kind, cnt, _ in prof) == [("gather", 1), ("matmul_decode", 3), ("matmul_prefill", 1)]
+        assert all(0.0 < ms < 50.0 for _, _, ms in prof) and [ms for _, _, ms in prof] == sorted((ms for _, _, ms in prof), reverse=True)
+        assert be.take_profile() == []          # drained
+    finally:
+        be.set_option("profile", "0")
+    want, _ = oracle.matmul(O.Q4_K, a1, qb, n, k, m=1)
+    assert max_rel(bufs[2].download().view(np.float32), want) <= 2e-5
