@@ -500,7 +500,7 @@ def gemv_kernel_name(fmt: int, m: int, n: int = 0, k: int = 0) -> str:
     if fmt == 7:
         return "qgemv_kq_stream_kernel<q5_k>" if m >= 3 else "qgemv_kq_fast_kernel<q5_k>"
     if fmt == 5:
-        return "qgemv_i4_kernel"
+        return "qgemv_i4_mma_kernel" if m >= 2 else "qgemv_i4_kernel"
     return "qgemv_i8_mma_kernel" if m >= 2 else "qgemv_i8_fast_kernel"
 
 

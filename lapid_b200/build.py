@@ -30,6 +30,7 @@ SOURCES = {
     "qgemv_i4.cu": [],
     "qgemv_mxfp4.cu": [],
     "qgemv_i8_mma.cu": [],
+    "qgemv_i4_mma.cu": [],
     "qgemm_f32.cu": [],
     "qgemm_tc.cu": [],
     "noalloc.cu": [],

@@ -451,7 +451,8 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
                 (p.stream ||
                  (l.b_dtype == LAPID_B200_DTYPE_Q4_K && p.rows >= dev.gemv_mma_rows && lb::qgemv_q4k_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
                  (l.b_dtype == LAPID_B200_DTYPE_Q6_K && p.rows > dev.gemv_mma_rows && lb::qgemv_q6k_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
-                 (l.b_dtype == LAPID_B200_DTYPE_INT8 && p.rows >= dev.gemv_mma_rows && lb::qgemv_i8_mma_shape_ok(p.rows, (uint32_t)l.k)));
+                 (l.b_dtype == LAPID_B200_DTYPE_INT8 && p.rows >= dev.gemv_mma_rows && lb::qgemv_i8_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
+                 (l.b_dtype == LAPID_B200_DTYPE_INT4 && p.rows >= dev.gemv_mma_rows && lb::qgemv_i4_mma_shape_ok(p.rows, (uint32_t)l.k)));
         if (p.mma) {
             size_t tiles = align_up(lb::qgemv_q4k_mma_act_bytes(p.rows, (uint32_t)l.k), 256);
             if (tiles > p.scratch) p.scratch = tiles;
@@ -848,7 +849,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         g.a_bs = q.a_bs;
         g.a_rs = q.a_rs;
         g.status = dev.status_dev;
-        if (pend && slot->records && l.b_dtype != LAPID_B200_DTYPE_INT8) {  // (the Int8 kernels take one launch at a time)
+        if (pend && slot->records && l.b_dtype != LAPID_B200_DTYPE_INT8 && l.b_dtype != LAPID_B200_DTYPE_INT4) {  // (the Int8 / Int4 kernels take one launch at a time)
             using Range = PendingGroup::Range;
             const char *ob = (const char *)out->ptr;
             Range wr{ob + 4 * l.out.offset, ob + 4 * last};
@@ -879,7 +880,9 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         g.early = dev.early_ok(slot->hoisted) ? 1 : 0;
         const bool pdl = dev.pdl_launch();
         const uint64_t ws_before = dev.stream_ws.kernels;
-        if (slot->records == 2 && l.b_dtype == LAPID_B200_DTYPE_INT8) {
+        if (slot->records == 2 && l.b_dtype == LAPID_B200_DTYPE_INT4) {
+            cuda_check(lb::launch_qgemv_i4_mma(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        } else if (slot->records == 2 && l.b_dtype == LAPID_B200_DTYPE_INT8) {
             cuda_check(lb::launch_qgemv_i8_mma(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         } else if (slot->records == 2) {
             lb::GemvGroup one{};

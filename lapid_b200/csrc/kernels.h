@@ -236,6 +236,9 @@ void qgemv_kq_stream_set_final_tiles(int v);    // tuning: row tiles per finalis
 void qgemv_kq_stream_set_spin_limit(int v);     // polls before the claim of a staging region gives up (0 = default)
 void qgemv_kq_stream_set_big_units(int v);      // tuning: 128-row units per SM from which the 32-row warps are used
 void qgemv_kq_stream_set_early_ctas(int v);     // tuning: CTAs per SM of a launch that runs ahead of its predecessor (0 = as any launch)
+// Int4 nibble planes on the same instruction (qgemv_i4_mma.cu; K a multiple of 512); same activation tiles.
+bool qgemv_i4_mma_shape_ok(uint32_t rows, uint32_t k);
+cudaError_t launch_qgemv_i4_mma(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // Int8 planes on the same instruction (K a multiple of 512); same activation tiles.
 bool qgemv_i8_mma_shape_ok(uint32_t rows, uint32_t k);
 cudaError_t launch_qgemv_i8_mma(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);

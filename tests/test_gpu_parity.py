@@ -391,6 +391,36 @@ def test_gemv_int8_tensor_core_decode_kernel(be, oracle):
         be.set_option("gemv_mma_rows", "2")
 
 
+def test_gemv_int4_tensor_core_decode_kernel(be, oracle):
+    """The Int4 tensor-core decode kernel (2..8 rows, K a multiple of 512) against the oracle and against the plain
+    streaming kernel: ragged n, every row count, bias, K with several chunks per warp, weights at both ends of the
+    4-bit range (a row of all 0 and all 15 codes)."""
+    try:
+        seed = 1050
+        for (m, n, k, bias) in [(3, 77, 512, True), (4, 513, 4096, False), (5, 100, 1536, False), (6, 1, 1024, False),
+                                (7, 33, 14336, True), (8, 300, 4096, False), (8, 17, 14336, False), (2, 130, 2048, False)]:
+            seed += 1
+            w = O.normal(seed, n * k, 0.05).reshape(n, k).copy()
+            w[0, :] = -1.0          # every group of the row: codes 0 (and one 8) ...
+            w[0, ::32] = 0.0
+            if n > 1:
+                w[n - 1, :] = 0.875 * np.abs(w[n - 1, :]).max()   # ... and codes 15
+                w[n - 1, ::32] = -np.abs(w[n - 1, :]).max()
+            qb = oracle.quantize(O.INT4, w.reshape(-1), n, k)
+            a = O.normal(seed + 50, m * k)
+            bv = O.normal(seed + 70, n) if bias else None
+            want, _ = oracle.matmul(O.INT4, a, qb, n, k, m=m, bias=bv)
+            be.set_option("gemv_mma_rows", "2")
+            be.take_launch_count()
+            got = run_matmul(be, lp.DType.Int4, a, qb, m, n, k, bias=bv)
+            be.set_option("gemv_mma_rows", "0")
+            ref = run_matmul(be, lp.DType.Int4, a, qb, m, n, k, bias=bv)
+            assert max_rel(got, want) <= 2e-5, (m, n, k, max_rel(got, want))
+            assert max_rel(got, ref) <= 2e-5, (m, n, k)
+    finally:
+        be.set_option("gemv_mma_rows", "2")
+
+
 def test_gemv_q6k_any_block_count(be, oracle):
     """Q6_K rows whose byte length is not a multiple of 16 (K not a multiple of 2048: every stage of
     the bulk-copy ring then starts at a different offset from a 16-byte boundary)."""
