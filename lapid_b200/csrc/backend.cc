@@ -1322,6 +1322,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             dev->two_row_dp4a = v != "0";
         } else if (k == "gemv_mma_config") {
             lb::qgemv_q4k_mma_set_config(std::atoi(value));
+        } else if (k == "gemv_q6k_mma_config") {
+            lb::qgemv_q6k_mma_set_config(std::atoi(value));
         } else if (k == "gemv_ctas_per_sm") {
             lb::qgemv_q4k_fast_set_cta_cap(std::atoi(value));
         } else if (k == "gemm_wide") {

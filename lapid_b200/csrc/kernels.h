@@ -209,6 +209,7 @@ bool qgemv_q4k_mma_group_fits(GemvGroup &group);
 struct StreamWs;
 cudaError_t launch_qgemv_q4k_mma(GemvGroup &group, int sm_count, bool pdl, cudaStream_t stream, StreamWs *ws = nullptr);
 void qgemv_q4k_mma_set_config(int index);  // -1 = pick by shared-memory fit
+void qgemv_q6k_mma_set_config(int index);  // tuning: layout of the Q6_K tensor-core decode kernel, -1 = choose
 // ---- qgemv_kq_stream.cu: Q4_K / Q5_K decode on the same instruction as one stream of equal work shares
 // (2..8 rows; any K that is a multiple of 256; same activation tiles). One workspace per device serves every launch
 // of its stream (all zero between launches): `pairs` ({f32 value, u32 flag}) through which the spans of a dependent

@@ -303,10 +303,29 @@ static void plan_acts(GemvGroup &g) {
     }
 }
 
+static int g_force_config = -1;  // tuning: -1 = choose
+static double g_balance_margin = 1.08;
+
 static int pick_config(size_t act_bytes) {
+    if (g_force_config >= 0 && fixed_smem(CONFIGS[g_force_config]) + act_bytes <= 227 * 1024 - 256) return g_force_config;
     for (int i = 0; i < (int)(sizeof(CONFIGS) / sizeof(CONFIGS[0])); i++)
         if (fixed_smem(CONFIGS[i]) + act_bytes <= 227 * 1024 - 256) return i;
     return -1;
+}
+
+// The launch's layout: the first that fits, unless the next one shares the row tiles among the CTAs more evenly by a
+// margin that outweighs what its 16-row warps lose (they load every activation fragment once per 16 instead of once
+// per 32 rows): 14336 rows are 448 tiles of 32 = rounds of 4 and 3 over 148 CTAs, but 896 of 16 = rounds of 7 and 6.
+static int pick_config_for(const GemvGroup &g, int sm_count) {
+    const int first = pick_config(g.act_bytes);
+    if (first != 0 || g_force_config >= 0 || fixed_smem(CONFIGS[1]) + g.act_bytes > 227 * 1024 - 256) return first;
+    auto eff = [&](int tiles) {
+        uint64_t tasks = 0;
+        for (int i = 0; i < g.count; i++) tasks += (g.item[i].n + 16 * tiles - 1) / (16 * tiles);
+        const uint64_t grid = tasks < (uint64_t)sm_count ? tasks : (uint64_t)sm_count;
+        return (double)tasks / ((double)grid * ((tasks + grid - 1) / grid));
+    };
+    return eff(1) > g_balance_margin * eff(2) ? 1 : 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -404,6 +423,8 @@ static cudaError_t launch_cfg(GemvGroup &g, int sm_count, bool pdl, cudaStream_t
 
 }  // namespace m6
 
+void qgemv_q6k_mma_set_config(int index) { m6::g_force_config = index < 0 || index > 2 ? -1 : index; }
+
 // K a multiple of 2048: a row of the packed matrix must be a multiple of 16 bytes for the tensor map.
 bool qgemv_q6k_mma_shape_ok(uint32_t rows, uint32_t k) {
     if (rows < 1 || rows > 8 || k % QK != 0 || k < QK || (k / QK) % 8 != 0 || !m6::encode_fn()) return false;
@@ -418,7 +439,7 @@ bool qgemv_q6k_mma_group_fits(GemvGroup &g) {
 cudaError_t launch_qgemv_q6k_mma(GemvGroup &g, int sm_count, bool pdl, cudaStream_t stream) {
     if (g.count < 1 || g.count > GEMV_GROUP_MAX) return cudaErrorInvalidValue;
     m6::plan_acts(g);
-    switch (m6::pick_config(g.act_bytes)) {
+    switch (m6::pick_config_for(g, sm_count)) {
         case 0: return m6::launch_cfg<8, 2>(g, sm_count, pdl, stream);
         case 1: return m6::launch_cfg<8, 1>(g, sm_count, pdl, stream);
         case 2: return m6::launch_cfg<4, 1>(g, sm_count, pdl, stream);
