@@ -65,6 +65,13 @@ typedef int32_t lapid_b200_status;
 #define LAPID_B200_DTYPE_Q5_K 7
 #define LAPID_B200_DTYPE_Q6_K 8
 #define LAPID_B200_DTYPE_MXFP4 9 /* ggml block_mxfp4: 32 elements in 17 bytes (crates/lapid-quant/src/mxfp4.rs) */
+/* ggml's grid-based i-quants, 256-element super-blocks stored as in GGUF (crates/lapid-c/src/lib.rs:53-60;
+ * crates/lapid-quant/src/iq2.rs, iq3.rs): dequantize, from_ggml_blocks (blocks kept), Gather, MatMul and MatMulId.
+ * lapid_b200_quantize answers `unsupported` for them. */
+#define LAPID_B200_DTYPE_IQ2_XXS 10 /* 66-byte blocks, 2.0625 bits per weight */
+#define LAPID_B200_DTYPE_IQ2_S 11   /* 82-byte blocks, 2.5625 */
+#define LAPID_B200_DTYPE_IQ3_XXS 12 /* 98-byte blocks, 3.0625 */
+#define LAPID_B200_DTYPE_IQ2_XS 13  /* 74-byte blocks, 2.3125 */
 /* Not a lapid dtype: as a launch's a_dtype it says that input 0 is an activation operand already
  * quantized for this launch by lapid_b200_rms_norm_act / lapid_b200_silu_mul_act (see there). */
 #define LAPID_B200_DTYPE_ACT_Q8 100
@@ -204,7 +211,7 @@ typedef struct lapid_b200_launch {
     int32_t kind;         /* LAPID_B200_KERNEL_MATMUL (the fields below describe it), LAPID_B200_KERNEL_GATHER or LAPID_B200_KERNEL_MATMUL_ID (see above) */
     int32_t a_dtype;      /* MatMulSpec.a_dtype: F32, F16 or BF16 -- half types are widened exactly to f32 as they are read, as
                              lapid-cpu's load_contig does (crates/lapid-cpu/src/matmul/mod.rs:165-286) -- or LAPID_B200_DTYPE_ACT_Q8 (above) */
-    int32_t b_dtype;      /* MatMulSpec.b_dtype: INT8 | INT4 | Q4_K | Q5_K | Q6_K | MXFP4 */
+    int32_t b_dtype;      /* MatMulSpec.b_dtype: INT8 | INT4 | Q4_K | Q5_K | Q6_K | MXFP4 | IQ2_XXS | IQ2_XS | IQ2_S | IQ3_XXS */
     int32_t out_dtype;    /* MatMulSpec.out_dtype: F32 */
     int32_t b_transposed; /* must be 1 for a quantized B */
     int32_t epilogue;     /* LAPID_B200_EPILOGUE_* */

@@ -30,6 +30,10 @@ class DType(enum.IntEnum):
     Q5K = 7
     Q6K = 8
     MXFP4 = 9
+    Iq2Xxs = 10
+    Iq2S = 11
+    Iq3Xxs = 12
+    Iq2Xs = 13
     ACT_Q8 = 100  # not a lapid dtype: an activation operand quantized by its producer (LAPID_B200_DTYPE_ACT_Q8)
 
 

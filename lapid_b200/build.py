@@ -29,6 +29,8 @@ SOURCES = {
     "qgemv_i8.cu": [],
     "qgemv_i4.cu": [],
     "qgemv_mxfp4.cu": [],
+    "qgemv_iq.cu": [],
+    "iquant.cu": ["-DLAPID_B200_IQ_GRIDS_FILE=" + os.path.join(CSRC, "iq_grids.bin")],
     "qgemv_i8_mma.cu": [],
     "qgemv_i4_mma.cu": [],
     "qgemm_f32.cu": [],
@@ -61,6 +63,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "lapid_b200.h"))
     headers.append(os.path.abspath(__file__))
+    headers.append(os.path.join(CSRC, "iq_grids.bin"))  # embedded by iquant.cu
     jobs = []
     objs = []
     for src, extra in SOURCES.items():

@@ -101,9 +101,13 @@ void cuda_check(cudaError_t e, const char *what) {
 }
 
 // ------------------------------------------------------------------ layout (lapid-quant lib.rs:84-125)
+// the grid-based i-quants (crates/lapid-quant/src/lib.rs:79-82)
+bool is_iquant(int32_t dt) {
+    return dt == LAPID_B200_DTYPE_IQ2_XXS || dt == LAPID_B200_DTYPE_IQ2_XS || dt == LAPID_B200_DTYPE_IQ2_S || dt == LAPID_B200_DTYPE_IQ3_XXS;
+}
 bool is_quant(int32_t dt) {
     return dt == LAPID_B200_DTYPE_INT8 || dt == LAPID_B200_DTYPE_INT4 || dt == LAPID_B200_DTYPE_Q4_K || dt == LAPID_B200_DTYPE_Q5_K ||
-           dt == LAPID_B200_DTYPE_Q6_K || dt == LAPID_B200_DTYPE_MXFP4;
+           dt == LAPID_B200_DTYPE_Q6_K || dt == LAPID_B200_DTYPE_MXFP4 || is_iquant(dt);
 }
 bool is_act_float(int32_t dt) { return dt == LAPID_B200_DTYPE_F32 || dt == LAPID_B200_DTYPE_F16 || dt == LAPID_B200_DTYPE_BF16; }
 // ACT_F32 / ACT_F16 / ACT_BF16 of the kernels, and the element size, for a launch's a_dtype
@@ -112,7 +116,17 @@ uint64_t act_elem_size(int32_t dt) { return dt == LAPID_B200_DTYPE_F32 ? 4 : 2; 
 bool has_min_term(int32_t dt) { return dt == LAPID_B200_DTYPE_Q4_K || dt == LAPID_B200_DTYPE_Q5_K; }  // the decode tiles need d * sum(q) per activation group
 uint64_t block_elems(int32_t dt) { return (dt == LAPID_B200_DTYPE_INT8 || dt == LAPID_B200_DTYPE_INT4 || dt == LAPID_B200_DTYPE_MXFP4) ? 32 : 256; }
 uint64_t block_bytes(int32_t dt) {  // array-of-structs formats (lib.rs:62-75); 0 for the plane formats
-    return dt == LAPID_B200_DTYPE_Q4_K ? 144 : dt == LAPID_B200_DTYPE_Q5_K ? 176 : dt == LAPID_B200_DTYPE_Q6_K ? 210 : dt == LAPID_B200_DTYPE_MXFP4 ? 17 : 0;
+    switch (dt) {
+        case LAPID_B200_DTYPE_Q4_K: return 144;
+        case LAPID_B200_DTYPE_Q5_K: return 176;
+        case LAPID_B200_DTYPE_Q6_K: return 210;
+        case LAPID_B200_DTYPE_MXFP4: return 17;
+        case LAPID_B200_DTYPE_IQ2_XXS: return 66;
+        case LAPID_B200_DTYPE_IQ2_XS: return 74;
+        case LAPID_B200_DTYPE_IQ2_S: return 82;
+        case LAPID_B200_DTYPE_IQ3_XXS: return 98;
+        default: return 0;
+    }
 }
 uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
@@ -403,7 +417,7 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
     Plan p;
     if (l.kind != LAPID_B200_KERNEL_MATMUL) fail("unsupported", "kernel kind " + std::to_string(l.kind) + " is not MatMul");
     if (!is_quant(l.b_dtype))
-        fail("unsupported_dtype", "b200 matmul: b dtype " + std::to_string(l.b_dtype) + " (want int8, int4, q4_k, q5_k, q6_k or mxfp4)");
+        fail("unsupported_dtype", "b200 matmul: b dtype " + std::to_string(l.b_dtype) + " (want int8, int4, q4_k, q5_k, q6_k, mxfp4 or an i-quant)");
     if ((!is_act_float(l.a_dtype) && l.a_dtype != LAPID_B200_DTYPE_ACT_Q8) || l.out_dtype != LAPID_B200_DTYPE_F32)
         fail("unsupported_dtype", "b200 matmul: a must be f32, f16 or bf16 and out f32");
     if (l.epilogue != LAPID_B200_EPILOGUE_NONE && l.epilogue != LAPID_B200_EPILOGUE_ADD && l.epilogue != LAPID_B200_EPILOGUE_EXPR)
@@ -498,7 +512,7 @@ lb::ActOut act_out_checked(lapid_b200_device *dev, lapid_b200_buffer *qact, int3
 void check_gather(const lapid_b200_launch &l) {
     const bool quant = is_quant(l.b_dtype);
     if (!quant && l.b_dtype != LAPID_B200_DTYPE_F32)
-        fail("unsupported_dtype", "b200 gather: table dtype " + std::to_string(l.b_dtype) + " (want f32, int8, int4, q4_k, q5_k, q6_k or mxfp4)");
+        fail("unsupported_dtype", "b200 gather: table dtype " + std::to_string(l.b_dtype) + " (want f32, int8, int4, q4_k, q5_k, q6_k, mxfp4 or an i-quant)");
     if (l.out_dtype != LAPID_B200_DTYPE_F32) fail("unsupported_dtype", "b200 gather: out must be f32");
     if (l.n_inputs != 2) fail("invalid_launch", "expected 2 inputs, got " + std::to_string(l.n_inputs));
     if (l.batch != 1) fail("invalid_launch", "b200 gather: batch must be 1");
@@ -554,7 +568,7 @@ struct MoePlan {
 MoePlan plan_matmul_id(const lapid_b200_device &dev, const lapid_b200_launch &l) {
     MoePlan p;
     if (!is_quant(l.b_dtype))
-        fail("unsupported_dtype", "b200 matmul_id: w dtype " + std::to_string(l.b_dtype) + " (want int8, int4, q4_k, q5_k, q6_k or mxfp4)");
+        fail("unsupported_dtype", "b200 matmul_id: w dtype " + std::to_string(l.b_dtype) + " (want int8, int4, q4_k, q5_k, q6_k, mxfp4 or an i-quant)");
     if (l.a_dtype != LAPID_B200_DTYPE_F32 || l.out_dtype != LAPID_B200_DTYPE_F32)
         fail("unsupported_dtype", "b200 matmul_id: x and out must be f32");
     if (l.epilogue != LAPID_B200_EPILOGUE_NONE) fail("unsupported", "b200 matmul_id: no epilogue");
@@ -660,6 +674,7 @@ void run_matmul_id(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b20
         const bool pdl = dev.pdl_launch();
         if (l.b_dtype == LAPID_B200_DTYPE_INT4) cuda_check(lb::launch_qgemv_i4(g, dev.sm_count, pdl, dev.stream), "matmul_id launch");
         else if (l.b_dtype == LAPID_B200_DTYPE_MXFP4) cuda_check(lb::launch_qgemv_mxfp4(g, dev.sm_count, pdl, dev.stream), "matmul_id launch");
+        else if (is_iquant(l.b_dtype)) cuda_check(lb::launch_qgemv_iq(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "matmul_id launch");
         else if (p.fast) cuda_check(lb::launch_qgemv_kq_moe(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "matmul_id launch");
         else cuda_check(lb::launch_qgemv_moe(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "matmul_id launch");
         dev.launches += 2;
@@ -895,6 +910,7 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         } else if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (l.b_dtype == LAPID_B200_DTYPE_INT4) cuda_check(lb::launch_qgemv_i4(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (l.b_dtype == LAPID_B200_DTYPE_MXFP4) cuda_check(lb::launch_qgemv_mxfp4(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        else if (is_iquant(l.b_dtype)) cuda_check(lb::launch_qgemv_iq(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (p.fast_i8 && ((uintptr_t)g.w & 15) == 0) cuda_check(lb::launch_qgemv_i8_fast(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else cuda_check(lb::launch_qgemv(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         dev.launches += dev.stream_ws.kernels > ws_before ? dev.stream_ws.kernels - ws_before : 1;  // (the stream kernel may take two)
@@ -1226,6 +1242,7 @@ lapid_b200_status lapid_b200_device_open(int32_t ordinal, lapid_b200_device **ou
             d->stream_ws.pairs = (uint2 *)ws;
             d->stream_ws.stage = (uint8_t *)ws + d->stream_ws.n_pairs * 8;
             cuda_check(cudaMemset(ws, 0, ws_bytes), "cudaMemset(decode workspace)");
+            cuda_check(lb::iq_grids_upload(), "i-quant codebook upload");
         } catch (...) {
             delete d;
             throw;
@@ -1524,6 +1541,8 @@ lapid_b200_status lapid_b200_quantize(lapid_b200_device *dev, int32_t format, co
         need(dev);
         if (!src || !dst) fail("invalid_argument", "src or dst is NULL");
         if (cols == 0) fail("invalid_launch", "quantized cols must be positive");
+        if (is_iquant(format))
+            fail("unsupported", "quantize: the i-quant quantizers (lattice searches) are not built; import blocks with from_ggml_blocks");
         lapid_b200_layout l = layout_of(format, rows, cols);
         if (src->bytes / 4 < rows * cols)
             fail("shape_mismatch", "quantize: data has " + std::to_string(src->bytes / 4) + " elements, expected " +

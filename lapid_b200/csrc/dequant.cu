@@ -11,6 +11,7 @@
 // owns element t, so stores are fully coalesced and the block's bytes are read through L1.
 // The kernels are bound by the 4 bytes written per element (HBM store bandwidth).
 #include "common.cuh"
+#include "iquant.cuh"
 #include "kernels.h"
 
 namespace lb {
@@ -75,7 +76,7 @@ __global__ void __launch_bounds__(256) dequant_q6k_kernel(const uint8_t *__restr
 template <int FMT>
 __global__ void __launch_bounds__(256) gather_kernel(const uint8_t *__restrict__ table, uint64_t scales_offset,
                                                      const int32_t *__restrict__ ids, uint64_t rows, uint64_t cols, uint64_t count,
-                                                     float *__restrict__ out, int *status) {
+                                                     float *__restrict__ out, int *status, const uint8_t *__restrict__ iq_grid = nullptr) {
     const uint64_t per_row = (cols + 255) / 256;
     for (uint64_t u = blockIdx.x; u < count * per_row; u += gridDim.x) {
         const uint64_t i = u / per_row, c = (u % per_row) * 256 + threadIdx.x;
@@ -90,6 +91,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t *__restrict__
         else if (FMT == FMT_Q5K) v = q5k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q5K_BYTES, (int)(c % QK));
         else if (FMT == FMT_Q6K) v = q6k_element(table + ((uint64_t)r * (cols / QK) + c / QK) * Q6K_BYTES, (int)(c % QK));
         else if (FMT == FMT_MXFP4) v = mxfp4_element(table + (((uint64_t)r * cols + c) >> 5) * MXFP4_BYTES, (uint32_t)(c & 31));
+        else if (is_iq(FMT)) v = iq_element<FMT>(table + ((uint64_t)r * (cols / QK) + c / QK) * iq_block_bytes(FMT), (int)(c % QK), iq_grid);
         else if (FMT == FMT_INT4) {
             const uint64_t pos = (uint64_t)r * cols + c, g = pos >> 5;
             const uint32_t e = (uint32_t)(pos & 31);
@@ -116,6 +118,14 @@ __global__ void __launch_bounds__(256) dequant_int4_kernel(const uint8_t *__rest
                                                            float *__restrict__ dst, uint64_t n_elems) {
     uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_elems; i += stride) dst[i] = int4_element(qs, scales, i);
+}
+
+// one CTA per i-quant block, one thread per element (crates/lapid-quant/src/iq2.rs:38-90, iq3.rs:18-39)
+template <int FMT>
+__global__ void __launch_bounds__(256) dequant_iq_kernel(const uint8_t *__restrict__ src, float *__restrict__ dst, uint64_t n_blocks,
+                                                         const uint8_t *__restrict__ grid) {
+    for (uint64_t blk = blockIdx.x; blk < n_blocks; blk += gridDim.x)
+        dst[blk * QK + threadIdx.x] = iq_element<FMT>(src + blk * iq_block_bytes(FMT), threadIdx.x, grid);
 }
 
 __global__ void __launch_bounds__(256) dequant_mxfp4_kernel(const uint8_t *__restrict__ src, float *__restrict__ dst, uint64_t n_elems) {
@@ -180,6 +190,15 @@ cudaError_t launch_dequantize(int fmt, const void *src, uint64_t rows, uint64_t 
         dequant_q6k_kernel<<<grid_for(n / QK, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n / QK);
     } else if (fmt == FMT_MXFP4) {
         dequant_mxfp4_kernel<<<grid_for((n + 255) / 256, sm_count), 256, 0, stream>>>((const uint8_t *)src, dst, n);
+    } else if (is_iq(fmt)) {
+        const uint8_t *grids = iq_grids();
+        if (!grids) return cudaErrorNotReady;
+        const uint8_t *g = grids + iq_grid_offset(fmt), *b = (const uint8_t *)src;
+        const int ctas = grid_for(n / QK, sm_count);
+        if (fmt == FMT_IQ2XXS) dequant_iq_kernel<FMT_IQ2XXS><<<ctas, 256, 0, stream>>>(b, dst, n / QK, g);
+        else if (fmt == FMT_IQ2XS) dequant_iq_kernel<FMT_IQ2XS><<<ctas, 256, 0, stream>>>(b, dst, n / QK, g);
+        else if (fmt == FMT_IQ2S) dequant_iq_kernel<FMT_IQ2S><<<ctas, 256, 0, stream>>>(b, dst, n / QK, g);
+        else dequant_iq_kernel<FMT_IQ3XXS><<<ctas, 256, 0, stream>>>(b, dst, n / QK, g);
     } else if (fmt == FMT_INT4) {
         const uint8_t *p = (const uint8_t *)src;
         dequant_int4_kernel<<<grid_for((n + 255) / 256, sm_count), 256, 0, stream>>>(p, (const uint16_t *)(p + scales_offset), dst, n);
@@ -203,6 +222,15 @@ cudaError_t launch_gather(int fmt, const void *table, uint64_t scales_offset, co
     else if (fmt == FMT_INT8) gather_kernel<FMT_INT8><<<grid, 256, 0, stream>>>(t, scales_offset, ids, rows, cols, count, out, status);
     else if (fmt == FMT_INT4) gather_kernel<FMT_INT4><<<grid, 256, 0, stream>>>(t, scales_offset, ids, rows, cols, count, out, status);
     else if (fmt == FMT_MXFP4) gather_kernel<FMT_MXFP4><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
+    else if (is_iq(fmt)) {
+        const uint8_t *grids = iq_grids();
+        if (!grids) return cudaErrorNotReady;
+        const uint8_t *g = grids + iq_grid_offset(fmt);
+        if (fmt == FMT_IQ2XXS) gather_kernel<FMT_IQ2XXS><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status, g);
+        else if (fmt == FMT_IQ2XS) gather_kernel<FMT_IQ2XS><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status, g);
+        else if (fmt == FMT_IQ2S) gather_kernel<FMT_IQ2S><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status, g);
+        else gather_kernel<FMT_IQ3XXS><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status, g);
+    }
     else gather_kernel<-1><<<grid, 256, 0, stream>>>(t, 0, ids, rows, cols, count, out, status);
     return cudaGetLastError();
 }

@@ -132,6 +132,12 @@ cudaError_t launch_qgemv_moe(int fmt, const GemvArgs &args, int sm_count, bool p
 cudaError_t launch_qgemv_i4(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // ---- qgemv_mxfp4.cu: MXFP4 blocks, 1..8 rows (and the expert-indexed form: args.ids set, rows = tokens); reads the planes
 cudaError_t launch_qgemv_mxfp4(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+
+// ---- qgemv_iq.cu: the grid-based i-quants (IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS), 1..8 rows (and the expert-indexed form);
+// reads the activation planes, the codebooks from the per-device table of iquant.cu
+cudaError_t launch_qgemv_iq(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+// iquant.cu: uploads the codebooks to the current device (once; outside stream captures)
+cudaError_t iq_grids_upload();
 // Opt in to the dynamic shared memory the GEMV variants need; once per device.
 cudaError_t qgemv_init();
 
@@ -281,6 +287,7 @@ struct GemmF32Args {
     const int32_t *row_pair;
     uint64_t id_stride;          // bytes between the experts' matrices
     uint32_t id_r;               // slots per token: pair p reads activation row p / id_r, writes output row p
+    const uint8_t *iq_grid;      // i-quants: the format's codebook on this device (set by the launcher)
 };
 cudaError_t launch_qgemm_f32(int fmt, const GemmF32Args &args, cudaStream_t stream);
 

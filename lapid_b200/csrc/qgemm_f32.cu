@@ -15,6 +15,7 @@
 // 32-element group; the W tile is expanded into shared memory once per step (so each weight is
 // dequantized once per 64 activation rows) and A is staged beside it.
 #include "common.cuh"
+#include "iquant.cuh"
 #include "kernels.h"
 
 namespace lb {
@@ -64,6 +65,17 @@ __device__ __forceinline__ void dequant8(const GemmF32Args &p, uint32_t row, uin
         const uint32_t e = k0 % GROUP;  // 0, 8, 16 or 24
 #pragma unroll
         for (int i = 0; i < 8; i++) y[i] = mxfp4_element(b, e + i);
+    } else if constexpr (is_iq(FMT)) {  // one 8-group: y = db * grid byte * sign (crates/lapid-quant/src/iq2.rs:38-90, iq3.rs:18-39)
+        const uint8_t *b = p.w + ((uint64_t)row * (p.k / QK) + k0 / QK) * iq_block_bytes(FMT);
+        const uint32_t e = k0 % QK;
+        uint32_t lo, hi, signs;
+        iq_group8<FMT>(b, (int)(e >> 3), p.iq_grid, lo, hi, signs);
+        const float db = iq_half_scale<FMT>(b, (int)(e >> 4));
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float v = xmul(db, (float)(((i < 4 ? lo : hi) >> (8 * (i & 3))) & 255u));
+            y[i] = (signs >> i) & 1u ? -v : v;
+        }
     } else if constexpr (FMT == FMT_INT4) {
         const uint64_t g = ((uint64_t)row * p.k + k0) / GROUP;
         const uint32_t e = k0 % GROUP;  // 0, 8, 16 or 24: elements 16.. are the high nibbles of the same bytes
@@ -173,6 +185,20 @@ cudaError_t launch_qgemm_f32(int fmt, const GemmF32Args &a, cudaStream_t stream)
         case FMT_INT8: qgemm_f32_kernel<FMT_INT8><<<grid, 256, 0, stream>>>(a); break;
         case FMT_INT4: qgemm_f32_kernel<FMT_INT4><<<grid, 256, 0, stream>>>(a); break;
         case FMT_MXFP4: qgemm_f32_kernel<FMT_MXFP4><<<grid, 256, 0, stream>>>(a); break;
+        case FMT_IQ2XXS:
+        case FMT_IQ2XS:
+        case FMT_IQ2S:
+        case FMT_IQ3XXS: {
+            const uint8_t *grids = iq_grids();
+            if (!grids) return cudaErrorNotReady;
+            GemmF32Args b = a;
+            b.iq_grid = grids + iq_grid_offset(fmt);
+            if (fmt == FMT_IQ2XXS) qgemm_f32_kernel<FMT_IQ2XXS><<<grid, 256, 0, stream>>>(b);
+            else if (fmt == FMT_IQ2XS) qgemm_f32_kernel<FMT_IQ2XS><<<grid, 256, 0, stream>>>(b);
+            else if (fmt == FMT_IQ2S) qgemm_f32_kernel<FMT_IQ2S><<<grid, 256, 0, stream>>>(b);
+            else qgemm_f32_kernel<FMT_IQ3XXS><<<grid, 256, 0, stream>>>(b);
+            break;
+        }
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

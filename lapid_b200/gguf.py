@@ -2,7 +2,7 @@
 
 The counterpart, for this path only, of the reference's GGUF reader and its "keep the blocks" import
 (crates/lapid-convert/src/gguf.rs:1-12 container layout, :177-215 `write_ggml_tensor`): K-quant blocks
-(Q4_K, Q5_K, Q6_K) and MXFP4 blocks are kept byte for byte, Q8_0 and Q4_0 blocks are repacked losslessly into lapid's
+(Q4_K, Q5_K, Q6_K), MXFP4 blocks and the i-quants (IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS) are kept byte for byte, Q8_0 and Q4_0 blocks are repacked losslessly into lapid's
 Int8 / Int4 planes (`lapid_quant::from_ggml_blocks`, crates/lapid-quant/src/imp.rs:171-200, here
 `lapid_b200_from_ggml_blocks` on the device), F32 / F16 tensors are handed over as they are. Nothing is
 dequantized and nothing is re-quantized.
@@ -44,6 +44,7 @@ GGML_TYPES: Dict[int, Tuple[str, int, int]] = {
 }
 # ggml type -> the lapid dtype this backend keeps it in (crates/lapid-convert/src/ggml.rs `lapid_format`)
 LAPID_DTYPE = {"Q8_0": DType.Int8, "Q4_0": DType.Int4, "Q4_K": DType.Q4K, "Q5_K": DType.Q5K, "Q6_K": DType.Q6K, "MXFP4": DType.MXFP4,
+               "IQ2_XXS": DType.Iq2Xxs, "IQ2_XS": DType.Iq2Xs, "IQ2_S": DType.Iq2S, "IQ3_XXS": DType.Iq3Xxs,
                "F32": DType.F32, "F16": DType.F16, "BF16": DType.BF16}
 
 

@@ -25,12 +25,21 @@ class Format(enum.IntEnum):
     Q5K = 7
     Q6K = 8
     MXFP4 = 9  # ggml block_mxfp4: 32 elements in 17 bytes
+    # ggml's grid-based i-quants, blocks kept as in GGUF (crates/lapid-quant/src/lib.rs:43-51); no quantizer here
+    Iq2Xxs = 10
+    Iq2S = 11
+    Iq3Xxs = 12
+    Iq2Xs = 13
 
     def block_elems(self) -> int:
         return 32 if self in (Format.Int8, Format.Int4, Format.MXFP4) else 256
 
     def block_bytes(self) -> int:
-        return {Format.Int8: 0, Format.Int4: 0, Format.Q4K: 144, Format.Q5K: 176, Format.Q6K: 210, Format.MXFP4: 17}[self]
+        return {Format.Int8: 0, Format.Int4: 0, Format.Q4K: 144, Format.Q5K: 176, Format.Q6K: 210, Format.MXFP4: 17,
+                Format.Iq2Xxs: 66, Format.Iq2Xs: 74, Format.Iq2S: 82, Format.Iq3Xxs: 98}[self]
+
+    def is_iquant(self) -> bool:
+        return self in (Format.Iq2Xxs, Format.Iq2Xs, Format.Iq2S, Format.Iq3Xxs)
 
     def is_aos(self) -> bool:
         return self.block_bytes() != 0

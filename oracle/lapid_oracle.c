@@ -14,6 +14,7 @@
  *   ... and dequantizers ........ crates/lapid-quant/src/kquant.rs:337-396
  *   Int8 (GGUF Q8_0 as planes) .. crates/lapid-quant/src/imp.rs:24-40, :73-116, :143-200
  *   Int4 (nibble planes) ........ crates/lapid-quant/src/imp.rs:47-71, :148-156; crates/lapid-cpu/src/qmat.rs:97-112
+ *   i-quants (dequantizers, decode tile) crates/lapid-quant/src/iq2.rs:38-90, iq3.rs:18-39; crates/lapid-cpu/src/iquant.rs:40-128
  *   f32 -> f16 .................. `half` 2.7.1 f16::from_f32 (Cargo.lock:1188), IEEE round to
  *                                 nearest even; not vendored in the reference tree, so restated
  *                                 from the IEEE definition and pinned by the 0x3008 known answer
@@ -31,7 +32,9 @@
  * dequantization is pinned bit-for-bit against an independent third-party dequantizer (the
  * `gguf` Python package) in the tests; K-format *quantizer bytes* are pinned only by the
  * reference's property tests (round-trip error bounds, constants, zeros) because the reference
- * checks in no golden bytes for them: quantizer byte parity is "parity unpinned".
+ * checks in no golden bytes for them: quantizer byte parity is "parity unpinned". The i-quant
+ * dequantizers are pinned bit for bit by the golden bytes the reference itself holds
+ * (crates/lapid-quant/tests/fixtures/iquant/) and by the `gguf` package's dequantizers.
  */
 #include <math.h>
 #include <stdint.h>
@@ -48,6 +51,15 @@
 #define LO_FMT_Q6K 8
 #define LO_FMT_MXFP4 9
 #define MXFP4_BYTES 17
+/* the grid-based i-quants (crates/lapid-c/src/lib.rs:53-60; block sizes crates/lapid-quant/src/iq2.rs:24-26, iq3.rs:16) */
+#define LO_FMT_IQ2XXS 10
+#define LO_FMT_IQ2S 11
+#define LO_FMT_IQ3XXS 12
+#define LO_FMT_IQ2XS 13
+#define IQ2XXS_BYTES 66
+#define IQ2XS_BYTES 74
+#define IQ2S_BYTES 82
+#define IQ3XXS_BYTES 98
 
 #define GROUP 32
 #define ALIGN 256
@@ -118,16 +130,26 @@ static inline int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ?
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 static int block_elems(int fmt) { return (fmt == LO_FMT_INT8 || fmt == LO_FMT_INT4 || fmt == LO_FMT_MXFP4) ? GROUP : QK; }
+static int is_iqfmt(int fmt) { return fmt == LO_FMT_IQ2XXS || fmt == LO_FMT_IQ2S || fmt == LO_FMT_IQ3XXS || fmt == LO_FMT_IQ2XS; }
 static int block_bytes(int fmt) {
-    return fmt == LO_FMT_Q4K ? Q4K_BYTES
-                             : (fmt == LO_FMT_Q5K ? Q5K_BYTES : (fmt == LO_FMT_Q6K ? Q6K_BYTES : (fmt == LO_FMT_MXFP4 ? MXFP4_BYTES : 0)));
+    switch (fmt) {
+        case LO_FMT_Q4K: return Q4K_BYTES;
+        case LO_FMT_Q5K: return Q5K_BYTES;
+        case LO_FMT_Q6K: return Q6K_BYTES;
+        case LO_FMT_MXFP4: return MXFP4_BYTES;
+        case LO_FMT_IQ2XXS: return IQ2XXS_BYTES;
+        case LO_FMT_IQ2XS: return IQ2XS_BYTES;
+        case LO_FMT_IQ2S: return IQ2S_BYTES;
+        case LO_FMT_IQ3XXS: return IQ3XXS_BYTES;
+        default: return 0;
+    }
 }
 static int is_kfmt(int fmt) { return fmt == LO_FMT_Q4K || fmt == LO_FMT_Q5K || fmt == LO_FMT_Q6K; }
 
 /* out = {qs_offset, qs_bytes, scales_offset, scales_bytes, total}; returns 0, or -1 on a bad
  * format / cols not a multiple of the block. */
 int lo_layout(int fmt, size_t rows, size_t cols, size_t out[5]) {
-    if (fmt != LO_FMT_INT8 && fmt != LO_FMT_INT4 && fmt != LO_FMT_MXFP4 && !is_kfmt(fmt)) return -1;
+    if (fmt != LO_FMT_INT8 && fmt != LO_FMT_INT4 && fmt != LO_FMT_MXFP4 && !is_kfmt(fmt) && !is_iqfmt(fmt)) return -1;
     size_t be = (size_t)block_elems(fmt);
     if (cols % be != 0) return -1;
     if (block_bytes(fmt) != 0) {
@@ -588,6 +610,7 @@ void lo_mxfp4_from_e2m1_pairs(const uint8_t *packed, const uint8_t *scales, size
 int lo_quantize(int fmt, const float *data, size_t rows, size_t cols, uint8_t *out) {
     size_t L[5];
     if (cols == 0 || lo_layout(fmt, rows, cols, L) != 0) return -1;
+    if (is_iqfmt(fmt)) return -1; /* the lattice-search quantizers (iq2.rs:99-452, iq3.rs:47-220) are not restated */
     memset(out, 0, L[4]);
     if (fmt == LO_FMT_MXFP4) {
         size_t nb = rows * cols / GROUP;
@@ -617,9 +640,16 @@ int lo_quantize(int fmt, const float *data, size_t rows, size_t cols, uint8_t *o
 }
 
 /* imp.rs:124-160 */
+int lo_dequantize_iq_block(int fmt, const uint8_t *b, float *y);
 int lo_dequantize_row(int fmt, const uint8_t *bytes, size_t rows, size_t cols, size_t row, float *out) {
     size_t L[5];
     if (cols == 0 || lo_layout(fmt, rows, cols, L) != 0 || row >= rows) return -1;
+    if (is_iqfmt(fmt)) {
+        size_t nb = cols / QK, bb = (size_t)block_bytes(fmt);
+        for (size_t b = 0; b < nb; b++)
+            if (lo_dequantize_iq_block(fmt, bytes + (row * nb + b) * bb, out + b * QK) != 0) return -1;
+        return 0;
+    }
     if (fmt == LO_FMT_MXFP4) {
         size_t nb = cols / GROUP;
         for (size_t b = 0; b < nb; b++) lo_dequantize_mxfp4_block(bytes + (row * nb + b) * MXFP4_BYTES, out + b * GROUP);
@@ -804,6 +834,98 @@ static void kcol(int fmt, const uint8_t *wrow, size_t k, size_t rows, const int8
     }
 }
 
+/* ------------------------------------------------------------------ i-quants (crates/lapid-quant/src/iq2.rs, iq3.rs; crates/lapid-cpu/src/iquant.rs)
+ * The codebooks are data of the formats, not arithmetic: the caller hands in the 15488 bytes the reference keeps
+ * as its own test fixture (crates/lapid-quant/tests/fixtures/iquant/grids.bin, read by iquant_golden.rs:53-62 as
+ * iq2xxs_grid u64[256] | iq2s_grid u64[1024] | iq3xxs_grid u32[256] | ksigns u8[128] | iq2xs_grid u64[512]). */
+#define IQ_GRID_BYTES 15488
+static uint8_t IQ_GRIDS[IQ_GRID_BYTES];
+static int iq_grids_set = 0;
+void lo_set_iq_grids(const uint8_t *bytes) {
+    memcpy(IQ_GRIDS, bytes, IQ_GRID_BYTES);
+    iq_grids_set = 1;
+}
+static inline uint32_t rd_u32(const uint8_t *b, size_t o) { return (uint32_t)b[o] | ((uint32_t)b[o + 1] << 8) | ((uint32_t)b[o + 2] << 16) | ((uint32_t)b[o + 3] << 24); }
+
+/* iquant.rs:40-64 (`group8`): the 8 grid bytes of 8-group j (0..32) and its sign bits */
+static uint8_t iq_group8(int fmt, const uint8_t *b, int j, uint8_t g[8]) {
+    const uint8_t *ksigns = IQ_GRIDS + 11264;
+    int ib = j / 4, l = j % 4;
+    if (fmt == LO_FMT_IQ2XXS) {
+        uint32_t a1 = rd_u32(b, 6 + 8 * (size_t)ib);
+        memcpy(g, IQ_GRIDS + 8 * (size_t)b[2 + 8 * ib + l], 8);
+        return ksigns[(a1 >> (7 * l)) & 127];
+    }
+    if (fmt == LO_FMT_IQ2XS) {
+        uint32_t q = (uint32_t)b[2 + 2 * j] | ((uint32_t)b[3 + 2 * j] << 8);
+        memcpy(g, IQ_GRIDS + 11392 + 8 * (size_t)(q & 511), 8);
+        return ksigns[q >> 9];
+    }
+    if (fmt == LO_FMT_IQ2S) {
+        size_t idx = (size_t)b[2 + j] | (((size_t)b[66 + ib] << (8 - 2 * l)) & 0x300);
+        memcpy(g, IQ_GRIDS + 2048 + 8 * idx, 8);
+        return b[34 + j];
+    }
+    uint32_t aux = rd_u32(b, 66 + 4 * (size_t)ib);
+    memcpy(g, IQ_GRIDS + 10240 + 4 * (size_t)b[2 + 8 * ib + 2 * l], 4);
+    memcpy(g + 4, IQ_GRIDS + 10240 + 4 * (size_t)b[2 + 8 * ib + 2 * l + 1], 4);
+    return ksigns[(aux >> (7 * l)) & 127];
+}
+
+/* iquant.rs:66-89 (`half_scales`), the same expressions as the dequantizers (iq2.rs:41-44, :59-60, :78; iq3.rs:24-25) */
+static void iq_half_scales(int fmt, const uint8_t *b, float s[16]) {
+    float d = rd_h(b, 0);
+    for (int ib = 0; ib < 8; ib++) {
+        float v0, v1;
+        if (fmt == LO_FMT_IQ2XXS) {
+            v0 = v1 = d * (0.5f + (float)(rd_u32(b, 6 + 8 * (size_t)ib) >> 28)) * 0.25f;
+        } else if (fmt == LO_FMT_IQ2XS || fmt == LO_FMT_IQ2S) {
+            uint8_t sc = b[(fmt == LO_FMT_IQ2XS ? 66 : 74) + ib];
+            v0 = d * (0.5f + (float)(sc & 15)) * 0.25f;
+            v1 = d * (0.5f + (float)(sc >> 4)) * 0.25f;
+        } else {
+            v0 = v1 = d * (0.5f + (float)(rd_u32(b, 66 + 4 * (size_t)ib) >> 28)) * 0.5f;
+        }
+        s[2 * ib] = v0;
+        s[2 * ib + 1] = v1;
+    }
+}
+
+/* iq2.rs:38-90, iq3.rs:18-39: y = db * f32(grid byte) * (+1 | -1) */
+int lo_dequantize_iq_block(int fmt, const uint8_t *b, float *y) {
+    if (!is_iqfmt(fmt) || !iq_grids_set) return -1;
+    float s[16];
+    iq_half_scales(fmt, b, s);
+    for (int j = 0; j < 32; j++) {
+        uint8_t g[8];
+        uint8_t signs = iq_group8(fmt, b, j, g);
+        for (int i = 0; i < 8; i++) y[8 * j + i] = s[j / 2] * (float)g[i] * ((signs >> i) & 1 ? -1.0f : 1.0f);
+    }
+    return 0;
+}
+
+/* iquant.rs:92-103 (`unpack_block`) and :108-128 (`tile_scalar`): one output column,
+ * acc += sc[h] * da[h / 2] * f32(dot of 16 elements), halves in order */
+static void iqcol(int fmt, const uint8_t *wrow, size_t k, size_t rows, const int8_t *qa, const float *sa, float *acc) {
+    size_t kg = k / GROUP, bb = (size_t)block_bytes(fmt);
+    int8_t q[QK];
+    float sc[16];
+    for (size_t r = 0; r < rows; r++) acc[r] = 0.0f;
+    for (size_t blk = 0; blk < k / QK; blk++) {
+        const uint8_t *b = wrow + blk * bb;
+        for (int j = 0; j < 32; j++) {
+            uint8_t g[8];
+            uint8_t signs = iq_group8(fmt, b, j, g);
+            for (int i = 0; i < 8; i++) q[8 * j + i] = (signs >> i) & 1 ? (int8_t)-(int)g[i] : (int8_t)g[i];
+        }
+        iq_half_scales(fmt, b, sc);
+        for (size_t r = 0; r < rows; r++) {
+            const int8_t *a = qa + r * k + blk * QK;
+            for (int h = 0; h < 16; h++) acc[r] += sc[h] * sa[r * kg + blk * 8 + (size_t)h / 2] * idot(a + 16 * h, q + 16 * h, 16);
+        }
+    }
+}
+
 /* crates/lapid-cpu/src/mxfp4.rs:27-58: one output column of the MXFP4 decode tile, acc += d * da * f32(dot) */
 static void mxcol(const uint8_t *wrow, size_t k, size_t rows, const int8_t *qa, const float *sa, float *acc) {
     size_t kg = k / GROUP;
@@ -888,6 +1010,7 @@ int lo_matmul(int fmt, const float *a, size_t a_len, lo_view av, const uint8_t *
     if (lo_layout(fmt, w_rows, w_cols, L) != 0) return LO_INVALID_LAUNCH; /* QMat::new, qmat.rs:38-60 */
     if (w_len < L[2] + L[3]) return LO_OUT_OF_BOUNDS;
     if (w_rows != n || w_cols != k) return LO_SHAPE_MISMATCH;
+    if (is_iqfmt(fmt) && !iq_grids_set) return LO_UNSUPPORTED;
 
     if (rows <= 8 && !force_f32_act) {
         if (path) *path = 0;
@@ -904,6 +1027,7 @@ int lo_matmul(int fmt, const float *a, size_t a_len, lo_view av, const uint8_t *
         for (long long j = 0; j < (long long)n; j++) {
             float acc[8];
             if (fmt == LO_FMT_MXFP4) mxcol(w + (size_t)j * kg * MXFP4_BYTES, k, rows, qa, sa, acc);
+            else if (is_iqfmt(fmt)) iqcol(fmt, w + (size_t)j * (k / QK) * bb, k, rows, qa, sa, acc);
             else if (fmt == LO_FMT_INT8 || fmt == LO_FMT_INT4) i8col(fmt, w, L[2], (size_t)j, k, rows, qa, sa, acc);
             else kcol(fmt, w + (size_t)j * (k / QK) * bb, k, rows, qa, sa, bs, acc);
             for (size_t r = 0; r < rows; r++) {

@@ -28,8 +28,14 @@ SRC = os.path.join(HERE, "lapid_oracle.c")
 
 # dtype codes shared with crates/lapid-c/src/lib.rs:37-60
 INT8, INT4, Q4_K, Q5_K, Q6_K, MXFP4 = 4, 5, 6, 7, 8, 9
-FORMATS = {"int8": INT8, "int4": INT4, "q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K, "mxfp4": MXFP4}
-BLOCK_BYTES = {Q4_K: 144, Q5_K: 176, Q6_K: 210, MXFP4: 17}
+IQ2_XXS, IQ2_S, IQ3_XXS, IQ2_XS = 10, 11, 12, 13
+IQUANTS = (IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS)
+FORMATS = {"int8": INT8, "int4": INT4, "q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K, "mxfp4": MXFP4,
+           "iq2_xxs": IQ2_XXS, "iq2_xs": IQ2_XS, "iq2_s": IQ2_S, "iq3_xxs": IQ3_XXS}
+BLOCK_BYTES = {Q4_K: 144, Q5_K: 176, Q6_K: 210, MXFP4: 17, IQ2_XXS: 66, IQ2_XS: 74, IQ2_S: 82, IQ3_XXS: 98}
+# The i-quant codebooks: the reference's own fixture (crates/lapid-quant/tests/fixtures/iquant/grids.bin), kept with the
+# other golden files of the tests.
+IQ_GRIDS = os.path.join(os.path.dirname(HERE), "tests", "golden", "iquant", "grids.bin")
 
 ERRORS = {1: "invalid_launch", 2: "shape_mismatch", 3: "out_of_bounds", 4: "unsupported_dtype"}
 
@@ -115,6 +121,13 @@ class Oracle:
         lib.lo_dequantize_mxfp4_block.argtypes = [C.c_void_p, C.c_void_p]
         lib.lo_mxfp4_from_e2m1_pairs.argtypes = [C.c_void_p, C.c_void_p, sz, sz, C.c_void_p]
         lib.lo_mxfp4_from_e2m1_pairs.restype = None
+        lib.lo_set_iq_grids.argtypes = [C.c_void_p]
+        lib.lo_set_iq_grids.restype = None
+        lib.lo_dequantize_iq_block.argtypes = [C.c_int, C.c_void_p, C.c_void_p]
+        if os.path.exists(IQ_GRIDS):
+            grids = np.fromfile(IQ_GRIDS, dtype=np.uint8)
+            assert grids.size == 15488
+            lib.lo_set_iq_grids(grids.ctypes.data)
         lib.lo_matmul.argtypes = [C.c_int, C.c_void_p, sz, _View, C.c_void_p, sz, sz, sz, C.c_void_p, C.c_void_p, sz,
                                   _View, sz, sz, sz, sz, C.c_int, C.c_int, C.POINTER(C.c_int)]
         lib.lo_num_threads.restype = C.c_int
@@ -185,6 +198,10 @@ class Oracle:
     def dequantize_block(self, fmt: int, b: np.ndarray) -> np.ndarray:
         b = np.ascontiguousarray(b, dtype=np.uint8)
         out = np.empty(32 if fmt == MXFP4 else 256, dtype=np.float32)
+        if fmt in IQUANTS:
+            if self.lib.lo_dequantize_iq_block(fmt, b.ctypes.data, out.ctypes.data) != 0:
+                raise OracleError("unsupported_dtype", "i-quant codebooks not loaded")
+            return out
         {Q4_K: self.lib.lo_dequantize_q4k_block, Q5_K: self.lib.lo_dequantize_q5k_block,
          Q6_K: self.lib.lo_dequantize_q6k_block, MXFP4: self.lib.lo_dequantize_mxfp4_block}[fmt](b.ctypes.data, out.ctypes.data)
         return out

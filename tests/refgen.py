@@ -52,3 +52,34 @@ def make_blocks(fmt_bytes, n_blocks, seed, d_off, dmin_off=None):
     if dmin_off is not None:
         b[:, dmin_off:dmin_off + 2] = dm
     return v
+
+
+IQ_BLOCK_BYTES = {10: 66, 11: 82, 12: 98, 13: 74}   # IQ2_XXS, IQ2_S, IQ3_XXS, IQ2_XS by lapid dtype code
+
+
+def iq_matrix(fmt, rows, cols, seed, pad=True):
+    """Random i-quant blocks for a [rows, cols] matrix: every bit pattern of the index, sign and scale fields is a
+    valid block, so the bytes are uniform; the f16 super-block scales cycle through magnitudes from 6e-8 (a denormal)
+    to 7, both signs. The result is padded to the 256-byte multiple of ``layout(..).total``."""
+    bb = IQ_BLOCK_BYTES[int(fmt)]
+    nb = rows * cols // 256
+    raw = np.random.default_rng(seed).integers(0, 256, nb * bb, dtype=np.uint8)
+    ds = np.array([0.01, 0.25, 3e-5, -0.02, 6e-8, 1.5, 0.003, 7.0, 0.0], np.float16).view(np.uint8).reshape(-1, 2)
+    b = raw.reshape(nb, bb)
+    b[:, 0:2] = ds[np.arange(nb) % ds.shape[0]]
+    if not pad:
+        return raw
+    return np.concatenate([raw, np.zeros((-raw.size) % 256, np.uint8)])
+
+
+def iq_fixture(name):
+    """The reference's golden file for one i-quant (crates/lapid-quant/tests/fixtures/iquant/<name>.bin, read by
+    tests/iquant_golden.rs:36-52): sections of (block bytes of an 8 x 512 matrix quantized by ggml, the f32 values ggml
+    dequantizes them to). Returns a list of (blocks u8, values f32)."""
+    import os
+    bb = {"iq2_xxs": 66, "iq2_xs": 74, "iq2_s": 82, "iq3_xxs": 98}[name]
+    f = np.fromfile(os.path.join(os.path.dirname(__file__), "golden", "iquant", name + ".bin"), dtype=np.uint8)
+    qn = 16 * bb
+    sec = qn + 4 * 4096
+    assert f.size % sec == 0
+    return [(f[i * sec:i * sec + qn].copy(), f[i * sec + qn:(i + 1) * sec].copy().view(np.float32)) for i in range(f.size // sec)]

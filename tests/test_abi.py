@@ -45,7 +45,8 @@ def test_abi_version_and_mismatch_error_json():
 
 
 def test_layout_matches_oracle_and_reference_sizes(oracle):
-    for fmt in (quant.Format.Int8, quant.Format.Int4, quant.Format.Q4K, quant.Format.Q5K, quant.Format.Q6K, quant.Format.MXFP4):
+    for fmt in (quant.Format.Int8, quant.Format.Int4, quant.Format.Q4K, quant.Format.Q5K, quant.Format.Q6K, quant.Format.MXFP4,
+                quant.Format.Iq2Xxs, quant.Format.Iq2Xs, quant.Format.Iq2S, quant.Format.Iq3Xxs):
         for rows, cols in [(1, 256), (3, 512), (768, 768 if fmt.block_elems() == 32 else 1024), (4096, 4096), (14336, 4096),
                            (4096, 14336), (128256, 4096)]:
             a, b = quant.layout(fmt, rows, cols), oracle.layout(int(fmt), rows, cols)
@@ -60,8 +61,11 @@ def test_layout_matches_oracle_and_reference_sizes(oracle):
     assert e.value.code == "invalid_launch" and e.value.status == 8
     l = quant.layout(quant.Format.MXFP4, 2, 128)  # 8 blocks of 17 bytes (crates/lapid-quant/src/lib.rs:62-75, :108-112)
     assert (l.qs_bytes, l.scales_offset, l.scales_bytes, l.total) == (136, 136, 0, 256)
+    l = quant.layout(quant.Format.Iq2Xxs, 2, 512)  # 4 blocks of 66 bytes (crates/lapid-quant/tests/iquant_golden.rs:88-99)
+    assert (l.qs_bytes, l.scales_offset, l.scales_bytes, l.total) == (264, 264, 0, 512)
+    assert [quant.layout(f, 1, 256).qs_bytes for f in (quant.Format.Iq2Xs, quant.Format.Iq2S, quant.Format.Iq3Xxs)] == [74, 82, 98]
     with pytest.raises(lp.LapidError) as e:
-        quant.layout(10, 2, 256)  # iq2_xxs: the grid-based i-quants are not implemented here
+        quant.layout(14, 2, 256)  # no such dtype code
     assert e.value.code == "unsupported_dtype" and e.value.status == 3
 
 

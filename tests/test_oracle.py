@@ -473,3 +473,69 @@ def test_seeded_generator_is_counter_based():
     assert np.array_equal(a[600:], b)
     assert abs(float(a.std()) - 0.02) < 0.002 and abs(float(a.mean())) < 0.003
     assert not np.array_equal(O.normal(4, 1000, 0.02), a)
+
+
+# ------------------------------------------------------------------ i-quants
+IQ_CASES = [("iq2_xxs", O.IQ2_XXS), ("iq2_xs", O.IQ2_XS), ("iq2_s", O.IQ2_S), ("iq3_xxs", O.IQ3_XXS)]
+
+
+@pytest.mark.parametrize("name,fmt", IQ_CASES)
+def test_iquant_dequantizers_match_the_reference_golden_bytes(oracle, name, fmt):
+    """The reference's `iq*_matches_ggml` (crates/lapid-quant/tests/iquant_golden.rs:64-86): the blocks ggml produced
+    for the fixture input dequantize to ggml's f32 bits. (Its quantizer half is not restated: no i-quant quantizer.)"""
+    from tests.refgen import iq_fixture
+    secs = iq_fixture(name)
+    assert len(secs) == (2 if name in ("iq2_s", "iq3_xxs") else 1)
+    for blocks, values in secs:
+        bb = O.BLOCK_BYTES[fmt]
+        for i in range(16):
+            y = oracle.dequantize_block(fmt, blocks[i * bb:(i + 1) * bb])
+            assert np.array_equal(y.view(np.uint32), values[i * 256:(i + 1) * 256].view(np.uint32))
+        qb = np.concatenate([blocks, np.zeros((-blocks.size) % 256, np.uint8)])
+        assert np.array_equal(oracle.dequantize(fmt, qb, 8, 512).reshape(-1).view(np.uint32), values.view(np.uint32))
+
+
+def test_iquant_codebooks(oracle):
+    """`grids_match_ggml` (iquant_golden.rs:53-62) fixes the order of the codebook file; its sign table follows the
+    parity rule of crates/lapid-quant/src/iqgrid.rs:19-30, the 2-bit grids hold the levels 8, 25, 43 and the 3-bit grid
+    4, 12 .. 52, 62 (iqgrid.rs:33-71). The copy the CUDA library embeds is the same file."""
+    import os
+    g = np.fromfile(O.IQ_GRIDS, dtype=np.uint8)
+    assert g.size == 2048 + 8192 + 1024 + 128 + 4096
+    assert np.array_equal(g[11264:11392], np.array([i | ((bin(i).count("1") & 1) << 7) for i in range(128)], np.uint8))
+    for a, b in ((0, 2048), (2048, 10240), (11392, 15488)):
+        assert set(np.unique(g[a:b])) == {8, 25, 43}
+    assert set(np.unique(g[10240:11264])) == {4, 12, 20, 28, 36, 44, 52, 62}
+    for a, b, w in ((0, 2048, 8), (2048, 10240, 8), (10240, 11264, 4), (11392, 15488, 8)):   # no entry twice
+        assert np.unique(g[a:b].reshape(-1, w), axis=0).shape[0] == (b - a) // w
+    shipped = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lapid_b200", "csrc", "iq_grids.bin")
+    assert np.array_equal(np.fromfile(shipped, dtype=np.uint8), g)
+
+
+@pytest.mark.parametrize("name,fmt", IQ_CASES)
+def test_iquant_random_blocks_against_the_gguf_package_and_the_decode_tile(oracle, name, fmt):
+    """Every byte pattern is a valid block: random blocks dequantize like the `gguf` package's independent
+    dequantizer, bit for bit; the int8-activation decode tile (crates/lapid-cpu/src/iquant.rs:108-128) agrees with the
+    dequantized weights times the dequantized activations (the reference's `tiles_match_dequant_reference`, :319-352);
+    layout and block sizes as `layout_and_generic_quantize` (iquant_golden.rs:88-99) states them."""
+    from tests.refgen import iq_matrix
+    n, k = 24, 1024
+    l = oracle.layout(fmt, n, k)
+    assert l.qs_bytes == n * k // 256 * {"iq2_xxs": 66, "iq2_xs": 74, "iq2_s": 82, "iq3_xxs": 98}[name] and l.scales_bytes == 0
+    qb = iq_matrix(fmt, n, k, 17)
+    deq = oracle.dequantize(fmt, qb, n, k).reshape(n, k)
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    t = getattr(gguf.GGMLQuantizationType, name.upper())
+    theirs = quants.dequantize(qb[:l.qs_bytes].reshape(n, -1), t).astype(np.float32)
+    assert np.array_equal(theirs.view(np.uint32), deq.view(np.uint32))
+    for m in (1, 3, 8):
+        a = O.normal(18 + m, m * k).reshape(m, k)
+        got, path = oracle.matmul(fmt, a, qb, n, k, m=m)
+        assert path == "int8_act"
+        qa = [oracle.quantize_row_sums(a[i], want_bs=False) for i in range(m)]
+        adq = np.stack([q[0].astype(np.float64).reshape(-1, 32) * q[1].astype(np.float64)[:, None] for q in qa]).reshape(m, k)
+        ref = adq @ deq.astype(np.float64).T
+        assert np.abs(got.reshape(m, n) - ref).max() <= 1e-5 * np.abs(ref).max()
+    with pytest.raises(O.OracleError):
+        oracle.quantize(fmt, np.zeros(256, np.float32), 1, 256)
