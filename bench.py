@@ -41,16 +41,13 @@ sys.path.insert(0, ROOT)
 
 SHAPES = [(4096, 4096, "q/o"), (1024, 4096, "k/v"), (14336, 4096, "gate/up"), (4096, 14336, "down")]
 MS = [1, 2, 4, 8]
-FMT_NAMES = {4: "int8", 5: "int4", 6: "q4_k", 7: "q5_k", 8: "q6_k"}
+FMT_NAMES = {4: "int8", 5: "int4", 6: "q4_k", 7: "q5_k", 8: "q6_k", 9: "mxfp4", 10: "iq2_xxs", 11: "iq2_s", 12: "iq3_xxs", 13: "iq2_xs"}
+AOS_BLOCK = {6: (256, 144), 7: (256, 176), 8: (256, 210), 9: (32, 17), 10: (256, 66), 11: (256, 82), 12: (256, 98), 13: (256, 74)}
 
 
 def weight_bytes(fmt: int, n: int, k: int) -> int:
-    if fmt == 6:
-        b = n * k // 256 * 144
-    elif fmt == 7:
-        b = n * k // 256 * 176
-    elif fmt == 8:
-        b = n * k // 256 * 210
+    if fmt in AOS_BLOCK:
+        b = n * k // AOS_BLOCK[fmt][0] * AOS_BLOCK[fmt][1]
     elif fmt == 5:
         b = (n * k // 2 + 255) // 256 * 256 + n * k // 32 * 2
     else:
@@ -963,6 +960,15 @@ def run_case(args):
     one = quant.layout(fmt, n, k).total
     stack = torch.empty((e or 1) * one, dtype=torch.uint8, device="cuda")
     for x in range(e or 1):
+        if fmt >= 10:   # the i-quants have no quantizer here; every byte pattern is a valid block: random blocks, small f16 scales
+            g = torch.Generator(device="cuda")
+            g.manual_seed(7 + x)
+            blocks = torch.randint(0, 256, (n * k // 256, AOS_BLOCK[fmt][1]), dtype=torch.uint8, device="cuda", generator=g)
+            blocks[:, 0] = 0x1F          # d = f16 0x211F, about 0.01
+            blocks[:, 1] = 0x21
+            stack[x * one:x * one + blocks.numel()] = blocks.reshape(-1)
+            torch.cuda.synchronize()
+            continue
         w = torch.randn(n * k, device="cuda") * 0.02
         torch.cuda.synchronize()
         be.quantize_into(fmt, be.wrap_tensor(w), n, k, be.wrap_tensor(stack[x * one:(x + 1) * one]))

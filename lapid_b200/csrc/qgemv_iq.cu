@@ -4,13 +4,16 @@
 //     acc += sc[h] * da[h / 2] * f32(sum_16 qa * grid * sign)        per 16-element half h of a block
 //
 // These formats hold 2 to 3 bits per weight, so a launch reads little from HBM and spends its time looking up
-// grid entries: the kernel is built around that. Each CTA first copies the format's codebook (1 to 8 KB) into
-// shared memory. One warp takes one weight row at a time; a lane takes one half (two 8-groups) of a block, so a
-// warp covers two blocks per step: it reads the half's index and sign bits straight from the 2-byte-aligned block
-// (L1 serves the neighbours), fetches the two grid entries from shared memory, applies the signs to get sixteen
-// int8 weights in four registers, and multiplies them with `dp4a` against each activation row's sixteen int8
-// values (one 16-byte load per row from the activation planes). The sum over 16 elements is exact, the products
-// are the reference's; only the order in which the halves are added differs (lanes, then a shuffle tree).
+// grid entries and applying signs: the kernel is built around that. Each CTA first copies the format's codebook (1 to
+// 8 KB) into shared memory; a lookup is one shared-memory load at a data-dependent address (bank conflicts are the
+// cost that remains), the signs are applied in three arithmetic instructions per four weights (signed4 below) rather
+// than through a second table.
+// One warp takes ROWS weight rows at a time; a lane takes one 32-element sub-block of a block (four 8-groups: 4 to
+// 12 bytes of indices and signs, read as 16-bit halves because blocks are only 2-byte aligned), so a warp covers
+// four blocks per step. The lane turns its sub-block into eight registers of int8 weights and multiplies them with
+// `dp4a` against each activation row's 32 int8 values (two 16-byte loads per row from the activation planes, shared
+// by the ROWS weight rows). The sums over 16 elements are exact and the products are the reference's; only the
+// order in which the halves are added differs (lanes, then a shuffle tree).
 #include "common.cuh"
 #include "iquant.cuh"
 #include "kernels.h"
@@ -20,7 +23,71 @@ namespace iq {
 
 constexpr int WARPS = 8;
 
-template <int FMT, int M> __global__ void __launch_bounds__(WARPS * 32) qgemv_iq_kernel(GemvArgs p, const uint8_t *__restrict__ grid_global) {
+// Four grid bytes with the signs of bits 0..3 of `s4` (0..15) applied, as four int8 values. The multiplication puts
+// sign bit j into the top bit of byte j (the other product bits land elsewhere), the byte-permute in its
+// sign-replicating mode turns that into the byte mask m, and (g ^ m) + (m & 0x01010101) negates the masked bytes:
+// a grid byte is never 0, so the + 1 of a negation never carries into the next byte.
+__device__ __forceinline__ uint32_t signed4(uint32_t g, uint32_t s4) {
+    uint32_t m;  // prmt's selector nibbles 8 | j: replicate the top bit of byte j (the __byte_perm intrinsic drops that bit)
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(s4 * 0x10204080u), "r"(0u), "r"(0xBA98u));
+    return (g ^ m) + (m & 0x01010101u);
+}
+// ... and of the 8-group whose sign bits are `s8`: lo takes bits 0..3, hi bits 4..7
+__device__ __forceinline__ void signed8(uint32_t glo, uint32_t ghi, uint32_t s8, uint32_t &lo, uint32_t &hi) {
+    lo = signed4(glo, s8 & 15u);
+    hi = signed4(ghi, s8 >> 4);
+}
+
+// The eight int8-weight registers (w[2l], w[2l + 1] = 8-group l) and the two half scales of sub-block ib.
+template <int FMT>
+__device__ __forceinline__ void unpack32(const uint8_t *b, int ib, const uint8_t *grid, uint32_t (&w)[8], float &sc0, float &sc1) {
+    const float d = half_bits_to_float(ld16(b));
+    uint32_t idx[4], sg[4], s0, s1;  // grid entry and sign-table entry of each 8-group; the 4-bit scales
+    if constexpr (FMT == FMT_IQ2XXS) {
+        const uint8_t *p = b + 2 + 8 * ib;
+        const uint32_t q = ld32_by16(p), a1 = ld32_by16(p + 4);
+#pragma unroll
+        for (int l = 0; l < 4; l++) idx[l] = (q >> (8 * l)) & 255u, sg[l] = (a1 >> (7 * l)) & 127u;
+        s0 = s1 = a1 >> 28;
+    } else if constexpr (FMT == FMT_IQ2XS) {
+        const uint8_t *p = b + 2 + 8 * ib;
+        const uint32_t q01 = ld32_by16(p), q23 = ld32_by16(p + 4), sc = b[66 + ib];
+        idx[0] = q01 & 511u, sg[0] = (q01 >> 9) & 127u, idx[1] = (q01 >> 16) & 511u, sg[1] = q01 >> 25;
+        idx[2] = q23 & 511u, sg[2] = (q23 >> 9) & 127u, idx[3] = (q23 >> 16) & 511u, sg[3] = q23 >> 25;
+        s0 = sc & 15u, s1 = sc >> 4;
+    } else if constexpr (FMT == FMT_IQ2S) {
+        const uint32_t q = ld32_by16(b + 2 + 4 * ib), sn = ld32_by16(b + 34 + 4 * ib), qh = b[66 + ib], sc = b[74 + ib];
+#pragma unroll
+        for (int l = 0; l < 4; l++) idx[l] = ((q >> (8 * l)) & 255u) | (((qh >> (2 * l)) & 3u) << 8), sg[l] = (sn >> (8 * l)) & 255u;
+        s0 = sc & 15u, s1 = sc >> 4;
+    } else {
+        const uint32_t aux = ld32_by16(b + 66 + 4 * ib);
+#pragma unroll
+        for (int l = 0; l < 4; l++) sg[l] = (aux >> (7 * l)) & 127u;
+        s0 = s1 = aux >> 28;
+    }
+    if constexpr (FMT == FMT_IQ3XXS) {
+        const uint8_t *p = b + 2 + 8 * ib;
+        const uint32_t q0 = ld32_by16(p), q1 = ld32_by16(p + 4);
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint32_t q = l < 2 ? q0 >> (16 * l) : q1 >> (16 * (l - 2));
+            signed8(*(const uint32_t *)(grid + 4 * (q & 255u)), *(const uint32_t *)(grid + 4 * ((q >> 8) & 255u)), iq_ksign(sg[l]), w[2 * l], w[2 * l + 1]);
+        }
+    } else {
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const uint2 g = *(const uint2 *)(grid + 8 * idx[l]);
+            signed8(g.x, g.y, FMT == FMT_IQ2S ? sg[l] : iq_ksign(sg[l]), w[2 * l], w[2 * l + 1]);
+        }
+    }
+    constexpr float F = FMT == FMT_IQ3XXS ? 0.5f : 0.25f;  // crates/lapid-cpu/src/iquant.rs:66-89, each operation rounded on its own
+    sc0 = xmul(xmul(d, xadd(0.5f, (float)s0)), F);
+    sc1 = xmul(xmul(d, xadd(0.5f, (float)s1)), F);
+}
+
+template <int FMT, int M, int ROWS>
+__global__ void __launch_bounds__(WARPS * 32) qgemv_iq_kernel(GemvArgs p, const uint8_t *__restrict__ grid_global) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ __align__(16) uint8_t grid[iq_grid_bytes(FMT)];
     {  // the codebook never changes: it may be read before the launch this one depends on has finished
@@ -44,50 +111,62 @@ template <int FMT, int M> __global__ void __launch_bounds__(WARPS * 32) qgemv_iq
         p.da += (uint64_t)token * kg;
         p.out_off += (uint64_t)pair * p.n;
     }
-    const int h = lane & 15;  // this lane's half of the block
-    for (uint32_t row = blockIdx.x * WARPS + warp; row < p.n; row += gridDim.x * WARPS) {
-        float acc[M];
+    const int ib = lane & 7;  // this lane's sub-block
+    for (uint32_t row0 = (blockIdx.x * WARPS + warp) * ROWS; row0 < p.n; row0 += gridDim.x * WARPS * ROWS) {
+        float acc[ROWS][M];
 #pragma unroll
-        for (int r = 0; r < M; r++) acc[r] = 0.0f;
-        const uint8_t *wrow = p.w + (uint64_t)row * nblk * BB;
-        for (uint32_t blk = lane >> 4; blk < nblk; blk += 2) {
-            const uint8_t *b = wrow + (uint64_t)blk * BB;
-            uint32_t w[4], s0, s1;
-            iq_group8<FMT>(b, 2 * h, grid, w[0], w[1], s0);
-            iq_group8<FMT>(b, 2 * h + 1, grid, w[2], w[3], s1);
-            w[0] = iq_apply_signs(w[0], s0);
-            w[1] = iq_apply_signs(w[1], s0 >> 4);
-            w[2] = iq_apply_signs(w[2], s1);
-            w[3] = iq_apply_signs(w[3], s1 >> 4);
-            const float sc = iq_half_scale<FMT>(b, h);
-            const uint32_t g = blk * 8 + (h >> 1);  // activation group of this half
+        for (int j = 0; j < ROWS; j++)
+#pragma unroll
+            for (int r = 0; r < M; r++) acc[j][r] = 0.0f;
+        for (uint32_t blk = lane >> 3; blk < nblk; blk += 4) {
+            uint32_t w[ROWS][8];
+            float sc[ROWS][2];
+#pragma unroll
+            for (int j = 0; j < ROWS; j++) {
+                const uint32_t row = row0 + j < p.n ? row0 + j : p.n - 1;  // (a row past the end repeats the last one; not stored)
+                unpack32<FMT>(p.w + ((uint64_t)row * nblk + blk) * BB, ib, grid, w[j], sc[j][0], sc[j][1]);
+            }
+            const uint32_t g = blk * 8 + ib;  // activation group of this sub-block
 #pragma unroll
             for (int r = 0; r < M; r++) {
-                const uint4 a = __ldg((const uint4 *)(p.qa + (uint64_t)r * k + (uint64_t)blk * QK + 16 * h));
+                const uint4 *ap = (const uint4 *)(p.qa + (uint64_t)r * k + (uint64_t)g * GROUP);
+                const uint4 a0 = __ldg(ap), a1 = __ldg(ap + 1);
                 const float da = __ldg(p.da + (uint64_t)r * kg + g);
-                int dot = __dp4a((int)w[0], (int)a.x, 0);
-                dot = __dp4a((int)w[1], (int)a.y, dot);
-                dot = __dp4a((int)w[2], (int)a.z, dot);
-                dot = __dp4a((int)w[3], (int)a.w, dot);
-                acc[r] += (sc * da) * (float)dot;
+#pragma unroll
+                for (int j = 0; j < ROWS; j++) {
+                    int d0 = __dp4a((int)w[j][0], (int)a0.x, 0);
+                    d0 = __dp4a((int)w[j][1], (int)a0.y, d0);
+                    d0 = __dp4a((int)w[j][2], (int)a0.z, d0);
+                    d0 = __dp4a((int)w[j][3], (int)a0.w, d0);
+                    int d1 = __dp4a((int)w[j][4], (int)a1.x, 0);
+                    d1 = __dp4a((int)w[j][5], (int)a1.y, d1);
+                    d1 = __dp4a((int)w[j][6], (int)a1.z, d1);
+                    d1 = __dp4a((int)w[j][7], (int)a1.w, d1);
+                    acc[j][r] += (sc[j][0] * da) * (float)d0;
+                    acc[j][r] += (sc[j][1] * da) * (float)d1;
+                }
             }
         }
 #pragma unroll
-        for (int r = 0; r < M; r++) {
-            float v = acc[r];
+        for (int j = 0; j < ROWS; j++) {
 #pragma unroll
-            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0) {
-                const uint32_t bt = r / p.m, i = r % p.m;
-                if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
-                p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
+            for (int r = 0; r < M; r++) {
+                float v = acc[j][r];
+#pragma unroll
+                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                const uint32_t row = row0 + j;
+                if (lane == 0 && row < p.n) {
+                    const uint32_t bt = r / p.m, i = r % p.m;
+                    if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
+                    p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
+                }
             }
         }
     }
 }
 
-template <int FMT, int M> static cudaError_t launch_m(const GemvArgs &a, const uint8_t *grid, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
-    const uint32_t want = (a.n + WARPS - 1) / WARPS;
+template <int FMT, int M, int ROWS> static cudaError_t launch_r(const GemvArgs &a, const uint8_t *grid, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
+    const uint32_t want = (a.n + WARPS * ROWS - 1) / (WARPS * ROWS);
     uint32_t cap = (uint32_t)sm_count * 8;
     if (pairs > 1) cap = cap / pairs > 0 ? cap / pairs : 1;
     cudaLaunchConfig_t cfg = {};
@@ -99,7 +178,16 @@ template <int FMT, int M> static cudaError_t launch_m(const GemvArgs &a, const u
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, qgemv_iq_kernel<FMT, M>, a, grid);
+    return cudaLaunchKernelEx(&cfg, qgemv_iq_kernel<FMT, M, ROWS>, a, grid);
+}
+
+// Two weight rows per warp share the activation loads; one row per warp where that would leave SMs without work.
+template <int FMT, int M> static cudaError_t launch_m(const GemvArgs &a, const uint8_t *grid, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
+    const uint64_t warps2 = ((uint64_t)a.n + 1) / 2 * pairs;
+    if constexpr (M <= 4) {
+        if (warps2 >= (uint64_t)sm_count * WARPS * 4) return launch_r<FMT, M, 2>(a, grid, pairs, sm_count, pdl, stream);
+    }
+    return launch_r<FMT, M, 1>(a, grid, pairs, sm_count, pdl, stream);
 }
 
 template <int FMT> static cudaError_t launch_fmt(const GemvArgs &args, const uint8_t *grid, int sm_count, bool pdl, cudaStream_t stream) {
