@@ -136,6 +136,7 @@ cudaError_t launch_qgemv_mxfp4(const GemvArgs &args, int sm_count, bool pdl, cud
 // ---- qgemv_iq.cu: the grid-based i-quants (IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS), 1..8 rows (and the expert-indexed form);
 // reads the activation planes, the codebooks from the per-device table of iquant.cu
 cudaError_t launch_qgemv_iq(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+void qgemv_iq_set_rows_per_warp(int rows);  // 0: per launch (default); 1, 2: forced
 // iquant.cu: uploads the codebooks to the current device (once; outside stream captures)
 cudaError_t iq_grids_upload();
 // Opt in to the dynamic shared memory the GEMV variants need; once per device.

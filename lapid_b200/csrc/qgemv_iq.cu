@@ -8,7 +8,7 @@
 // 8 KB) into shared memory; a lookup is one shared-memory load at a data-dependent address (bank conflicts are the
 // cost that remains), the signs are applied in three arithmetic instructions per four weights (signed4 below) rather
 // than through a second table.
-// One warp takes ROWS weight rows at a time; a lane takes one 32-element sub-block of a block (four 8-groups: 4 to
+// One warp takes ROWS (1 or 2) weight rows at a time; a lane takes one 32-element sub-block of a block (four 8-groups: 4 to
 // 12 bytes of indices and signs, read as 16-bit halves because blocks are only 2-byte aligned), so a warp covers
 // four blocks per step. The lane turns its sub-block into eight registers of int8 weights and multiplies them with
 // `dp4a` against each activation row's 32 int8 values (two 16-byte loads per row from the activation planes, shared
@@ -20,8 +20,6 @@
 
 namespace lb {
 namespace iq {
-
-constexpr int WARPS = 8;
 
 // Four grid bytes with the signs of bits 0..3 of `s4` (0..15) applied, as four int8 values. The multiplication puts
 // sign bit j into the top bit of byte j (the other product bits land elsewhere), the byte-permute in its
@@ -86,7 +84,7 @@ __device__ __forceinline__ void unpack32(const uint8_t *b, int ib, const uint8_t
     sc1 = xmul(xmul(d, xadd(0.5f, (float)s1)), F);
 }
 
-template <int FMT, int M, int ROWS>
+template <int FMT, int M, int ROWS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) qgemv_iq_kernel(GemvArgs p, const uint8_t *__restrict__ grid_global) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ __align__(16) uint8_t grid[iq_grid_bytes(FMT)];
@@ -165,9 +163,9 @@ __global__ void __launch_bounds__(WARPS * 32) qgemv_iq_kernel(GemvArgs p, const 
     }
 }
 
-template <int FMT, int M, int ROWS> static cudaError_t launch_r(const GemvArgs &a, const uint8_t *grid, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
+template <int FMT, int M, int ROWS, int WARPS> static cudaError_t launch_r(const GemvArgs &a, const uint8_t *grid, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
     const uint32_t want = (a.n + WARPS * ROWS - 1) / (WARPS * ROWS);
-    uint32_t cap = (uint32_t)sm_count * 8;
+    uint32_t cap = (uint32_t)sm_count * 8 * (8 / WARPS);
     if (pairs > 1) cap = cap / pairs > 0 ? cap / pairs : 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(want < cap ? want : cap, pairs);
@@ -178,16 +176,18 @@ template <int FMT, int M, int ROWS> static cudaError_t launch_r(const GemvArgs &
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, qgemv_iq_kernel<FMT, M, ROWS>, a, grid);
+    return cudaLaunchKernelEx(&cfg, qgemv_iq_kernel<FMT, M, ROWS, WARPS>, a, grid);
 }
 
-// Two weight rows per warp share the activation loads; one row per warp where that would leave SMs without work.
+// Two weight rows per warp share the activation loads and give the scheduler two independent decode chains: the
+// fastest form measured at every row count (four rows per warp need 128 registers and lose more to occupancy than
+// they save in loads). One row per warp where two would leave SMs short of CTAs.
+static int g_rows_per_warp = 0;  // 0: chosen per launch; 1, 2: forced (tests, sweeps)
 template <int FMT, int M> static cudaError_t launch_m(const GemvArgs &a, const uint8_t *grid, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
-    const uint64_t warps2 = ((uint64_t)a.n + 1) / 2 * pairs;
-    if constexpr (M <= 4) {
-        if (warps2 >= (uint64_t)sm_count * WARPS * 4) return launch_r<FMT, M, 2>(a, grid, pairs, sm_count, pdl, stream);
-    }
-    return launch_r<FMT, M, 1>(a, grid, pairs, sm_count, pdl, stream);
+    const uint64_t ctas2 = (uint64_t)((a.n + 7) / 8) * pairs;  // CTAs of four warps, two rows each
+    const int forced = g_rows_per_warp;
+    if (forced == 2 || (!forced && ctas2 >= (uint64_t)sm_count * 2)) return launch_r<FMT, M, 2, 4>(a, grid, pairs, sm_count, pdl, stream);
+    return launch_r<FMT, M, 1, 8>(a, grid, pairs, sm_count, pdl, stream);
 }
 
 template <int FMT> static cudaError_t launch_fmt(const GemvArgs &args, const uint8_t *grid, int sm_count, bool pdl, cudaStream_t stream) {
@@ -213,6 +213,8 @@ template <int FMT> static cudaError_t launch_fmt(const GemvArgs &args, const uin
 }
 
 }  // namespace iq
+
+void qgemv_iq_set_rows_per_warp(int rows) { iq::g_rows_per_warp = rows == 1 || rows == 2 ? rows : 0; }
 
 cudaError_t launch_qgemv_iq(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream) {
     if (args.n == 0 || args.rows == 0) return cudaSuccess;

@@ -65,7 +65,9 @@ def test_decode_matches_oracle_all_row_counts(be, oracle, fmt, name, m):
         a = O.normal(seed + 100, m * k)
         want, path = oracle.matmul(int(fmt), a, qb, n, k, m=m)
         assert path == "int8_act"
-        assert max_rel(run_matmul(be, fmt, a, qb, m, n, k), want) <= 2e-5
+        for rows in ("1", "2", "0"):      # one and two weight rows per warp, then the launch's own choice
+            be.set_option("gemv_iq_rows", rows)
+            assert max_rel(run_matmul(be, fmt, a, qb, m, n, k), want) <= 2e-5, (n, k, rows)
 
 
 @pytest.mark.parametrize("fmt,name", IQ)
