@@ -238,6 +238,28 @@ LAPID_B200_API lapid_b200_status lapid_b200_execute(lapid_b200_device *dev, cons
  * counterpart in the reference, whose execute always waits. */
 LAPID_B200_API lapid_b200_status lapid_b200_execute_async(lapid_b200_device *dev, const lapid_b200_launch *launches,
                                            size_t n_launches, lapid_b200_buffer *const *buffers, size_t n_buffers);
+
+/* One decode step with host buffers as ONE call: Backend::write of the step's inputs, Backend::execute and
+ * Backend::read of its results (backend.rs:36-58), pipelined. The launches run in consecutive chunks of
+ * `chunk_launches` (0: the library picks); every write is uploaded on a copy stream of its own just before the
+ * chunk that holds the launch it names (`launch`: the FIRST launch that reads what it brings), every read is
+ * downloaded on a second copy stream right after the chunk that holds the launch it names (`launch`: the LAST launch
+ * that writes what it takes), so that uploads, launches and downloads of different chunks overlap (the two copy
+ * engines and the SMs at the same time). The result is that of all writes, execute, all reads in that order; the
+ * call returns when everything has finished. Declarations are checked against the launches' views: a write whose
+ * memory an earlier chunk uses, or a read whose memory a later chunk writes, is `invalid_launch`. Host memory
+ * should be page-locked (pageable memory is staged by the driver and overlaps nothing). Not for use inside a
+ * stream capture. */
+typedef struct lapid_b200_io {
+    uint32_t buffer; /* index into the call's buffers */
+    uint32_t launch; /* index into the call's launches (see above) */
+    uint64_t offset; /* bytes from the start of the buffer */
+    void *host;      /* source of a write, destination of a read */
+    uint64_t bytes;
+} lapid_b200_io;
+LAPID_B200_API lapid_b200_status lapid_b200_execute_io(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n_launches,
+                                        lapid_b200_buffer *const *buffers, size_t n_buffers, const lapid_b200_io *writes, size_t n_writes,
+                                        const lapid_b200_io *reads, size_t n_reads, size_t chunk_launches);
 /* Number of kernels this library launched on `dev` since the last call. */
 LAPID_B200_API uint64_t lapid_b200_take_launch_count(lapid_b200_device *dev);
 /* Backend::take_profile (backend.rs:59-62; CUDA side crates/lapid-cuda/src/execute.rs:45-76): GPU time per kernel kind

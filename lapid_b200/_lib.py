@@ -42,6 +42,11 @@ class LaunchC(C.Structure):
     ]
 
 
+class IoC(C.Structure):
+    """lapid_b200_io: one host <-> device transfer of an execute_io call."""
+    _fields_ = [("buffer", C.c_uint32), ("launch", C.c_uint32), ("offset", C.c_uint64), ("host", C.c_void_p), ("bytes", C.c_uint64)]
+
+
 class ProfileEntryC(C.Structure):
     _fields_ = [("kind", C.c_char * 24), ("launches", C.c_uint64), ("ms", C.c_double)]
 
@@ -75,6 +80,8 @@ SYMBOLS = {
     "lapid_b200_prepare": (C.c_int32, [P, C.POINTER(LaunchC), C.c_size_t]),
     "lapid_b200_execute": (C.c_int32, [P, C.POINTER(LaunchC), C.c_size_t, C.POINTER(P), C.c_size_t]),
     "lapid_b200_execute_async": (C.c_int32, [P, C.POINTER(LaunchC), C.c_size_t, C.POINTER(P), C.c_size_t]),
+    "lapid_b200_execute_io": (C.c_int32, [P, C.POINTER(LaunchC), C.c_size_t, C.POINTER(P), C.c_size_t, C.POINTER(IoC), C.c_size_t,
+                                         C.POINTER(IoC), C.c_size_t, C.c_size_t]),
     "lapid_b200_take_launch_count": (C.c_uint64, [P]),
     "lapid_b200_take_profile": (C.c_int32, [P, C.POINTER(ProfileEntryC), C.c_size_t, C.POINTER(C.c_size_t)]),
     "lapid_b200_decode_trace_begin": (C.c_int32, [P, C.c_uint32]),

@@ -210,24 +210,24 @@ class Launch:
 def matmul_launch(b_dtype: DType, m: int, n: int, k: int, *, batch: int = 1, a_row_stride: Optional[int] = None,
                   inputs=(0, 1), output=2, bias_input: Optional[int] = None, out: Optional[MatView] = None,
                   a_quantized: bool = False, a_dtype: DType = DType.F32, expr: Optional[Expr] = None, extra_input: Optional[int] = None,
-                  extra_view: Optional[View] = None) -> Launch:
+                  extra_view: Optional[View] = None, a: Optional[MatView] = None) -> Launch:
     """The launch lapid lowers ``x.matmul_t(w)`` to: contiguous A (or padded rows), quantized
     transposed B, contiguous f32 output (the `mm` helper of kbench_tests.rs:86-107).
     ``a_quantized``: input 0 is the quantized operand a producer wrote for this launch (``Backend.act_layout``);
     ``a_dtype``: F32, F16 or BF16 activations (widened exactly to f32 as they are read, like lapid-cpu's ``load_contig``);
     ``expr``: an epilogue expression; when it loads extras[0], ``extra_input`` is that buffer and ``extra_view`` its view
-    over [batch, m, n] (default: a contiguous [m, n] array)."""
+    over [batch, m, n] (default: a contiguous [m, n] array); ``a``: the view of A inside its buffer (default: at the start)."""
     rs = a_row_stride if a_row_stride is not None else k
     if expr is not None:
         has = expr.reads_extra()
         spec = MatMulSpec(a_dtype=DType.ACT_Q8 if a_quantized else DType(a_dtype), b_dtype=DType(b_dtype), extra_dtypes=(DType.F32,) if has else (),
                           epilogue=Epilogue.EXPR, expr=expr)
-        dims = MatMulDims(batch, m, n, k, a=MatView(0, m * rs, rs), b=MatView(0, 0, k), out=out or MatView.contiguous(m, n),
+        dims = MatMulDims(batch, m, n, k, a=a or MatView(0, m * rs, rs), b=MatView(0, 0, k), out=out or MatView.contiguous(m, n),
                           extra_views=((extra_view or View(0, (m * n, n, 1)),) if has else ()))
         return Launch(spec, dims, tuple(inputs) + ((extra_input,) if has else ()), output)
     spec = MatMulSpec(a_dtype=DType.ACT_Q8 if a_quantized else DType(a_dtype), b_dtype=DType(b_dtype), extra_dtypes=(DType.F32,) if bias_input is not None else (),
                       epilogue=Epilogue.ADD if bias_input is not None else Epilogue.NONE)
-    dims = MatMulDims(batch, m, n, k, a=MatView(0, m * rs, rs), b=MatView(0, 0, k), out=out or MatView.contiguous(m, n),
+    dims = MatMulDims(batch, m, n, k, a=a or MatView(0, m * rs, rs), b=MatView(0, 0, k), out=out or MatView.contiguous(m, n),
                       extra_views=(View(0, (0, 0, 1)),) if bias_input is not None else ())
     ins = tuple(inputs) + ((bias_input,) if bias_input is not None else ())
     return Launch(spec, dims, ins, output)
@@ -372,6 +372,25 @@ class Backend:
     def execute_async(self, launches: Sequence[Launch], buffers: Sequence[Buffer]) -> None:
         arr, bufs = self._pack(launches, buffers)
         check(_lib.lib().lapid_b200_execute_async(self._h, arr, len(launches), bufs, len(buffers)))
+
+    def packed_io(self, launches: Sequence[Launch], buffers: Sequence[Buffer], writes: Sequence[tuple], reads: Sequence[tuple], chunk: int = 0):
+        """One step with host buffers as one pipelined call (``lapid_b200_execute_io``): ``writes`` and ``reads`` are
+        ``(buffer index, byte offset, host pointer, bytes, launch index)`` -- for a write the first launch that reads what
+        it brings, for a read the last launch that writes what it takes. The launches run in chunks of ``chunk`` (0: the
+        library picks); uploads, launches and downloads of different chunks overlap; the result is that of all writes,
+        ``execute``, all reads. Host memory should be page-locked. Returns a zero-argument callable (pre-marshalled)."""
+        arr, bufs = self._pack(launches, buffers)
+        mk = lambda ios: (_lib.IoC * max(1, len(ios)))(*[_lib.IoC(int(b), int(l), int(off), C.c_void_p(int(h)), int(nb)) for (b, off, h, nb, l) in ios])
+        w, r = mk(writes), mk(reads)
+        fn, hd, n, nb_, nw, nr = _lib.lib().lapid_b200_execute_io, self._h, len(launches), len(buffers), len(writes), len(reads)
+
+        def run():
+            check(fn(hd, arr, n, bufs, nb_, w, nw, r, nr, chunk))
+        run.keep = (arr, bufs, w, r, list(buffers))
+        return run
+
+    def execute_io(self, launches: Sequence[Launch], buffers: Sequence[Buffer], writes: Sequence[tuple], reads: Sequence[tuple], chunk: int = 0) -> None:
+        self.packed_io(launches, buffers, writes, reads, chunk)()
 
     def packed(self, launches: Sequence[Launch], buffers: Sequence[Buffer]):
         """Pre-marshalled launch arrays for hot loops: returns a zero-argument callable that

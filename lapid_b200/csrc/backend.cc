@@ -166,6 +166,9 @@ struct lapid_b200_device {
     std::string name;
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
+    // execute_io: the copy streams (one per direction: the two copy engines run at the same time) and one event per chunk
+    cudaStream_t io_in = nullptr, io_out = nullptr;
+    std::vector<cudaEvent_t> io_events;
     std::mutex mu;  // serialises launches, like lapid-cuda's mutex-guarded Exec
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
@@ -210,6 +213,9 @@ struct lapid_b200_device {
             if (stream_ws.pairs) cudaFree(stream_ws.pairs);
             if (status_host) cudaFreeHost(status_host);
             for (cudaEvent_t e : profile_events) cudaEventDestroy(e);
+            for (cudaEvent_t e : io_events) cudaEventDestroy(e);
+            if (io_in) cudaStreamDestroy(io_in);
+            if (io_out) cudaStreamDestroy(io_out);
             if (own_stream) cudaStreamDestroy(own_stream);
         }
     }
@@ -989,13 +995,9 @@ void check_status_word(lapid_b200_device *dev) {
     fail("backend", "a device-side wait gave up (status " + std::to_string(st) + "); the results of this call are invalid");
 }
 
-void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n, lapid_b200_buffer *const *buffers,
-                  size_t nbuf, bool wait) {
-    need(dev);
-    if (n && !launches) fail("invalid_argument", "launches is NULL");
-    if (nbuf && !buffers) fail("invalid_argument", "buffers is NULL");
-    std::lock_guard<std::mutex> lock(dev->mu);
-    dev->make_current();
+// (the caller holds dev->mu and has made the device current)
+void execute_locked(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n, lapid_b200_buffer *const *buffers,
+                    size_t nbuf, bool wait) {
     // Plan the activation pre-passes of the decode launches of this list:
     //  * launches that read the same A operand (q/k/v, gate/up) share one quantized copy, as long
     //    as no launch in between writes the buffer it comes from;
@@ -1182,6 +1184,160 @@ void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, siz
             }
         check_status_word(dev);
     }
+}
+
+void execute_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n, lapid_b200_buffer *const *buffers,
+                  size_t nbuf, bool wait) {
+    need(dev);
+    if (n && !launches) fail("invalid_argument", "launches is NULL");
+    if (nbuf && !buffers) fail("invalid_argument", "buffers is NULL");
+    std::lock_guard<std::mutex> lock(dev->mu);
+    dev->make_current();
+    execute_locked(dev, launches, n, buffers, nbuf, wait);
+}
+
+// Byte range of buffer `b` that launch `l` reads as its A operand / gather ids / x (`in`) or writes (`!in`);
+// false when the launch does not touch the buffer that way. Conservative: whole buffers for the launch kinds whose
+// views are not simple matrices.
+bool launch_range(const lapid_b200_launch &l, uint32_t b, bool in, uint64_t buf_bytes, uint64_t &lo, uint64_t &hi) {
+    auto span = [&](const lapid_b200_matview &v, uint64_t width, uint64_t elem) {
+        const uint64_t batch = l.batch ? l.batch : 1, m = l.m ? l.m : 1;
+        lo = v.offset * elem;
+        hi = (v.offset + (batch - 1) * v.batch_stride + (m - 1) * v.row_stride + width) * elem;
+    };
+    if (in) {
+        bool hit = false;
+        for (int i = 0; i < l.n_inputs && i < 3; i++) hit = hit || l.inputs[i] == b;
+        if (!hit) return false;
+        lo = 0, hi = buf_bytes;
+        if (l.kind == LAPID_B200_KERNEL_MATMUL && l.n_inputs >= 1 && l.inputs[0] == b && (l.n_inputs < 2 || l.inputs[1] != b) &&
+            (l.n_inputs < 3 || l.inputs[2] != b) && is_act_float(l.a_dtype))
+            span(l.a, l.k, act_elem_size(l.a_dtype));
+        return true;
+    }
+    if (l.output != b) return false;
+    lo = 0, hi = buf_bytes;
+    if (l.kind == LAPID_B200_KERNEL_MATMUL) span(l.out, l.n, 4);
+    return true;
+}
+
+// write + execute + read of one step as one pipelined call (see the header).
+void execute_io_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n, lapid_b200_buffer *const *buffers, size_t nbuf,
+                     const lapid_b200_io *writes, size_t n_writes, const lapid_b200_io *reads, size_t n_reads, size_t chunk) {
+    need(dev);
+    if (n && !launches) fail("invalid_argument", "launches is NULL");
+    if (nbuf && !buffers) fail("invalid_argument", "buffers is NULL");
+    if ((n_writes && !writes) || (n_reads && !reads)) fail("invalid_argument", "writes or reads is NULL");
+    if (chunk == 0) chunk = n > 8 ? (n + 3) / 4 : (n > 1 ? (n + 1) / 2 : 1);
+    const size_t n_chunks = n ? (n + chunk - 1) / chunk : 0;
+    auto check_io = [&](const lapid_b200_io &io, const char *what) {
+        if (io.buffer >= nbuf || !buffers[io.buffer])
+            fail("invalid_launch", std::string("execute_io: ") + what + " names buffer " + std::to_string(io.buffer) + " of " + std::to_string(nbuf));
+        if (buffers[io.buffer]->dev != dev) fail("wrong_backend", std::string("execute_io: ") + what + " buffer belongs to another device");
+        if (io.bytes && !io.host) fail("invalid_argument", std::string("execute_io: ") + what + " host pointer is NULL");
+        if (io.offset > buffers[io.buffer]->bytes || io.bytes > buffers[io.buffer]->bytes - io.offset)
+            fail("out_of_bounds", std::string("execute_io: ") + what + " of " + std::to_string(io.bytes) + " bytes at " + std::to_string(io.offset) +
+                                      " in a buffer of " + std::to_string(buffers[io.buffer]->bytes));
+        if (n && io.launch >= n) fail("invalid_launch", std::string("execute_io: ") + what + " names launch " + std::to_string(io.launch) + " of " + std::to_string(n));
+    };
+    // A write is uploaded just before the chunk of the launch it names: no launch of an earlier chunk may read or
+    // write what it brings. A read is downloaded right after the chunk of the launch it names: no launch of a
+    // later chunk may write what it takes.
+    for (size_t i = 0; i < n_writes; i++) {
+        check_io(writes[i], "write");
+        for (size_t j = 0; n && j < (writes[i].launch / chunk) * chunk; j++) {
+            uint64_t lo, hi;
+            for (int in = 0; in < 2; in++)
+                if (launch_range(launches[j], writes[i].buffer, in != 0, buffers[writes[i].buffer]->bytes, lo, hi) && lo < writes[i].offset + writes[i].bytes &&
+                    writes[i].offset < hi)
+                    fail("invalid_launch", "execute_io: write " + std::to_string(i) + " is tied to launch " + std::to_string(writes[i].launch) +
+                                               " but launch " + std::to_string(j) + " of an earlier chunk uses that memory");
+        }
+    }
+    for (size_t i = 0; i < n_reads; i++) {
+        check_io(reads[i], "read");
+        for (size_t j = (reads[i].launch / chunk + 1) * chunk; j < n; j++) {
+            uint64_t lo, hi;
+            if (launch_range(launches[j], reads[i].buffer, false, buffers[reads[i].buffer]->bytes, lo, hi) && lo < reads[i].offset + reads[i].bytes &&
+                reads[i].offset < hi)
+                fail("invalid_launch", "execute_io: read " + std::to_string(i) + " is tied to launch " + std::to_string(reads[i].launch) +
+                                           " but launch " + std::to_string(j) + " of a later chunk writes that memory");
+        }
+    }
+    std::lock_guard<std::mutex> lock(dev->mu);
+    dev->make_current();
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(dev->stream, &capturing);
+    if (capturing != cudaStreamCaptureStatusNone) fail("invalid_launch", "execute_io waits for its copies: not inside a stream capture");
+    if (!dev->io_in) cuda_check(cudaStreamCreateWithFlags(&dev->io_in, cudaStreamNonBlocking), "cudaStreamCreate");
+    if (!dev->io_out) cuda_check(cudaStreamCreateWithFlags(&dev->io_out, cudaStreamNonBlocking), "cudaStreamCreate");
+    while (dev->io_events.size() < 2 * n_chunks + 1) {
+        cudaEvent_t e;
+        cuda_check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+        dev->io_events.push_back(e);
+    }
+    // the copies start behind whatever is already queued on the device's stream
+    cudaEvent_t start = dev->io_events[2 * n_chunks];
+    cuda_check(cudaEventRecord(start, dev->stream), "cudaEventRecord");
+    cuda_check(cudaStreamWaitEvent(dev->io_in, start, 0), "cudaStreamWaitEvent");
+    cuda_check(cudaStreamWaitEvent(dev->io_out, start, 0), "cudaStreamWaitEvent");
+    auto finish = [&]() {  // leave nothing in flight, whatever happened
+        cudaStreamSynchronize(dev->io_in);
+        cudaStreamSynchronize(dev->stream);
+        cudaStreamSynchronize(dev->io_out);
+    };
+    try {
+        // Transfers of one chunk that continue each other in the buffer and in host memory go as one copy (a copy
+        // costs microseconds of host time to queue, whatever its size).
+        auto copies_of = [&](const lapid_b200_io *ios, size_t count, size_t c) {
+            std::vector<lapid_b200_io> v;
+            for (size_t i = 0; i < count; i++)
+                if ((n ? ios[i].launch / chunk : 0) == c && ios[i].bytes) v.push_back(ios[i]);
+            std::sort(v.begin(), v.end(), [](const lapid_b200_io &a, const lapid_b200_io &b) {
+                return a.buffer != b.buffer ? a.buffer < b.buffer : a.offset < b.offset;
+            });
+            std::vector<lapid_b200_io> out;
+            for (const lapid_b200_io &io : v) {
+                if (!out.empty() && out.back().buffer == io.buffer && out.back().offset + out.back().bytes == io.offset &&
+                    (char *)out.back().host + out.back().bytes == (char *)io.host)
+                    out.back().bytes += io.bytes;
+                else
+                    out.push_back(io);
+            }
+            return out;
+        };
+        // all uploads are queued now, in chunk order: chunk c + 1 arrives while chunk c computes
+        for (size_t c = 0; c < (n_chunks ? n_chunks : 1); c++) {
+            for (const lapid_b200_io &w : copies_of(writes, n_writes, c))
+                cuda_check(cudaMemcpyAsync((char *)buffers[w.buffer]->ptr + w.offset, w.host, w.bytes, cudaMemcpyHostToDevice, dev->io_in),
+                           "execute_io upload");
+            if (n_chunks) cuda_check(cudaEventRecord(dev->io_events[2 * c], dev->io_in), "cudaEventRecord");
+        }
+        for (size_t c = 0; c < n_chunks; c++) {
+            const size_t first = c * chunk, count = first + chunk <= n ? chunk : n - first;
+            cuda_check(cudaStreamWaitEvent(dev->stream, dev->io_events[2 * c], 0), "cudaStreamWaitEvent");
+            execute_locked(dev, launches + first, count, buffers, nbuf, false);
+            cuda_check(cudaEventRecord(dev->io_events[2 * c + 1], dev->stream), "cudaEventRecord");
+            cuda_check(cudaStreamWaitEvent(dev->io_out, dev->io_events[2 * c + 1], 0), "cudaStreamWaitEvent");
+            for (const lapid_b200_io &r : copies_of(reads, n_reads, c))
+                cuda_check(cudaMemcpyAsync(r.host, (const char *)buffers[r.buffer]->ptr + r.offset, r.bytes, cudaMemcpyDeviceToHost, dev->io_out),
+                           "execute_io download");
+        }
+        if (!n_chunks) {  // no launches: the writes, then the reads
+            cuda_check(cudaStreamSynchronize(dev->io_in), "execute_io");
+            for (size_t i = 0; i < n_reads; i++)
+                if (reads[i].bytes)
+                    cuda_check(cudaMemcpyAsync(reads[i].host, (const char *)buffers[reads[i].buffer]->ptr + reads[i].offset, reads[i].bytes,
+                                               cudaMemcpyDeviceToHost, dev->io_out), "execute_io download");
+        }
+    } catch (...) {
+        finish();
+        throw;
+    }
+    cuda_check(cudaStreamSynchronize(dev->io_in), "execute_io");
+    cuda_check(cudaStreamSynchronize(dev->stream), "execute_io");
+    cuda_check(cudaStreamSynchronize(dev->io_out), "execute_io");
+    check_status_word(dev);
 }
 
 }  // namespace
@@ -1467,6 +1623,12 @@ lapid_b200_status lapid_b200_execute(lapid_b200_device *dev, const lapid_b200_la
 lapid_b200_status lapid_b200_execute_async(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n,
                                            lapid_b200_buffer *const *buffers, size_t nbuf) {
     return guard([&] { execute_impl(dev, launches, n, buffers, nbuf, false); });
+}
+
+lapid_b200_status lapid_b200_execute_io(lapid_b200_device *dev, const lapid_b200_launch *launches, size_t n, lapid_b200_buffer *const *buffers,
+                                        size_t nbuf, const lapid_b200_io *writes, size_t n_writes, const lapid_b200_io *reads, size_t n_reads,
+                                        size_t chunk) {
+    return guard([&] { execute_io_impl(dev, launches, n, buffers, nbuf, writes, n_writes, reads, n_reads, chunk); });
 }
 
 uint64_t lapid_b200_take_launch_count(lapid_b200_device *dev) { return dev ? dev->launches.exchange(0) : 0; }

@@ -96,6 +96,7 @@ def test_launch_marshalling_matches_header_struct():
     assert list(c.inputs) == [0, 1, 3] and c.output == 2 and list(c.extra.strides) == [0, 0, 1]
     # struct size as a C compiler lays it out: 8 int32 + 4 u64 + 3*3 u64 + (u64 + 3 i64) + 4 u32 + (1 + 24) u32, padded to 8
     assert C.sizeof(_lib.LaunchC) == 32 + 32 + 72 + 32 + 16 + 104
+    assert C.sizeof(_lib.IoC) == 32 and _lib.IoC.host.offset == 16   # lapid_b200_io: u32 buffer, u32 launch, u64 offset, void *host, u64 bytes
     # an epilogue expression: postfix words, Load(1) makes the extra the third input
     e = lp.backend.Expr.silu(lp.backend.Expr.load(0)) * lp.backend.Expr.load(1)
     c = lp.backend.matmul_launch(lp.DType.Q4K, 2, 64, 256, expr=e, extra_input=5).to_c()

@@ -1291,3 +1291,64 @@ def test_take_profile(be, oracle):
         be.set_option("profile", "0")
     want, _ = oracle.matmul(O.Q4_K, a1, qb, n, k, m=1)
     assert max_rel(bufs[2].download().view(np.float32), want) <= 2e-5
+
+
+def test_execute_io_pipelines_a_step_with_host_buffers(be, oracle):
+    """`lapid_b200_execute_io`: Backend::write, execute and read of a step (crates/lapid-compiler/src/backend.rs:36-58)
+    as one call whose uploads, launches and downloads overlap by chunks. Same results as the three calls one after
+    the other, for every chunk size; launches of a later chunk read what an earlier chunk wrote; misdeclared
+    transfers are refused."""
+    import torch
+    from lapid_b200.backend import matmul_launch
+    k = 2048
+    shapes = [(1, 96), (2, 130), (4, 77), (8, 2500), (3, 33), (8, 512), (40, 200), (1, 64)]
+    a_off = np.cumsum([0] + [m * k for m, _ in shapes])
+    o_off = np.cumsum([0] + [m * n for m, n in shapes])
+    h_in = torch.randn(int(a_off[-1])).pin_memory()
+    h_out = torch.zeros(int(o_off[-1]) + 8 * 64).pin_memory()
+    weights = [oracle.quantize(O.Q4_K, O.normal(1700 + i, n * k, 0.05), n, k) for i, (m, n) in enumerate(shapes)]
+    w_chain = oracle.quantize(O.Q4_K, O.normal(1750, 64 * shapes[5][1], 0.05), 64, shapes[5][1])   # reads launch 5's output (8 x 512)
+    bufs = [be.alloc(int(a_off[-1]) * 4), be.alloc(int(o_off[-1]) * 4)] + [be.upload(w) for w in weights] + [be.upload(w_chain), be.alloc(8 * 64 * 4)]
+    launches = [matmul_launch(lp.DType.Q4K, m, n, k, inputs=(0, 2 + i), output=1, a=MatView(int(a_off[i]), m * k, k), out=MatView(int(o_off[i]), m * n, n))
+                for i, (m, n) in enumerate(shapes)]
+    chain = len(launches)
+    launches.append(matmul_launch(lp.DType.Q4K, 8, 64, shapes[5][1], inputs=(1, 2 + len(shapes)), output=3 + len(shapes),
+                                  a=MatView(int(o_off[5]), 8 * 512, 512)))
+    writes = [(0, int(a_off[i]) * 4, h_in.data_ptr() + int(a_off[i]) * 4, shapes[i][0] * k * 4, i) for i in range(len(shapes))]
+    reads = [(1, int(o_off[i]) * 4, h_out.data_ptr() + int(o_off[i]) * 4, shapes[i][0] * shapes[i][1] * 4, i) for i in range(len(shapes))]
+    reads.append((3 + len(shapes), 0, h_out.data_ptr() + int(o_off[-1]) * 4, 8 * 64 * 4, chain))
+    # the three calls one after the other
+    be.write_ptr(bufs[0], 0, h_in.data_ptr(), int(a_off[-1]) * 4)
+    be.execute(launches, bufs)
+    want = np.concatenate([bufs[1].download().view(np.float32), bufs[3 + len(shapes)].download().view(np.float32)[:8 * 64]])
+    for i, (m, n) in enumerate(shapes):   # (and those against the oracle)
+        ref, _ = oracle.matmul(O.Q4_K, h_in.numpy()[a_off[i]:a_off[i + 1]], weights[i], n, k, m=m)
+        tc = m > 8
+        assert max_rel(want[o_off[i]:o_off[i + 1]], ref) <= (2e-2 if tc else 2e-5)
+    for chunk in (0, 1, 2, 3, 4, len(launches), 100):
+        bufs[0].write(0, np.zeros(int(a_off[-1]), np.float32))
+        bufs[1].write(0, np.zeros(int(o_off[-1]), np.float32))
+        h_out.zero_()
+        be.execute_io(launches, bufs, writes, reads, chunk)
+        # (which decode launches share a kernel depends on the chunk: the order of some f32 partial sums with it)
+        assert max_rel(h_out.numpy()[:want.size], want) <= 2e-6, chunk
+    # a write tied to launch 6 whose memory launch 1 (an earlier chunk) reads; a read tied to launch 0 of memory that launch 7 writes
+    bad_w = writes[:1] + [(0, int(a_off[1]) * 4, h_in.data_ptr(), 64, 6)]
+    with pytest.raises(lp.LapidError) as err:
+        be.execute_io(launches, bufs, bad_w, reads, 2)
+    assert err.value.code == "invalid_launch"
+    bad_r = [(1, int(o_off[7]) * 4, h_out.data_ptr(), 64, 0)]
+    with pytest.raises(lp.LapidError) as err:
+        be.execute_io(launches, bufs, writes, bad_r, 2)
+    assert err.value.code == "invalid_launch"
+    with pytest.raises(lp.LapidError) as err:
+        be.execute_io(launches, bufs, [(0, bufs[0].nbytes - 8, h_in.data_ptr(), 64, 0)], reads, 2)
+    assert err.value.code == "out_of_bounds"
+    with pytest.raises(lp.LapidError) as err:
+        be.execute_io(launches, bufs, [(0, 0, h_in.data_ptr(), 64, len(launches))], reads, 2)
+    assert err.value.code == "invalid_launch"
+    be.execute_io([], bufs, writes[:1], [(0, 0, h_out.data_ptr(), 64, 0)], 0)       # no launches: the writes, then the reads
+    assert np.array_equal(h_out.numpy()[:16], h_in.numpy()[:16])
+    h_out.zero_()
+    be.execute_io(launches, bufs, writes, reads, 0)                                  # and the device still works
+    assert max_rel(h_out.numpy()[:want.size], want) <= 2e-6
