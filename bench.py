@@ -507,10 +507,11 @@ def gemv_kernel_name(fmt: int, m: int, n: int = 0, k: int = 0) -> str:
         if m >= 2:
             return "qgemv_kq_stream_kernel<q4_k>" if units >= 2 * 148 else "qgemv_q4k_mma_kernel"
         return "qgemv_kq_fast_kernel<q4_k>"
+    small = m <= 4 and n * k <= (6 << 20)   # small matrices at three and four rows stay on the dp4a kernel
     if fmt == 8:
-        return "qgemv_q6k_mma_kernel" if m >= 3 else "qgemv_kq_fast_kernel<q6_k>"
+        return "qgemv_q6k_mma_kernel" if m >= 3 and not small else "qgemv_kq_fast_kernel<q6_k>"
     if fmt == 7:
-        return "qgemv_kq_stream_kernel<q5_k>" if m >= 3 else "qgemv_kq_fast_kernel<q5_k>"
+        return "qgemv_kq_stream_kernel<q5_k>" if m >= 3 and not small else "qgemv_kq_fast_kernel<q5_k>"
     if fmt == 5:
         return "qgemv_i4_mma_kernel" if m >= 2 else "qgemv_i4_kernel"
     return "qgemv_i8_mma_kernel" if m >= 2 else "qgemv_i8_fast_kernel"

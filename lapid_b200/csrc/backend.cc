@@ -197,6 +197,7 @@ struct lapid_b200_device {
     // balanced-stream tensor-core decode kernel (qgemv_kq_stream.cu): 0 never; 1 (default) Q5_K always and Q4_K where
     // it is the faster one (launch_qgemv_q4k_mma decides); 2 both formats always
     int gemv_stream = 1;
+    bool small_dp4a = true;  // small Q5_K / Q6_K matrices at 3 and 4 rows on the dp4a kernel (see plan_launch)
     bool two_row_dp4a = false;    // two early Q4_K rows on the dp4a kernel (see execute_impl)
     lb::StreamWs stream_ws{};    // workspace of that kernel: partial sums in flight between CTAs (all zero between launches)
     bool gemm_f32 = false;  // true: rows > gemv_max_rows always take the exact-f32 GEMM instead of the tensor cores
@@ -473,6 +474,14 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
                  (l.b_dtype == LAPID_B200_DTYPE_Q6_K && p.rows > dev.gemv_mma_rows && lb::qgemv_q6k_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
                  (l.b_dtype == LAPID_B200_DTYPE_INT8 && p.rows >= dev.gemv_mma_rows && lb::qgemv_i8_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
                  (l.b_dtype == LAPID_B200_DTYPE_INT4 && p.rows >= dev.gemv_mma_rows && lb::qgemv_i4_mma_shape_ok(p.rows, (uint32_t)l.k)));
+        // Small Q5_K / Q6_K matrices at three and four rows: their tensor-core kernels cost about 5 us whatever the size
+        // (1024 x 4096: 5.0-5.5 us), the dp4a kernel 3.8-4.6 us; from five rows on, and from 4096 x 4096 on, the
+        // tensor-core kernels win.
+        if (p.fast && p.rows <= 4 && (uint64_t)l.n * l.k <= (6ull << 20) &&
+            (l.b_dtype == LAPID_B200_DTYPE_Q5_K || l.b_dtype == LAPID_B200_DTYPE_Q6_K) && dev.small_dp4a) {
+            p.stream = false;
+            p.mma = false;
+        }
         if (p.mma) {
             size_t tiles = align_up(lb::qgemv_q4k_mma_act_bytes(p.rows, (uint32_t)l.k), 256);
             if (tiles > p.scratch) p.scratch = tiles;
@@ -1474,6 +1483,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             int r = std::atoi(value);
             if (r < 0 || r > 2) fail("invalid_argument", "gemv_stream must be 0 (never), 1 (Q5_K) or 2 (Q4_K and Q5_K)");
             dev->gemv_stream = r;
+        } else if (k == "gemv_small_dp4a") {
+            dev->small_dp4a = std::atoi(value) != 0;
         } else if (k == "gemv_stream_config") {
             lb::qgemv_kq_stream_set_config(std::atoi(value));
         } else if (k == "gemv_stream_ctas") {

@@ -28,7 +28,11 @@ GROUP32 = PLANES + (lp.DType.MXFP4,)      # formats whose K only has to be a mul
 
 @pytest.fixture(scope="module")
 def be():
-    return lp.Backend(0)
+    b = lp.Backend(0)
+    # the tests of the tensor-core decode kernels use small matrices: keep those on the tensor-core kernels (the
+    # default routing of small Q5_K / Q6_K launches has a test of its own)
+    b.set_option("gemv_small_dp4a", "0")
+    return b
 
 
 def max_rel(got, ref):
@@ -1352,3 +1356,21 @@ def test_execute_io_pipelines_a_step_with_host_buffers(be, oracle):
     h_out.zero_()
     be.execute_io(launches, bufs, writes, reads, 0)                                  # and the device still works
     assert max_rel(h_out.numpy()[:want.size], want) <= 2e-6
+
+
+@pytest.mark.parametrize("fmt,ofmt", [(lp.DType.Q5K, O.Q5_K), (lp.DType.Q6K, O.Q6_K)])
+def test_small_matrices_at_three_and_four_rows_take_the_dp4a_kernel(oracle, fmt, ofmt):
+    """Default routing: a Q5_K / Q6_K launch over at most 6 M weights with three or four rows runs on the dp4a kernel
+    (its result is bit-identical to the run with the tensor-core kernels switched off), five rows and larger matrices
+    on the tensor-core kernels; all of them agree with the oracle."""
+    be = lp.Backend(0)
+    for (m, n, k, dp4a) in [(3, 1024, 4096, True), (4, 1024, 4096, True), (5, 1024, 4096, False), (4, 1536, 4096, True), (4, 4096, 4096, False)]:
+        qb = oracle.quantize(ofmt, O.normal(1800 + m, n * k, 0.05), n, k)
+        a = O.normal(1810 + m, m * k)
+        want, _ = oracle.matmul(ofmt, a, qb, n, k, m=m)
+        got = run_matmul(be, fmt, a, qb, m, n, k)
+        assert max_rel(got, want) <= 2e-5, (m, n, k)
+        be.set_option("gemv_mma_rows", "0")
+        plain = run_matmul(be, fmt, a, qb, m, n, k)
+        be.set_option("gemv_mma_rows", "2")
+        assert np.array_equal(got, plain) == dp4a, (m, n, k)
