@@ -1508,6 +1508,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             lb::qgemv_q4k_mma_set_config(std::atoi(value));
         } else if (k == "gemv_q6k_mma_config") {
             lb::qgemv_q6k_mma_set_config(std::atoi(value));
+        } else if (k == "gemv_mxfp4_staged") {
+            lb::qgemv_mxfp4_set_staged(std::atoi(value));
         } else if (k == "gemv_iq_rows") {  // weight rows per warp of the i-quant decode kernel: 1, 2 (0: per launch)
             lb::qgemv_iq_set_rows_per_warp(std::atoi(value));
         } else if (k == "gemv_ctas_per_sm") {

@@ -10,8 +10,12 @@
 // nibble becomes its KV magnitude with one byte-permute (the eight magnitudes 0,1,2,3,4,6,8,12 are a two-register
 // table and the three low bits of four nibbles the selector); the sign bits split the four magnitudes into a
 // positive and a negative word, each multiplied with `dp4a` against the activation planes (served by L1/L2).
-// A straightforward streaming kernel: the format is outside the benchmark's configurations and has no
-// bulk-copy or tensor-core variant yet.
+// Two forms. When a weight row is a multiple of 16 bytes (K a multiple of 512) every warp streams its rows through a
+// shared-memory double buffer with 16-byte `cp.async` copies: the copy of the next row is in flight while the current
+// one is multiplied (one and two activation rows, K up to 8192: 4096 x 4096 at one row 7.6 against 9.2 us, 14336 x 4096
+// 15.8 against 17.2 us). Other launches read the blocks straight from global memory. Either way the kernel is bound
+// by the instructions that unpack a block (some 120 per 32 weights at one row), not by HBM (0.2-0.3 of its rate);
+// no tensor-core variant yet: from about four rows on the `dp4a` work per weight dominates.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -30,6 +34,42 @@ __device__ __forceinline__ void kv_split(uint32_t n, uint32_t &pos, uint32_t &ne
     const uint32_t s = ((n >> 3) & 0x01010101u) * 0xFFu;  // 0xFF in the bytes whose code has the sign bit
     pos = mag & ~s;
     neg = mag & s;
+}
+
+// One 17-byte block at `b` (global or shared memory, any alignment) against activation group g of every row.
+template <int M> __device__ __forceinline__ void block_dot(const uint8_t *b, const GemvArgs &p, uint32_t g, uint32_t k, uint32_t kg, float (&acc)[M]) {
+    const float d = e8m0_half(*b);
+    // the 16 nibble bytes b[1..16] from the aligned words around them
+    const uintptr_t q0 = (uintptr_t)(b + 1);
+    const uint32_t *wp = (const uint32_t *)(q0 & ~(uintptr_t)3);
+    const uint32_t sh = (uint32_t)(q0 & 3) * 8;
+    uint32_t raw[5];
+#pragma unroll
+    for (int i = 0; i < 4; i++) raw[i] = wp[i];
+    raw[4] = sh ? wp[4] : 0u;  // (aligned blocks end with the fourth word: nothing is read behind them)
+    uint32_t lp[4], ln[4], hp[4], hn[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t w = __funnelshift_r(raw[i], raw[i + 1], sh);
+        kv_split(w & 0x0F0F0F0Fu, lp[i], ln[i]);         // elements 4i .. 4i + 3
+        kv_split((w >> 4) & 0x0F0F0F0Fu, hp[i], hn[i]);  // elements 16 + 4i ..
+    }
+#pragma unroll
+    for (int r = 0; r < M; r++) {
+        const uint4 *ap = (const uint4 *)(p.qa + (uint64_t)r * k + (uint64_t)g * GROUP);
+        const uint4 a0 = __ldg(ap), a1 = __ldg(ap + 1);
+        const float da = __ldg(p.da + (uint64_t)r * kg + g);
+        const uint32_t al[4] = {a0.x, a0.y, a0.z, a0.w}, ah[4] = {a1.x, a1.y, a1.z, a1.w};
+        int dp = 0, dn = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            dp = __dp4a((int)lp[i], (int)al[i], dp);
+            dn = __dp4a((int)ln[i], (int)al[i], dn);
+            dp = __dp4a((int)hp[i], (int)ah[i], dp);
+            dn = __dp4a((int)hn[i], (int)ah[i], dn);
+        }
+        acc[r] = fmaf(d * da, (float)(dp - dn), acc[r]);
+    }
 }
 
 template <int M> __global__ void __launch_bounds__(WARPS * 32) qgemv_mxfp4_kernel(GemvArgs p) {
@@ -53,41 +93,7 @@ template <int M> __global__ void __launch_bounds__(WARPS * 32) qgemv_mxfp4_kerne
 #pragma unroll
         for (int r = 0; r < M; r++) acc[r] = 0.0f;
         const uint8_t *wrow = p.w + (uint64_t)row * kg * MXFP4_BYTES;
-        for (uint32_t g = lane; g < kg; g += 32) {
-            const uint8_t *b = wrow + (uint64_t)g * MXFP4_BYTES;
-            const float d = e8m0_half(__ldg(b));
-            // the 16 nibble bytes b[1..16] from the aligned words around them
-            const uintptr_t q0 = (uintptr_t)(b + 1);
-            const uint32_t *wp = (const uint32_t *)(q0 & ~(uintptr_t)3);
-            const uint32_t sh = (uint32_t)(q0 & 3) * 8;
-            uint32_t raw[5];
-#pragma unroll
-            for (int i = 0; i < 4; i++) raw[i] = __ldg(wp + i);
-            raw[4] = sh ? __ldg(wp + 4) : 0u;  // (aligned blocks end with the fourth word: nothing is read behind them)
-            uint32_t lp[4], ln[4], hp[4], hn[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint32_t w = __funnelshift_r(raw[i], raw[i + 1], sh);
-                kv_split(w & 0x0F0F0F0Fu, lp[i], ln[i]);         // elements 4i .. 4i + 3
-                kv_split((w >> 4) & 0x0F0F0F0Fu, hp[i], hn[i]);  // elements 16 + 4i ..
-            }
-#pragma unroll
-            for (int r = 0; r < M; r++) {
-                const uint4 *ap = (const uint4 *)(p.qa + (uint64_t)r * k + (uint64_t)g * GROUP);
-                const uint4 a0 = __ldg(ap), a1 = __ldg(ap + 1);
-                const float da = __ldg(p.da + (uint64_t)r * kg + g);
-                const uint32_t al[4] = {a0.x, a0.y, a0.z, a0.w}, ah[4] = {a1.x, a1.y, a1.z, a1.w};
-                int dp = 0, dn = 0;
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    dp = __dp4a((int)lp[i], (int)al[i], dp);
-                    dn = __dp4a((int)ln[i], (int)al[i], dn);
-                    dp = __dp4a((int)hp[i], (int)ah[i], dp);
-                    dn = __dp4a((int)hn[i], (int)ah[i], dn);
-                }
-                acc[r] = fmaf(d * da, (float)(dp - dn), acc[r]);
-            }
-        }
+        for (uint32_t g = lane; g < kg; g += 32) block_dot<M>(wrow + (uint64_t)g * MXFP4_BYTES, p, g, k, kg, acc);
 #pragma unroll
         for (int r = 0; r < M; r++) {
             float v = acc[r];
@@ -102,6 +108,68 @@ template <int M> __global__ void __launch_bounds__(WARPS * 32) qgemv_mxfp4_kerne
     }
 }
 
+// K a multiple of 512 (weight rows are multiples of 16 bytes): the same arithmetic with every warp's rows streamed
+// through its own double buffer in shared memory. The weights do not depend on the launch before this one, so the
+// first row is requested before that launch's results are waited for.
+template <int M> __global__ void __launch_bounds__(WARPS * 32) qgemv_mxfp4_staged_kernel(GemvArgs p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t k = p.k, kg = k / GROUP, rowb = kg * MXFP4_BYTES;
+    const uint32_t slot = rowb + 16;  // (the aligned loads around a block's last nibble bytes may reach up to three bytes past the row)
+    uint8_t *buf = smem + (size_t)warp * 2 * slot;
+    if (p.ids) {
+        // Expert-indexed launch (Kernel::MatMulId at decode sizes): grid row y is one (token, slot) pair; the ids may
+        // come from the launch before this one
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        const uint32_t pair = blockIdx.y, token = pair / p.id_r;
+        const int32_t id = p.ids[pair];
+        const bool bad = id < 0 || (uint32_t)id >= p.id_e;
+        if (bad && p.status && threadIdx.x == 0) atomicOr(p.status, 128);
+        p.w += bad ? 0 : (uint64_t)id * p.id_stride;
+        p.qa += (uint64_t)token * k;
+        p.da += (uint64_t)token * kg;
+        p.out_off += (uint64_t)pair * p.n;
+    }
+    auto request = [&](uint32_t row, uint8_t *dst) {
+        const uint8_t *src = p.w + (uint64_t)row * rowb;
+        for (uint32_t c = lane; c < rowb / 16; c += 32)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst + 16 * c)), "l"(src + 16 * (size_t)c) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const uint32_t stride = gridDim.x * WARPS;
+    uint32_t row = blockIdx.x * WARPS + warp;
+    if (row < p.n) request(row, buf);
+    if (!p.ids) asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int cur = 0; row < p.n; row += stride, cur ^= 1) {
+        if (row + stride < p.n) {
+            request(row + stride, buf + (cur ^ 1) * slot);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncwarp();  // every lane's part of the row has landed
+        float acc[M];
+#pragma unroll
+        for (int r = 0; r < M; r++) acc[r] = 0.0f;
+        const uint8_t *wrow = buf + cur * slot;
+        for (uint32_t g = lane; g < kg; g += 32) block_dot<M>(wrow + g * MXFP4_BYTES, p, g, k, kg, acc);
+#pragma unroll
+        for (int r = 0; r < M; r++) {
+            float v = acc[r];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) {
+                const uint32_t bt = r / p.m, i = r % p.m;
+                if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
+                p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
+            }
+        }
+        __syncwarp();  // the buffer is refilled one iteration from now: every lane is done reading it
+    }
+}
+
+static bool g_staged = true;  // (tests switch the staged form off to reach the other one at the same shapes)
 template <int M> static cudaError_t launch_m(const GemvArgs &a, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
     const uint32_t want = (a.n + WARPS - 1) / WARPS;
     uint32_t cap = (uint32_t)sm_count * 8;
@@ -115,10 +183,24 @@ template <int M> static cudaError_t launch_m(const GemvArgs &a, uint32_t pairs, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
+    // rows of 16-byte multiples at 16-byte aligned addresses: the staged form, for one and two activation rows (beyond
+    // that the `dp4a` work hides the loads anyway) and while at least three CTAs' buffers fit an SM
+    // (4096 x 14336 at eight rows: 83 us staged with one CTA per SM, 45 us direct)
+    const size_t smem = (size_t)WARPS * 2 * ((size_t)a.k / GROUP * MXFP4_BYTES + 16);
+    const bool aligned = a.k % 512 == 0 && ((uintptr_t)a.w & 15) == 0 && (!a.ids || (a.id_stride & 15) == 0);
+    if (aligned && M <= 2 && smem <= 72 * 1024 && g_staged) {
+        static DynamicSmemOptIn optin;
+        cudaError_t e = optin.raise((const void *)qgemv_mxfp4_staged_kernel<M>, smem);
+        if (e != cudaSuccess) return e;
+        cfg.dynamicSmemBytes = smem;
+        return cudaLaunchKernelEx(&cfg, qgemv_mxfp4_staged_kernel<M>, a);
+    }
     return cudaLaunchKernelEx(&cfg, qgemv_mxfp4_kernel<M>, a);
 }
 
 }  // namespace mx
+
+void qgemv_mxfp4_set_staged(int on) { mx::g_staged = on != 0; }
 
 cudaError_t launch_qgemv_mxfp4(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream) {
     if (args.n == 0 || args.rows == 0) return cudaSuccess;

@@ -1374,3 +1374,43 @@ def test_small_matrices_at_three_and_four_rows_take_the_dp4a_kernel(oracle, fmt,
         plain = run_matmul(be, fmt, a, qb, m, n, k)
         be.set_option("gemv_mma_rows", "2")
         assert np.array_equal(got, plain) == dp4a, (m, n, k)
+
+
+def test_mxfp4_decode_staged_and_direct_forms(be, oracle):
+    """The MXFP4 decode kernel streams rows through shared memory when K is a multiple of 512 and reads them directly
+    otherwise: same arithmetic in the same order, so the two forms agree bit for bit on shapes both can run; both
+    against the oracle; the expert-indexed launch included."""
+    from lapid_b200.backend import matmul_id_launch
+    rng = np.random.default_rng(21)
+    for (m, n, k) in [(1, 4096, 4096), (2, 130, 512), (2, 77, 1024), (8, 1030, 14336), (1, 9, 2560), (1, 33, 28672), (2, 700, 7680), (4, 50, 96)]:
+        raw = rng.integers(0, 256, n * k // 32 * 17, dtype=np.uint8)
+        raw.reshape(-1, 17)[:, 0] = rng.integers(118, 132, n * k // 32, dtype=np.uint8)   # scales around 2^-8
+        qb = np.concatenate([raw, np.zeros((-raw.size) % 256, np.uint8)])
+        a = O.normal(1900 + m, m * k)
+        want, _ = oracle.matmul(O.MXFP4, a, qb, n, k, m=m)
+        got = {}
+        for staged in ("1", "0"):
+            be.set_option("gemv_mxfp4_staged", staged)
+            got[staged] = run_matmul(be, lp.DType.MXFP4, a, qb, m, n, k)
+            assert max_rel(got[staged], want) <= 2e-5, (m, n, k, staged)
+        be.set_option("gemv_mxfp4_staged", "1")
+        assert np.array_equal(got["0"], got["1"]), (m, n, k)
+    t, r, e, n, k = 3, 2, 4, 200, 1024   # (an expert-indexed launch is one-row work per pair: staged)
+    one = oracle.layout(O.MXFP4, n, k).total
+    stack = np.zeros(e * one, np.uint8)
+    for x in range(e):
+        raw = rng.integers(0, 256, n * k // 32 * 17, dtype=np.uint8)
+        raw.reshape(-1, 17)[:, 0] = rng.integers(118, 132, n * k // 32, dtype=np.uint8)
+        stack[x * one:x * one + raw.size] = raw
+    xs = O.normal(1950, t * k)
+    ids = np.array([(i * 3 + 1) % e for i in range(t * r)], np.int32)
+    want = oracle.matmul_id(O.MXFP4, xs, stack, ids, t, r, e, n, k)
+    bufs = [be.upload(xs), be.upload(stack), be.upload(ids.view(np.uint8)), be.alloc(t * r * n * 4)]
+    res = {}
+    for staged in ("1", "0"):
+        be.set_option("gemv_mxfp4_staged", staged)
+        be.execute([matmul_id_launch(lp.DType.MXFP4, t, r, e, n, k)], bufs)
+        res[staged] = bufs[3].download().view(np.float32).copy()
+        assert max_rel(res[staged], want) <= 2e-5
+    be.set_option("gemv_mxfp4_staged", "1")
+    assert np.array_equal(res["0"], res["1"])
