@@ -29,6 +29,7 @@ SOURCES = {
     "qgemv_i8.cu": [],
     "qgemv_i4.cu": [],
     "qgemv_mxfp4.cu": [],
+    "qgemv_mxfp4_mma.cu": [],
     "qgemv_iq.cu": [],
     "iquant.cu": ["-DLAPID_B200_IQ_GRIDS_FILE=" + os.path.join(CSRC, "iq_grids.bin")],
     "qgemv_i8_mma.cu": [],

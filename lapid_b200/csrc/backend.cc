@@ -197,6 +197,9 @@ struct lapid_b200_device {
     // balanced-stream tensor-core decode kernel (qgemv_kq_stream.cu): 0 never; 1 (default) Q5_K always and Q4_K where
     // it is the faster one (launch_qgemv_q4k_mma decides); 2 both formats always
     int gemv_stream = 1;
+    // MXFP4 decode launches with at least this many rows use the int8 tensor-core kernel (0 = never): about 18.5 us on
+    // 14336 x 4096 whatever the row count, against 15.8 / 17.9 / 25.4 / 42.9 us of the dp4a kernel at 1 / 2 / 4 / 8 rows
+    uint32_t mxfp4_mma_rows = 3;
     bool small_dp4a = true;  // small Q5_K / Q6_K matrices at 3 and 4 rows on the dp4a kernel (see plan_launch)
     bool two_row_dp4a = false;    // two early Q4_K rows on the dp4a kernel (see execute_impl)
     lb::StreamWs stream_ws{};    // workspace of that kernel: partial sums in flight between CTAs (all zero between launches)
@@ -473,7 +476,9 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
                  (l.b_dtype == LAPID_B200_DTYPE_Q4_K && p.rows >= dev.gemv_mma_rows && lb::qgemv_q4k_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
                  (l.b_dtype == LAPID_B200_DTYPE_Q6_K && p.rows > dev.gemv_mma_rows && lb::qgemv_q6k_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
                  (l.b_dtype == LAPID_B200_DTYPE_INT8 && p.rows >= dev.gemv_mma_rows && lb::qgemv_i8_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
-                 (l.b_dtype == LAPID_B200_DTYPE_INT4 && p.rows >= dev.gemv_mma_rows && lb::qgemv_i4_mma_shape_ok(p.rows, (uint32_t)l.k)));
+                 (l.b_dtype == LAPID_B200_DTYPE_INT4 && p.rows >= dev.gemv_mma_rows && lb::qgemv_i4_mma_shape_ok(p.rows, (uint32_t)l.k)) ||
+                 (l.b_dtype == LAPID_B200_DTYPE_MXFP4 && dev.mxfp4_mma_rows > 0 && p.rows >= dev.mxfp4_mma_rows &&
+                  lb::qgemv_mxfp4_mma_shape_ok(p.rows, (uint32_t)l.k)));
         // Small Q5_K / Q6_K matrices at three and four rows: their tensor-core kernels cost about 5 us whatever the size
         // (1024 x 4096: 5.0-5.5 us), the dp4a kernel 3.8-4.6 us; from five rows on, and from 4096 x 4096 on, the
         // tensor-core kernels win.
@@ -879,7 +884,8 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         g.a_bs = q.a_bs;
         g.a_rs = q.a_rs;
         g.status = dev.status_dev;
-        if (pend && slot->records && l.b_dtype != LAPID_B200_DTYPE_INT8 && l.b_dtype != LAPID_B200_DTYPE_INT4) {  // (the Int8 / Int4 kernels take one launch at a time)
+        if (pend && slot->records && l.b_dtype != LAPID_B200_DTYPE_INT8 && l.b_dtype != LAPID_B200_DTYPE_INT4 &&
+            l.b_dtype != LAPID_B200_DTYPE_MXFP4) {  // (the Int8 / Int4 / MXFP4 kernels take one launch at a time)
             using Range = PendingGroup::Range;
             const char *ob = (const char *)out->ptr;
             Range wr{ob + 4 * l.out.offset, ob + 4 * last};
@@ -910,7 +916,9 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
         g.early = dev.early_ok(slot->hoisted) ? 1 : 0;
         const bool pdl = dev.pdl_launch();
         const uint64_t ws_before = dev.stream_ws.kernels;
-        if (slot->records == 2 && l.b_dtype == LAPID_B200_DTYPE_INT4) {
+        if (slot->records == 2 && l.b_dtype == LAPID_B200_DTYPE_MXFP4) {
+            cuda_check(lb::launch_qgemv_mxfp4_mma(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        } else if (slot->records == 2 && l.b_dtype == LAPID_B200_DTYPE_INT4) {
             cuda_check(lb::launch_qgemv_i4_mma(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         } else if (slot->records == 2 && l.b_dtype == LAPID_B200_DTYPE_INT8) {
             cuda_check(lb::launch_qgemv_i8_mma(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
@@ -1508,6 +1516,10 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             lb::qgemv_q4k_mma_set_config(std::atoi(value));
         } else if (k == "gemv_q6k_mma_config") {
             lb::qgemv_q6k_mma_set_config(std::atoi(value));
+        } else if (k == "gemv_mxfp4_mma_rows") {
+            int r = std::atoi(value);
+            if (r < 0 || r > 8) fail("invalid_argument", "gemv_mxfp4_mma_rows must be in 0..8");
+            dev->mxfp4_mma_rows = (uint32_t)r;
         } else if (k == "gemv_mxfp4_staged") {
             lb::qgemv_mxfp4_set_staged(std::atoi(value));
         } else if (k == "gemv_iq_rows") {  // weight rows per warp of the i-quant decode kernel: 1, 2 (0: per launch)

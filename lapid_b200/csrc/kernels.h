@@ -132,6 +132,10 @@ cudaError_t launch_qgemv_moe(int fmt, const GemvArgs &args, int sm_count, bool p
 cudaError_t launch_qgemv_i4(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 // ---- qgemv_mxfp4.cu: MXFP4 blocks, 1..8 rows (and the expert-indexed form: args.ids set, rows = tokens); reads the planes
 cudaError_t launch_qgemv_mxfp4(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+// qgemv_mxfp4_mma.cu: the same blocks on the int8 tensor-core instruction (K a multiple of 512; the activation tiles
+// of the K-quant kernels)
+bool qgemv_mxfp4_mma_shape_ok(uint32_t rows, uint32_t k);
+cudaError_t launch_qgemv_mxfp4_mma(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 void qgemv_mxfp4_set_staged(int on);  // 1 (default): rows staged through shared memory where K allows; 0: direct loads only
 
 // ---- qgemv_iq.cu: the grid-based i-quants (IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS), 1..8 rows (and the expert-indexed form);

@@ -15,7 +15,7 @@
 // one is multiplied (one and two activation rows, K up to 8192: 4096 x 4096 at one row 7.6 against 9.2 us, 14336 x 4096
 // 15.8 against 17.2 us). Other launches read the blocks straight from global memory. Either way the kernel is bound
 // by the instructions that unpack a block (some 120 per 32 weights at one row), not by HBM (0.2-0.3 of its rate);
-// no tensor-core variant yet: from about four rows on the `dp4a` work per weight dominates.
+// from three rows on the launches go to the tensor-core kernel of qgemv_mxfp4_mma.cu.
 #include "common.cuh"
 #include "kernels.h"
 

@@ -1414,3 +1414,32 @@ def test_mxfp4_decode_staged_and_direct_forms(be, oracle):
         assert max_rel(res[staged], want) <= 2e-5
     be.set_option("gemv_mxfp4_staged", "1")
     assert np.array_equal(res["0"], res["1"])
+
+
+def test_gemv_mxfp4_tensor_core_decode_kernel(be, oracle):
+    """The MXFP4 tensor-core decode kernel (1..8 rows, K a multiple of 512) against the oracle and against the dp4a
+    kernel: random blocks (every code, "-0" included, scale bytes from denormal to large), ragged n, every row
+    count, a bias, K with several chunks per warp, a row of all-negative and a row of all-zero codes."""
+    rng = np.random.default_rng(23)
+    try:
+        for (m, n, k, bias) in [(1, 200, 512, False), (2, 130, 2048, False), (3, 77, 512, True), (4, 513, 4096, False), (5, 100, 1536, False),
+                                (6, 1, 1024, False), (7, 33, 14336, True), (8, 300, 4096, False), (8, 17, 14336, False), (1, 4096, 4096, False)]:
+            raw = rng.integers(0, 256, n * k // 32 * 17, dtype=np.uint8)
+            b2 = raw.reshape(-1, 17)
+            b2[:, 0] = rng.integers(110, 140, b2.shape[0], dtype=np.uint8)
+            b2[:4, 0] = [0, 1, 2, 150]                     # denormal, smallest normal and a large scale
+            b2[5, 1:] = 0xFF                               # all codes 15 (-12)
+            b2[6, 1:] = 0x88                               # all "-0"
+            b2[7, 1:] = 0x00
+            qb = np.concatenate([raw, np.zeros((-raw.size) % 256, np.uint8)])
+            a = O.normal(2000 + m, m * k)
+            bv = O.normal(2050 + m, n) if bias else None
+            want, _ = oracle.matmul(O.MXFP4, a, qb, n, k, m=m, bias=bv)
+            be.set_option("gemv_mxfp4_mma_rows", "1")
+            got = run_matmul(be, lp.DType.MXFP4, a, qb, m, n, k, bias=bv)
+            be.set_option("gemv_mxfp4_mma_rows", "0")
+            ref = run_matmul(be, lp.DType.MXFP4, a, qb, m, n, k, bias=bv)
+            assert max_rel(got, want) <= 2e-5, (m, n, k, max_rel(got, want))
+            assert max_rel(got, ref) <= 2e-5, (m, n, k)
+    finally:
+        be.set_option("gemv_mxfp4_mma_rows", "3")
