@@ -64,6 +64,28 @@ __device__ __forceinline__ float mxfp4_element(const uint8_t *b, uint32_t e) {
     return xmul((float)mxfp4_kv(e < 16 ? q & 15 : q >> 4), e8m0_half(b[0]));
 }
 
+// `prmt.b32` as the instruction defines it (selector nibble: bits 0..2 pick one of the eight source bytes, bit 3 replaces
+// the byte by eight copies of its top bit; the __byte_perm intrinsic drops bit 3).
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+// Four MXFP4 codes in the nibbles of the low 16 bits of `h` -> their KV values (the doubled e2m1 values, mxfp4_kv) as four
+// int8, byte i = nibble i. Four nibbles are exactly a `prmt` selector: with the sign bits masked off, one `prmt` over
+// the table of magnitudes gives the four |KV|, a second over the negated magnitudes the four -|KV|; `prmt` of 0x80
+// bytes with the unmasked half as selector gives 0x80 where a sign bit is clear (byte copied) and 0xFF where it is set
+// (top bit replicated), which a shift and one logic operation turn into a byte mask and a last one uses to pick per
+// byte. The code 8 ("-0") comes out as 0.
+__device__ __forceinline__ uint32_t mxfp4_kv4(uint32_t h) {
+    const uint32_t sel = h & 0x7777u;
+    const uint32_t pos = prmt(0x03020100u, 0x0C080604u, sel);  // 0, 1, 2, 3 | 4, 6, 8, 12
+    const uint32_t neg = prmt(0xFDFEFF00u, 0xF4F8FAFCu, sel);  // 0, -1, -2, -3 | -4, -6, -8, -12
+    const uint32_t r = prmt(0x80808080u, 0x80808080u, h);
+    const uint32_t m = (r & 0x7F7F7F7Fu) | ((r << 1) & 0x80808080u);  // 0x00 / 0xFF
+    return (pos & ~m) | (neg & m);
+}
+
 // The epilogue expression of a launch at one output element (postfix program, see EpiProg): a four-deep stack in
 // registers, one pass over the program's words. f32 throughout; Exp, Log, Sin, Cos, Tanh, Erf and Pow are CUDA's
 // full-precision functions, Recip and Div IEEE divisions (the reference's CPU backend has polynomial versions of its

@@ -6,10 +6,10 @@
 //     acc += d * da_g * f32(sum_32 qa * KV[q])          one activation group per weight block
 //
 // One warp per weight row; a lane takes every 32nd block of the row. Blocks are 17 bytes long, so they start on
-// any byte boundary: the 16 nibble bytes are fetched as aligned 32-bit words and funnel-shifted into place. A
-// nibble becomes its KV magnitude with one byte-permute (the eight magnitudes 0,1,2,3,4,6,8,12 are a two-register
-// table and the three low bits of four nibbles the selector); the sign bits split the four magnitudes into a
-// positive and a negative word, each multiplied with `dp4a` against the activation planes (served by L1/L2).
+// any byte boundary: the 16 nibble bytes are fetched as aligned 32-bit words and funnel-shifted into place. Four
+// codes become four int8 KV values with three byte-permutes and three logic operations (mxfp4_kv4 in common.cuh: the
+// four nibbles of a 16-bit half are used as the permute's selector as they are), multiplied with `dp4a` against the
+// activation planes (served by L1/L2), whose bytes one more permute per word brings into the same element order.
 // Two forms. When a weight row is a multiple of 16 bytes (K a multiple of 512) every warp streams its rows through a
 // shared-memory double buffer with 16-byte `cp.async` copies: the copy of the next row is in flight while the current
 // one is multiplied (one and two activation rows, K up to 8192: 4096 x 4096 at one row 7.6 against 9.2 us, 14336 x 4096
@@ -24,18 +24,6 @@ namespace mx {
 
 constexpr int WARPS = 8;
 
-// The four nibbles in bytes of `n` (each 0..15) -> their KV magnitudes, split by sign: pos holds the magnitudes of
-// the non-negative codes, neg those of the negative ones (the other bytes are 0).
-__device__ __forceinline__ void kv_split(uint32_t n, uint32_t &pos, uint32_t &neg) {
-    const uint32_t t = n & 0x07070707u;
-    const uint32_t u = (t | (t >> 4)) & 0x00FF00FFu;  // byte 0: nibbles 0, 1; byte 2: nibbles 2, 3
-    const uint32_t sel = (u | (u >> 8)) & 0xFFFFu;    // one selector nibble per output byte
-    const uint32_t mag = __byte_perm(0x03020100u, 0x0C080604u, sel);
-    const uint32_t s = ((n >> 3) & 0x01010101u) * 0xFFu;  // 0xFF in the bytes whose code has the sign bit
-    pos = mag & ~s;
-    neg = mag & s;
-}
-
 // One 17-byte block at `b` (global or shared memory, any alignment) against activation group g of every row.
 template <int M> __device__ __forceinline__ void block_dot(const uint8_t *b, const GemvArgs &p, uint32_t g, uint32_t k, uint32_t kg, float (&acc)[M]) {
     const float d = e8m0_half(*b);
@@ -47,12 +35,14 @@ template <int M> __device__ __forceinline__ void block_dot(const uint8_t *b, con
 #pragma unroll
     for (int i = 0; i < 4; i++) raw[i] = wp[i];
     raw[4] = sh ? wp[4] : 0u;  // (aligned blocks end with the fourth word: nothing is read behind them)
-    uint32_t lp[4], ln[4], hp[4], hn[4];
+    // word i holds the codes of elements 4i..4i+3 (low nibbles) and 16+4i.. (high nibbles): q[2i] = KV of elements
+    // (4i, 4i+16, 4i+1, 4i+17), q[2i+1] of (4i+2, 4i+18, 4i+3, 4i+19) as int8 (mxfp4_kv4)
+    uint32_t q[8];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const uint32_t w = __funnelshift_r(raw[i], raw[i + 1], sh);
-        kv_split(w & 0x0F0F0F0Fu, lp[i], ln[i]);         // elements 4i .. 4i + 3
-        kv_split((w >> 4) & 0x0F0F0F0Fu, hp[i], hn[i]);  // elements 16 + 4i ..
+        q[2 * i] = mxfp4_kv4(w);
+        q[2 * i + 1] = mxfp4_kv4(w >> 16);
     }
 #pragma unroll
     for (int r = 0; r < M; r++) {
@@ -60,15 +50,13 @@ template <int M> __device__ __forceinline__ void block_dot(const uint8_t *b, con
         const uint4 a0 = __ldg(ap), a1 = __ldg(ap + 1);
         const float da = __ldg(p.da + (uint64_t)r * kg + g);
         const uint32_t al[4] = {a0.x, a0.y, a0.z, a0.w}, ah[4] = {a1.x, a1.y, a1.z, a1.w};
-        int dp = 0, dn = 0;
+        int dp = 0;
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            dp = __dp4a((int)lp[i], (int)al[i], dp);
-            dn = __dp4a((int)ln[i], (int)al[i], dn);
-            dp = __dp4a((int)hp[i], (int)ah[i], dp);
-            dn = __dp4a((int)hn[i], (int)ah[i], dn);
+        for (int i = 0; i < 4; i++) {  // the activations in the same element order
+            dp = __dp4a((int)q[2 * i], (int)prmt(al[i], ah[i], 0x5140u), dp);
+            dp = __dp4a((int)q[2 * i + 1], (int)prmt(al[i], ah[i], 0x7362u), dp);
         }
-        acc[r] = fmaf(d * da, (float)(dp - dn), acc[r]);
+        acc[r] = fmaf(d * da, (float)dp, acc[r]);
     }
 }
 

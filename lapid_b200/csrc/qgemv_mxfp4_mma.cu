@@ -43,21 +43,6 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0x4B400000));
 }
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t r;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-    return r;
-}
-// The four codes in the nibbles of the low 16 bits of `h` -> their KV values as four int8 (byte i = nibble i).
-__device__ __forceinline__ uint32_t kv4(uint32_t h) {
-    const uint32_t sel = h & 0x7777u;
-    const uint32_t pos = prmt(0x03020100u, 0x0C080604u, sel);  // 0, 1, 2, 3 | 4, 6, 8, 12
-    const uint32_t neg = prmt(0xFDFEFF00u, 0xF4F8FAFCu, sel);  // 0, -1, -2, -3 | -4, -6, -8, -12
-    const uint32_t r = prmt(0x80808080u, 0x80808080u, h);      // 0x80: sign bit clear, 0xFF: set (selector bit 3 replicates the top bit)
-    const uint32_t m = (r & 0x7F7F7F7Fu) | ((r << 1) & 0x80808080u);  // 0x00 / 0xFF
-    return (pos & ~m) | (neg & m);
-}
-
 __host__ __device__ constexpr uint32_t act_block_bytes(uint32_t rows) { return 256 * rows + 512; }  // per 256 k, as the K-quant kernels' tiles
 
 template <int WARPS>
@@ -142,7 +127,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 4) qgemv_mxfp4_mm
                     const uint32_t at = off + 1 + 4 * t4, sh = (at & 3u) * 8u;
                     const uint32_t *pl = (const uint32_t *)(row_lo + (at & ~3u)), *ph = (const uint32_t *)(row_hi + (at & ~3u));
                     const uint32_t wl = __funnelshift_r(pl[0], pl[1], sh), wh = __funnelshift_r(ph[0], ph[1], sh);
-                    const uint32_t a0 = kv4(wl), a2 = kv4(wl >> 16), a1 = kv4(wh), a3 = kv4(wh >> 16);
+                    const uint32_t a0 = mxfp4_kv4(wl), a2 = mxfp4_kv4(wl >> 16), a1 = mxfp4_kv4(wh), a3 = mxfp4_kv4(wh >> 16);
                     // the activations of elements 4 t4 .. and 16 + 4 t4 .., brought into the same order
                     const uint8_t *bp = ab + s * (M * 32) + colq * 32 + 4 * t4;
                     const uint32_t bl = *(const uint32_t *)bp, bh = *(const uint32_t *)(bp + 16);
