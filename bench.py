@@ -212,6 +212,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     def quantized(fmt, n, k, seed):
         g = torch.Generator(device=dev)
         g.manual_seed(seed)
+        if fmt >= 10:   # the i-quants have no quantizer here; every byte pattern is a valid block: random blocks, d = f16 0.01
+            out = torch.zeros(weight_bytes(fmt, n, k), dtype=torch.uint8, device=dev)
+            blocks = torch.randint(0, 256, (n * k // 256, AOS_BLOCK[fmt][1]), dtype=torch.uint8, device=dev, generator=g)
+            blocks[:, 0] = 0x1F
+            blocks[:, 1] = 0x21
+            out[:blocks.numel()] = blocks.reshape(-1)
+            torch.cuda.synchronize()
+            return out
         w = torch.randn(n * k, device=dev, generator=g) * 0.02
         out = torch.empty(weight_bytes(fmt, n, k), dtype=torch.uint8, device=dev)
         torch.cuda.synchronize()
@@ -376,7 +384,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     roof_kernel, roof_traffic, roof_detail = None, None, None
     if world == 1 and not args.no_cases:
         POOL = 512 << 20
-        for f in (6, 8, 4, 7, 5):
+        for f in (6, 8, 4, 7, 5, 9, 10, 12):   # Q4_K, Q6_K, Int8 (the benchmark's formats), then Q5_K, Int4, MXFP4, IQ2_XXS, IQ3_XXS
             for si, (n, k, tag) in enumerate(SHAPES):
                 wq = base[(n, k)] if f == 6 else quantized(f, n, k, 300 + si)
                 wb = wq.numel()

@@ -1522,6 +1522,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             dev->mxfp4_mma_rows = (uint32_t)r;
         } else if (k == "gemv_mxfp4_staged") {
             lb::qgemv_mxfp4_set_staged(std::atoi(value));
+        } else if (k == "gemv_iq_k_split") {
+            lb::qgemv_iq_set_k_split(std::atoi(value));
         } else if (k == "gemv_iq_rows") {  // weight rows per warp of the i-quant decode kernel: 1, 2 (0: per launch)
             lb::qgemv_iq_set_rows_per_warp(std::atoi(value));
         } else if (k == "gemv_ctas_per_sm") {

@@ -142,6 +142,7 @@ void qgemv_mxfp4_set_staged(int on);  // 1 (default): rows staged through shared
 // reads the activation planes, the codebooks from the per-device table of iquant.cu
 cudaError_t launch_qgemv_iq(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
 void qgemv_iq_set_rows_per_warp(int rows);  // 0: per launch (default); 1, 2: forced
+void qgemv_iq_set_k_split(int ways);        // warps per row at one row per warp: 0: per launch (default); 1, 2, 4: forced
 // iquant.cu: uploads the codebooks to the current device (once; outside stream captures)
 cudaError_t iq_grids_upload();
 // Opt in to the dynamic shared memory the GEMV variants need; once per device.

@@ -84,7 +84,9 @@ __device__ __forceinline__ void unpack32(const uint8_t *b, int ib, const uint8_t
     sc1 = xmul(xmul(d, xadd(0.5f, (float)s1)), F);
 }
 
-template <int FMT, int M, int ROWS, int WARPS>
+// KS warps share the rows of a warp group and split their blocks (matrices with few rows and a long K would otherwise
+// leave most warp slots of an SM empty); their partial sums meet in shared memory and are added in warp order.
+template <int FMT, int M, int ROWS, int WARPS, int KS>
 __global__ void __launch_bounds__(WARPS * 32) qgemv_iq_kernel(GemvArgs p, const uint8_t *__restrict__ grid_global) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ __align__(16) uint8_t grid[iq_grid_bytes(FMT)];
@@ -110,13 +112,17 @@ __global__ void __launch_bounds__(WARPS * 32) qgemv_iq_kernel(GemvArgs p, const 
         p.out_off += (uint64_t)pair * p.n;
     }
     const int ib = lane & 7;  // this lane's sub-block
-    for (uint32_t row0 = (blockIdx.x * WARPS + warp) * ROWS; row0 < p.n; row0 += gridDim.x * WARPS * ROWS) {
+    constexpr int RPC = WARPS / KS * ROWS;  // rows of a CTA per pass
+    const int wg = warp / KS, ks = warp % KS;
+    __shared__ float part[KS > 1 ? WARPS * ROWS * M : 1];
+    for (uint32_t base = blockIdx.x * RPC; base < p.n; base += gridDim.x * RPC) {  // (the same number of passes for every warp of the CTA)
+        const uint32_t row0 = base + wg * ROWS;
         float acc[ROWS][M];
 #pragma unroll
         for (int j = 0; j < ROWS; j++)
 #pragma unroll
             for (int r = 0; r < M; r++) acc[j][r] = 0.0f;
-        for (uint32_t blk = lane >> 3; blk < nblk; blk += 4) {
+        for (uint32_t blk = (lane >> 3) + 4 * ks; blk < nblk; blk += 4 * KS) {
             uint32_t w[ROWS][8];
             float sc[ROWS][2];
 #pragma unroll
@@ -153,18 +159,37 @@ __global__ void __launch_bounds__(WARPS * 32) qgemv_iq_kernel(GemvArgs p, const 
 #pragma unroll
                 for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
                 const uint32_t row = row0 + j;
-                if (lane == 0 && row < p.n) {
+                if constexpr (KS > 1) {
+                    if (lane == 0) part[(warp * ROWS + j) * M + r] = v;
+                } else if (lane == 0 && row < p.n) {
                     const uint32_t bt = r / p.m, i = r % p.m;
                     if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
                     p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
                 }
             }
         }
+        if constexpr (KS > 1) {
+            __syncthreads();
+            if (ks == 0 && lane < ROWS * M) {  // one lane per (row, activation row) of the group
+                const int j = lane / M, r = lane % M;
+                float v = part[(warp * ROWS + j) * M + r];
+#pragma unroll
+                for (int s2 = 1; s2 < KS; s2++) v += part[((warp + s2) * ROWS + j) * M + r];
+                const uint32_t row = row0 + j;
+                if (row < p.n) {
+                    const uint32_t bt = r / p.m, i = r % p.m;
+                    if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
+                    p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
+                }
+            }
+            __syncthreads();  // the partial sums are read: the next pass may overwrite them
+        }
     }
 }
 
-template <int FMT, int M, int ROWS, int WARPS> static cudaError_t launch_r(const GemvArgs &a, const uint8_t *grid, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
-    const uint32_t want = (a.n + WARPS * ROWS - 1) / (WARPS * ROWS);
+template <int FMT, int M, int ROWS, int WARPS, int KS = 1> static cudaError_t launch_r(const GemvArgs &a, const uint8_t *grid, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
+    constexpr uint32_t RPC = WARPS / KS * ROWS;
+    const uint32_t want = (a.n + RPC - 1) / RPC;
     uint32_t cap = (uint32_t)sm_count * 8 * (8 / WARPS);
     if (pairs > 1) cap = cap / pairs > 0 ? cap / pairs : 1;
     cudaLaunchConfig_t cfg = {};
@@ -176,17 +201,27 @@ template <int FMT, int M, int ROWS, int WARPS> static cudaError_t launch_r(const
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, qgemv_iq_kernel<FMT, M, ROWS, WARPS>, a, grid);
+    return cudaLaunchKernelEx(&cfg, qgemv_iq_kernel<FMT, M, ROWS, WARPS, KS>, a, grid);
 }
 
 // Two weight rows per warp share the activation loads and give the scheduler two independent decode chains: the
-// fastest form measured at every row count (four rows per warp need 128 registers and lose more to occupancy than
-// they save in loads). One row per warp where two would leave SMs short of CTAs.
+// fastest form measured where the matrix has rows enough to fill the SMs' warp slots that way (four rows per warp need
+// 128 registers and lose more to occupancy than they save in loads). With fewer rows: one row per warp, and two or
+// four warps per row when even that leaves slots empty and the rows are long enough to split (4096 x 14336 at one
+// activation row: 24.2 us with two rows per warp, 19.8 with one).
 static int g_rows_per_warp = 0;  // 0: chosen per launch; 1, 2: forced (tests, sweeps)
+static int g_k_split = 0;        // 0: chosen per launch; 1, 2, 4: forced
 template <int FMT, int M> static cudaError_t launch_m(const GemvArgs &a, const uint8_t *grid, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
-    const uint64_t ctas2 = (uint64_t)((a.n + 7) / 8) * pairs;  // CTAs of four warps, two rows each
-    const int forced = g_rows_per_warp;
-    if (forced == 2 || (!forced && ctas2 >= (uint64_t)sm_count * 2)) return launch_r<FMT, M, 2, 4>(a, grid, pairs, sm_count, pdl, stream);
+    const uint64_t slots = (uint64_t)sm_count * 32;  // warps that keep the SMs' schedulers busy
+    const uint64_t rows = (uint64_t)a.n * pairs, steps = a.k / QK / 4;  // steps: passes of a warp over a row at four blocks per pass
+    int rpw = g_rows_per_warp ? g_rows_per_warp : ((rows + 1) / 2 >= slots ? 2 : 1);
+    int ksp = 1;
+    if (g_k_split) ksp = g_k_split;
+    else if (rpw == 1)
+        while (ksp < 4 && rows * ksp < slots && steps / (2 * ksp) >= 2) ksp *= 2;
+    if (rpw == 2) return launch_r<FMT, M, 2, 4>(a, grid, pairs, sm_count, pdl, stream);
+    if (ksp == 2) return launch_r<FMT, M, 1, 8, 2>(a, grid, pairs, sm_count, pdl, stream);
+    if (ksp == 4) return launch_r<FMT, M, 1, 8, 4>(a, grid, pairs, sm_count, pdl, stream);
     return launch_r<FMT, M, 1, 8>(a, grid, pairs, sm_count, pdl, stream);
 }
 
@@ -215,6 +250,7 @@ template <int FMT> static cudaError_t launch_fmt(const GemvArgs &args, const uin
 }  // namespace iq
 
 void qgemv_iq_set_rows_per_warp(int rows) { iq::g_rows_per_warp = rows == 1 || rows == 2 ? rows : 0; }
+void qgemv_iq_set_k_split(int ways) { iq::g_k_split = ways == 1 || ways == 2 || ways == 4 ? ways : 0; }
 
 cudaError_t launch_qgemv_iq(int fmt, const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream) {
     if (args.n == 0 || args.rows == 0) return cudaSuccess;

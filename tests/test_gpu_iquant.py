@@ -65,9 +65,10 @@ def test_decode_matches_oracle_all_row_counts(be, oracle, fmt, name, m):
         a = O.normal(seed + 100, m * k)
         want, path = oracle.matmul(int(fmt), a, qb, n, k, m=m)
         assert path == "int8_act"
-        for rows in ("1", "2", "0"):      # one and two weight rows per warp, then the launch's own choice
+        for rows, split in (("1", "1"), ("2", "0"), ("1", "2"), ("1", "4"), ("0", "0")):   # rows per warp, warps per row; last: the launch's own choice
             be.set_option("gemv_iq_rows", rows)
-            assert max_rel(run_matmul(be, fmt, a, qb, m, n, k), want) <= 2e-5, (n, k, rows)
+            be.set_option("gemv_iq_k_split", split)
+            assert max_rel(run_matmul(be, fmt, a, qb, m, n, k), want) <= 2e-5, (n, k, rows, split)
 
 
 @pytest.mark.parametrize("fmt,name", IQ)
