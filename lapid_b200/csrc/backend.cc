@@ -1520,6 +1520,8 @@ lapid_b200_status lapid_b200_device_set_option(lapid_b200_device *dev, const cha
             int r = std::atoi(value);
             if (r < 0 || r > 8) fail("invalid_argument", "gemv_mxfp4_mma_rows must be in 0..8");
             dev->mxfp4_mma_rows = (uint32_t)r;
+        } else if (k == "gemv_mxfp4_k_split") {
+            lb::qgemv_mxfp4_set_k_split(std::atoi(value));
         } else if (k == "gemv_mxfp4_staged") {
             lb::qgemv_mxfp4_set_staged(std::atoi(value));
         } else if (k == "gemv_iq_k_split") {

@@ -136,6 +136,7 @@ cudaError_t launch_qgemv_mxfp4(const GemvArgs &args, int sm_count, bool pdl, cud
 // of the K-quant kernels)
 bool qgemv_mxfp4_mma_shape_ok(uint32_t rows, uint32_t k);
 cudaError_t launch_qgemv_mxfp4_mma(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);
+void qgemv_mxfp4_set_k_split(int ways);  // warps per row of the direct form: 0: per launch (default); 1, 2, 4: forced
 void qgemv_mxfp4_set_staged(int on);  // 1 (default): rows staged through shared memory where K allows; 0: direct loads only
 
 // ---- qgemv_iq.cu: the grid-based i-quants (IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS), 1..8 rows (and the expert-indexed form);

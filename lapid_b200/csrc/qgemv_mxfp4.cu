@@ -60,7 +60,9 @@ template <int M> __device__ __forceinline__ void block_dot(const uint8_t *b, con
     }
 }
 
-template <int M> __global__ void __launch_bounds__(WARPS * 32) qgemv_mxfp4_kernel(GemvArgs p) {
+// KS warps share a row and split its blocks (matrices with few rows and a long K would otherwise leave most warp slots of
+// an SM empty); their partial sums meet in shared memory and are added in warp order.
+template <int M, int KS> __global__ void __launch_bounds__(WARPS * 32) qgemv_mxfp4_kernel(GemvArgs p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -76,22 +78,41 @@ template <int M> __global__ void __launch_bounds__(WARPS * 32) qgemv_mxfp4_kerne
         p.da += (uint64_t)token * kg;
         p.out_off += (uint64_t)pair * p.n;
     }
-    for (uint32_t row = blockIdx.x * WARPS + warp; row < p.n; row += gridDim.x * WARPS) {
+    constexpr int RPC = WARPS / KS;  // rows of a CTA per pass
+    const int wg = warp / KS, ks = warp % KS;
+    __shared__ float part[KS > 1 ? WARPS * M : 1];
+    for (uint32_t base = blockIdx.x * RPC; base < p.n; base += gridDim.x * RPC) {  // (the same number of passes for every warp of the CTA)
+        const uint32_t row = base + wg, rrow = row < p.n ? row : p.n - 1;  // (a row past the end repeats the last one; not stored)
         float acc[M];
 #pragma unroll
         for (int r = 0; r < M; r++) acc[r] = 0.0f;
-        const uint8_t *wrow = p.w + (uint64_t)row * kg * MXFP4_BYTES;
-        for (uint32_t g = lane; g < kg; g += 32) block_dot<M>(wrow + (uint64_t)g * MXFP4_BYTES, p, g, k, kg, acc);
+        const uint8_t *wrow = p.w + (uint64_t)rrow * kg * MXFP4_BYTES;
+        for (uint32_t g = lane + 32 * ks; g < kg; g += 32 * KS) block_dot<M>(wrow + (uint64_t)g * MXFP4_BYTES, p, g, k, kg, acc);
 #pragma unroll
         for (int r = 0; r < M; r++) {
             float v = acc[r];
 #pragma unroll
             for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0) {
+            if constexpr (KS > 1) {
+                if (lane == 0) part[warp * M + r] = v;
+            } else if (lane == 0 && row < p.n) {
                 const uint32_t bt = r / p.m, i = r % p.m;
                 if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
                 p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
             }
+        }
+        if constexpr (KS > 1) {
+            __syncthreads();
+            if (ks == 0 && lane < M && row < p.n) {
+                const int r = lane;
+                float v = part[warp * M + r];
+#pragma unroll
+                for (int s2 = 1; s2 < KS; s2++) v += part[(warp + s2) * M + r];
+                const uint32_t bt = r / p.m, i = r % p.m;
+                if (p.extra && !p.epi.n) v += p.extra[p.ex_off + (int64_t)bt * p.ex_s0 + (int64_t)i * p.ex_s1 + (int64_t)row * p.ex_s2];
+                p.out[p.out_off + (uint64_t)bt * p.out_bs + (uint64_t)i * p.out_rs + row] = v;
+            }
+            __syncthreads();  // the partial sums are read: the next pass may overwrite them
         }
     }
 }
@@ -158,6 +179,7 @@ template <int M> __global__ void __launch_bounds__(WARPS * 32) qgemv_mxfp4_stage
 }
 
 static bool g_staged = true;  // (tests switch the staged form off to reach the other one at the same shapes)
+static int g_k_split = 0;     // warps per row of the direct form: 0: chosen per launch; 1, 2, 4: forced
 template <int M> static cudaError_t launch_m(const GemvArgs &a, uint32_t pairs, int sm_count, bool pdl, cudaStream_t stream) {
     const uint32_t want = (a.n + WARPS - 1) / WARPS;
     uint32_t cap = (uint32_t)sm_count * 8;
@@ -183,12 +205,26 @@ template <int M> static cudaError_t launch_m(const GemvArgs &a, uint32_t pairs, 
         cfg.dynamicSmemBytes = smem;
         return cudaLaunchKernelEx(&cfg, qgemv_mxfp4_staged_kernel<M>, a);
     }
-    return cudaLaunchKernelEx(&cfg, qgemv_mxfp4_kernel<M>, a);
+    // direct loads: one warp per row, or two / four warps per row when the rows alone leave most warp slots empty
+    // and are long enough to split
+    const uint64_t rows = (uint64_t)a.n * pairs, slots = (uint64_t)sm_count * 32, steps = a.k / GROUP / 32;
+    int ksp = 1;
+    if (g_k_split) ksp = g_k_split;
+    else
+        while (ksp < 4 && rows * ksp < slots && steps / (2 * ksp) >= 2) ksp *= 2;
+    if (ksp > 1) {
+        const uint32_t rpc = WARPS / ksp, want2 = (a.n + rpc - 1) / rpc;
+        cfg.gridDim = dim3(want2 < cap ? want2 : cap, pairs);
+        if (ksp == 2) return cudaLaunchKernelEx(&cfg, qgemv_mxfp4_kernel<M, 2>, a);
+        return cudaLaunchKernelEx(&cfg, qgemv_mxfp4_kernel<M, 4>, a);
+    }
+    return cudaLaunchKernelEx(&cfg, qgemv_mxfp4_kernel<M, 1>, a);
 }
 
 }  // namespace mx
 
 void qgemv_mxfp4_set_staged(int on) { mx::g_staged = on != 0; }
+void qgemv_mxfp4_set_k_split(int ways) { mx::g_k_split = ways == 1 || ways == 2 || ways == 4 ? ways : 0; }
 
 cudaError_t launch_qgemv_mxfp4(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream) {
     if (args.n == 0 || args.rows == 0) return cudaSuccess;

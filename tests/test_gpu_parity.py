@@ -1389,12 +1389,18 @@ def test_mxfp4_decode_staged_and_direct_forms(be, oracle):
         a = O.normal(1900 + m, m * k)
         want, _ = oracle.matmul(O.MXFP4, a, qb, n, k, m=m)
         got = {}
+        be.set_option("gemv_mxfp4_mma_rows", "0")       # (the dp4a kernel at every row count)
+        be.set_option("gemv_mxfp4_k_split", "1")
         for staged in ("1", "0"):
             be.set_option("gemv_mxfp4_staged", staged)
             got[staged] = run_matmul(be, lp.DType.MXFP4, a, qb, m, n, k)
             assert max_rel(got[staged], want) <= 2e-5, (m, n, k, staged)
-        be.set_option("gemv_mxfp4_staged", "1")
         assert np.array_equal(got["0"], got["1"]), (m, n, k)
+        for split in ("2", "4", "0"):                   # two and four warps per row, then the launch's own choice
+            be.set_option("gemv_mxfp4_k_split", split)
+            assert max_rel(run_matmul(be, lp.DType.MXFP4, a, qb, m, n, k), want) <= 2e-5, (m, n, k, split)
+        be.set_option("gemv_mxfp4_staged", "1")
+        be.set_option("gemv_mxfp4_mma_rows", "3")
     t, r, e, n, k = 3, 2, 4, 200, 1024   # (an expert-indexed launch is one-row work per pair: staged)
     one = oracle.layout(O.MXFP4, n, k).total
     stack = np.zeros(e * one, np.uint8)
