@@ -521,7 +521,7 @@ def gemv_kernel_name(fmt: int, m: int, n: int = 0, k: int = 0) -> str:
     if fmt == 7:
         return "qgemv_kq_stream_kernel<q5_k>" if m >= 3 and not small else "qgemv_kq_fast_kernel<q5_k>"
     if fmt == 5:
-        return "qgemv_i4_mma_kernel" if m >= 2 else "qgemv_i4_kernel"
+        return "qgemv_i4_mma_kernel" if m >= 2 else ("qgemv_i8_fast_kernel<int4>" if k % 512 == 0 else "qgemv_i4_kernel")
     if fmt == 9:
         return "qgemv_mxfp4_mma_kernel" if m >= 3 and k % 512 == 0 else "qgemv_mxfp4_kernel"
     if fmt >= 10:

@@ -292,7 +292,7 @@ struct Plan {
     bool mma = false;    // Q4_K GEMV on the int8 tensor-core instruction (activations as tiles)
     bool stream = false; // ... through the balanced-stream kernel (Q4_K, Q5_K)
     int records() const { return mma ? 2 : fast ? 1 : 0; }  // ActQuantArgs::records
-    bool fast_i8 = false;  // specialised Int8 GEMV (activations as planes)
+    bool fast_i8 = false;  // specialised Int8 / Int4 GEMV with bulk-copy rings (activations as planes)
     bool tc = false;     // tensor-core GEMM (needs a bf16 copy of the activations in the scratch)
 };
 
@@ -465,7 +465,8 @@ Plan plan_launch(const lapid_b200_device &dev, const lapid_b200_launch &l) {
         size_t rec = align_up((uint64_t)p.rows * ((l.k + 255) / 256) * lb::REC, 256);  // record layout of the fast path
         p.scratch = qa + 2 * sc > rec ? qa + 2 * sc : rec;
         p.fast = dev.gemv_fast && lb::qgemv_kq_fast_shape_ok(l.b_dtype, p.rows, (uint32_t)l.k);
-        p.fast_i8 = dev.gemv_fast && l.b_dtype == LAPID_B200_DTYPE_INT8 && lb::qgemv_i8_fast_shape_ok(p.rows, (uint32_t)l.k);
+        p.fast_i8 = dev.gemv_fast && (l.b_dtype == LAPID_B200_DTYPE_INT8 || l.b_dtype == LAPID_B200_DTYPE_INT4) &&
+                    lb::qgemv_i8_fast_shape_ok(p.rows, (uint32_t)l.k);  // (Int4: the same kernel over nibble planes)
         // (Q6_K pays more per weight for unpacking: its tensor-core kernel wins one row later than Q4_K's)
         p.stream = dev.gemv_fast && dev.gemv_mma_rows > 0 &&
                    ((dev.gemv_stream >= 2 && l.b_dtype == LAPID_B200_DTYPE_Q4_K && p.rows >= dev.gemv_mma_rows) ||
@@ -931,6 +932,8 @@ void run_launch(lapid_b200_device &dev, const lapid_b200_launch &l, lapid_b200_b
             else cuda_check(lb::launch_qgemv_q4k_mma(one, dev.sm_count, pdl, dev.stream, dev.gemv_stream ? &dev.stream_ws : nullptr), "qgemv launch");
             g.epi.n = one.item[0].epi.n;  // (cleared when the launch evaluated its expression itself)
         } else if (slot->records) cuda_check(lb::launch_qgemv_kq_fast(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");
+        else if (l.b_dtype == LAPID_B200_DTYPE_INT4 && p.fast_i8 && ((uintptr_t)g.w & 15) == 0 && (g.scales_offset & 15) == 0)
+            cuda_check(lb::launch_qgemv_i4_fast(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (l.b_dtype == LAPID_B200_DTYPE_INT4) cuda_check(lb::launch_qgemv_i4(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (l.b_dtype == LAPID_B200_DTYPE_MXFP4) cuda_check(lb::launch_qgemv_mxfp4(g, dev.sm_count, pdl, dev.stream), "qgemv launch");
         else if (is_iquant(l.b_dtype)) cuda_check(lb::launch_qgemv_iq(l.b_dtype, g, dev.sm_count, pdl, dev.stream), "qgemv launch");

@@ -272,6 +272,7 @@ cudaError_t launch_qgemv_kq_moe(int fmt, const GemvArgs &args, int sm_count, boo
 // ---- qgemv_i8.cu: fast path for Int8 planes (K % 512 == 0); reads the activation planes
 bool qgemv_i8_fast_shape_ok(uint32_t rows, uint32_t k);
 cudaError_t launch_qgemv_i8_fast(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);  // tuning: at most this many CTAs per SM (0 = as many as fit)
+cudaError_t launch_qgemv_i4_fast(const GemvArgs &args, int sm_count, bool pdl, cudaStream_t stream);  // Int4 nibble planes, same shapes
 
 // out[bt, i, j] = 0 (+ extra) for the k == 0 case (crates/lapid-cpu/src/matmul/mod.rs:237-247).
 cudaError_t launch_fill_zero_k(const GemvArgs &args, cudaStream_t stream);

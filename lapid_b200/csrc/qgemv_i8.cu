@@ -52,7 +52,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 // after the dependency wait; launched as one CTA per SM so that consecutive launches share the SMs
 // (see qgemv_q4k.cu).
 constexpr int PEND_ROWS = 32;  // parked results per warp
-template <int M, bool EARLY = false>
+// I4: the same kernel over Int4 nibble planes (GGUF Q4_0 in lapid's plane layout: 16 bytes per 32-element group, byte j =
+// element j in the low and element j + 16 in the high nibble, x = (q - 8) * d; crates/lapid-quant/src/lib.rs:5-17,
+// crates/lapid-cpu/src/qmat.rs:97-112). A stage holds the nibbles of the same 4096 weights (2048 bytes) and their
+// scales; a lane takes one whole group per step (16 bytes), turns each nibble into the int8 value 16 (q - 8) with two
+// logic operations per word (the nibble moved into the high half of its byte, its top bit flipped) and multiplies
+// with eight `dp4a`; the exact factor 1/16 goes into the scale.
+template <int M, bool EARLY = false, bool I4 = false>
 __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgemv_i8_fast_kernel(GemvArgs p) {
     static_assert(!EARLY || M == 1, "early mode is built for one row");
     constexpr int WARPS = Shape<M>::WARPS, THREADS = WARPS * 32, STAGES = 2;
@@ -81,8 +87,9 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
         if (lane == 0) {
             const uint32_t e0 = pc * CHUNK, len = min((uint32_t)CHUNK, k - e0);
             uint8_t *dst = ring + (size_t)pslot * STAGE;
-            mbar_expect_tx(bars + pslot, len + len / 16);
-            bulk_g2s(dst, p.w + (uint64_t)pt * k + e0, len, bars + pslot);
+            const uint32_t qbytes = I4 ? len / 2 : len;
+            mbar_expect_tx(bars + pslot, qbytes + len / 16);
+            bulk_g2s(dst, p.w + (I4 ? ((uint64_t)pt * k + e0) / 2 : (uint64_t)pt * k + e0), qbytes, bars + pslot);
             bulk_g2s(dst + CHUNK, p.w + p.scales_offset + ((uint64_t)pt * kg + e0 / GROUP) * 2, len / 16, bars + pslot);
         }
         pslot ^= 1;
@@ -134,7 +141,36 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
             }
             const uint32_t e0 = c * CHUNK, len = min((uint32_t)CHUNK, k - e0);
             const uint8_t *st = ring + (size_t)cslot * STAGE;
-            if (healthy) {
+            if (healthy && I4) {
+                for (uint32_t u = 0; u < len; u += 1024) {  // a group per lane: 1024 weights per warp step
+                    if (u + 32 * lane >= len) continue;      // (K is a multiple of 512: the last step may be half empty)
+                    const uint4 wq = *(const uint4 *)(st + (u >> 1) + 16 * lane);
+                    const float db = half_bits_to_float(*(const uint16_t *)(st + CHUNK + 2 * ((u >> 5) + lane))) * 0.0625f;
+                    const uint32_t kk = e0 + u + 32 * lane;  // first of this lane's 32 k
+                    const uint32_t w4[4] = {wq.x, wq.y, wq.z, wq.w};
+                    uint32_t lo[4], hi[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        lo[i] = ((w4[i] << 4) & 0xF0F0F0F0u) ^ 0x80808080u;  // 16 (q - 8), elements 4i .. 4i + 3
+                        hi[i] = (w4[i] & 0xF0F0F0F0u) ^ 0x80808080u;         // elements 16 + 4i ..
+                    }
+#pragma unroll
+                    for (int r = 0; r < M; r++) {
+                        const uint4 a0 = *(const uint4 *)(act_q + (size_t)r * k + kk), a1 = *(const uint4 *)(act_q + (size_t)r * k + kk + 16);
+                        const float da = act_d[(size_t)r * kg + (kk >> 5)];
+                        int dsum = __dp4a((int)lo[0], (int)a0.x, 0);
+                        dsum = __dp4a((int)lo[1], (int)a0.y, dsum);
+                        dsum = __dp4a((int)lo[2], (int)a0.z, dsum);
+                        dsum = __dp4a((int)lo[3], (int)a0.w, dsum);
+                        dsum = __dp4a((int)hi[0], (int)a1.x, dsum);
+                        dsum = __dp4a((int)hi[1], (int)a1.y, dsum);
+                        dsum = __dp4a((int)hi[2], (int)a1.z, dsum);
+                        dsum = __dp4a((int)hi[3], (int)a1.w, dsum);
+                        acc[r] = fmaf((float)dsum, da * db, acc[r]);
+                    }
+                }
+            }
+            if (healthy && !I4) {
                 for (uint32_t u = 0; u < len; u += 512) {
                     const uint4 wq = *(const uint4 *)(st + u + 16 * lane);
                     const float db = half_bits_to_float(*(const uint16_t *)(st + CHUNK + 2 * ((u >> 5) + (lane >> 1))));
@@ -186,11 +222,11 @@ __global__ void __launch_bounds__(Shape<M>::WARPS * 32, Shape<M>::MIN_CTAS) qgem
     }
 }
 
-template <int M, bool EARLY = false> static cudaError_t launch_m(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t stream) {
+template <int M, bool EARLY = false, bool I4 = false> static cudaError_t launch_m(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t stream) {
     if constexpr (M == 1 && !EARLY) {
-        if (pdl && a.early && !a.tp) return launch_m<M, true>(a, sm_count, pdl, stream);
+        if (pdl && a.early && !a.tp) return launch_m<M, true, I4>(a, sm_count, pdl, stream);
     }
-    auto kern = qgemv_i8_fast_kernel<M, EARLY>;
+    auto kern = qgemv_i8_fast_kernel<M, EARLY, I4>;
     constexpr int WARPS = Shape<M>::WARPS;
     const size_t smem = BAR_BYTES + (size_t)WARPS * 2 * STAGE + (size_t)a.rows * a.k + (size_t)a.rows * (a.k / GROUP) * 4 +
                         (EARLY ? (size_t)WARPS * PEND_ROWS * 4 : 0);
@@ -237,6 +273,21 @@ cudaError_t launch_qgemv_i8_fast(const GemvArgs &a, int sm_count, bool pdl, cuda
         case 6: return i8::launch_m<6>(a, sm_count, pdl, s);
         case 7: return i8::launch_m<7>(a, sm_count, pdl, s);
         case 8: return i8::launch_m<8>(a, sm_count, pdl, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+// The same for Int4 nibble planes (see the kernel): same shapes (qgemv_i8_fast_shape_ok).
+cudaError_t launch_qgemv_i4_fast(const GemvArgs &a, int sm_count, bool pdl, cudaStream_t s) {
+    switch (a.rows) {
+        case 1: return i8::launch_m<1, false, true>(a, sm_count, pdl, s);
+        case 2: return i8::launch_m<2, false, true>(a, sm_count, pdl, s);
+        case 3: return i8::launch_m<3, false, true>(a, sm_count, pdl, s);
+        case 4: return i8::launch_m<4, false, true>(a, sm_count, pdl, s);
+        case 5: return i8::launch_m<5, false, true>(a, sm_count, pdl, s);
+        case 6: return i8::launch_m<6, false, true>(a, sm_count, pdl, s);
+        case 7: return i8::launch_m<7, false, true>(a, sm_count, pdl, s);
+        case 8: return i8::launch_m<8, false, true>(a, sm_count, pdl, s);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -1449,3 +1449,42 @@ def test_gemv_mxfp4_tensor_core_decode_kernel(be, oracle):
             assert max_rel(got, ref) <= 2e-5, (m, n, k)
     finally:
         be.set_option("gemv_mxfp4_mma_rows", "3")
+
+
+def test_gemv_int4_bulk_copy_kernel(be, oracle):
+    """The bulk-copy decode kernel over Int4 nibble planes (K a multiple of 512; one row by default, every row count
+    with the tensor-core kernels switched off) against the oracle and against the plain streaming kernel: a K whose last
+    1024-weight step is half empty, several stages per row, ragged n, a bias, launches that run ahead of their
+    predecessor (a list of one-row launches), both ends of the 4-bit range."""
+    be.set_option("gemv_mma_rows", "0")
+    try:
+        seed = 2100
+        for (m, n, k, bias) in [(1, 77, 512, True), (1, 4096, 4096, False), (2, 513, 1536, False), (3, 100, 5632, True), (5, 33, 14336, False),
+                                (8, 300, 4096, False), (1, 9, 28672, False)]:
+            seed += 1
+            w = O.normal(seed, n * k, 0.05).reshape(n, k).copy()
+            w[0, :] = -1.0
+            w[0, ::32] = 0.0
+            qb = oracle.quantize(O.INT4, w.reshape(-1), n, k)
+            a = O.normal(seed + 50, m * k)
+            bv = O.normal(seed + 70, n) if bias else None
+            want, _ = oracle.matmul(O.INT4, a, qb, n, k, m=m, bias=bv)
+            got = run_matmul(be, lp.DType.Int4, a, qb, m, n, k, bias=bv)
+            be.set_option("gemv", "generic")
+            ref = run_matmul(be, lp.DType.Int4, a, qb, m, n, k, bias=bv)
+            be.set_option("gemv", "fast")
+            assert max_rel(got, want) <= 2e-5, (m, n, k, max_rel(got, want))
+            assert max_rel(ref, want) <= 2e-5, (m, n, k)
+        # a list of one-row launches: all but the first run ahead of their predecessor (early mode)
+        n, k = 1024, 4096
+        qbs = [oracle.quantize(O.INT4, O.normal(2150 + i, n * k, 0.05), n, k) for i in range(4)]
+        x = O.normal(2160, k)
+        bufs = [be.upload(x)] + [be.upload(q) for q in qbs] + [be.alloc(n * 4) for _ in range(4)]
+        ls = [matmul_launch(lp.DType.Int4, 1, n, k, inputs=(0, 1 + i), output=5 + i) for i in range(4)]
+        be.execute(ls, bufs)
+        for i in range(4):
+            want, _ = oracle.matmul(O.INT4, x, qbs[i], n, k, m=1)
+            assert max_rel(bufs[5 + i].download().view(np.float32), want) <= 2e-5, i
+    finally:
+        be.set_option("gemv_mma_rows", "2")
+        be.set_option("gemv", "fast")
