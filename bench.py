@@ -462,7 +462,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "clocks": sampler.summary(),
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": ao * 4, "d2h_bytes_per_step": oo * 4,
                 "ms_per_step": e2e_s * 1e3,
-                "calls_per_step": f"one execute_io: 16 writes, 16 launches in chunks of {args.e2e_chunk}, 16 reads (a chunk's adjacent transfers go as one copy; "
+                "calls_per_step": "one execute_io: 16 writes, 16 launches in " + (f"chunks of {args.e2e_chunk}" if args.e2e_chunk else "three chunks of about equal transfer bytes (the library's choice)") + ", 16 reads (a chunk's adjacent transfers go as one copy; "
                                   "uploads, launches and downloads of different chunks overlap); waits",
                 "three_calls": {"value": world * step_bytes / three_s / 1e9, "ms_per_step": three_s * 1e3,
                                 "calls_per_step": "write + execute(16 launches, waits) + download, one after the other"}},
@@ -1107,7 +1107,7 @@ def main():
     ap.add_argument("--experts", type=int, default=0, help="--case: MatMulId over a stack of this many matrices (0: a plain MatMul)")
     ap.add_argument("--slots", type=int, default=2, help="--case with --experts: experts per token")
     ap.add_argument("--opt", action="append", default=[], help="device option key=value (repeatable)")
-    ap.add_argument("--e2e-chunk", type=int, default=8, help="launches per chunk of the end-to-end step's pipelined call (0: the library picks)")
+    ap.add_argument("--e2e-chunk", type=int, default=0, help="launches per chunk of the end-to-end step's pipelined call (0: the library picks)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -241,7 +241,7 @@ LAPID_B200_API lapid_b200_status lapid_b200_execute_async(lapid_b200_device *dev
 
 /* One decode step with host buffers as ONE call: Backend::write of the step's inputs, Backend::execute and
  * Backend::read of its results (backend.rs:36-58), pipelined. The launches run in consecutive chunks of
- * `chunk_launches` (0: the library picks); every write is uploaded on a copy stream of its own just before the
+ * `chunk_launches` (0: the library picks up to three chunks that carry about the same number of transferred bytes); every write is uploaded on a copy stream of its own just before the
  * chunk that holds the launch it names (`launch`: the FIRST launch that reads what it brings), every read is
  * downloaded on a second copy stream right after the chunk that holds the launch it names (`launch`: the LAST launch
  * that writes what it takes), so that uploads, launches and downloads of different chunks overlap (the two copy

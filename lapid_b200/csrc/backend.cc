@@ -1248,8 +1248,32 @@ void execute_io_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, 
     if (n && !launches) fail("invalid_argument", "launches is NULL");
     if (nbuf && !buffers) fail("invalid_argument", "buffers is NULL");
     if ((n_writes && !writes) || (n_reads && !reads)) fail("invalid_argument", "writes or reads is NULL");
-    if (chunk == 0) chunk = n > 8 ? (n + 3) / 4 : (n > 1 ? (n + 1) / 2 : 1);
-    const size_t n_chunks = n ? (n + chunk - 1) / chunk : 0;
+    // Chunk boundaries: `chunk` launches each, or (0) up to three chunks holding about the same number of transferred
+    // bytes each, by the launches the transfers are tied to -- the first upload and the last download are the copies
+    // nothing hides, so neither the first nor the last chunk should carry most of the bytes.
+    std::vector<size_t> first_of;  // first launch of every chunk, then n
+    if (chunk) {
+        for (size_t f = 0; f < n; f += chunk) first_of.push_back(f);
+    } else if (n) {
+        std::vector<uint64_t> bytes_at(n, 0);
+        uint64_t total = 0;
+        for (size_t i = 0; i < n_writes; i++)
+            if (writes[i].launch < n) bytes_at[writes[i].launch] += writes[i].bytes, total += writes[i].bytes;
+        for (size_t i = 0; i < n_reads; i++)
+            if (reads[i].launch < n) bytes_at[reads[i].launch] += reads[i].bytes, total += reads[i].bytes;
+        const size_t want = n >= 6 && total >= (1u << 20) ? 3 : (n >= 2 && total >= (256u << 10) ? 2 : 1);
+        first_of.push_back(0);
+        uint64_t run = 0;
+        for (size_t i = 0; i + 1 < n && first_of.size() < want; i++) {
+            run += bytes_at[i];
+            if (run * want >= total * first_of.size()) first_of.push_back(i + 1);
+        }
+    }
+    const size_t n_chunks = first_of.size();
+    first_of.push_back(n);
+    std::vector<uint32_t> chunk_of(n, 0);
+    for (size_t c = 0; c < n_chunks; c++)
+        for (size_t i = first_of[c]; i < first_of[c + 1]; i++) chunk_of[i] = (uint32_t)c;
     auto check_io = [&](const lapid_b200_io &io, const char *what) {
         if (io.buffer >= nbuf || !buffers[io.buffer])
             fail("invalid_launch", std::string("execute_io: ") + what + " names buffer " + std::to_string(io.buffer) + " of " + std::to_string(nbuf));
@@ -1265,7 +1289,7 @@ void execute_io_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, 
     // later chunk may write what it takes.
     for (size_t i = 0; i < n_writes; i++) {
         check_io(writes[i], "write");
-        for (size_t j = 0; n && j < (writes[i].launch / chunk) * chunk; j++) {
+        for (size_t j = 0; n && j < first_of[chunk_of[writes[i].launch]]; j++) {
             uint64_t lo, hi;
             for (int in = 0; in < 2; in++)
                 if (launch_range(launches[j], writes[i].buffer, in != 0, buffers[writes[i].buffer]->bytes, lo, hi) && lo < writes[i].offset + writes[i].bytes &&
@@ -1276,7 +1300,7 @@ void execute_io_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, 
     }
     for (size_t i = 0; i < n_reads; i++) {
         check_io(reads[i], "read");
-        for (size_t j = (reads[i].launch / chunk + 1) * chunk; j < n; j++) {
+        for (size_t j = n ? first_of[chunk_of[reads[i].launch] + 1] : 0; j < n; j++) {
             uint64_t lo, hi;
             if (launch_range(launches[j], reads[i].buffer, false, buffers[reads[i].buffer]->bytes, lo, hi) && lo < reads[i].offset + reads[i].bytes &&
                 reads[i].offset < hi)
@@ -1312,7 +1336,7 @@ void execute_io_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, 
         auto copies_of = [&](const lapid_b200_io *ios, size_t count, size_t c) {
             std::vector<lapid_b200_io> v;
             for (size_t i = 0; i < count; i++)
-                if ((n ? ios[i].launch / chunk : 0) == c && ios[i].bytes) v.push_back(ios[i]);
+                if ((n ? chunk_of[ios[i].launch] : 0) == c && ios[i].bytes) v.push_back(ios[i]);
             std::sort(v.begin(), v.end(), [](const lapid_b200_io &a, const lapid_b200_io &b) {
                 return a.buffer != b.buffer ? a.buffer < b.buffer : a.offset < b.offset;
             });
@@ -1334,7 +1358,7 @@ void execute_io_impl(lapid_b200_device *dev, const lapid_b200_launch *launches, 
             if (n_chunks) cuda_check(cudaEventRecord(dev->io_events[2 * c], dev->io_in), "cudaEventRecord");
         }
         for (size_t c = 0; c < n_chunks; c++) {
-            const size_t first = c * chunk, count = first + chunk <= n ? chunk : n - first;
+            const size_t first = first_of[c], count = first_of[c + 1] - first;
             cuda_check(cudaStreamWaitEvent(dev->stream, dev->io_events[2 * c], 0), "cudaStreamWaitEvent");
             execute_locked(dev, launches + first, count, buffers, nbuf, false);
             cuda_check(cudaEventRecord(dev->io_events[2 * c + 1], dev->stream), "cudaEventRecord");
