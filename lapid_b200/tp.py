@@ -4,10 +4,10 @@ The reference has no multi-GPU code at all, so there is no interface to mirror; 
 is "the sum of the shards' results equals the unsharded result".
 
 * Column-parallel (q, k, v, gate, up): rank r owns weight rows ``[r*n/p, (r+1)*n/p)``. Rows of a
-  lapid-quant matrix are independent block runs, so a shard is a byte range (K formats) or a pair of
-  plane slices (Int8). No communication; the outputs stay sharded and feed the row-parallel op.
+  lapid-quant matrix are independent block runs, so a shard is a byte range (the block formats: K-quants,
+  MXFP4, i-quants) or a pair of plane slices (Int8, Int4). No communication; the outputs stay sharded and feed the row-parallel op.
 * Row-parallel (o, down): rank r owns columns ``[r*k/p, (r+1)*k/p)``; ``k/p`` must be a multiple of
-  256 (32 for Int8) so shards are whole blocks, bit-identical to the unsharded ones. Shards are
+  the format's block length (256; 32 for Int8, Int4 and MXFP4) so shards are whole blocks, bit-identical to the unsharded ones. Shards are
   repacked once, at load, into a contiguous ``[n, k/p]`` matrix. Every rank produces a partial
   ``[M, n]`` f32 result and the partials are summed by an all-reduce.
 
@@ -19,8 +19,17 @@ from dataclasses import dataclass
 
 import numpy as np
 
-INT8, Q4_K, Q6_K = 4, 6, 8
-_BLOCK = {Q4_K: (256, 144), Q6_K: (256, 210)}
+INT8, INT4, Q4_K, Q5_K, Q6_K, MXFP4 = 4, 5, 6, 7, 8, 9
+IQ2_XXS, IQ2_S, IQ3_XXS, IQ2_XS = 10, 11, 12, 13
+# array-of-structs formats: (elements, bytes) per block; Int8 and Int4 are planes of quants and f16 scales
+_BLOCK = {Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), MXFP4: (32, 17),
+          IQ2_XXS: (256, 66), IQ2_XS: (256, 74), IQ2_S: (256, 82), IQ3_XXS: (256, 98)}
+_PLANES = {INT8: 1.0, INT4: 0.5}   # bytes of quants per element
+
+
+def _known(fmt: int) -> None:
+    if fmt not in _BLOCK and fmt not in _PLANES:
+        raise ValueError(f"format {fmt} is not a quantized format of this backend")
 
 
 def _align(x: int, a: int = 256) -> int:
@@ -28,10 +37,11 @@ def _align(x: int, a: int = 256) -> int:
 
 
 def layout_total(fmt: int, n: int, k: int) -> int:
+    _known(fmt)
     if fmt in _BLOCK:
         be, bb = _BLOCK[fmt]
         return _align(n * (k // be) * bb)
-    return _align(_align(n * k) + n * (k // 32) * 2)
+    return _align(_align(int(n * k * _PLANES[fmt])) + n * (k // 32) * 2)
 
 
 def _is_torch(x) -> bool:
@@ -59,7 +69,8 @@ def check_divisible(fmt: int, n: int, k: int, world: int, kind: str) -> None:
         if n % world:
             raise ValueError(f"column-parallel: n = {n} is not divisible by {world} ranks")
     else:
-        unit = 32 if fmt == INT8 else 256
+        _known(fmt)
+        unit = _BLOCK[fmt][0] if fmt in _BLOCK else 32
         if k % (world * unit):
             raise ValueError(f"row-parallel: k = {k} must be a multiple of {world} x {unit}")
 
@@ -73,11 +84,13 @@ def shard_rows(fmt: int, q, n: int, k: int, rank: int, world: int):
         be, bb = _BLOCK[fmt]
         rb = (k // be) * bb
         return _pack([(0, q[r0 * rb:(r0 + nl) * rb])], layout_total(fmt, nl, k), q), nl
-    so = _align(n * k)
+    _known(fmt)
+    rb = int(k * _PLANES[fmt])   # bytes of quants per weight row (Int4: a group's 32 nibbles are 16 consecutive bytes)
+    so = _align(n * rb)
     kg = k // 32
-    quants = q[r0 * k:(r0 + nl) * k]
+    quants = q[r0 * rb:(r0 + nl) * rb]
     scales = q[so + r0 * kg * 2: so + (r0 + nl) * kg * 2]
-    return _pack([(0, quants), (_align(nl * k), scales)], layout_total(fmt, nl, k), q), nl
+    return _pack([(0, quants), (_align(nl * rb), scales)], layout_total(fmt, nl, k), q), nl
 
 
 def shard_cols(fmt: int, q, n: int, k: int, rank: int, world: int):
@@ -91,15 +104,17 @@ def shard_cols(fmt: int, q, n: int, k: int, rank: int, world: int):
         blocks = q[:n * nb * bb].reshape(n, nb, bb)[:, rank * nbl:(rank + 1) * nbl, :]
         blocks = blocks.contiguous() if _is_torch(blocks) else np.ascontiguousarray(blocks)
         return _pack([(0, blocks)], layout_total(fmt, n, kl), q), kl
-    so = _align(n * k)
+    _known(fmt)
+    rb, rbl = int(k * _PLANES[fmt]), int(kl * _PLANES[fmt])   # (shards are whole 32-element groups, so also whole bytes of Int4)
+    so = _align(n * rb)
     kg, kgl = k // 32, kl // 32
-    quants = q[:n * k].reshape(n, k)[:, rank * kl:(rank + 1) * kl]
+    quants = q[:n * rb].reshape(n, rb)[:, rank * rbl:(rank + 1) * rbl]
     scales = q[so:so + n * kg * 2].reshape(n, kg, 2)[:, rank * kgl:(rank + 1) * kgl, :]
     if _is_torch(q):
         quants, scales = quants.contiguous(), scales.contiguous()
     else:
         quants, scales = np.ascontiguousarray(quants), np.ascontiguousarray(scales)
-    return _pack([(0, quants), (_align(n * kl), scales)], layout_total(fmt, n, kl), q), kl
+    return _pack([(0, quants), (_align(n * rbl), scales)], layout_total(fmt, n, kl), q), kl
 
 
 # ---------------------------------------------------------------------------------------------

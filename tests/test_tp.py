@@ -10,6 +10,37 @@ from lapid_b200 import tp
 from oracle import oracle as O
 
 FMTS = [O.INT8, O.Q4_K, O.Q6_K]
+MORE = [O.INT4, O.Q5_K, O.MXFP4, O.IQ2_XXS, O.IQ2_XS, O.IQ2_S, O.IQ3_XXS]   # the formats beyond the benchmark's three
+
+
+@pytest.mark.parametrize("fmt", MORE)
+@pytest.mark.parametrize("world", [2, 4])
+def test_shards_of_the_other_formats(oracle, fmt, world):
+    """Every quantized format shards the same way: a column-parallel shard dequantizes to the rows, a row-parallel
+    shard to the columns of the unsharded matrix, bit for bit, and has the size the layout gives; the partial results of
+    the row-parallel shards add up to the unsharded result."""
+    from tests.refgen import iq_matrix
+    n, k = 24, 2048
+    q = iq_matrix(fmt, n, k, 40 + fmt) if fmt in O.IQUANTS else oracle.quantize(fmt, O.normal(5 + fmt, n * k, 0.02), n, k)
+    full = oracle.dequantize(fmt, q, n, k).reshape(n, k)
+    a = O.normal(60 + fmt, 3 * k).reshape(3, k)
+    want, _ = oracle.matmul(fmt, a, q, n, k, m=3)
+    total = np.zeros(3 * n, np.float32)
+    for rank in range(world):
+        qs, nl = tp.shard_rows(fmt, q, n, k, rank, world)
+        assert nl == n // world and qs.size == oracle.layout(fmt, nl, k).total == tp.layout_total(fmt, nl, k)
+        assert np.array_equal(oracle.dequantize(fmt, qs, nl, k).reshape(nl, k).view(np.uint32), full[rank * nl:(rank + 1) * nl].view(np.uint32))
+        qc, kl = tp.shard_cols(fmt, q, n, k, rank, world)
+        assert kl == k // world and qc.size == oracle.layout(fmt, n, kl).total
+        assert np.array_equal(oracle.dequantize(fmt, qc, n, kl).reshape(n, kl).view(np.uint32),
+                              np.ascontiguousarray(full[:, rank * kl:(rank + 1) * kl]).view(np.uint32))
+        total += oracle.matmul(fmt, np.ascontiguousarray(a[:, rank * kl:(rank + 1) * kl]), qc, n, kl, m=3)[0]
+    rms = float(np.sqrt((want.astype(np.float64) ** 2).mean()))
+    assert (np.abs(total - want) / np.maximum(np.abs(want), rms)).max() <= 1e-5
+    with pytest.raises(ValueError):
+        tp.shard_cols(fmt, q, n, k, 0, 128)
+    with pytest.raises(ValueError):
+        tp.layout_total(3, n, k)      # not a quantized format
 
 
 @pytest.mark.parametrize("fmt", FMTS)
