@@ -12,6 +12,13 @@ X3 = normal(seed 20, [3, 512]), X12 = normal(seed 21, [12, 512]):
   y3_<f>    matmul(X3, w)  -- int8-activation decode path (batch*m <= 8)
   y12_<f>   matmul(X12, w) -- f32 path with fused multiply-add accumulation
 plus the activation quantizer's output for X3: qa3 (int8), sa3 (f32 scales), bs3 (f32 sums).
+
+``tests/golden/iquant/`` is different: those files are golden bytes the reference itself holds for the grid-based
+i-quants (``crates/lapid-quant/tests/fixtures/iquant/``: blocks quantized and values dequantized by ggml, and the
+codebook file ``grids.bin``; made by the reference's ``tools/iquant_golden/gen.sh`` from the llama.cpp commit its
+``SOURCE`` file names). ``python tests/golden/make_golden.py --iquant <reference checkout>`` copies them byte for byte
+(``input.bin``, the quantizers' input, is not used here: the i-quant quantizers are not restated) and refreshes the
+copy of ``grids.bin`` the CUDA library embeds (``lapid_b200/csrc/iq_grids.bin``).
 """
 import os
 import sys
@@ -25,7 +32,21 @@ from oracle import oracle as O  # noqa: E402
 N, K = 24, 512
 
 
+def copy_iquant_fixtures(reference: str) -> None:
+    import shutil
+    src = os.path.join(reference, "crates", "lapid-quant", "tests", "fixtures", "iquant")
+    dst = os.path.join(ROOT, "tests", "golden", "iquant")
+    os.makedirs(dst, exist_ok=True)
+    for name in ("grids.bin", "iq2_xxs.bin", "iq2_xs.bin", "iq2_s.bin", "iq3_xxs.bin"):
+        shutil.copyfile(os.path.join(src, name), os.path.join(dst, name))
+    shutil.copyfile(os.path.join(src, "grids.bin"), os.path.join(ROOT, "lapid_b200", "csrc", "iq_grids.bin"))
+    print("copied the i-quant fixtures from", src)
+
+
 def main():
+    if len(sys.argv) >= 3 and sys.argv[1] == "--iquant":
+        copy_iquant_fixtures(sys.argv[2])
+        return
     o = O.load()
     out = {}
     x3 = O.normal(20, 3 * K).reshape(3, K)
